@@ -1,0 +1,384 @@
+#!/usr/bin/env python3
+"""Benchmark of the batched RWKV-7 forward step (decode), 3B shape, int8 weights.
+
+  python bench.py --gpus 1 --steps K --warmup W          # this repository's CUDA path
+  python bench.py --impl reference --steps K --warmup W  # the reference algorithm's fp32 CPU path (the oracle)
+
+One "step" = one decode step of `--batch` sessions per GPU (default 1: benchmark config 2, a 512-token
+prompt prefilled and then an arg-max self-loop).  Prints ONE JSON line.
+  value     decode tok/s summed over all GPUs, device-timed (CUDA events on the model's stream) with tokens
+            and state resident in HBM (GPU self-loop, no host round-trip)
+  e2e       the same metric through the host-buffer API: per step the tokens go host->device and the
+            logits come back device->host
+  roofline  the dominant kernel's algorithmic bytes / its mean device time, against the measured HBM peak
+  cpu_baseline  the CPU oracle timed on this box (bounded sample)
+Inputs are synthetic: seeded random-init weights of the named shape, uniform random prompt tokens.
+Every step streams all weights (3.1 GB at the 3B int8 shape), far more than the 126 MB L2, so no L2 flush
+is needed between timed iterations.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode_tokens_per_second"
+UNIT = "tok/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--shape", default="3b", choices=["tiny", "3b", "7b"])
+    ap.add_argument("--quant", default="int8", choices=["fp16", "int8"])
+    ap.add_argument("--batch", type=int, default=1, help="sessions per GPU")
+    ap.add_argument("--prompt", type=int, default=512, help="prompt tokens prefilled before decoding")
+    ap.add_argument("--sweep", default="1,8,64,256,1024", help="batch sizes of the decode sweep (N=1 only); '' disables it")
+    ap.add_argument("--sweep-steps", type=int, default=32)
+    ap.add_argument("--cpu-seconds", type=float, default=20.0, help="time budget of the CPU baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--model-dir", default=os.environ.get("RSV_BENCH_DIR", "/tmp/rsv_bench"))
+    return ap.parse_args()
+
+
+def model_path(args):
+    return os.path.join(args.model_dir, f"rwkv7_{args.shape}_{args.quant}_seed0.st")
+
+
+def ensure_model(args):
+    import rwkv_rsv_b200 as rsv
+    path = model_path(args)
+    if not os.path.exists(path):
+        os.makedirs(args.model_dir, exist_ok=True)
+        tmp = path + f".tmp{os.getpid()}"
+        rsv.write_synthetic(tmp, args.shape, seed=0, quant=1 if args.quant == "int8" else 0)
+        os.replace(tmp, path)
+    return path
+
+
+def shape_of(args):
+    import rwkv_rsv_b200 as rsv
+    return rsv.SHAPES[args.shape]
+
+
+def algorithmic_bytes(sh, quant, B):
+    """Dense algorithmic bytes of one decode step: every weight byte once, state read + written once per
+    session, the embedding row and the logits per session."""
+    L, C, F, V, H, N = sh["n_layer"], sh["n_embd"], sh["ffn_hidden"], sh["vocab"], sh["n_head"], sh["head_size"]
+    mids = sh["w_mid"] + sh["a_mid"] + sh["v_mid"] + sh["g_mid"]
+    big = L * (4 * C * C + 2 * C * F)
+    if quant == "int8":
+        w = big + big // 128 * 4
+    else:
+        w = big * 2
+    w += L * 2 * C * mids * 2 + L * 19 * C * 4 + V * C * 2
+    s_rw = 2 * L * H * N * N * 4 + 2 * L * 2 * C * 4
+    a = 2 * C + 2 * V * 4
+    return w + B * (s_rw + a), w
+
+
+def kernel_bytes(sh, quant, B):
+    """Algorithmic bytes of one launch of each weight-streaming kernel (weights once + activations in/out)."""
+    C, F, V = sh["n_embd"], sh["ffn_hidden"], sh["vocab"]
+    mids = sh["w_mid"] + sh["a_mid"] + sh["v_mid"] + sh["g_mid"]
+    wb = (lambda m, k: m * k + m * k // 128 * 4) if quant == "int8" else (lambda m, k: m * k * 2)
+    act = lambda n_in, n_out: 4 * B * (n_in + n_out)
+    return {
+        "linear_rkv_rank": 3 * wb(C, C) + C * mids * 2 + act(6 * C, 3 * C + mids),
+        "linear_rank_back": C * mids * 2 + act(mids, 4 * C),
+        "linear_att_out": wb(C, C) + act(C, 2 * C),
+        "linear_ffn_key": wb(F, C) + act(C, F),
+        "linear_ffn_value": wb(C, F) + act(F, 2 * C),
+        "linear_head": V * C * 2 + act(C, V),
+        "wkv7": B * (sh["n_head"] * 64 * 64 * 4 * 2 + 4 * 7 * C),
+    }
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=2)
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+                power.append(float(r[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "power_w_max": max(power) if power else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_baseline(path, sh, seconds, threads=None, prompt=8):
+    """Times the CPU oracle (fp32, the reference's algorithm) on a bounded sample of the same workload."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import orc
+    nthr = threads or (os.cpu_count() or 1)
+    orc.set_threads(nthr)
+    t0 = time.perf_counter()
+    m = orc.OracleModel(path)
+    load_s = time.perf_counter() - t0
+    rng = np.random.default_rng(1)
+    toks = rng.integers(0, sh["vocab"], size=prompt).astype(np.uint32)
+    m.forward(toks[:2])  # warm-up: page in the weights
+    tok, n, t0 = int(toks[-1]), 0, time.perf_counter()
+    while True:
+        tok = orc.argmax(m.forward([tok]))
+        n += 1
+        el = time.perf_counter() - t0
+        if (el >= seconds and n >= 3) or n >= 4096:
+            break
+    res = {"value": n / el, "unit": UNIT, "cores": nthr, "kind": "port",
+           "sample": f"{n} arg-max decode tokens of the same checkpoint after a {2}-token warm-up, fp32 CPU oracle, {nthr} OpenMP threads "
+                     f"(model load {load_s:.1f} s not timed)"}
+    m.close()
+    return res, m
+
+
+def run_reference(args):
+    """--impl reference: the reference algorithm's own CPU implementation (the fp32 oracle; the Rust crate
+    cannot be built in this image) on all host threads, same config and metric."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    path = ensure_model(args)
+    sh = shape_of(args)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import orc
+    nthr = os.cpu_count() or 1
+    orc.set_threads(nthr)
+    m = orc.OracleModel(path)
+    rng = np.random.default_rng(1)
+    tok = int(rng.integers(0, sh["vocab"]))
+    budget = 120.0
+    t_w = time.perf_counter()
+    for i in range(max(args.warmup, 1)):
+        tok = orc.argmax(m.forward([tok]))
+        if time.perf_counter() - t_w > budget / 4:
+            break
+    n, t0 = 0, time.perf_counter()
+    while n < args.steps:
+        tok = orc.argmax(m.forward([tok]))
+        n += 1
+        if time.perf_counter() - t0 > budget and n >= 3:
+            break
+    el = time.perf_counter() - t0
+    v = n / el
+    sample = f"{n} of the requested {args.steps} decode steps (time-bounded), batch 1, {nthr} OpenMP threads, oracle port of src/model.rs"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": n, "warmup": args.warmup,
+        "ms_per_step": 1000.0 * el / n, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args), "shape": args.shape, "weights": args.quant, "batch_per_gpu": 1},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": nthr, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_name(args):
+    return (f"RWKV-7 {args.shape} shape {args.quant}, random init seed 0: {args.prompt}-token uniform-random prompt prefill, then arg-max "
+            f"GPU self-loop decode, batch {args.batch} per GPU")
+
+
+def decode_run(rsv, model, state, seeds, steps):
+    """Queues `steps` self-loop rounds; returns device ms (CUDA events on the model's stream)."""
+    model.timer_start()
+    t = model.submit_sample_selfloop_batch(state, seeds, steps, None)
+    ms = model.timer_stop()
+    out = model.collect_sample_selfloop_batch(t)
+    return ms, out
+
+
+def prefix_states(rsv, model, B, prompt, vocab, rng):
+    """Per-slot prefix state: up to 8 distinct prompts are prefilled and their states tiled over the slots
+    (the state's content does not change the work of a decode step)."""
+    st = model.create_batch_state(B)
+    nd = min(B, 8)
+    small = model.create_batch_state(nd)
+    prompts = [rng.integers(0, vocab, size=prompt).astype(np.uint32) for _ in range(nd)]
+    seeds = model.forward_seq_batch(small, prompts)
+    per = [small.slot_back(i) for i in range(nd)]
+    for b in range(B):
+        st.slot_load(b, per[b % nd])
+    small.close()
+    return st, np.asarray([seeds[b % nd] for b in range(B)], dtype=np.uint32)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    import torch
+    import rwkv_rsv_b200 as rsv
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    sh = shape_of(args)
+    if rank == 0:
+        ensure_model(args)
+    if dist:
+        dist.barrier()
+    path = model_path(args)
+    B, K, W = args.batch, args.steps, max(args.warmup, 3)
+    rng = np.random.default_rng(1000 + rank)
+
+    model = rsv.Model(path, device=local)
+    state, seeds = prefix_states(rsv, model, B, args.prompt, sh["vocab"], rng)
+
+    # ---- device-resident decode: warm-up, then exactly K timed steps ----
+    decode_run(rsv, model, state, seeds, W)
+    clocks = ClockSampler(local)
+    clocks.start()
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    model.clear_kernel_prof()
+    ms, out = decode_run(rsv, model, state, seeds, K)
+    launches = model.launch_count()
+    torch.cuda.synchronize()
+    if dist:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clk = clocks.stop()
+    value = world * B * K / (ms / 1000.0)
+
+    # ---- end to end through the host-buffer API (batch 1: Bundle::infer_tokens per token) ----
+    e2e = None
+    if B == 1:
+        tok_pin = torch.zeros(1, dtype=torch.int32).pin_memory()
+        lg_pin = torch.zeros(sh["vocab"], dtype=torch.float32).pin_memory()
+        tok_np, lg_np = tok_pin.numpy().view(np.uint32), lg_pin.numpy()
+        lib = rsv.native()
+        tok_np[0] = int(out[0, -1])
+        import ctypes
+        tp, lp = ctypes.c_void_p(tok_pin.data_ptr()), ctypes.c_void_p(lg_pin.data_ptr())
+        for _ in range(W):
+            assert lib.rsv_infer_tokens(model._h, state._h, tp, 1, lp) == 0
+            tok_np[0] = int(lg_np.argmax())
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(K):
+            rc = lib.rsv_infer_tokens(model._h, state._h, tp, 1, lp)
+            tok_np[0] = int(lg_np.argmax())
+        torch.cuda.synchronize()
+        el = time.perf_counter() - t0
+        assert rc == 0
+        if dist:
+            t = torch.tensor([el], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            el = float(t.item())
+        e2e = {"value": world * K / el, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * sh["vocab"],
+               "api": "rsv_infer_tokens (Bundle::infer_tokens), one token in, logits out, host arg-max"}
+
+    result = None
+    if rank == 0:
+        # ---- per-kernel device time -> roofline of the dominant kernel ----
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        peak, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+        model.clear_kernel_prof()
+        model.prof_enable(True)
+        decode_run(rsv, model, state, seeds, min(K, 16))
+        model.prof_enable(False)
+        prof = model.kernel_prof()
+        tot = sum(v["ms"] for v in prof.values())
+        dom = max(prof.items(), key=lambda kv: kv[1]["ms"])
+        kb = kernel_bytes(sh, args.quant, B)
+        step_bytes, w_bytes = algorithmic_bytes(sh, args.quant, B)
+        dom_ms = dom[1]["ms"] / dom[1]["launches"]
+        achieved = kb.get(dom[0], 0) / (dom_ms / 1000.0) / 1e9
+        roofline = {"bound": "hbm", "kernel": dom[0], "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
+                    "traffic": None, "bytes_per_launch": kb.get(dom[0], 0), "ms_per_launch": dom_ms, "share_of_step": dom[1]["ms"] / tot,
+                    "step": {"bytes": step_bytes, "achieved": step_bytes / (ms / K / 1000.0) / 1e9,
+                             "frac": step_bytes / (ms / K / 1000.0) / 1e9 / peak},
+                    "kernels": {k: {"share": v["ms"] / tot, "us_per_launch": 1000.0 * v["ms"] / v["launches"],
+                                    "gbs": (kb[k] / (v["ms"] / v["launches"] / 1000.0) / 1e9) if k in kb else None} for k, v in prof.items()}}
+        result = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name(args), "shape": args.shape, "weights": args.quant, "batch_per_gpu": B, "prompt": args.prompt,
+                       "l2": "every step streams all weights (>> 126 MB L2); no flush needed", "sessions": "one full replica per GPU, no collective"},
+            "clocks": clk, "gpu_launches": launches, "e2e": e2e, "roofline": roofline,
+        }
+        # ---- decode batch sweep (benchmark config 4), single GPU only ----
+        if world == 1 and args.sweep:
+            sweep = {}
+            for b in [int(x) for x in args.sweep.split(",") if x]:
+                if b == B:
+                    sweep[str(b)] = {"tok_s": value, "ms_per_step": ms / K, "hbm_frac": roofline["step"]["frac"]}
+                    continue
+                st_b, seeds_b = prefix_states(rsv, model, b, min(args.prompt, 256), sh["vocab"], rng)
+                decode_run(rsv, model, st_b, seeds_b, 3)
+                ms_b, _ = decode_run(rsv, model, st_b, seeds_b, args.sweep_steps)
+                bts, _ = algorithmic_bytes(sh, args.quant, b)
+                sweep[str(b)] = {"tok_s": b * args.sweep_steps / (ms_b / 1000.0), "ms_per_step": ms_b / args.sweep_steps,
+                                 "hbm_frac": bts / (ms_b / args.sweep_steps / 1000.0) / 1e9 / peak}
+                st_b.close()
+            result["batch_sweep"] = sweep
+    state.close()
+    model.close()
+    if rank == 0:
+        if not args.no_cpu_baseline and world == 1:
+            result["cpu_baseline"], _ = cpu_baseline(path, sh, args.cpu_seconds)
+        elif not args.no_cpu_baseline:
+            result["cpu_baseline"] = None
+        print(json.dumps(result))
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,603 @@
+// Engine implementation: checkpoint loading, HBM layout, work buffers, the packed forward step.
+#include "engine.hpp"
+
+#include <algorithm>
+#include <cstring>
+
+#include "kernels.cuh"
+#include "safetensors.hpp"
+
+namespace rsv {
+
+// ------------------------------------------------------------------------------------------------
+// launch bookkeeping: every kernel goes through LAUNCH so that it is counted and, when profiling is
+// on, timed with a CUDA event pair on the model's stream (PROF_CUDA_KERNEL in the reference,
+// src/backend_cuda.rs:412-460).
+// ------------------------------------------------------------------------------------------------
+struct LaunchScope {
+    Model& m;
+    const char* name;
+    LaunchScope(Model& m_, const char* n) : m(m_), name(n) {
+        if (m.prof_on) cudaEventRecord(m.ev0, m.stream);
+    }
+    ~LaunchScope() {
+        ++m.launches;
+        if (m.prof_on) {
+            cudaEventRecord(m.ev1, m.stream);
+            cudaEventSynchronize(m.ev1);
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, m.ev0, m.ev1);
+            auto& p = m.prof[name];
+            p.ms += ms;
+            p.launches += 1;
+        }
+    }
+};
+#define LAUNCH(model, name) if (LaunchScope _ls{model, name}; true)
+
+static void check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) throw CudaError(std::string("kernel launch failed (") + what + "): " + cudaGetErrorString(e));
+}
+
+// ------------------------------------------------------------------------------------------------
+// loading
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+std::vector<float> to_f32(const StTensor& t) {
+    std::vector<float> out((size_t)t.numel());
+    if (t.dtype == "F32") {
+        if (t.nbytes != out.size() * 4) throw std::runtime_error("tensor byte size mismatch");
+        memcpy(out.data(), t.data, t.nbytes);
+    } else if (t.dtype == "F16") {
+        if (t.nbytes != out.size() * 2) throw std::runtime_error("tensor byte size mismatch");
+        const uint16_t* h = (const uint16_t*)t.data;
+        for (size_t i = 0; i < out.size(); ++i) out[i] = half_bits_to_float(h[i]);
+    } else {
+        throw std::runtime_error("unsupported dtype " + t.dtype + " (need F16 or F32)");  // src/model.rs:208-217
+    }
+    return out;
+}
+
+std::vector<uint16_t> to_f16_bits(const StTensor& t) {
+    std::vector<uint16_t> out((size_t)t.numel());
+    if (t.dtype == "F16") {
+        memcpy(out.data(), t.data, out.size() * 2);
+    } else if (t.dtype == "F32") {
+        const float* f = (const float*)t.data;
+        for (size_t i = 0; i < out.size(); ++i) out[i] = float_to_half_bits(f[i]);
+    } else {
+        throw std::runtime_error("unsupported dtype " + t.dtype + " (need F16 or F32)");
+    }
+    return out;
+}
+
+struct Loader {
+    Model& m;
+    const SafeTensorsFile& st;
+
+    void* dev_alloc(size_t bytes) {
+        void* p = nullptr;
+        RSV_CUDA(cudaMalloc(&p, std::max<size_t>(bytes, 16)));
+        m.allocs.push_back(p);
+        m.weight_bytes += bytes;
+        return p;
+    }
+    void* upload(const void* src, size_t bytes) {
+        void* p = dev_alloc(bytes);
+        RSV_CUDA(cudaMemcpy(p, src, bytes, cudaMemcpyHostToDevice));
+        return p;
+    }
+    float* vec(const std::string& key, size_t expect) {
+        std::vector<float> v = to_f32(st.get(key));
+        if (v.size() != expect) throw std::runtime_error(key + ": expected " + std::to_string(expect) + " elements, file has " + std::to_string(v.size()));
+        return (float*)upload(v.data(), v.size() * 4);
+    }
+    // [out,in] matrix: int8 pair if `{key}.int8_idx` exists (as src/gpu_model.rs:3438-3441), else fp16.
+    LinearW linear(const std::string& key, int M, int K) {
+        LinearW L;
+        L.M = M;
+        L.K = K;
+        if (st.has(key + ".int8_idx")) {
+            const StTensor& it = st.get(key + ".int8_idx");
+            const StTensor& zt = st.get(key + ".int8_sz");
+            if (K % 128) throw std::runtime_error(key + ": int8 needs K % 128 == 0");
+            if (it.dtype != "U8" || it.nbytes != (size_t)M * K) throw std::runtime_error(key + ".int8_idx: expected U8 [" + std::to_string(M) + "," + std::to_string(K) + "]");
+            if (zt.dtype != "U32" || zt.nbytes != (size_t)M * (K / 128) * 4) throw std::runtime_error(key + ".int8_sz: expected U32 [M, K/128]");
+            L.wtype = W_INT8;
+            L.w = upload(it.data, it.nbytes);
+            L.sz = (uint32_t*)upload(zt.data, zt.nbytes);
+        } else {
+            const StTensor& t = st.get(key);
+            if (t.numel() != (int64_t)M * K) throw std::runtime_error(key + ": shape mismatch");
+            if (K % 8) throw std::runtime_error(key + ": fp16 needs K % 8 == 0");
+            L.wtype = W_F16;
+            if (t.dtype == "F16") {
+                L.w = upload(t.data, t.nbytes);
+            } else {
+                auto h = to_f16_bits(t);
+                L.w = upload(h.data(), h.size() * 2);
+            }
+        }
+        return L;
+    }
+    // Low-rank pair member.  The file holds either [in,out] or [out,in] (src/model.rs:564-581 accepts
+    // both, first match wins when in == out); HBM always holds [out,in] fp16.
+    LinearW lowrank(const std::string& key, int in_dim, int out_dim) {
+        const StTensor& t = st.get(key);
+        if (t.shape.size() != 2) throw std::runtime_error(key + ": expected a 2-D tensor");
+        std::vector<uint16_t> h = to_f16_bits(t);
+        std::vector<uint16_t> oi((size_t)in_dim * out_dim);
+        if (t.shape[0] == in_dim && t.shape[1] == out_dim) {
+            for (int i = 0; i < in_dim; ++i)
+                for (int o = 0; o < out_dim; ++o) oi[(size_t)o * in_dim + i] = h[(size_t)i * out_dim + o];
+        } else if (t.shape[0] == out_dim && t.shape[1] == in_dim) {
+            oi = h;
+        } else {
+            throw std::runtime_error(key + ": unexpected shape, want [" + std::to_string(in_dim) + "," + std::to_string(out_dim) + "] or its transpose");
+        }
+        if (in_dim % 8) throw std::runtime_error(key + ": inner dimension must be a multiple of 8");
+        LinearW L;
+        L.M = out_dim;
+        L.K = in_dim;
+        L.wtype = W_F16;
+        L.w = upload(oi.data(), oi.size() * 2);
+        return L;
+    }
+};
+
+}  // namespace
+
+std::unique_ptr<Model> Model::load(const std::string& path, int device) {
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0)
+        throw CudaError(std::string("no CUDA device available (") + cudaGetErrorString(e) + "): this library has no CPU fallback");
+    if (device < 0 || device >= ndev) throw std::runtime_error("device index out of range");
+    RSV_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    RSV_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) throw std::runtime_error("this library is built for sm_100a (B200) only; device is sm_" + std::to_string(prop.major) + std::to_string(prop.minor));
+
+    SafeTensorsFile st(path);
+    auto m = std::make_unique<Model>();
+    m->device = device;
+    Config& c = m->cfg;
+    // hyper-parameters come from tensor shapes only (src/gpu_model.rs:406-444)
+    int max_layer = -1;
+    for (auto& kv : st.tensors()) {
+        const std::string& k = kv.first;
+        if (k.rfind("blocks.", 0) == 0) {
+            size_t p = k.find('.', 7);
+            if (p != std::string::npos) {
+                bool digits = p > 7;
+                for (size_t i = 7; i < p; ++i) digits = digits && k[i] >= '0' && k[i] <= '9';
+                if (digits) max_layer = std::max(max_layer, std::stoi(k.substr(7, p - 7)));
+            }
+        }
+    }
+    if (max_layer < 0) throw std::runtime_error("no blocks.* tensors in checkpoint");
+    c.n_layer = max_layer + 1;
+    const StTensor& emb = st.get("emb.weight");
+    if (emb.shape.size() != 2) throw std::runtime_error("emb.weight must be 2-D");
+    c.vocab = (int)emb.shape[0];
+    c.n_embd = (int)emb.shape[1];
+    const StTensor& rk = st.get("blocks.0.att.r_k");
+    if (rk.shape.size() != 2) throw std::runtime_error("blocks.0.att.r_k must be [H,N]");
+    c.n_head = (int)rk.shape[0];
+    c.head_size = (int)rk.shape[1];
+    auto mid_of = [&](const char* k) {
+        const StTensor& t = st.get(k);
+        if (t.shape.size() != 2) throw std::runtime_error(std::string(k) + " must be 2-D");
+        return (int)(t.shape[0] == c.n_embd ? t.shape[1] : t.shape[0]);
+    };
+    c.w_mid = mid_of("blocks.0.att.w1");
+    c.a_mid = mid_of("blocks.0.att.a1");
+    c.v_mid = mid_of("blocks.0.att.v1");
+    c.g_mid = mid_of("blocks.0.att.g1");
+    c.ffn_hidden = (int)(st.has("blocks.0.ffn.key.weight") ? st.get("blocks.0.ffn.key.weight").shape.at(0)
+                                                            : st.get("blocks.0.ffn.key.weight.int8_idx").shape.at(0));
+    if (c.head_size != kHeadSize) throw std::runtime_error("head_size must be 64");
+    if (c.n_head * c.head_size != c.n_embd) throw std::runtime_error("n_head * head_size != n_embd");
+    if (c.n_embd % 8 || c.ffn_hidden % 8) throw std::runtime_error("n_embd and ffn_hidden must be multiples of 8");
+
+    RSV_CUDA(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+    RSV_CUDA(cudaEventCreate(&m->ev0));
+    RSV_CUDA(cudaEventCreate(&m->ev1));
+    RSV_CUDA(cudaEventCreate(&m->tev[0]));
+    RSV_CUDA(cudaEventCreate(&m->tev[1]));
+
+    Loader ld{*m, st};
+    const int C = c.n_embd, F = c.ffn_hidden;
+    {
+        auto h = to_f16_bits(emb);
+        m->emb = (__half*)ld.upload(h.data(), h.size() * 2);
+    }
+    m->ln0_w = ld.vec("blocks.0.ln0.weight", C);
+    m->ln0_b = ld.vec("blocks.0.ln0.bias", C);
+    m->ln_out_w = ld.vec("ln_out.weight", C);
+    m->ln_out_b = ld.vec("ln_out.bias", C);
+    m->head = ld.linear("head.weight", c.vocab, C);
+    m->layers.resize(c.n_layer);
+    for (int i = 0; i < c.n_layer; ++i) {
+        const std::string p = "blocks." + std::to_string(i) + ".";
+        LayerW& L = m->layers[i];
+        L.ln1_w = ld.vec(p + "ln1.weight", C);
+        L.ln1_b = ld.vec(p + "ln1.bias", C);
+        L.ln2_w = ld.vec(p + "ln2.weight", C);
+        L.ln2_b = ld.vec(p + "ln2.bias", C);
+        L.lnx_w = ld.vec(p + "att.ln_x.weight", C);
+        L.lnx_b = ld.vec(p + "att.ln_x.bias", C);
+        L.x_r = ld.vec(p + "att.x_r", C);
+        L.x_w = ld.vec(p + "att.x_w", C);
+        L.x_k = ld.vec(p + "att.x_k", C);
+        L.x_v = ld.vec(p + "att.x_v", C);
+        L.x_a = ld.vec(p + "att.x_a", C);
+        L.x_g = ld.vec(p + "att.x_g", C);
+        L.ffn_x_k = ld.vec(p + "ffn.x_k", C);
+        L.w0 = ld.vec(p + "att.w0", C);
+        L.a0 = ld.vec(p + "att.a0", C);
+        L.v0 = ld.vec(p + "att.v0", C);
+        L.r_k = ld.vec(p + "att.r_k", C);
+        L.k_k = ld.vec(p + "att.k_k", C);
+        L.k_a = ld.vec(p + "att.k_a", C);
+        L.Wr = ld.linear(p + "att.receptance.weight", C, C);
+        L.Wk = ld.linear(p + "att.key.weight", C, C);
+        L.Wv = ld.linear(p + "att.value.weight", C, C);
+        L.Wo = ld.linear(p + "att.output.weight", C, C);
+        L.Wfk = ld.linear(p + "ffn.key.weight", F, C);
+        L.Wfv = ld.linear(p + "ffn.value.weight", C, F);
+        L.w1 = ld.lowrank(p + "att.w1", C, c.w_mid);
+        L.w2 = ld.lowrank(p + "att.w2", c.w_mid, C);
+        L.a1 = ld.lowrank(p + "att.a1", C, c.a_mid);
+        L.a2 = ld.lowrank(p + "att.a2", c.a_mid, C);
+        L.v1 = ld.lowrank(p + "att.v1", C, c.v_mid);
+        L.v2 = ld.lowrank(p + "att.v2", c.v_mid, C);
+        L.g1 = ld.lowrank(p + "att.g1", C, c.g_mid);
+        L.g2 = ld.lowrank(p + "att.g2", c.g_mid, C);
+    }
+    m->pinned_bytes = 1 << 20;
+    RSV_CUDA(cudaMallocHost(&m->pinned, m->pinned_bytes));
+    RSV_CUDA(cudaMalloc(&m->ws.status, sizeof(int)));
+    RSV_CUDA(cudaMalloc(&m->ws.tok_pos, sizeof(int)));
+    RSV_CUDA(cudaMemset(m->ws.status, 0, sizeof(int)));
+    RSV_CUDA(cudaMemset(m->ws.tok_pos, 0, sizeof(int)));
+    return m;
+}
+
+static void free_workspace(Workspace& w) {
+    void* ptrs[] = {w.x, w.xmix, w.r, w.k, w.v, w.w, w.a, w.g, w.yg, w.xb, w.mid, w.h, w.vfirst, w.xn, w.logits, w.staging, w.tokens, w.row_meta, w.seg_meta, w.out_rows, w.samp_temp, w.samp_cnt};
+    for (void* p : ptrs)
+        if (p) cudaFree(p);
+    int* status = w.status;
+    int* pos = w.tok_pos;
+    uint32_t* tl = w.tok_list;
+    size_t tlc = w.tok_list_cap;
+    w = Workspace{};
+    w.status = status;
+    w.tok_pos = pos;
+    w.tok_list = tl;
+    w.tok_list_cap = tlc;
+}
+
+Model::~Model() {
+    cudaSetDevice(device);
+    if (stream) cudaStreamSynchronize(stream);
+    free_workspace(ws);
+    if (ws.status) cudaFree(ws.status);
+    if (ws.tok_pos) cudaFree(ws.tok_pos);
+    if (ws.tok_list) cudaFree(ws.tok_list);
+    for (void* p : allocs) cudaFree(p);
+    if (pinned) cudaFreeHost(pinned);
+    if (ev0) cudaEventDestroy(ev0);
+    if (ev1) cudaEventDestroy(ev1);
+    if (tev[0]) cudaEventDestroy(tev[0]);
+    if (tev[1]) cudaEventDestroy(tev[1]);
+    if (stream) cudaStreamDestroy(stream);
+}
+
+State::~State() {
+    if (model) cudaSetDevice(model->device);
+    for (float* p : {tmix_x, wkv, cmix_x, v_first})
+        if (p) cudaFree(p);
+}
+
+void Model::ensure_workspace(int rows, int outs, int segs) {
+    if (rows <= ws.rows && outs <= ws.outs && segs <= ws.segs) return;
+    RSV_CUDA(cudaStreamSynchronize(stream));
+    rows = std::max(rows, ws.rows);
+    outs = std::max(outs, ws.outs);
+    segs = std::max(segs, ws.segs);
+    free_workspace(ws);
+    const size_t C = cfg.n_embd, F = cfg.ffn_hidden, V = cfg.vocab, R = rows;
+    auto fa = [&](float*& p, size_t n) { RSV_CUDA(cudaMalloc(&p, std::max<size_t>(n, 4) * sizeof(float))); };
+    fa(ws.x, R * C);
+    fa(ws.xmix, 6 * R * C);
+    fa(ws.r, R * C);
+    fa(ws.k, R * C);
+    fa(ws.v, R * C);
+    fa(ws.w, R * C);
+    fa(ws.a, R * C);
+    fa(ws.g, R * C);
+    fa(ws.yg, R * C);
+    fa(ws.xb, R * C);
+    fa(ws.mid, R * (size_t)cfg.mids());
+    fa(ws.h, R * F);
+    fa(ws.vfirst, R * C);
+    fa(ws.xn, (size_t)outs * C);
+    fa(ws.logits, (size_t)outs * V);
+    fa(ws.staging, (size_t)segs * C);
+    fa(ws.samp_temp, (size_t)outs * V);
+    RSV_CUDA(cudaMalloc(&ws.samp_cnt, std::max<size_t>((size_t)outs * V, 4) * sizeof(uint32_t)));
+    RSV_CUDA(cudaMalloc(&ws.tokens, R * sizeof(uint32_t)));
+    RSV_CUDA(cudaMemset(ws.tokens, 0, R * sizeof(uint32_t)));
+    RSV_CUDA(cudaMalloc(&ws.row_meta, R * sizeof(RowMeta)));
+    RSV_CUDA(cudaMalloc(&ws.seg_meta, (size_t)segs * sizeof(SegMeta)));
+    RSV_CUDA(cudaMalloc(&ws.out_rows, (size_t)std::max(outs, 1) * sizeof(int)));
+    ws.rows = rows;
+    ws.outs = outs;
+    ws.segs = segs;
+    const size_t need = R * sizeof(RowMeta) + (size_t)segs * sizeof(SegMeta) + (size_t)outs * sizeof(int) + R * sizeof(uint32_t) + 256;
+    if (need > pinned_bytes) {
+        cudaFreeHost(pinned);
+        pinned = nullptr;
+        pinned_bytes = need * 2;
+        RSV_CUDA(cudaMallocHost(&pinned, pinned_bytes));
+    }
+}
+
+void Model::upload_plan(const StepPlan& plan) {
+    const int R = (int)plan.rows.size(), S = (int)plan.segs.size(), O = (int)plan.out_rows.size();
+    ensure_workspace(R, std::max(O, 1), S);
+    // the pinned staging buffer is reused: the previous step's copies must have been issued AND consumed
+    RSV_CUDA(cudaStreamSynchronize(stream));
+    char* p = (char*)pinned;
+    memcpy(p, plan.rows.data(), R * sizeof(RowMeta));
+    RSV_CUDA(cudaMemcpyAsync(ws.row_meta, p, R * sizeof(RowMeta), cudaMemcpyHostToDevice, stream));
+    p += R * sizeof(RowMeta);
+    memcpy(p, plan.segs.data(), S * sizeof(SegMeta));
+    RSV_CUDA(cudaMemcpyAsync(ws.seg_meta, p, S * sizeof(SegMeta), cudaMemcpyHostToDevice, stream));
+    p += S * sizeof(SegMeta);
+    if (O) {
+        memcpy(p, plan.out_rows.data(), O * sizeof(int));
+        RSV_CUDA(cudaMemcpyAsync(ws.out_rows, p, O * sizeof(int), cudaMemcpyHostToDevice, stream));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// linear launch helper
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+struct LinReq {
+    const LinearW* W;
+    const float* x;
+    int ldx;
+    float* y;
+    int ldy;
+    int epi;
+    const float* bias = nullptr;
+    const float* aux = nullptr;
+    int ldaux = 0;
+    float* y2 = nullptr;
+};
+
+template <int RT>
+void launch_linear_rt(Model& m, const LinGroup& g, int nblk, int R, size_t smem) {
+    static bool configured[8] = {false};
+    int dev = m.device & 7;
+    if (!configured[dev]) {
+        RSV_CUDA(cudaFuncSetAttribute(linear_rows_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        configured[dev] = true;
+    }
+    dim3 grid(nblk, (R + RT - 1) / RT);
+    linear_rows_kernel<RT><<<grid, kLinWarps * 32, smem, m.stream>>>(g, R);
+    check_launch("linear_rows");
+}
+
+void run_linear(Model& m, const char* name, const LinReq* reqs, int n, int R) {
+    LinGroup g;
+    memset(&g, 0, sizeof(g));
+    g.n = n;
+    int total_rows = 0, kmax = 0;
+    bool any_i8 = false;
+    for (int i = 0; i < n; ++i) {
+        total_rows += reqs[i].W->M;
+        kmax = std::max(kmax, reqs[i].W->K);
+        any_i8 = any_i8 || reqs[i].W->wtype == W_INT8;
+    }
+    // rows per CTA: aim for a few waves over 148 SMs, but amortise the x staging
+    const int unit = kLinWarps * kLinWR;
+    int rpb = (total_rows / (148 * 4)) / unit * unit;
+    rpb = std::min(std::max(rpb, unit), 8 * unit);
+    int blk = 0;
+    for (int i = 0; i < n; ++i) {
+        const LinReq& q = reqs[i];
+        LinProb& P = g.p[i];
+        P.w = q.W->w;
+        P.sz = q.W->sz;
+        P.x = q.x;
+        P.y = q.y;
+        P.y2 = q.y2;
+        P.bias = q.bias;
+        P.aux = q.aux;
+        P.M = q.W->M;
+        P.K = q.W->K;
+        P.ldx = q.ldx;
+        P.ldy = q.ldy;
+        P.ldaux = q.ldaux;
+        P.wtype = q.W->wtype;
+        P.epi = q.epi;
+        P.rows_per_blk = rpb;
+        P.blk0 = blk;
+        blk += (P.M + rpb - 1) / rpb;
+    }
+    auto smem_for = [&](int rt) { return (size_t)rt * kmax * 4 + (any_i8 ? (size_t)rt * (kmax / 16) * 4 : 0); };
+    int rt = R >= 4 ? 4 : (R >= 2 ? 2 : 1);
+    while (rt > 1 && smem_for(rt) > 200 * 1024) rt >>= 1;
+    if (smem_for(rt) > 200 * 1024) throw std::runtime_error("linear: inner dimension too large for the shared-memory tile");
+    LAUNCH(m, name) {
+        if (rt == 4)
+            launch_linear_rt<4>(m, g, blk, R, smem_for(4));
+        else if (rt == 2)
+            launch_linear_rt<2>(m, g, blk, R, smem_for(2));
+        else
+            launch_linear_rt<1>(m, g, blk, R, smem_for(1));
+    }
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------------
+// the packed forward step (one token per row), Appendix-style data flow of src/model.rs:396-516
+// ------------------------------------------------------------------------------------------------
+void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
+    const int R = (int)plan.rows.size(), S = (int)plan.segs.size(), O = (int)plan.out_rows.size();
+    const int C = cfg.n_embd, H = cfg.n_head, F = cfg.ffn_hidden, V = cfg.vocab, MIDS = cfg.mids();
+    if (R == 0) return;
+    RSV_CUDA(cudaSetDevice(device));
+    const size_t RC = (size_t)R * C;
+    float* xm[6];
+    for (int i = 0; i < 6; ++i) xm[i] = ws.xmix + i * RC;  // order: r, w, k, v, a, g
+    float* staging = plan.multi_row_segments ? ws.staging : nullptr;
+
+    LAUNCH(*this, "embed_ln0") {
+        embed_ln0_kernel<<<R, kRowThreads, 0, stream>>>(emb, ln0_w, ln0_b, use_cursor ? ws.tok_list : ws.tokens, use_cursor ? ws.tok_pos : nullptr, R, C, V,
+                                                        ws.x, ws.status);
+        check_launch("embed_ln0");
+    }
+    const size_t lay_x = (size_t)st.cap * C, lay_s = (size_t)st.cap * H * kHeadSize * kHeadSize;
+    for (int l = 0; l < cfg.n_layer; ++l) {
+        const LayerW& L = layers[l];
+        float* tmix_x = st.tmix_x + l * lay_x;
+        float* cmix_x = st.cmix_x + l * lay_x;
+        float* wkv = st.wkv + l * lay_s;
+        LAUNCH(*this, "ln_shift6") {
+            MixPtrs mp{{L.x_r, L.x_w, L.x_k, L.x_v, L.x_a, L.x_g}};
+            ln_shift_kernel<6><<<R, kRowThreads, 0, stream>>>(ws.x, L.ln1_w, L.ln1_b, mp, ws.row_meta, R, C, tmix_x, staging, ws.xmix);
+            check_launch("ln_shift6");
+        }
+        if (staging) LAUNCH(*this, "commit_shift") {
+                commit_shift_kernel<<<S, 256, 0, stream>>>(staging, ws.seg_meta, C, tmix_x);
+                check_launch("commit_shift");
+            }
+        {
+            // r, k, v and the four rank-space projections in one launch
+            float* mw = ws.mid;
+            float* ma = mw + cfg.w_mid;
+            float* mv = ma + cfg.a_mid;
+            float* mg = mv + cfg.v_mid;
+            LinReq q[7] = {
+                {&L.Wr, xm[0], C, ws.r, C, EPI_STORE},
+                {&L.Wk, xm[2], C, ws.k, C, EPI_STORE},
+                {&L.Wv, xm[3], C, ws.v, C, EPI_STORE, nullptr, nullptr, 0, l == 0 ? ws.vfirst : nullptr},
+                {&L.w1, xm[1], C, mw, MIDS, EPI_TANH},
+                {&L.a1, xm[4], C, ma, MIDS, EPI_STORE},
+                {&L.g1, xm[5], C, mg, MIDS, EPI_SIGMOID},
+                {&L.v1, xm[3], C, mv, MIDS, EPI_STORE},
+            };
+            run_linear(*this, "linear_rkv_rank", q, l == 0 ? 6 : 7, R);
+            LinReq q2[4] = {
+                {&L.w2, mw, MIDS, ws.w, C, EPI_DECAY, L.w0},
+                {&L.a2, ma, MIDS, ws.a, C, EPI_SIGMOID_BIAS, L.a0},
+                {&L.g2, mg, MIDS, ws.g, C, EPI_STORE},
+                {&L.v2, mv, MIDS, ws.v, C, EPI_VLERP, L.v0, ws.vfirst, C},
+            };
+            run_linear(*this, "linear_rank_back", q2, l == 0 ? 3 : 4, R);
+        }
+        LAUNCH(*this, "wkv7") {
+            wkv7_kernel<<<dim3(H, S), kHeadSize, 0, stream>>>(ws.seg_meta, ws.r, ws.k, ws.v, ws.w, ws.a, ws.g, L.k_k, L.k_a, L.r_k, L.lnx_w, L.lnx_b, wkv,
+                                                              l == 0 ? st.v_first : nullptr, ws.yg, H, C);
+            check_launch("wkv7");
+        }
+        {
+            LinReq q = {&L.Wo, ws.yg, C, ws.x, C, EPI_ADD};
+            run_linear(*this, "linear_att_out", &q, 1, R);
+        }
+        LAUNCH(*this, "ln_shift1") {
+            MixPtrs mp{{L.ffn_x_k, nullptr, nullptr, nullptr, nullptr, nullptr}};
+            ln_shift_kernel<1><<<R, kRowThreads, 0, stream>>>(ws.x, L.ln2_w, L.ln2_b, mp, ws.row_meta, R, C, cmix_x, staging, ws.xb);
+            check_launch("ln_shift1");
+        }
+        if (staging) LAUNCH(*this, "commit_shift") {
+                commit_shift_kernel<<<S, 256, 0, stream>>>(staging, ws.seg_meta, C, cmix_x);
+                check_launch("commit_shift");
+            }
+        {
+            LinReq q = {&L.Wfk, ws.xb, C, ws.h, F, EPI_RELU2};
+            run_linear(*this, "linear_ffn_key", &q, 1, R);
+            LinReq q2 = {&L.Wfv, ws.h, F, ws.x, C, EPI_ADD};
+            run_linear(*this, "linear_ffn_value", &q2, 1, R);
+        }
+    }
+    if (O) {
+        LAUNCH(*this, "ln_out") {
+            ln_rows_kernel<<<O, kRowThreads, 0, stream>>>(ws.x, ln_out_w, ln_out_b, ws.out_rows, C, ws.xn);
+            check_launch("ln_out");
+        }
+        LinReq q = {&head, ws.xn, C, ws.logits, V, EPI_STORE};
+        run_linear(*this, "linear_head", &q, 1, O);
+    }
+    if (use_cursor) LAUNCH(*this, "advance_cursor") {
+            advance_cursor_kernel<<<1, 1, 0, stream>>>(ws.tok_pos);
+            check_launch("advance_cursor");
+        }
+}
+
+void Model::check_status() {
+    int s = 0;
+    RSV_CUDA(cudaMemcpyAsync(&s, ws.status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    RSV_CUDA(cudaStreamSynchronize(stream));
+    if (s) {
+        RSV_CUDA(cudaMemsetAsync(ws.status, 0, sizeof(int), stream));
+        if (s & 1) throw std::runtime_error("token id out of range (>= vocab); the embedding row 0 was used instead");
+        throw std::runtime_error("device status word = " + std::to_string(s));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// helpers used by the C ABI
+// ------------------------------------------------------------------------------------------------
+void engine_argmax(Model& m, const float* logits_dev, int rows, uint32_t* next_tok_dev, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap) {
+    LAUNCH(m, "argmax") {
+        argmax_rows_kernel<<<rows, kArgmaxThreads, 0, m.stream>>>(logits_dev, m.cfg.vocab, next_tok_dev, seq_dev, seq_cnt_dev, seq_cap);
+        check_launch("argmax");
+    }
+}
+
+void engine_sample(Model& m, const float* logits_dev, int rows, const float* sampler8_dev, const uint32_t* hist_dev, int hist_stride,
+                   const int* round_cnt_dev, uint32_t* next_tok_dev, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap) {
+    if (rows > m.ws.outs) throw std::runtime_error("engine_sample: more rows than the work area holds");
+    LAUNCH(m, "sample") {
+        sample_rows_kernel<<<rows, kSampleThreads, 0, m.stream>>>(logits_dev, m.cfg.vocab, sampler8_dev, hist_dev, hist_stride, round_cnt_dev, m.ws.samp_temp,
+                                                                  m.ws.samp_cnt, next_tok_dev, seq_dev, seq_cnt_dev, seq_cap);
+        check_launch("sample");
+    }
+}
+
+void engine_sample_raw(cudaStream_t stream, const float* logits_dev, int rows, int V, const float* sampler8_dev, const uint32_t* hist_dev,
+                       int hist_stride, float* temp_dev, uint32_t* counter_dev, uint32_t* out_dev) {
+    sample_rows_kernel<<<rows, kSampleThreads, 0, stream>>>(logits_dev, V, sampler8_dev, hist_dev, hist_stride, nullptr, temp_dev, counter_dev, out_dev,
+                                                            nullptr, nullptr, 0);
+    check_launch("sample");
+}
+
+Ticket::~Ticket() {
+    if (model) cudaSetDevice(model->device);
+    if (seq) cudaFree(seq);
+    if (cnt) cudaFree(cnt);
+    if (sampler) cudaFree(sampler);
+}
+
+void engine_argmax_raw(cudaStream_t stream, const float* logits_dev, int rows, int V, uint32_t* out_dev) {
+    argmax_rows_kernel<<<rows, kArgmaxThreads, 0, stream>>>(logits_dev, V, out_dev, nullptr, nullptr, 0);
+    check_launch("argmax");
+}
+
+void engine_dequant_int8(cudaStream_t stream, const uint8_t* idx_dev, const uint32_t* sz_dev, size_t M, size_t K, float* out_dev) {
+    dequant_int8_kernel<<<148 * 8, 256, 0, stream>>>(idx_dev, sz_dev, M, K, out_dev);
+    check_launch("dequant_int8");
+}
+
+}  // namespace rsv

@@ -1,0 +1,133 @@
+// Host-side engine: weights in HBM, session state, work buffers and the forward step over packed rows.
+// Replaces, for the batched RWKV-7 forward step, the reference's GpuModel dispatch graph
+// (src/gpu_model.rs:401-546, 868-1803, 1968-2543, 2911-3568) and its CudaBackend
+// (src/backend_cuda.rs).  One host thread drives one Model; all work goes to the model's stream.
+#pragma once
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace rsv {
+
+struct Config {
+    int n_layer = 0, n_embd = 0, vocab = 0, head_size = 0, n_head = 0, ffn_hidden = 0;
+    int w_mid = 0, a_mid = 0, v_mid = 0, g_mid = 0;
+    int mids() const { return w_mid + a_mid + v_mid + g_mid; }
+    size_t state_floats_per_slot() const {
+        return (size_t)n_layer * (2 * (size_t)n_embd + (size_t)n_head * head_size * head_size) + (size_t)n_embd;
+    }
+};
+
+// One weight matrix in HBM, row-major [M,K] = [out,in] exactly as stored in the checkpoint.
+struct LinearW {
+    int M = 0, K = 0, wtype = W_F16;
+    void* w = nullptr;         // fp16 [M,K] or u8 [M,K]
+    uint32_t* sz = nullptr;    // int8: [M,K/128] (fp16 scale | fp16 zero << 16), the reference container
+    size_t bytes() const { return wtype == W_INT8 ? (size_t)M * K + (size_t)M * (K / 128) * 4 : (size_t)M * K * 2; }
+};
+
+struct LayerW {
+    float *ln1_w, *ln1_b, *ln2_w, *ln2_b, *lnx_w, *lnx_b;
+    float *x_r, *x_w, *x_k, *x_v, *x_a, *x_g, *ffn_x_k;
+    float *w0, *a0, *v0, *r_k, *k_k, *k_a;
+    LinearW Wr, Wk, Wv, Wo, Wfk, Wfv;
+    LinearW w1, a1, v1, g1;  // rank-space projections, stored [mid, C] fp16
+    LinearW w2, a2, v2, g2;  // back-projections, stored [C, mid] fp16
+};
+
+struct Workspace {
+    int rows = 0, outs = 0, segs = 0;  // capacities
+    float *x = nullptr, *xmix = nullptr, *r = nullptr, *k = nullptr, *v = nullptr, *w = nullptr, *a = nullptr, *g = nullptr;
+    float *yg = nullptr, *xb = nullptr, *mid = nullptr, *h = nullptr, *vfirst = nullptr, *xn = nullptr, *logits = nullptr, *staging = nullptr;
+    float* samp_temp = nullptr;      // [outs, V] sampler work area
+    uint32_t* samp_cnt = nullptr;    // [outs, V] penalty histogram
+    uint32_t* tokens = nullptr;    // [rows] input token of every row (device-resident between self-loop rounds)
+    uint32_t* tok_list = nullptr;  // token cursor mode: [tok_list_cap]
+    size_t tok_list_cap = 0;
+    RowMeta* row_meta = nullptr;
+    SegMeta* seg_meta = nullptr;
+    int* out_rows = nullptr;
+    int* status = nullptr;   // bit 0: token id out of range
+    int* tok_pos = nullptr;  // cursor into tok_list
+};
+
+struct KernelProf {
+    double ms = 0;
+    long launches = 0;
+};
+
+struct Model;
+
+// Session state: per layer tmix_x[cap,C], wkv[cap,H,N,N], cmix_x[cap,C], plus v_first[cap,C]
+// (src/gpu_model.rs:194-199, 3915-3963).  fp32 on the device, so back/load round-trips bit-exactly.
+struct State {
+    Model* model = nullptr;
+    int64_t cap = 0;
+    float *tmix_x = nullptr, *wkv = nullptr, *cmix_x = nullptr, *v_first = nullptr;
+    ~State();
+};
+
+// A packed step: R rows grouped into segments (one per session present in the step).
+struct StepPlan {
+    std::vector<RowMeta> rows;
+    std::vector<SegMeta> segs;
+    std::vector<int> out_rows;  // rows whose logits are wanted (may be empty)
+    bool multi_row_segments = false;
+};
+
+enum class PostOp { None, Argmax };
+
+struct Model {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    Config cfg;
+    __half* emb = nullptr;
+    float *ln0_w = nullptr, *ln0_b = nullptr, *ln_out_w = nullptr, *ln_out_b = nullptr;
+    LinearW head;
+    std::vector<LayerW> layers;
+    std::vector<void*> allocs;  // every weight allocation, freed in the destructor
+    size_t weight_bytes = 0;
+    Workspace ws;
+    // pinned staging for per-step metadata
+    void* pinned = nullptr;
+    size_t pinned_bytes = 0;
+    // profiling (clear_kernel_prof / dump_kernel_prof of the reference, src/gpu_model.rs:561-570)
+    bool prof_on = false;
+    std::map<std::string, KernelProf> prof;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr, tev[2] = {nullptr, nullptr};
+    long launches = 0;  // kernels launched since the counter was last cleared
+
+    static std::unique_ptr<Model> load(const std::string& path, int device);
+    ~Model();
+
+    void ensure_workspace(int rows, int outs, int segs);
+    void upload_plan(const StepPlan& plan);
+    // Runs one packed step.  Input tokens are read from ws.tokens[r] (or ws.tok_list[*tok_pos * R + r] when
+    // `use_cursor`).  With out_rows non-empty, logits land in ws.logits[o, V] in out_rows order.
+    void forward_rows(State& st, const StepPlan& plan, bool use_cursor);
+    void check_status();
+};
+
+// Device-side products of a queued self-loop (SelfloopTicket, src/gpu_model.rs:204-212).
+struct Ticket {
+    Model* model = nullptr;
+    int64_t batch = 0, n = 0;
+    uint32_t* seq = nullptr;   // [batch, n] generated tokens
+    int* cnt = nullptr;        // [batch] tokens generated so far per slot
+    float* sampler = nullptr;  // [batch, 8] sampler rows (null for arg-max)
+    ~Ticket();
+};
+
+// launch wrappers defined next to the kernels
+void engine_argmax(Model& m, const float* logits_dev, int rows, uint32_t* next_tok_dev, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap);
+void engine_sample(Model& m, const float* logits_dev, int rows, const float* sampler8_dev, const uint32_t* hist_dev, int hist_stride,
+                   const int* round_cnt_dev, uint32_t* next_tok_dev, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap);
+void engine_argmax_raw(cudaStream_t stream, const float* logits_dev, int rows, int V, uint32_t* out_dev);
+void engine_sample_raw(cudaStream_t stream, const float* logits_dev, int rows, int V, const float* sampler8_dev, const uint32_t* hist_dev,
+                       int hist_stride, float* temp_dev, uint32_t* counter_dev, uint32_t* out_dev);
+void engine_dequant_int8(cudaStream_t stream, const uint8_t* idx_dev, const uint32_t* sz_dev, size_t M, size_t K, float* out_dev);
+
+}  // namespace rsv

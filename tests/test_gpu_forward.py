@@ -1,0 +1,238 @@
+"""GPU parity of the forward step against the CPU oracle, through the reference-shaped API
+(ModelBuilder / Bundle / State), which calls the C ABI.
+
+Tolerances (as the benchmark's north star states them): int8 dequant and state round-trip bit-exact,
+arg-max token streams identical, logits within an RMSE of 1e-3 of the fp32 CPU path.
+"""
+import os
+
+import numpy as np
+import pytest
+
+import orc
+import rwkv_rsv_b200 as rsv
+from conftest import GOLDEN, config1_tokens
+
+pytestmark = pytest.mark.gpu
+RMSE_TOL = 1e-3
+
+
+def rmse(a, b):
+    return float(np.sqrt(np.mean((np.asarray(a, dtype=np.float64) - np.asarray(b, dtype=np.float64)) ** 2)))
+
+
+@pytest.fixture(scope="module")
+def bundles(tiny_paths):
+    return {k: rsv.ModelBuilder(p).build() for k, p in tiny_paths.items()}
+
+
+@pytest.fixture(scope="module")
+def oracles(tiny_paths):
+    return {k: orc.OracleModel(p) for k, p in tiny_paths.items()}
+
+
+def test_model_info(bundles):
+    i = bundles["fp16"].info()
+    assert (i.version, i.num_layer, i.num_emb, i.num_hidden, i.num_vocab, i.num_head, i.head_size, i.ffn_hidden) == ("V7", 4, 512, 512, 4096, 8, 64, 2048)
+    assert (i.w_mid, i.a_mid, i.v_mid, i.g_mid) == (32, 32, 16, 64)
+    assert bundles["int8"].model.weight_bytes() < bundles["fp16"].model.weight_bytes()
+
+
+@pytest.mark.parametrize("name", ["fp16", "int8", "int8g"])
+def test_decode_logits_and_state_vs_oracle_and_golden(bundles, oracles, name):
+    b, o = bundles[name], oracles[name]
+    toks = config1_tokens()
+    b.reset()
+    o.reset()
+    lg = b.infer_tokens(toks)
+    want = o.forward(toks)
+    g = np.load(os.path.join(GOLDEN, f"tiny_{name}.npz"))
+    assert np.array_equal(want, g["logits"])
+    assert rmse(lg, want) <= RMSE_TOL and rmse(lg, want) <= 1e-3 * float(want.std())
+    assert int(lg.argmax()) == int(want.argmax())
+    sg, so = b.state_back(), o.state_back()
+    assert sg.shape == so.shape
+    assert np.abs(sg - so).max() <= 1e-4 * max(1.0, float(np.abs(so).max()))
+
+
+@pytest.mark.parametrize("name", ["fp16", "int8"])
+def test_argmax_stream_identical_config1(bundles, name):
+    # benchmark config 1: 128 prompt tokens, then 64 arg-max tokens from the GPU self-loop
+    b = bundles[name]
+    g = np.load(os.path.join(GOLDEN, f"tiny_{name}.npz"))
+    b.reset()
+    b.infer_seq(g["tokens"])
+    stream = b.infer_argmax_selfloop(int(g["tokens"][-1]), 64)
+    assert list(stream) == list(g["stream"]), f"first divergence at {int(np.argmax(stream != g['stream']))}, oracle top-2 gaps {g['top2_gap'][:8]}"
+
+
+def test_teacher_forced_top1_agreement(bundles, oracles):
+    # the reference's own check (src/main.rs:378-446): per-position arg-max with the oracle's tokens forced
+    b, o = bundles["int8"], oracles["int8"]
+    toks = config1_tokens()[:48]
+    b.reset()
+    o.reset()
+    full = b.infer(rsv.RnnInput(toks, 0, rsv.RnnOption.Full)).reshape(len(toks), -1)
+    want = o.forward(toks, full=True)
+    assert np.array_equal(full.argmax(1), want.argmax(1))
+    assert rmse(full, want) <= RMSE_TOL
+
+
+@pytest.mark.parametrize("name", ["fp16", "int8g"])
+def test_seq_chunked_and_token_paths_agree(bundles, oracles, name):
+    b, o = bundles[name], oracles[name]
+    toks = config1_tokens()[:77]
+    o.reset()
+    want = o.forward(toks)
+    outs = {}
+    b.reset()
+    outs["tokens"] = b.infer_tokens(toks)
+    s_tok = b.state_back()
+    b.reset()
+    outs["seq"] = b.infer_seq(toks)
+    s_seq = b.state_back()
+    b.reset()
+    outs["chunk16"] = b.infer_chunked(toks, 16)
+    b.reset()
+    outs["chunk1"] = b.infer_chunked(toks, 1)
+    b.reset()
+    b.infer_seq(toks[:30])
+    outs["split"] = b.infer_tokens(toks[30:])
+    for k, v in outs.items():
+        assert rmse(v, want) <= RMSE_TOL, k
+        assert int(v.argmax()) == int(want.argmax()), k
+    assert np.abs(s_tok - s_seq).max() <= 1e-4
+
+
+def test_state_roundtrip_bit_exact_and_reset(bundles):
+    # examples/state_persist.rs:54-67: back -> load -> back must give max_diff == 0
+    b = bundles["int8"]
+    toks = config1_tokens()
+    b.reset()
+    b.infer_seq(toks[:40])
+    s = b.state_back()
+    cont = b.infer_tokens(toks[40:48])
+    s_after = b.state_back()
+    b.reset()
+    z = b.state_back()
+    assert not z.any()
+    b.state_load(s)
+    assert np.array_equal(b.state_back().view(np.uint32), s.view(np.uint32))
+    again = b.infer_tokens(toks[40:48])
+    assert np.array_equal(again.view(np.uint32), cont.view(np.uint32))        # deterministic kernels: same bits
+    assert np.array_equal(b.state_back().view(np.uint32), s_after.view(np.uint32))
+    with pytest.raises(rsv.RsvError, match="length"):
+        b.state_load(s[:-1])
+
+
+def test_argmax_and_sample_entry_points(bundles, oracles):
+    b, o = bundles["fp16"], oracles["fp16"]
+    toks = config1_tokens()[:20]
+    b.reset()
+    o.reset()
+    want = o.forward(toks)
+    assert b.infer_argmax(toks) == int(want.argmax())
+    b.reset()
+    sp = rsv.SamplerParams(temperature=0.8, top_k=0, top_p=0.9, seed=1234)
+    hist = [1, 2, 3]
+    got = b.infer_sample(toks, sp, hist)
+    assert got == orc.sample(want, history=hist, temperature=0.8, top_p=0.9, seed=1234)
+    # top_k = 1 is arg-max whatever the seed
+    b.reset()
+    assert b.infer_sample(toks, rsv.SamplerParams(top_k=1, seed=99)) == int(want.argmax())
+
+
+def test_sample_selfloop_follows_oracle(bundles, oracles):
+    # round r: RNG seed = seed_token + r, history = the r tokens generated so far (src/gpu_model.rs:790-810)
+    b, o = bundles["int8"], oracles["int8"]
+    toks = config1_tokens()[:32]
+    sp = rsv.SamplerParams(temperature=1.0, top_p=0.9, repetition_penalty=1.1)
+    b.reset()
+    o.reset()
+    b.infer_seq(toks)
+    o.forward(toks)
+    seed, n = int(toks[-1]), 24
+    got = b.infer_sample_selfloop(seed, n, sp)
+    tok, want = seed, []
+    for r in range(n):
+        lg = o.forward([tok])
+        tok = orc.sample(lg, history=want, temperature=1.0, top_p=0.9, repetition_penalty=1.1, seed=(seed + r) & 0xFFFFFFFF)
+        want.append(tok)
+    assert list(got) == want
+
+
+def test_batch_equals_single(bundles, tiny_paths):
+    # batch == single equivalence, the reference's gemv_variant_mb / rkv_stage1_batch / sample_batch tests
+    # (src/backend_cuda.rs:7919, 8074, 8195) at the level of whole sessions
+    b = bundles["int8"]
+    m = b.model
+    rng = np.random.default_rng(4)
+    prompts = [rng.integers(0, 4096, size=n).astype(np.uint32) for n in (5, 17, 1, 64, 33)]
+    B, n = len(prompts), 12
+    singles, states = [], []
+    for p in prompts:
+        b.reset()
+        b.infer_seq(p)
+        singles.append(b.infer_argmax_selfloop(int(p[-1]), n))
+        states.append(b.state_back())
+    st = m.create_batch_state(B)
+    seeds = m.forward_seq_batch(st, prompts)
+    assert list(seeds) == [int(p[-1]) for p in prompts]
+    out = m.collect_sample_selfloop_batch(m.submit_sample_selfloop_batch(st, seeds, n, None))
+    for i in range(B):
+        assert list(out[i]) == list(singles[i]), i
+        assert np.abs(st.slot_back(i) - states[i]).max() <= 1e-4
+    # slot_load / slot_back round trip and whole-state layout = slots concatenated
+    whole = st.back()
+    per = len(whole) // B
+    assert np.array_equal(whole[2 * per:3 * per], st.slot_back(2))
+    st.slot_load(1, states[3])
+    assert np.array_equal(st.slot_back(1), states[3])
+    with pytest.raises(rsv.RsvError, match="slot"):
+        st.slot_back(B)
+    # sampling in a batch: slot b uses seeds[b] + round as its RNG seed, like the single-session loop
+    sp = rsv.SamplerParams(top_p=0.9)
+    st2 = m.create_batch_state(2)
+    m.forward_seq_batch(st2, prompts[:2])
+    got = m.collect_sample_selfloop_batch(m.submit_sample_selfloop_batch(st2, [int(prompts[0][-1]), int(prompts[1][-1])], 8, sp))
+    for i in range(2):
+        b.reset()
+        b.infer_seq(prompts[i])
+        assert list(b.infer_sample_selfloop(int(prompts[i][-1]), 8, sp)) == list(got[i])
+
+
+def test_error_paths(bundles, tiny_paths):
+    b = bundles["fp16"]
+    with pytest.raises(rsv.RsvError, match="vocab"):
+        b.infer_tokens([5, 4096])
+    with pytest.raises(rsv.RsvError, match="empty"):
+        b.infer_tokens([])
+    st = b.model.create_batch_state(3)
+    with pytest.raises(rsv.RsvError, match="batch"):
+        b.model.submit_sample_selfloop_batch(st, [1, 2], 4, None)
+    with pytest.raises(rsv.RsvError):
+        rsv.ModelBuilder(tiny_paths["fp16"] + ".missing").build()
+    b.reset()
+    assert b.infer_tokens([7]).shape == (4096,)       # the handle is still usable after errors
+
+
+def test_lowrank_transposed_and_quantised_head_checkpoints(model_dir, bundles):
+    # the loader accepts both low-rank orientations (src/model.rs:564-581) and an int8 head
+    # (tools/quantize_any4.py:696-712)
+    p = rsv.write_synthetic(os.path.join(model_dir, "tiny_t.st"), "tiny", seed=0, quant=2, lowrank_transposed=True, quant_head=True)
+    b, o = rsv.ModelBuilder(p).build(), orc.OracleModel(p)
+    toks = config1_tokens()[:24]
+    lg, want = b.infer_seq(toks), o.forward(toks)
+    assert rmse(lg, want) <= RMSE_TOL and int(lg.argmax()) == int(want.argmax())
+
+
+def test_kernel_profile_and_launch_count(bundles):
+    b = bundles["fp16"]
+    b.reset()
+    b.clear_kernel_prof()
+    b.model.prof_enable(True)
+    b.infer_tokens([1, 2, 3])
+    b.model.prof_enable(False)
+    prof = b.model.kernel_prof()
+    assert prof["wkv7"]["launches"] == 3 * 4 and prof["linear_head"]["launches"] == 1
+    assert b.model.launch_count() == sum(v["launches"] for v in prof.values())
