@@ -1,0 +1,481 @@
+// Weight-streaming linear layers on the 5th-generation tensor cores (sm_100a): TMA -> shared memory ->
+// tcgen05.mma -> TMEM.  Replaces, for many rows at once, the reference's dequant-to-scratch + cuBLAS GEMM +
+// separate epilogue pass (rwkv_dequant_int8, cublasGemmEx, rwkv_gemm_epilogue; src/backend_cuda.rs:4195-4227,
+// 1254-1368, 4613-4633) and its register-tiled batched GEMVs (gemv_variant_mb, gemv_int8_rkv_stage1_batch;
+// :3381-3554, :1665-1910).
+//
+// Arithmetic.  The weights are never converted: the u8 codes q of the int8 container are the A operand of
+// `tcgen05.mma.kind::i8` exactly as they sit in HBM (row-major [M,K], K contiguous).  An activation row x is
+// turned once into D signed base-128 digits of a fixed-point value t = rint(x / e * 2^P), e = 2^ceil(log2 max|x|),
+// P = 7D-1, which form D columns of the B operand (int8, [N,K], K contiguous).  The tensor core returns the exact
+// int32 sums I_j = sum_k q_k d_jk; Q = sum_j 128^(D-1-j) I_j = sum_k q_k t_k exactly (int64), and with the per-row
+// (scale s_m, zero z_m) of the container  y = e 2^-P (s_m Q + z_m T),  T = sum_k t_k, which is
+// sum_k (s_m q_k + z_m) x_k up to the 2^-P fixed-point step of x — no accumulation rounding at all, and any
+// split of K across CTAs sums exactly, so results do not depend on the schedule.  This needs one (scale, zero)
+// per output row; checkpoints whose groups of 128 differ within a row take the SIMT kernel instead.
+// fp16 weights use `kind::f16` with x/e split into hi + lo halves (two B columns), fp32 accumulation in TMEM.
+//
+// Work decomposition.  A unit is one (128-row M tile, N tile, 128-byte K block) = 16 KB of weights.  Units are
+// ordered problem -> M tile -> N tile -> K block and cut into equal contiguous ranges, one per CTA (persistent,
+// one CTA per SM), so every SM streams the same number of bytes whatever the matrix shape.  Each maximal run of
+// units inside one tile accumulates in TMEM and is written as an int32/fp32 partial [slot][n][m]; a second small
+// kernel adds a tile's partials in slot order, applies scale/zero and the fused epilogue.
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2-5 = epilogue.
+// Every wait on an mbarrier is bounded; on expiry the kernel raises bit 1 of the status word and drains.
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace rsv {
+
+constexpr int kTcThreads = 192;
+constexpr int kTcTileM = 128;
+constexpr int kTcKBlockBytes = 128;
+constexpr int kTcMaxProblems = 8;
+constexpr uint32_t kTcSpinLimit = 1u << 26;  // ~ seconds; far beyond any legitimate wait
+
+struct TcProb {
+    int M;        // output rows (weights rows)
+    int kblocks;  // K in 128-byte blocks
+    int ncols;    // valid B columns
+    int n_tiles;  // ceil(ncols / nt)
+    int unit0;    // first unit of this problem
+    int tile0;    // first (M tile, N tile) index of this problem in the partial buffer
+};
+struct alignas(64) TcLaunch {
+    CUtensorMap amap[kTcMaxProblems];
+    CUtensorMap bmap[kTcMaxProblems];
+    TcProb p[kTcMaxProblems];
+    int nprob, total_units, nt, is_i8, pmax, nstages;
+    void* partials;  // [tile][pmax][nt][128] int32 or fp32
+    int* status;
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false (and leaves `*abort_flag` set) when the limit is hit or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < kTcSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+                 "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+template <bool I8>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (I8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+          "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the 128-byte swizzle
+// the TMA applies: 8-row groups are 1024 bytes apart (SBO), layout type 2, descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                    // leading byte offset (unused with swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                    // version
+    d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D format (1 = f32, 2 = s32) bits [4,6); A format [7,10); B format [10,13);
+// A/B K-major (bits 15,16 = 0); N>>3 at [17,23); M>>4 at [24,29).
+__device__ __forceinline__ uint32_t tc_idesc(bool i8, int n) {
+    uint32_t d = i8 ? ((2u << 4) | (0u << 7) | (1u << 10)) : ((1u << 4) | (0u << 7) | (0u << 10));  // i8: A u8, B s8; f16: A,B f16
+    d |= (uint32_t)(n >> 3) << 17;
+    d |= (uint32_t)(kTcTileM >> 4) << 24;
+    return d;
+}
+
+struct TcUnit {
+    int p, mt, nt, kb, tile;  // problem, M tile, N tile, K block, global tile index
+};
+__device__ __forceinline__ TcUnit tc_decode(const TcLaunch& L, int u) {
+    int p = 0;
+    while (p + 1 < L.nprob && u >= L.p[p + 1].unit0) ++p;
+    const TcProb& P = L.p[p];
+    const int local = u - P.unit0;
+    TcUnit r;
+    r.p = p;
+    r.kb = local % P.kblocks;
+    const int t = local / P.kblocks;
+    r.nt = t % P.n_tiles;
+    r.mt = t / P.n_tiles;
+    r.tile = P.tile0 + t;
+    return r;
+}
+// CTA c owns units [c*U/G, (c+1)*U/G).  Partial slot of a run = how many CTA boundaries lie inside the tile before it.
+__host__ __device__ __forceinline__ int tc_cta_begin(int c, int U, int G) { return (int)(((long long)c * U) / G); }
+__host__ __device__ __forceinline__ int tc_cta_of_unit(int u, int U, int G) { return (int)((((long long)u + 1) * G - 1) / U); }
+
+template <bool I8>
+__global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_constant__ TcLaunch L) {
+    extern __shared__ __align__(1024) uint8_t tc_smem_raw[];
+    // carve: stages (1024-aligned), then barriers
+    uint8_t* smem = (uint8_t*)(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    const int NT = L.nt, NS = L.nstages;
+    const uint32_t a_bytes = kTcTileM * kTcKBlockBytes, b_bytes = (uint32_t)NT * kTcKBlockBytes, stage_bytes = a_bytes + b_bytes;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)NS * stage_bytes);
+    uint64_t* empty = full + NS;
+    uint64_t* acc_full = empty + NS;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = gridDim.x, U = L.total_units;
+    const int u_begin = tc_cta_begin(blockIdx.x, U, G), u_end = tc_cta_begin(blockIdx.x + 1, U, G);
+    const uint32_t tmem_cols = (2 * NT <= 32) ? 32u : (uint32_t)(2 * NT);  // NT is a power of two >= 16
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int u = u_begin; u < u_end; ++u, ++it) {
+                const TcUnit un = tc_decode(L, u);
+                const int s = it % NS;
+                const uint32_t par = ((it / NS) & 1u) ^ 1u;  // a fresh barrier passes a wait on parity 1
+                if (!mbar_wait(&empty[s], par, abort_flag)) break;
+                uint8_t* a_dst = smem + (size_t)s * stage_bytes;
+                uint8_t* b_dst = a_dst + a_bytes;
+                mbar_expect_tx(&full[s], stage_bytes);
+                const int kelem = un.kb * (I8 ? 128 : 64);
+                tma_load_2d(&L.amap[un.p], &full[s], a_dst, kelem, un.mt * kTcTileM);
+                tma_load_2d(&L.bmap[un.p], &full[s], b_dst, kelem, un.nt * NT);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = tc_idesc(I8, NT);
+            uint32_t it = 0, run = 0;
+            int prev_tile = -1;
+            bool ok = true;
+            for (int u = u_begin; u < u_end && ok; ++u, ++it) {
+                const TcUnit un = tc_decode(L, u);
+                const bool first = un.tile != prev_tile;
+                if (first) {
+                    if (prev_tile >= 0) {
+                        tc_commit(&acc_full[run & 1]);  // previous run complete -> epilogue
+                        ++run;
+                    }
+                    // accumulator buffer (run & 1) must have been drained (its use number is run >> 1)
+                    ok = mbar_wait(&acc_empty[run & 1], (((run >> 1) & 1u) ^ 1u), abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    prev_tile = un.tile;
+                }
+                const int s = it % NS;
+                ok = mbar_wait(&full[s], (it / NS) & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
+                const uint64_t adesc = tc_smem_desc(a_addr), bdesc = tc_smem_desc(a_addr + a_bytes);
+                const uint32_t d_tmem = tmem_base + (run & 1) * NT;
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4)  // 4 x 32 bytes of K per 128-byte block; +2 = 32 bytes in 16-byte units
+                    tc_mma<I8>(d_tmem, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (first && k4 == 0) ? 0u : 1u);
+                tc_commit(&empty[s]);  // stage may be refilled once these MMAs have read it
+            }
+            if (ok && prev_tile >= 0) tc_commit(&acc_full[run & 1]);
+        }
+    } else {
+        // ---------------- epilogue: TMEM -> partial buffer ----------------
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        uint32_t run = 0;
+        int u = u_begin;
+        while (u < u_end) {
+            const TcUnit un = tc_decode(L, u);
+            const TcProb& P = L.p[un.p];
+            // the run = units of this tile inside [u_begin, u_end)
+            const int tile_first = u - un.kb;                       // unit index of the tile's K block 0
+            const int run_end = min(u_end, tile_first + P.kblocks);  // exclusive
+            const int slot = (u == tile_first) ? 0 : (blockIdx.x - tc_cta_of_unit(tile_first, U, G));
+            if (!mbar_wait(&acc_full[run & 1], (run >> 1) & 1u, abort_flag)) break;
+            tc_fence_after();
+            const int ncols = min(NT, P.ncols - un.nt * NT);
+            uint32_t* dst = reinterpret_cast<uint32_t*>(L.partials) + ((size_t)un.tile * L.pmax + slot) * ((size_t)NT * kTcTileM);
+            const int row = q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (run & 1) * NT;
+            for (int c0 = 0; c0 < ncols; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(taddr + c0, v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (c0 + j < ncols) dst[(size_t)(c0 + j) * kTcTileM + row] = v[j];
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[run & 1]);
+            ++run;
+            u = run_end;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(L.status, 2);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Operand preparation: one CTA per activation row.
+//   int8 path : t = rint(x / e * 2^P); D balanced base-128 digits -> B[(r*D + j), k] (s8); xscale[r] = e*2^-P;
+//               tsum[r] = sum_k t_k
+//   fp16 path : hi = fp16(x/e), lo = fp16(x/e - hi) -> B[2r, k], B[2r+1, k]; xscale[r] = e
+// ------------------------------------------------------------------------------------------------
+constexpr int kPrepThreads = 256;
+template <int D>
+__global__ void __launch_bounds__(kPrepThreads) tc_prepare_i8_kernel(const float* __restrict__ x, int ldx, int K, int8_t* __restrict__ B,
+                                                                     float* __restrict__ xscale, long long* __restrict__ tsum) {
+    __shared__ float redf[kPrepThreads / 32];
+    __shared__ long long redl[kPrepThreads / 32];
+    constexpr int P = 7 * D - 1;
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)r * ldx;
+    float amax = 0.f;
+    for (int k = threadIdx.x; k < K; k += kPrepThreads) amax = fmaxf(amax, fabsf(xr[k]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) redf[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = redf[0];
+#pragma unroll
+    for (int i = 1; i < kPrepThreads / 32; ++i) amax = fmaxf(amax, redf[i]);
+    // e = smallest power of two >= amax (1 for an all-zero row; non-finite input is clamped below)
+    int ex = 0;
+    if (amax > 0.f && amax < 3.0e38f) {
+        (void)frexpf(amax, &ex);                    // amax = f * 2^ex, f in [0.5, 1)
+        if (amax == ldexpf(0.5f, ex)) ex -= 1;       // exactly a power of two
+    }
+    ex = max(-100, min(100, ex));
+    const float inv = ldexpf(1.0f, P - ex);  // 2^P / e, exact
+    long long ts = 0;
+    for (int k = threadIdx.x; k < K; k += kPrepThreads) {
+        float v = xr[k] * inv;
+        v = fminf(fmaxf(v, -(float)(1 << P)), (float)(1 << P));
+        int t = __float2int_rn(v);
+        if (!(v == v)) t = 0;  // NaN
+        ts += t;
+        int8_t d[D];
+#pragma unroll
+        for (int j = D - 1; j > 0; --j) {
+            const int dj = ((t + 64) & 127) - 64;
+            d[j] = (int8_t)dj;
+            t = (t - dj) >> 7;
+        }
+        d[0] = (int8_t)t;
+#pragma unroll
+        for (int j = 0; j < D; ++j) B[((size_t)r * D + j) * K + k] = d[j];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ts += __shfl_xor_sync(0xffffffffu, ts, o);
+    if ((threadIdx.x & 31) == 0) redl[threadIdx.x >> 5] = ts;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        long long t = 0;
+        for (int i = 0; i < kPrepThreads / 32; ++i) t += redl[i];
+        tsum[r] = t;
+        xscale[r] = ldexpf(1.0f, ex - P);
+    }
+}
+__global__ void __launch_bounds__(kPrepThreads) tc_prepare_f16_kernel(const float* __restrict__ x, int ldx, int K, __half* __restrict__ B,
+                                                                      float* __restrict__ xscale) {
+    __shared__ float redf[kPrepThreads / 32];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)r * ldx;
+    float amax = 0.f;
+    for (int k = threadIdx.x; k < K; k += kPrepThreads) amax = fmaxf(amax, fabsf(xr[k]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) redf[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = redf[0];
+#pragma unroll
+    for (int i = 1; i < kPrepThreads / 32; ++i) amax = fmaxf(amax, redf[i]);
+    int ex = 0;
+    if (amax > 0.f && amax < 3.0e38f) {
+        (void)frexpf(amax, &ex);
+        if (amax == ldexpf(0.5f, ex)) ex -= 1;
+    }
+    ex = max(-100, min(100, ex));
+    const float inv = ldexpf(1.0f, -ex);
+    for (int k = threadIdx.x; k < K; k += kPrepThreads) {
+        float v = xr[k] * inv;
+        v = fminf(fmaxf(v, -1.0f), 1.0f);
+        if (!(v == v)) v = 0.f;
+        const __half hi = __float2half_rn(v);
+        const __half lo = __float2half_rn(v - __half2float(hi));
+        B[((size_t)r * 2) * K + k] = hi;
+        B[((size_t)r * 2 + 1) * K + k] = lo;
+    }
+    if (threadIdx.x == 0) xscale[r] = ldexpf(1.0f, ex);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Finalize: add a tile's partials in slot order, undo the fixed-point / split representation, apply the
+// weight row's (scale, zero) and the fused epilogue.  One thread per (activation row r, output m).
+// ------------------------------------------------------------------------------------------------
+struct TcFinProb {
+    int M, R, D;          // D digits (int8) or 2 (fp16 hi/lo)
+    int kblocks, n_tiles, unit0, tile0;
+    const float* wscale;  // int8: [M] per-row scale and zero of the container
+    const float* wzero;
+    const float* xscale;       // [R]
+    const long long* tsum;     // int8: [R]
+    float* y;
+    float* y2;
+    const float* bias;
+    const float* aux;
+    int ldy, ldaux, epi, is_i8;
+    int out0;  // first flat output index (r*M + m) of this problem in the launch
+};
+struct TcFinLaunch {
+    TcFinProb p[kTcMaxProblems];
+    int nprob, total_out, nt, pmax, U, G;
+    const void* partials;
+};
+__device__ __forceinline__ void tc_store_epi(const TcFinProb& P, int r, int m, float acc) {
+    float* yp = P.y + (size_t)r * P.ldy + m;
+    switch (P.epi) {
+        case EPI_STORE:
+            *yp = acc;
+            if (P.y2) P.y2[(size_t)r * P.ldy + m] = acc;
+            break;
+        case EPI_ADD: *yp += acc; break;
+        case EPI_RELU2: {
+            const float t = fmaxf(acc, 0.f);
+            *yp = t * t;
+            break;
+        }
+        case EPI_TANH: *yp = tanhf(acc); break;
+        case EPI_SIGMOID: *yp = 1.0f / (1.0f + expf(-acc)); break;
+        case EPI_DECAY: *yp = expf((1.0f / (1.0f + expf(-(acc + P.bias[m])))) * kDecayScale); break;
+        case EPI_SIGMOID_BIAS: *yp = 1.0f / (1.0f + expf(-(acc + P.bias[m]))); break;
+        case EPI_VLERP: {
+            const float v = *yp;
+            const float gate = 1.0f / (1.0f + expf(-(acc + P.bias[m])));
+            *yp = v + gate * (P.aux[(size_t)r * P.ldaux + m] - v);
+            break;
+        }
+    }
+}
+__global__ void __launch_bounds__(256) tc_finalize_kernel(const __grid_constant__ TcFinLaunch L) {
+    for (int o = blockIdx.x * blockDim.x + threadIdx.x; o < L.total_out; o += gridDim.x * blockDim.x) {
+        int pi = 0;
+        while (pi + 1 < L.nprob && o >= L.p[pi + 1].out0) ++pi;
+        const TcFinProb& P = L.p[pi];
+        const int local = o - P.out0;
+        const int r = local / P.M, m = local - r * P.M;
+        const int mt = m >> 7, ml = m & 127;
+        const int ncol0 = r * P.D;  // first B column of this activation row
+        double result = 0.0;
+        long long Q = 0;
+        float facc = 0.f;
+        for (int j = 0; j < P.D; ++j) {
+            const int n = ncol0 + j, nt = n / L.nt, nl = n - nt * L.nt;
+            const int t = mt * P.n_tiles + nt;  // tile index inside the problem
+            const int tile_first = P.unit0 + t * P.kblocks;
+            const int c_lo = tc_cta_of_unit(tile_first, L.U, L.G), c_hi = tc_cta_of_unit(tile_first + P.kblocks - 1, L.U, L.G);
+            const size_t base = ((size_t)(P.tile0 + t) * L.pmax) * ((size_t)L.nt * kTcTileM) + (size_t)nl * kTcTileM + ml;
+            if (P.is_i8) {
+                long long I = 0;
+                for (int s = 0; s <= c_hi - c_lo; ++s) I += reinterpret_cast<const int*>(L.partials)[base + (size_t)s * L.nt * kTcTileM];
+                Q = Q * 128 + I;
+            } else {
+                float f = 0.f;
+                for (int s = 0; s <= c_hi - c_lo; ++s) f += reinterpret_cast<const float*>(L.partials)[base + (size_t)s * L.nt * kTcTileM];
+                facc += f;
+            }
+        }
+        if (P.is_i8)
+            result = (double)P.xscale[r] * ((double)P.wscale[m] * (double)Q + (double)P.wzero[m] * (double)P.tsum[r]);
+        else
+            result = (double)P.xscale[r] * (double)facc;
+        tc_store_epi(P, r, m, (float)result);
+    }
+}
+
+}  // namespace rsv
