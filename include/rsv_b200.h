@@ -133,6 +133,22 @@ int rsv_op_argmax(int device, const float* logits, int64_t rows, int64_t V, uint
 int rsv_op_sample(int device, const float* logits, int64_t rows, int64_t V, const float* sampler8, const uint32_t* hist, int64_t hist_stride,
                   uint32_t* out);
 
+/* Sampling for callers that cannot allocate device memory.  It has no counterpart in the reference.
+ * Same kernel and semantics as rsv_op_sample, but every pointer is a DEVICE pointer supplied by the caller
+ * (logits_dev[rows*V], sampler8_dev[rows*8], hist_dev[rows*hist_stride] or NULL, out_dev[rows]), the launch goes
+ * to `stream` (a cudaStream_t, NULL = default stream) and returns without synchronising, and the kernel's work
+ * area is a fixed pair of static device arrays inside the library: no cudaMalloc / cudaFree happens here.
+ *   - limit: rows * V <= 1,048,576 elements (8 MiB of static device memory per GPU, held until exit); larger
+ *     requests are rejected with an error, not truncated;
+ *   - the first call on each device looks up the arrays' device addresses; make that call before any stream
+ *     capture begins;
+ *   - all calls share the one work area: calls whose kernels can overlap on the GPU (different streams) race;
+ *     serialise them.  The work area needs no clearing between calls (the kernel rewrites what it reads);
+ *   - each row's hist_len (word 7 of its sampler row) must not exceed hist_stride; this cannot be checked here
+ *     because the rows live in device memory. */
+int rsv_op_sample_static(int device, void* stream, const float* logits_dev, int64_t rows, int64_t V, const float* sampler8_dev,
+                         const uint32_t* hist_dev, int64_t hist_stride, uint32_t* out_dev);
+
 #ifdef __cplusplus
 }
 #endif

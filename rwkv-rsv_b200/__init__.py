@@ -30,7 +30,7 @@ ABI_SYMBOLS = [
     "rsv_infer_tokens", "rsv_infer_seq", "rsv_infer_chunked", "rsv_infer_full", "rsv_infer_argmax", "rsv_infer_argmax_selfloop",
     "rsv_infer_sample", "rsv_infer_sample_selfloop", "rsv_prefill_batch", "rsv_sample_selfloop_submit", "rsv_sample_selfloop_collect",
     "rsv_prof_enable", "rsv_prof_clear", "rsv_prof_dump", "rsv_launch_count", "rsv_timer_start", "rsv_timer_stop", "rsv_synchronize",
-    "rsv_op_dequant_int8", "rsv_op_argmax", "rsv_op_sample",
+    "rsv_op_dequant_int8", "rsv_op_argmax", "rsv_op_sample", "rsv_op_sample_static",
 ]
 
 
@@ -99,6 +99,7 @@ def native():
         L.rsv_op_dequant_int8.argtypes = [_c.c_int, vp, vp, i64, i64, vp]
         L.rsv_op_argmax.argtypes = [_c.c_int, vp, i64, i64, vp]
         L.rsv_op_sample.argtypes = [_c.c_int, vp, i64, i64, vp, vp, i64, vp]
+        L.rsv_op_sample_static.argtypes = [_c.c_int, vp, vp, i64, i64, vp, vp, i64, vp]
         _native = L
     return _native
 

@@ -198,6 +198,10 @@ void selfloop_collect(rsv_ticket* tk, uint32_t* out, int64_t len) {
 
 }  // namespace
 
+namespace rsv {
+void set_last_error(const std::string& msg) { g_err = msg; }
+}  // namespace rsv
+
 extern "C" {
 
 const char* rsv_last_error(void) { return g_err.c_str(); }

@@ -600,4 +600,66 @@ void engine_dequant_int8(cudaStream_t stream, const uint8_t* idx_dev, const uint
     check_launch("dequant_int8");
 }
 
+// ------------------------------------------------------------------------------------------------
+// Sampling without any allocation.  Some callers must not allocate device memory at the moment they
+// sample: code running inside a memory-pool or arena discipline that forbids cudaMalloc on the hot
+// path, latency-critical serving loops (cudaMalloc/cudaFree synchronise the device), and plugins that
+// are handed device buffers by a host framework and may not own allocations of their own.  For them
+// the sampler's work area lives in two file-scope device arrays that every GPU loading this library
+// holds until the process exits: 2 x 4 MiB (kStaticSampleMaxElems floats + as many u32).
+// ------------------------------------------------------------------------------------------------
+constexpr size_t kStaticSampleMaxElems = size_t(1) << 20;  // rows * V <= 1,048,576 (e.g. 16 rows of a 65536 vocabulary)
+static __device__ __align__(256) float g_static_sample_temp[kStaticSampleMaxElems];
+static __device__ __align__(256) uint32_t g_static_sample_cnt[kStaticSampleMaxElems];
+
+namespace {
+struct StaticScratch {
+    float* temp = nullptr;
+    uint32_t* cnt = nullptr;
+};
+constexpr int kMaxDevices = 64;
+StaticScratch g_static_scratch[kMaxDevices];
+}  // namespace
+
+void set_last_error(const std::string& msg);  // defined with the C ABI
+
 }  // namespace rsv
+
+// The sampling kernel with its work area in static device memory; device pointers in, device pointer out.
+// See include/rsv_b200.h for the contract.
+extern "C" int rsv_op_sample_static(int device, void* stream, const float* logits_dev, int64_t rows, int64_t V, const float* sampler8_dev,
+                                    const uint32_t* hist_dev, int64_t hist_stride, uint32_t* out_dev) {
+    using namespace rsv;
+    try {
+        if (!logits_dev || !sampler8_dev || !out_dev) throw std::runtime_error("sample_static: null argument");
+        if (rows < 1 || V < 1) throw std::runtime_error("sample_static: empty input");
+        if (hist_stride < 0 || (hist_stride > 0 && !hist_dev)) throw std::runtime_error("sample_static: history is null but hist_stride > 0");
+        if ((uint64_t)rows * (uint64_t)V > kStaticSampleMaxElems)
+            throw std::runtime_error("sample_static: rows * V = " + std::to_string((uint64_t)rows * (uint64_t)V) + " exceeds the static work area of " +
+                                     std::to_string(kStaticSampleMaxElems) + " elements; use rsv_op_sample or fewer rows per call");
+        if (device < 0 || device >= kMaxDevices) throw std::runtime_error("sample_static: device index out of range");
+        RSV_CUDA(cudaSetDevice(device));
+        StaticScratch& sc = g_static_scratch[device];
+        if (!sc.temp) {
+            // first call on this device: resolve the device addresses of the static arrays (in host code their
+            // names are only handles, not device pointers)
+            float* t = nullptr;
+            uint32_t* c = nullptr;
+            RSV_CUDA(cudaGetSymbolAddress((void**)&t, g_static_sample_temp));
+            RSV_CUDA(cudaGetSymbolAddress((void**)&c, g_static_sample_cnt));
+            sc.cnt = c;
+            sc.temp = t;
+        }
+        sample_rows_kernel<<<(unsigned)rows, kSampleThreads, 0, (cudaStream_t)stream>>>(logits_dev, (int)V, sampler8_dev, hist_stride ? hist_dev : nullptr,
+                                                                                        (int)hist_stride, nullptr, sc.temp, sc.cnt, out_dev, nullptr,
+                                                                                        nullptr, 0);
+        check_launch("sample_static");
+        return 0;
+    } catch (const CudaError& e) {
+        set_last_error(e.what());
+        return 2;
+    } catch (const std::exception& e) {
+        set_last_error(e.what());
+        return 1;
+    }
+}
