@@ -125,6 +125,11 @@ int rsv_synchronize(rsv_model* m);
 /* ---- operator-level entry points (host buffers in and out; used for kernel parity tests) ------ */
 /* int8 container decode, w = scale*q + zero in fp32 (dequant_int8, src/model.rs:234-252): out[M*K]. */
 int rsv_op_dequant_int8(int device, const uint8_t* idx, const uint32_t* sz, int64_t M, int64_t K, float* out);
+/* One linear layer on its own: y[R*M] = x[R*K] . W[M,K]^T with W either fp16 (wtype 0, sz NULL) or the int8 container
+ * (wtype 1: w = u8 [M,K], sz = u32 [M,K/128]).  path 0 = SIMT weight-streaming kernel, 1 = tcgen05 tensor-core kernel.
+ * Stands in for the reference's per-kernel GEMV/GEMM unit tests (gemv_f16, gemv_variant, gemm; src/backend_cuda.rs:7440-7480,
+ * 8880-9066, 9607-9675). */
+int rsv_op_linear(int device, int path, int wtype, const void* w, const uint32_t* sz, int64_t M, int64_t K, const float* x, int64_t R, float* y);
 /* arg-max per row of logits[rows*V], ties to the smaller index (rwkv_argmax, src/backend_cuda.rs:3640-3680). */
 int rsv_op_argmax(int device, const float* logits, int64_t rows, int64_t V, uint32_t* out);
 /* The sampling kernel on its own (rwkv_sample(_batch), src/backend_cuda.rs:3690-4009, 2069-2387):

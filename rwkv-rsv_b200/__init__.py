@@ -16,7 +16,7 @@ LIB_CUDA = _os.path.join(_PKG, "librsv_b200.so")
 LIB_SYNTH = _os.path.join(_PKG, "librsv_synth.so")
 
 __all__ = ["ModelBuilder", "Bundle", "State", "SamplerParams", "RnnInput", "RnnOption", "ModelInfo", "RsvError", "write_synthetic", "SHAPES",
-           "op_dequant_int8", "op_argmax", "op_sample", "native", "ABI_SYMBOLS"]
+           "op_dequant_int8", "op_linear", "op_argmax", "op_sample", "native", "ABI_SYMBOLS"]
 
 
 class RsvError(RuntimeError):
@@ -30,7 +30,7 @@ ABI_SYMBOLS = [
     "rsv_infer_tokens", "rsv_infer_seq", "rsv_infer_chunked", "rsv_infer_full", "rsv_infer_argmax", "rsv_infer_argmax_selfloop",
     "rsv_infer_sample", "rsv_infer_sample_selfloop", "rsv_prefill_batch", "rsv_sample_selfloop_submit", "rsv_sample_selfloop_collect",
     "rsv_prof_enable", "rsv_prof_clear", "rsv_prof_dump", "rsv_launch_count", "rsv_timer_start", "rsv_timer_stop", "rsv_synchronize",
-    "rsv_op_dequant_int8", "rsv_op_argmax", "rsv_op_sample", "rsv_op_sample_static",
+    "rsv_op_dequant_int8", "rsv_op_linear", "rsv_op_argmax", "rsv_op_sample", "rsv_op_sample_static",
 ]
 
 
@@ -98,6 +98,7 @@ def native():
         L.rsv_synchronize.argtypes = [vp]
         L.rsv_op_dequant_int8.argtypes = [_c.c_int, vp, vp, i64, i64, vp]
         L.rsv_op_argmax.argtypes = [_c.c_int, vp, i64, i64, vp]
+        L.rsv_op_linear.argtypes = [_c.c_int, _c.c_int, _c.c_int, vp, vp, i64, i64, vp, i64, vp]
         L.rsv_op_sample.argtypes = [_c.c_int, vp, i64, i64, vp, vp, i64, vp]
         L.rsv_op_sample_static.argtypes = [_c.c_int, vp, vp, i64, i64, vp, vp, i64, vp]
         _native = L
@@ -371,6 +372,21 @@ def op_dequant_int8(idx_u8, sz_u32, device=0):
     out = _np.empty((m, k), dtype=_np.float32)
     _check(native().rsv_op_dequant_int8(device, _ptr(idx), _ptr(sz), m, k, _ptr(out)))
     return out
+
+
+def op_linear(x, w, sz=None, path=0, device=0):
+    """y = x @ W^T.  w: float16 [M,K], or uint8 [M,K] with sz uint32 [M,K/128] (the int8 container).  path 0 SIMT, 1 tensor core."""
+    xx = _np.ascontiguousarray(_np.atleast_2d(x), dtype=_np.float32)
+    if sz is None:
+        ww, wtype, szp = _np.ascontiguousarray(w, dtype=_np.float16), 0, None
+    else:
+        ww, wtype = _np.ascontiguousarray(w, dtype=_np.uint8), 1
+        szz = _np.ascontiguousarray(sz, dtype=_np.uint32)
+        szp = _ptr(szz)
+    m, k = ww.shape
+    y = _np.empty((xx.shape[0], m), dtype=_np.float32)
+    _check(native().rsv_op_linear(device, int(path), wtype, _ptr(ww), szp, m, k, _ptr(xx), xx.shape[0], _ptr(y)))
+    return y
 
 
 def op_argmax(logits, device=0):

@@ -557,6 +557,16 @@ int rsv_op_dequant_int8(int device, const uint8_t* idx, const uint32_t* sz, int6
         RSV_CUDA(cudaMemcpy(out, dout.p, (size_t)M * K * 4, cudaMemcpyDeviceToHost));
     });
 }
+int rsv_op_linear(int device, int path, int wtype, const void* w, const uint32_t* sz, int64_t M, int64_t K, const float* x, int64_t R, float* y) {
+    return guarded([&] {
+        need(w && x && y, "null argument");
+        need(wtype == W_F16 || (wtype == W_INT8 && sz), "op_linear: wtype must be 0 (fp16) or 1 (int8, with sz)");
+        need(path == 0 || path == 1, "op_linear: path must be 0 (SIMT) or 1 (tensor core)");
+        select_device(device);
+        auto m = Model::create_bare(device);
+        engine_op_linear(*m, path, wtype, w, sz, (int)M, (int)K, x, (int)R, y);
+    });
+}
 int rsv_op_argmax(int device, const float* logits, int64_t rows, int64_t V, uint32_t* out) {
     return guarded([&] {
         need(logits && out, "null argument");

@@ -6,6 +6,7 @@
 
 #include "kernels.cuh"
 #include "safetensors.hpp"
+#include "tc_linear.cuh"
 
 namespace rsv {
 
@@ -73,9 +74,38 @@ std::vector<uint16_t> to_f16_bits(const StTensor& t) {
     return out;
 }
 
+
+// cuTensorMapEncodeTiled is fetched through the runtime so that the library does not link libcuda directly.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        RSV_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        if (!p || q != cudaDriverEntryPointSuccess) throw CudaError("cuTensorMapEncodeTiled is not available in this driver");
+        fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+// 2-D K-major operand [rows, kelems]: box = 128 bytes of K x box_rows rows, 128-byte swizzle.
+void encode_kmajor_map(CUtensorMap* map, bool i8, void* base, size_t rows, size_t kelems, int box_rows) {
+    const size_t es = i8 ? 1 : 2;
+    cuuint64_t dims[2] = {(cuuint64_t)kelems, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(kelems * es)};
+    cuuint32_t box[2] = {(cuuint32_t)(kTcKBlockBytes / es), (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_tiled_fn()(map, i8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw CudaError("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+}
+inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
 struct Loader {
     Model& m;
-    const SafeTensorsFile& st;
+    const SafeTensorsFile* st;
 
     void* dev_alloc(size_t bytes) {
         void* p = nullptr;
@@ -90,7 +120,7 @@ struct Loader {
         return p;
     }
     float* vec(const std::string& key, size_t expect) {
-        std::vector<float> v = to_f32(st.get(key));
+        std::vector<float> v = to_f32(st->get(key));
         if (v.size() != expect) throw std::runtime_error(key + ": expected " + std::to_string(expect) + " elements, file has " + std::to_string(v.size()));
         return (float*)upload(v.data(), v.size() * 4);
     }
@@ -99,33 +129,71 @@ struct Loader {
         LinearW L;
         L.M = M;
         L.K = K;
-        if (st.has(key + ".int8_idx")) {
-            const StTensor& it = st.get(key + ".int8_idx");
-            const StTensor& zt = st.get(key + ".int8_sz");
+        if (st->has(key + ".int8_idx")) {
+            const StTensor& it = st->get(key + ".int8_idx");
+            const StTensor& zt = st->get(key + ".int8_sz");
             if (K % 128) throw std::runtime_error(key + ": int8 needs K % 128 == 0");
             if (it.dtype != "U8" || it.nbytes != (size_t)M * K) throw std::runtime_error(key + ".int8_idx: expected U8 [" + std::to_string(M) + "," + std::to_string(K) + "]");
             if (zt.dtype != "U32" || zt.nbytes != (size_t)M * (K / 128) * 4) throw std::runtime_error(key + ".int8_sz: expected U32 [M, K/128]");
             L.wtype = W_INT8;
             L.w = upload(it.data, it.nbytes);
             L.sz = (uint32_t*)upload(zt.data, zt.nbytes);
+            prepare_tc_i8(L, (const uint32_t*)zt.data);
         } else {
-            const StTensor& t = st.get(key);
+            const StTensor& t = st->get(key);
             if (t.numel() != (int64_t)M * K) throw std::runtime_error(key + ": shape mismatch");
             if (K % 8) throw std::runtime_error(key + ": fp16 needs K % 8 == 0");
             L.wtype = W_F16;
             if (t.dtype == "F16") {
                 L.w = upload(t.data, t.nbytes);
+                prepare_tc_f16(L, (const uint16_t*)t.data);
             } else {
                 auto h = to_f16_bits(t);
                 L.w = upload(h.data(), h.size() * 2);
+                prepare_tc_f16(L, h.data());
             }
         }
         return L;
     }
+    // int8: the tensor-core path needs one (scale, zero) per output row (all groups of a row equal) and
+    // M, K multiples of 128; other files keep tc_ok = false and run on the SIMT kernel.
+    void prepare_tc_i8(LinearW& L, const uint32_t* sz_host) {
+        const int KG = L.K / 128;
+        if (L.M % kTcTileM || L.K % kTcKBlockBytes) return;
+        std::vector<float> sc(L.M), zr(L.M);
+        for (int m = 0; m < L.M; ++m) {
+            const uint32_t w0 = sz_host[(size_t)m * KG];
+            for (int g = 1; g < KG; ++g)
+                if (sz_host[(size_t)m * KG + g] != w0) return;
+            sc[m] = half_bits_to_float((uint16_t)(w0 & 0xFFFFu));
+            zr[m] = half_bits_to_float((uint16_t)(w0 >> 16));
+        }
+        L.wscale = (float*)upload(sc.data(), sc.size() * 4);
+        L.wzero = (float*)upload(zr.data(), zr.size() * 4);
+        L.Mpad = L.M;
+        L.Kpad = L.K;
+        L.w_tc = L.w;
+        encode_kmajor_map(&L.amap, true, L.w_tc, L.Mpad, L.Kpad, kTcTileM);
+        L.tc_ok = true;
+    }
+    // fp16: zero-pad to [Mpad = ceil128(M), Kpad = ceil64(K)] when the shape needs it (only small matrices do).
+    void prepare_tc_f16(LinearW& L, const uint16_t* w_host) {
+        L.Mpad = (int)round_up(L.M, kTcTileM);
+        L.Kpad = (int)round_up(L.K, 64);
+        if (L.Mpad == L.M && L.Kpad == L.K) {
+            L.w_tc = L.w;
+        } else {
+            std::vector<uint16_t> pad((size_t)L.Mpad * L.Kpad, 0);
+            for (int m = 0; m < L.M; ++m) memcpy(&pad[(size_t)m * L.Kpad], &w_host[(size_t)m * L.K], (size_t)L.K * 2);
+            L.w_tc = upload(pad.data(), pad.size() * 2);
+        }
+        encode_kmajor_map(&L.amap, false, L.w_tc, L.Mpad, L.Kpad, kTcTileM);
+        L.tc_ok = true;
+    }
     // Low-rank pair member.  The file holds either [in,out] or [out,in] (src/model.rs:564-581 accepts
     // both, first match wins when in == out); HBM always holds [out,in] fp16.
     LinearW lowrank(const std::string& key, int in_dim, int out_dim) {
-        const StTensor& t = st.get(key);
+        const StTensor& t = st->get(key);
         if (t.shape.size() != 2) throw std::runtime_error(key + ": expected a 2-D tensor");
         std::vector<uint16_t> h = to_f16_bits(t);
         std::vector<uint16_t> oi((size_t)in_dim * out_dim);
@@ -143,6 +211,7 @@ struct Loader {
         L.K = in_dim;
         L.wtype = W_F16;
         L.w = upload(oi.data(), oi.size() * 2);
+        prepare_tc_f16(L, oi.data());
         return L;
     }
 };
@@ -202,13 +271,16 @@ std::unique_ptr<Model> Model::load(const std::string& path, int device) {
     if (c.n_head * c.head_size != c.n_embd) throw std::runtime_error("n_head * head_size != n_embd");
     if (c.n_embd % 8 || c.ffn_hidden % 8) throw std::runtime_error("n_embd and ffn_hidden must be multiples of 8");
 
+    m->num_sms = prop.multiProcessorCount;
+    if (const char* e = getenv("RSV_TC_MIN_ROWS"))
+        if (*e) m->tc_min_rows = atoi(e);
     RSV_CUDA(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
     RSV_CUDA(cudaEventCreate(&m->ev0));
     RSV_CUDA(cudaEventCreate(&m->ev1));
     RSV_CUDA(cudaEventCreate(&m->tev[0]));
     RSV_CUDA(cudaEventCreate(&m->tev[1]));
 
-    Loader ld{*m, st};
+    Loader ld{*m, &st};
     const int C = c.n_embd, F = c.ffn_hidden;
     {
         auto h = to_f16_bits(emb);
@@ -266,19 +338,48 @@ std::unique_ptr<Model> Model::load(const std::string& path, int device) {
     return m;
 }
 
+std::unique_ptr<Model> Model::create_bare(int device) {
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0)
+        throw CudaError(std::string("no CUDA device available (") + cudaGetErrorString(e) + "): this library has no CPU fallback");
+    if (device < 0 || device >= ndev) throw std::runtime_error("device index out of range");
+    RSV_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    RSV_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) throw std::runtime_error("this library is built for sm_100a (B200) only");
+    auto m = std::make_unique<Model>();
+    m->device = device;
+    m->num_sms = prop.multiProcessorCount;
+    RSV_CUDA(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+    RSV_CUDA(cudaEventCreate(&m->ev0));
+    RSV_CUDA(cudaEventCreate(&m->ev1));
+    RSV_CUDA(cudaEventCreate(&m->tev[0]));
+    RSV_CUDA(cudaEventCreate(&m->tev[1]));
+    RSV_CUDA(cudaMalloc(&m->ws.status, sizeof(int)));
+    RSV_CUDA(cudaMemset(m->ws.status, 0, sizeof(int)));
+    return m;
+}
+
 static void free_workspace(Workspace& w) {
     void* ptrs[] = {w.x, w.xmix, w.r, w.k, w.v, w.w, w.a, w.g, w.yg, w.xb, w.mid, w.h, w.vfirst, w.xn, w.logits, w.staging, w.tokens, w.row_meta, w.seg_meta, w.out_rows, w.samp_temp, w.samp_cnt};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     int* status = w.status;
     int* pos = w.tok_pos;
-    uint32_t* tl = w.tok_list;
-    size_t tlc = w.tok_list_cap;
+    Workspace keep = w;
     w = Workspace{};
     w.status = status;
     w.tok_pos = pos;
-    w.tok_list = tl;
-    w.tok_list_cap = tlc;
+    w.tok_list = keep.tok_list;
+    w.tok_list_cap = keep.tok_list_cap;
+    w.tc_b = keep.tc_b;
+    w.tc_b_bytes = keep.tc_b_bytes;
+    w.tc_xscale = keep.tc_xscale;
+    w.tc_tsum = keep.tc_tsum;
+    w.tc_rows = keep.tc_rows;
+    w.tc_partials = keep.tc_partials;
+    w.tc_partials_bytes = keep.tc_partials_bytes;
 }
 
 Model::~Model() {
@@ -289,6 +390,8 @@ Model::~Model() {
     if (ws.tok_pos) cudaFree(ws.tok_pos);
     if (ws.tok_list) cudaFree(ws.tok_list);
     for (void* p : allocs) cudaFree(p);
+    for (void* p : {(void*)ws.tc_b, (void*)ws.tc_xscale, (void*)ws.tc_tsum, ws.tc_partials})
+        if (p) cudaFree(p);
     if (pinned) cudaFreeHost(pinned);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
@@ -396,7 +499,7 @@ void launch_linear_rt(Model& m, const LinGroup& g, int nblk, int R, size_t smem)
     check_launch("linear_rows");
 }
 
-void run_linear(Model& m, const char* name, const LinReq* reqs, int n, int R) {
+void run_linear_simt(Model& m, const char* name, const LinReq* reqs, int n, int R) {
     LinGroup g;
     memset(&g, 0, sizeof(g));
     g.n = n;
@@ -447,6 +550,200 @@ void run_linear(Model& m, const char* name, const LinReq* reqs, int n, int R) {
     }
 }
 
+
+// ---- tensor-core path ---------------------------------------------------------------------------
+void ensure_tc_buffers(Model& m, size_t b_bytes, size_t rows, size_t partial_bytes) {
+    Workspace& w = m.ws;
+    if (b_bytes <= w.tc_b_bytes && rows <= w.tc_rows && partial_bytes <= w.tc_partials_bytes) return;
+    RSV_CUDA(cudaStreamSynchronize(m.stream));
+    if (b_bytes > w.tc_b_bytes) {
+        if (w.tc_b) cudaFree(w.tc_b);
+        w.tc_b = nullptr;
+        w.tc_b_bytes = 0;
+        const size_t nb = b_bytes + b_bytes / 4;
+        RSV_CUDA(cudaMalloc(&w.tc_b, nb));
+        RSV_CUDA(cudaMemset(w.tc_b, 0, nb));
+        w.tc_b_bytes = nb;
+    }
+    if (rows > w.tc_rows) {
+        if (w.tc_xscale) cudaFree(w.tc_xscale);
+        if (w.tc_tsum) cudaFree(w.tc_tsum);
+        w.tc_xscale = nullptr;
+        w.tc_tsum = nullptr;
+        w.tc_rows = 0;
+        const size_t nr = rows + rows / 4;
+        RSV_CUDA(cudaMalloc(&w.tc_xscale, nr * sizeof(float)));
+        RSV_CUDA(cudaMalloc(&w.tc_tsum, nr * sizeof(long long)));
+        w.tc_rows = nr;
+    }
+    if (partial_bytes > w.tc_partials_bytes) {
+        if (w.tc_partials) cudaFree(w.tc_partials);
+        w.tc_partials = nullptr;
+        w.tc_partials_bytes = 0;
+        const size_t np = partial_bytes + partial_bytes / 4;
+        RSV_CUDA(cudaMalloc(&w.tc_partials, np));
+        w.tc_partials_bytes = np;
+    }
+}
+
+constexpr int kTcDigits = 4;  // base-128 digits of the fixed-point activations (P = 27 bits)
+
+// One launch group of the tensor-core path: all requests share the weight kind (int8 or fp16).
+void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, int R, bool i8) {
+    const int D = i8 ? kTcDigits : 2;
+    const int ncols = R * D;
+    int NT = 16;
+    while (NT < ncols && NT < 256) NT <<= 1;
+    const int ncols_pad = (int)round_up(ncols, NT);
+    const size_t es = i8 ? 1 : 2;
+    // B operand regions (requests that read the same activations share one)
+    struct Region {
+        const float* x;
+        int ldx, K, Kpad;
+        size_t off;
+        int row0;
+    };
+    std::vector<Region> regions;
+    std::vector<int> region_of(n);
+    size_t b_bytes = 0;
+    int rows = 0;
+    for (int i = 0; i < n; ++i) {
+        const LinearW& W = *reqs[i].W;
+        int found = -1;
+        for (size_t j = 0; j < regions.size(); ++j)
+            if (regions[j].x == reqs[i].x && regions[j].K == W.K && regions[j].Kpad == W.Kpad && regions[j].ldx == reqs[i].ldx) found = (int)j;
+        if (found < 0) {
+            regions.push_back(Region{reqs[i].x, reqs[i].ldx, W.K, W.Kpad, b_bytes, rows});
+            found = (int)regions.size() - 1;
+            b_bytes += round_up((size_t)ncols_pad * W.Kpad * es, 1024);
+            rows += R;
+        }
+        region_of[i] = found;
+    }
+    // units, tiles, CTA count
+    TcLaunch L;
+    memset(&L, 0, sizeof(L));
+    TcFinLaunch F;
+    memset(&F, 0, sizeof(F));
+    int U = 0, T = 0, out = 0;
+    const int n_tiles = ncols_pad / NT;
+    for (int i = 0; i < n; ++i) {
+        const LinearW& W = *reqs[i].W;
+        TcProb& P = L.p[i];
+        P.M = W.M;
+        P.kblocks = (int)((size_t)W.Kpad * es / kTcKBlockBytes);
+        P.ncols = ncols;
+        P.n_tiles = n_tiles;
+        P.unit0 = U;
+        P.tile0 = T;
+        const int mtiles = W.Mpad / kTcTileM;
+        U += mtiles * n_tiles * P.kblocks;
+        T += mtiles * n_tiles;
+        L.amap[i] = W.amap;
+    }
+    const int G = std::min(m.num_sms, U);
+    int pmax = 1;
+    for (int i = 0; i < n; ++i) {
+        const TcProb& P = L.p[i];
+        const int tiles = (reqs[i].W->Mpad / kTcTileM) * n_tiles;
+        for (int t = 0; t < tiles; ++t) {
+            const int u0 = P.unit0 + t * P.kblocks;
+            pmax = std::max(pmax, tc_cta_of_unit(u0 + P.kblocks - 1, U, G) - tc_cta_of_unit(u0, U, G) + 1);
+        }
+    }
+    const size_t partial_bytes = (size_t)T * pmax * NT * kTcTileM * 4;
+    ensure_tc_buffers(m, b_bytes, (size_t)rows, partial_bytes);
+    Workspace& w = m.ws;
+    // operand preparation
+    for (const Region& rg : regions) {
+        LAUNCH(m, i8 ? "tc_prepare_i8" : "tc_prepare_f16") {
+            if (i8)
+                tc_prepare_i8_kernel<kTcDigits><<<R, kPrepThreads, 0, m.stream>>>(rg.x, rg.ldx, rg.K, rg.Kpad, (int8_t*)(w.tc_b + rg.off), w.tc_xscale + rg.row0,
+                                                                                 w.tc_tsum + rg.row0);
+            else
+                tc_prepare_f16_kernel<<<R, kPrepThreads, 0, m.stream>>>(rg.x, rg.ldx, rg.K, rg.Kpad, (__half*)(w.tc_b + rg.off), w.tc_xscale + rg.row0);
+            check_launch("tc_prepare");
+        }
+    }
+    for (int i = 0; i < n; ++i) {
+        const Region& rg = regions[region_of[i]];
+        encode_kmajor_map(&L.bmap[i], i8, w.tc_b + rg.off, ncols_pad, rg.Kpad, NT);
+    }
+    L.nprob = n;
+    L.total_units = U;
+    L.nt = NT;
+    L.is_i8 = i8;
+    L.pmax = pmax;
+    const size_t stage_bytes = (size_t)kTcTileM * kTcKBlockBytes + (size_t)NT * kTcKBlockBytes;
+    L.nstages = (int)std::min<size_t>(8, (200 * 1024) / stage_bytes);
+    L.partials = w.tc_partials;
+    L.status = w.status;
+    const size_t smem = (size_t)L.nstages * stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static bool configured = false;
+    if (!configured) {
+        RSV_CUDA(cudaFuncSetAttribute(tc_linear_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        RSV_CUDA(cudaFuncSetAttribute(tc_linear_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured = true;
+    }
+    LAUNCH(m, name) {
+        if (i8)
+            tc_linear_kernel<true><<<G, kTcThreads, smem, m.stream>>>(L);
+        else
+            tc_linear_kernel<false><<<G, kTcThreads, smem, m.stream>>>(L);
+        check_launch("tc_linear");
+    }
+    // finalize
+    for (int i = 0; i < n; ++i) {
+        const LinReq& q = reqs[i];
+        const Region& rg = regions[region_of[i]];
+        TcFinProb& P = F.p[i];
+        P.M = q.W->M;
+        P.R = R;
+        P.D = D;
+        P.kblocks = L.p[i].kblocks;
+        P.n_tiles = n_tiles;
+        P.unit0 = L.p[i].unit0;
+        P.tile0 = L.p[i].tile0;
+        P.wscale = q.W->wscale;
+        P.wzero = q.W->wzero;
+        P.xscale = w.tc_xscale + rg.row0;
+        P.tsum = w.tc_tsum + rg.row0;
+        P.y = q.y;
+        P.y2 = q.y2;
+        P.bias = q.bias;
+        P.aux = q.aux;
+        P.ldy = q.ldy;
+        P.ldaux = q.ldaux;
+        P.epi = q.epi;
+        P.is_i8 = i8;
+        P.out0 = out;
+        out += R * q.W->M;
+    }
+    F.nprob = n;
+    F.total_out = out;
+    F.nt = NT;
+    F.pmax = pmax;
+    F.U = U;
+    F.G = G;
+    F.partials = w.tc_partials;
+    LAUNCH(m, "tc_finalize") {
+        const int blocks = std::min((out + 255) / 256, m.num_sms * 16);
+        tc_finalize_kernel<<<blocks, 256, 0, m.stream>>>(F);
+        check_launch("tc_finalize");
+    }
+}
+
+void run_linear(Model& m, const char* name, const LinReq* reqs, int n, int R) {
+    bool tc = R >= m.tc_min_rows;
+    for (int i = 0; i < n; ++i) tc = tc && reqs[i].W->tc_ok;
+    if (!tc) return run_linear_simt(m, name, reqs, n, R);
+    LinReq a[kTcMaxProblems], b[kTcMaxProblems];
+    int na = 0, nb = 0;
+    for (int i = 0; i < n; ++i) (reqs[i].W->wtype == W_INT8 ? a[na++] : b[nb++]) = reqs[i];
+    std::string nm = std::string(name) + "_tc";
+    if (na) run_linear_tc_kind(m, nm.c_str(), a, na, R, true);
+    if (nb) run_linear_tc_kind(m, nm.c_str(), b, nb, R, false);
+}
 }  // namespace
 
 // ------------------------------------------------------------------------------------------------
@@ -551,6 +848,7 @@ void Model::check_status() {
     RSV_CUDA(cudaStreamSynchronize(stream));
     if (s) {
         RSV_CUDA(cudaMemsetAsync(ws.status, 0, sizeof(int), stream));
+        if (s & 2) throw std::runtime_error("tensor-core kernel gave up waiting on a barrier (device status bit 1)");
         if (s & 1) throw std::runtime_error("token id out of range (>= vocab); the embedding row 0 was used instead");
         throw std::runtime_error("device status word = " + std::to_string(s));
     }
@@ -598,6 +896,59 @@ void engine_argmax_raw(cudaStream_t stream, const float* logits_dev, int rows, i
 void engine_dequant_int8(cudaStream_t stream, const uint8_t* idx_dev, const uint32_t* sz_dev, size_t M, size_t K, float* out_dev) {
     dequant_int8_kernel<<<148 * 8, 256, 0, stream>>>(idx_dev, sz_dev, M, K, out_dev);
     check_launch("dequant_int8");
+}
+
+
+void engine_op_linear(Model& m, int path, int wtype, const void* w_host, const uint32_t* sz_host, int M, int K, const float* x_host, int R,
+                      float* y_host) {
+    RSV_CUDA(cudaSetDevice(m.device));
+    if (M < 1 || K < 8 || R < 1) throw std::runtime_error("op_linear: empty problem");
+    if (wtype == W_INT8 ? (K % 128 != 0) : (K % 8 != 0)) throw std::runtime_error("op_linear: K must be a multiple of 128 (int8) or 8 (fp16)");
+    Loader ld{m, nullptr};
+    LinearW W;
+    W.M = M;
+    W.K = K;
+    W.wtype = wtype;
+    const size_t first_alloc = m.allocs.size();
+    float *dx = nullptr, *dy = nullptr;
+    try {
+        if (wtype == W_INT8) {
+            W.w = ld.upload(w_host, (size_t)M * K);
+            W.sz = (uint32_t*)ld.upload(sz_host, (size_t)M * (K / 128) * 4);
+            ld.prepare_tc_i8(W, sz_host);
+        } else {
+            W.w = ld.upload(w_host, (size_t)M * K * 2);
+            ld.prepare_tc_f16(W, (const uint16_t*)w_host);
+        }
+        if (path == 1 && !W.tc_ok) throw std::runtime_error("op_linear: this matrix cannot take the tensor-core path (needs one scale/zero per row, M and K multiples of 128)");
+        RSV_CUDA(cudaMalloc(&dx, (size_t)R * K * 4));
+        RSV_CUDA(cudaMalloc(&dy, (size_t)R * M * 4));
+        RSV_CUDA(cudaMemcpyAsync(dx, x_host, (size_t)R * K * 4, cudaMemcpyHostToDevice, m.stream));
+        LinReq q = {&W, dx, K, dy, M, EPI_STORE};
+        if (path == 1) {
+            LinReq a[1] = {q};
+            run_linear_tc_kind(m, "op_linear_tc", a, 1, R, wtype == W_INT8);
+        } else {
+            run_linear_simt(m, "op_linear_simt", &q, 1, R);
+        }
+        RSV_CUDA(cudaMemcpyAsync(y_host, dy, (size_t)R * M * 4, cudaMemcpyDeviceToHost, m.stream));
+        m.check_status();
+    } catch (...) {
+        cudaStreamSynchronize(m.stream);
+        if (dx) cudaFree(dx);
+        if (dy) cudaFree(dy);
+        while (m.allocs.size() > first_alloc) {
+            cudaFree(m.allocs.back());
+            m.allocs.pop_back();
+        }
+        throw;
+    }
+    cudaFree(dx);
+    cudaFree(dy);
+    while (m.allocs.size() > first_alloc) {
+        cudaFree(m.allocs.back());
+        m.allocs.pop_back();
+    }
 }
 
 // ------------------------------------------------------------------------------------------------

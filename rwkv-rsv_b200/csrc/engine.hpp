@@ -8,6 +8,8 @@
 #include <string>
 #include <vector>
 
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace rsv {
@@ -27,6 +29,13 @@ struct LinearW {
     void* w = nullptr;         // fp16 [M,K] or u8 [M,K]
     uint32_t* sz = nullptr;    // int8: [M,K/128] (fp16 scale | fp16 zero << 16), the reference container
     size_t bytes() const { return wtype == W_INT8 ? (size_t)M * K + (size_t)M * (K / 128) * 4 : (size_t)M * K * 2; }
+    // tensor-core path (tcgen05): A operand = the same bytes (or a zero-padded copy when M % 128 or the K pitch
+    // does not fit), one (scale, zero) pair per output row for int8, and the TMA descriptor of the A operand
+    bool tc_ok = false;
+    int Mpad = 0, Kpad = 0;
+    void* w_tc = nullptr;
+    float *wscale = nullptr, *wzero = nullptr;
+    CUtensorMap amap;
 };
 
 struct LayerW {
@@ -42,6 +51,14 @@ struct Workspace {
     int rows = 0, outs = 0, segs = 0;  // capacities
     float *x = nullptr, *xmix = nullptr, *r = nullptr, *k = nullptr, *v = nullptr, *w = nullptr, *a = nullptr, *g = nullptr;
     float *yg = nullptr, *xb = nullptr, *mid = nullptr, *h = nullptr, *vfirst = nullptr, *xn = nullptr, *logits = nullptr, *staging = nullptr;
+    // tensor-core linear path: B operands, per-row scales, fixed-point sums, split-K partials (grown on demand)
+    uint8_t* tc_b = nullptr;
+    size_t tc_b_bytes = 0;
+    float* tc_xscale = nullptr;
+    long long* tc_tsum = nullptr;
+    size_t tc_rows = 0;
+    void* tc_partials = nullptr;
+    size_t tc_partials_bytes = 0;
     float* samp_temp = nullptr;      // [outs, V] sampler work area
     uint32_t* samp_cnt = nullptr;    // [outs, V] penalty histogram
     uint32_t* tokens = nullptr;    // [rows] input token of every row (device-resident between self-loop rounds)
@@ -99,6 +116,10 @@ struct Model {
     std::map<std::string, KernelProf> prof;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr, tev[2] = {nullptr, nullptr};
     long launches = 0;  // kernels launched since the counter was last cleared
+    int num_sms = 148;
+    int tc_min_rows = 5;  // packed steps with at least this many rows use the tensor-core linear path
+
+    static std::unique_ptr<Model> create_bare(int device);  // stream + events only (operator-level entry points)
 
     static std::unique_ptr<Model> load(const std::string& path, int device);
     ~Model();
@@ -128,6 +149,9 @@ void engine_sample(Model& m, const float* logits_dev, int rows, const float* sam
 void engine_argmax_raw(cudaStream_t stream, const float* logits_dev, int rows, int V, uint32_t* out_dev);
 void engine_sample_raw(cudaStream_t stream, const float* logits_dev, int rows, int V, const float* sampler8_dev, const uint32_t* hist_dev,
                        int hist_stride, float* temp_dev, uint32_t* counter_dev, uint32_t* out_dev);
+// Operator-level linear layer on host data: y[R,M] = x[R,K] . W[M,K]^T.  path 0 = SIMT kernel, 1 = tcgen05 kernel.
+void engine_op_linear(Model& m, int path, int wtype, const void* w_host, const uint32_t* sz_host, int M, int K, const float* x_host, int R,
+                      float* y_host);
 void engine_dequant_int8(cudaStream_t stream, const uint8_t* idx_dev, const uint32_t* sz_dev, size_t M, size_t K, float* out_dev);
 
 }  // namespace rsv

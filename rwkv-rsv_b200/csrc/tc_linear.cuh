@@ -271,7 +271,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
             const int tile_first = u - un.kb;                       // unit index of the tile's K block 0
             const int run_end = min(u_end, tile_first + P.kblocks);  // exclusive
             const int slot = (u == tile_first) ? 0 : (blockIdx.x - tc_cta_of_unit(tile_first, U, G));
-            if (!mbar_wait(&acc_full[run & 1], (run >> 1) & 1u, abort_flag)) break;
+            const bool got = mbar_wait(&acc_full[run & 1], (run >> 1) & 1u, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) break;
             tc_fence_after();
             const int ncols = min(NT, P.ncols - un.nt * NT);
             uint32_t* dst = reinterpret_cast<uint32_t*>(L.partials) + ((size_t)un.tile * L.pmax + slot) * ((size_t)NT * kTcTileM);
@@ -295,6 +296,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicOr(L.status, 2);
     if (warp == 1) {
+        __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);
     }
@@ -308,7 +310,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
 // ------------------------------------------------------------------------------------------------
 constexpr int kPrepThreads = 256;
 template <int D>
-__global__ void __launch_bounds__(kPrepThreads) tc_prepare_i8_kernel(const float* __restrict__ x, int ldx, int K, int8_t* __restrict__ B,
+__global__ void __launch_bounds__(kPrepThreads) tc_prepare_i8_kernel(const float* __restrict__ x, int ldx, int K, int Kpad, int8_t* __restrict__ B,
                                                                      float* __restrict__ xscale, long long* __restrict__ tsum) {
     __shared__ float redf[kPrepThreads / 32];
     __shared__ long long redl[kPrepThreads / 32];
@@ -348,8 +350,11 @@ __global__ void __launch_bounds__(kPrepThreads) tc_prepare_i8_kernel(const float
         }
         d[0] = (int8_t)t;
 #pragma unroll
-        for (int j = 0; j < D; ++j) B[((size_t)r * D + j) * K + k] = d[j];
+        for (int j = 0; j < D; ++j) B[((size_t)r * D + j) * Kpad + k] = d[j];
     }
+    for (int k = K + threadIdx.x; k < Kpad; k += kPrepThreads)
+#pragma unroll
+        for (int j = 0; j < D; ++j) B[((size_t)r * D + j) * Kpad + k] = 0;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ts += __shfl_xor_sync(0xffffffffu, ts, o);
     if ((threadIdx.x & 31) == 0) redl[threadIdx.x >> 5] = ts;
@@ -361,7 +366,7 @@ __global__ void __launch_bounds__(kPrepThreads) tc_prepare_i8_kernel(const float
         xscale[r] = ldexpf(1.0f, ex - P);
     }
 }
-__global__ void __launch_bounds__(kPrepThreads) tc_prepare_f16_kernel(const float* __restrict__ x, int ldx, int K, __half* __restrict__ B,
+__global__ void __launch_bounds__(kPrepThreads) tc_prepare_f16_kernel(const float* __restrict__ x, int ldx, int K, int Kpad, __half* __restrict__ B,
                                                                       float* __restrict__ xscale) {
     __shared__ float redf[kPrepThreads / 32];
     const int r = blockIdx.x;
@@ -388,8 +393,12 @@ __global__ void __launch_bounds__(kPrepThreads) tc_prepare_f16_kernel(const floa
         if (!(v == v)) v = 0.f;
         const __half hi = __float2half_rn(v);
         const __half lo = __float2half_rn(v - __half2float(hi));
-        B[((size_t)r * 2) * K + k] = hi;
-        B[((size_t)r * 2 + 1) * K + k] = lo;
+        B[((size_t)r * 2) * Kpad + k] = hi;
+        B[((size_t)r * 2 + 1) * Kpad + k] = lo;
+    }
+    for (int k = K + threadIdx.x; k < Kpad; k += kPrepThreads) {
+        B[((size_t)r * 2) * Kpad + k] = __float2half_rn(0.f);
+        B[((size_t)r * 2 + 1) * Kpad + k] = __float2half_rn(0.f);
     }
     if (threadIdx.x == 0) xscale[r] = ldexpf(1.0f, ex);
 }

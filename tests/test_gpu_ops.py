@@ -90,3 +90,68 @@ def test_sampler_large_vocab_top_p_cap():
     assert [int(g) for g in got] == want
     for r in range(4):
         assert logits[r, int(got[r])] >= np.sort(logits[r])[-512]
+
+
+def _int8_container(rng, m, k, per_row):
+    idx = rng.integers(0, 256, size=(m, k), dtype=np.uint8)
+    scale = (rng.random((m, 1 if per_row else k // 128)) * 0.01 + 0.001).astype(np.float16)
+    zero = (-128.0 * scale.astype(np.float32)).astype(np.float16) if per_row else (rng.standard_normal(scale.shape) * 0.05).astype(np.float16)
+    sz = (zero.view(np.uint16).astype(np.uint32) << 16) | scale.view(np.uint16).astype(np.uint32)
+    if per_row:
+        sz = np.repeat(sz, k // 128, axis=1)
+    return idx, np.ascontiguousarray(sz)
+
+
+def _ref_linear(x, w64):
+    return x.astype(np.float64) @ w64.T
+
+
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("shape", [(128, 128, 1), (256, 512, 3), (2560, 2560, 1), (512, 2048, 8), (1024, 512, 70), (384, 256, 300)])
+def test_linear_int8_vs_float64(path, shape):
+    # fp16/int8 GEMV / GEMM unit tests of the reference (src/backend_cuda.rs:8880-9066) with fp32-accurate bounds
+    m, k, r = shape
+    rng = np.random.default_rng(m * 7 + k + r)
+    idx, sz = _int8_container(rng, m, k, per_row=True)
+    x = rng.standard_normal((r, k)).astype(np.float32)
+    x[0, :5] = [0.0, 1e-6, -3.0, 7.5, -1e-3]
+    want = _ref_linear(x, orc.dequant_int8(idx, sz).astype(np.float64))
+    got = rsv.op_linear(x, idx, sz, path=path)
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() <= 2e-5 * scale, (path, shape, float(np.abs(got - want).max()), float(scale))
+
+
+def test_linear_int8_per_group_container_simt():
+    rng = np.random.default_rng(9)
+    idx, sz = _int8_container(rng, 256, 512, per_row=False)
+    x = rng.standard_normal((5, 512)).astype(np.float32)
+    want = _ref_linear(x, orc.dequant_int8(idx, sz).astype(np.float64))
+    got = rsv.op_linear(x, idx, sz, path=0)
+    assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max()
+    with pytest.raises(rsv.RsvError, match="tensor-core path"):
+        rsv.op_linear(x, idx, sz, path=1)
+
+
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("shape", [(128, 64, 1), (96, 512, 4), (512, 96, 9), (4096, 512, 2), (320, 2560, 33), (2560, 16, 6)])
+def test_linear_fp16_vs_float64(path, shape):
+    m, k, r = shape
+    rng = np.random.default_rng(m + k * 3 + r)
+    w = (rng.standard_normal((m, k)) * 0.02).astype(np.float16)
+    x = rng.standard_normal((r, k)).astype(np.float32)
+    want = _ref_linear(x, w.astype(np.float64))
+    got = rsv.op_linear(x, w, None, path=path)
+    assert np.abs(got - want).max() <= 2e-5 * max(np.abs(want).max(), 1e-3), (path, shape, float(np.abs(got - want).max()))
+
+
+def test_linear_tc_is_schedule_independent_and_exact_in_integers():
+    # the int8 tensor-core path accumulates exactly: integer-valued activations give the exact integer result
+    rng = np.random.default_rng(2)
+    m, k = 256, 1024
+    idx = rng.integers(0, 256, size=(m, k), dtype=np.uint8)
+    one, mz = np.float16(1.0).view(np.uint16), np.float16(-128.0).view(np.uint16)
+    sz = np.full((m, k // 128), (int(mz) << 16) | int(one), dtype=np.uint32)
+    x = rng.integers(-64, 65, size=(3, k)).astype(np.float32)
+    want = x.astype(np.int64) @ (idx.astype(np.int64) - 128).T
+    got = rsv.op_linear(x, idx, sz, path=1)
+    assert np.array_equal(got.astype(np.int64), want)
