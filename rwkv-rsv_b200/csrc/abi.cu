@@ -176,12 +176,49 @@ std::unique_ptr<rsv_ticket> selfloop_submit(Model& m, State& st, const uint32_t*
         RSV_CUDA(cudaMemcpyAsync(t.sampler, rows.data(), rows.size() * sizeof(float), cudaMemcpyHostToDevice, m.stream));
         RSV_CUDA(cudaStreamSynchronize(m.stream));  // `rows` is a stack-lifetime pageable buffer
     }
-    for (int64_t round = 0; round < n; ++round) {
+    auto one_round = [&] {
         m.forward_rows(st, p, false);
         if (sp)
             engine_sample(m, m.ws.logits, B, t.sampler, t.seq, (int)n, t.cnt, m.ws.tokens, t.seq, t.cnt, (int)n);
         else
             engine_argmax(m, m.ws.logits, B, m.ws.tokens, t.seq, t.cnt, (int)n);
+    };
+    // Round 0 runs eagerly (it also sizes every work buffer); the remaining rounds replay one captured CUDA graph
+    // of the step, as the reference replays its captured self-loop step (src/gpu_model.rs:1847-1859).  Per-kernel
+    // profiling needs event pairs between launches, so it keeps the eager path.
+    one_round();
+    if (n > 1) {
+        if (m.prof_on || !m.use_graphs) {
+            for (int64_t round = 1; round < n; ++round) one_round();
+        } else {
+            cudaGraph_t graph = nullptr;
+            cudaGraphExec_t exec = nullptr;
+            RSV_CUDA(cudaStreamBeginCapture(m.stream, cudaStreamCaptureModeThreadLocal));
+            const long launches_before = m.launches;
+            try {
+                one_round();
+            } catch (...) {
+                cudaStreamEndCapture(m.stream, &graph);
+                if (graph) cudaGraphDestroy(graph);
+                throw;
+            }
+            RSV_CUDA(cudaStreamEndCapture(m.stream, &graph));
+            const long per_round = m.launches - launches_before;
+            cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+            if (e != cudaSuccess) {
+                cudaGraphDestroy(graph);
+                throw CudaError(std::string("cudaGraphInstantiate failed: ") + cudaGetErrorString(e));
+            }
+            m.launches = launches_before;  // the capture itself launched nothing
+            for (int64_t round = 1; round < n; ++round) {
+                e = cudaGraphLaunch(exec, m.stream);
+                if (e != cudaSuccess) break;
+                m.launches += per_round;
+            }
+            t.graph = graph;
+            t.graph_exec = exec;
+            if (e != cudaSuccess) throw CudaError(std::string("cudaGraphLaunch failed: ") + cudaGetErrorString(e));
+        }
     }
     return tk;
 }

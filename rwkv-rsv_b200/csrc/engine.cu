@@ -274,6 +274,8 @@ std::unique_ptr<Model> Model::load(const std::string& path, int device) {
     m->num_sms = prop.multiProcessorCount;
     if (const char* e = getenv("RSV_TC_MIN_ROWS"))
         if (*e) m->tc_min_rows = atoi(e);
+    if (const char* e = getenv("RSV_NO_GRAPH"))
+        if (*e && *e != '0') m->use_graphs = false;
     RSV_CUDA(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
     RSV_CUDA(cudaEventCreate(&m->ev0));
     RSV_CUDA(cudaEventCreate(&m->ev1));
@@ -623,9 +625,7 @@ void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, i
     // units, tiles, CTA count
     TcLaunch L;
     memset(&L, 0, sizeof(L));
-    TcFinLaunch F;
-    memset(&F, 0, sizeof(F));
-    int U = 0, T = 0, out = 0;
+    int U = 0, T = 0;
     const int n_tiles = ncols_pad / NT;
     for (int i = 0; i < n; ++i) {
         const LinearW& W = *reqs[i].W;
@@ -642,16 +642,25 @@ void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, i
         L.amap[i] = W.amap;
     }
     const int G = std::min(m.num_sms, U);
-    int pmax = 1;
-    for (int i = 0; i < n; ++i) {
-        const TcProb& P = L.p[i];
-        const int tiles = (reqs[i].W->Mpad / kTcTileM) * n_tiles;
-        for (int t = 0; t < tiles; ++t) {
-            const int u0 = P.unit0 + t * P.kblocks;
-            pmax = std::max(pmax, tc_cta_of_unit(u0 + P.kblocks - 1, U, G) - tc_cta_of_unit(u0, U, G) + 1);
+    // tiles cut by a CTA boundary keep partial sums and are finished by tc_finalize_kernel
+    int pmax = 1, nsplit = 0;
+    for (int c = 1; c < G; ++c) {
+        const int bnd = tc_cta_begin(c, U, G);
+        int pi = 0;
+        while (pi + 1 < n && bnd >= L.p[pi + 1].unit0) ++pi;
+        const TcProb& P = L.p[pi];
+        const int local = bnd - P.unit0;
+        if (local % P.kblocks == 0) continue;  // boundary falls between tiles
+        const int tile_first = bnd - local % P.kblocks;
+        if (nsplit > 0 && L.split_unit[nsplit - 1] == tile_first) {
+            // same tile cut again
+        } else {
+            if (nsplit >= kTcMaxSplit) throw std::runtime_error("tc_linear: too many split tiles");
+            L.split_unit[nsplit++] = tile_first;
         }
+        pmax = std::max(pmax, tc_cta_of_unit(tile_first + P.kblocks - 1, U, G) - tc_cta_of_unit(tile_first, U, G) + 1);
     }
-    const size_t partial_bytes = (size_t)T * pmax * NT * kTcTileM * 4;
+    const size_t partial_bytes = (size_t)nsplit * pmax * NT * kTcTileM * 4;
     ensure_tc_buffers(m, b_bytes, (size_t)rows, partial_bytes);
     Workspace& w = m.ws;
     // operand preparation
@@ -667,43 +676,11 @@ void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, i
     }
     for (int i = 0; i < n; ++i) {
         const Region& rg = regions[region_of[i]];
-        encode_kmajor_map(&L.bmap[i], i8, w.tc_b + rg.off, ncols_pad, rg.Kpad, NT);
-    }
-    L.nprob = n;
-    L.total_units = U;
-    L.nt = NT;
-    L.is_i8 = i8;
-    L.pmax = pmax;
-    const size_t stage_bytes = (size_t)kTcTileM * kTcKBlockBytes + (size_t)NT * kTcKBlockBytes;
-    L.nstages = (int)std::min<size_t>(8, (200 * 1024) / stage_bytes);
-    L.partials = w.tc_partials;
-    L.status = w.status;
-    const size_t smem = (size_t)L.nstages * stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-    static bool configured = false;
-    if (!configured) {
-        RSV_CUDA(cudaFuncSetAttribute(tc_linear_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        RSV_CUDA(cudaFuncSetAttribute(tc_linear_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured = true;
-    }
-    LAUNCH(m, name) {
-        if (i8)
-            tc_linear_kernel<true><<<G, kTcThreads, smem, m.stream>>>(L);
-        else
-            tc_linear_kernel<false><<<G, kTcThreads, smem, m.stream>>>(L);
-        check_launch("tc_linear");
-    }
-    // finalize
-    for (int i = 0; i < n; ++i) {
         const LinReq& q = reqs[i];
-        const Region& rg = regions[region_of[i]];
-        TcFinProb& P = F.p[i];
-        P.M = q.W->M;
+        encode_kmajor_map(&L.bmap[i], i8, w.tc_b + rg.off, ncols_pad, rg.Kpad, NT);
+        TcProb& P = L.p[i];
         P.R = R;
         P.D = D;
-        P.kblocks = L.p[i].kblocks;
-        P.n_tiles = n_tiles;
-        P.unit0 = L.p[i].unit0;
-        P.tile0 = L.p[i].tile0;
         P.wscale = q.W->wscale;
         P.wzero = q.W->wzero;
         P.xscale = w.tc_xscale + rg.row0;
@@ -715,22 +692,36 @@ void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, i
         P.ldy = q.ldy;
         P.ldaux = q.ldaux;
         P.epi = q.epi;
-        P.is_i8 = i8;
-        P.out0 = out;
-        out += R * q.W->M;
     }
-    F.nprob = n;
-    F.total_out = out;
-    F.nt = NT;
-    F.pmax = pmax;
-    F.U = U;
-    F.G = G;
-    F.partials = w.tc_partials;
-    LAUNCH(m, "tc_finalize") {
-        const int blocks = std::min((out + 255) / 256, m.num_sms * 16);
-        tc_finalize_kernel<<<blocks, 256, 0, m.stream>>>(F);
-        check_launch("tc_finalize");
+    L.nprob = n;
+    L.total_units = U;
+    L.nt = NT;
+    L.is_i8 = i8;
+    L.pmax = pmax;
+    L.grid = G;
+    L.nsplit = nsplit;
+    const size_t stage_bytes = (size_t)kTcTileM * kTcKBlockBytes + (size_t)NT * kTcKBlockBytes;
+    L.nstages = (int)std::min<size_t>(8, (200 * 1024) / stage_bytes);
+    L.partials = w.tc_partials;
+    L.status = w.status;
+    const size_t smem = (size_t)L.nstages * stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static bool configured[16] = {false};
+    if (!configured[m.device & 15]) {
+        RSV_CUDA(cudaFuncSetAttribute(tc_linear_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        RSV_CUDA(cudaFuncSetAttribute(tc_linear_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured[m.device & 15] = true;
     }
+    LAUNCH(m, name) {
+        if (i8)
+            tc_linear_kernel<true><<<G, kTcThreads, smem, m.stream>>>(L);
+        else
+            tc_linear_kernel<false><<<G, kTcThreads, smem, m.stream>>>(L);
+        check_launch("tc_linear");
+    }
+    if (nsplit) LAUNCH(m, "tc_finalize") {
+            tc_finalize_kernel<<<dim3(nsplit, std::max(1, std::min(8, NT / 16))), 256, 0, m.stream>>>(L);
+            check_launch("tc_finalize");
+        }
 }
 
 void run_linear(Model& m, const char* name, const LinReq* reqs, int n, int R) {
@@ -882,7 +873,12 @@ void engine_sample_raw(cudaStream_t stream, const float* logits_dev, int rows, i
 }
 
 Ticket::~Ticket() {
-    if (model) cudaSetDevice(model->device);
+    if (model) {
+        cudaSetDevice(model->device);
+        if (graph_exec || graph) cudaStreamSynchronize(model->stream);
+    }
+    if (graph_exec) cudaGraphExecDestroy(graph_exec);
+    if (graph) cudaGraphDestroy(graph);
     if (seq) cudaFree(seq);
     if (cnt) cudaFree(cnt);
     if (sampler) cudaFree(sampler);

@@ -117,6 +117,7 @@ struct Model {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr, tev[2] = {nullptr, nullptr};
     long launches = 0;  // kernels launched since the counter was last cleared
     int num_sms = 148;
+    bool use_graphs = true;  // replay self-loop rounds from a captured CUDA graph (RSV_NO_GRAPH=1 disables)
     int tc_min_rows = 5;  // packed steps with at least this many rows use the tensor-core linear path
 
     static std::unique_ptr<Model> create_bare(int device);  // stream + events only (operator-level entry points)
@@ -139,6 +140,8 @@ struct Ticket {
     uint32_t* seq = nullptr;   // [batch, n] generated tokens
     int* cnt = nullptr;        // [batch] tokens generated so far per slot
     float* sampler = nullptr;  // [batch, 8] sampler rows (null for arg-max)
+    cudaGraph_t graph = nullptr;  // captured step, alive until the queued replays have been collected
+    cudaGraphExec_t graph_exec = nullptr;
     ~Ticket();
 };
 

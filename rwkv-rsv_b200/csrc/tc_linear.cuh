@@ -21,7 +21,8 @@
 // units inside one tile accumulates in TMEM and is written as an int32/fp32 partial [slot][n][m]; a second small
 // kernel adds a tile's partials in slot order, applies scale/zero and the fused epilogue.
 //
-// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2-5 = epilogue.
+// Roles per CTA (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2-9 = epilogue
+// (two warps per TMEM lane quarter, alternating 16-column chunks).
 // Every wait on an mbarrier is bounded; on expiry the kernel raises bit 1 of the status word and drains.
 #pragma once
 #include <cuda.h>
@@ -30,7 +31,7 @@
 
 namespace rsv {
 
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
 constexpr int kTcTileM = 128;
 constexpr int kTcKBlockBytes = 128;
 constexpr int kTcMaxProblems = 8;
@@ -39,18 +40,31 @@ constexpr uint32_t kTcSpinLimit = 1u << 26;  // ~ seconds; far beyond any legiti
 struct TcProb {
     int M;        // output rows (weights rows)
     int kblocks;  // K in 128-byte blocks
-    int ncols;    // valid B columns
+    int ncols;    // valid B columns (= R * D)
     int n_tiles;  // ceil(ncols / nt)
     int unit0;    // first unit of this problem
     int tile0;    // first (M tile, N tile) index of this problem in the partial buffer
+    int R, D;     // activation rows; B columns per row (int8: digits, fp16: 2 = hi/lo)
+    // epilogue
+    const float* wscale;    // int8: [M] per-row scale and zero of the container
+    const float* wzero;
+    const float* xscale;    // [R]
+    const long long* tsum;  // int8: [R]
+    float* y;
+    float* y2;
+    const float* bias;
+    const float* aux;
+    int ldy, ldaux, epi, pad;
 };
+constexpr int kTcMaxSplit = 320;  // a CTA boundary can cut at most one tile: < number of CTAs
 struct alignas(64) TcLaunch {
     CUtensorMap amap[kTcMaxProblems];
     CUtensorMap bmap[kTcMaxProblems];
     TcProb p[kTcMaxProblems];
-    int nprob, total_units, nt, is_i8, pmax, nstages;
-    void* partials;  // [tile][pmax][nt][128] int32 or fp32
+    int nprob, total_units, nt, is_i8, pmax, nstages, grid, nsplit;
+    void* partials;  // [cut tile][pmax][nt][128] int32 or fp32
     int* status;
+    int split_unit[kTcMaxSplit];  // first unit of every tile that is cut by a CTA boundary
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -167,6 +181,72 @@ __device__ __forceinline__ TcUnit tc_decode(const TcLaunch& L, int u) {
 __host__ __device__ __forceinline__ int tc_cta_begin(int c, int U, int G) { return (int)(((long long)c * U) / G); }
 __host__ __device__ __forceinline__ int tc_cta_of_unit(int u, int U, int G) { return (int)((((long long)u + 1) * G - 1) / U); }
 
+// Fused epilogue for NR activation rows (r0 .. r0+NR-1) of one output m.  Loads that the epilogue needs (the
+// old y for += and v-lerp, aux) are issued together before any of them is used, so a thread keeps NR (or 2 NR)
+// independent requests in flight instead of one.
+__device__ __forceinline__ bool tc_epi_reads_y(int epi) { return epi == EPI_ADD || epi == EPI_VLERP; }
+template <int NR>
+__device__ __forceinline__ void tc_epilogue_rows(const TcProb& P, int r0, int m, float bias, const float (&acc)[NR]) {
+    float yold[NR], aux[NR];
+    const bool ry = tc_epi_reads_y(P.epi), ra = P.epi == EPI_VLERP;
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+        yold[i] = 0.f;
+        aux[i] = 0.f;
+        if (r0 + i < P.R) {
+            if (ry) yold[i] = P.y[(size_t)(r0 + i) * P.ldy + m];
+            if (ra) aux[i] = P.aux[(size_t)(r0 + i) * P.ldaux + m];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+        if (r0 + i >= P.R) continue;
+        const float a = acc[i];
+        float out;
+        switch (P.epi) {
+            case EPI_ADD: out = yold[i] + a; break;
+            case EPI_RELU2: {
+                const float t = fmaxf(a, 0.f);
+                out = t * t;
+                break;
+            }
+            case EPI_TANH: out = tanhf(a); break;
+            case EPI_SIGMOID: out = 1.0f / (1.0f + expf(-a)); break;
+            case EPI_DECAY: out = expf((1.0f / (1.0f + expf(-(a + bias)))) * kDecayScale); break;
+            case EPI_SIGMOID_BIAS: out = 1.0f / (1.0f + expf(-(a + bias))); break;
+            case EPI_VLERP: {
+                const float gate = 1.0f / (1.0f + expf(-(a + bias)));
+                out = yold[i] + gate * (aux[i] - yold[i]);
+                break;
+            }
+            default: out = a; break;  // EPI_STORE
+        }
+        P.y[(size_t)(r0 + i) * P.ldy + m] = out;
+        if (P.epi == EPI_STORE && P.y2) P.y2[(size_t)(r0 + i) * P.ldy + m] = out;
+    }
+}
+// 16 accumulator columns -> outputs.  int8: 4 activation rows x 4 digits; fp16: 8 rows x (hi, lo).
+template <bool I8>
+__device__ __forceinline__ void tc_finish16(const TcProb& P, int n0, int m, float ws, float wz, float bias, const long long (&Q)[4],
+                                            const float (&fsum)[8]) {
+    if constexpr (I8) {
+        float acc[4];
+        const int r0 = n0 >> 2;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = min(r0 + i, P.R - 1);
+            acc[i] = (float)((double)P.xscale[r] * ((double)ws * (double)Q[i] + (double)wz * (double)P.tsum[r]));
+        }
+        tc_epilogue_rows<4>(P, r0, m, bias, acc);
+    } else {
+        float acc[8];
+        const int r0 = n0 >> 1;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = P.xscale[min(r0 + i, P.R - 1)] * fsum[i];
+        tc_epilogue_rows<8>(P, r0, m, bias, acc);
+    }
+}
+
 template <bool I8>
 __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_constant__ TcLaunch L) {
     extern __shared__ __align__(1024) uint8_t tc_smem_raw[];
@@ -193,7 +273,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+            mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -275,15 +355,57 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
             if (!__all_sync(0xffffffffu, got)) break;
             tc_fence_after();
             const int ncols = min(NT, P.ncols - un.nt * NT);
-            uint32_t* dst = reinterpret_cast<uint32_t*>(L.partials) + ((size_t)un.tile * L.pmax + slot) * ((size_t)NT * kTcTileM);
             const int row = q * 32 + lane;
+            const int chalf = (warp - 2) >> 2;  // which of the two warps of this lane quarter
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (run & 1) * NT;
-            for (int c0 = 0; c0 < ncols; c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(taddr + c0, v);
+            const bool whole = (u == tile_first) && (run_end == tile_first + P.kblocks);
+            if (whole) {
+                // the run holds the complete K sum: scale and store the outputs directly
+                const int m = un.mt * kTcTileM + row;
+                const bool mok = m < P.M;
+                float ws = 0.f, wz = 0.f, bias = 0.f;
+                if (mok) {
+                    if (I8) {
+                        ws = P.wscale[m];
+                        wz = P.wzero[m];
+                    }
+                    if (P.bias) bias = P.bias[m];
+                }
+                for (int c0 = chalf * 16; c0 < ncols; c0 += 32) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + c0, v);
+                    if (mok) {
+                        long long Q[4];
+                        float fs[8];
+                        if (I8) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (c0 + j < ncols) dst[(size_t)(c0 + j) * kTcTileM + row] = v[j];
+                            for (int i = 0; i < 4; ++i) {
+                                long long t = (int)v[4 * i];
+                                t = t * 128 + (int)v[4 * i + 1];
+                                t = t * 128 + (int)v[4 * i + 2];
+                                Q[i] = t * 128 + (int)v[4 * i + 3];
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) fs[i] = __uint_as_float(v[2 * i]) + __uint_as_float(v[2 * i + 1]);
+                        }
+                        tc_finish16<I8>(P, un.nt * NT + c0, m, ws, wz, bias, Q, fs);
+                    }
+                }
+            } else {
+                int lo = 0, hi = L.nsplit - 1;  // ordinal of this tile among the cut tiles (sorted by first unit)
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (L.split_unit[mid] < tile_first) lo = mid + 1; else hi = mid;
+                }
+                uint32_t* dst = reinterpret_cast<uint32_t*>(L.partials) + ((size_t)lo * L.pmax + slot) * ((size_t)NT * kTcTileM);
+                for (int c0 = chalf * 16; c0 < ncols; c0 += 32) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + c0, v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c0 + j < ncols) dst[(size_t)(c0 + j) * kTcTileM + row] = v[j];
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -404,86 +526,58 @@ __global__ void __launch_bounds__(kPrepThreads) tc_prepare_f16_kernel(const floa
 }
 
 // ------------------------------------------------------------------------------------------------
-// Finalize: add a tile's partials in slot order, undo the fixed-point / split representation, apply the
-// weight row's (scale, zero) and the fused epilogue.  One thread per (activation row r, output m).
+// Finalize the tiles that a CTA boundary cut: add the tile's partials in slot order (exact for int32, fixed
+// order for fp32), then scale and store like the in-kernel epilogue.  One CTA per cut tile.
 // ------------------------------------------------------------------------------------------------
-struct TcFinProb {
-    int M, R, D;          // D digits (int8) or 2 (fp16 hi/lo)
-    int kblocks, n_tiles, unit0, tile0;
-    const float* wscale;  // int8: [M] per-row scale and zero of the container
-    const float* wzero;
-    const float* xscale;       // [R]
-    const long long* tsum;     // int8: [R]
-    float* y;
-    float* y2;
-    const float* bias;
-    const float* aux;
-    int ldy, ldaux, epi, is_i8;
-    int out0;  // first flat output index (r*M + m) of this problem in the launch
-};
-struct TcFinLaunch {
-    TcFinProb p[kTcMaxProblems];
-    int nprob, total_out, nt, pmax, U, G;
-    const void* partials;
-};
-__device__ __forceinline__ void tc_store_epi(const TcFinProb& P, int r, int m, float acc) {
-    float* yp = P.y + (size_t)r * P.ldy + m;
-    switch (P.epi) {
-        case EPI_STORE:
-            *yp = acc;
-            if (P.y2) P.y2[(size_t)r * P.ldy + m] = acc;
-            break;
-        case EPI_ADD: *yp += acc; break;
-        case EPI_RELU2: {
-            const float t = fmaxf(acc, 0.f);
-            *yp = t * t;
-            break;
-        }
-        case EPI_TANH: *yp = tanhf(acc); break;
-        case EPI_SIGMOID: *yp = 1.0f / (1.0f + expf(-acc)); break;
-        case EPI_DECAY: *yp = expf((1.0f / (1.0f + expf(-(acc + P.bias[m])))) * kDecayScale); break;
-        case EPI_SIGMOID_BIAS: *yp = 1.0f / (1.0f + expf(-(acc + P.bias[m]))); break;
-        case EPI_VLERP: {
-            const float v = *yp;
-            const float gate = 1.0f / (1.0f + expf(-(acc + P.bias[m])));
-            *yp = v + gate * (P.aux[(size_t)r * P.ldaux + m] - v);
-            break;
-        }
-    }
-}
-__global__ void __launch_bounds__(256) tc_finalize_kernel(const __grid_constant__ TcFinLaunch L) {
-    for (int o = blockIdx.x * blockDim.x + threadIdx.x; o < L.total_out; o += gridDim.x * blockDim.x) {
-        int pi = 0;
-        while (pi + 1 < L.nprob && o >= L.p[pi + 1].out0) ++pi;
-        const TcFinProb& P = L.p[pi];
-        const int local = o - P.out0;
-        const int r = local / P.M, m = local - r * P.M;
-        const int mt = m >> 7, ml = m & 127;
-        const int ncol0 = r * P.D;  // first B column of this activation row
-        double result = 0.0;
-        long long Q = 0;
-        float facc = 0.f;
-        for (int j = 0; j < P.D; ++j) {
-            const int n = ncol0 + j, nt = n / L.nt, nl = n - nt * L.nt;
-            const int t = mt * P.n_tiles + nt;  // tile index inside the problem
-            const int tile_first = P.unit0 + t * P.kblocks;
-            const int c_lo = tc_cta_of_unit(tile_first, L.U, L.G), c_hi = tc_cta_of_unit(tile_first + P.kblocks - 1, L.U, L.G);
-            const size_t base = ((size_t)(P.tile0 + t) * L.pmax) * ((size_t)L.nt * kTcTileM) + (size_t)nl * kTcTileM + ml;
-            if (P.is_i8) {
-                long long I = 0;
-                for (int s = 0; s <= c_hi - c_lo; ++s) I += reinterpret_cast<const int*>(L.partials)[base + (size_t)s * L.nt * kTcTileM];
-                Q = Q * 128 + I;
-            } else {
-                float f = 0.f;
-                for (int s = 0; s <= c_hi - c_lo; ++s) f += reinterpret_cast<const float*>(L.partials)[base + (size_t)s * L.nt * kTcTileM];
-                facc += f;
+__global__ void __launch_bounds__(256) tc_finalize_kernel(const __grid_constant__ TcLaunch L) {
+    const int tile_first = L.split_unit[blockIdx.x];
+    const TcUnit un = tc_decode(L, tile_first);
+    const TcProb& P = L.p[un.p];
+    const int U = L.total_units, G = L.grid, NT = L.nt;
+    const int c_lo = tc_cta_of_unit(tile_first, U, G), c_hi = tc_cta_of_unit(tile_first + P.kblocks - 1, U, G);
+    const int nslots = c_hi - c_lo + 1;
+    const size_t slot_stride = (size_t)NT * kTcTileM;
+    const size_t base = (size_t)blockIdx.x * L.pmax * slot_stride;
+    const int ncols = min(NT, P.ncols - un.nt * NT);
+    const int ngroups = (ncols + 15) / 16;  // groups of 16 columns
+    for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < ngroups * kTcTileM; idx += gridDim.y * blockDim.x) {
+        const int grp = idx >> 7, ml = idx & 127;
+        const int m = un.mt * kTcTileM + ml;
+        if (m >= P.M) continue;
+        const size_t off = base + (size_t)(grp * 16) * kTcTileM + ml;
+        float bias = P.bias ? P.bias[m] : 0.f;
+        long long Q[4] = {0, 0, 0, 0};
+        float fs[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (L.is_i8) {
+            int I[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) I[j] = 0;
+            for (int sl = 0; sl < nslots; ++sl) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (grp * 16 + j < ncols) I[j] += reinterpret_cast<const int*>(L.partials)[off + (size_t)sl * slot_stride + (size_t)j * kTcTileM];
             }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                long long t = I[4 * i];
+                t = t * 128 + I[4 * i + 1];
+                t = t * 128 + I[4 * i + 2];
+                Q[i] = t * 128 + I[4 * i + 3];
+            }
+            tc_finish16<true>(P, un.nt * NT + grp * 16, m, P.wscale[m], P.wzero[m], bias, Q, fs);
+        } else {
+            float f[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) f[j] = 0.f;
+            for (int sl = 0; sl < nslots; ++sl) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (grp * 16 + j < ncols) f[j] += reinterpret_cast<const float*>(L.partials)[off + (size_t)sl * slot_stride + (size_t)j * kTcTileM];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) fs[i] = f[2 * i] + f[2 * i + 1];
+            tc_finish16<false>(P, un.nt * NT + grp * 16, m, 0.f, 0.f, bias, Q, fs);
         }
-        if (P.is_i8)
-            result = (double)P.xscale[r] * ((double)P.wscale[m] * (double)Q + (double)P.wzero[m] * (double)P.tsum[r]);
-        else
-            result = (double)P.xscale[r] * (double)facc;
-        tc_store_epi(P, r, m, (float)result);
     }
 }
 
