@@ -102,6 +102,11 @@ void decode_tokens(Model& m, State& st, const uint32_t* tokens, int64_t n) {
     m.upload_plan(with_head);
     ensure_tok_list(m, (size_t)n);
     RSV_CUDA(cudaMemcpyAsync(m.ws.tok_list, tokens, (size_t)n * sizeof(uint32_t), cudaMemcpyHostToDevice, m.stream));
+    if (!m.prof_on && m.persistent_available(1)) {
+        const int slot0 = 0;
+        m.run_persistent(st, 1, &slot0, (int)n, true, false, nullptr, nullptr, 0);  // all n tokens in one launch, head on the last
+        return;
+    }
     RSV_CUDA(cudaMemsetAsync(m.ws.tok_pos, 0, sizeof(int), m.stream));
     for (int64_t i = 0; i < n; ++i) m.forward_rows(st, i == n - 1 ? with_head : no_head, true);
 }
@@ -183,6 +188,19 @@ std::unique_ptr<rsv_ticket> selfloop_submit(Model& m, State& st, const uint32_t*
         else
             engine_argmax(m, m.ws.logits, B, m.ws.tokens, t.seq, t.cnt, (int)n);
     };
+    if (!m.prof_on && B <= 4 && m.persistent_available(B)) {
+        // up to 4 sessions: the persistent kernel runs whole steps (and, for arg-max, the whole self-loop) in one launch
+        int slots[4] = {0, 1, 2, 3};
+        if (!sp) {
+            m.run_persistent(st, B, slots, (int)n, false, true, t.seq, t.cnt, (int)n);
+        } else {
+            for (int64_t round = 0; round < n; ++round) {
+                m.run_persistent(st, B, slots, 1, false, false, nullptr, nullptr, 0);
+                engine_sample(m, m.ws.logits, B, t.sampler, t.seq, (int)n, t.cnt, m.ws.tokens, t.seq, t.cnt, (int)n);
+            }
+        }
+        return tk;
+    }
     // Round 0 runs eagerly (it also sizes every work buffer); the remaining rounds replay one captured CUDA graph
     // of the step, as the reference replays its captured self-loop step (src/gpu_model.rs:1847-1859).  Per-kernel
     // profiling needs event pairs between launches, so it keeps the eager path.

@@ -7,6 +7,7 @@
 #include "kernels.cuh"
 #include "safetensors.hpp"
 #include "tc_linear.cuh"
+#include "decode_persistent.cuh"
 
 namespace rsv {
 
@@ -274,6 +275,8 @@ std::unique_ptr<Model> Model::load(const std::string& path, int device) {
     m->num_sms = prop.multiProcessorCount;
     if (const char* e = getenv("RSV_TC_MIN_ROWS"))
         if (*e) m->tc_min_rows = atoi(e);
+    if (const char* e = getenv("RSV_NO_PERSISTENT"))
+        if (*e && *e != '0') m->use_persistent = false;
     if (const char* e = getenv("RSV_NO_GRAPH"))
         if (*e && *e != '0') m->use_graphs = false;
     RSV_CUDA(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
@@ -394,6 +397,13 @@ Model::~Model() {
     for (void* p : allocs) cudaFree(p);
     for (void* p : {(void*)ws.tc_b, (void*)ws.tc_xscale, (void*)ws.tc_tsum, ws.tc_partials})
         if (p) cudaFree(p);
+    for (void* p : {pctx.d_layers, pctx.d_maps, (void*)pctx.x, (void*)pctx.yg, (void*)pctx.vfirst, (void*)pctx.cand_val, (void*)pctx.cand_idx,
+                    (void*)pctx.grid_bar})
+        if (p) cudaFree(p);
+    for (int i = 0; i < 5; ++i) {
+        if (pctx.region_data[i]) cudaFree(pctx.region_data[i]);
+        if (pctx.region_meta[i]) cudaFree(pctx.region_meta[i]);
+    }
     if (pinned) cudaFreeHost(pinned);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
@@ -833,12 +843,271 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
         }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// persistent decode kernel: host side
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+DpMat make_dpmat(const LinearW& W, int map_index) {
+    DpMat d;
+    d.map = map_index;
+    d.M = W.M;
+    d.mtiles = W.Mpad / kTcTileM;
+    d.is_i8 = W.wtype == W_INT8;
+    d.kblocks = (int)((size_t)W.Kpad * (d.is_i8 ? 1 : 2) / kTcKBlockBytes);
+    d.K = W.K;
+    d.wscale = W.wscale;
+    d.wzero = W.wzero;
+    return d;
+}
+struct HostProb {
+    int mtiles, kblocks;
+};
+// largest number of CTAs that share one tile, and the largest number of operand tiles a CTA needs, for a phase
+void phase_shape(const std::vector<HostProb>& probs, int G, int& pmax, int& btiles, int& tiles) {
+    int U = 0;
+    for (auto& q : probs) U += q.mtiles * q.kblocks;
+    G = std::min(G, U);  // only the first min(G, U) CTAs take part in a phase
+    tiles = 0;
+    pmax = 1;
+    int u0 = 0;
+    for (auto& q : probs) {
+        for (int t = 0; t < q.mtiles; ++t) {
+            const int first = u0 + t * q.kblocks;
+            pmax = std::max(pmax, tc_cta_of_unit(first + q.kblocks - 1, U, G) - tc_cta_of_unit(first, U, G) + 1);
+        }
+        u0 += q.mtiles * q.kblocks;
+        tiles += q.mtiles;
+    }
+    btiles = 0;
+    for (int c = 0; c < G; ++c) {
+        const int ub = tc_cta_begin(c, U, G), ue = tc_cta_begin(c + 1, U, G);
+        int need = 0, p0 = 0;
+        for (auto& q : probs) {
+            const int lo = std::max(ub, p0), hi = std::min(ue, p0 + q.mtiles * q.kblocks);
+            if (hi > lo) need += std::min(hi - lo, q.kblocks);
+            p0 += q.mtiles * q.kblocks;
+        }
+        btiles = std::max(btiles, need);
+    }
+}
+
+}  // namespace
+
+bool Model::persistent_available(int nb) {
+    if (!use_persistent || nb < 1 || nb > kDpMaxNB) return false;
+    PersistentCtx& pc = pctx;
+    if (pc.tried) return pc.ok;
+    pc.tried = true;
+    auto fail = [&](const std::string& why) {
+        pc.why = why;
+        pc.ok = false;
+        return false;
+    };
+    RSV_CUDA(cudaSetDevice(device));
+    int coop = 0;
+    RSV_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));
+    if (!coop) return fail("device does not support cooperative launches");
+    if (!head.tc_ok) return fail("head matrix cannot take the tensor-core path");
+    for (const LayerW& L : layers)
+        for (const LinearW* W : {&L.Wr, &L.Wk, &L.Wv, &L.Wo, &L.Wfk, &L.Wfv, &L.w1, &L.a1, &L.v1, &L.g1})
+            if (!W->tc_ok) return fail("a weight matrix cannot take the tensor-core path (int8 files need one scale/zero per output row)");
+    const int L = cfg.n_layer, C = cfg.n_embd;
+    // tensor maps and per-layer tables
+    std::vector<CUtensorMap> maps;
+    std::vector<DpLayer> dl(L);
+    auto add = [&](const LinearW& W) {
+        maps.push_back(W.amap);
+        return make_dpmat(W, (int)maps.size() - 1);
+    };
+    for (int l = 0; l < L; ++l) {
+        const LayerW& Lw = layers[l];
+        DpLayer& d = dl[l];
+        memset(&d, 0, sizeof(d));
+        d.Wr = add(Lw.Wr);
+        d.Wk = add(Lw.Wk);
+        d.Wv = add(Lw.Wv);
+        d.Wo = add(Lw.Wo);
+        d.Wfk = add(Lw.Wfk);
+        d.Wfv = add(Lw.Wfv);
+        d.w1 = add(Lw.w1);
+        d.a1 = add(Lw.a1);
+        d.v1 = add(Lw.v1);
+        d.g1 = add(Lw.g1);
+        d.w2 = (const __half*)Lw.w2.w;
+        d.a2 = (const __half*)Lw.a2.w;
+        d.v2 = (const __half*)Lw.v2.w;
+        d.g2 = (const __half*)Lw.g2.w;
+        d.ln1_w = Lw.ln1_w;
+        d.ln1_b = Lw.ln1_b;
+        d.ln2_w = Lw.ln2_w;
+        d.ln2_b = Lw.ln2_b;
+        d.lnx_w = Lw.lnx_w;
+        d.lnx_b = Lw.lnx_b;
+        d.x_r = Lw.x_r;
+        d.x_w = Lw.x_w;
+        d.x_k = Lw.x_k;
+        d.x_v = Lw.x_v;
+        d.x_a = Lw.x_a;
+        d.x_g = Lw.x_g;
+        d.ffn_x_k = Lw.ffn_x_k;
+        d.w0 = Lw.w0;
+        d.a0 = Lw.a0;
+        d.v0 = Lw.v0;
+        d.r_k = Lw.r_k;
+        d.k_k = Lw.k_k;
+        d.k_a = Lw.k_a;
+    }
+    DpParams P;
+    memset(&P, 0, sizeof(P));
+    P.head = add(head);
+    const int G = num_sms;
+    // phase shapes (layer 0 has no v1 problem; all layers share the matrix shapes)
+    auto hp = [&](const DpMat& d) { return HostProb{d.mtiles, d.kblocks}; };
+    const DpLayer& d0 = dl[0];
+    std::vector<HostProb> p1a = {hp(d0.Wr), hp(d0.Wk), hp(d0.Wv), hp(d0.w1), hp(d0.a1), hp(d0.g1)};
+    std::vector<HostProb> p1b = p1a;
+    p1b.push_back(hp(d0.v1));
+    int pm, bt, tl, pmax[5], tiles[5], btiles = 0;
+    phase_shape(p1a, G, pm, bt, tl);
+    pmax[0] = pm;
+    btiles = std::max(btiles, bt);
+    phase_shape(p1b, G, pm, bt, tl);
+    pmax[0] = std::max(pmax[0], pm);
+    tiles[0] = tl;
+    btiles = std::max(btiles, bt);
+    const DpMat* single[4] = {&d0.Wo, &d0.Wfk, &d0.Wfv, &P.head};
+    for (int i = 0; i < 4; ++i) {
+        phase_shape({hp(*single[i])}, G, pm, bt, tl);
+        pmax[i + 1] = pm;
+        tiles[i + 1] = tl;
+        btiles = std::max(btiles, bt);
+    }
+    // shared memory: ring + operand tiles + barriers + worker scratch
+    const size_t fixed = (size_t)btiles * kDpBTile + 1024 /*alignment*/ + 4096 /*barriers, small scratch*/ + (size_t)btiles * kDpMaxNB * 8 +
+                         (size_t)cfg.mids() * 4 + 8 * 64 * 4;
+    const size_t budget = 227 * 1024;
+    if (fixed + 3 * (size_t)kDpATile > budget) return fail("operand tiles do not fit in shared memory for this shape");
+    const int nstages = (int)std::min<size_t>(10, (budget - fixed) / kDpATile);
+    pc.smem = fixed + (size_t)nstages * kDpATile;
+    pc.grid = G;
+    pc.nstages = nstages;
+    pc.btiles = btiles;
+    RSV_CUDA(cudaFuncSetAttribute(decode_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pc.smem));
+    int per_sm = 0;
+    RSV_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_persistent_kernel, kDpThreads, pc.smem));
+    if (per_sm < 1) return fail("persistent kernel does not fit on an SM");
+    // device tables and scratch
+    RSV_CUDA(cudaMalloc(&pc.d_layers, dl.size() * sizeof(DpLayer)));
+    RSV_CUDA(cudaMalloc(&pc.d_maps, maps.size() * sizeof(CUtensorMap)));
+    RSV_CUDA(cudaMemcpy(pc.d_maps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+    RSV_CUDA(cudaMalloc(&pc.x, (size_t)kDpMaxNB * C * 4));
+    RSV_CUDA(cudaMalloc(&pc.yg, (size_t)kDpMaxNB * C * 4));
+    RSV_CUDA(cudaMalloc(&pc.vfirst, (size_t)kDpMaxNB * C * 4));
+    RSV_CUDA(cudaMalloc(&pc.cand_val, (size_t)G * kDpMaxNB * 4));
+    RSV_CUDA(cudaMalloc(&pc.cand_idx, (size_t)G * kDpMaxNB * 4));
+    RSV_CUDA(cudaMalloc(&pc.grid_bar, 4));
+    RSV_CUDA(cudaMemset(pc.vfirst, 0, (size_t)kDpMaxNB * C * 4));
+    for (int i = 0; i < 5; ++i) {
+        const size_t runs = (size_t)tiles[i] * pmax[i];
+        RSV_CUDA(cudaMalloc(&pc.region_data[i], runs * kDpN * 128 * 4));
+        RSV_CUDA(cudaMalloc(&pc.region_meta[i], runs * sizeof(DpRunMeta)));
+        RSV_CUDA(cudaMemset(pc.region_data[i], 0, runs * kDpN * 128 * 4));
+        RSV_CUDA(cudaMemset(pc.region_meta[i], 0, runs * sizeof(DpRunMeta)));
+        pc.region_pmax[i] = pmax[i];
+    }
+    // layer tables need the state pointers of the call: only the state-independent part is stored here
+    pc.params_template.resize(sizeof(DpParams) + dl.size() * sizeof(DpLayer));
+    P.maps = (const CUtensorMap*)pc.d_maps;
+    P.layers = (const DpLayer*)pc.d_layers;
+    P.emb = emb;
+    P.ln0_w = ln0_w;
+    P.ln0_b = ln0_b;
+    P.lno_w = ln_out_w;
+    P.lno_b = ln_out_b;
+    P.L = L;
+    P.C = C;
+    P.H = cfg.n_head;
+    P.F = cfg.ffn_hidden;
+    P.V = cfg.vocab;
+    P.wm = cfg.w_mid;
+    P.am = cfg.a_mid;
+    P.vm = cfg.v_mid;
+    P.gm = cfg.g_mid;
+    P.x = pc.x;
+    P.yg = pc.yg;
+    P.vfirst = pc.vfirst;
+    for (int i = 0; i < 5; ++i) {
+        P.reg[i].data = (uint32_t*)pc.region_data[i];
+        P.reg[i].meta = (DpRunMeta*)pc.region_meta[i];
+        P.reg[i].pmax = pmax[i];
+    }
+    P.cand_val = pc.cand_val;
+    P.cand_idx = pc.cand_idx;
+    P.grid_bar = pc.grid_bar;
+    P.status = ws.status;
+    P.nstages = nstages;
+    P.btiles = btiles;
+    memcpy(pc.params_template.data(), &P, sizeof(P));
+    memcpy(pc.params_template.data() + sizeof(P), dl.data(), dl.size() * sizeof(DpLayer));
+    pc.ok = true;
+    return true;
+}
+
+void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bool tok_from_list, bool argmax_feed, uint32_t* seq_dev, int* seq_cnt_dev,
+                           int seq_cap) {
+    if (!persistent_available(nb)) throw std::runtime_error("persistent decode path unavailable: " + pctx.why);
+    PersistentCtx& pc = pctx;
+    RSV_CUDA(cudaSetDevice(device));
+    const int L = cfg.n_layer, C = cfg.n_embd, H = cfg.n_head;
+    ensure_workspace(std::max(nb, 1), std::max(nb, 1), std::max(nb, 1));
+    DpParams P;
+    memcpy(&P, pc.params_template.data(), sizeof(P));
+    // the device layer table carries the state pointers: rewrite it only when another state is used
+    if (pc.bound_tmix != st.tmix_x || pc.bound_wkv != st.wkv || pc.bound_cmix != st.cmix_x) {
+        std::vector<DpLayer> dl(L);
+        memcpy(dl.data(), pc.params_template.data() + sizeof(P), dl.size() * sizeof(DpLayer));
+        const size_t lay_x = (size_t)st.cap * C, lay_s = (size_t)st.cap * H * kHeadSize * kHeadSize;
+        for (int l = 0; l < L; ++l) {
+            dl[l].tmix_x = st.tmix_x + l * lay_x;
+            dl[l].cmix_x = st.cmix_x + l * lay_x;
+            dl[l].wkv = st.wkv + l * lay_s;
+        }
+        RSV_CUDA(cudaStreamSynchronize(stream));  // earlier launches may still read the table
+        RSV_CUDA(cudaMemcpyAsync(pc.d_layers, dl.data(), dl.size() * sizeof(DpLayer), cudaMemcpyHostToDevice, stream));
+        RSV_CUDA(cudaStreamSynchronize(stream));  // `dl` is a local pageable buffer
+        pc.bound_tmix = st.tmix_x;
+        pc.bound_wkv = st.wkv;
+        pc.bound_cmix = st.cmix_x;
+    }
+    P.nb = nb;
+    for (int b = 0; b < kDpMaxNB; ++b) P.slot[b] = b < nb ? slots[b] : 0;
+    P.state_vfirst = st.v_first;
+    P.tokens = ws.tokens;
+    P.tok_list = ws.tok_list;
+    P.seq = seq_dev;
+    P.seq_cnt = seq_cnt_dev;
+    P.seq_cap = seq_cap;
+    P.logits = ws.logits;
+    P.status = ws.status;
+    P.n_tokens = n_tokens;
+    P.tok_from_list = tok_from_list ? 1 : 0;
+    P.argmax_feed = argmax_feed ? 1 : 0;
+    RSV_CUDA(cudaMemsetAsync(pc.grid_bar, 0, 4, stream));
+    void* args[] = {&P};
+    LAUNCH(*this, "decode_persistent") {
+        RSV_CUDA(cudaLaunchCooperativeKernel((const void*)decode_persistent_kernel, dim3(pc.grid), dim3(kDpThreads), args, pc.smem, stream));
+    }
+}
+
 void Model::check_status() {
     int s = 0;
     RSV_CUDA(cudaMemcpyAsync(&s, ws.status, sizeof(int), cudaMemcpyDeviceToHost, stream));
     RSV_CUDA(cudaStreamSynchronize(stream));
     if (s) {
         RSV_CUDA(cudaMemsetAsync(ws.status, 0, sizeof(int), stream));
+        if (s & 4) throw std::runtime_error("persistent decode kernel gave up waiting on a barrier (device status bit 2)");
         if (s & 2) throw std::runtime_error("tensor-core kernel gave up waiting on a barrier (device status bit 1)");
         if (s & 1) throw std::runtime_error("token id out of range (>= vocab); the embedding row 0 was used instead");
         throw std::runtime_error("device status word = " + std::to_string(s));

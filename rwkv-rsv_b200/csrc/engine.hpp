@@ -71,6 +71,24 @@ struct Workspace {
     int* tok_pos = nullptr;  // cursor into tok_list
 };
 
+// Device-side tables and scratch of the persistent decode kernel (built on first use).
+struct PersistentCtx {
+    bool tried = false, ok = false;
+    std::string why;            // reason when the model cannot take the persistent path
+    void* d_layers = nullptr;   // DpLayer[L]
+    void* d_maps = nullptr;     // CUtensorMap[]
+    float *x = nullptr, *yg = nullptr, *vfirst = nullptr, *cand_val = nullptr;
+    int* cand_idx = nullptr;
+    unsigned* grid_bar = nullptr;
+    void* region_data[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    void* region_meta[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    int region_pmax[5] = {1, 1, 1, 1, 1};
+    int grid = 0, nstages = 0, btiles = 0;
+    size_t smem = 0;
+    std::vector<char> params_template;  // DpParams with everything but the per-call fields
+    const float *bound_tmix = nullptr, *bound_wkv = nullptr, *bound_cmix = nullptr;  // state whose pointers the device layer table holds
+};
+
 struct KernelProf {
     double ms = 0;
     long launches = 0;
@@ -119,6 +137,14 @@ struct Model {
     int num_sms = 148;
     bool use_graphs = true;  // replay self-loop rounds from a captured CUDA graph (RSV_NO_GRAPH=1 disables)
     int tc_min_rows = 5;  // packed steps with at least this many rows use the tensor-core linear path
+
+    bool use_persistent = true;  // batch <= 4 decode goes through the persistent kernel (RSV_NO_PERSISTENT=1 disables)
+    PersistentCtx pctx;
+    // Persistent decode: n_tokens steps for nb <= 4 sessions (slots[b] of `st`) in one cooperative launch.
+    // Returns false (with pctx.why set) when this model cannot take that path.
+    bool persistent_available(int nb);
+    void run_persistent(State& st, int nb, const int* slots, int n_tokens, bool tok_from_list, bool argmax_feed, uint32_t* seq_dev, int* seq_cnt_dev,
+                        int seq_cap);
 
     static std::unique_ptr<Model> create_bare(int device);  // stream + events only (operator-level entry points)
 
