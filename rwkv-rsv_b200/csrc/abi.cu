@@ -98,15 +98,18 @@ void decode_tokens(Model& m, State& st, const uint32_t* tokens, int64_t n) {
     need(n >= 1, "empty token list");
     check_tokens(m, tokens, n);
     RSV_CUDA(cudaSetDevice(m.device));
-    StepPlan with_head = decode_plan(1, true), no_head = decode_plan(1, false);
-    m.upload_plan(with_head);
-    ensure_tok_list(m, (size_t)n);
-    RSV_CUDA(cudaMemcpyAsync(m.ws.tok_list, tokens, (size_t)n * sizeof(uint32_t), cudaMemcpyHostToDevice, m.stream));
     if (!m.prof_on && m.persistent_available(1)) {
+        m.ensure_workspace(1, 1, 1);
+        ensure_tok_list(m, (size_t)n);
+        RSV_CUDA(cudaMemcpyAsync(m.ws.tok_list, tokens, (size_t)n * sizeof(uint32_t), cudaMemcpyHostToDevice, m.stream));
         const int slot0 = 0;
         m.run_persistent(st, 1, &slot0, (int)n, true, false, nullptr, nullptr, 0);  // all n tokens in one launch, head on the last
         return;
     }
+    StepPlan with_head = decode_plan(1, true), no_head = decode_plan(1, false);
+    m.upload_plan(with_head);
+    ensure_tok_list(m, (size_t)n);
+    RSV_CUDA(cudaMemcpyAsync(m.ws.tok_list, tokens, (size_t)n * sizeof(uint32_t), cudaMemcpyHostToDevice, m.stream));
     RSV_CUDA(cudaMemsetAsync(m.ws.tok_pos, 0, sizeof(int), m.stream));
     for (int64_t i = 0; i < n; ++i) m.forward_rows(st, i == n - 1 ? with_head : no_head, true);
 }

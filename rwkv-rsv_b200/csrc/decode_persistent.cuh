@@ -3,7 +3,7 @@
 // step (forward_token / forward_layer / selfloop_step, src/gpu_model.rs:1879-2392) whose 8 kernels per layer
 // are latency-bound at batch 1.
 //
-// Structure.  One CTA per SM, 192 threads:
+// Structure.  One CTA per SM, 320 threads:
 //   warp 0   TMA producer.  Walks the fixed sequence of weight tiles (16 KB = 128 rows x 128 bytes) this CTA will
 //            ever need — token after token, layer after layer, phase after phase — and keeps a shared-memory ring
 //            full.  It never waits on a grid barrier, only on free ring slots, so HBM keeps streaming while the
@@ -11,15 +11,16 @@
 //   warp 1   MMA issuer.  tcgen05.mma (kind::i8 on the u8 codes / kind::f16) of each weight tile against the
 //            activation operand tiles the workers left in shared memory; accumulators in TMEM (N = 16 columns:
 //            4 sessions x 4 base-128 digits, or 4 x (hi, lo) halves).
-//   warps 2-5  workers.  Per phase: build the activation operand tiles (LayerNorm, token shift, fixed-point
+//   warps 2-9  workers.  Per phase: build the activation operand tiles (LayerNorm, token shift, fixed-point
 //            digits), drain finished accumulators to global partial sums, do the per-head WKV-7 work, take part
 //            in the grid barriers.
 // Work split: every GEMV phase is cut into units (128-row tile x 128-byte K block); CTA c owns the contiguous
-// unit range [c*U/G, (c+1)*U/G), so each SM streams the same number of weight bytes.  A run (the units of one
-// tile inside one CTA) leaves an exact int32 (or fp32) partial [16 columns][128 rows] plus its own fixed-point
-// scale; consumers add a tile's partials in slot order.  Integer partials make the split exact, and every
-// floating-point sum has a fixed order: results are deterministic and independent of timing.
-// Phases per layer (grid barrier after each; a/b = finish the residual stream on disjoint slices, then share it):
+// unit range [c*U/G, (c+1)*U/G), so each SM streams the same number of weight bytes.  The unit lists of the six
+// phase shapes are tabulated in shared memory once per launch.  A run (the units of one tile inside one CTA)
+// leaves an exact int32 (or fp32) partial [16 columns][128 rows] plus its own fixed-point scale; consumers add a
+// tile's partials in slot order.  Integer partials make the split exact, and every floating-point sum has a
+// fixed order: results are deterministic and independent of timing.
+// Phases per layer (grid barrier after each; b = finish the residual stream on disjoint slices, then share it):
 //   1  LN1 + token shift -> r,k,v (int8) and the four rank projections (fp16)
 //   2  per (session, head): rank back-projections, decay/a/v/g, WKV-7 state update in place, GroupNorm, gate
 //   3  att.output           3b  x += ...        4  LN2 + shift -> ffn.key        5  relu^2 -> ffn.value   5b  x += ...
@@ -30,8 +31,9 @@
 
 namespace rsv {
 
-constexpr int kDpThreads = 192;
-constexpr int kDpWorkers = 128;
+constexpr int kDpThreads = 320;
+constexpr int kDpWorkers = 256;
+constexpr int kDpWarps = kDpWorkers / 32;
 constexpr int kDpMaxNB = 4;
 constexpr int kDpN = 16;
 constexpr int kDpATile = 128 * 128;
@@ -39,14 +41,17 @@ constexpr int kDpBTile = kDpN * 128;
 constexpr int kDpDigits = 4;
 constexpr int kDpP = 7 * kDpDigits - 1;
 constexpr uint32_t kDpBarSpin = 1u << 22;
+constexpr int kDpMaxRuns = 8;    // runs (tiles touched) per CTA and phase
+constexpr int kDpMaxShares = 4;  // problems touched per CTA and phase
 
 struct DpMat {
     int map, M, mtiles, kblocks, is_i8, K;
     const float* wscale;
     const float* wzero;
 };
+enum { DM_WR = 0, DM_WK, DM_WV, DM_WO, DM_WFK, DM_WFV, DM_W1, DM_A1, DM_V1, DM_G1, DM_HEAD };
 struct DpLayer {
-    DpMat Wr, Wk, Wv, Wo, Wfk, Wfv, w1, a1, v1, g1;
+    DpMat mat[10];                    // indexed by DM_*
     const __half *w2, *a2, *v2, *g2;  // [C, mid] fp16
     const float *ln1_w, *ln1_b, *ln2_w, *ln2_b, *lnx_w, *lnx_b;
     const float *x_r, *x_w, *x_k, *x_v, *x_a, *x_g, *ffn_x_k;
@@ -63,9 +68,11 @@ struct DpRegion {
     int pmax;
     int pad;
 };
-enum { DP_P1 = 0, DP_P3 = 1, DP_P4 = 2, DP_P5 = 3, DP_HEAD = 4 };
+// phase variants: the schedule shapes that occur in a launch
+enum { DV_P1A = 0 /*layer 0: no v1*/, DV_P1B, DV_P3, DV_P4, DV_P5, DV_HEAD, DV_COUNT };
+enum { DR_P1 = 0, DR_P3, DR_P4, DR_P5, DR_HEAD };  // partial-sum regions
 struct DpParams {
-    const CUtensorMap* maps;
+    const CUtensorMap* maps;  // [10*L + 1]: layer l, matrix DM_x -> 10*l + x; head -> 10*L
     const DpLayer* layers;
     DpMat head;
     const __half* emb;
@@ -89,99 +96,61 @@ struct DpParams {
     int n_tokens;
     int tok_from_list;  // 1: step t reads tok_list[t*nb + b]; 0: step 0 reads tokens[b]
     int argmax_feed;    // 1: head + arg-max every step, the result is the next step's input (self-loop); 0: head on the last step only
-    int nstages, btiles;
+    int nstages, btiles, max_units;  // max_units: capacity of the per-CTA unit table (all variants together)
+    long long* dbg;                  // optional [64] time stamps (ns) of CTA 0 at phase boundaries of token 1, layer 1
 };
 
-struct DpProb {
-    DpMat mat;
-    int unit0, tile0, in_kind;
-    const float* mix;
+// ---- per-CTA schedule tables (shared memory) ----
+struct DpUnit {
+    uint16_t kb, mt;
+    uint8_t prob, btile, flags, pad;  // flags: 1 = first unit of its run, 2 = last unit of its run, 4 = int8 problem
 };
-struct DpPhase {
-    DpProb p[7];
-    int nprob, U, region;
+struct DpRun {
+    uint16_t tile;  // tile index inside the region
+    uint16_t u0;    // first unit (index into the variant's unit list)
+    uint8_t nu, slot, prob, pad;
 };
-enum { DP_IN_LNMIX = 0, DP_IN_VEC = 1, DP_IN_H = 2, DP_IN_LNOUT = 3 };
+struct DpShare {  // the K blocks of one problem this CTA feeds: operand tiles base .. base+ntile-1
+    uint8_t prob, ntile, kb0, base;
+};
+struct DpVar {
+    int nprob, U, ge, region;
+    int nunits, nruns, nshares, unit0;  // unit0: offset of this variant's units in the unit table
+    int p_mat[7], p_mtiles[7], p_kblocks[7], p_i8[7], p_unit0[7], p_tile0[7], p_K[7];
+    DpRun run[kDpMaxRuns];
+    DpShare share[kDpMaxShares];
+};
 
-__device__ __forceinline__ void dp_add_prob(DpPhase& ph, const DpMat& m, int in_kind, const float* mix) {
-    DpProb& q = ph.p[ph.nprob];
-    q.mat = m;
-    q.unit0 = ph.U;
-    q.tile0 = ph.nprob ? ph.p[ph.nprob - 1].tile0 + ph.p[ph.nprob - 1].mat.mtiles : 0;
-    q.in_kind = in_kind;
-    q.mix = mix;
-    ph.U += m.mtiles * m.kblocks;
-    ++ph.nprob;
+__device__ __forceinline__ long long dp_now() {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
 }
-__device__ __forceinline__ void dp_build_phase(const DpParams& P, int layer, int phase, DpPhase& ph) {
-    ph.nprob = 0;
-    ph.U = 0;
-    ph.region = phase;
-    if (phase == DP_HEAD) {
-        dp_add_prob(ph, P.head, DP_IN_LNOUT, nullptr);
-        return;
-    }
-    const DpLayer& Ly = P.layers[layer];
-    switch (phase) {
-        case DP_P1:
-            dp_add_prob(ph, Ly.Wr, DP_IN_LNMIX, Ly.x_r);
-            dp_add_prob(ph, Ly.Wk, DP_IN_LNMIX, Ly.x_k);
-            dp_add_prob(ph, Ly.Wv, DP_IN_LNMIX, Ly.x_v);
-            dp_add_prob(ph, Ly.w1, DP_IN_LNMIX, Ly.x_w);
-            dp_add_prob(ph, Ly.a1, DP_IN_LNMIX, Ly.x_a);
-            dp_add_prob(ph, Ly.g1, DP_IN_LNMIX, Ly.x_g);
-            if (layer > 0) dp_add_prob(ph, Ly.v1, DP_IN_LNMIX, Ly.x_v);
-            break;
-        case DP_P3: dp_add_prob(ph, Ly.Wo, DP_IN_VEC, nullptr); break;
-        case DP_P4: dp_add_prob(ph, Ly.Wfk, DP_IN_LNMIX, Ly.ffn_x_k); break;
-        case DP_P5: dp_add_prob(ph, Ly.Wfv, DP_IN_H, nullptr); break;
-    }
-}
-__device__ __forceinline__ int dp_prob_of(const DpPhase& ph, int u) {
-    int p = 0;
-    while (p + 1 < ph.nprob && u >= ph.p[p + 1].unit0) ++p;
-    return p;
-}
-// Shared-memory operand tile of unit u inside this CTA's range [ub, ue): problems whose share of the range spans a
-// whole K sweep keep one tile per K block; shorter shares keep one tile per unit.
-__device__ __forceinline__ int dp_btile_of(const DpPhase& ph, int ub, int ue, int u) {
-    int base = 0;
-    for (int p = 0; p < ph.nprob; ++p) {
-        const DpProb& q = ph.p[p];
-        const int lo = max(ub, q.unit0), hi = min(ue, q.unit0 + q.mat.mtiles * q.mat.kblocks);
-        if (hi <= lo) continue;
-        const int cnt = hi - lo;
-        if (u >= lo && u < hi) return base + (cnt >= q.mat.kblocks ? (u - q.unit0) % q.mat.kblocks : u - lo);
-        base += min(cnt, q.mat.kblocks);
-    }
-    return 0;
-}
+#define DP_STAMP(id)                                                                  \
+    do {                                                                              \
+        if (P.dbg && cta == 0 && wtid == 0 && t == 1 && l == 1) P.dbg[id] = dp_now(); \
+    } while (0)
 
-// Unit range of CTA `cta` in a phase.  Only the first min(G, U) CTAs take part, so that every participating CTA owns at
-// least one unit and the CTAs sharing a tile are consecutive (the partial-slot numbering relies on it).
-__device__ __forceinline__ void dp_range(const DpPhase& ph, int cta, int G, int& ub, int& ue) {
-    const int ge = min(G, ph.U);
-    ub = cta < ge ? tc_cta_begin(cta, ph.U, ge) : 0;
-    ue = cta < ge ? tc_cta_begin(cta + 1, ph.U, ge) : 0;
+__device__ __forceinline__ int dp_cta_begin(int c, int U, int ge) { return (int)(((unsigned)c * (unsigned)U) / (unsigned)ge); }
+__device__ __forceinline__ int dp_cta_of(int u, int U, int ge) { return (int)((((unsigned)u + 1u) * (unsigned)ge - 1u) / (unsigned)U); }
+
+// 2^n as a float for -126 <= n <= 127 (exponent field only)
+__device__ __forceinline__ float dp_pow2(int n) { return __int_as_float((n + 127) << 23); }
+// smallest e with 2^e >= a for a normal positive float a (exponent field, +1 unless a is a power of two)
+__device__ __forceinline__ int dp_ceil_log2(float a) {
+    const int bits = __float_as_int(a);
+    return ((bits >> 23) & 0xFF) - 127 + ((bits & 0x7FFFFF) ? 1 : 0);
 }
 
 __device__ __forceinline__ void dp_worker_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kDpWorkers) : "memory"); }
 
-// Sum over the 128 worker threads; every worker gets the result.  `red` holds 4 floats.
+// Sum over the 256 worker threads; every worker gets the result.  `red` holds 8 floats.
 __device__ __forceinline__ float dp_worker_sum(float v, float* red, int wtid) {
     v = warp_sum(v);
     dp_worker_sync();
     if ((wtid & 31) == 0) red[wtid >> 5] = v;
     dp_worker_sync();
-    return (red[0] + red[1]) + (red[2] + red[3]);
-}
-__device__ __forceinline__ float dp_worker_max(float v, float* red, int wtid) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    dp_worker_sync();
-    if ((wtid & 31) == 0) red[wtid >> 5] = v;
-    dp_worker_sync();
-    return fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    return ((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]));
 }
 
 // Grid-wide barrier among the workers of all CTAs (bounded spin).  Returns false after a timeout / abort.
@@ -217,34 +186,159 @@ struct DpStats {
     float mean, inv;
 };
 
-// value of output m of problem `pi` of a finished phase for session b: partials added in slot order
-__device__ __forceinline__ float dp_finalize(const DpParams& P, const DpPhase& ph, int pi, int m, int b, int G) {
-    const DpProb& q = ph.p[pi];
-    const DpRegion& R = P.reg[ph.region];
+// Value of output m (problem `pi` of variant V, matrix `mat`) for session b: the tile's partials added in slot order.
+// The loads of a slot are independent of one another and the slot loop is unrolled, so many requests are in flight.
+__device__ __noinline__ float dp_finalize(const DpRegion& R, const DpVar& V, int pi, const DpMat& mat, int m, int b) {
     const int mt = m >> 7, ml = m & 127;
-    const int tile_first = q.unit0 + mt * q.mat.kblocks;
-    const int ge = min(G, ph.U);
-    const int c_lo = tc_cta_of_unit(tile_first, ph.U, ge), c_hi = tc_cta_of_unit(tile_first + q.mat.kblocks - 1, ph.U, ge);
-    const size_t t = (size_t)(q.tile0 + mt) * R.pmax;
+    const int tile_first = V.p_unit0[pi] + mt * V.p_kblocks[pi];
+    const int ns = dp_cta_of(tile_first + V.p_kblocks[pi] - 1, V.U, V.ge) - dp_cta_of(tile_first, V.U, V.ge) + 1;
+    const size_t t = (size_t)(V.p_tile0[pi] + mt) * R.pmax;
     double acc = 0.0;
-    if (q.mat.is_i8) {
-        const double ws = q.mat.wscale[m], wz = q.mat.wzero[m];
-        for (int s = 0; s <= c_hi - c_lo; ++s) {
-            const uint32_t* d = R.data + (t + s) * (size_t)(kDpN * 128) + (size_t)(b * kDpDigits) * 128 + ml;
-            long long Q = (int)d[0];
-            Q = Q * 128 + (int)d[128];
-            Q = Q * 128 + (int)d[256];
-            Q = Q * 128 + (int)d[384];
-            const DpRunMeta& mm = R.meta[t + s];
-            acc += (double)mm.xscale[b] * (ws * (double)Q + wz * (double)mm.tsum[b]);
+    if (V.p_i8[pi]) {
+        const double ws = mat.wscale[m], wz = mat.wzero[m];
+        const uint32_t* d0 = R.data + t * (size_t)(kDpN * 128) + (size_t)(b * kDpDigits) * 128 + ml;
+#pragma unroll 4
+        for (int s = 0; s < ns; ++s) {
+            const uint32_t* d = d0 + (size_t)s * (kDpN * 128);
+            const int i0 = (int)d[0], i1 = (int)d[128], i2 = (int)d[256], i3 = (int)d[384];
+            const float xs = R.meta[t + s].xscale[b];
+            const long long ts = R.meta[t + s].tsum[b];
+            const long long Q = (((long long)i0 * 128 + i1) * 128 + i2) * 128 + i3;
+            acc += (double)xs * (ws * (double)Q + wz * (double)ts);
         }
     } else {
-        for (int s = 0; s <= c_hi - c_lo; ++s) {
-            const uint32_t* d = R.data + (t + s) * (size_t)(kDpN * 128) + (size_t)(b * 2) * 128 + ml;
+        const uint32_t* d0 = R.data + t * (size_t)(kDpN * 128) + (size_t)(b * 2) * 128 + ml;
+#pragma unroll 4
+        for (int s = 0; s < ns; ++s) {
+            const uint32_t* d = d0 + (size_t)s * (kDpN * 128);
             acc += (double)R.meta[t + s].xscale[b] * (double)(__uint_as_float(d[0]) + __uint_as_float(d[128]));
         }
     }
     return (float)acc;
+}
+
+// Builds the schedule of one phase variant for this CTA.  Executed by one thread.
+__device__ void dp_build_variant(const DpParams& P, int v, int cta, int G, DpVar& V, DpUnit* units, int& unit_cursor, int* status) {
+    const DpMat* lm = P.layers[0].mat;
+    int mats[7], n = 0;
+    switch (v) {
+        case DV_P1A:
+        case DV_P1B:
+            mats[0] = DM_WR;
+            mats[1] = DM_WK;
+            mats[2] = DM_WV;
+            mats[3] = DM_W1;
+            mats[4] = DM_A1;
+            mats[5] = DM_G1;
+            n = 6;
+            if (v == DV_P1B) mats[n++] = DM_V1;
+            V.region = DR_P1;
+            break;
+        case DV_P3:
+            mats[0] = DM_WO;
+            n = 1;
+            V.region = DR_P3;
+            break;
+        case DV_P4:
+            mats[0] = DM_WFK;
+            n = 1;
+            V.region = DR_P4;
+            break;
+        case DV_P5:
+            mats[0] = DM_WFV;
+            n = 1;
+            V.region = DR_P5;
+            break;
+        default:
+            mats[0] = DM_HEAD;
+            n = 1;
+            V.region = DR_HEAD;
+            break;
+    }
+    V.nprob = n;
+    int U = 0, T = 0;
+    for (int i = 0; i < n; ++i) {
+        const DpMat& mt = mats[i] == DM_HEAD ? P.head : lm[mats[i]];
+        V.p_mat[i] = mats[i];
+        V.p_mtiles[i] = mt.mtiles;
+        V.p_kblocks[i] = mt.kblocks;
+        V.p_i8[i] = mt.is_i8;
+        V.p_K[i] = mt.K;
+        V.p_unit0[i] = U;
+        V.p_tile0[i] = T;
+        U += mt.mtiles * mt.kblocks;
+        T += mt.mtiles;
+    }
+    V.U = U;
+    V.ge = min(G, U);  // only the first min(G, U) CTAs take part: the CTAs sharing a tile are consecutive
+    V.unit0 = unit_cursor;
+    V.nunits = V.nruns = V.nshares = 0;
+    if (cta >= V.ge) return;
+    const int ub = dp_cta_begin(cta, U, V.ge), ue = dp_cta_begin(cta + 1, U, V.ge);
+    int base = 0;
+    for (int i = 0; i < n; ++i) {  // operand shares
+        const int lo = max(ub, V.p_unit0[i]), hi = min(ue, V.p_unit0[i] + V.p_mtiles[i] * V.p_kblocks[i]);
+        if (hi <= lo) continue;
+        const int nt = min(hi - lo, V.p_kblocks[i]);
+        if (V.nshares < kDpMaxShares)
+            V.share[V.nshares] = DpShare{(uint8_t)i, (uint8_t)nt, (uint8_t)((lo - V.p_unit0[i]) % V.p_kblocks[i]), (uint8_t)base};
+        else
+            atomicOr(status, 8);
+        ++V.nshares;
+        base += nt;
+    }
+    if (base > P.btiles || (ue - ub) + unit_cursor > P.max_units) {
+        atomicOr(status, 8);  // tables too small for this shape (the host sizes them with the same formulas)
+        V.nshares = 0;
+        return;
+    }
+    int prev_tile = -1;
+    for (int u = ub; u < ue; ++u) {
+        int pi = 0;
+        while (pi + 1 < n && u >= V.p_unit0[pi + 1]) ++pi;
+        const int local = u - V.p_unit0[pi], kb = local % V.p_kblocks[pi], mt = local / V.p_kblocks[pi];
+        const int tile = V.p_tile0[pi] + mt;
+        int bt = 0, b2 = 0;  // operand tile of this unit
+        for (int i = 0; i < n; ++i) {
+            const int lo = max(ub, V.p_unit0[i]), hi = min(ue, V.p_unit0[i] + V.p_mtiles[i] * V.p_kblocks[i]);
+            if (hi <= lo) continue;
+            const int cnt = hi - lo;
+            if (i == pi) {
+                bt = b2 + (cnt >= V.p_kblocks[i] ? kb : u - lo);
+                break;
+            }
+            b2 += min(cnt, V.p_kblocks[i]);
+        }
+        DpUnit& e = units[unit_cursor + V.nunits];
+        e.kb = (uint16_t)kb;
+        e.mt = (uint16_t)mt;
+        e.prob = (uint8_t)pi;
+        e.btile = (uint8_t)bt;
+        e.flags = V.p_i8[pi] ? 4 : 0;
+        e.pad = 0;
+        if (tile != prev_tile) {
+            e.flags |= 1;
+            if (V.nunits > 0) units[unit_cursor + V.nunits - 1].flags |= 2;
+            const int tile_first = u - kb;
+            DpRun r;
+            r.tile = (uint16_t)tile;
+            r.u0 = (uint16_t)V.nunits;
+            r.nu = 0;
+            r.slot = (uint8_t)((u == tile_first) ? 0 : (cta - dp_cta_of(tile_first, U, V.ge)));
+            r.prob = (uint8_t)pi;
+            r.pad = 0;
+            if (V.nruns < kDpMaxRuns)
+                V.run[V.nruns] = r;
+            else
+                atomicOr(status, 8);
+            ++V.nruns;
+            prev_tile = tile;
+        }
+        if (V.nruns <= kDpMaxRuns) V.run[V.nruns - 1].nu++;
+        ++V.nunits;
+    }
+    if (V.nunits > 0) units[unit_cursor + V.nunits - 1].flags |= 2;
+    unit_cursor += V.nunits;
 }
 
 __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const __grid_constant__ DpParams P) {
@@ -260,15 +354,18 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
     uint64_t* b_ready = acc_empty + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_ready + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    // worker scratch
-    float* red = reinterpret_cast<float*>(tmem_slot + 4);                                  // [8]
-    DpStats* st_ln = reinterpret_cast<DpStats*>(red + 8);                                   // [4] stats of the current LN input
-    DpStats* st_emb = st_ln + kDpMaxNB;                                                     // [4] LN0 stats of the embedding rows
-    float* sc_scale = reinterpret_cast<float*>(st_emb + kDpMaxNB);                          // [7][4] operand scale per (problem, session)
-    long long* sc_tsum = reinterpret_cast<long long*>(sc_scale + 32);                       // [btiles][4]
-    float* sc_mid = reinterpret_cast<float*>(sc_tsum + (size_t)P.btiles * kDpMaxNB);        // [wm+am+vm+gm]
-    float* sc_hv = sc_mid + (P.wm + P.am + P.vm + P.gm);                                    // r,k,v,w,a(5x64) + kk,b,kt (3x64)
-    uint32_t* sc_tok = reinterpret_cast<uint32_t*>(sc_hv + 8 * 64);                          // [4]
+    float* red = reinterpret_cast<float*>(tmem_slot + 4);                              // [16]
+    DpStats* st_ln = reinterpret_cast<DpStats*>(red + 16);                             // [4] stats of the current LN input
+    DpStats* st_emb = st_ln + kDpMaxNB;                                                // [4] LN0 stats of the embedding rows
+    float* sc_scale = reinterpret_cast<float*>(st_emb + kDpMaxNB);                     // [4 shares][4] operand scale
+    int* sc_ex = reinterpret_cast<int*>(sc_scale + 16);                                // [4 shares][4] operand exponent
+    float* sc_amax = reinterpret_cast<float*>(sc_ex + 16);                             // [8 warps][4]
+    long long* sc_tsum = reinterpret_cast<long long*>(sc_amax + kDpWarps * 4);         // [btiles][4]
+    float* sc_mid = reinterpret_cast<float*>(sc_tsum + (size_t)P.btiles * kDpMaxNB);   // [wm+am+vm+gm]
+    float* sc_hv = sc_mid + (P.wm + P.am + P.vm + P.gm);                               // 8 x 64
+    uint32_t* sc_tok = reinterpret_cast<uint32_t*>(sc_hv + 8 * 64);                    // [4]
+    DpVar* vars = reinterpret_cast<DpVar*>(sc_tok + 4);                                // [DV_COUNT]
+    DpUnit* units = reinterpret_cast<DpUnit*>(vars + DV_COUNT);                        // [max_units]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = gridDim.x, cta = blockIdx.x;
@@ -281,16 +378,18 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 4);
+            mbar_init(&acc_empty[b], kDpWarps);
         }
         mbar_init(b_ready, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        int cursor = 0;
+        for (int v = 0; v < DV_COUNT; ++v) dp_build_variant(P, v, cta, G, vars[v], units, cursor, P.status);
     }
     // zero the operand tiles once: columns of absent sessions stay zero for the whole launch
     for (int i = threadIdx.x; i < P.btiles * kDpBTile / 16; i += kDpThreads) reinterpret_cast<uint4*>(btile)[i] = make_uint4(0, 0, 0, 0);
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 32);
+        tmem_alloc(tmem_slot, 128);  // 2 run buffers x 4 accumulator chains x 16 columns
         tmem_relinquish();
     }
     tc_fence_before();
@@ -308,22 +407,23 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                 for (int l = 0; l <= P.L && ok; ++l) {
                     if (l == P.L && !do_head) break;
                     for (int phs = 0; phs < (l == P.L ? 1 : 4) && ok; ++phs) {
-                        DpPhase ph;
-                        dp_build_phase(P, l, l == P.L ? DP_HEAD : phs, ph);
-                        int ub, ue;
-                        dp_range(ph, cta, G, ub, ue);
-                        for (int u = ub; u < ue; ++u, ++it) {
-                            const int pi = dp_prob_of(ph, u);
-                            const DpProb& q = ph.p[pi];
-                            const int local = u - q.unit0, kb = local % q.mat.kblocks, mt = local / q.mat.kblocks;
+                        const int v = l == P.L ? DV_HEAD : (phs == 0 ? (l == 0 ? DV_P1A : DV_P1B) : DV_P3 + phs - 1);
+                        const DpVar& V = vars[v];
+                        const DpUnit* un = units + V.unit0;
+                        const bool dbg_here = P.dbg && cta == 0 && t == 1 && l == 1 && v == DV_P4;
+                        if (dbg_here) P.dbg[55] = dp_now();
+                        for (int i = 0; i < V.nunits; ++i, ++it) {
+                            const DpUnit e = un[i];
+                            const int map = V.p_mat[e.prob] == DM_HEAD ? P.L * 10 : l * 10 + V.p_mat[e.prob];
                             const int s = it % NS;
                             if (!mbar_wait(&empty[s], ((it / NS) & 1u) ^ 1u, abort_flag)) {
                                 ok = false;
                                 break;
                             }
                             mbar_expect_tx(&full[s], kDpATile);
-                            tma_load_2d(&P.maps[q.mat.map], &full[s], ring + (size_t)s * kDpATile, kb * (q.mat.is_i8 ? 128 : 64), mt * 128);
+                            tma_load_2d(&P.maps[map], &full[s], ring + (size_t)s * kDpATile, (int)e.kb * ((e.flags & 4) ? 128 : 64), (int)e.mt * 128);
                         }
+                        if (dbg_here) P.dbg[56] = dp_now();
                     }
                 }
             }
@@ -333,57 +433,58 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
         if (lane == 0) {
             uint32_t it = 0, run = 0, phase_seq = 0;
             bool ok = true;
+            const uint32_t idesc_i8 = tc_idesc(true, kDpN), idesc_f16 = tc_idesc(false, kDpN);
             for (int t = 0; t < P.n_tokens && ok; ++t) {
                 const bool do_head = P.argmax_feed || t == P.n_tokens - 1;
                 for (int l = 0; l <= P.L && ok; ++l) {
                     if (l == P.L && !do_head) break;
                     for (int phs = 0; phs < (l == P.L ? 1 : 4) && ok; ++phs) {
-                        DpPhase ph;
-                        dp_build_phase(P, l, l == P.L ? DP_HEAD : phs, ph);
-                        int ub, ue;
-                        dp_range(ph, cta, G, ub, ue);
+                        const int v = l == P.L ? DV_HEAD : (phs == 0 ? (l == 0 ? DV_P1A : DV_P1B) : DV_P3 + phs - 1);
+                        const DpVar& V = vars[v];
+                        const DpUnit* un = units + V.unit0;
                         ok = mbar_wait(b_ready, phase_seq & 1u, abort_flag);
                         ++phase_seq;
                         if (!ok) break;
                         tc_fence_after();
-                        int prev_tile = -1;
-                        for (int u = ub; u < ue; ++u, ++it) {
-                            const int pi = dp_prob_of(ph, u);
-                            const DpProb& q = ph.p[pi];
-                            const int local = u - q.unit0, mt = local / q.mat.kblocks;
-                            const int tile = q.tile0 + mt;
-                            const bool first = tile != prev_tile;
-                            if (first) {
-                                if (prev_tile >= 0) {
-                                    tc_commit(&acc_full[run & 1]);
-                                    ++run;
-                                }
+                        const bool dbg_here = P.dbg && cta == 0 && t == 1 && l == 1 && v == DV_P4;
+                        long long twait = 0;
+                        if (dbg_here) P.dbg[50] = dp_now();
+                        for (int i = 0; i < V.nunits; ++i, ++it) {
+                            const DpUnit e = un[i];
+                            const long long tw0 = dbg_here ? dp_now() : 0;
+                            if (e.flags & 1) {
                                 ok = mbar_wait(&acc_empty[run & 1], (((run >> 1) & 1u) ^ 1u), abort_flag);
                                 if (!ok) break;
                                 tc_fence_after();
-                                prev_tile = tile;
                             }
                             const int s = it % NS;
                             ok = mbar_wait(&full[s], (it / NS) & 1u, abort_flag);
                             if (!ok) break;
+                            if (dbg_here) twait += dp_now() - tw0;
                             tc_fence_after();
                             const uint64_t adesc = tc_smem_desc(smem_u32(ring + (size_t)s * kDpATile));
-                            const uint64_t bdesc = tc_smem_desc(smem_u32(btile + (size_t)dp_btile_of(ph, ub, ue, u) * kDpBTile));
-                            const uint32_t d_tmem = tmem_base + (run & 1) * kDpN;
-                            if (q.mat.is_i8) {
-                                const uint32_t idesc = tc_idesc(true, kDpN);
+                            const uint64_t bdesc = tc_smem_desc(smem_u32(btile + (size_t)e.btile * kDpBTile));
+                            // The four 32-byte K sub-blocks of a tile accumulate into four separate accumulators (summed when
+                            // the run is drained): back-to-back MMAs into one accumulator would serialise on its latency.
+                            const uint32_t d_tmem = tmem_base + (run & 1) * (4 * kDpN);
+                            const uint32_t acc0 = (e.flags & 1) ? 0u : 1u;
+                            if (e.flags & 4) {
 #pragma unroll
-                                for (int k4 = 0; k4 < 4; ++k4) tc_mma<true>(d_tmem, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (first && k4 == 0) ? 0u : 1u);
+                                for (int k4 = 0; k4 < 4; ++k4) tc_mma<true>(d_tmem + k4 * kDpN, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc_i8, acc0);
                             } else {
-                                const uint32_t idesc = tc_idesc(false, kDpN);
 #pragma unroll
-                                for (int k4 = 0; k4 < 4; ++k4) tc_mma<false>(d_tmem, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (first && k4 == 0) ? 0u : 1u);
+                                for (int k4 = 0; k4 < 4; ++k4) tc_mma<false>(d_tmem + k4 * kDpN, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc_f16, acc0);
                             }
                             tc_commit(&empty[s]);
+                            if (e.flags & 2) {
+                                tc_commit(&acc_full[run & 1]);
+                                ++run;
+                            }
                         }
-                        if (ok && prev_tile >= 0) {
-                            tc_commit(&acc_full[run & 1]);
-                            ++run;
+                        if (dbg_here) {
+                            P.dbg[51] = dp_now();
+                            P.dbg[52] = twait;
+                            P.dbg[53] = V.nunits;
                         }
                     }
                 }
@@ -391,12 +492,15 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
         }
     } else {
         // =========================== workers ===========================
-        const int wtid = threadIdx.x - 64;  // 0..127
-        const int q4 = warp & 3;            // TMEM lane quarter of this warp
+        const int wtid = threadIdx.x - 64;  // 0..255
+        const int wwarp = wtid >> 5;
+        const int q4 = warp & 3;       // TMEM lane quarter of this warp
+        const int chalf = wwarp >> 2;  // which half of the 16 accumulator columns this warp drains
         unsigned bar_target = 0;
         uint32_t run = 0;
         bool ok = true;
         const int c0 = (int)(((long long)cta * C) / G), c1 = (int)(((long long)(cta + 1) * C) / G);  // this CTA's slice of the channels
+        const int nmid = P.wm + P.am + P.vm + P.gm;
 
         for (int t = 0; t < P.n_tokens && ok; ++t) {
             const bool do_head = P.argmax_feed || t == P.n_tokens - 1;
@@ -416,13 +520,19 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
             dp_worker_sync();
             for (int b = 0; b < NB; ++b) {
                 const __half* row = P.emb + (size_t)sc_tok[b] * C;
-                float s = 0.f;
-                for (int k = wtid; k < C; k += kDpWorkers) s += __half2float(row[k]);
+                float ev[16], s = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int k = wtid + i * kDpWorkers;
+                    ev[i] = k < C ? __half2float(row[k]) : 0.f;
+                    s += ev[i];
+                }
                 const float mean = dp_worker_sum(s, red, wtid) / (float)C;
                 float qv = 0.f;
-                for (int k = wtid; k < C; k += kDpWorkers) {
-                    const float d = __half2float(row[k]) - mean;
-                    qv += d * d;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float d = ev[i] - mean;
+                    if (wtid + i * kDpWorkers < C) qv += d * d;
                 }
                 const float inv = 1.0f / sqrtf(dp_worker_sum(qv, red, wtid) / (float)C + kLnEps);
                 if (wtid == 0) st_emb[b] = DpStats{mean, inv};
@@ -438,61 +548,66 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                 if (l == P.L && !do_head) break;
                 const int nph = l == P.L ? 1 : 4;
                 for (int phs = 0; phs < nph && ok; ++phs) {
-                    const int phase = l == P.L ? DP_HEAD : phs;
-                    DpPhase ph;
-                    dp_build_phase(P, l, phase, ph);
-                    int ub, ue;
-                        dp_range(ph, cta, G, ub, ue);
+                    const int v = l == P.L ? DV_HEAD : (phs == 0 ? (l == 0 ? DV_P1A : DV_P1B) : DV_P3 + phs - 1);
+                    const DpVar& V = vars[v];
                     const DpLayer* Ly = l < P.L ? &P.layers[l] : nullptr;
-                    const bool x_from_emb = (l == 0 && phase == DP_P1);  // x has not crossed a barrier yet: rebuild it from the embedding
+                    const bool x_from_emb = (v == DV_P1A);  // x has not crossed a barrier yet: rebuild it from the embedding
+                    DP_STAMP(phs * 10 + 0);
 
                     // ---------- phase 2 (heads) runs between P1 and P3 ----------
-                    if (phase == DP_P3) {
-                        DpPhase p1;
-                        dp_build_phase(P, l, DP_P1, p1);
+                    if (v == DV_P3) {
+                        const DpVar& V1 = vars[l == 0 ? DV_P1A : DV_P1B];
+                        const DpRegion& R1 = P.reg[DR_P1];
                         // new time-mix shift state = LN1(x) on this CTA's slice (all readers of the old state are past barrier 1)
                         for (int i = wtid; i < NB * (c1 - c0); i += kDpWorkers) {
                             const int b = i / (c1 - c0), m = c0 + i % (c1 - c0);
                             Ly->tmix_x[(size_t)P.slot[b] * C + m] = (P.x[(size_t)b * C + m] - st_ln[b].mean) * st_ln[b].inv * Ly->ln1_w[m] + Ly->ln1_b[m];
                         }
-                        const int nmid = P.wm + P.am + P.vm + P.gm;
                         for (int item = cta; item < NB * P.H; item += G) {
                             const int b = item / P.H, h = item % P.H;
-                            dp_worker_sync();
-                            // rank-space vectors of session b: tanh / sigmoid applied here
-                            for (int j = wtid; j < nmid; j += kDpWorkers) {
-                                int pi, jj;
-                                if (j < P.wm) {
-                                    pi = 3;
-                                    jj = j;
-                                } else if (j < P.wm + P.am) {
-                                    pi = 4;
-                                    jj = j - P.wm;
-                                } else if (j < P.wm + P.am + P.vm) {
-                                    pi = 6;
-                                    jj = j - P.wm - P.am;
+                            const int ch = h * 64 + (wtid >> 2), quad = wtid & 3;  // 4 threads per channel / state row
+                            // state row (wtid>>2), columns [16*quad, 16*quad+16): requested first, used last
+                            float* srow = Ly->wkv + (((size_t)P.slot[b] * P.H + h) * 64 + (wtid >> 2)) * 64 + quad * 16;
+                            float4 s4[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) s4[j] = *reinterpret_cast<const float4*>(srow + 4 * j);
+                            dp_worker_sync();  // the previous item is done with the scratch vectors
+                            // rank-space vectors of session b (tanh / sigmoid applied here) and r, k, v of this head
+                            for (int j = wtid; j < nmid + 3 * 64; j += kDpWorkers) {
+                                if (j < nmid) {
+                                    int pi, jj;
+                                    if (j < P.wm) {
+                                        pi = 3;
+                                        jj = j;
+                                    } else if (j < P.wm + P.am) {
+                                        pi = 4;
+                                        jj = j - P.wm;
+                                    } else if (j < P.wm + P.am + P.vm) {
+                                        pi = 6;
+                                        jj = j - P.wm - P.am;
+                                    } else {
+                                        pi = 5;
+                                        jj = j - P.wm - P.am - P.vm;
+                                    }
+                                    float vv = 0.f;
+                                    if (pi != 6 || l > 0) vv = dp_finalize(R1, V1, pi, Ly->mat[V1.p_mat[pi]], jj, b);
+                                    if (pi == 3) vv = tanhf(vv);
+                                    if (pi == 5) vv = 1.0f / (1.0f + expf(-vv));
+                                    sc_mid[j] = vv;
                                 } else {
-                                    pi = 5;
-                                    jj = j - P.wm - P.am - P.vm;
+                                    const int jj = j - nmid, pi = jj >> 6;
+                                    sc_hv[jj] = dp_finalize(R1, V1, pi, Ly->mat[V1.p_mat[pi]], h * 64 + (jj & 63), b);
                                 }
-                                float v = 0.f;
-                                if (pi != 6 || l > 0) v = dp_finalize(P, p1, pi, jj, b, G);
-                                if (pi == 3) v = tanhf(v);
-                                if (pi == 5) v = 1.0f / (1.0f + expf(-v));
-                                sc_mid[j] = v;
                             }
-                            // r, k, v of this head
-                            for (int j = wtid; j < 3 * 64; j += kDpWorkers) sc_hv[j] = dp_finalize(P, p1, j / 64, h * 64 + (j & 63), b, G);
                             dp_worker_sync();
-                            const int ch = h * 64 + (wtid >> 1), half = wtid & 1;
-                            // back-projections: each thread pair splits the rank dimension in two contiguous halves
-                            auto dot_half = [&](const __half* W, int mid, const float* vec) {
-                                const int hl = mid >> 1;
-                                const __half* wrow = W + (size_t)ch * mid + half * hl;
-                                const float* vv = vec + half * hl;
+                            // back-projections: the four threads of a channel split the rank dimension in contiguous quarters
+                            auto dot_q = [&](const __half* W, int mid, const float* vec) {
                                 float a = 0.f;
-                                if ((hl & 7) == 0) {
-                                    for (int j = 0; j < hl; j += 8) {
+                                const int ql = mid >> 2;
+                                if ((mid & 3) == 0 && (ql & 7) == 0) {
+                                    const __half* wrow = W + (size_t)ch * mid + quad * ql;
+                                    const float* vv = vec + quad * ql;
+                                    for (int j = 0; j < ql; j += 8) {
                                         const uint4 pk = *reinterpret_cast<const uint4*>(wrow + j);
                                         const __half2* h2 = reinterpret_cast<const __half2*>(&pk);
 #pragma unroll
@@ -503,34 +618,34 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                                         }
                                     }
                                 } else {
-                                    for (int j = 0; j < hl; ++j) a = fmaf(__half2float(wrow[j]), vv[j], a);
+                                    for (int j = quad; j < mid; j += 4) a = fmaf(__half2float(W[(size_t)ch * mid + j]), vec[j], a);
                                 }
-                                if ((mid & 1) && half == 1) a = fmaf(__half2float(W[(size_t)ch * mid + mid - 1]), vec[mid - 1], a);
-                                return a + __shfl_xor_sync(0xffffffffu, a, 1);
+                                a += __shfl_xor_sync(0xffffffffu, a, 1);
+                                return a + __shfl_xor_sync(0xffffffffu, a, 2);
                             };
-                            const float dw = dot_half(Ly->w2, P.wm, sc_mid);
-                            const float da = dot_half(Ly->a2, P.am, sc_mid + P.wm);
-                            const float dg = dot_half(Ly->g2, P.gm, sc_mid + P.wm + P.am + P.vm);
+                            const float dw = dot_q(Ly->w2, P.wm, sc_mid);
+                            const float da = dot_q(Ly->a2, P.am, sc_mid + P.wm);
+                            const float dg = dot_q(Ly->g2, P.gm, sc_mid + P.wm + P.am + P.vm);
                             const float wdec = expf((1.0f / (1.0f + expf(-(dw + Ly->w0[ch])))) * kDecayScale);
                             const float aa = 1.0f / (1.0f + expf(-(da + Ly->a0[ch])));
-                            const float rr = sc_hv[(wtid >> 1)], kk0 = sc_hv[64 + (wtid >> 1)];
-                            float vv0 = sc_hv[128 + (wtid >> 1)];
+                            const float rr = sc_hv[(wtid >> 2)], kk0 = sc_hv[64 + (wtid >> 2)];
+                            float vv0 = sc_hv[128 + (wtid >> 2)];
                             if (l == 0) {
-                                if (half == 0) {
+                                if (quad == 0) {
                                     P.vfirst[(size_t)b * C + ch] = vv0;
                                     P.state_vfirst[(size_t)P.slot[b] * C + ch] = vv0;
                                 }
                             } else {
-                                const float dv = dot_half(Ly->v2, P.vm, sc_mid + P.wm + P.am);
+                                const float dv = dot_q(Ly->v2, P.vm, sc_mid + P.wm + P.am);
                                 const float gate = 1.0f / (1.0f + expf(-(dv + Ly->v0[ch])));
                                 vv0 = vv0 + gate * (P.vfirst[(size_t)b * C + ch] - vv0);
                             }
                             const float kkj = kk0 * Ly->k_k[ch];
-                            const float ss = dp_worker_sum(half == 0 ? kkj * kkj : 0.f, red, wtid);
+                            const float ss = dp_worker_sum(quad == 0 ? kkj * kkj : 0.f, red, wtid);
                             const float kkh = kkj * (1.0f / fmaxf(sqrtf(ss), kL2Eps));
                             const float kt = kk0 + Ly->k_a[ch] * (kk0 * aa - kk0);
-                            if (half == 0) {
-                                const int i = wtid >> 1;
+                            if (quad == 0) {
+                                const int i = wtid >> 2;
                                 sc_hv[3 * 64 + i] = wdec;
                                 sc_hv[4 * 64 + i] = rr;
                                 sc_hv[5 * 64 + i] = kkh;
@@ -538,239 +653,299 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                                 sc_hv[7 * 64 + i] = kt;
                             }
                             dp_worker_sync();
-                            // state row (wtid>>1), columns [32*half, 32*half+32)
-                            float* srow = Ly->wkv + (((size_t)P.slot[b] * P.H + h) * 64 + (wtid >> 1)) * 64 + half * 32;
-                            float S[32];
+                            float S[16];
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                const float4 v4 = *reinterpret_cast<const float4*>(srow + j);
-                                S[j] = v4.x;
-                                S[j + 1] = v4.y;
-                                S[j + 2] = v4.z;
-                                S[j + 3] = v4.w;
+                            for (int j = 0; j < 4; ++j) {
+                                S[4 * j] = s4[j].x;
+                                S[4 * j + 1] = s4[j].y;
+                                S[4 * j + 2] = s4[j].z;
+                                S[4 * j + 3] = s4[j].w;
                             }
-                            const float *s_w = sc_hv + 3 * 64 + half * 32, *s_r = sc_hv + 4 * 64 + half * 32, *s_kk = sc_hv + 5 * 64 + half * 32,
-                                        *s_b = sc_hv + 6 * 64 + half * 32, *s_kt = sc_hv + 7 * 64 + half * 32;
+                            const float *s_w = sc_hv + 3 * 64 + quad * 16, *s_r = sc_hv + 4 * 64 + quad * 16, *s_kk = sc_hv + 5 * 64 + quad * 16,
+                                        *s_b = sc_hv + 6 * 64 + quad * 16, *s_kt = sc_hv + 7 * 64 + quad * 16;
                             float sa = 0.f;
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) sa = fmaf(S[j], s_kk[j], sa);
+                            for (int j = 0; j < 16; ++j) sa = fmaf(S[j], s_kk[j], sa);
                             sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+                            sa += __shfl_xor_sync(0xffffffffu, sa, 2);
                             float y = 0.f;
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
+                            for (int j = 0; j < 16; ++j) {
                                 S[j] = fmaf(S[j], s_w[j], fmaf(sa, s_b[j], vv0 * s_kt[j]));
                                 y = fmaf(S[j], s_r[j], y);
                             }
                             y += __shfl_xor_sync(0xffffffffu, y, 1);
+                            y += __shfl_xor_sync(0xffffffffu, y, 2);
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(srow + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
-                            const float mean = dp_worker_sum(half == 0 ? y : 0.f, red, wtid) / 64.0f;
+                            for (int j = 0; j < 4; ++j) *reinterpret_cast<float4*>(srow + 4 * j) = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+                            const float mean = dp_worker_sum(quad == 0 ? y : 0.f, red, wtid) / 64.0f;
                             const float d = y - mean;
-                            const float var = dp_worker_sum(half == 0 ? d * d : 0.f, red, wtid) / 64.0f + kGnEps;
-                            const float srk = dp_worker_sum(half == 0 ? rr * kt * Ly->r_k[ch] : 0.f, red, wtid);
-                            if (half == 0) P.yg[(size_t)b * C + ch] = (d * (1.0f / sqrtf(var)) * Ly->lnx_w[ch] + Ly->lnx_b[ch] + srk * vv0) * dg;
+                            const float var = dp_worker_sum(quad == 0 ? d * d : 0.f, red, wtid) / 64.0f + kGnEps;
+                            const float srk = dp_worker_sum(quad == 0 ? rr * kt * Ly->r_k[ch] : 0.f, red, wtid);
+                            if (quad == 0) P.yg[(size_t)b * C + ch] = (d * (1.0f / sqrtf(var)) * Ly->lnx_w[ch] + Ly->lnx_b[ch] + srk * vv0) * dg;
                         }
+                        DP_STAMP(40);
                         ok = dp_grid_barrier(P.grid_bar, bar_target, G, abort_flag, wtid);
                         if (!ok) break;
+                        DP_STAMP(41);
                     }
 
                     // ---------- LayerNorm statistics of the phase input (full rows, every CTA) ----------
-                    if (phase == DP_P1 || phase == DP_P4 || phase == DP_HEAD) {
+                    if (v == DV_P1A || v == DV_P1B || v == DV_P4 || v == DV_HEAD) {
                         for (int b = 0; b < NB; ++b) {
                             const __half* erow = P.emb + (size_t)sc_tok[b] * C;
                             const DpStats se = st_emb[b];
-                            auto xval = [&](int k) {
-                                return x_from_emb ? ((__half2float(erow[k]) - se.mean) * se.inv * P.ln0_w[k] + P.ln0_b[k]) : P.x[(size_t)b * C + k];
-                            };
+                            // C <= 16 * 256: each worker keeps its elements in registers between the two passes
+                            float xv[16];
                             float s = 0.f;
-                            for (int k = wtid; k < C; k += kDpWorkers) s += xval(k);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const int k = wtid + i * kDpWorkers;
+                                xv[i] = 0.f;
+                                if (k < C) xv[i] = x_from_emb ? ((__half2float(erow[k]) - se.mean) * se.inv * P.ln0_w[k] + P.ln0_b[k]) : P.x[(size_t)b * C + k];
+                                s += xv[i];
+                            }
                             const float mean = dp_worker_sum(s, red, wtid) / (float)C;
                             float qv = 0.f;
-                            for (int k = wtid; k < C; k += kDpWorkers) {
-                                const float dd = xval(k) - mean;
-                                qv += dd * dd;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const float dd = xv[i] - mean;
+                                if (wtid + i * kDpWorkers < C) qv += dd * dd;
                             }
                             const float inv = 1.0f / sqrtf(dp_worker_sum(qv, red, wtid) / (float)C + kLnEps);
                             if (wtid == 0) st_ln[b] = DpStats{mean, inv};
                         }
                         dp_worker_sync();
                     }
-                    if (phase == DP_P5) {
+                    if (v == DV_P5) {
                         // new channel-mix shift state = LN2(x) on this CTA's slice (readers of the old state are past barrier 4)
                         for (int i = wtid; i < NB * (c1 - c0); i += kDpWorkers) {
                             const int b = i / (c1 - c0), m = c0 + i % (c1 - c0);
                             Ly->cmix_x[(size_t)P.slot[b] * C + m] = (P.x[(size_t)b * C + m] - st_ln[b].mean) * st_ln[b].inv * Ly->ln2_w[m] + Ly->ln2_b[m];
                         }
                     }
+                    DP_STAMP(phs * 10 + 1);
 
                     // ---------- operand tiles of this CTA's units ----------
-                    DpPhase p4;  // producer of h
-                    if (phase == DP_P5) dp_build_phase(P, l, DP_P4, p4);
-                    const float *lw = nullptr, *lb = nullptr, *shift = nullptr;
-                    if (phase == DP_P1) {
-                        lw = Ly->ln1_w;
-                        lb = Ly->ln1_b;
-                        shift = Ly->tmix_x;
-                    } else if (phase == DP_P4) {
-                        lw = Ly->ln2_w;
-                        lb = Ly->ln2_b;
-                        shift = Ly->cmix_x;
-                    } else if (phase == DP_HEAD) {
-                        lw = P.lno_w;
-                        lb = P.lno_b;
-                    }
-                    auto input = [&](const DpProb& q, int b, int k) -> float {
-                        switch (q.in_kind) {
-                            case DP_IN_LNMIX: {
-                                const float xv = x_from_emb ? ((__half2float(P.emb[(size_t)sc_tok[b] * C + k]) - st_emb[b].mean) * st_emb[b].inv * P.ln0_w[k] + P.ln0_b[k])
-                                                            : P.x[(size_t)b * C + k];
-                                const float cur = (xv - st_ln[b].mean) * st_ln[b].inv * lw[k] + lb[k];
-                                const float prev = shift[(size_t)P.slot[b] * C + k];
-                                return cur + q.mix[k] * (prev - cur);
+                    {
+                        const float *lw = nullptr, *lb = nullptr, *shift = nullptr;
+                        if (v == DV_P1A || v == DV_P1B) {
+                            lw = Ly->ln1_w;
+                            lb = Ly->ln1_b;
+                            shift = Ly->tmix_x;
+                        } else if (v == DV_P4) {
+                            lw = Ly->ln2_w;
+                            lb = Ly->ln2_b;
+                            shift = Ly->cmix_x;
+                        } else if (v == DV_HEAD) {
+                            lw = P.lno_w;
+                            lb = P.lno_b;
+                        }
+                        const DpVar& V4 = vars[DV_P4];
+                        auto mixptr = [&](int pi) -> const float* {  // mix vector of a problem of phase 1 / 4
+                            if (v == DV_P4) return Ly->ffn_x_k;
+                            switch (V.p_mat[pi]) {
+                                case DM_WR: return Ly->x_r;
+                                case DM_WK: return Ly->x_k;
+                                case DM_WV: return Ly->x_v;
+                                case DM_W1: return Ly->x_w;
+                                case DM_A1: return Ly->x_a;
+                                case DM_G1: return Ly->x_g;
+                                default: return Ly->x_v;  // DM_V1
                             }
-                            case DP_IN_VEC: return P.yg[(size_t)b * C + k];
-                            case DP_IN_H: {
-                                const float a = fmaxf(dp_finalize(P, p4, 0, k, b, G), 0.f);
+                        };
+                        auto input = [&](int pi, int b, int k) -> float {
+                            if (v == DV_P3) return P.yg[(size_t)b * C + k];
+                            if (v == DV_P5) {
+                                const float a = fmaxf(dp_finalize(P.reg[DR_P4], V4, 0, Ly->mat[DM_WFK], k, b), 0.f);
                                 return a * a;
                             }
-                            default: return (P.x[(size_t)b * C + k] - st_ln[b].mean) * st_ln[b].inv * lw[k] + lb[k];
-                        }
-                    };
-                    {
-                        int base = 0;
-                        for (int pi = 0; pi < ph.nprob; ++pi) {
-                            const DpProb& q = ph.p[pi];
-                            const int lo = max(ub, q.unit0), hi = min(ue, q.unit0 + q.mat.mtiles * q.mat.kblocks);
-                            if (hi <= lo) continue;
-                            const int ntile = min(hi - lo, q.mat.kblocks);
-                            const int kb0 = (lo - q.unit0) % q.mat.kblocks;  // K block of local tile 0 (all K blocks when ntile == kblocks)
-                            const int epb = q.mat.is_i8 ? 128 : 64;          // elements per K block
-                            const bool act = wtid < epb;
-                            // pass 1: largest magnitude over everything this CTA feeds into this problem
-                            float am[kDpMaxNB] = {0.f, 0.f, 0.f, 0.f};
-                            for (int tl = 0; tl < ntile; ++tl) {
-                                const int kb = ntile == q.mat.kblocks ? tl : (kb0 + tl) % q.mat.kblocks;
-                                const int k = kb * epb + wtid;
-                                if (act && k < q.mat.K)
-                                    for (int b = 0; b < NB; ++b) am[b] = fmaxf(am[b], fabsf(input(q, b, k)));
-                            }
-                            int ex[kDpMaxNB];
-                            for (int b = 0; b < NB; ++b) {
-                                const float a = dp_worker_max(am[b], red, wtid);
-                                int e = 0;
-                                if (a > 0.f && a < 3.0e38f) {
-                                    (void)frexpf(a, &e);
-                                    if (a == ldexpf(0.5f, e)) e -= 1;
+                            const float xv = x_from_emb ? ((__half2float(P.emb[(size_t)sc_tok[b] * C + k]) - st_emb[b].mean) * st_emb[b].inv * P.ln0_w[k] + P.ln0_b[k])
+                                                        : P.x[(size_t)b * C + k];
+                            const float cur = (xv - st_ln[b].mean) * st_ln[b].inv * lw[k] + lb[k];
+                            if (v == DV_HEAD) return cur;
+                            const float prev = shift[(size_t)P.slot[b] * C + k];
+                            return cur + mixptr(pi)[k] * (prev - cur);
+                        };
+                        // quantise one element into its operand tile and add it to the tile's exact fixed-point sum
+                        auto emit = [&](bool i8, uint8_t* tile, int tile_idx, int sh, int b, int e, float val) {
+                            if (i8) {
+                                float vq = val * dp_pow2(kDpP - sc_ex[sh * 4 + b]);
+                                vq = fminf(fmaxf(vq, -(float)(1 << kDpP)), (float)(1 << kDpP));
+                                int tq = (vq == vq) ? __float2int_rn(vq) : 0;
+                                long long ts = tq;
+#pragma unroll
+                                for (int j = kDpDigits - 1; j > 0; --j) {
+                                    const int dj = ((tq + 64) & 127) - 64;
+                                    tile[dp_b_offset(b * kDpDigits + j, e)] = (uint8_t)(int8_t)dj;
+                                    tq = (tq - dj) >> 7;
                                 }
-                                ex[b] = max(-100, min(100, e));
-                                if (wtid == 0) sc_scale[pi * kDpMaxNB + b] = q.mat.is_i8 ? ldexpf(1.0f, ex[b] - kDpP) : ldexpf(1.0f, ex[b]);
+                                tile[dp_b_offset(b * kDpDigits, e)] = (uint8_t)(int8_t)tq;
+                                // the 32 lanes of a warp work on the same tile: one shared-memory add per warp
+#pragma unroll
+                                for (int o = 16; o > 0; o >>= 1) ts += __shfl_xor_sync(0xffffffffu, ts, o);
+                                if (lane == 0) atomicAdd(reinterpret_cast<unsigned long long*>(&sc_tsum[(size_t)tile_idx * kDpMaxNB + b]), (unsigned long long)ts);
+                            } else {
+                                float vq = val * dp_pow2(-sc_ex[sh * 4 + b]);
+                                vq = fminf(fmaxf(vq, -1.0f), 1.0f);
+                                if (!(vq == vq)) vq = 0.f;
+                                const __half hi16 = __float2half_rn(vq);
+                                const __half lo16 = __float2half_rn(vq - __half2float(hi16));
+                                *reinterpret_cast<__half*>(tile + dp_b_offset(b * 2, e * 2)) = hi16;
+                                *reinterpret_cast<__half*>(tile + dp_b_offset(b * 2 + 1, e * 2)) = lo16;
                             }
-                            // pass 2: digits (int8) or hi/lo halves (fp16) into the swizzled tiles
-                            for (int tl = 0; tl < ntile; ++tl) {
-                                const int kb = ntile == q.mat.kblocks ? tl : (kb0 + tl) % q.mat.kblocks;
-                                const int k = kb * epb + wtid;
-                                uint8_t* tile = btile + (size_t)(base + tl) * kDpBTile;
-                                for (int b = 0; b < NB; ++b) {
-                                    float v = (act && k < q.mat.K) ? input(q, b, k) : 0.f;
-                                    long long tsum = 0;
-                                    if (q.mat.is_i8) {
-                                        v *= ldexpf(1.0f, kDpP - ex[b]);
-                                        v = fminf(fmaxf(v, -(float)(1 << kDpP)), (float)(1 << kDpP));
-                                        int tq = (v == v) ? __float2int_rn(v) : 0;
-                                        tsum = tq;
-                                        if (act) {
+                        };
+                        // reduce the per-thread magnitudes to the power-of-two scale of (share, session); all workers call this
+                        auto set_scale = [&](bool i8, int sh, int b, float am) {
 #pragma unroll
-                                            for (int j = kDpDigits - 1; j > 0; --j) {
-                                                const int dj = ((tq + 64) & 127) - 64;
-                                                tile[dp_b_offset(b * kDpDigits + j, wtid)] = (uint8_t)(int8_t)dj;
-                                                tq = (tq - dj) >> 7;
-                                            }
-                                            tile[dp_b_offset(b * kDpDigits, wtid)] = (uint8_t)(int8_t)tq;
-                                        }
-                                        // exact integer sum of this tile's fixed-point values
+                            for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+                            if (lane == 0) sc_amax[wwarp] = am;
+                            dp_worker_sync();
+                            if (wtid == 0) {
+                                float a = 0.f;
+                                for (int w = 0; w < kDpWarps; ++w) a = fmaxf(a, sc_amax[w]);
+                                int ex = 0;
+                                if (a >= 1.0e-30f && a < 3.0e38f) ex = dp_ceil_log2(a);
+                                ex = max(-90, min(90, ex));
+                                sc_ex[sh * 4 + b] = ex;
+                                sc_scale[sh * 4 + b] = i8 ? dp_pow2(ex - kDpP) : dp_pow2(ex);
+                            }
+                            dp_worker_sync();
+                        };
+                        constexpr int kMaxItems = 6;  // register-resident (tile, element) items per worker
+                        const int nshare = min(V.nshares, kDpMaxShares);
+                        int tiles_total = 0;
+                        for (int sh = 0; sh < nshare; ++sh) tiles_total += V.share[sh].ntile;
+                        for (int i = wtid; i < tiles_total * kDpMaxNB; i += kDpWorkers) sc_tsum[i] = 0;  // made visible by the syncs in set_scale
+                        // loops over shares and sessions stay rolled: this code runs once per phase, so its size (instruction
+                        // fetch) matters more than its issue rate
+#pragma unroll 1
+                        for (int sh = 0; sh < nshare; ++sh) {
+                            const DpShare S = V.share[sh];
+                            const int pi = S.prob;
+                            const bool i8 = V.p_i8[pi] != 0;
+                            const int epb = i8 ? 128 : 64, kbs = V.p_kblocks[pi], K = V.p_K[pi];
+                            const int grp = kDpWorkers / epb;  // tiles handled side by side
+                            const int sub = wtid / epb, e = wtid % epb;
+#pragma unroll 1
+                            for (int b = 0; b < NB; ++b) {
+                                float am = 0.f;
+                                if (S.ntile <= grp * kMaxItems) {
+                                    // everything fits in registers: load once, reduce the magnitude, quantise
+                                    float val[kMaxItems];
 #pragma unroll
-                                        for (int o = 16; o > 0; o >>= 1) tsum += __shfl_xor_sync(0xffffffffu, tsum, o);
-                                        dp_worker_sync();
-                                        if ((wtid & 31) == 0) reinterpret_cast<long long*>(red)[wtid >> 5] = tsum;
-                                        dp_worker_sync();
-                                        if (wtid == 0) {
-                                            const long long* r4 = reinterpret_cast<const long long*>(red);
-                                            sc_tsum[(size_t)(base + tl) * kDpMaxNB + b] = r4[0] + r4[1] + r4[2] + r4[3];
-                                        }
-                                    } else if (act) {
-                                        v *= ldexpf(1.0f, -ex[b]);
-                                        v = fminf(fmaxf(v, -1.0f), 1.0f);
-                                        if (!(v == v)) v = 0.f;
-                                        const __half hi16 = __float2half_rn(v);
-                                        const __half lo16 = __float2half_rn(v - __half2float(hi16));
-                                        *reinterpret_cast<__half*>(tile + dp_b_offset(b * 2, wtid * 2)) = hi16;
-                                        *reinterpret_cast<__half*>(tile + dp_b_offset(b * 2 + 1, wtid * 2)) = lo16;
+                                    for (int it = 0; it < kMaxItems; ++it) {
+                                        const int tl = it * grp + sub;
+                                        const int kb = S.ntile == kbs ? tl : (S.kb0 + tl) % kbs;
+                                        const int k = kb * epb + e;
+                                        val[it] = (tl < S.ntile && k < K) ? input(pi, b, k) : 0.f;
+                                        am = fmaxf(am, fabsf(val[it]));
+                                    }
+                                    set_scale(i8, sh, b, am);
+#pragma unroll
+                                    for (int it = 0; it < kMaxItems; ++it) {
+                                        const int tl = it * grp + sub;
+                                        if (tl < S.ntile) emit(i8, btile + (size_t)(S.base + tl) * kDpBTile, S.base + tl, sh, b, e, val[it]);
+                                    }
+                                } else {
+                                    // many tiles (the head): one pass for the magnitude, a second one that recomputes and quantises
+#pragma unroll 1
+                                    for (int tl = sub; tl < S.ntile; tl += grp) {
+                                        const int kb = S.ntile == kbs ? tl : (S.kb0 + tl) % kbs;
+                                        const int k = kb * epb + e;
+                                        if (k < K) am = fmaxf(am, fabsf(input(pi, b, k)));
+                                    }
+                                    set_scale(i8, sh, b, am);
+#pragma unroll 1
+                                    for (int tl = sub; tl < S.ntile; tl += grp) {
+                                        const int kb = S.ntile == kbs ? tl : (S.kb0 + tl) % kbs;
+                                        const int k = kb * epb + e;
+                                        emit(i8, btile + (size_t)(S.base + tl) * kDpBTile, S.base + tl, sh, b, e, k < K ? input(pi, b, k) : 0.f);
                                     }
                                 }
                             }
-                            base += ntile;
                         }
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     dp_worker_sync();
                     if (wtid == 0) mbar_arrive(b_ready);
+                    DP_STAMP(phs * 10 + 2);
 
                     // ---------- drain the runs of this CTA ----------
                     {
-                        const DpRegion& Rg = P.reg[ph.region];
-                        int u = ub;
-                        while (u < ue) {
-                            const int pi = dp_prob_of(ph, u);
-                            const DpProb& q = ph.p[pi];
-                            const int local = u - q.unit0, kb = local % q.mat.kblocks, mt = local / q.mat.kblocks;
-                            const int tile_first = u - kb;
-                            const int run_end = min(ue, tile_first + q.mat.kblocks);
-                            const int slot = (u == tile_first) ? 0 : (cta - tc_cta_of_unit(tile_first, ph.U, min(G, ph.U)));
-                            const size_t tidx = (size_t)(q.tile0 + mt) * Rg.pmax + slot;
+                        const DpRegion& Rg = P.reg[V.region];
+                        const int nruns = min(V.nruns, kDpMaxRuns);
+                        for (int ri = 0; ri < nruns; ++ri) {
+                            const DpRun r = V.run[ri];
+                            const size_t tidx = (size_t)r.tile * Rg.pmax + r.slot;
                             const bool got = mbar_wait(&acc_full[run & 1], (run >> 1) & 1u, abort_flag);
                             if (!__all_sync(0xffffffffu, got)) break;  // the abort flag is set; decided for all workers below
                             tc_fence_after();
-                            uint32_t v[16];
-                            tmem_ld16(tmem_base + ((uint32_t)(q4 * 32) << 16) + (run & 1) * kDpN, v);
-                            uint32_t* dst = Rg.data + tidx * (size_t)(kDpN * 128) + q4 * 32 + lane;
+                            uint32_t vv[8], v2[8];
+                            const uint32_t tbase = tmem_base + ((uint32_t)(q4 * 32) << 16) + (run & 1) * (4 * kDpN) + chalf * 8;
+                            const bool r_i8 = V.p_i8[r.prob] != 0;
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) dst[(size_t)j * 128] = v[j];
+                            for (int k4 = 0; k4 < 4; ++k4) {  // add the four accumulator chains (exact for int32; fixed order for fp32)
+                                asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                             : "=r"(v2[0]), "=r"(v2[1]), "=r"(v2[2]), "=r"(v2[3]), "=r"(v2[4]), "=r"(v2[5]), "=r"(v2[6]), "=r"(v2[7])
+                                             : "r"(tbase + k4 * kDpN));
+                                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    if (k4 == 0)
+                                        vv[j] = v2[j];
+                                    else if (r_i8)
+                                        vv[j] = (uint32_t)((int)vv[j] + (int)v2[j]);
+                                    else
+                                        vv[j] = __float_as_uint(__uint_as_float(vv[j]) + __uint_as_float(v2[j]));
+                                }
+                            }
+                            uint32_t* dst = Rg.data + tidx * (size_t)(kDpN * 128) + (size_t)(chalf * 8) * 128 + q4 * 32 + lane;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) dst[(size_t)j * 128] = vv[j];
                             if (wtid < NB) {
                                 // scale of this CTA's operand for the problem, exact sum of the run's fixed-point values
+                                const DpUnit* un = units + V.unit0 + r.u0;
                                 long long ts = 0;
-                                for (int uu = u; uu < run_end; ++uu) ts += sc_tsum[(size_t)dp_btile_of(ph, ub, ue, uu) * kDpMaxNB + wtid];
-                                Rg.meta[tidx].xscale[wtid] = sc_scale[pi * kDpMaxNB + wtid];
+                                for (int uu = 0; uu < r.nu; ++uu) ts += sc_tsum[(size_t)un[uu].btile * kDpMaxNB + wtid];
+                                int sh = 0;
+                                while (sh + 1 < V.nshares && V.share[sh].prob != r.prob) ++sh;
+                                Rg.meta[tidx].xscale[wtid] = sc_scale[sh * 4 + wtid];
                                 Rg.meta[tidx].tsum[wtid] = ts;
                             }
                             tc_fence_before();
                             __syncwarp();
                             if (lane == 0) mbar_arrive(&acc_empty[run & 1]);
                             ++run;
-                            u = run_end;
                         }
                     }
+                    DP_STAMP(phs * 10 + 3);
                     // every worker reaches the barrier below whether or not its warp left the loop early;
                     // dp_grid_barrier returns the shared abort state, so the decision to stop is the same for all
                     ok = dp_grid_barrier(P.grid_bar, bar_target, G, abort_flag, wtid);
                     if (!ok) break;
+                    DP_STAMP(phs * 10 + 4);
 
                     // ---------- residual stream: x += result, on disjoint slices, then a second barrier ----------
-                    if (phase == DP_P3 || phase == DP_P5) {
+                    if (v == DV_P3 || v == DV_P5) {
+                        const DpMat& mat = Ly->mat[v == DV_P3 ? DM_WO : DM_WFV];
                         for (int i = wtid; i < NB * (c1 - c0); i += kDpWorkers) {
                             const int b = i / (c1 - c0), m = c0 + i % (c1 - c0);
-                            P.x[(size_t)b * C + m] += dp_finalize(P, ph, 0, m, b, G);
+                            P.x[(size_t)b * C + m] += dp_finalize(P.reg[V.region], V, 0, mat, m, b);
                         }
+                        DP_STAMP(phs * 10 + 5);
                         ok = dp_grid_barrier(P.grid_bar, bar_target, G, abort_flag, wtid);
                         if (!ok) break;
+                        DP_STAMP(phs * 10 + 6);
                     }
                     // ---------- logits, arg-max ----------
-                    if (phase == DP_HEAD) {
+                    if (v == DV_HEAD) {
                         const int v0 = (int)(((long long)cta * P.V) / G), v1 = (int)(((long long)(cta + 1) * P.V) / G);
                         for (int b = 0; b < NB; ++b) {
                             float bv = -1e30f;
                             int bi = 0x7fffffff;
                             for (int vv = v0 + wtid; vv < v1; vv += kDpWorkers) {
-                                const float lg = dp_finalize(P, ph, 0, vv, b, G);
+                                const float lg = dp_finalize(P.reg[DR_HEAD], V, 0, P.head, vv, b);
                                 P.logits[(size_t)b * P.V + vv] = lg;
                                 if (lg > bv) {
                                     bv = lg;
@@ -787,15 +962,15 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                                 }
                             }
                             dp_worker_sync();
-                            if ((wtid & 31) == 0) {
-                                red[wtid >> 5] = bv;
-                                reinterpret_cast<int*>(red)[4 + (wtid >> 5)] = bi;
+                            if (lane == 0) {
+                                red[wwarp] = bv;
+                                reinterpret_cast<int*>(red)[8 + wwarp] = bi;
                             }
                             dp_worker_sync();
                             if (wtid == 0) {
-                                for (int w2 = 1; w2 < 4; ++w2) {
+                                for (int w2 = 1; w2 < kDpWarps; ++w2) {
                                     const float ov = red[w2];
-                                    const int oi = reinterpret_cast<int*>(red)[4 + w2];
+                                    const int oi = reinterpret_cast<int*>(red)[8 + w2];
                                     if (ov > bv || (ov == bv && oi < bi)) {
                                         bv = ov;
                                         bi = oi;
@@ -844,7 +1019,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc(tmem_base, 32);
+        tmem_dealloc(tmem_base, 128);
     }
 }
 

@@ -864,33 +864,43 @@ DpMat make_dpmat(const LinearW& W, int map_index) {
 struct HostProb {
     int mtiles, kblocks;
 };
-// largest number of CTAs that share one tile, and the largest number of operand tiles a CTA needs, for a phase
-void phase_shape(const std::vector<HostProb>& probs, int G, int& pmax, int& btiles, int& tiles) {
+// largest number of CTAs that share one tile, and per CTA the largest numbers of operand tiles, units, runs and
+// problem shares, for one phase shape (the device builds its tables with the same formulas)
+struct PhaseShape {
+    int pmax = 1, btiles = 0, tiles = 0, units = 0, runs = 0, shares = 0;
+};
+PhaseShape phase_shape(const std::vector<HostProb>& probs, int G) {
+    PhaseShape ps;
     int U = 0;
     for (auto& q : probs) U += q.mtiles * q.kblocks;
     G = std::min(G, U);  // only the first min(G, U) CTAs take part in a phase
-    tiles = 0;
-    pmax = 1;
     int u0 = 0;
     for (auto& q : probs) {
         for (int t = 0; t < q.mtiles; ++t) {
             const int first = u0 + t * q.kblocks;
-            pmax = std::max(pmax, tc_cta_of_unit(first + q.kblocks - 1, U, G) - tc_cta_of_unit(first, U, G) + 1);
+            ps.pmax = std::max(ps.pmax, tc_cta_of_unit(first + q.kblocks - 1, U, G) - tc_cta_of_unit(first, U, G) + 1);
         }
         u0 += q.mtiles * q.kblocks;
-        tiles += q.mtiles;
+        ps.tiles += q.mtiles;
     }
-    btiles = 0;
     for (int c = 0; c < G; ++c) {
         const int ub = tc_cta_begin(c, U, G), ue = tc_cta_begin(c + 1, U, G);
-        int need = 0, p0 = 0;
+        int need = 0, p0 = 0, runs = 0, shares = 0;
         for (auto& q : probs) {
             const int lo = std::max(ub, p0), hi = std::min(ue, p0 + q.mtiles * q.kblocks);
-            if (hi > lo) need += std::min(hi - lo, q.kblocks);
+            if (hi > lo) {
+                need += std::min(hi - lo, q.kblocks);
+                ++shares;
+                runs += (hi - 1 - p0) / q.kblocks - (lo - p0) / q.kblocks + 1;
+            }
             p0 += q.mtiles * q.kblocks;
         }
-        btiles = std::max(btiles, need);
+        ps.btiles = std::max(ps.btiles, need);
+        ps.units = std::max(ps.units, ue - ub);
+        ps.runs = std::max(ps.runs, runs);
+        ps.shares = std::max(ps.shares, shares);
     }
+    return ps;
 }
 
 }  // namespace
@@ -925,16 +935,16 @@ bool Model::persistent_available(int nb) {
         const LayerW& Lw = layers[l];
         DpLayer& d = dl[l];
         memset(&d, 0, sizeof(d));
-        d.Wr = add(Lw.Wr);
-        d.Wk = add(Lw.Wk);
-        d.Wv = add(Lw.Wv);
-        d.Wo = add(Lw.Wo);
-        d.Wfk = add(Lw.Wfk);
-        d.Wfv = add(Lw.Wfv);
-        d.w1 = add(Lw.w1);
-        d.a1 = add(Lw.a1);
-        d.v1 = add(Lw.v1);
-        d.g1 = add(Lw.g1);
+        d.mat[DM_WR] = add(Lw.Wr);
+        d.mat[DM_WK] = add(Lw.Wk);
+        d.mat[DM_WV] = add(Lw.Wv);
+        d.mat[DM_WO] = add(Lw.Wo);
+        d.mat[DM_WFK] = add(Lw.Wfk);
+        d.mat[DM_WFV] = add(Lw.Wfv);
+        d.mat[DM_W1] = add(Lw.w1);
+        d.mat[DM_A1] = add(Lw.a1);
+        d.mat[DM_V1] = add(Lw.v1);
+        d.mat[DM_G1] = add(Lw.g1);
         d.w2 = (const __half*)Lw.w2.w;
         d.a2 = (const __half*)Lw.a2.w;
         d.v2 = (const __half*)Lw.v2.w;
@@ -966,27 +976,35 @@ bool Model::persistent_available(int nb) {
     // phase shapes (layer 0 has no v1 problem; all layers share the matrix shapes)
     auto hp = [&](const DpMat& d) { return HostProb{d.mtiles, d.kblocks}; };
     const DpLayer& d0 = dl[0];
-    std::vector<HostProb> p1a = {hp(d0.Wr), hp(d0.Wk), hp(d0.Wv), hp(d0.w1), hp(d0.a1), hp(d0.g1)};
+    std::vector<HostProb> p1a = {hp(d0.mat[DM_WR]), hp(d0.mat[DM_WK]), hp(d0.mat[DM_WV]), hp(d0.mat[DM_W1]), hp(d0.mat[DM_A1]), hp(d0.mat[DM_G1])};
     std::vector<HostProb> p1b = p1a;
-    p1b.push_back(hp(d0.v1));
-    int pm, bt, tl, pmax[5], tiles[5], btiles = 0;
-    phase_shape(p1a, G, pm, bt, tl);
-    pmax[0] = pm;
-    btiles = std::max(btiles, bt);
-    phase_shape(p1b, G, pm, bt, tl);
-    pmax[0] = std::max(pmax[0], pm);
-    tiles[0] = tl;
-    btiles = std::max(btiles, bt);
-    const DpMat* single[4] = {&d0.Wo, &d0.Wfk, &d0.Wfv, &P.head};
-    for (int i = 0; i < 4; ++i) {
-        phase_shape({hp(*single[i])}, G, pm, bt, tl);
-        pmax[i + 1] = pm;
-        tiles[i + 1] = tl;
-        btiles = std::max(btiles, bt);
+    p1b.push_back(hp(d0.mat[DM_V1]));
+    int pmax[5], tiles[5], btiles = 0, max_units = 8, max_runs = 0, max_shares = 0;
+    {
+        const PhaseShape a = phase_shape(p1a, G), b = phase_shape(p1b, G);
+        pmax[0] = std::max(a.pmax, b.pmax);
+        tiles[0] = b.tiles;
+        btiles = std::max(a.btiles, b.btiles);
+        max_units += a.units + b.units;
+        max_runs = std::max(a.runs, b.runs);
+        max_shares = std::max(a.shares, b.shares);
     }
+    const DpMat* single[4] = {&d0.mat[DM_WO], &d0.mat[DM_WFK], &d0.mat[DM_WFV], &P.head};
+    for (int i = 0; i < 4; ++i) {
+        const PhaseShape a = phase_shape({hp(*single[i])}, G);
+        pmax[i + 1] = a.pmax;
+        tiles[i + 1] = a.tiles;
+        btiles = std::max(btiles, a.btiles);
+        max_units += a.units;
+        max_runs = std::max(max_runs, a.runs);
+        max_shares = std::max(max_shares, a.shares);
+    }
+    if (max_runs > kDpMaxRuns || max_shares > kDpMaxShares) return fail("schedule tables of the persistent kernel are too small for this shape");
+    if (btiles > 255) return fail("too many operand tiles per CTA for this shape");
+    if (C > 16 * kDpWorkers) return fail("n_embd too large for the persistent kernel's register-resident LayerNorm");
     // shared memory: ring + operand tiles + barriers + worker scratch
-    const size_t fixed = (size_t)btiles * kDpBTile + 1024 /*alignment*/ + 4096 /*barriers, small scratch*/ + (size_t)btiles * kDpMaxNB * 8 +
-                         (size_t)cfg.mids() * 4 + 8 * 64 * 4;
+    const size_t fixed = (size_t)btiles * kDpBTile + 1024 /*alignment*/ + 2048 /*barriers, small scratch*/ + (size_t)btiles * kDpMaxNB * 8 +
+                         (size_t)cfg.mids() * 4 + 8 * 64 * 4 + DV_COUNT * sizeof(DpVar) + (size_t)max_units * sizeof(DpUnit);
     const size_t budget = 227 * 1024;
     if (fixed + 3 * (size_t)kDpATile > budget) return fail("operand tiles do not fit in shared memory for this shape");
     const int nstages = (int)std::min<size_t>(10, (budget - fixed) / kDpATile);
@@ -1008,6 +1026,11 @@ bool Model::persistent_available(int nb) {
     RSV_CUDA(cudaMalloc(&pc.cand_val, (size_t)G * kDpMaxNB * 4));
     RSV_CUDA(cudaMalloc(&pc.cand_idx, (size_t)G * kDpMaxNB * 4));
     RSV_CUDA(cudaMalloc(&pc.grid_bar, 4));
+    if (const char* e = getenv("RSV_DP_DEBUG"))
+        if (*e && *e != '0') {
+            RSV_CUDA(cudaMalloc(&pc.dbg, 64 * sizeof(long long)));
+            RSV_CUDA(cudaMemset(pc.dbg, 0, 64 * sizeof(long long)));
+        }
     RSV_CUDA(cudaMemset(pc.vfirst, 0, (size_t)kDpMaxNB * C * 4));
     for (int i = 0; i < 5; ++i) {
         const size_t runs = (size_t)tiles[i] * pmax[i];
@@ -1043,12 +1066,14 @@ bool Model::persistent_available(int nb) {
         P.reg[i].meta = (DpRunMeta*)pc.region_meta[i];
         P.reg[i].pmax = pmax[i];
     }
+    P.dbg = pc.dbg;
     P.cand_val = pc.cand_val;
     P.cand_idx = pc.cand_idx;
     P.grid_bar = pc.grid_bar;
     P.status = ws.status;
     P.nstages = nstages;
     P.btiles = btiles;
+    P.max_units = max_units;
     memcpy(pc.params_template.data(), &P, sizeof(P));
     memcpy(pc.params_template.data() + sizeof(P), dl.data(), dl.size() * sizeof(DpLayer));
     pc.ok = true;
@@ -1099,6 +1124,21 @@ void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bo
     LAUNCH(*this, "decode_persistent") {
         RSV_CUDA(cudaLaunchCooperativeKernel((const void*)decode_persistent_kernel, dim3(pc.grid), dim3(kDpThreads), args, pc.smem, stream));
     }
+    if (pc.dbg && n_tokens >= 2) {
+        long long h[64];
+        RSV_CUDA(cudaStreamSynchronize(stream));
+        RSV_CUDA(cudaMemcpy(h, pc.dbg, sizeof(h), cudaMemcpyDeviceToHost));
+        const char* names[7] = {"phase start", "stats done", "operands done", "runs drained", "barrier done", "x slice done", "barrier b done"};
+        long long t0 = h[0];
+        fprintf(stderr, "[persistent kernel, CTA 0, token 1, layer 1] times in us since P1 start\n");
+        for (int ph = 0; ph < 4; ++ph) {
+            if (ph == 1) fprintf(stderr, "  heads done %.2f, barrier 2 done %.2f\n", (h[40] - t0) / 1e3, (h[41] - t0) / 1e3);
+            for (int i = 0; i < 7; ++i)
+                if (h[ph * 10 + i]) fprintf(stderr, "  phase %d %-14s %.2f\n", ph, names[i], (h[ph * 10 + i] - t0) / 1e3);
+        }
+        fprintf(stderr, "  ffn.key phase: producer issued its %lld tiles from %.2f to %.2f; MMA thread started %.2f, last issue %.2f, waited %.2f us for tiles/accumulators\n",
+                h[53], (h[55] - t0) / 1e3, (h[56] - t0) / 1e3, (h[50] - t0) / 1e3, (h[51] - t0) / 1e3, h[52] / 1e3);
+    }
 }
 
 void Model::check_status() {
@@ -1107,6 +1147,7 @@ void Model::check_status() {
     RSV_CUDA(cudaStreamSynchronize(stream));
     if (s) {
         RSV_CUDA(cudaMemsetAsync(ws.status, 0, sizeof(int), stream));
+        if (s & 8) throw std::runtime_error("persistent decode kernel: schedule tables too small for this shape (device status bit 3)");
         if (s & 4) throw std::runtime_error("persistent decode kernel gave up waiting on a barrier (device status bit 2)");
         if (s & 2) throw std::runtime_error("tensor-core kernel gave up waiting on a barrier (device status bit 1)");
         if (s & 1) throw std::runtime_error("token id out of range (>= vocab); the embedding row 0 was used instead");

@@ -80,6 +80,7 @@ struct PersistentCtx {
     float *x = nullptr, *yg = nullptr, *vfirst = nullptr, *cand_val = nullptr;
     int* cand_idx = nullptr;
     unsigned* grid_bar = nullptr;
+    long long* dbg = nullptr;  // RSV_DP_DEBUG=1: phase time stamps of the persistent kernel
     void* region_data[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     void* region_meta[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     int region_pmax[5] = {1, 1, 1, 1, 1};
