@@ -108,6 +108,29 @@ int rsv_sample_selfloop_submit(rsv_model* m, rsv_state* s, const uint32_t* seeds
  * (slot-major) and frees the ticket. */
 int rsv_sample_selfloop_collect(rsv_ticket* t, uint32_t* out, int64_t len);
 
+/* ---- continuous batching ----------------------------------------------------------------------
+ * No counterpart in the reference, whose batching is static (fixed batch, prompts padded to a common length, all slots
+ * decode the same number of steps; src/gpu_model.rs:868-1803, examples/batch_summarize.rs:270-370).  Sessions are submitted
+ * at any time; each rsv_sched_step packs one ragged step — a decode row per generating session plus prompt chunks of at most
+ * `chunk` tokens — and queues it on the model's stream without waiting for it.  Per session the result equals the
+ * single-session API: the prompt is prefilled, then token r is sampled from the previous token's logits with RNG seed
+ * sp->seed + r and the r tokens generated so far as penalty history (sp == NULL: arg-max). */
+typedef struct rsv_sched rsv_sched;
+/* max_slots: concurrent sessions (state slots); chunk: prompt tokens of one session per step; max_rows: rows per step
+ * (>= max_slots); max_new_cap: upper bound on max_new of any session. */
+int rsv_sched_new(rsv_model* m, int64_t max_slots, int64_t chunk, int64_t max_rows, int64_t max_new_cap, rsv_sched** out);
+void rsv_sched_free(rsv_sched* s);
+int rsv_sched_submit(rsv_sched* s, const uint32_t* prompt, int64_t n_prompt, int64_t max_new, const rsv_sampler_params* sp, int64_t* id_out);
+/* Queues one step.  rows_out: rows packed into it (0 = nothing to do); active_out: sessions not yet finished. */
+int rsv_sched_step(rsv_sched* s, int64_t* rows_out, int64_t* active_out);
+/* Ids of sessions whose tokens have reached the host since the last poll (never blocks). */
+int rsv_sched_poll(rsv_sched* s, int64_t* ids, int64_t cap, int64_t* n_out);
+/* Generated tokens of a finished session; the session is forgotten afterwards. */
+int rsv_sched_result(rsv_sched* s, int64_t id, uint32_t* out, int64_t cap, int64_t* n_out);
+/* Waits for everything queued so far and reports device-side errors. */
+int rsv_sched_sync(rsv_sched* s);
+int rsv_sched_stats(rsv_sched* s, int64_t* steps_out, int64_t* rows_out);
+
 /* ---- profiling / timing ----------------------------------------------------------------------- */
 /* Bundle::clear_kernel_prof / dump_kernel_prof (src/gpu_model.rs:3739-3746).  While enabled every kernel is
  * bracketed by a CUDA event pair on the model's stream (this serialises the stream: diagnostics only). */

@@ -15,7 +15,7 @@ _PKG = _os.path.dirname(_os.path.abspath(__file__))
 LIB_CUDA = _os.path.join(_PKG, "librsv_b200.so")
 LIB_SYNTH = _os.path.join(_PKG, "librsv_synth.so")
 
-__all__ = ["ModelBuilder", "Bundle", "State", "SamplerParams", "RnnInput", "RnnOption", "ModelInfo", "RsvError", "write_synthetic", "SHAPES",
+__all__ = ["ModelBuilder", "Bundle", "State", "Scheduler", "SamplerParams", "RnnInput", "RnnOption", "ModelInfo", "RsvError", "write_synthetic", "SHAPES",
            "op_dequant_int8", "op_linear", "op_argmax", "op_sample", "native", "ABI_SYMBOLS"]
 
 
@@ -30,7 +30,8 @@ ABI_SYMBOLS = [
     "rsv_infer_tokens", "rsv_infer_seq", "rsv_infer_chunked", "rsv_infer_full", "rsv_infer_argmax", "rsv_infer_argmax_selfloop",
     "rsv_infer_sample", "rsv_infer_sample_selfloop", "rsv_prefill_batch", "rsv_sample_selfloop_submit", "rsv_sample_selfloop_collect",
     "rsv_prof_enable", "rsv_prof_clear", "rsv_prof_dump", "rsv_launch_count", "rsv_timer_start", "rsv_timer_stop", "rsv_synchronize",
-    "rsv_op_dequant_int8", "rsv_op_linear", "rsv_op_argmax", "rsv_op_sample", "rsv_op_sample_static",
+    "rsv_sched_new", "rsv_sched_free", "rsv_sched_submit", "rsv_sched_step", "rsv_sched_poll", "rsv_sched_result", "rsv_sched_sync",
+    "rsv_sched_stats", "rsv_op_dequant_int8", "rsv_op_linear", "rsv_op_argmax", "rsv_op_sample", "rsv_op_sample_static",
 ]
 
 
@@ -96,6 +97,15 @@ def native():
         L.rsv_timer_start.argtypes = [vp]
         L.rsv_timer_stop.argtypes = [vp, _c.POINTER(_c.c_float)]
         L.rsv_synchronize.argtypes = [vp]
+        L.rsv_sched_new.argtypes = [vp, i64, i64, i64, i64, pp]
+        L.rsv_sched_free.argtypes = [vp]
+        L.rsv_sched_free.restype = None
+        L.rsv_sched_submit.argtypes = [vp, vp, i64, i64, _c.POINTER(SamplerParams), _c.POINTER(i64)]
+        L.rsv_sched_step.argtypes = [vp, _c.POINTER(i64), _c.POINTER(i64)]
+        L.rsv_sched_poll.argtypes = [vp, vp, i64, _c.POINTER(i64)]
+        L.rsv_sched_result.argtypes = [vp, i64, vp, i64, _c.POINTER(i64)]
+        L.rsv_sched_sync.argtypes = [vp]
+        L.rsv_sched_stats.argtypes = [vp, _c.POINTER(i64), _c.POINTER(i64)]
         L.rsv_op_dequant_int8.argtypes = [_c.c_int, vp, vp, i64, i64, vp]
         L.rsv_op_argmax.argtypes = [_c.c_int, vp, i64, i64, vp]
         L.rsv_op_linear.argtypes = [_c.c_int, _c.c_int, _c.c_int, vp, vp, i64, i64, vp, i64, vp]
@@ -352,6 +362,74 @@ class Bundle:
     def dump_kernel_prof(self):
         for k, v in sorted(self.model.kernel_prof().items(), key=lambda kv: -kv[1]["ms"]):
             print(f"{k:24s} {v['launches']:8d} launches {v['ms']:10.3f} ms")
+
+
+class Scheduler:
+    """Continuous batching over one model (rsv_sched_*): submit sessions at any time, call step() repeatedly."""
+
+    def __init__(self, model, max_slots, chunk=512, max_rows=None, max_new_cap=4096):
+        h = _c.c_void_p()
+        max_rows = max_rows if max_rows is not None else max(max_slots, chunk) + max_slots
+        _check(native().rsv_sched_new(model._h, int(max_slots), int(chunk), int(max_rows), int(max_new_cap), _c.byref(h)))
+        self._h, self._model, self._cap = h, model, int(max_new_cap)
+
+    def submit(self, prompt, max_new, sp=None):
+        t = _tokens(prompt)
+        rid = _c.c_int64()
+        _check(native().rsv_sched_submit(self._h, _ptr(t), t.size, int(max_new), _c.byref(sp) if sp is not None else None, _c.byref(rid)))
+        return int(rid.value)
+
+    def step(self):
+        """Queues one packed step; returns (rows in the step, sessions not yet finished)."""
+        rows, active = _c.c_int64(), _c.c_int64()
+        _check(native().rsv_sched_step(self._h, _c.byref(rows), _c.byref(active)))
+        return int(rows.value), int(active.value)
+
+    def poll(self):
+        ids = _np.zeros(1024, dtype=_np.int64)
+        n = _c.c_int64()
+        _check(native().rsv_sched_poll(self._h, _ptr(ids), ids.size, _c.byref(n)))
+        return [int(i) for i in ids[:n.value]]
+
+    def result(self, rid):
+        out = _np.zeros(self._cap, dtype=_np.uint32)
+        n = _c.c_int64()
+        _check(native().rsv_sched_result(self._h, int(rid), _ptr(out), out.size, _c.byref(n)))
+        return out[:n.value].copy()
+
+    def sync(self):
+        _check(native().rsv_sched_sync(self._h))
+
+    def stats(self):
+        a, b = _c.c_int64(), _c.c_int64()
+        _check(native().rsv_sched_stats(self._h, _c.byref(a), _c.byref(b)))
+        return {"steps": int(a.value), "rows": int(b.value)}
+
+    def run_until_done(self):
+        """Steps until every submitted session has finished; returns {id: tokens}."""
+        done = {}
+        while True:
+            rows, active = self.step()
+            for rid in self.poll():
+                done[rid] = self.result(rid)
+            if active == 0:
+                break
+            if rows == 0:
+                self.sync()
+        for rid in self.poll():
+            done[rid] = self.result(rid)
+        return done
+
+    def close(self):
+        if getattr(self, "_h", None):
+            native().rsv_sched_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class ModelBuilder:

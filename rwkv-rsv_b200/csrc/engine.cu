@@ -334,8 +334,9 @@ std::unique_ptr<Model> Model::load(const std::string& path, int device) {
         L.g1 = ld.lowrank(p + "att.g1", C, c.g_mid);
         L.g2 = ld.lowrank(p + "att.g2", c.g_mid, C);
     }
-    m->pinned_bytes = 1 << 20;
-    RSV_CUDA(cudaMallocHost(&m->pinned, m->pinned_bytes));
+    m->pinned_bytes = 1 << 18;
+    RSV_CUDA(cudaMallocHost(&m->pinned, m->pinned_bytes * Model::kPinRing));
+    for (int i = 0; i < Model::kPinRing; ++i) RSV_CUDA(cudaEventCreateWithFlags(&m->pin_ev[i], cudaEventDisableTiming));
     RSV_CUDA(cudaMalloc(&m->ws.status, sizeof(int)));
     RSV_CUDA(cudaMalloc(&m->ws.tok_pos, sizeof(int)));
     RSV_CUDA(cudaMemset(m->ws.status, 0, sizeof(int)));
@@ -405,6 +406,8 @@ Model::~Model() {
         if (pctx.region_meta[i]) cudaFree(pctx.region_meta[i]);
     }
     if (pinned) cudaFreeHost(pinned);
+    for (int i = 0; i < kPinRing; ++i)
+        if (pin_ev[i]) cudaEventDestroy(pin_ev[i]);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
     if (tev[0]) cudaEventDestroy(tev[0]);
@@ -458,16 +461,18 @@ void Model::ensure_workspace(int rows, int outs, int segs) {
         cudaFreeHost(pinned);
         pinned = nullptr;
         pinned_bytes = need * 2;
-        RSV_CUDA(cudaMallocHost(&pinned, pinned_bytes));
+        RSV_CUDA(cudaMallocHost(&pinned, pinned_bytes * kPinRing));
     }
 }
 
 void Model::upload_plan(const StepPlan& plan) {
     const int R = (int)plan.rows.size(), S = (int)plan.segs.size(), O = (int)plan.out_rows.size();
     ensure_workspace(R, std::max(O, 1), S);
-    // the pinned staging buffer is reused: the previous step's copies must have been issued AND consumed
-    RSV_CUDA(cudaStreamSynchronize(stream));
-    char* p = (char*)pinned;
+    // next area of the staging ring; its previous copies (kPinRing uploads ago) must have completed
+    const int slot = pin_next;
+    pin_next = (pin_next + 1) % kPinRing;
+    if (pin_ev[slot]) RSV_CUDA(cudaEventSynchronize(pin_ev[slot]));
+    char* p = (char*)pinned + (size_t)slot * pinned_bytes;
     memcpy(p, plan.rows.data(), R * sizeof(RowMeta));
     RSV_CUDA(cudaMemcpyAsync(ws.row_meta, p, R * sizeof(RowMeta), cudaMemcpyHostToDevice, stream));
     p += R * sizeof(RowMeta);
@@ -478,6 +483,7 @@ void Model::upload_plan(const StepPlan& plan) {
         memcpy(p, plan.out_rows.data(), O * sizeof(int));
         RSV_CUDA(cudaMemcpyAsync(ws.out_rows, p, O * sizeof(int), cudaMemcpyHostToDevice, stream));
     }
+    if (pin_ev[slot]) RSV_CUDA(cudaEventRecord(pin_ev[slot], stream));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1158,19 +1164,20 @@ void Model::check_status() {
 // ------------------------------------------------------------------------------------------------
 // helpers used by the C ABI
 // ------------------------------------------------------------------------------------------------
-void engine_argmax(Model& m, const float* logits_dev, int rows, uint32_t* next_tok_dev, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap) {
+void engine_argmax(Model& m, const float* logits_dev, int rows, uint32_t* next_tok_dev, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap,
+                   const int* row_map_dev) {
     LAUNCH(m, "argmax") {
-        argmax_rows_kernel<<<rows, kArgmaxThreads, 0, m.stream>>>(logits_dev, m.cfg.vocab, next_tok_dev, seq_dev, seq_cnt_dev, seq_cap);
+        argmax_rows_kernel<<<rows, kArgmaxThreads, 0, m.stream>>>(logits_dev, m.cfg.vocab, next_tok_dev, seq_dev, seq_cnt_dev, seq_cap, row_map_dev);
         check_launch("argmax");
     }
 }
 
 void engine_sample(Model& m, const float* logits_dev, int rows, const float* sampler8_dev, const uint32_t* hist_dev, int hist_stride,
-                   const int* round_cnt_dev, uint32_t* next_tok_dev, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap) {
+                   const int* round_cnt_dev, uint32_t* next_tok_dev, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap, const int* row_map_dev) {
     if (rows > m.ws.outs) throw std::runtime_error("engine_sample: more rows than the work area holds");
     LAUNCH(m, "sample") {
         sample_rows_kernel<<<rows, kSampleThreads, 0, m.stream>>>(logits_dev, m.cfg.vocab, sampler8_dev, hist_dev, hist_stride, round_cnt_dev, m.ws.samp_temp,
-                                                                  m.ws.samp_cnt, next_tok_dev, seq_dev, seq_cnt_dev, seq_cap);
+                                                                  m.ws.samp_cnt, next_tok_dev, seq_dev, seq_cnt_dev, seq_cap, row_map_dev);
         check_launch("sample");
     }
 }
@@ -1178,7 +1185,7 @@ void engine_sample(Model& m, const float* logits_dev, int rows, const float* sam
 void engine_sample_raw(cudaStream_t stream, const float* logits_dev, int rows, int V, const float* sampler8_dev, const uint32_t* hist_dev,
                        int hist_stride, float* temp_dev, uint32_t* counter_dev, uint32_t* out_dev) {
     sample_rows_kernel<<<rows, kSampleThreads, 0, stream>>>(logits_dev, V, sampler8_dev, hist_dev, hist_stride, nullptr, temp_dev, counter_dev, out_dev,
-                                                            nullptr, nullptr, 0);
+                                                            nullptr, nullptr, 0, nullptr);
     check_launch("sample");
 }
 
@@ -1194,8 +1201,15 @@ Ticket::~Ticket() {
     if (sampler) cudaFree(sampler);
 }
 
+void engine_merge_tokens(Model& m, const uint32_t* host_tok_dev, const uint32_t* slot_tok_dev, int R) {
+    LAUNCH(m, "merge_tokens") {
+        merge_tokens_kernel<<<(R + 255) / 256, 256, 0, m.stream>>>(host_tok_dev, m.ws.row_meta, slot_tok_dev, R, m.ws.tokens);
+        check_launch("merge_tokens");
+    }
+}
+
 void engine_argmax_raw(cudaStream_t stream, const float* logits_dev, int rows, int V, uint32_t* out_dev) {
-    argmax_rows_kernel<<<rows, kArgmaxThreads, 0, stream>>>(logits_dev, V, out_dev, nullptr, nullptr, 0);
+    argmax_rows_kernel<<<rows, kArgmaxThreads, 0, stream>>>(logits_dev, V, out_dev, nullptr, nullptr, 0, nullptr);
     check_launch("argmax");
 }
 
@@ -1309,7 +1323,7 @@ extern "C" int rsv_op_sample_static(int device, void* stream, const float* logit
         }
         sample_rows_kernel<<<(unsigned)rows, kSampleThreads, 0, (cudaStream_t)stream>>>(logits_dev, (int)V, sampler8_dev, hist_stride ? hist_dev : nullptr,
                                                                                         (int)hist_stride, nullptr, sc.temp, sc.cnt, out_dev, nullptr,
-                                                                                        nullptr, 0);
+                                                                                        nullptr, 0, nullptr);
         check_launch("sample_static");
         return 0;
     } catch (const CudaError& e) {

@@ -127,9 +127,13 @@ struct Model {
     std::vector<void*> allocs;  // every weight allocation, freed in the destructor
     size_t weight_bytes = 0;
     Workspace ws;
-    // pinned staging for per-step metadata
+    // pinned staging for per-step metadata: a ring of kPinRing areas, each guarded by an event, so that queuing a step
+    // never waits for the previous one
+    static constexpr int kPinRing = 4;
     void* pinned = nullptr;
-    size_t pinned_bytes = 0;
+    size_t pinned_bytes = 0;  // bytes per ring area
+    cudaEvent_t pin_ev[kPinRing] = {nullptr, nullptr, nullptr, nullptr};
+    int pin_next = 0;
     // profiling (clear_kernel_prof / dump_kernel_prof of the reference, src/gpu_model.rs:561-570)
     bool prof_on = false;
     std::map<std::string, KernelProf> prof;
@@ -173,9 +177,13 @@ struct Ticket {
 };
 
 // launch wrappers defined next to the kernels
-void engine_argmax(Model& m, const float* logits_dev, int rows, uint32_t* next_tok_dev, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap);
+// `row_map_dev` (optional): logits row r belongs to entry row_map[r] of the per-session arrays
+void engine_argmax(Model& m, const float* logits_dev, int rows, uint32_t* next_tok_dev, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap,
+                   const int* row_map_dev = nullptr);
 void engine_sample(Model& m, const float* logits_dev, int rows, const float* sampler8_dev, const uint32_t* hist_dev, int hist_stride,
-                   const int* round_cnt_dev, uint32_t* next_tok_dev, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap);
+                   const int* round_cnt_dev, uint32_t* next_tok_dev, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap, const int* row_map_dev = nullptr);
+// ws.tokens[r] = host_tok[r], or slot_tok[slot of row r] where host_tok[r] == 0xFFFFFFFF (rows as last uploaded with upload_plan)
+void engine_merge_tokens(Model& m, const uint32_t* host_tok_dev, const uint32_t* slot_tok_dev, int R);
 void engine_argmax_raw(cudaStream_t stream, const float* logits_dev, int rows, int V, uint32_t* out_dev);
 void engine_sample_raw(cudaStream_t stream, const float* logits_dev, int rows, int V, const float* sampler8_dev, const uint32_t* hist_dev,
                        int hist_stride, float* temp_dev, uint32_t* counter_dev, uint32_t* out_dev);

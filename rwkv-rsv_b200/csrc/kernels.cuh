@@ -444,8 +444,11 @@ __device__ __forceinline__ void argmax_combine(float& bv, int& bi, float ov, int
         bi = oi;
     }
 }
+// `row_map` (optional) sends logits row r to entry row_map[r] of next_tok / seq / seq_cnt (the continuous-batching
+// scheduler keeps those per slot, while the logits rows are packed per step).
 __global__ void __launch_bounds__(kArgmaxThreads) argmax_rows_kernel(const float* __restrict__ logits, int V, uint32_t* __restrict__ next_tok,
-                                                                     uint32_t* __restrict__ seq, int* __restrict__ seq_cnt, int seq_cap) {
+                                                                     uint32_t* __restrict__ seq, int* __restrict__ seq_cnt, int seq_cap,
+                                                                     const int* __restrict__ row_map) {
     __shared__ float sv[kArgmaxThreads / 32];
     __shared__ int si[kArgmaxThreads / 32];
     const int row = blockIdx.x;
@@ -472,11 +475,12 @@ __global__ void __launch_bounds__(kArgmaxThreads) argmax_rows_kernel(const float
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int i2 = 1; i2 < kArgmaxThreads / 32; ++i2) argmax_combine(bv, bi, sv[i2], si[i2]);
-        next_tok[row] = (uint32_t)bi;
+        const int dst = row_map ? row_map[row] : row;
+        next_tok[dst] = (uint32_t)bi;
         if (seq) {
-            const int c = seq_cnt[row];
-            if (c < seq_cap) seq[(size_t)row * seq_cap + c] = (uint32_t)bi;
-            seq_cnt[row] = c + 1;
+            const int c = seq_cnt[dst];
+            if (c < seq_cap) seq[(size_t)dst * seq_cap + c] = (uint32_t)bi;
+            seq_cnt[dst] = c + 1;
         }
     }
 }
@@ -552,7 +556,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_rows_kernel(const float
                                                                      const uint32_t* __restrict__ hist, int hist_stride,
                                                                      const int* __restrict__ round_cnt, float* __restrict__ temp_all,
                                                                      uint32_t* __restrict__ counter_all, uint32_t* __restrict__ next_tok,
-                                                                     uint32_t* __restrict__ seq, int* __restrict__ seq_cnt, int seq_cap) {
+                                                                     uint32_t* __restrict__ seq, int* __restrict__ seq_cnt, int seq_cap,
+                                                                     const int* __restrict__ row_map) {
     __shared__ float red[kSampleThreads / 32];
     __shared__ uint32_t s_hist[256];
     __shared__ uint32_t s_sh[2];
@@ -561,9 +566,10 @@ __global__ void __launch_bounds__(kSampleThreads) sample_rows_kernel(const float
     __shared__ float s_cut;
     __shared__ int s_chosen;
     const int row = blockIdx.x, tid = threadIdx.x;
+    const int ent = row_map ? row_map[row] : row;  // entry of the per-session arrays (sampler rows, history, counters, tokens)
     const float* lg = logits + (size_t)row * V;
     float* temp = temp_all + (size_t)row * V;
-    const float* sp = sampler8 + (size_t)row * 8;
+    const float* sp = sampler8 + (size_t)ent * 8;
     const float temperature = sp[0];
     const uint32_t top_k = __float_as_uint(sp[1]);
     const float top_p = sp[2];
@@ -571,11 +577,11 @@ __global__ void __launch_bounds__(kSampleThreads) sample_rows_kernel(const float
     const float rep = sp[4], freq = sp[5], pres = sp[6];
     uint32_t hist_len = __float_as_uint(sp[7]);
     if (round_cnt) {  // self-loop: round r uses seed+r and the r tokens generated so far
-        const uint32_t round = (uint32_t)round_cnt[row];
+        const uint32_t round = (uint32_t)round_cnt[ent];
         seed += round;
         hist_len = min(round, (uint32_t)hist_stride);
     }
-    const uint32_t* hrow = hist ? hist + (size_t)row * hist_stride : nullptr;
+    const uint32_t* hrow = hist ? hist + (size_t)ent * hist_stride : nullptr;
     const bool penal = hist_len > 0u && hrow && (rep != 1.0f || freq != 0.0f || pres != 0.0f);
     if (penal) {
         uint32_t* counter = counter_all + (size_t)row * V;
@@ -715,13 +721,21 @@ __global__ void __launch_bounds__(kSampleThreads) sample_rows_kernel(const float
     __syncthreads();
     if (tid == 0) {
         const uint32_t tok = (uint32_t)s_chosen;
-        next_tok[row] = tok;
+        next_tok[ent] = tok;
         if (seq) {
-            const int c = seq_cnt[row];
-            if (c < seq_cap) seq[(size_t)row * seq_cap + c] = tok;
-            seq_cnt[row] = c + 1;
+            const int c = seq_cnt[ent];
+            if (c < seq_cap) seq[(size_t)ent * seq_cap + c] = tok;
+            seq_cnt[ent] = c + 1;
         }
     }
+}
+
+// Continuous batching: the input token of row r is either a prompt token supplied by the host or, for a decode
+// row (host value 0xFFFFFFFF), the token last generated for the row's session, which never left the GPU.
+__global__ void merge_tokens_kernel(const uint32_t* __restrict__ host_tok, const RowMeta* __restrict__ rows, const uint32_t* __restrict__ slot_tok, int R,
+                                    uint32_t* __restrict__ tokens) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < R) tokens[r] = host_tok[r] == 0xFFFFFFFFu ? slot_tok[rows[r].slot] : host_tok[r];
 }
 
 // Bit-exact int8 container decode to fp32: w = scale*q + zero evaluated in fp32 with separate
