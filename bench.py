@@ -282,10 +282,8 @@ def main():
     ms, out = decode_run(rsv, model, state, seeds, K)
     launches = model.launch_count()
     torch.cuda.synchronize()
-    if dist:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    from rwkv_rsv_b200.shard import max_over_ranks
+    ms = max_over_ranks(ms, dist, torch.device("cuda", local))  # the slowest replica's device time
     clk = clocks.stop()
     value = world * B * K / (ms / 1000.0)
 
@@ -312,10 +310,7 @@ def main():
         torch.cuda.synchronize()
         el = time.perf_counter() - t0
         assert rc == 0
-        if dist:
-            t = torch.tensor([el], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            el = float(t.item())
+        el = max_over_ranks(el, dist, torch.device("cuda", local))
         e2e = {"value": world * K / el, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * sh["vocab"],
                "api": "rsv_infer_tokens (Bundle::infer_tokens), one token in, logits out, host arg-max"}
 

@@ -499,7 +499,7 @@ SHAPES = {
 }
 
 
-def write_synthetic(path, shape="tiny", seed=0, quant=0, lowrank_transposed=False, quant_head=False, **overrides):
+def write_synthetic(path, shape="tiny", seed=0, quant=0, lowrank_transposed=False, quant_head=False, threads=None, **overrides):
     """Writes a seeded random-init RWKV-7 checkpoint.  quant: 0 fp16, 1 int8 symmetric per output row (in the
     reference's container), 2 int8 per group of 128 (the reference quantiser's rule)."""
     if not _os.path.exists(LIB_SYNTH):
@@ -508,6 +508,8 @@ def write_synthetic(path, shape="tiny", seed=0, quant=0, lowrank_transposed=Fals
     L = _c.CDLL(LIB_SYNTH)
     L.rsv_synth_write.argtypes = [_c.c_char_p, _c.POINTER(_SynthShape), _c.c_uint64, _c.c_int, _c.c_int]
     L.rsv_synth_last_error.restype = _c.c_char_p
+    L.rsv_synth_set_threads.argtypes = [_c.c_int]
+    L.rsv_synth_set_threads(int(threads) if threads else (_os.cpu_count() or 1))
     d = dict(SHAPES[shape]) if isinstance(shape, str) else dict(shape)
     d.update(overrides)
     sh = _SynthShape(**d)

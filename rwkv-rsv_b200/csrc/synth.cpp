@@ -25,6 +25,9 @@
 #include <vector>
 
 #include "safetensors.hpp"
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 namespace {
 
@@ -277,5 +280,14 @@ int rsv_synth_write(const char* path, const rsv_synth_shape* s, uint64_t seed, i
 }
 
 const char* rsv_synth_last_error(void) { return g_err.c_str(); }
+
+// Number of OpenMP threads the generator uses (launchers such as torchrun export OMP_NUM_THREADS=1).
+void rsv_synth_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
 
 }  // extern "C"
