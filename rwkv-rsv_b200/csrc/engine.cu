@@ -368,7 +368,7 @@ std::unique_ptr<Model> Model::create_bare(int device) {
 }
 
 static void free_workspace(Workspace& w) {
-    void* ptrs[] = {w.x, w.xmix, w.r, w.k, w.v, w.w, w.a, w.g, w.yg, w.xb, w.mid, w.h, w.vfirst, w.xn, w.logits, w.staging, w.tokens, w.row_meta, w.seg_meta, w.out_rows, w.samp_temp, w.samp_cnt};
+    void* ptrs[] = {w.x, w.x2, w.delta, w.xmix, w.r, w.k, w.v, w.w, w.a, w.g, w.yg, w.xb, w.mid, w.h, w.vfirst, w.xn, w.logits, w.staging, w.tokens, w.row_meta, w.seg_meta, w.out_rows, w.samp_temp, w.samp_cnt};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     int* status = w.status;
@@ -385,6 +385,7 @@ static void free_workspace(Workspace& w) {
     w.tc_tsum = keep.tc_tsum;
     w.tc_rows = keep.tc_rows;
     w.tc_partials = keep.tc_partials;
+    w.tc_cnt = keep.tc_cnt;
     w.tc_partials_bytes = keep.tc_partials_bytes;
 }
 
@@ -396,7 +397,7 @@ Model::~Model() {
     if (ws.tok_pos) cudaFree(ws.tok_pos);
     if (ws.tok_list) cudaFree(ws.tok_list);
     for (void* p : allocs) cudaFree(p);
-    for (void* p : {(void*)ws.tc_b, (void*)ws.tc_xscale, (void*)ws.tc_tsum, ws.tc_partials})
+    for (void* p : {(void*)ws.tc_b, (void*)ws.tc_xscale, (void*)ws.tc_tsum, ws.tc_partials, (void*)ws.tc_cnt})
         if (p) cudaFree(p);
     for (void* p : {pctx.d_layers, pctx.d_maps, (void*)pctx.x, (void*)pctx.yg, (void*)pctx.vfirst, (void*)pctx.cand_val, (void*)pctx.cand_idx,
                     (void*)pctx.grid_bar})
@@ -431,6 +432,8 @@ void Model::ensure_workspace(int rows, int outs, int segs) {
     const size_t C = cfg.n_embd, F = cfg.ffn_hidden, V = cfg.vocab, R = rows;
     auto fa = [&](float*& p, size_t n) { RSV_CUDA(cudaMalloc(&p, std::max<size_t>(n, 4) * sizeof(float))); };
     fa(ws.x, R * C);
+    fa(ws.x2, R * C);
+    fa(ws.delta, R * C);
     fa(ws.xmix, 6 * R * C);
     fa(ws.r, R * C);
     fa(ws.k, R * C);
@@ -572,6 +575,10 @@ void run_linear_simt(Model& m, const char* name, const LinReq* reqs, int n, int 
 // ---- tensor-core path ---------------------------------------------------------------------------
 void ensure_tc_buffers(Model& m, size_t b_bytes, size_t rows, size_t partial_bytes) {
     Workspace& w = m.ws;
+    if (!w.tc_cnt) {
+        RSV_CUDA(cudaMalloc(&w.tc_cnt, (size_t)kTcMaxSplit * kTcEpiWarps * sizeof(int)));
+        RSV_CUDA(cudaMemset(w.tc_cnt, 0, (size_t)kTcMaxSplit * kTcEpiWarps * sizeof(int)));
+    }
     if (b_bytes <= w.tc_b_bytes && rows <= w.tc_rows && partial_bytes <= w.tc_partials_bytes) return;
     RSV_CUDA(cudaStreamSynchronize(m.stream));
     if (b_bytes > w.tc_b_bytes) {
@@ -658,7 +665,7 @@ void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, i
         L.amap[i] = W.amap;
     }
     const int G = std::min(m.num_sms, U);
-    // tiles cut by a CTA boundary keep partial sums and are finished by tc_finalize_kernel
+    // tiles cut by a CTA boundary keep partial sums; the epilogue warp that arrives last on a sub-block finishes it
     int pmax = 1, nsplit = 0;
     for (int c = 1; c < G; ++c) {
         const int bnd = tc_cta_begin(c, U, G);
@@ -679,14 +686,21 @@ void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, i
     const size_t partial_bytes = (size_t)nsplit * pmax * NT * kTcTileM * 4;
     ensure_tc_buffers(m, b_bytes, (size_t)rows, partial_bytes);
     Workspace& w = m.ws;
-    // operand preparation
-    for (const Region& rg : regions) {
+    // operand preparation: one launch for all the group's activation operands
+    {
+        TcPrepLaunch PL;
+        memset(&PL, 0, sizeof(PL));
+        if (regions.size() > (size_t)kTcMaxProblems) throw std::runtime_error("tc_linear: too many operand regions");
+        for (size_t j = 0; j < regions.size(); ++j) {
+            const Region& rg = regions[j];
+            PL.r[j] = TcPrepRegion{rg.x, w.tc_b + rg.off, w.tc_xscale + rg.row0, w.tc_tsum + rg.row0, rg.ldx, rg.K, rg.Kpad, 0};
+        }
         LAUNCH(m, i8 ? "tc_prepare_i8" : "tc_prepare_f16") {
+            const dim3 grid(R, (unsigned)regions.size());
             if (i8)
-                tc_prepare_i8_kernel<kTcDigits><<<R, kPrepThreads, 0, m.stream>>>(rg.x, rg.ldx, rg.K, rg.Kpad, (int8_t*)(w.tc_b + rg.off), w.tc_xscale + rg.row0,
-                                                                                 w.tc_tsum + rg.row0);
+                tc_prepare_i8_kernel<kTcDigits><<<grid, kPrepThreads, 0, m.stream>>>(PL);
             else
-                tc_prepare_f16_kernel<<<R, kPrepThreads, 0, m.stream>>>(rg.x, rg.ldx, rg.K, rg.Kpad, (__half*)(w.tc_b + rg.off), w.tc_xscale + rg.row0);
+                tc_prepare_f16_kernel<<<grid, kPrepThreads, 0, m.stream>>>(PL);
             check_launch("tc_prepare");
         }
     }
@@ -719,6 +733,7 @@ void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, i
     const size_t stage_bytes = (size_t)kTcTileM * kTcKBlockBytes + (size_t)NT * kTcKBlockBytes;
     L.nstages = (int)std::min<size_t>(8, (200 * 1024) / stage_bytes);
     L.partials = w.tc_partials;
+    L.tile_cnt = w.tc_cnt;
     L.status = w.status;
     const size_t smem = (size_t)L.nstages * stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static bool configured[16] = {false};
@@ -734,10 +749,6 @@ void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, i
             tc_linear_kernel<false><<<G, kTcThreads, smem, m.stream>>>(L);
         check_launch("tc_linear");
     }
-    if (nsplit) LAUNCH(m, "tc_finalize") {
-            tc_finalize_kernel<<<dim3(nsplit, std::max(1, std::min(8, NT / 16))), 256, 0, m.stream>>>(L);
-            check_launch("tc_finalize");
-        }
 }
 
 void run_linear(Model& m, const char* name, const LinReq* reqs, int n, int R) {
@@ -771,6 +782,10 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
                                                         ws.x, ws.status);
         check_launch("embed_ln0");
     }
+    // The residual stream ping-pongs between two buffers: each LayerNorm kernel folds in the pending residual of the
+    // linear layer before it (x_cur + pending -> x_alt) so that no linear epilogue has to read-modify-write x.
+    float *x_cur = ws.x, *x_alt = ws.x2;
+    const float* pending = nullptr;
     const size_t lay_x = (size_t)st.cap * C, lay_s = (size_t)st.cap * H * kHeadSize * kHeadSize;
     for (int l = 0; l < cfg.n_layer; ++l) {
         const LayerW& L = layers[l];
@@ -779,13 +794,18 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
         float* wkv = st.wkv + l * lay_s;
         LAUNCH(*this, "ln_shift6") {
             MixPtrs mp{{L.x_r, L.x_w, L.x_k, L.x_v, L.x_a, L.x_g}};
-            ln_shift_kernel<6><<<R, kRowThreads, 0, stream>>>(ws.x, L.ln1_w, L.ln1_b, mp, ws.row_meta, R, C, tmix_x, staging, ws.xmix);
+            ln_shift_kernel<6><<<R, kRowThreads, 0, stream>>>(x_cur, pending, x_alt, L.ln1_w, L.ln1_b, mp, ws.row_meta, R, C, tmix_x, staging, ws.xmix);
             check_launch("ln_shift6");
+        }
+        if (pending) {
+            std::swap(x_cur, x_alt);
+            pending = nullptr;
         }
         if (staging) LAUNCH(*this, "commit_shift") {
                 commit_shift_kernel<<<S, 256, 0, stream>>>(staging, ws.seg_meta, C, tmix_x);
                 check_launch("commit_shift");
             }
+        float* vgate = l == 0 ? nullptr : ws.xb;  // xb is free until ln_shift1
         {
             // r, k, v and the four rank-space projections in one launch
             float* mw = ws.mid;
@@ -802,28 +822,32 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
                 {&L.v1, xm[3], C, mv, MIDS, EPI_STORE},
             };
             run_linear(*this, "linear_rkv_rank", q, l == 0 ? 6 : 7, R);
+            // back-projections: decay w, a, gate g and (layers > 0) the v-lerp gate; all plain stores
             LinReq q2[4] = {
                 {&L.w2, mw, MIDS, ws.w, C, EPI_DECAY, L.w0},
                 {&L.a2, ma, MIDS, ws.a, C, EPI_SIGMOID_BIAS, L.a0},
                 {&L.g2, mg, MIDS, ws.g, C, EPI_STORE},
-                {&L.v2, mv, MIDS, ws.v, C, EPI_VLERP, L.v0, ws.vfirst, C},
+                {&L.v2, mv, MIDS, vgate, C, EPI_SIGMOID_BIAS, L.v0},
             };
             run_linear(*this, "linear_rank_back", q2, l == 0 ? 3 : 4, R);
         }
         LAUNCH(*this, "wkv7") {
-            wkv7_kernel<<<dim3(H, S), kHeadSize, 0, stream>>>(ws.seg_meta, ws.r, ws.k, ws.v, ws.w, ws.a, ws.g, L.k_k, L.k_a, L.r_k, L.lnx_w, L.lnx_b, wkv,
-                                                              l == 0 ? st.v_first : nullptr, ws.yg, H, C);
+            wkv7_kernel<<<dim3(H, S), kWkvThreads, 0, stream>>>(ws.seg_meta, ws.r, ws.k, ws.v, vgate, ws.vfirst, ws.w, ws.a, ws.g, L.k_k, L.k_a, L.r_k,
+                                                                L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C);
             check_launch("wkv7");
         }
         {
-            LinReq q = {&L.Wo, ws.yg, C, ws.x, C, EPI_ADD};
+            LinReq q = {&L.Wo, ws.yg, C, ws.delta, C, EPI_STORE};
             run_linear(*this, "linear_att_out", &q, 1, R);
+            pending = ws.delta;
         }
         LAUNCH(*this, "ln_shift1") {
             MixPtrs mp{{L.ffn_x_k, nullptr, nullptr, nullptr, nullptr, nullptr}};
-            ln_shift_kernel<1><<<R, kRowThreads, 0, stream>>>(ws.x, L.ln2_w, L.ln2_b, mp, ws.row_meta, R, C, cmix_x, staging, ws.xb);
+            ln_shift_kernel<1><<<R, kRowThreads, 0, stream>>>(x_cur, pending, x_alt, L.ln2_w, L.ln2_b, mp, ws.row_meta, R, C, cmix_x, staging, ws.xb);
             check_launch("ln_shift1");
         }
+        std::swap(x_cur, x_alt);
+        pending = nullptr;
         if (staging) LAUNCH(*this, "commit_shift") {
                 commit_shift_kernel<<<S, 256, 0, stream>>>(staging, ws.seg_meta, C, cmix_x);
                 check_launch("commit_shift");
@@ -831,13 +855,14 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
         {
             LinReq q = {&L.Wfk, ws.xb, C, ws.h, F, EPI_RELU2};
             run_linear(*this, "linear_ffn_key", &q, 1, R);
-            LinReq q2 = {&L.Wfv, ws.h, F, ws.x, C, EPI_ADD};
+            LinReq q2 = {&L.Wfv, ws.h, F, ws.delta, C, EPI_STORE};
             run_linear(*this, "linear_ffn_value", &q2, 1, R);
+            pending = ws.delta;
         }
     }
     if (O) {
         LAUNCH(*this, "ln_out") {
-            ln_rows_kernel<<<O, kRowThreads, 0, stream>>>(ws.x, ln_out_w, ln_out_b, ws.out_rows, C, ws.xn);
+            ln_rows_kernel<<<O, kRowThreads, 0, stream>>>(x_cur, pending, ln_out_w, ln_out_b, ws.out_rows, C, ws.xn);
             check_launch("ln_out");
         }
         LinReq q = {&head, ws.xn, C, ws.logits, V, EPI_STORE};

@@ -49,7 +49,7 @@ struct LayerW {
 
 struct Workspace {
     int rows = 0, outs = 0, segs = 0;  // capacities
-    float *x = nullptr, *xmix = nullptr, *r = nullptr, *k = nullptr, *v = nullptr, *w = nullptr, *a = nullptr, *g = nullptr;
+    float *x = nullptr, *x2 = nullptr, *delta = nullptr, *xmix = nullptr, *r = nullptr, *k = nullptr, *v = nullptr, *w = nullptr, *a = nullptr, *g = nullptr;
     float *yg = nullptr, *xb = nullptr, *mid = nullptr, *h = nullptr, *vfirst = nullptr, *xn = nullptr, *logits = nullptr, *staging = nullptr;
     // tensor-core linear path: B operands, per-row scales, fixed-point sums, split-K partials (grown on demand)
     uint8_t* tc_b = nullptr;
@@ -58,6 +58,7 @@ struct Workspace {
     long long* tc_tsum = nullptr;
     size_t tc_rows = 0;
     void* tc_partials = nullptr;
+    int* tc_cnt = nullptr;
     size_t tc_partials_bytes = 0;
     float* samp_temp = nullptr;      // [outs, V] sampler work area
     uint32_t* samp_cnt = nullptr;    // [outs, V] penalty histogram

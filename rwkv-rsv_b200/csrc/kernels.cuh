@@ -100,6 +100,9 @@ __global__ void advance_cursor_kernel(int* pos) { *pos += 1; }
 // lerp.  Stands in for norm_lerp6(_batch), cmix_norm_lerp(_batch), rwkv_seq_shift(_batch) and
 // rwkv_copy_token(_batch) (src/backend_cuda.rs:2412-2549, 1505-1640, 4313-4406); math per
 // src/model.rs:402-411, 487-490: out_m = cur + mix_m * (prev - cur), state <- cur.
+// The residual add of the preceding linear layer is folded in: when `delta` is given the row's input is
+// x_in + delta (src/model.rs:484, 495) and that sum is written to x_out, a different buffer, because
+// row r also needs row r-1's sum while another CTA produces it.
 // `prev` is the LayerNorm of row r-1 when that row is the session's previous token (recomputed here
 // with the same code, hence the same bits) and the slot's shift state otherwise.  When a step holds
 // multi-row segments the new shift state goes to `staging` (one row per segment) and is committed by
@@ -107,22 +110,45 @@ __global__ void advance_cursor_kernel(int* pos) { *pos += 1; }
 struct MixPtrs {
     const float* m[6];
 };
+template <int NT>
+__device__ __forceinline__ void row_stats2(const float* __restrict__ x, const float* __restrict__ d, int C, float eps, float* red, float& mean,
+                                           float& inv_std) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < C; i += NT) s += d ? x[i] + d[i] : x[i];
+    mean = block_sum<NT / 32>(s, red) / (float)C;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < C; i += NT) {
+        const float t = (d ? x[i] + d[i] : x[i]) - mean;
+        q += t * t;
+    }
+    const float var = block_sum<NT / 32>(q, red) / (float)C + eps;
+    inv_std = 1.0f / sqrtf(var);
+}
 template <int NMIX>
-__global__ void __launch_bounds__(kRowThreads) ln_shift_kernel(const float* __restrict__ x, const float* __restrict__ lw,
-                                                               const float* __restrict__ lb, MixPtrs mix, const RowMeta* __restrict__ rows, int R,
-                                                               int C, float* __restrict__ shift_state, float* __restrict__ staging,
-                                                               float* __restrict__ out) {
+__global__ void __launch_bounds__(kRowThreads) ln_shift_kernel(const float* __restrict__ x_in, const float* __restrict__ delta, float* __restrict__ x_out,
+                                                               const float* __restrict__ lw, const float* __restrict__ lb, MixPtrs mix,
+                                                               const RowMeta* __restrict__ rows, int R, int C, float* __restrict__ shift_state,
+                                                               float* __restrict__ staging, float* __restrict__ out) {
     __shared__ float red[kRowThreads / 32];
     const int r = blockIdx.x;
     const RowMeta rm = rows[r];
-    const float* xr = x + (size_t)r * C;
+    const float* xr = x_in + (size_t)r * C;
+    const float* dr = delta ? delta + (size_t)r * C : nullptr;
     float mean, inv_std, pmean = 0.f, pinv = 0.f;
-    row_stats<kRowThreads>(xr, C, kLnEps, red, mean, inv_std);
-    if (rm.has_prev) row_stats<kRowThreads>(xr - C, C, kLnEps, red, pmean, pinv);
+    row_stats2<kRowThreads>(xr, dr, C, kLnEps, red, mean, inv_std);
+    if (rm.has_prev) row_stats2<kRowThreads>(xr - C, dr ? dr - C : nullptr, C, kLnEps, red, pmean, pinv);
     for (int i = threadIdx.x; i < C; i += kRowThreads) {
         const float wi = lw[i], bi = lb[i];
-        const float cur = (xr[i] - mean) * inv_std * wi + bi;
-        const float prev = rm.has_prev ? ((xr[i - C] - pmean) * pinv * wi + bi) : shift_state[(size_t)rm.slot * C + i];
+        const float xv = dr ? xr[i] + dr[i] : xr[i];
+        if (dr) x_out[(size_t)r * C + i] = xv;
+        const float cur = (xv - mean) * inv_std * wi + bi;
+        float prev;
+        if (rm.has_prev) {
+            const float xp = dr ? xr[i - C] + dr[i - C] : xr[i - C];
+            prev = (xp - pmean) * pinv * wi + bi;
+        } else {
+            prev = shift_state[(size_t)rm.slot * C + i];
+        }
 #pragma unroll
         for (int m = 0; m < NMIX; ++m) out[((size_t)m * R + r) * C + i] = cur + mix.m[m][i] * (prev - cur);
         if (rm.is_last) {
@@ -139,14 +165,18 @@ __global__ void commit_shift_kernel(const float* __restrict__ staging, const Seg
 }
 
 // Plain LayerNorm of selected rows (ln_out before the head; src/model.rs:507, rwkv_norm at
-// src/backend_cuda.rs:2555-2610).  out[o] = LN(x[out_rows[o]]).
-__global__ void __launch_bounds__(kRowThreads) ln_rows_kernel(const float* __restrict__ x, const float* __restrict__ lw, const float* __restrict__ lb,
-                                                              const int* __restrict__ out_rows, int C, float* __restrict__ out) {
+// src/backend_cuda.rs:2555-2610).  out[o] = LN(x[out_rows[o]] (+ delta[out_rows[o]])).
+__global__ void __launch_bounds__(kRowThreads) ln_rows_kernel(const float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ lw,
+                                                              const float* __restrict__ lb, const int* __restrict__ out_rows, int C,
+                                                              float* __restrict__ out) {
     __shared__ float red[kRowThreads / 32];
-    const float* xr = x + (size_t)out_rows[blockIdx.x] * C;
+    const size_t row = (size_t)out_rows[blockIdx.x];
+    const float* xr = x + row * C;
+    const float* dr = delta ? delta + row * C : nullptr;
     float mean, inv_std;
-    row_stats<kRowThreads>(xr, C, kLnEps, red, mean, inv_std);
-    for (int i = threadIdx.x; i < C; i += kRowThreads) out[(size_t)blockIdx.x * C + i] = (xr[i] - mean) * inv_std * lw[i] + lb[i];
+    row_stats2<kRowThreads>(xr, dr, C, kLnEps, red, mean, inv_std);
+    for (int i = threadIdx.x; i < C; i += kRowThreads)
+        out[(size_t)blockIdx.x * C + i] = ((dr ? xr[i] + dr[i] : xr[i]) - mean) * inv_std * lw[i] + lb[i];
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -364,72 +394,117 @@ __global__ void __launch_bounds__(kLinWarps * 32) linear_rows_kernel(const __gri
 //   k~ = k + k_a*(k*a - k) ; b = -kk^*a
 //   sa[i] = sum_j S[i][j] kk^[j] ; S[i][j] = S[i][j] w[j] + sa[i] b[j] + v[i] k~[j] ; y[i] = sum_j S[i][j] r[j]
 //   out = (GroupNorm(y; eps 64e-5) + (sum_j r[j] k~[j] r_k[j]) * v) * g
-// Thread i owns state row i in registers; the j-sums run sequentially in j like the CPU path.
+// Four threads share state row i (16 columns each, in registers); their partial sums are combined with shuffles.
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float head_sum(float v, float* red2) {  // 64 threads = 2 warps
-    v = warp_sum(v);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) red2[threadIdx.x >> 5] = v;
-    __syncthreads();
-    return red2[0] + red2[1];
-}
-__global__ void __launch_bounds__(kHeadSize) wkv7_kernel(const SegMeta* __restrict__ segs, const float* __restrict__ r, const float* __restrict__ k,
-                                                         const float* __restrict__ v, const float* __restrict__ w, const float* __restrict__ a,
-                                                         const float* __restrict__ g, const float* __restrict__ k_k, const float* __restrict__ k_a,
-                                                         const float* __restrict__ r_k, const float* __restrict__ lnx_w,
-                                                         const float* __restrict__ lnx_b, float* __restrict__ state, float* __restrict__ v_first_state,
-                                                         float* __restrict__ yg, int H, int C) {
+constexpr int kWkvThreads = 256;
+// One CTA per (head, segment); warp w owns state rows 8w .. 8w+7, four lanes per row.  Lane quad q of a row holds
+// columns 16 jj + 4 q + c (jj, c = 0..3), so one float4 instruction of a warp covers eight full 64-byte runs.
+// The per-token vectors over the column index (normalised kk, decay w, b = -kk a, k~, r) and the two scalars that
+// depend on the inputs only (|kk|^2 and the bonus dot product) are computed by every warp for itself with warp
+// shuffles; only the GroupNorm statistics of y cross warps (two block barriers per token).  All global loads of a
+// token are issued before the first use, so a CTA waits for memory once per token.
+// `vgate` (layers > 0): v <- v + vgate * (vfirst - v), the lerp of src/model.rs:424-430 (the gate itself,
+// sigmoid(v0 + (xv v1) v2), comes from the rank back-projection).
+__global__ void __launch_bounds__(kWkvThreads, 4) wkv7_kernel(const SegMeta* __restrict__ segs, const float* __restrict__ r, const float* __restrict__ k,
+                                                              const float* __restrict__ v, const float* __restrict__ vgate,
+                                                              const float* __restrict__ vfirst, const float* __restrict__ w, const float* __restrict__ a,
+                                                              const float* __restrict__ g, const float* __restrict__ k_k, const float* __restrict__ k_a,
+                                                              const float* __restrict__ r_k, const float* __restrict__ lnx_w, const float* __restrict__ lnx_b,
+                                                              float* __restrict__ state, float* __restrict__ v_first_state, float* __restrict__ yg, int H,
+                                                              int C) {
     constexpr int N = kHeadSize;
-    __shared__ float s_kk[N], s_w[N], s_b[N], s_kt[N], s_r[N];
-    __shared__ float red2[2];
-    const int h = blockIdx.x, tid = threadIdx.x;
+    __shared__ __align__(16) float s_vec[kWkvThreads / 32][5][N];  // per warp: kk, w, b, k~, r
+    __shared__ float red_a[kWkvThreads / 32], red_b[kWkvThreads / 32];
+    const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, i = tid >> 2, quad = tid & 3;
     const SegMeta sg = segs[blockIdx.y];
-    float* srow = state + (((size_t)sg.slot * H + h) * N + tid) * N;
-    float S[N];
+    float* srow = state + (((size_t)sg.slot * H + h) * N + i) * N + quad * 4;
+    float S[16];
 #pragma unroll
-    for (int j = 0; j < N; j += 4) {
-        const float4 t = *reinterpret_cast<const float4*>(srow + j);
-        S[j] = t.x;
-        S[j + 1] = t.y;
-        S[j + 2] = t.z;
-        S[j + 3] = t.w;
+    for (int jj = 0; jj < 4; ++jj) {
+        const float4 t = *reinterpret_cast<const float4*>(srow + 16 * jj);
+        S[4 * jj] = t.x;
+        S[4 * jj + 1] = t.y;
+        S[4 * jj + 2] = t.z;
+        S[4 * jj + 3] = t.w;
     }
-    const int ch = h * N + tid;
-    const float kk_c = k_k[ch], ka_c = k_a[ch], rk_c = r_k[ch], gw = lnx_w[ch], gb = lnx_b[ch];
+    const int hc = h * N;
+    const float kkc0 = k_k[hc + lane], kkc1 = k_k[hc + lane + 32], kac0 = k_a[hc + lane], kac1 = k_a[hc + lane + 32];
+    const float rkc0 = r_k[hc + lane], rkc1 = r_k[hc + lane + 32];
+    const float gw = lnx_w[hc + i], gb = lnx_b[hc + i];
+    float(*sv)[N] = s_vec[warp];
     for (int t = 0; t < sg.len; ++t) {
-        const size_t base = (size_t)(sg.start + t) * C + ch;
-        const float kj = k[base], aj = a[base], vj = v[base], rj = r[base];
-        const float kkj = kj * kk_c;
-        const float ss = head_sum(kkj * kkj, red2);
+        const size_t hb = (size_t)(sg.start + t) * C + hc;
+        const float k0 = k[hb + lane], k1 = k[hb + lane + 32], a0 = a[hb + lane], a1 = a[hb + lane + 32];
+        const float r0 = r[hb + lane], r1 = r[hb + lane + 32], w0 = w[hb + lane], w1 = w[hb + lane + 32];
+        float vj = v[hb + i];
+        const float gj = g[hb + i];
+        if (vgate) vj = vj + vgate[hb + i] * (vfirst[hb + i] - vj);
+        const float kk0 = k0 * kkc0, kk1 = k1 * kkc1;
+        const float ss = warp_sum(kk0 * kk0 + kk1 * kk1);
         const float inv = 1.0f / fmaxf(sqrtf(ss), kL2Eps);
-        const float kkh = kkj * inv;
-        const float kt = kj + ka_c * (kj * aj - kj);
-        __syncthreads();  // previous token's readers of s_* are done
-        s_kk[tid] = kkh;
-        s_w[tid] = w[base];
-        s_b[tid] = kkh * (-aj);
-        s_kt[tid] = kt;
-        s_r[tid] = rj;
-        __syncthreads();
+        const float kh0 = kk0 * inv, kh1 = kk1 * inv;
+        const float kt0 = k0 + kac0 * (k0 * a0 - k0), kt1 = k1 + kac1 * (k1 * a1 - k1);
+        const float srk = warp_sum(r0 * kt0 * rkc0 + r1 * kt1 * rkc1);
+        __syncwarp();  // the previous token's readers are done with sv
+        sv[0][lane] = kh0;
+        sv[0][lane + 32] = kh1;
+        sv[1][lane] = w0;
+        sv[1][lane + 32] = w1;
+        sv[2][lane] = kh0 * (-a0);
+        sv[2][lane + 32] = kh1 * (-a1);
+        sv[3][lane] = kt0;
+        sv[3][lane + 32] = kt1;
+        sv[4][lane] = r0;
+        sv[4][lane + 32] = r1;
+        __syncwarp();
         float sa = 0.f;
 #pragma unroll
-        for (int j = 0; j < N; ++j) sa = fmaf(S[j], s_kk[j], sa);
+        for (int jj = 0; jj < 4; ++jj) {
+            const float4 kk4 = *reinterpret_cast<const float4*>(&sv[0][16 * jj + 4 * quad]);
+            sa = fmaf(S[4 * jj], kk4.x, sa);
+            sa = fmaf(S[4 * jj + 1], kk4.y, sa);
+            sa = fmaf(S[4 * jj + 2], kk4.z, sa);
+            sa = fmaf(S[4 * jj + 3], kk4.w, sa);
+        }
+        sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+        sa += __shfl_xor_sync(0xffffffffu, sa, 2);
         float y = 0.f;
 #pragma unroll
-        for (int j = 0; j < N; ++j) {
-            S[j] = fmaf(S[j], s_w[j], fmaf(sa, s_b[j], vj * s_kt[j]));
-            y = fmaf(S[j], s_r[j], y);
+        for (int jj = 0; jj < 4; ++jj) {
+            const int c0 = 16 * jj + 4 * quad;
+            const float4 w4 = *reinterpret_cast<const float4*>(&sv[1][c0]);
+            const float4 b4 = *reinterpret_cast<const float4*>(&sv[2][c0]);
+            const float4 t4 = *reinterpret_cast<const float4*>(&sv[3][c0]);
+            const float4 r4 = *reinterpret_cast<const float4*>(&sv[4][c0]);
+            S[4 * jj] = fmaf(S[4 * jj], w4.x, fmaf(sa, b4.x, vj * t4.x));
+            S[4 * jj + 1] = fmaf(S[4 * jj + 1], w4.y, fmaf(sa, b4.y, vj * t4.y));
+            S[4 * jj + 2] = fmaf(S[4 * jj + 2], w4.z, fmaf(sa, b4.z, vj * t4.z));
+            S[4 * jj + 3] = fmaf(S[4 * jj + 3], w4.w, fmaf(sa, b4.w, vj * t4.w));
+            y = fmaf(S[4 * jj], r4.x, y);
+            y = fmaf(S[4 * jj + 1], r4.y, y);
+            y = fmaf(S[4 * jj + 2], r4.z, y);
+            y = fmaf(S[4 * jj + 3], r4.w, y);
         }
-        const float mean = head_sum(y, red2) / (float)N;
+        y += __shfl_xor_sync(0xffffffffu, y, 1);
+        y += __shfl_xor_sync(0xffffffffu, y, 2);
+        // GroupNorm over the head's 64 outputs (two-pass, like the CPU path)
+        const float ys = warp_sum(quad == 0 ? y : 0.f);
+        if (lane == 0) red_a[warp] = ys;
+        __syncthreads();
+        const float mean = (((red_a[0] + red_a[1]) + (red_a[2] + red_a[3])) + ((red_a[4] + red_a[5]) + (red_a[6] + red_a[7]))) / (float)N;
         const float d = y - mean;
-        const float var = head_sum(d * d, red2) / (float)N + kGnEps;
+        const float qs = warp_sum(quad == 0 ? d * d : 0.f);
+        if (lane == 0) red_b[warp] = qs;
+        __syncthreads();
+        const float var = (((red_b[0] + red_b[1]) + (red_b[2] + red_b[3])) + ((red_b[4] + red_b[5]) + (red_b[6] + red_b[7]))) / (float)N + kGnEps;
         const float inv_std = 1.0f / sqrtf(var);
-        const float srk = head_sum(rj * kt * rk_c, red2);
-        yg[base] = (d * inv_std * gw + gb + srk * vj) * g[base];
-        if (v_first_state && t == sg.len - 1) v_first_state[(size_t)sg.slot * C + ch] = vj;
+        if (quad == 0) {
+            yg[hb + i] = (d * inv_std * gw + gb + srk * vj) * gj;
+            if (v_first_state && t == sg.len - 1) v_first_state[(size_t)sg.slot * C + hc + i] = vj;
+        }
     }
 #pragma unroll
-    for (int j = 0; j < N; j += 4) *reinterpret_cast<float4*>(srow + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+    for (int jj = 0; jj < 4; ++jj) *reinterpret_cast<float4*>(srow + 16 * jj) = make_float4(S[4 * jj], S[4 * jj + 1], S[4 * jj + 2], S[4 * jj + 3]);
 }
 
 // ------------------------------------------------------------------------------------------------

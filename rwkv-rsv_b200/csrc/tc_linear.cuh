@@ -18,11 +18,14 @@
 // Work decomposition.  A unit is one (128-row M tile, N tile, 128-byte K block) = 16 KB of weights.  Units are
 // ordered problem -> M tile -> N tile -> K block and cut into equal contiguous ranges, one per CTA (persistent,
 // one CTA per SM), so every SM streams the same number of bytes whatever the matrix shape.  Each maximal run of
-// units inside one tile accumulates in TMEM and is written as an int32/fp32 partial [slot][n][m]; a second small
-// kernel adds a tile's partials in slot order, applies scale/zero and the fused epilogue.
+// units inside one tile accumulates in TMEM.  A run that covers its tile's whole K range is scaled and stored by the
+// fused epilogue directly.  A tile that a CTA boundary cuts is written as int32/fp32 partials [slot][n][m]; every
+// epilogue warp owns a fixed (lane quarter, column chunk class) sub-block of a tile, counts its arrival on that
+// sub-block with one atomic, and the warp that arrives last adds the sub-block's partials in slot order (exact for
+// int32, fixed order for fp32) and runs the epilogue - no second kernel and no barrier inside the CTA.
 //
-// Roles per CTA (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2-9 = epilogue
-// (two warps per TMEM lane quarter, alternating 16-column chunks).
+// Roles per CTA (576 threads): warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2-17 = epilogue
+// (four warps per TMEM lane quarter, interleaved 16-column chunks).
 // Every wait on an mbarrier is bounded; on expiry the kernel raises bit 1 of the status word and drains.
 #pragma once
 #include <cuda.h>
@@ -31,7 +34,8 @@
 
 namespace rsv {
 
-constexpr int kTcThreads = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
+constexpr int kTcEpiWarps = 16;
+constexpr int kTcThreads = 64 + 32 * kTcEpiWarps;  // warp 0 TMA, warp 1 MMA, then the epilogue warps
 constexpr int kTcTileM = 128;
 constexpr int kTcKBlockBytes = 128;
 constexpr int kTcMaxProblems = 8;
@@ -63,6 +67,7 @@ struct alignas(64) TcLaunch {
     TcProb p[kTcMaxProblems];
     int nprob, total_units, nt, is_i8, pmax, nstages, grid, nsplit;
     void* partials;  // [cut tile][pmax][nt][128] int32 or fp32
+    int* tile_cnt;   // [cut tile][epilogue warp] arrival counters, zero between launches
     int* status;
     int split_unit[kTcMaxSplit];  // first unit of every tile that is cut by a CTA boundary
 };
@@ -273,7 +278,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
+            mbar_init(&acc_empty[b], kTcEpiWarps);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -340,8 +345,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
             if (ok && prev_tile >= 0) tc_commit(&acc_full[run & 1]);
         }
     } else {
-        // ---------------- epilogue: TMEM -> partial buffer ----------------
+        // ---------------- epilogue: TMEM -> outputs, or -> partial buffer for tiles cut by a CTA boundary ----------------
         const int q = warp & 3;  // TMEM lane quarter this warp may read
+        const int ew = warp - 2, cidx = ew >> 2;  // which of the warps of this lane quarter
+        constexpr int kChunkStep = 16 * (kTcEpiWarps / 4);
         uint32_t run = 0;
         int u = u_begin;
         while (u < u_end) {
@@ -356,60 +363,93 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
             tc_fence_after();
             const int ncols = min(NT, P.ncols - un.nt * NT);
             const int row = q * 32 + lane;
-            const int chalf = (warp - 2) >> 2;  // which of the two warps of this lane quarter
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (run & 1) * NT;
             const bool whole = (u == tile_first) && (run_end == tile_first + P.kblocks);
-            if (whole) {
-                // the run holds the complete K sum: scale and store the outputs directly
-                const int m = un.mt * kTcTileM + row;
-                const bool mok = m < P.M;
-                float ws = 0.f, wz = 0.f, bias = 0.f;
-                if (mok) {
-                    if (I8) {
-                        ws = P.wscale[m];
-                        wz = P.wzero[m];
+            const int m = un.mt * kTcTileM + row;
+            const bool mok = m < P.M;
+            // 16 accumulator columns of output row m, complete in K -> scale, epilogue, store
+            auto finish_chunk = [&](int c0, const uint32_t(&v)[16], float ws, float wz, float bias) {
+                long long Q[4];
+                float fs[8];
+                if (I8) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        long long t = (int)v[4 * i];
+                        t = t * 128 + (int)v[4 * i + 1];
+                        t = t * 128 + (int)v[4 * i + 2];
+                        Q[i] = t * 128 + (int)v[4 * i + 3];
                     }
-                    if (P.bias) bias = P.bias[m];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) fs[i] = __uint_as_float(v[2 * i]) + __uint_as_float(v[2 * i + 1]);
                 }
-                for (int c0 = chalf * 16; c0 < ncols; c0 += 32) {
+                tc_finish16<I8>(P, un.nt * NT + c0, m, ws, wz, bias, Q, fs);
+            };
+            float ws = 0.f, wz = 0.f, bias = 0.f;
+            if (mok) {
+                if (I8) {
+                    ws = P.wscale[m];
+                    wz = P.wzero[m];
+                }
+                if (P.bias) bias = P.bias[m];
+            }
+            if (whole) {
+                for (int c0 = cidx * 16; c0 < ncols; c0 += kChunkStep) {
                     uint32_t v[16];
                     tmem_ld16(taddr + c0, v);
-                    if (mok) {
-                        long long Q[4];
-                        float fs[8];
-                        if (I8) {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                long long t = (int)v[4 * i];
-                                t = t * 128 + (int)v[4 * i + 1];
-                                t = t * 128 + (int)v[4 * i + 2];
-                                Q[i] = t * 128 + (int)v[4 * i + 3];
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) fs[i] = __uint_as_float(v[2 * i]) + __uint_as_float(v[2 * i + 1]);
-                        }
-                        tc_finish16<I8>(P, un.nt * NT + c0, m, ws, wz, bias, Q, fs);
-                    }
+                    if (mok) finish_chunk(c0, v, ws, wz, bias);
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[run & 1]);
             } else {
                 int lo = 0, hi = L.nsplit - 1;  // ordinal of this tile among the cut tiles (sorted by first unit)
                 while (lo < hi) {
                     const int mid = (lo + hi) >> 1;
                     if (L.split_unit[mid] < tile_first) lo = mid + 1; else hi = mid;
                 }
-                uint32_t* dst = reinterpret_cast<uint32_t*>(L.partials) + ((size_t)lo * L.pmax + slot) * ((size_t)NT * kTcTileM);
-                for (int c0 = chalf * 16; c0 < ncols; c0 += 32) {
+                const size_t slot_stride = (size_t)NT * kTcTileM;
+                uint32_t* tile_base = reinterpret_cast<uint32_t*>(L.partials) + (size_t)lo * L.pmax * slot_stride;
+                uint32_t* dst = tile_base + (size_t)slot * slot_stride;
+                for (int c0 = cidx * 16; c0 < ncols; c0 += kChunkStep) {
                     uint32_t v[16];
                     tmem_ld16(taddr + c0, v);
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         if (c0 + j < ncols) dst[(size_t)(c0 + j) * kTcTileM + row] = v[j];
                 }
+                tc_fence_before();
+                __threadfence();  // this lane's partials are visible device-wide before the arrival is counted
+                __syncwarp();
+                int old = 0;
+                if (lane == 0) {
+                    mbar_arrive(&acc_empty[run & 1]);  // the accumulator may be reused while the tile is finished
+                    old = atomicAdd(&L.tile_cnt[lo * kTcEpiWarps + ew], 1);
+                }
+                old = __shfl_sync(0xffffffffu, old, 0);
+                const int nslots = tc_cta_of_unit(tile_first + P.kblocks - 1, U, G) - tc_cta_of_unit(tile_first, U, G) + 1;
+                if (old == nslots - 1) {
+                    // last arrival on this sub-block: every slot is complete
+                    if (lane == 0) L.tile_cnt[lo * kTcEpiWarps + ew] = 0;  // ready for the next launch
+                    __threadfence();
+                    for (int c0 = cidx * 16; c0 < ncols; c0 += kChunkStep) {
+                        uint32_t v[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0u;
+                        for (int sl = 0; sl < nslots; ++sl) {
+                            const uint32_t* src = tile_base + (size_t)sl * slot_stride + (size_t)c0 * kTcTileM + row;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                if (c0 + j < ncols) {
+                                    const uint32_t t = __ldcg(src + (size_t)j * kTcTileM);
+                                    v[j] = I8 ? (uint32_t)((int)v[j] + (int)t) : __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(t));
+                                }
+                            }
+                        }
+                        if (mok) finish_chunk(c0, v, ws, wz, bias);
+                    }
+                }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[run & 1]);
             ++run;
             u = run_end;
         }
@@ -431,16 +471,26 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
 //   fp16 path : hi = fp16(x/e), lo = fp16(x/e - hi) -> B[2r, k], B[2r+1, k]; xscale[r] = e
 // ------------------------------------------------------------------------------------------------
 constexpr int kPrepThreads = 256;
-template <int D>
-__global__ void __launch_bounds__(kPrepThreads) tc_prepare_i8_kernel(const float* __restrict__ x, int ldx, int K, int Kpad, int8_t* __restrict__ B,
-                                                                     float* __restrict__ xscale, long long* __restrict__ tsum) {
-    __shared__ float redf[kPrepThreads / 32];
-    __shared__ long long redl[kPrepThreads / 32];
-    constexpr int P = 7 * D - 1;
-    const int r = blockIdx.x;
-    const float* xr = x + (size_t)r * ldx;
-    float amax = 0.f;
-    for (int k = threadIdx.x; k < K; k += kPrepThreads) amax = fmaxf(amax, fabsf(xr[k]));
+struct TcPrepRegion {
+    const float* x;
+    void* B;
+    float* xscale;
+    long long* tsum;
+    int ldx, K, Kpad, pad;
+};
+struct TcPrepLaunch {
+    TcPrepRegion r[kTcMaxProblems];
+};
+// smallest ex with 2^ex >= amax (0 for an all-zero or non-finite row; non-finite input is clamped by the callers)
+__device__ __forceinline__ int tc_scale_exp(float amax) {
+    int ex = 0;
+    if (amax > 0.f && amax < 3.0e38f) {
+        (void)frexpf(amax, &ex);                // amax = f * 2^ex, f in [0.5, 1)
+        if (amax == ldexpf(0.5f, ex)) ex -= 1;   // exactly a power of two
+    }
+    return max(-100, min(100, ex));
+}
+__device__ __forceinline__ float tc_block_max(float amax, float* redf) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if ((threadIdx.x & 31) == 0) redf[threadIdx.x >> 5] = amax;
@@ -448,13 +498,21 @@ __global__ void __launch_bounds__(kPrepThreads) tc_prepare_i8_kernel(const float
     amax = redf[0];
 #pragma unroll
     for (int i = 1; i < kPrepThreads / 32; ++i) amax = fmaxf(amax, redf[i]);
-    // e = smallest power of two >= amax (1 for an all-zero row; non-finite input is clamped below)
-    int ex = 0;
-    if (amax > 0.f && amax < 3.0e38f) {
-        (void)frexpf(amax, &ex);                    // amax = f * 2^ex, f in [0.5, 1)
-        if (amax == ldexpf(0.5f, ex)) ex -= 1;       // exactly a power of two
-    }
-    ex = max(-100, min(100, ex));
+    return amax;
+}
+// grid (rows, regions): every activation operand of a launch group is prepared by one kernel
+template <int D>
+__global__ void __launch_bounds__(kPrepThreads) tc_prepare_i8_kernel(const __grid_constant__ TcPrepLaunch L) {
+    __shared__ float redf[kPrepThreads / 32];
+    __shared__ long long redl[kPrepThreads / 32];
+    constexpr int P = 7 * D - 1;
+    const TcPrepRegion& G = L.r[blockIdx.y];
+    const int r = blockIdx.x, K = G.K, Kpad = G.Kpad;
+    const float* xr = G.x + (size_t)r * G.ldx;
+    int8_t* B = reinterpret_cast<int8_t*>(G.B);
+    float amax = 0.f;
+    for (int k = threadIdx.x; k < K; k += kPrepThreads) amax = fmaxf(amax, fabsf(xr[k]));
+    const int ex = tc_scale_exp(tc_block_max(amax, redf));
     const float inv = ldexpf(1.0f, P - ex);  // 2^P / e, exact
     long long ts = 0;
     for (int k = threadIdx.x; k < K; k += kPrepThreads) {
@@ -484,30 +542,19 @@ __global__ void __launch_bounds__(kPrepThreads) tc_prepare_i8_kernel(const float
     if (threadIdx.x == 0) {
         long long t = 0;
         for (int i = 0; i < kPrepThreads / 32; ++i) t += redl[i];
-        tsum[r] = t;
-        xscale[r] = ldexpf(1.0f, ex - P);
+        G.tsum[r] = t;
+        G.xscale[r] = ldexpf(1.0f, ex - P);
     }
 }
-__global__ void __launch_bounds__(kPrepThreads) tc_prepare_f16_kernel(const float* __restrict__ x, int ldx, int K, int Kpad, __half* __restrict__ B,
-                                                                      float* __restrict__ xscale) {
+__global__ void __launch_bounds__(kPrepThreads) tc_prepare_f16_kernel(const __grid_constant__ TcPrepLaunch L) {
     __shared__ float redf[kPrepThreads / 32];
-    const int r = blockIdx.x;
-    const float* xr = x + (size_t)r * ldx;
+    const TcPrepRegion& G = L.r[blockIdx.y];
+    const int r = blockIdx.x, K = G.K, Kpad = G.Kpad;
+    const float* xr = G.x + (size_t)r * G.ldx;
+    __half* B = reinterpret_cast<__half*>(G.B);
     float amax = 0.f;
     for (int k = threadIdx.x; k < K; k += kPrepThreads) amax = fmaxf(amax, fabsf(xr[k]));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if ((threadIdx.x & 31) == 0) redf[threadIdx.x >> 5] = amax;
-    __syncthreads();
-    amax = redf[0];
-#pragma unroll
-    for (int i = 1; i < kPrepThreads / 32; ++i) amax = fmaxf(amax, redf[i]);
-    int ex = 0;
-    if (amax > 0.f && amax < 3.0e38f) {
-        (void)frexpf(amax, &ex);
-        if (amax == ldexpf(0.5f, ex)) ex -= 1;
-    }
-    ex = max(-100, min(100, ex));
+    const int ex = tc_scale_exp(tc_block_max(amax, redf));
     const float inv = ldexpf(1.0f, -ex);
     for (int k = threadIdx.x; k < K; k += kPrepThreads) {
         float v = xr[k] * inv;
@@ -522,63 +569,7 @@ __global__ void __launch_bounds__(kPrepThreads) tc_prepare_f16_kernel(const floa
         B[((size_t)r * 2) * Kpad + k] = __float2half_rn(0.f);
         B[((size_t)r * 2 + 1) * Kpad + k] = __float2half_rn(0.f);
     }
-    if (threadIdx.x == 0) xscale[r] = ldexpf(1.0f, ex);
-}
-
-// ------------------------------------------------------------------------------------------------
-// Finalize the tiles that a CTA boundary cut: add the tile's partials in slot order (exact for int32, fixed
-// order for fp32), then scale and store like the in-kernel epilogue.  One CTA per cut tile.
-// ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) tc_finalize_kernel(const __grid_constant__ TcLaunch L) {
-    const int tile_first = L.split_unit[blockIdx.x];
-    const TcUnit un = tc_decode(L, tile_first);
-    const TcProb& P = L.p[un.p];
-    const int U = L.total_units, G = L.grid, NT = L.nt;
-    const int c_lo = tc_cta_of_unit(tile_first, U, G), c_hi = tc_cta_of_unit(tile_first + P.kblocks - 1, U, G);
-    const int nslots = c_hi - c_lo + 1;
-    const size_t slot_stride = (size_t)NT * kTcTileM;
-    const size_t base = (size_t)blockIdx.x * L.pmax * slot_stride;
-    const int ncols = min(NT, P.ncols - un.nt * NT);
-    const int ngroups = (ncols + 15) / 16;  // groups of 16 columns
-    for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < ngroups * kTcTileM; idx += gridDim.y * blockDim.x) {
-        const int grp = idx >> 7, ml = idx & 127;
-        const int m = un.mt * kTcTileM + ml;
-        if (m >= P.M) continue;
-        const size_t off = base + (size_t)(grp * 16) * kTcTileM + ml;
-        float bias = P.bias ? P.bias[m] : 0.f;
-        long long Q[4] = {0, 0, 0, 0};
-        float fs[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if (L.is_i8) {
-            int I[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) I[j] = 0;
-            for (int sl = 0; sl < nslots; ++sl) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (grp * 16 + j < ncols) I[j] += reinterpret_cast<const int*>(L.partials)[off + (size_t)sl * slot_stride + (size_t)j * kTcTileM];
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                long long t = I[4 * i];
-                t = t * 128 + I[4 * i + 1];
-                t = t * 128 + I[4 * i + 2];
-                Q[i] = t * 128 + I[4 * i + 3];
-            }
-            tc_finish16<true>(P, un.nt * NT + grp * 16, m, P.wscale[m], P.wzero[m], bias, Q, fs);
-        } else {
-            float f[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) f[j] = 0.f;
-            for (int sl = 0; sl < nslots; ++sl) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (grp * 16 + j < ncols) f[j] += reinterpret_cast<const float*>(L.partials)[off + (size_t)sl * slot_stride + (size_t)j * kTcTileM];
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) fs[i] = f[2 * i] + f[2 * i + 1];
-            tc_finish16<false>(P, un.nt * NT + grp * 16, m, 0.f, 0.f, bias, Q, fs);
-        }
-    }
+    if (threadIdx.x == 0) G.xscale[r] = ldexpf(1.0f, ex);
 }
 
 }  // namespace rsv
