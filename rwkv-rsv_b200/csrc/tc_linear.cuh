@@ -410,13 +410,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
                 }
                 const size_t slot_stride = (size_t)NT * kTcTileM;
                 uint32_t* tile_base = reinterpret_cast<uint32_t*>(L.partials) + (size_t)lo * L.pmax * slot_stride;
-                uint32_t* dst = tile_base + (size_t)slot * slot_stride;
+                // partial layout of a slot: uint4 index (chunk * 4 + j4) * 128 + row holds columns 16 chunk + 4 j4 .. + 3 of that row
+                uint4* dst = reinterpret_cast<uint4*>(tile_base + (size_t)slot * slot_stride);
                 for (int c0 = cidx * 16; c0 < ncols; c0 += kChunkStep) {
                     uint32_t v[16];
                     tmem_ld16(taddr + c0, v);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (c0 + j < ncols) dst[(size_t)(c0 + j) * kTcTileM + row] = v[j];
+                    for (int j4 = 0; j4 < 4; ++j4) dst[(size_t)((c0 >> 4) * 4 + j4) * kTcTileM + row] = make_uint4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
                 }
                 tc_fence_before();
                 __threadfence();  // this lane's partials are visible device-wide before the arrival is counted
@@ -432,19 +432,30 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
                     // last arrival on this sub-block: every slot is complete
                     if (lane == 0) L.tile_cnt[lo * kTcEpiWarps + ew] = 0;  // ready for the next launch
                     __threadfence();
+                    auto accumulate = [&](uint32_t(&v)[16], const uint4(&t)[4]) {
+#pragma unroll
+                        for (int j4 = 0; j4 < 4; ++j4) {
+                            const uint32_t e[4] = {t[j4].x, t[j4].y, t[j4].z, t[j4].w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                v[4 * j4 + i] = I8 ? (uint32_t)((int)v[4 * j4 + i] + (int)e[i]) : __float_as_uint(__uint_as_float(v[4 * j4 + i]) + __uint_as_float(e[i]));
+                        }
+                    };
                     for (int c0 = cidx * 16; c0 < ncols; c0 += kChunkStep) {
                         uint32_t v[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = 0u;
-                        for (int sl = 0; sl < nslots; ++sl) {
-                            const uint32_t* src = tile_base + (size_t)sl * slot_stride + (size_t)c0 * kTcTileM + row;
+                        const uint4* src = reinterpret_cast<const uint4*>(tile_base) + (size_t)((c0 >> 4) * 4) * kTcTileM + row;
+                        for (int sl = 0; sl < nslots; sl += 2) {  // two slots' loads in flight; added in slot order
+                            const bool two = sl + 1 < nslots;
+                            uint4 ta[4], tb[4];
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                if (c0 + j < ncols) {
-                                    const uint32_t t = __ldcg(src + (size_t)j * kTcTileM);
-                                    v[j] = I8 ? (uint32_t)((int)v[j] + (int)t) : __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(t));
-                                }
-                            }
+                            for (int j4 = 0; j4 < 4; ++j4) ta[j4] = __ldcg(src + (size_t)sl * (slot_stride / 4) + (size_t)j4 * kTcTileM);
+#pragma unroll
+                            for (int j4 = 0; j4 < 4; ++j4)
+                                tb[j4] = two ? __ldcg(src + (size_t)(sl + 1) * (slot_stride / 4) + (size_t)j4 * kTcTileM) : make_uint4(0u, 0u, 0u, 0u);
+                            accumulate(v, ta);
+                            if (two) accumulate(v, tb);
                         }
                         if (mok) finish_chunk(c0, v, ws, wz, bias);
                     }
