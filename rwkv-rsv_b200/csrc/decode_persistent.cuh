@@ -17,13 +17,15 @@
 // Work split: every GEMV phase is cut into units (128-row tile x 128-byte K block); CTA c owns the contiguous
 // unit range [c*U/G, (c+1)*U/G), so each SM streams the same number of weight bytes.  The unit lists of the six
 // phase shapes are tabulated in shared memory once per launch.  A run (the units of one tile inside one CTA)
-// leaves an exact int32 (or fp32) partial [16 columns][128 rows] plus its own fixed-point scale; consumers add a
-// tile's partials in slot order.  Integer partials make the split exact, and every floating-point sum has a
-// fixed order: results are deterministic and independent of timing.
-// Phases per layer (grid barrier after each; b = finish the residual stream on disjoint slices, then share it):
-//   1  LN1 + token shift -> r,k,v (int8) and the four rank projections (fp16)
+// leaves an exact int32 (or fp32) partial [16 columns][128 rows] plus its own fixed-point scale.  Every worker
+// warp owns a fixed (32-row, 8-column) sub-block of a tile and counts its arrival on it with one atomic; the warp
+// that arrives last adds the sub-block's partials in slot order, applies the phase's epilogue and stores plain
+// fp32 outputs, so consumers never see partial sums.  Integer partials make the split exact, and every
+// floating-point sum has a fixed order: results are deterministic and independent of timing.
+// Phases per layer (one grid barrier after each):
+//   1  LN1 + token shift -> r,k,v (int8) and the four rank projections (fp16; tanh / sigmoid applied)
 //   2  per (session, head): rank back-projections, decay/a/v/g, WKV-7 state update in place, GroupNorm, gate
-//   3  att.output           3b  x += ...        4  LN2 + shift -> ffn.key        5  relu^2 -> ffn.value   5b  x += ...
+//   3  att.output, x += ...        4  LN2 + shift -> relu(ffn.key)^2        5  ffn.value, x += ...
 // then ln_out + head (fp16) -> logits, arg-max across CTAs, next token.
 // All spin-waits are bounded; on expiry bit 2 of the status word is set and every role drains and exits.
 #pragma once
@@ -43,6 +45,7 @@ constexpr int kDpP = 7 * kDpDigits - 1;
 constexpr uint32_t kDpBarSpin = 1u << 22;
 constexpr int kDpMaxRuns = 8;    // runs (tiles touched) per CTA and phase
 constexpr int kDpMaxShares = 4;  // problems touched per CTA and phase
+constexpr int kDpMaxSlice = 64;  // channels of the residual stream per CTA (ceil(C / grid))
 
 struct DpMat {
     int map, M, mtiles, kblocks, is_i8, K;
@@ -64,7 +67,8 @@ struct DpRunMeta {
 };
 struct DpRegion {
     uint32_t* data;   // [tile][pmax][16][128]
-    DpRunMeta* meta;  // [tile][pmax]
+    DpRunMeta* meta;  // [tile][pmax][worker warp]: every warp leaves its own copy, ordered with its own arrival
+    int* cnt;         // [tile][worker warp] arrivals on a sub-block; zero between phases
     int pmax;
     int pad;
 };
@@ -81,6 +85,9 @@ struct DpParams {
     int nb;
     int slot[kDpMaxNB];
     float *x, *yg, *vfirst;  // [4][C]
+    float* rkv;              // [4][3][C] r, k, v of the current layer
+    float* mid;              // [4][wm+am+vm+gm] rank-space vectors (tanh / sigmoid applied)
+    float* hbuf;             // [4][F] relu(ffn.key)^2
     float* state_vfirst;     // [cap][C]
     DpRegion reg[5];
     uint32_t* tokens;          // [4] current input token of every session (read at start, written after arg-max)
@@ -108,7 +115,7 @@ struct DpUnit {
 struct DpRun {
     uint16_t tile;  // tile index inside the region
     uint16_t u0;    // first unit (index into the variant's unit list)
-    uint8_t nu, slot, prob, pad;
+    uint8_t nu, slot, prob, ns;  // ns: number of CTAs (partial slots) that share the tile
 };
 struct DpShare {  // the K blocks of one problem this CTA feeds: operand tiles base .. base+ntile-1
     uint8_t prob, ntile, kb0, base;
@@ -126,6 +133,10 @@ __device__ __forceinline__ long long dp_now() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
+#define DP_STAMP_ALL(k)                                                                                         \
+    do {                                                                                                        \
+        if (P.dbg && wtid == 0 && t == 1 && l == 1 && v == DV_P3) P.dbg[64 + cta * 8 + (k)] = dp_now();         \
+    } while (0)
 #define DP_STAMP(id)                                                                  \
     do {                                                                              \
         if (P.dbg && cta == 0 && wtid == 0 && t == 1 && l == 1) P.dbg[id] = dp_now(); \
@@ -142,6 +153,15 @@ __device__ __forceinline__ int dp_ceil_log2(float a) {
     return ((bits >> 23) & 0xFF) - 127 + ((bits & 0x7FFFFF) ? 1 : 0);
 }
 
+// The CTAs of the grid share the work of pulling a small array into L2 ahead of its use (one 128-byte line per request).
+__device__ __forceinline__ void dp_prefetch_l2(const void* base, size_t bytes, int cta, int G, int tid, int nthreads) {
+    if (!base) return;
+    const size_t lines = (bytes + 127) / 128;
+    for (size_t i = (size_t)cta + (size_t)G * tid; i < lines; i += (size_t)G * nthreads)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(base) + i * 128));
+}
+__device__ __forceinline__ void dp_prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
+
 __device__ __forceinline__ void dp_worker_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kDpWorkers) : "memory"); }
 
 // Sum over the 256 worker threads; every worker gets the result.  `red` holds 8 floats.
@@ -157,7 +177,7 @@ __device__ __forceinline__ float dp_worker_sum(float v, float* red, int wtid) {
 __device__ __forceinline__ bool dp_grid_barrier(unsigned* bar, unsigned& target, int G, volatile int* abort_flag, int wtid) {
     dp_worker_sync();
     if (wtid == 0) {
-        __threadfence();
+        fence_acq_rel_gpu();
         atomicAdd(bar, 1u);
         const unsigned want = target + (unsigned)G;
         bool ok = false;
@@ -171,7 +191,6 @@ __device__ __forceinline__ bool dp_grid_barrier(unsigned* bar, unsigned& target,
             if ((i & 255u) == 255u && *abort_flag) break;
         }
         if (!ok) *abort_flag = 1;
-        __threadfence();
     }
     target += (unsigned)G;
     dp_worker_sync();
@@ -186,35 +205,124 @@ struct DpStats {
     float mean, inv;
 };
 
-// Value of output m (problem `pi` of variant V, matrix `mat`) for session b: the tile's partials added in slot order.
-// The loads of a slot are independent of one another and the slot loop is unrolled, so many requests are in flight.
-__device__ __noinline__ float dp_finalize(const DpRegion& R, const DpVar& V, int pi, const DpMat& mat, int m, int b) {
-    const int mt = m >> 7, ml = m & 127;
-    const int tile_first = V.p_unit0[pi] + mt * V.p_kblocks[pi];
-    const int ns = dp_cta_of(tile_first + V.p_kblocks[pi] - 1, V.U, V.ge) - dp_cta_of(tile_first, V.U, V.ge) + 1;
-    const size_t t = (size_t)(V.p_tile0[pi] + mt) * R.pmax;
-    double acc = 0.0;
-    if (V.p_i8[pi]) {
-        const double ws = mat.wscale[m], wz = mat.wzero[m];
-        const uint32_t* d0 = R.data + t * (size_t)(kDpN * 128) + (size_t)(b * kDpDigits) * 128 + ml;
-#pragma unroll 4
-        for (int s = 0; s < ns; ++s) {
-            const uint32_t* d = d0 + (size_t)s * (kDpN * 128);
-            const int i0 = (int)d[0], i1 = (int)d[128], i2 = (int)d[256], i3 = (int)d[384];
-            const float xs = R.meta[t + s].xscale[b];
-            const long long ts = R.meta[t + s].tsum[b];
-            const long long Q = (((long long)i0 * 128 + i1) * 128 + i2) * 128 + i3;
-            acc += (double)xs * (ws * (double)Q + wz * (double)ts);
+// Epilogue of one finished output (row m of problem `pi`, session b) of phase variant v.
+__device__ __forceinline__ void dp_store_output(const DpParams& P, int v, int mat_id, int m, int b, float val) {
+    switch (v) {
+        case DV_P1A:
+        case DV_P1B: {
+            const int nmid = P.wm + P.am + P.vm + P.gm;
+            if (mat_id <= DM_WV) {
+                P.rkv[((size_t)b * 3 + mat_id) * P.C + m] = val;
+            } else if (mat_id == DM_W1) {
+                P.mid[(size_t)b * nmid + m] = tanhf(val);
+            } else if (mat_id == DM_A1) {
+                P.mid[(size_t)b * nmid + P.wm + m] = val;
+            } else if (mat_id == DM_V1) {
+                P.mid[(size_t)b * nmid + P.wm + P.am + m] = val;
+            } else {
+                P.mid[(size_t)b * nmid + P.wm + P.am + P.vm + m] = 1.0f / (1.0f + expf(-val));
+            }
+            break;
         }
-    } else {
-        const uint32_t* d0 = R.data + t * (size_t)(kDpN * 128) + (size_t)(b * 2) * 128 + ml;
-#pragma unroll 4
-        for (int s = 0; s < ns; ++s) {
-            const uint32_t* d = d0 + (size_t)s * (kDpN * 128);
-            acc += (double)R.meta[t + s].xscale[b] * (double)(__uint_as_float(d[0]) + __uint_as_float(d[128]));
+        case DV_P4: {
+            const float a = fmaxf(val, 0.f);
+            P.hbuf[(size_t)b * P.F + m] = a * a;
+            break;
+        }
+        default: P.logits[(size_t)b * P.V + m] = val; break;
+    }
+}
+
+// Sum of one output row's int8-path partials over the tile's slots, in slot order.  The loads of BATCH slots are in flight
+// together.  TWO: the column half holds two sessions.
+template <bool TWO, int BATCH>
+__device__ __forceinline__ void dp_sum_slots_i8(const uint32_t* d0, const DpRunMeta* mp, int ns, int b0, double ws, double wz, double& acc0, double& acc1) {
+    for (int s0 = 0; s0 < ns; s0 += BATCH) {
+        int i[BATCH][TWO ? 8 : 4];
+        float xs[BATCH][TWO ? 2 : 1];
+        long long ts[BATCH][TWO ? 2 : 1];
+#pragma unroll
+        for (int k = 0; k < BATCH; ++k) {
+            const bool live = s0 + k < ns;
+            const uint32_t* d = d0 + (size_t)(s0 + k) * (kDpN * 128);
+            const DpRunMeta* ms = mp + (size_t)(s0 + k) * kDpWarps;
+#pragma unroll
+            for (int j = 0; j < (TWO ? 8 : 4); ++j) i[k][j] = live ? (int)__ldcg(d + j * 128) : 0;
+#pragma unroll
+            for (int e = 0; e < (TWO ? 2 : 1); ++e) {
+                xs[k][e] = live ? __ldcg(&ms->xscale[b0 + e]) : 0.f;
+                ts[k][e] = live ? __ldcg(&ms->tsum[b0 + e]) : 0;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < BATCH; ++k) {
+            if (s0 + k < ns) {
+                const long long Q0 = (((long long)i[k][0] * 128 + i[k][1]) * 128 + i[k][2]) * 128 + i[k][3];
+                acc0 += (double)xs[k][0] * (ws * (double)Q0 + wz * (double)ts[k][0]);
+                if (TWO) {
+                    const long long Q1 = (((long long)i[k][TWO ? 4 : 0] * 128 + i[k][TWO ? 5 : 1]) * 128 + i[k][TWO ? 6 : 2]) * 128 + i[k][TWO ? 7 : 3];
+                    acc1 += (double)xs[k][TWO ? 1 : 0] * (ws * (double)Q1 + wz * (double)ts[k][TWO ? 1 : 0]);
+                }
+            }
         }
     }
-    return (float)acc;
+}
+
+// The warp in charge of sub-block (tile, q4, chalf) adds the partials of the tile's `ns` slots in slot order and stores the
+// outputs of its 32 rows.  int8 tiles: column half `chalf` holds sessions 2 chalf, 2 chalf + 1 (4 digits each); fp16 tiles:
+// half 0 holds all four sessions as (hi, lo) pairs.  Loads of data written by other CTAs bypass L1.
+__device__ __noinline__ void dp_finish_subblock(const DpParams& P, const DpRegion& R, int v, int mat_id, const DpMat& mat, bool i8, int tile, int mt, int ns,
+                                                int q4, int chalf, int wwarp, int lane, int NB) {
+    const int ml = q4 * 32 + lane, m = mt * 128 + ml;
+    const bool mok = m < mat.M;
+    const size_t t = (size_t)tile * R.pmax;
+    const uint32_t* d0 = R.data + t * (size_t)(kDpN * 128) + (size_t)(chalf * 8) * 128 + ml;
+    const DpRunMeta* mp = R.meta + t * kDpWarps + wwarp;
+    const bool to_x = v == DV_P3 || v == DV_P5;  // the result is added to the residual stream: its old value is requested first
+    if (i8) {
+        double acc0 = 0.0, acc1 = 0.0;
+        const int b0 = chalf * 2;
+        const bool two = b0 + 1 < NB;
+        const float x0 = (to_x && mok) ? __ldcg(P.x + (size_t)b0 * P.C + m) : 0.f;
+        const float x1 = (to_x && mok && two) ? __ldcg(P.x + (size_t)(b0 + 1) * P.C + m) : 0.f;
+        const double ws = mok ? mat.wscale[m] : 0.f, wz = mok ? mat.wzero[m] : 0.f;
+        if (two)
+            dp_sum_slots_i8<true, 4>(d0, mp, ns, b0, ws, wz, acc0, acc1);
+        else
+            dp_sum_slots_i8<false, 8>(d0, mp, ns, b0, ws, wz, acc0, acc1);
+        if (mok) {
+            if (to_x) {
+                P.x[(size_t)b0 * P.C + m] = x0 + (float)acc0;  // exactly one warp of the grid finishes a given output
+                if (two) P.x[(size_t)(b0 + 1) * P.C + m] = x1 + (float)acc1;
+            } else {
+                dp_store_output(P, v, mat_id, m, b0, (float)acc0);
+                if (two) dp_store_output(P, v, mat_id, m, b0 + 1, (float)acc1);
+            }
+        }
+    } else {
+        double acc[kDpMaxNB] = {0.0, 0.0, 0.0, 0.0};
+        float xo[kDpMaxNB];
+#pragma unroll
+        for (int b = 0; b < kDpMaxNB; ++b) xo[b] = (to_x && mok && b < NB) ? __ldcg(P.x + (size_t)b * P.C + m) : 0.f;
+#pragma unroll 4
+        for (int s = 0; s < ns; ++s) {
+            const uint32_t* d = d0 + (size_t)s * (kDpN * 128);
+            const DpRunMeta* ms = mp + (size_t)s * kDpWarps;
+#pragma unroll
+            for (int b = 0; b < kDpMaxNB; ++b)
+                if (b < NB) acc[b] += (double)__ldcg(&ms->xscale[b]) * (double)(__uint_as_float(__ldcg(d + (2 * b) * 128)) + __uint_as_float(__ldcg(d + (2 * b + 1) * 128)));
+        }
+        if (mok) {
+#pragma unroll
+            for (int b = 0; b < kDpMaxNB; ++b)
+                if (b < NB) {
+                    if (to_x)
+                        P.x[(size_t)b * P.C + m] = xo[b] + (float)acc[b];
+                    else
+                        dp_store_output(P, v, mat_id, m, b, (float)acc[b]);
+                }
+        }
+    }
 }
 
 // Builds the schedule of one phase variant for this CTA.  Executed by one thread.
@@ -326,7 +434,7 @@ __device__ void dp_build_variant(const DpParams& P, int v, int cta, int G, DpVar
             r.nu = 0;
             r.slot = (uint8_t)((u == tile_first) ? 0 : (cta - dp_cta_of(tile_first, U, V.ge)));
             r.prob = (uint8_t)pi;
-            r.pad = 0;
+            r.ns = (uint8_t)(dp_cta_of(tile_first + V.p_kblocks[pi] - 1, U, V.ge) - dp_cta_of(tile_first, U, V.ge) + 1);
             if (V.nruns < kDpMaxRuns)
                 V.run[V.nruns] = r;
             else
@@ -364,7 +472,8 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
     float* sc_mid = reinterpret_cast<float*>(sc_tsum + (size_t)P.btiles * kDpMaxNB);   // [wm+am+vm+gm]
     float* sc_hv = sc_mid + (P.wm + P.am + P.vm + P.gm);                               // 8 x 64
     uint32_t* sc_tok = reinterpret_cast<uint32_t*>(sc_hv + 8 * 64);                    // [4]
-    DpVar* vars = reinterpret_cast<DpVar*>(sc_tok + 4);                                // [DV_COUNT]
+    float* sc_shift = reinterpret_cast<float*>(sc_tok + 4);                            // [4][slice] pending channel-mix shift state
+    DpVar* vars = reinterpret_cast<DpVar*>(sc_shift + kDpMaxNB * kDpMaxSlice);         // [DV_COUNT]
     DpUnit* units = reinterpret_cast<DpUnit*>(vars + DV_COUNT);                        // [max_units]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -399,16 +508,59 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
 
     if (warp == 0) {
         // =========================== TMA producer ===========================
-        if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (int t = 0; t < P.n_tokens && ok; ++t) {
-                const bool do_head = P.argmax_feed || t == P.n_tokens - 1;
-                for (int l = 0; l <= P.L && ok; ++l) {
-                    if (l == P.L && !do_head) break;
-                    for (int phs = 0; phs < (l == P.L ? 1 : 4) && ok; ++phs) {
-                        const int v = l == P.L ? DV_HEAD : (phs == 0 ? (l == 0 ? DV_P1A : DV_P1B) : DV_P3 + phs - 1);
-                        const DpVar& V = vars[v];
+        // Lane 0 issues the weight tiles.  Before each phase's tiles all 32 lanes pull the small arrays of that phase
+        // (LayerNorm / mix vectors, rank back-projection matrices, per-row scales, recurrent state) into L2, every CTA
+        // its share of the lines: they are not part of the TMA stream, and the producer runs about one phase ahead of
+        // the workers, so their dependent loads find the data in L2 instead of HBM.
+        auto pf = [&](const void* p, size_t bytes) { dp_prefetch_l2(p, bytes, cta, G, lane, 32); };
+        const size_t cb = (size_t)C * 4;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = 0; t < P.n_tokens && ok; ++t) {
+            const bool do_head = P.argmax_feed || t == P.n_tokens - 1;
+            for (int l = 0; l <= P.L && ok; ++l) {
+                if (l == P.L && !do_head) break;
+                for (int phs = 0; phs < (l == P.L ? 1 : 4) && ok; ++phs) {
+                    const int v = l == P.L ? DV_HEAD : (phs == 0 ? (l == 0 ? DV_P1A : DV_P1B) : DV_P3 + phs - 1);
+                    const DpVar& V = vars[v];
+                    if (v == DV_HEAD) {
+                        pf(P.lno_w, cb);
+                        pf(P.lno_b, cb);
+                    } else {
+                        const DpLayer* Ln = &P.layers[l];
+                        if (v == DV_P1A || v == DV_P1B) {
+                            for (const float* p : {Ln->ln1_w, Ln->ln1_b, Ln->x_r, Ln->x_w, Ln->x_k, Ln->x_v, Ln->x_a, Ln->x_g}) pf(p, cb);
+                            for (int mi : {DM_WR, DM_WK, DM_WV})
+                                if (Ln->mat[mi].is_i8) {
+                                    pf(Ln->mat[mi].wscale, cb);
+                                    pf(Ln->mat[mi].wzero, cb);
+                                }
+                            for (int b = 0; b < NB; ++b) pf(Ln->tmix_x + (size_t)P.slot[b] * C, cb);
+                        } else if (v == DV_P3) {  // the heads phase runs before phase 3
+                            pf(Ln->w2, (size_t)C * P.wm * 2);
+                            pf(Ln->a2, (size_t)C * P.am * 2);
+                            pf(Ln->v2, (size_t)C * P.vm * 2);
+                            pf(Ln->g2, (size_t)C * P.gm * 2);
+                            for (const float* p : {Ln->w0, Ln->a0, Ln->v0, Ln->k_k, Ln->k_a, Ln->r_k, Ln->lnx_w, Ln->lnx_b}) pf(p, cb);
+                            if (Ln->mat[DM_WO].is_i8) {
+                                pf(Ln->mat[DM_WO].wscale, cb);
+                                pf(Ln->mat[DM_WO].wzero, cb);
+                            }
+                            for (int b = 0; b < NB; ++b) pf(Ln->wkv + (size_t)P.slot[b] * P.H * 64 * 64, (size_t)P.H * 64 * 64 * 4);
+                        } else if (v == DV_P4) {
+                            for (const float* p : {Ln->ln2_w, Ln->ln2_b, Ln->ffn_x_k}) pf(p, cb);
+                            for (int b = 0; b < NB; ++b) pf(Ln->cmix_x + (size_t)P.slot[b] * C, cb);
+                            if (Ln->mat[DM_WFK].is_i8) {
+                                pf(Ln->mat[DM_WFK].wscale, (size_t)P.F * 4);
+                                pf(Ln->mat[DM_WFK].wzero, (size_t)P.F * 4);
+                            }
+                            if (Ln->mat[DM_WFV].is_i8) {
+                                pf(Ln->mat[DM_WFV].wscale, cb);
+                                pf(Ln->mat[DM_WFV].wzero, cb);
+                            }
+                        }
+                    }
+                    if (lane == 0) {
                         const DpUnit* un = units + V.unit0;
                         const bool dbg_here = P.dbg && cta == 0 && t == 1 && l == 1 && v == DV_P4;
                         if (dbg_here) P.dbg[55] = dp_now();
@@ -425,6 +577,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                         }
                         if (dbg_here) P.dbg[56] = dp_now();
                     }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // keeps the lanes in step with the tile issue
                 }
             }
         }
@@ -556,8 +709,6 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
 
                     // ---------- phase 2 (heads) runs between P1 and P3 ----------
                     if (v == DV_P3) {
-                        const DpVar& V1 = vars[l == 0 ? DV_P1A : DV_P1B];
-                        const DpRegion& R1 = P.reg[DR_P1];
                         // new time-mix shift state = LN1(x) on this CTA's slice (all readers of the old state are past barrier 1)
                         for (int i = wtid; i < NB * (c1 - c0); i += kDpWorkers) {
                             const int b = i / (c1 - c0), m = c0 + i % (c1 - c0);
@@ -571,32 +722,23 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                             float4 s4[4];
 #pragma unroll
                             for (int j = 0; j < 4; ++j) s4[j] = *reinterpret_cast<const float4*>(srow + 4 * j);
+                            // this thread's quarter rows of the back-projection matrices -> L1, per-channel parameters -> registers
+                            dp_prefetch_l1(Ly->w2 + (size_t)ch * P.wm + quad * (P.wm >> 2));
+                            dp_prefetch_l1(Ly->a2 + (size_t)ch * P.am + quad * (P.am >> 2));
+                            dp_prefetch_l1(Ly->g2 + (size_t)ch * P.gm + quad * (P.gm >> 2));
+                            if ((P.gm >> 2) > 64) dp_prefetch_l1(Ly->g2 + (size_t)ch * P.gm + quad * (P.gm >> 2) + 64);
+                            if (l > 0) dp_prefetch_l1(Ly->v2 + (size_t)ch * P.vm + quad * (P.vm >> 2));
+                            const float p_w0 = Ly->w0[ch], p_a0 = Ly->a0[ch], p_kk = Ly->k_k[ch], p_ka = Ly->k_a[ch], p_rk = Ly->r_k[ch];
+                            const float p_gw = Ly->lnx_w[ch], p_gb = Ly->lnx_b[ch];
+                            const float p_v0 = l > 0 ? Ly->v0[ch] : 0.f, p_vf = l > 0 ? P.vfirst[(size_t)b * C + ch] : 0.f;
                             dp_worker_sync();  // the previous item is done with the scratch vectors
-                            // rank-space vectors of session b (tanh / sigmoid applied here) and r, k, v of this head
+                            // rank-space vectors of session b and r, k, v of this head
                             for (int j = wtid; j < nmid + 3 * 64; j += kDpWorkers) {
                                 if (j < nmid) {
-                                    int pi, jj;
-                                    if (j < P.wm) {
-                                        pi = 3;
-                                        jj = j;
-                                    } else if (j < P.wm + P.am) {
-                                        pi = 4;
-                                        jj = j - P.wm;
-                                    } else if (j < P.wm + P.am + P.vm) {
-                                        pi = 6;
-                                        jj = j - P.wm - P.am;
-                                    } else {
-                                        pi = 5;
-                                        jj = j - P.wm - P.am - P.vm;
-                                    }
-                                    float vv = 0.f;
-                                    if (pi != 6 || l > 0) vv = dp_finalize(R1, V1, pi, Ly->mat[V1.p_mat[pi]], jj, b);
-                                    if (pi == 3) vv = tanhf(vv);
-                                    if (pi == 5) vv = 1.0f / (1.0f + expf(-vv));
-                                    sc_mid[j] = vv;
+                                    sc_mid[j] = P.mid[(size_t)b * nmid + j];
                                 } else {
-                                    const int jj = j - nmid, pi = jj >> 6;
-                                    sc_hv[jj] = dp_finalize(R1, V1, pi, Ly->mat[V1.p_mat[pi]], h * 64 + (jj & 63), b);
+                                    const int jj = j - nmid;
+                                    sc_hv[jj] = P.rkv[((size_t)b * 3 + (jj >> 6)) * C + h * 64 + (jj & 63)];
                                 }
                             }
                             dp_worker_sync();
@@ -626,8 +768,8 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                             const float dw = dot_q(Ly->w2, P.wm, sc_mid);
                             const float da = dot_q(Ly->a2, P.am, sc_mid + P.wm);
                             const float dg = dot_q(Ly->g2, P.gm, sc_mid + P.wm + P.am + P.vm);
-                            const float wdec = expf((1.0f / (1.0f + expf(-(dw + Ly->w0[ch])))) * kDecayScale);
-                            const float aa = 1.0f / (1.0f + expf(-(da + Ly->a0[ch])));
+                            const float wdec = expf((1.0f / (1.0f + expf(-(dw + p_w0)))) * kDecayScale);
+                            const float aa = 1.0f / (1.0f + expf(-(da + p_a0)));
                             const float rr = sc_hv[(wtid >> 2)], kk0 = sc_hv[64 + (wtid >> 2)];
                             float vv0 = sc_hv[128 + (wtid >> 2)];
                             if (l == 0) {
@@ -637,13 +779,13 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                                 }
                             } else {
                                 const float dv = dot_q(Ly->v2, P.vm, sc_mid + P.wm + P.am);
-                                const float gate = 1.0f / (1.0f + expf(-(dv + Ly->v0[ch])));
-                                vv0 = vv0 + gate * (P.vfirst[(size_t)b * C + ch] - vv0);
+                                const float gate = 1.0f / (1.0f + expf(-(dv + p_v0)));
+                                vv0 = vv0 + gate * (p_vf - vv0);
                             }
-                            const float kkj = kk0 * Ly->k_k[ch];
+                            const float kkj = kk0 * p_kk;
                             const float ss = dp_worker_sum(quad == 0 ? kkj * kkj : 0.f, red, wtid);
                             const float kkh = kkj * (1.0f / fmaxf(sqrtf(ss), kL2Eps));
-                            const float kt = kk0 + Ly->k_a[ch] * (kk0 * aa - kk0);
+                            const float kt = kk0 + p_ka * (kk0 * aa - kk0);
                             if (quad == 0) {
                                 const int i = wtid >> 2;
                                 sc_hv[3 * 64 + i] = wdec;
@@ -681,8 +823,8 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                             const float mean = dp_worker_sum(quad == 0 ? y : 0.f, red, wtid) / 64.0f;
                             const float d = y - mean;
                             const float var = dp_worker_sum(quad == 0 ? d * d : 0.f, red, wtid) / 64.0f + kGnEps;
-                            const float srk = dp_worker_sum(quad == 0 ? rr * kt * Ly->r_k[ch] : 0.f, red, wtid);
-                            if (quad == 0) P.yg[(size_t)b * C + ch] = (d * (1.0f / sqrtf(var)) * Ly->lnx_w[ch] + Ly->lnx_b[ch] + srk * vv0) * dg;
+                            const float srk = dp_worker_sum(quad == 0 ? rr * kt * p_rk : 0.f, red, wtid);
+                            if (quad == 0) P.yg[(size_t)b * C + ch] = (d * (1.0f / sqrtf(var)) * p_gw + p_gb + srk * vv0) * dg;
                         }
                         DP_STAMP(40);
                         ok = dp_grid_barrier(P.grid_bar, bar_target, G, abort_flag, wtid);
@@ -717,11 +859,18 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                         }
                         dp_worker_sync();
                     }
-                    if (v == DV_P5) {
-                        // new channel-mix shift state = LN2(x) on this CTA's slice (readers of the old state are past barrier 4)
+                    if (v == DV_P4) {
+                        // new channel-mix shift state = LN2(x) on this CTA's slice: computed now, while x is stable, stored in
+                        // phase 5 when every reader of the old state is past the barrier (phase 5 itself updates x)
                         for (int i = wtid; i < NB * (c1 - c0); i += kDpWorkers) {
                             const int b = i / (c1 - c0), m = c0 + i % (c1 - c0);
-                            Ly->cmix_x[(size_t)P.slot[b] * C + m] = (P.x[(size_t)b * C + m] - st_ln[b].mean) * st_ln[b].inv * Ly->ln2_w[m] + Ly->ln2_b[m];
+                            sc_shift[i] = (P.x[(size_t)b * C + m] - st_ln[b].mean) * st_ln[b].inv * Ly->ln2_w[m] + Ly->ln2_b[m];
+                        }
+                    }
+                    if (v == DV_P5) {
+                        for (int i = wtid; i < NB * (c1 - c0); i += kDpWorkers) {
+                            const int b = i / (c1 - c0), m = c0 + i % (c1 - c0);
+                            Ly->cmix_x[(size_t)P.slot[b] * C + m] = sc_shift[i];
                         }
                     }
                     DP_STAMP(phs * 10 + 1);
@@ -741,7 +890,6 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                             lw = P.lno_w;
                             lb = P.lno_b;
                         }
-                        const DpVar& V4 = vars[DV_P4];
                         auto mixptr = [&](int pi) -> const float* {  // mix vector of a problem of phase 1 / 4
                             if (v == DV_P4) return Ly->ffn_x_k;
                             switch (V.p_mat[pi]) {
@@ -756,10 +904,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                         };
                         auto input = [&](int pi, int b, int k) -> float {
                             if (v == DV_P3) return P.yg[(size_t)b * C + k];
-                            if (v == DV_P5) {
-                                const float a = fmaxf(dp_finalize(P.reg[DR_P4], V4, 0, Ly->mat[DM_WFK], k, b), 0.f);
-                                return a * a;
-                            }
+                            if (v == DV_P5) return P.hbuf[(size_t)b * P.F + k];
                             const float xv = x_from_emb ? ((__half2float(P.emb[(size_t)sc_tok[b] * C + k]) - st_emb[b].mean) * st_emb[b].inv * P.ln0_w[k] + P.ln0_b[k])
                                                         : P.x[(size_t)b * C + k];
                             const float cur = (xv - st_ln[b].mean) * st_ln[b].inv * lw[k] + lb[k];
@@ -868,6 +1013,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     dp_worker_sync();
+                    DP_STAMP_ALL(0);
                     if (wtid == 0) mbar_arrive(b_ready);
                     DP_STAMP(phs * 10 + 2);
 
@@ -875,6 +1021,8 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                     {
                         const DpRegion& Rg = P.reg[V.region];
                         const int nruns = min(V.nruns, kDpMaxRuns);
+                        int ndone = 0;
+                        // pass 1: every run's accumulator -> partial sums and scale in global memory
                         for (int ri = 0; ri < nruns; ++ri) {
                             const DpRun r = V.run[ri];
                             const size_t tidx = (size_t)r.tile * Rg.pmax + r.slot;
@@ -900,44 +1048,80 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                                         vv[j] = __float_as_uint(__uint_as_float(vv[j]) + __uint_as_float(v2[j]));
                                 }
                             }
-                            uint32_t* dst = Rg.data + tidx * (size_t)(kDpN * 128) + (size_t)(chalf * 8) * 128 + q4 * 32 + lane;
+                            // sessions live in the first 4 NB (int8) or 2 NB (fp16) columns: a warp whose column half holds none skips
+                            if (chalf * 8 < (r_i8 ? 4 : 2) * NB) {
+                                uint32_t* dst = Rg.data + tidx * (size_t)(kDpN * 128) + (size_t)(chalf * 8) * 128 + q4 * 32 + lane;
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) dst[(size_t)j * 128] = vv[j];
-                            if (wtid < NB) {
-                                // scale of this CTA's operand for the problem, exact sum of the run's fixed-point values
-                                const DpUnit* un = units + V.unit0 + r.u0;
-                                long long ts = 0;
-                                for (int uu = 0; uu < r.nu; ++uu) ts += sc_tsum[(size_t)un[uu].btile * kDpMaxNB + wtid];
-                                int sh = 0;
-                                while (sh + 1 < V.nshares && V.share[sh].prob != r.prob) ++sh;
-                                Rg.meta[tidx].xscale[wtid] = sc_scale[sh * 4 + wtid];
-                                Rg.meta[tidx].tsum[wtid] = ts;
+                                for (int j = 0; j < 8; ++j) dst[(size_t)j * 128] = vv[j];
+                                if (lane < NB) {
+                                    // scale of this CTA's operand for the problem, exact sum of the run's fixed-point values
+                                    const DpUnit* un = units + V.unit0 + r.u0;
+                                    long long ts = 0;
+                                    for (int uu = 0; uu < r.nu; ++uu) ts += sc_tsum[(size_t)un[uu].btile * kDpMaxNB + lane];
+                                    int sh = 0;
+                                    while (sh + 1 < V.nshares && V.share[sh].prob != r.prob) ++sh;
+                                    DpRunMeta* mp = Rg.meta + tidx * kDpWarps + wwarp;
+                                    mp->xscale[lane] = sc_scale[sh * 4 + lane];
+                                    mp->tsum[lane] = ts;
+                                }
                             }
                             tc_fence_before();
                             __syncwarp();
                             if (lane == 0) mbar_arrive(&acc_empty[run & 1]);
                             ++run;
+                            ++ndone;
+                        }
+                        // arrivals: one reduction per run and warp after a single fence
+                        DP_STAMP_ALL(1);
+                        __syncwarp();
+                        if (lane == 0) {
+                            fence_acq_rel_gpu();  // the warp's partials and scales are visible device-wide before the arrivals are counted
+                            for (int ri = 0; ri < ndone; ++ri) {
+                                const DpRun r = V.run[ri];
+                                if (chalf * 8 < (V.p_i8[r.prob] ? 4 : 2) * NB) atomicAdd(&Rg.cnt[(size_t)r.tile * kDpWarps + wwarp], 1);
+                            }
+                        }
+                        DP_STAMP_ALL(2);
+                        // pass 2: sub-block w of a tile is finished by the CTA whose slot is (w + tile) mod ns, so the finishing work of
+                        // a tile is spread over its sharers and no warp finishes two sub-blocks of one tile.  That warp waits (bounded)
+                        // until all ns arrivals are counted.
+                        for (int ri = 0; ri < ndone; ++ri) {
+                            const DpRun r = V.run[ri];
+                            const bool r_i8 = V.p_i8[r.prob] != 0;
+                            if (!(chalf * 8 < (r_i8 ? 4 : 2) * NB) || (wwarp + (int)r.tile) % (int)r.ns != (int)r.slot) continue;
+                            int* cnt = &Rg.cnt[(size_t)r.tile * kDpWarps + wwarp];
+                            int seen = 0;
+                            if (lane == 0) {
+                                for (uint32_t i = 0; i < kDpBarSpin; ++i) {
+                                    int c;
+                                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(c) : "l"(cnt) : "memory");
+                                    if (c >= (int)r.ns) {
+                                        seen = 1;
+                                        break;
+                                    }
+                                    if ((i & 255u) == 255u && *abort_flag) break;
+                                }
+                                if (seen)
+                                    *cnt = 0;  // all arrivals counted: ready for the next use
+                                else
+                                    *abort_flag = 1;
+                            }
+                            seen = __shfl_sync(0xffffffffu, seen, 0);
+                            if (!seen) break;
+                            const int mat_id = V.p_mat[r.prob];
+                            const DpUnit u0 = units[V.unit0 + r.u0];
+                            dp_finish_subblock(P, Rg, v, mat_id, mat_id == DM_HEAD ? P.head : Ly->mat[mat_id], r_i8, r.tile, u0.mt, r.ns, q4, chalf, wwarp, lane, NB);
                         }
                     }
                     DP_STAMP(phs * 10 + 3);
+                    DP_STAMP_ALL(3);
                     // every worker reaches the barrier below whether or not its warp left the loop early;
                     // dp_grid_barrier returns the shared abort state, so the decision to stop is the same for all
                     ok = dp_grid_barrier(P.grid_bar, bar_target, G, abort_flag, wtid);
                     if (!ok) break;
                     DP_STAMP(phs * 10 + 4);
+                    DP_STAMP_ALL(4);
 
-                    // ---------- residual stream: x += result, on disjoint slices, then a second barrier ----------
-                    if (v == DV_P3 || v == DV_P5) {
-                        const DpMat& mat = Ly->mat[v == DV_P3 ? DM_WO : DM_WFV];
-                        for (int i = wtid; i < NB * (c1 - c0); i += kDpWorkers) {
-                            const int b = i / (c1 - c0), m = c0 + i % (c1 - c0);
-                            P.x[(size_t)b * C + m] += dp_finalize(P.reg[V.region], V, 0, mat, m, b);
-                        }
-                        DP_STAMP(phs * 10 + 5);
-                        ok = dp_grid_barrier(P.grid_bar, bar_target, G, abort_flag, wtid);
-                        if (!ok) break;
-                        DP_STAMP(phs * 10 + 6);
-                    }
                     // ---------- logits, arg-max ----------
                     if (v == DV_HEAD) {
                         const int v0 = (int)(((long long)cta * P.V) / G), v1 = (int)(((long long)(cta + 1) * P.V) / G);
@@ -945,8 +1129,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                             float bv = -1e30f;
                             int bi = 0x7fffffff;
                             for (int vv = v0 + wtid; vv < v1; vv += kDpWorkers) {
-                                const float lg = dp_finalize(P.reg[DR_HEAD], V, 0, P.head, vv, b);
-                                P.logits[(size_t)b * P.V + vv] = lg;
+                                const float lg = P.logits[(size_t)b * P.V + vv];
                                 if (lg > bv) {
                                     bv = lg;
                                     bi = vv;

@@ -399,12 +399,13 @@ Model::~Model() {
     for (void* p : allocs) cudaFree(p);
     for (void* p : {(void*)ws.tc_b, (void*)ws.tc_xscale, (void*)ws.tc_tsum, ws.tc_partials, (void*)ws.tc_cnt})
         if (p) cudaFree(p);
-    for (void* p : {pctx.d_layers, pctx.d_maps, (void*)pctx.x, (void*)pctx.yg, (void*)pctx.vfirst, (void*)pctx.cand_val, (void*)pctx.cand_idx,
+    for (void* p : {pctx.d_layers, pctx.d_maps, (void*)pctx.x, (void*)pctx.yg, (void*)pctx.vfirst, (void*)pctx.cand_val, (void*)pctx.cand_idx, (void*)pctx.rkv, (void*)pctx.mid, (void*)pctx.hbuf,
                     (void*)pctx.grid_bar})
         if (p) cudaFree(p);
     for (int i = 0; i < 5; ++i) {
         if (pctx.region_data[i]) cudaFree(pctx.region_data[i]);
         if (pctx.region_meta[i]) cudaFree(pctx.region_meta[i]);
+        if (pctx.region_cnt[i]) cudaFree(pctx.region_cnt[i]);
     }
     if (pinned) cudaFreeHost(pinned);
     for (int i = 0; i < kPinRing; ++i)
@@ -1033,9 +1034,10 @@ bool Model::persistent_available(int nb) {
     if (max_runs > kDpMaxRuns || max_shares > kDpMaxShares) return fail("schedule tables of the persistent kernel are too small for this shape");
     if (btiles > 255) return fail("too many operand tiles per CTA for this shape");
     if (C > 16 * kDpWorkers) return fail("n_embd too large for the persistent kernel's register-resident LayerNorm");
+    if ((C + G - 1) / G + 1 > kDpMaxSlice) return fail("n_embd too large for the persistent kernel's per-CTA slice of the residual stream");
     // shared memory: ring + operand tiles + barriers + worker scratch
     const size_t fixed = (size_t)btiles * kDpBTile + 1024 /*alignment*/ + 2048 /*barriers, small scratch*/ + (size_t)btiles * kDpMaxNB * 8 +
-                         (size_t)cfg.mids() * 4 + 8 * 64 * 4 + DV_COUNT * sizeof(DpVar) + (size_t)max_units * sizeof(DpUnit);
+                         (size_t)cfg.mids() * 4 + 8 * 64 * 4 + (size_t)kDpMaxNB * kDpMaxSlice * 4 + DV_COUNT * sizeof(DpVar) + (size_t)max_units * sizeof(DpUnit);
     const size_t budget = 227 * 1024;
     if (fixed + 3 * (size_t)kDpATile > budget) return fail("operand tiles do not fit in shared memory for this shape");
     const int nstages = (int)std::min<size_t>(10, (budget - fixed) / kDpATile);
@@ -1054,21 +1056,27 @@ bool Model::persistent_available(int nb) {
     RSV_CUDA(cudaMalloc(&pc.x, (size_t)kDpMaxNB * C * 4));
     RSV_CUDA(cudaMalloc(&pc.yg, (size_t)kDpMaxNB * C * 4));
     RSV_CUDA(cudaMalloc(&pc.vfirst, (size_t)kDpMaxNB * C * 4));
+    RSV_CUDA(cudaMalloc(&pc.rkv, (size_t)kDpMaxNB * 3 * C * 4));
+    RSV_CUDA(cudaMalloc(&pc.mid, (size_t)kDpMaxNB * cfg.mids() * 4));
+    RSV_CUDA(cudaMalloc(&pc.hbuf, (size_t)kDpMaxNB * cfg.ffn_hidden * 4));
+    RSV_CUDA(cudaMemset(pc.mid, 0, (size_t)kDpMaxNB * cfg.mids() * 4));
     RSV_CUDA(cudaMalloc(&pc.cand_val, (size_t)G * kDpMaxNB * 4));
     RSV_CUDA(cudaMalloc(&pc.cand_idx, (size_t)G * kDpMaxNB * 4));
     RSV_CUDA(cudaMalloc(&pc.grid_bar, 4));
     if (const char* e = getenv("RSV_DP_DEBUG"))
         if (*e && *e != '0') {
-            RSV_CUDA(cudaMalloc(&pc.dbg, 64 * sizeof(long long)));
-            RSV_CUDA(cudaMemset(pc.dbg, 0, 64 * sizeof(long long)));
+            RSV_CUDA(cudaMalloc(&pc.dbg, (64 + 8 * 1024) * sizeof(long long)));
+            RSV_CUDA(cudaMemset(pc.dbg, 0, (64 + 8 * 1024) * sizeof(long long)));
         }
     RSV_CUDA(cudaMemset(pc.vfirst, 0, (size_t)kDpMaxNB * C * 4));
     for (int i = 0; i < 5; ++i) {
         const size_t runs = (size_t)tiles[i] * pmax[i];
         RSV_CUDA(cudaMalloc(&pc.region_data[i], runs * kDpN * 128 * 4));
-        RSV_CUDA(cudaMalloc(&pc.region_meta[i], runs * sizeof(DpRunMeta)));
+        RSV_CUDA(cudaMalloc(&pc.region_meta[i], runs * kDpWarps * sizeof(DpRunMeta)));
+        RSV_CUDA(cudaMalloc(&pc.region_cnt[i], (size_t)tiles[i] * kDpWarps * sizeof(int)));
         RSV_CUDA(cudaMemset(pc.region_data[i], 0, runs * kDpN * 128 * 4));
-        RSV_CUDA(cudaMemset(pc.region_meta[i], 0, runs * sizeof(DpRunMeta)));
+        RSV_CUDA(cudaMemset(pc.region_meta[i], 0, runs * kDpWarps * sizeof(DpRunMeta)));
+        RSV_CUDA(cudaMemset(pc.region_cnt[i], 0, (size_t)tiles[i] * kDpWarps * sizeof(int)));
         pc.region_pmax[i] = pmax[i];
     }
     // layer tables need the state pointers of the call: only the state-independent part is stored here
@@ -1092,9 +1100,13 @@ bool Model::persistent_available(int nb) {
     P.x = pc.x;
     P.yg = pc.yg;
     P.vfirst = pc.vfirst;
+    P.rkv = pc.rkv;
+    P.mid = pc.mid;
+    P.hbuf = pc.hbuf;
     for (int i = 0; i < 5; ++i) {
         P.reg[i].data = (uint32_t*)pc.region_data[i];
         P.reg[i].meta = (DpRunMeta*)pc.region_meta[i];
+        P.reg[i].cnt = pc.region_cnt[i];
         P.reg[i].pmax = pmax[i];
     }
     P.dbg = pc.dbg;
@@ -1156,9 +1168,10 @@ void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bo
         RSV_CUDA(cudaLaunchCooperativeKernel((const void*)decode_persistent_kernel, dim3(pc.grid), dim3(kDpThreads), args, pc.smem, stream));
     }
     if (pc.dbg && n_tokens >= 2) {
-        long long h[64];
+        std::vector<long long> hv(64 + 8 * 1024);
+        long long* h = hv.data();
         RSV_CUDA(cudaStreamSynchronize(stream));
-        RSV_CUDA(cudaMemcpy(h, pc.dbg, sizeof(h), cudaMemcpyDeviceToHost));
+        RSV_CUDA(cudaMemcpy(h, pc.dbg, hv.size() * sizeof(long long), cudaMemcpyDeviceToHost));
         const char* names[7] = {"phase start", "stats done", "operands done", "runs drained", "barrier done", "x slice done", "barrier b done"};
         long long t0 = h[0];
         fprintf(stderr, "[persistent kernel, CTA 0, token 1, layer 1] times in us since P1 start\n");
@@ -1166,6 +1179,26 @@ void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bo
             if (ph == 1) fprintf(stderr, "  heads done %.2f, barrier 2 done %.2f\n", (h[40] - t0) / 1e3, (h[41] - t0) / 1e3);
             for (int i = 0; i < 7; ++i)
                 if (h[ph * 10 + i]) fprintf(stderr, "  phase %d %-14s %.2f\n", ph, names[i], (h[ph * 10 + i] - t0) / 1e3);
+        }
+        {
+            const char* nm[5] = {"operands done", "partials stored", "arrivals returned", "finishing done", "barrier left"};
+            const long long p3 = h[10];  // CTA 0, phase 3 start
+            for (int k = 0; k < 5; ++k) {
+                long long mn = 1LL << 62, mx = 0, sum = 0;
+                int amx = -1, n = 0;
+                for (int c = 0; c < pc.grid && c < 1024; ++c) {
+                    const long long v = h[64 + c * 8 + k];
+                    if (!v) continue;
+                    ++n;
+                    sum += v - p3;
+                    if (v < mn) mn = v;
+                    if (v > mx) {
+                        mx = v;
+                        amx = c;
+                    }
+                }
+                if (n) fprintf(stderr, "  att.output phase, all CTAs: %-18s min %.2f avg %.2f max %.2f (CTA %d) [us since CTA 0 entered the phase]\n", nm[k], (mn - p3) / 1e3, sum / 1e3 / n, (mx - p3) / 1e3, amx);
+            }
         }
         fprintf(stderr, "  ffn.key phase: producer issued its %lld tiles from %.2f to %.2f; MMA thread started %.2f, last issue %.2f, waited %.2f us for tiles/accumulators\n",
                 h[53], (h[55] - t0) / 1e3, (h[56] - t0) / 1e3, (h[50] - t0) / 1e3, (h[51] - t0) / 1e3, h[52] / 1e3);

@@ -84,6 +84,8 @@ struct PersistentCtx {
     long long* dbg = nullptr;  // RSV_DP_DEBUG=1: phase time stamps of the persistent kernel
     void* region_data[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     void* region_meta[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    int* region_cnt[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    float *rkv = nullptr, *mid = nullptr, *hbuf = nullptr;
     int region_pmax[5] = {1, 1, 1, 1, 1};
     int grid = 0, nstages = 0, btiles = 0;
     size_t smem = 0;

@@ -108,6 +108,10 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* ba
                  "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
                  : "memory");
 }
+// Release / acquire fence at device scope (lighter than the sequentially consistent fence of __threadfence()).  Used as
+// "stores; __syncwarp(); lane 0: fence, atomic" on the producing side and "lane 0: atomic, fence; __syncwarp(); loads that
+// bypass L1" on the consuming side.
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
 }
@@ -419,19 +423,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
                     for (int j4 = 0; j4 < 4; ++j4) dst[(size_t)((c0 >> 4) * 4 + j4) * kTcTileM + row] = make_uint4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
                 }
                 tc_fence_before();
-                __threadfence();  // this lane's partials are visible device-wide before the arrival is counted
                 __syncwarp();
                 int old = 0;
                 if (lane == 0) {
                     mbar_arrive(&acc_empty[run & 1]);  // the accumulator may be reused while the tile is finished
+                    fence_acq_rel_gpu();               // the warp's partials are visible device-wide before the arrival is counted
                     old = atomicAdd(&L.tile_cnt[lo * kTcEpiWarps + ew], 1);
+                    fence_acq_rel_gpu();
                 }
                 old = __shfl_sync(0xffffffffu, old, 0);
                 const int nslots = tc_cta_of_unit(tile_first + P.kblocks - 1, U, G) - tc_cta_of_unit(tile_first, U, G) + 1;
                 if (old == nslots - 1) {
                     // last arrival on this sub-block: every slot is complete
                     if (lane == 0) L.tile_cnt[lo * kTcEpiWarps + ew] = 0;  // ready for the next launch
-                    __threadfence();
                     auto accumulate = [&](uint32_t(&v)[16], const uint4(&t)[4]) {
 #pragma unroll
                         for (int j4 = 0; j4 < 4; ++j4) {
