@@ -473,7 +473,8 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
     float* sc_hv = sc_mid + (P.wm + P.am + P.vm + P.gm);                               // 8 x 64
     uint32_t* sc_tok = reinterpret_cast<uint32_t*>(sc_hv + 8 * 64);                    // [4]
     float* sc_shift = reinterpret_cast<float*>(sc_tok + 4);                            // [4][slice] pending channel-mix shift state
-    DpVar* vars = reinterpret_cast<DpVar*>(sc_shift + kDpMaxNB * kDpMaxSlice);         // [DV_COUNT]
+    DpLayer* sc_layer = reinterpret_cast<DpLayer*>(sc_shift + kDpMaxNB * kDpMaxSlice); // [2] table of the current / next layer
+    DpVar* vars = reinterpret_cast<DpVar*>(sc_layer + 2);                              // [DV_COUNT]
     DpUnit* units = reinterpret_cast<DpUnit*>(vars + DV_COUNT);                        // [max_units]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -654,6 +655,14 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
         bool ok = true;
         const int c0 = (int)(((long long)cta * C) / G), c1 = (int)(((long long)(cta + 1) * C) / G);  // this CTA's slice of the channels
         const int nmid = P.wm + P.am + P.vm + P.gm;
+        // The layer table (pointers, matrix shapes) is read through shared memory: a pointer fetched from global memory in front of
+        // every dependent load would add an L2 / HBM round trip to each step of the chain.
+        auto stage_layer = [&](int l) {
+            static_assert(sizeof(DpLayer) % 4 == 0, "DpLayer is copied word by word");
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(&P.layers[l]);
+            uint32_t* dst = reinterpret_cast<uint32_t*>(&sc_layer[l & 1]);
+            for (int i = wtid; i < (int)(sizeof(DpLayer) / 4); i += kDpWorkers) dst[i] = src[i];
+        };
 
         for (int t = 0; t < P.n_tokens && ok; ++t) {
             const bool do_head = P.argmax_feed || t == P.n_tokens - 1;
@@ -670,6 +679,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                 }
                 sc_tok[wtid] = tok;
             }
+            stage_layer(0);
             dp_worker_sync();
             for (int b = 0; b < NB; ++b) {
                 const __half* row = P.emb + (size_t)sc_tok[b] * C;
@@ -703,7 +713,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                 for (int phs = 0; phs < nph && ok; ++phs) {
                     const int v = l == P.L ? DV_HEAD : (phs == 0 ? (l == 0 ? DV_P1A : DV_P1B) : DV_P3 + phs - 1);
                     const DpVar& V = vars[v];
-                    const DpLayer* Ly = l < P.L ? &P.layers[l] : nullptr;
+                    const DpLayer* Ly = l < P.L ? &sc_layer[l & 1] : nullptr;
                     const bool x_from_emb = (v == DV_P1A);  // x has not crossed a barrier yet: rebuild it from the embedding
                     DP_STAMP(phs * 10 + 0);
 
@@ -732,13 +742,31 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                             const float p_gw = Ly->lnx_w[ch], p_gb = Ly->lnx_b[ch];
                             const float p_v0 = l > 0 ? Ly->v0[ch] : 0.f, p_vf = l > 0 ? P.vfirst[(size_t)b * C + ch] : 0.f;
                             dp_worker_sync();  // the previous item is done with the scratch vectors
-                            // rank-space vectors of session b and r, k, v of this head
-                            for (int j = wtid; j < nmid + 3 * 64; j += kDpWorkers) {
-                                if (j < nmid) {
-                                    sc_mid[j] = P.mid[(size_t)b * nmid + j];
-                                } else {
+                            // rank-space vectors of session b and r, k, v of this head (all loads issued before the first store)
+                            {
+                                constexpr int kGather = 4;  // nmid + 192 <= 4 * 256
+                                float gv[kGather];
+#pragma unroll
+                                for (int i = 0; i < kGather; ++i) {
+                                    const int j = min(wtid + i * kDpWorkers, nmid + 3 * 64 - 1);
                                     const int jj = j - nmid;
-                                    sc_hv[jj] = P.rkv[((size_t)b * 3 + (jj >> 6)) * C + h * 64 + (jj & 63)];
+                                    gv[i] = j < nmid ? P.mid[(size_t)b * nmid + j] : P.rkv[((size_t)b * 3 + (jj >> 6)) * C + h * 64 + (jj & 63)];
+                                }
+#pragma unroll
+                                for (int i = 0; i < kGather; ++i) {
+                                    const int j = wtid + i * kDpWorkers;
+                                    if (j < nmid)
+                                        sc_mid[j] = gv[i];
+                                    else if (j < nmid + 3 * 64)
+                                        sc_hv[j - nmid] = gv[i];
+                                }
+                                for (int j = wtid + kGather * kDpWorkers; j < nmid + 3 * 64; j += kDpWorkers) {  // larger rank spaces
+                                    const int jj = j - nmid;
+                                    const float t2 = j < nmid ? P.mid[(size_t)b * nmid + j] : P.rkv[((size_t)b * 3 + (jj >> 6)) * C + h * 64 + (jj & 63)];
+                                    if (j < nmid)
+                                        sc_mid[j] = t2;
+                                    else
+                                        sc_hv[jj] = t2;
                                 }
                             }
                             dp_worker_sync();
@@ -859,6 +887,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                         }
                         dp_worker_sync();
                     }
+                    if (v == DV_P4 && l + 1 < P.L) stage_layer(l + 1);
                     if (v == DV_P4) {
                         // new channel-mix shift state = LN2(x) on this CTA's slice: computed now, while x is stable, stored in
                         // phase 5 when every reader of the old state is past the barrier (phase 5 itself updates x)
@@ -890,7 +919,17 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                             lw = P.lno_w;
                             lb = P.lno_b;
                         }
+                        // The value of element k of the phase input is computed without a branch: every load has a valid (if unused)
+                        // address and the phase kind only selects among the results, so that the loads of all of a thread's elements are
+                        // in flight together instead of one element per memory round trip.
+                        const bool has_ln = !(v == DV_P3 || v == DV_P5), has_mix = has_ln && v != DV_HEAD;
+                        const float* src = v == DV_P3 ? P.yg : (v == DV_P5 ? P.hbuf : P.x);
+                        const int sstride = v == DV_P5 ? P.F : C;
+                        const float* lwp = has_ln ? lw : P.ln0_w;
+                        const float* lbp = has_ln ? lb : P.ln0_b;
+                        const float* shiftp = has_mix ? shift : P.ln0_w;
                         auto mixptr = [&](int pi) -> const float* {  // mix vector of a problem of phase 1 / 4
+                            if (!has_mix) return P.ln0_w;
                             if (v == DV_P4) return Ly->ffn_x_k;
                             switch (V.p_mat[pi]) {
                                 case DM_WR: return Ly->x_r;
@@ -902,15 +941,15 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                                 default: return Ly->x_v;  // DM_V1
                             }
                         };
-                        auto input = [&](int pi, int b, int k) -> float {
-                            if (v == DV_P3) return P.yg[(size_t)b * C + k];
-                            if (v == DV_P5) return P.hbuf[(size_t)b * P.F + k];
-                            const float xv = x_from_emb ? ((__half2float(P.emb[(size_t)sc_tok[b] * C + k]) - st_emb[b].mean) * st_emb[b].inv * P.ln0_w[k] + P.ln0_b[k])
-                                                        : P.x[(size_t)b * C + k];
-                            const float cur = (xv - st_ln[b].mean) * st_ln[b].inv * lw[k] + lb[k];
-                            if (v == DV_HEAD) return cur;
-                            const float prev = shift[(size_t)P.slot[b] * C + k];
-                            return cur + mixptr(pi)[k] * (prev - cur);
+                        auto input = [&](const float* mixp, int b, int k) -> float {
+                            const int kl = has_ln ? k : 0;
+                            const float xs = src[(size_t)b * sstride + k];
+                            const float xe = (__half2float(P.emb[(size_t)sc_tok[b] * C + kl]) - st_emb[b].mean) * st_emb[b].inv * P.ln0_w[kl] + P.ln0_b[kl];
+                            const float xv = x_from_emb ? xe : xs;
+                            const float cur = (xv - st_ln[b].mean) * st_ln[b].inv * lwp[kl] + lbp[kl];
+                            const float prev = shiftp[(has_mix ? (size_t)P.slot[b] * C : (size_t)0) + kl];
+                            const float mixed = cur + mixp[kl] * (prev - cur);
+                            return has_mix ? mixed : (has_ln ? cur : xs);
                         };
                         // quantise one element into its operand tile and add it to the tile's exact fixed-point sum
                         auto emit = [&](bool i8, uint8_t* tile, int tile_idx, int sh, int b, int e, float val) {
@@ -968,6 +1007,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                         for (int sh = 0; sh < nshare; ++sh) {
                             const DpShare S = V.share[sh];
                             const int pi = S.prob;
+                            const float* mixp = mixptr(pi);
                             const bool i8 = V.p_i8[pi] != 0;
                             const int epb = i8 ? 128 : 64, kbs = V.p_kblocks[pi], K = V.p_K[pi];
                             const int grp = kDpWorkers / epb;  // tiles handled side by side
@@ -978,34 +1018,51 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                                 if (S.ntile <= grp * kMaxItems) {
                                     // everything fits in registers: load once, reduce the magnitude, quantise
                                     float val[kMaxItems];
+                                    if (v == DV_P4) DP_STAMP(63);
+                                    // the loads are unconditional (clamped index) so that all of them are in flight before the first use
+                                    int kk[kMaxItems];
 #pragma unroll
                                     for (int it = 0; it < kMaxItems; ++it) {
-                                        const int tl = it * grp + sub;
-                                        const int kb = S.ntile == kbs ? tl : (S.kb0 + tl) % kbs;
+                                        const int tl = it * grp + sub, tlc = min(tl, (int)S.ntile - 1);
+                                        const int kb = S.ntile == kbs ? tlc : (S.kb0 + tlc) % kbs;
                                         const int k = kb * epb + e;
-                                        val[it] = (tl < S.ntile && k < K) ? input(pi, b, k) : 0.f;
-                                        am = fmaxf(am, fabsf(val[it]));
+                                        kk[it] = (tl >= S.ntile || k >= K) ? -1 : k;
                                     }
+                                    if (has_ln) {
+#pragma unroll
+                                        for (int it = 0; it < kMaxItems; ++it) val[it] = input(mixp, b, max(kk[it], 0));
+                                    } else {  // att.output, ffn.value: the input vector as it is
+#pragma unroll
+                                        for (int it = 0; it < kMaxItems; ++it) val[it] = src[(size_t)b * sstride + max(kk[it], 0)];
+                                    }
+#pragma unroll
+                                    for (int it = 0; it < kMaxItems; ++it)
+                                        if (kk[it] < 0) val[it] = 0.f;
+#pragma unroll
+                                    for (int it = 0; it < kMaxItems; ++it) am = fmaxf(am, fabsf(val[it]));
+                                    if (v == DV_P4) DP_STAMP(60);
                                     set_scale(i8, sh, b, am);
+                                    if (v == DV_P4) DP_STAMP(61);
 #pragma unroll
                                     for (int it = 0; it < kMaxItems; ++it) {
                                         const int tl = it * grp + sub;
                                         if (tl < S.ntile) emit(i8, btile + (size_t)(S.base + tl) * kDpBTile, S.base + tl, sh, b, e, val[it]);
                                     }
+                                    if (v == DV_P4) DP_STAMP(62);
                                 } else {
                                     // many tiles (the head): one pass for the magnitude, a second one that recomputes and quantises
 #pragma unroll 1
                                     for (int tl = sub; tl < S.ntile; tl += grp) {
                                         const int kb = S.ntile == kbs ? tl : (S.kb0 + tl) % kbs;
                                         const int k = kb * epb + e;
-                                        if (k < K) am = fmaxf(am, fabsf(input(pi, b, k)));
+                                        if (k < K) am = fmaxf(am, fabsf(input(mixp, b, k)));
                                     }
                                     set_scale(i8, sh, b, am);
 #pragma unroll 1
                                     for (int tl = sub; tl < S.ntile; tl += grp) {
                                         const int kb = S.ntile == kbs ? tl : (S.kb0 + tl) % kbs;
                                         const int k = kb * epb + e;
-                                        emit(i8, btile + (size_t)(S.base + tl) * kDpBTile, S.base + tl, sh, b, e, k < K ? input(pi, b, k) : 0.f);
+                                        emit(i8, btile + (size_t)(S.base + tl) * kDpBTile, S.base + tl, sh, b, e, k < K ? input(mixp, b, k) : 0.f);
                                     }
                                 }
                             }

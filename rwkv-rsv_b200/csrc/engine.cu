@@ -1037,7 +1037,7 @@ bool Model::persistent_available(int nb) {
     if ((C + G - 1) / G + 1 > kDpMaxSlice) return fail("n_embd too large for the persistent kernel's per-CTA slice of the residual stream");
     // shared memory: ring + operand tiles + barriers + worker scratch
     const size_t fixed = (size_t)btiles * kDpBTile + 1024 /*alignment*/ + 2048 /*barriers, small scratch*/ + (size_t)btiles * kDpMaxNB * 8 +
-                         (size_t)cfg.mids() * 4 + 8 * 64 * 4 + (size_t)kDpMaxNB * kDpMaxSlice * 4 + DV_COUNT * sizeof(DpVar) + (size_t)max_units * sizeof(DpUnit);
+                         (size_t)cfg.mids() * 4 + 8 * 64 * 4 + (size_t)kDpMaxNB * kDpMaxSlice * 4 + 2 * sizeof(DpLayer) + DV_COUNT * sizeof(DpVar) + (size_t)max_units * sizeof(DpUnit);
     const size_t budget = 227 * 1024;
     if (fixed + 3 * (size_t)kDpATile > budget) return fail("operand tiles do not fit in shared memory for this shape");
     const int nstages = (int)std::min<size_t>(10, (budget - fixed) / kDpATile);
@@ -1200,6 +1200,7 @@ void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bo
                 if (n) fprintf(stderr, "  att.output phase, all CTAs: %-18s min %.2f avg %.2f max %.2f (CTA %d) [us since CTA 0 entered the phase]\n", nm[k], (mn - p3) / 1e3, sum / 1e3 / n, (mx - p3) / 1e3, amx);
             }
         }
+        fprintf(stderr, "  ffn.key operands: loads start %.2f, values loaded %.2f, scale set %.2f, digits written %.2f\n", (h[63] - t0) / 1e3, (h[60] - t0) / 1e3, (h[61] - t0) / 1e3, (h[62] - t0) / 1e3);
         fprintf(stderr, "  ffn.key phase: producer issued its %lld tiles from %.2f to %.2f; MMA thread started %.2f, last issue %.2f, waited %.2f us for tiles/accumulators\n",
                 h[53], (h[55] - t0) / 1e3, (h[56] - t0) / 1e3, (h[50] - t0) / 1e3, (h[51] - t0) / 1e3, h[52] / 1e3);
     }
