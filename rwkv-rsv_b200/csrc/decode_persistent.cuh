@@ -241,17 +241,18 @@ __device__ __forceinline__ void dp_sum_slots_i8(const uint32_t* d0, const DpRunM
         int i[BATCH][TWO ? 8 : 4];
         float xs[BATCH][TWO ? 2 : 1];
         long long ts[BATCH][TWO ? 2 : 1];
+        // slot indices past the last one are clamped: every load is unconditional, so all of them are in flight together
 #pragma unroll
         for (int k = 0; k < BATCH; ++k) {
-            const bool live = s0 + k < ns;
-            const uint32_t* d = d0 + (size_t)(s0 + k) * (kDpN * 128);
-            const DpRunMeta* ms = mp + (size_t)(s0 + k) * kDpWarps;
+            const int sk = min(s0 + k, ns - 1);
+            const uint32_t* d = d0 + (size_t)sk * (kDpN * 128);
+            const DpRunMeta* ms = mp + (size_t)sk * kDpWarps;
 #pragma unroll
-            for (int j = 0; j < (TWO ? 8 : 4); ++j) i[k][j] = live ? (int)__ldcg(d + j * 128) : 0;
+            for (int j = 0; j < (TWO ? 8 : 4); ++j) i[k][j] = (int)__ldcg(d + j * 128);
 #pragma unroll
             for (int e = 0; e < (TWO ? 2 : 1); ++e) {
-                xs[k][e] = live ? __ldcg(&ms->xscale[b0 + e]) : 0.f;
-                ts[k][e] = live ? __ldcg(&ms->tsum[b0 + e]) : 0;
+                xs[k][e] = __ldcg(&ms->xscale[b0 + e]);
+                ts[k][e] = __ldcg(&ms->tsum[b0 + e]);
             }
         }
 #pragma unroll
@@ -304,13 +305,27 @@ __device__ __noinline__ void dp_finish_subblock(const DpParams& P, const DpRegio
         float xo[kDpMaxNB];
 #pragma unroll
         for (int b = 0; b < kDpMaxNB; ++b) xo[b] = (to_x && mok && b < NB) ? __ldcg(P.x + (size_t)b * P.C + m) : 0.f;
-#pragma unroll 4
-        for (int s = 0; s < ns; ++s) {
-            const uint32_t* d = d0 + (size_t)s * (kDpN * 128);
-            const DpRunMeta* ms = mp + (size_t)s * kDpWarps;
+        for (int s0 = 0; s0 < ns; s0 += 4) {  // four slots' loads in flight (clamped indices, unconditional loads); sums in slot order
+            float hi[4][kDpMaxNB], lo[4][kDpMaxNB], xs[4][kDpMaxNB];
 #pragma unroll
-            for (int b = 0; b < kDpMaxNB; ++b)
-                if (b < NB) acc[b] += (double)__ldcg(&ms->xscale[b]) * (double)(__uint_as_float(__ldcg(d + (2 * b) * 128)) + __uint_as_float(__ldcg(d + (2 * b + 1) * 128)));
+            for (int k = 0; k < 4; ++k) {
+                const int sk = min(s0 + k, ns - 1);
+                const uint32_t* d = d0 + (size_t)sk * (kDpN * 128);
+                const DpRunMeta* ms = mp + (size_t)sk * kDpWarps;
+#pragma unroll
+                for (int b = 0; b < kDpMaxNB; ++b) {
+                    const int bb = min(b, NB - 1);
+                    hi[k][b] = __uint_as_float(__ldcg(d + (2 * bb) * 128));
+                    lo[k][b] = __uint_as_float(__ldcg(d + (2 * bb + 1) * 128));
+                    xs[k][b] = __ldcg(&ms->xscale[bb]);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (s0 + k < ns) {
+#pragma unroll
+                    for (int b = 0; b < kDpMaxNB; ++b) acc[b] += (double)xs[k][b] * (double)(hi[k][b] + lo[k][b]);
+                }
         }
         if (mok) {
 #pragma unroll
@@ -584,6 +599,9 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
         }
     } else if (warp == 1) {
         // =========================== MMA issuer ===========================
+        // One thread issues every MMA of the CTA.  Measured here: a 128 x 16 x 32-byte kind::i8 MMA occupies the tensor pipe for about
+        // 230 cycles whatever its N, and consecutive MMAs do not overlap (separate accumulators or four issuing warps in parallel gave
+        // the same 0.5 us per 16 KB tile), so the issue thread is not the limit: the instruction shape is.
         if (lane == 0) {
             uint32_t it = 0, run = 0, phase_seq = 0;
             bool ok = true;
@@ -1083,7 +1101,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                         for (int ri = 0; ri < nruns; ++ri) {
                             const DpRun r = V.run[ri];
                             const size_t tidx = (size_t)r.tile * Rg.pmax + r.slot;
-                            const bool got = mbar_wait(&acc_full[run & 1], (run >> 1) & 1u, abort_flag);
+                            const bool got = mbar_wait_parked(&acc_full[run & 1], (run >> 1) & 1u, abort_flag);
                             if (!__all_sync(0xffffffffu, got)) break;  // the abort flag is set; decided for all workers below
                             tc_fence_after();
                             uint32_t vv[8], v2[8];

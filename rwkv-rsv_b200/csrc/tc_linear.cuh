@@ -103,6 +103,28 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     *abort_flag = 1;
     return false;
 }
+// The same for warps that expect to wait long (epilogue / worker warps waiting for an accumulator): the try_wait carries a
+// suspend-time hint, so the warp is parked by the hardware instead of re-issuing the instruction back to back and competing
+// with the single MMA-issuing thread of its scheduler for issue slots.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < (kTcSpinLimit >> 6); ++i) {
+        if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+        if ((i & 15u) == 15u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
 __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
                  "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
@@ -362,7 +384,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
             const int tile_first = u - un.kb;                       // unit index of the tile's K block 0
             const int run_end = min(u_end, tile_first + P.kblocks);  // exclusive
             const int slot = (u == tile_first) ? 0 : (blockIdx.x - tc_cta_of_unit(tile_first, U, G));
-            const bool got = mbar_wait(&acc_full[run & 1], (run >> 1) & 1u, abort_flag);
+            const bool got = mbar_wait_parked(&acc_full[run & 1], (run >> 1) & 1u, abort_flag);
             if (!__all_sync(0xffffffffu, got)) break;
             tc_fence_after();
             const int ncols = min(NT, P.ncols - un.nt * NT);
