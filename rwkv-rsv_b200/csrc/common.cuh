@@ -55,4 +55,12 @@ struct SegMeta {
     int start, len, slot, pad;
 };
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may start
+// while its predecessor in the stream still runs; pdl_wait() blocks until that predecessor has completed and its
+// memory is visible, pdl_launch_dependents() allows the successor to be scheduled.  Both are no-ops for a normal
+// launch.  Rule used here: a kernel reads or writes nothing but its parameters and the model's weights (and state that
+// only an earlier step wrote) before pdl_wait().
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 }  // namespace rsv

@@ -37,6 +37,25 @@ struct LaunchScope {
 };
 #define LAUNCH(model, name) if (LaunchScope _ls{model, name}; true)
 
+// Launch with the programmatic-stream-serialization attribute: the kernel may be scheduled while its predecessor in the
+// stream is still running and synchronises with it through pdl_wait().  Only kernels that call pdl_wait() before they
+// touch anything an earlier kernel of the step produces are launched this way.
+template <typename... KArgs, typename... Args>
+static void launch_pdl(Model& m, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = m.stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = m.use_pdl ? 1 : 0;
+    RSV_CUDA(cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...));
+}
+
 static void check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) throw CudaError(std::string("kernel launch failed (") + what + "): " + cudaGetErrorString(e));
@@ -279,6 +298,8 @@ std::unique_ptr<Model> Model::load(const std::string& path, int device) {
         if (*e && *e != '0') m->use_persistent = false;
     if (const char* e = getenv("RSV_NO_GRAPH"))
         if (*e && *e != '0') m->use_graphs = false;
+    if (const char* e = getenv("RSV_NO_PDL"))
+        if (*e && *e != '0') m->use_pdl = false;
     RSV_CUDA(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
     RSV_CUDA(cudaEventCreate(&m->ev0));
     RSV_CUDA(cudaEventCreate(&m->ev1));
@@ -698,10 +719,11 @@ void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, i
         }
         LAUNCH(m, i8 ? "tc_prepare_i8" : "tc_prepare_f16") {
             const dim3 grid(R, (unsigned)regions.size());
+            const dim3 block((size_t)R * regions.size() < 2 * (size_t)m.num_sms ? kPrepThreadsWide : kPrepThreads);
             if (i8)
-                tc_prepare_i8_kernel<kTcDigits><<<grid, kPrepThreads, 0, m.stream>>>(PL);
+                launch_pdl(m, tc_prepare_i8_kernel<kTcDigits>, grid, block, 0, PL);
             else
-                tc_prepare_f16_kernel<<<grid, kPrepThreads, 0, m.stream>>>(PL);
+                launch_pdl(m, tc_prepare_f16_kernel, grid, block, 0, PL);
             check_launch("tc_prepare");
         }
     }
@@ -745,9 +767,9 @@ void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, i
     }
     LAUNCH(m, name) {
         if (i8)
-            tc_linear_kernel<true><<<G, kTcThreads, smem, m.stream>>>(L);
+            launch_pdl(m, tc_linear_kernel<true>, dim3(G), dim3(kTcThreads), smem, L);
         else
-            tc_linear_kernel<false><<<G, kTcThreads, smem, m.stream>>>(L);
+            launch_pdl(m, tc_linear_kernel<false>, dim3(G), dim3(kTcThreads), smem, L);
         check_launch("tc_linear");
     }
 }
@@ -787,6 +809,10 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
     // linear layer before it (x_cur + pending -> x_alt) so that no linear epilogue has to read-modify-write x.
     float *x_cur = ws.x, *x_alt = ws.x2;
     const float* pending = nullptr;
+    // few rows: several CTAs share a row of the LayerNorm + shift kernels (each recomputes the row statistics, then handles a
+    // slice of the channels), so that the step's latency does not hang on R single CTAs
+    // (a thread's channels are handled one after the other, each a dependent round of loads: five CTAs per row keep that to two rounds)
+    const int ln_split = std::max(R <= 512 ? 5 : 1, std::min(10, (2 * num_sms) / std::max(R, 1)));
     const size_t lay_x = (size_t)st.cap * C, lay_s = (size_t)st.cap * H * kHeadSize * kHeadSize;
     for (int l = 0; l < cfg.n_layer; ++l) {
         const LayerW& L = layers[l];
@@ -795,7 +821,7 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
         float* wkv = st.wkv + l * lay_s;
         LAUNCH(*this, "ln_shift6") {
             MixPtrs mp{{L.x_r, L.x_w, L.x_k, L.x_v, L.x_a, L.x_g}};
-            ln_shift_kernel<6><<<R, kRowThreads, 0, stream>>>(x_cur, pending, x_alt, L.ln1_w, L.ln1_b, mp, ws.row_meta, R, C, tmix_x, staging, ws.xmix);
+            launch_pdl(*this, ln_shift_kernel<6>, dim3(R, ln_split), dim3(kRowThreads), 0, x_cur, pending, x_alt, L.ln1_w, L.ln1_b, mp, ws.row_meta, R, C, tmix_x, staging, ws.xmix);
             check_launch("ln_shift6");
         }
         if (pending) {
@@ -803,7 +829,7 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
             pending = nullptr;
         }
         if (staging) LAUNCH(*this, "commit_shift") {
-                commit_shift_kernel<<<S, 256, 0, stream>>>(staging, ws.seg_meta, C, tmix_x);
+                launch_pdl(*this, commit_shift_kernel, dim3(S), dim3(256), 0, staging, ws.seg_meta, C, tmix_x);
                 check_launch("commit_shift");
             }
         float* vgate = l == 0 ? nullptr : ws.xb;  // xb is free until ln_shift1
@@ -833,8 +859,8 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
             run_linear(*this, "linear_rank_back", q2, l == 0 ? 3 : 4, R);
         }
         LAUNCH(*this, "wkv7") {
-            wkv7_kernel<<<dim3(H, S), kWkvThreads, 0, stream>>>(ws.seg_meta, ws.r, ws.k, ws.v, vgate, ws.vfirst, ws.w, ws.a, ws.g, L.k_k, L.k_a, L.r_k,
-                                                                L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C);
+            launch_pdl(*this, wkv7_kernel, dim3(H, S), dim3(kWkvThreads), 0, ws.seg_meta, ws.r, ws.k, ws.v, vgate, ws.vfirst, ws.w, ws.a, ws.g, L.k_k, L.k_a, L.r_k,
+                       L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C);
             check_launch("wkv7");
         }
         {
@@ -844,13 +870,13 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
         }
         LAUNCH(*this, "ln_shift1") {
             MixPtrs mp{{L.ffn_x_k, nullptr, nullptr, nullptr, nullptr, nullptr}};
-            ln_shift_kernel<1><<<R, kRowThreads, 0, stream>>>(x_cur, pending, x_alt, L.ln2_w, L.ln2_b, mp, ws.row_meta, R, C, cmix_x, staging, ws.xb);
+            launch_pdl(*this, ln_shift_kernel<1>, dim3(R, ln_split), dim3(kRowThreads), 0, x_cur, pending, x_alt, L.ln2_w, L.ln2_b, mp, ws.row_meta, R, C, cmix_x, staging, ws.xb);
             check_launch("ln_shift1");
         }
         std::swap(x_cur, x_alt);
         pending = nullptr;
         if (staging) LAUNCH(*this, "commit_shift") {
-                commit_shift_kernel<<<S, 256, 0, stream>>>(staging, ws.seg_meta, C, cmix_x);
+                launch_pdl(*this, commit_shift_kernel, dim3(S), dim3(256), 0, staging, ws.seg_meta, C, cmix_x);
                 check_launch("commit_shift");
             }
         {

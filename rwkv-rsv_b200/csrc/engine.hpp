@@ -143,6 +143,7 @@ struct Model {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr, tev[2] = {nullptr, nullptr};
     long launches = 0;  // kernels launched since the counter was last cleared
     int num_sms = 148;
+    bool use_pdl = true;     // launch the per-layer kernels of the batched path as programmatic dependents (RSV_NO_PDL=1 disables)
     bool use_graphs = true;  // replay self-loop rounds from a captured CUDA graph (RSV_NO_GRAPH=1 disables)
     int tc_min_rows = 5;  // packed steps with at least this many rows use the tensor-core linear path
 

@@ -130,6 +130,8 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_kernel(const float* __re
                                                                const RowMeta* __restrict__ rows, int R, int C, float* __restrict__ shift_state,
                                                                float* __restrict__ staging, float* __restrict__ out) {
     __shared__ float red[kRowThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const RowMeta rm = rows[r];
     const float* xr = x_in + (size_t)r * C;
@@ -137,7 +139,9 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_kernel(const float* __re
     float mean, inv_std, pmean = 0.f, pinv = 0.f;
     row_stats2<kRowThreads>(xr, dr, C, kLnEps, red, mean, inv_std);
     if (rm.has_prev) row_stats2<kRowThreads>(xr - C, dr ? dr - C : nullptr, C, kLnEps, red, pmean, pinv);
-    for (int i = threadIdx.x; i < C; i += kRowThreads) {
+    // gridDim.y CTAs share a row: each has the full-row statistics and writes the channels [c_lo, c_hi)
+    const int c_lo = (int)(((long long)blockIdx.y * C) / gridDim.y), c_hi = (int)(((long long)(blockIdx.y + 1) * C) / gridDim.y);
+    for (int i = c_lo + threadIdx.x; i < c_hi; i += kRowThreads) {
         const float wi = lw[i], bi = lb[i];
         const float xv = dr ? xr[i] + dr[i] : xr[i];
         if (dr) x_out[(size_t)r * C + i] = xv;
@@ -160,6 +164,8 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_kernel(const float* __re
     }
 }
 __global__ void commit_shift_kernel(const float* __restrict__ staging, const SegMeta* __restrict__ segs, int C, float* __restrict__ shift_state) {
+    pdl_launch_dependents();
+    pdl_wait();
     const SegMeta sg = segs[blockIdx.x];
     for (int i = threadIdx.x; i < C; i += blockDim.x) shift_state[(size_t)sg.slot * C + i] = staging[(size_t)blockIdx.x * C + i];
 }
@@ -416,6 +422,9 @@ __global__ void __launch_bounds__(kWkvThreads, 4) wkv7_kernel(const SegMeta* __r
     __shared__ __align__(16) float s_vec[kWkvThreads / 32][5][N];  // per warp: kk, w, b, k~, r
     __shared__ float red_a[kWkvThreads / 32], red_b[kWkvThreads / 32];
     const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, i = tid >> 2, quad = tid & 3;
+    pdl_launch_dependents();
+    // The segment table and this layer's state were last written before the step's first kernel (plan upload, the previous
+    // step's launch of this kernel): they may be read before the predecessor in the stream has finished.
     const SegMeta sg = segs[blockIdx.y];
     float* srow = state + (((size_t)sg.slot * H + h) * N + i) * N + quad * 4;
     float S[16];
@@ -427,6 +436,7 @@ __global__ void __launch_bounds__(kWkvThreads, 4) wkv7_kernel(const SegMeta* __r
         S[4 * jj + 2] = t.z;
         S[4 * jj + 3] = t.w;
     }
+    pdl_wait();
     const int hc = h * N;
     const float kkc0 = k_k[hc + lane], kkc1 = k_k[hc + lane + 32], kac0 = k_a[hc + lane], kac1 = k_a[hc + lane + 32];
     const float rkc0 = r_k[hc + lane], rkc1 = r_k[hc + lane + 32];

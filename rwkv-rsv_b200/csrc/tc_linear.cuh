@@ -317,12 +317,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
+        // The weight tiles of the first ring pass do not depend on the predecessor kernel: they are requested before the
+        // dependency wait, so HBM streams while the predecessor (operand preparation) is still running.  The activation tiles
+        // follow after the wait, on the same barrier.
         if (lane == 0) {
-            uint32_t it = 0;
-            for (int u = u_begin; u < u_end; ++u, ++it) {
+            const int npre = min(NS, u_end - u_begin);
+            for (int j = 0; j < npre; ++j) {
+                const TcUnit un = tc_decode(L, u_begin + j);
+                uint8_t* a_dst = smem + (size_t)j * stage_bytes;
+                mbar_expect_tx(&full[j], stage_bytes);
+                tma_load_2d(&L.amap[un.p], &full[j], a_dst, un.kb * (I8 ? 128 : 64), un.mt * kTcTileM);
+            }
+            pdl_wait();
+            for (int j = 0; j < npre; ++j) {
+                const TcUnit un = tc_decode(L, u_begin + j);
+                uint8_t* b_dst = smem + (size_t)j * stage_bytes + a_bytes;
+                tma_load_2d(&L.bmap[un.p], &full[j], b_dst, un.kb * (I8 ? 128 : 64), un.nt * NT);
+            }
+            uint32_t it = (uint32_t)npre;
+            for (int u = u_begin + npre; u < u_end; ++u, ++it) {
                 const TcUnit un = tc_decode(L, u);
                 const int s = it % NS;
                 const uint32_t par = ((it / NS) & 1u) ^ 1u;  // a fresh barrier passes a wait on parity 1
@@ -372,6 +389,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
         }
     } else {
         // ---------------- epilogue: TMEM -> outputs, or -> partial buffer for tiles cut by a CTA boundary ----------------
+        pdl_wait();  // scales, sums, outputs and partial buffers are shared with the predecessor
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         const int ew = warp - 2, cidx = ew >> 2;  // which of the warps of this lane quarter
         constexpr int kChunkStep = 16 * (kTcEpiWarps / 4);
@@ -507,7 +525,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
 //               tsum[r] = sum_k t_k
 //   fp16 path : hi = fp16(x/e), lo = fp16(x/e - hi) -> B[2r, k], B[2r+1, k]; xscale[r] = e
 // ------------------------------------------------------------------------------------------------
-constexpr int kPrepThreads = 256;
+constexpr int kPrepThreads = 256;       // block size when there are enough rows to fill the GPU
+constexpr int kPrepThreadsWide = 1024;  // few rows: one large block per row keeps the row's latency chain short
+constexpr int kPrepCache = 10;          // elements per thread kept in registers between the two passes
 struct TcPrepRegion {
     const float* x;
     void* B;
@@ -533,27 +553,42 @@ __device__ __forceinline__ float tc_block_max(float amax, float* redf) {
     if ((threadIdx.x & 31) == 0) redf[threadIdx.x >> 5] = amax;
     __syncthreads();
     amax = redf[0];
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) amax = fmaxf(amax, redf[i]);
+    return amax;
+}
+// The first kPrepCache elements of a thread stay in registers (loaded with clamped indices so that all loads are in flight
+// together); longer rows re-read the rest.
+__device__ __forceinline__ float tc_prep_load(const float* xr, int K, float (&xv)[kPrepCache]) {
+    const int nt = blockDim.x;
+    float amax = 0.f;
 #pragma unroll
-    for (int i = 1; i < kPrepThreads / 32; ++i) amax = fmaxf(amax, redf[i]);
+    for (int c = 0; c < kPrepCache; ++c) {
+        const int k = threadIdx.x + c * nt;
+        const float t = xr[min(k, K - 1)];
+        xv[c] = k < K ? t : 0.f;
+        amax = fmaxf(amax, fabsf(xv[c]));
+    }
+    for (int k = threadIdx.x + kPrepCache * nt; k < K; k += nt) amax = fmaxf(amax, fabsf(xr[k]));
     return amax;
 }
 // grid (rows, regions): every activation operand of a launch group is prepared by one kernel
 template <int D>
-__global__ void __launch_bounds__(kPrepThreads) tc_prepare_i8_kernel(const __grid_constant__ TcPrepLaunch L) {
-    __shared__ float redf[kPrepThreads / 32];
-    __shared__ long long redl[kPrepThreads / 32];
+__global__ void __launch_bounds__(kPrepThreadsWide) tc_prepare_i8_kernel(const __grid_constant__ TcPrepLaunch L) {
+    __shared__ float redf[32];
+    __shared__ long long redl[32];
     constexpr int P = 7 * D - 1;
+    pdl_launch_dependents();
+    pdl_wait();
     const TcPrepRegion& G = L.r[blockIdx.y];
-    const int r = blockIdx.x, K = G.K, Kpad = G.Kpad;
+    const int r = blockIdx.x, K = G.K, Kpad = G.Kpad, nt = blockDim.x;
     const float* xr = G.x + (size_t)r * G.ldx;
     int8_t* B = reinterpret_cast<int8_t*>(G.B);
-    float amax = 0.f;
-    for (int k = threadIdx.x; k < K; k += kPrepThreads) amax = fmaxf(amax, fabsf(xr[k]));
-    const int ex = tc_scale_exp(tc_block_max(amax, redf));
+    float xv[kPrepCache];
+    const int ex = tc_scale_exp(tc_block_max(tc_prep_load(xr, K, xv), redf));
     const float inv = ldexpf(1.0f, P - ex);  // 2^P / e, exact
     long long ts = 0;
-    for (int k = threadIdx.x; k < K; k += kPrepThreads) {
-        float v = xr[k] * inv;
+    auto digits = [&](int k, float x) {
+        float v = x * inv;
         v = fminf(fmaxf(v, -(float)(1 << P)), (float)(1 << P));
         int t = __float2int_rn(v);
         if (!(v == v)) t = 0;  // NaN
@@ -568,8 +603,14 @@ __global__ void __launch_bounds__(kPrepThreads) tc_prepare_i8_kernel(const __gri
         d[0] = (int8_t)t;
 #pragma unroll
         for (int j = 0; j < D; ++j) B[((size_t)r * D + j) * Kpad + k] = d[j];
+    };
+#pragma unroll
+    for (int c = 0; c < kPrepCache; ++c) {
+        const int k = threadIdx.x + c * nt;
+        if (k < K) digits(k, xv[c]);
     }
-    for (int k = K + threadIdx.x; k < Kpad; k += kPrepThreads)
+    for (int k = threadIdx.x + kPrepCache * nt; k < K; k += nt) digits(k, xr[k]);
+    for (int k = K + threadIdx.x; k < Kpad; k += nt)
 #pragma unroll
         for (int j = 0; j < D; ++j) B[((size_t)r * D + j) * Kpad + k] = 0;
 #pragma unroll
@@ -578,31 +619,38 @@ __global__ void __launch_bounds__(kPrepThreads) tc_prepare_i8_kernel(const __gri
     __syncthreads();
     if (threadIdx.x == 0) {
         long long t = 0;
-        for (int i = 0; i < kPrepThreads / 32; ++i) t += redl[i];
+        for (int i = 0; i < (nt >> 5); ++i) t += redl[i];
         G.tsum[r] = t;
         G.xscale[r] = ldexpf(1.0f, ex - P);
     }
 }
-__global__ void __launch_bounds__(kPrepThreads) tc_prepare_f16_kernel(const __grid_constant__ TcPrepLaunch L) {
-    __shared__ float redf[kPrepThreads / 32];
+__global__ void __launch_bounds__(kPrepThreadsWide) tc_prepare_f16_kernel(const __grid_constant__ TcPrepLaunch L) {
+    __shared__ float redf[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const TcPrepRegion& G = L.r[blockIdx.y];
-    const int r = blockIdx.x, K = G.K, Kpad = G.Kpad;
+    const int r = blockIdx.x, K = G.K, Kpad = G.Kpad, nt = blockDim.x;
     const float* xr = G.x + (size_t)r * G.ldx;
     __half* B = reinterpret_cast<__half*>(G.B);
-    float amax = 0.f;
-    for (int k = threadIdx.x; k < K; k += kPrepThreads) amax = fmaxf(amax, fabsf(xr[k]));
-    const int ex = tc_scale_exp(tc_block_max(amax, redf));
+    float xv[kPrepCache];
+    const int ex = tc_scale_exp(tc_block_max(tc_prep_load(xr, K, xv), redf));
     const float inv = ldexpf(1.0f, -ex);
-    for (int k = threadIdx.x; k < K; k += kPrepThreads) {
-        float v = xr[k] * inv;
+    auto split = [&](int k, float x) {
+        float v = x * inv;
         v = fminf(fmaxf(v, -1.0f), 1.0f);
         if (!(v == v)) v = 0.f;
         const __half hi = __float2half_rn(v);
         const __half lo = __float2half_rn(v - __half2float(hi));
         B[((size_t)r * 2) * Kpad + k] = hi;
         B[((size_t)r * 2 + 1) * Kpad + k] = lo;
+    };
+#pragma unroll
+    for (int c = 0; c < kPrepCache; ++c) {
+        const int k = threadIdx.x + c * nt;
+        if (k < K) split(k, xv[c]);
     }
-    for (int k = K + threadIdx.x; k < Kpad; k += kPrepThreads) {
+    for (int k = threadIdx.x + kPrepCache * nt; k < K; k += nt) split(k, xr[k]);
+    for (int k = K + threadIdx.x; k < Kpad; k += nt) {
         B[((size_t)r * 2) * Kpad + k] = __float2half_rn(0.f);
         B[((size_t)r * 2 + 1) * Kpad + k] = __float2half_rn(0.f);
     }
