@@ -88,6 +88,12 @@ def algorithmic_bytes(sh, quant, B):
     return w + B * (s_rw + a), w
 
 
+# DRAM traffic of decode_persistent_kernel per decoded token, from one ncu capture of a 4-token launch
+# (dram__bytes_read.sum + dram__bytes_write.sum, divided by 4; summary under profiles/).  Every token streams the same weights,
+# so the traffic of a launch is this figure times its tokens.
+NCU_DRAM_BYTES_PER_TOKEN = {("3b", "int8", 1): (12.431568e9 + 0.664072e9) / 4}
+
+
 def kernel_bytes(sh, quant, B):
     """Algorithmic bytes of one launch of each weight-streaming kernel (weights once + activations in/out)."""
     C, F, V = sh["n_embd"], sh["ffn_hidden"], sh["vocab"]
@@ -337,9 +343,12 @@ def main():
         if launches == 1:
             # the whole timed region was ONE launch of the persistent decode kernel: its duration is the timed region itself
             achieved = step_bytes * K / (ms / 1000.0) / 1e9
+            per_tok = NCU_DRAM_BYTES_PER_TOKEN.get((args.shape, args.quant, B))
+            traffic = per_tok * K if per_tok else None
             roofline = {"bound": "hbm", "kernel": "decode_persistent_kernel", "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                        "frac": achieved / peak, "traffic": None, "bytes_per_launch": step_bytes * K, "ms_per_launch": ms, "share_of_step": 1.0,
-                        "note": "one cooperative launch runs all timed steps; bytes = algorithmic bytes of a decode step x steps",
+                        "frac": achieved / peak, "traffic": traffic, "bytes_per_launch": step_bytes * K, "ms_per_launch": ms, "share_of_step": 1.0,
+                        "note": "one cooperative launch runs all timed steps; bytes = algorithmic bytes of a decode step x steps; "
+                                "traffic = ncu DRAM bytes per token (4-token capture) x steps",
                         "step": {"bytes": step_bytes, "achieved": achieved, "frac": achieved / peak}, "multi_kernel_path": kernels}
         else:
             dom = max(prof.items(), key=lambda kv: kv[1]["ms"])
