@@ -599,13 +599,13 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
         }
     } else if (warp == 1) {
         // =========================== MMA issuer ===========================
-        // One thread issues every MMA of the CTA.  Measured here: a 128 x 16 x 32-byte kind::i8 MMA occupies the tensor pipe for about
-        // 230 cycles whatever its N, and consecutive MMAs do not overlap (separate accumulators or four issuing warps in parallel gave
-        // the same 0.5 us per 16 KB tile), so the issue thread is not the limit: the instruction shape is.
-        if (lane == 0) {
-            uint32_t it = 0, run = 0, phase_seq = 0;
+        // The whole warp runs this loop convergently and one elected lane issues (see tc_mma_elect): operands stay warp-uniform,
+        // ring slot and parity are counters instead of divisions.  Per 16 KB tile: one barrier wait, four MMAs, one commit.
+        {
+            uint32_t slot_i = 0, slot_par = 0, run = 0, phase_seq = 0;
             bool ok = true;
             const uint32_t idesc_i8 = tc_idesc(true, kDpN), idesc_f16 = tc_idesc(false, kDpN);
+            const uint32_t ring_addr = smem_u32(ring), btile_addr = smem_u32(btile);
             for (int t = 0; t < P.n_tokens && ok; ++t) {
                 const bool do_head = P.argmax_feed || t == P.n_tokens - 1;
                 for (int l = 0; l <= P.L && ok; ++l) {
@@ -614,49 +614,52 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                         const int v = l == P.L ? DV_HEAD : (phs == 0 ? (l == 0 ? DV_P1A : DV_P1B) : DV_P3 + phs - 1);
                         const DpVar& V = vars[v];
                         const DpUnit* un = units + V.unit0;
-                        ok = mbar_wait(b_ready, phase_seq & 1u, abort_flag);
+                        const int nunits = V.nunits;
+                        ok = __all_sync(0xffffffffu, mbar_wait(b_ready, phase_seq & 1u, abort_flag));
                         ++phase_seq;
                         if (!ok) break;
                         tc_fence_after();
                         const bool dbg_here = P.dbg && cta == 0 && t == 1 && l == 1 && v == DV_P4;
-                        long long twait = 0;
-                        if (dbg_here) P.dbg[50] = dp_now();
-                        for (int i = 0; i < V.nunits; ++i, ++it) {
+                        if (dbg_here && lane == 0) P.dbg[50] = dp_now();
+                        for (int i = 0; i < nunits; ++i) {
                             const DpUnit e = un[i];
-                            const long long tw0 = dbg_here ? dp_now() : 0;
                             if (e.flags & 1) {
-                                ok = mbar_wait(&acc_empty[run & 1], (((run >> 1) & 1u) ^ 1u), abort_flag);
+                                ok = __all_sync(0xffffffffu, mbar_wait(&acc_empty[run & 1], (((run >> 1) & 1u) ^ 1u), abort_flag));
                                 if (!ok) break;
                                 tc_fence_after();
                             }
-                            const int s = it % NS;
-                            ok = mbar_wait(&full[s], (it / NS) & 1u, abort_flag);
+                            ok = __all_sync(0xffffffffu, mbar_wait(&full[slot_i], slot_par, abort_flag));
                             if (!ok) break;
-                            if (dbg_here) twait += dp_now() - tw0;
                             tc_fence_after();
-                            const uint64_t adesc = tc_smem_desc(smem_u32(ring + (size_t)s * kDpATile));
-                            const uint64_t bdesc = tc_smem_desc(smem_u32(btile + (size_t)e.btile * kDpBTile));
-                            // The four 32-byte K sub-blocks of a tile accumulate into four separate accumulators (summed when
-                            // the run is drained): back-to-back MMAs into one accumulator would serialise on its latency.
+                            const uint64_t adesc = tc_smem_desc(ring_addr + slot_i * (uint32_t)kDpATile);
+                            const uint64_t bdesc = tc_smem_desc(btile_addr + (uint32_t)e.btile * (uint32_t)kDpBTile);
+                            // The four 32-byte K sub-blocks of a tile accumulate into four separate accumulators (summed when the run
+                            // is drained), so no MMA waits for the previous one's result.
                             const uint32_t d_tmem = tmem_base + (run & 1) * (4 * kDpN);
                             const uint32_t acc0 = (e.flags & 1) ? 0u : 1u;
                             if (e.flags & 4) {
 #pragma unroll
-                                for (int k4 = 0; k4 < 4; ++k4) tc_mma<true>(d_tmem + k4 * kDpN, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc_i8, acc0);
+                                for (int k4 = 0; k4 < 4; ++k4)
+                                    tc_mma_elect<true>(d_tmem + k4 * kDpN, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc_i8, acc0);
                             } else {
 #pragma unroll
-                                for (int k4 = 0; k4 < 4; ++k4) tc_mma<false>(d_tmem + k4 * kDpN, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc_f16, acc0);
+                                for (int k4 = 0; k4 < 4; ++k4)
+                                    tc_mma_elect<false>(d_tmem + k4 * kDpN, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc_f16, acc0);
                             }
-                            tc_commit(&empty[s]);
+                            tc_commit_elect(&empty[slot_i]);
                             if (e.flags & 2) {
-                                tc_commit(&acc_full[run & 1]);
+                                tc_commit_elect(&acc_full[run & 1]);
                                 ++run;
                             }
+                            if (++slot_i == (uint32_t)NS) {
+                                slot_i = 0;
+                                slot_par ^= 1u;
+                            }
                         }
-                        if (dbg_here) {
+                        if (dbg_here && lane == 0) {
                             P.dbg[51] = dp_now();
-                            P.dbg[52] = twait;
-                            P.dbg[53] = V.nunits;
+                            P.dbg[52] = 0;
+                            P.dbg[53] = nunits;
                         }
                     }
                 }
