@@ -234,6 +234,35 @@ __device__ __forceinline__ TcUnit tc_decode(const TcLaunch& L, int u) {
     r.tile = P.tile0 + t;
     return r;
 }
+// Walks consecutive units without divisions (the decode above costs two integer divisions per unit).
+struct TcWalk {
+    int p, mt, nt, kb, kblocks, n_tiles, prob_end;
+    __device__ __forceinline__ void start(const TcLaunch& L, int u) {
+        const TcUnit un = tc_decode(L, u);
+        p = un.p;
+        mt = un.mt;
+        nt = un.nt;
+        kb = un.kb;
+        kblocks = L.p[p].kblocks;
+        n_tiles = L.p[p].n_tiles;
+        prob_end = p + 1 < L.nprob ? L.p[p + 1].unit0 : L.total_units;
+    }
+    // moves from unit u to u + 1
+    __device__ __forceinline__ void next(const TcLaunch& L, int u) {
+        if (++kb < kblocks) return;
+        kb = 0;
+        if (u + 1 == prob_end && p + 1 < L.nprob) {
+            ++p;
+            mt = nt = 0;
+            kblocks = L.p[p].kblocks;
+            n_tiles = L.p[p].n_tiles;
+            prob_end = p + 1 < L.nprob ? L.p[p + 1].unit0 : L.total_units;
+        } else if (++nt == n_tiles) {
+            nt = 0;
+            ++mt;
+        }
+    }
+};
 // CTA c owns units [c*U/G, (c+1)*U/G).  Partial slot of a run = how many CTA boundaries lie inside the tile before it.
 __host__ __device__ __forceinline__ int tc_cta_begin(int c, int U, int G) { return (int)(((long long)c * U) / G); }
 __host__ __device__ __forceinline__ int tc_cta_of_unit(int u, int U, int G) { return (int)((((long long)u + 1) * G - 1) / U); }
@@ -350,68 +379,81 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
         // The weight tiles of the first ring pass do not depend on the predecessor kernel: they are requested before the
         // dependency wait, so HBM streams while the predecessor (operand preparation) is still running.  The activation tiles
         // follow after the wait, on the same barrier.
-        if (lane == 0) {
+        if (lane == 0 && u_begin < u_end) {
             const int npre = min(NS, u_end - u_begin);
+            TcWalk w;
+            w.start(L, u_begin);
             for (int j = 0; j < npre; ++j) {
-                const TcUnit un = tc_decode(L, u_begin + j);
                 uint8_t* a_dst = smem + (size_t)j * stage_bytes;
                 mbar_expect_tx(&full[j], stage_bytes);
-                tma_load_2d(&L.amap[un.p], &full[j], a_dst, un.kb * (I8 ? 128 : 64), un.mt * kTcTileM);
+                tma_load_2d(&L.amap[w.p], &full[j], a_dst, w.kb * (I8 ? 128 : 64), w.mt * kTcTileM);
+                w.next(L, u_begin + j);
             }
             pdl_wait();
+            w.start(L, u_begin);
             for (int j = 0; j < npre; ++j) {
-                const TcUnit un = tc_decode(L, u_begin + j);
                 uint8_t* b_dst = smem + (size_t)j * stage_bytes + a_bytes;
-                tma_load_2d(&L.bmap[un.p], &full[j], b_dst, un.kb * (I8 ? 128 : 64), un.nt * NT);
+                tma_load_2d(&L.bmap[w.p], &full[j], b_dst, w.kb * (I8 ? 128 : 64), w.nt * NT);
+                w.next(L, u_begin + j);
             }
-            uint32_t it = (uint32_t)npre;
-            for (int u = u_begin + npre; u < u_end; ++u, ++it) {
-                const TcUnit un = tc_decode(L, u);
-                const int s = it % NS;
-                const uint32_t par = ((it / NS) & 1u) ^ 1u;  // a fresh barrier passes a wait on parity 1
+            // w now stands on unit u_begin + npre
+            int s = npre == NS ? 0 : npre;
+            uint32_t par = npre == NS ? 0u : 1u;  // parity to wait for on empty[s]: a fresh barrier passes a wait on parity 1
+            for (int u = u_begin + npre; u < u_end; ++u) {
                 if (!mbar_wait(&empty[s], par, abort_flag)) break;
                 uint8_t* a_dst = smem + (size_t)s * stage_bytes;
                 uint8_t* b_dst = a_dst + a_bytes;
                 mbar_expect_tx(&full[s], stage_bytes);
-                const int kelem = un.kb * (I8 ? 128 : 64);
-                tma_load_2d(&L.amap[un.p], &full[s], a_dst, kelem, un.mt * kTcTileM);
-                tma_load_2d(&L.bmap[un.p], &full[s], b_dst, kelem, un.nt * NT);
+                const int kelem = w.kb * (I8 ? 128 : 64);
+                tma_load_2d(&L.amap[w.p], &full[s], a_dst, kelem, w.mt * kTcTileM);
+                tma_load_2d(&L.bmap[w.p], &full[s], b_dst, kelem, w.nt * NT);
+                w.next(L, u);
+                if (++s == NS) {
+                    s = 0;
+                    par ^= 1u;
+                }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // The warp runs this loop convergently; one elected lane issues (see tc_mma_elect).
+        if (u_begin < u_end) {
             const uint32_t idesc = tc_idesc(I8, NT);
-            uint32_t it = 0, run = 0;
-            int prev_tile = -1;
-            bool ok = true;
-            for (int u = u_begin; u < u_end && ok; ++u, ++it) {
-                const TcUnit un = tc_decode(L, u);
-                const bool first = un.tile != prev_tile;
+            const uint32_t smem_addr = smem_u32(smem);
+            uint32_t run = 0, s = 0, par = 0;
+            bool ok = true, started = false;
+            TcWalk w;
+            w.start(L, u_begin);
+            for (int u = u_begin; u < u_end; ++u) {
+                const bool first = w.kb == 0 || u == u_begin;
                 if (first) {
-                    if (prev_tile >= 0) {
-                        tc_commit(&acc_full[run & 1]);  // previous run complete -> epilogue
+                    if (started) {
+                        tc_commit_elect(&acc_full[run & 1]);  // previous run complete -> epilogue
                         ++run;
                     }
                     // accumulator buffer (run & 1) must have been drained (its use number is run >> 1)
-                    ok = mbar_wait(&acc_empty[run & 1], (((run >> 1) & 1u) ^ 1u), abort_flag);
+                    ok = __all_sync(0xffffffffu, mbar_wait(&acc_empty[run & 1], (((run >> 1) & 1u) ^ 1u), abort_flag));
                     if (!ok) break;
                     tc_fence_after();
-                    prev_tile = un.tile;
+                    started = true;
                 }
-                const int s = it % NS;
-                ok = mbar_wait(&full[s], (it / NS) & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, mbar_wait(&full[s], par, abort_flag));
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
+                const uint32_t a_addr = smem_addr + s * stage_bytes;
                 const uint64_t adesc = tc_smem_desc(a_addr), bdesc = tc_smem_desc(a_addr + a_bytes);
                 const uint32_t d_tmem = tmem_base + (run & 1) * NT;
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4)  // 4 x 32 bytes of K per 128-byte block; +2 = 32 bytes in 16-byte units
-                    tc_mma<I8>(d_tmem, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (first && k4 == 0) ? 0u : 1u);
-                tc_commit(&empty[s]);  // stage may be refilled once these MMAs have read it
+                    tc_mma_elect<I8>(d_tmem, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (first && k4 == 0) ? 0u : 1u);
+                tc_commit_elect(&empty[s]);  // stage may be refilled once these MMAs have read it
+                w.next(L, u);
+                if (++s == (uint32_t)NS) {
+                    s = 0;
+                    par ^= 1u;
+                }
             }
-            if (ok && prev_tile >= 0) tc_commit(&acc_full[run & 1]);
+            if (ok && started) tc_commit_elect(&acc_full[run & 1]);
         }
     } else {
         // ---------------- epilogue: TMEM -> outputs, or -> partial buffer for tiles cut by a CTA boundary ----------------
