@@ -104,6 +104,24 @@ def test_seq_chunked_and_token_paths_agree(bundles, oracles, name):
     assert np.abs(s_tok - s_seq).max() <= 1e-4
 
 
+@pytest.mark.parametrize("name", ["int8", "fp16"])
+def test_long_prompt_single_chunk(bundles, oracles, name):
+    # 700 rows in one step: the large-row variants of the LayerNorm / operand-preparation kernels and many N tiles per GEMM
+    b, o = bundles[name], oracles[name]
+    toks = np.random.default_rng(7).integers(0, 4096, size=700).astype(np.uint32)
+    o.reset()
+    want = o.forward(toks)
+    b.reset()
+    got = b.infer_seq(toks)
+    assert rmse(got, want) <= RMSE_TOL and int(got.argmax()) == int(want.argmax())
+    so, sg = o.state_back(), b.state_back()
+    assert np.abs(sg - so).max() <= 1e-4 * max(1.0, float(np.abs(so).max()))
+    # the same prompt in chunks of 256 reaches the same state
+    b.reset()
+    b.infer_chunked(toks, 256)
+    assert np.abs(b.state_back() - sg).max() <= 1e-4 * max(1.0, float(np.abs(sg).max()))
+
+
 def test_state_roundtrip_bit_exact_and_reset(bundles):
     # examples/state_persist.rs:54-67: back -> load -> back must give max_diff == 0
     b = bundles["int8"]
