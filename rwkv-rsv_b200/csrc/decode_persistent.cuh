@@ -142,6 +142,21 @@ __device__ __forceinline__ long long dp_now() {
         if (P.dbg && cta == 0 && wtid == 0 && t == 1 && l == 1) P.dbg[id] = dp_now(); \
     } while (0)
 
+// Number of CTAs that take part in a phase of `n` problems with `unit0[i]` = first unit of problem i and U units in all.
+// Normally min(G, U).  A CTA whose range straddles two problems has to build two sets of activation operands one after the
+// other and everybody waits for it at the barrier; so when a slightly smaller count (>= 85 % of G) gives every CTA the same
+// number of units q with every problem boundary on a multiple of q, that count is used: no CTA straddles.
+__host__ __device__ inline int dp_choose_ge(const int* unit0, int n, int U, int G) {
+    const int ge = G < U ? G : U;
+    if (n <= 1 || U <= G) return ge;
+    for (int q = (U + G - 1) / G; (U / q) * 100 >= G * 85; ++q) {
+        if (U % q) continue;
+        bool aligned = true;
+        for (int i = 1; i < n; ++i) aligned = aligned && (unit0[i] % q == 0);
+        if (aligned) return U / q;
+    }
+    return ge;
+}
 __device__ __forceinline__ int dp_cta_begin(int c, int U, int ge) { return (int)(((unsigned)c * (unsigned)U) / (unsigned)ge); }
 __device__ __forceinline__ int dp_cta_of(int u, int U, int ge) { return (int)((((unsigned)u + 1u) * (unsigned)ge - 1u) / (unsigned)U); }
 
@@ -393,7 +408,7 @@ __device__ void dp_build_variant(const DpParams& P, int v, int cta, int G, DpVar
         T += mt.mtiles;
     }
     V.U = U;
-    V.ge = min(G, U);  // only the first min(G, U) CTAs take part: the CTAs sharing a tile are consecutive
+    V.ge = dp_choose_ge(V.p_unit0, n, U, G);  // only the first ge CTAs take part: the CTAs sharing a tile are consecutive
     V.unit0 = unit_cursor;
     V.nunits = V.nruns = V.nshares = 0;
     if (cta >= V.ge) return;

@@ -930,8 +930,12 @@ struct PhaseShape {
 PhaseShape phase_shape(const std::vector<HostProb>& probs, int G) {
     PhaseShape ps;
     int U = 0;
-    for (auto& q : probs) U += q.mtiles * q.kblocks;
-    G = std::min(G, U);  // only the first min(G, U) CTAs take part in a phase
+    std::vector<int> unit0;
+    for (auto& q : probs) {
+        unit0.push_back(U);
+        U += q.mtiles * q.kblocks;
+    }
+    G = dp_choose_ge(unit0.data(), (int)unit0.size(), U, G);  // CTAs that take part in the phase (same rule as on the device)
     int u0 = 0;
     for (auto& q : probs) {
         for (int t = 0; t < q.mtiles; ++t) {
