@@ -859,8 +859,21 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
             run_linear(*this, "linear_rank_back", q2, l == 0 ? 3 : 4, R);
         }
         LAUNCH(*this, "wkv7") {
-            launch_pdl(*this, wkv7_kernel, dim3(H, S), dim3(kWkvThreads), 0, ws.seg_meta, ws.r, ws.k, ws.v, vgate, ws.vfirst, ws.w, ws.a, ws.g, L.k_k, L.k_a, L.r_k,
-                       L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C);
+            const int n_items = H * S;
+            if (n_items >= 4 * num_sms) {
+                // many (session, head) pairs: persistent CTAs with the state staged through shared memory
+                const size_t smem = (size_t)kWkvStages * kHeadSize * kHeadSize * sizeof(float);
+                static bool configured[16] = {false};
+                if (!configured[device & 15]) {
+                    RSV_CUDA(cudaFuncSetAttribute(wkv7_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                    configured[device & 15] = true;
+                }
+                launch_pdl(*this, wkv7_staged_kernel, dim3(std::min(n_items, 3 * num_sms)), dim3(kWkvThreads), smem, ws.seg_meta, n_items, ws.r, ws.k, ws.v, vgate,
+                           ws.vfirst, ws.w, ws.a, ws.g, L.k_k, L.k_a, L.r_k, L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C, ws.status);
+            } else {
+                launch_pdl(*this, wkv7_kernel, dim3(H, S), dim3(kWkvThreads), 0, ws.seg_meta, ws.r, ws.k, ws.v, vgate, ws.vfirst, ws.w, ws.a, ws.g, L.k_k, L.k_a,
+                           L.r_k, L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C);
+            }
             check_launch("wkv7");
         }
         {
@@ -1242,6 +1255,7 @@ void Model::check_status() {
     RSV_CUDA(cudaStreamSynchronize(stream));
     if (s) {
         RSV_CUDA(cudaMemsetAsync(ws.status, 0, sizeof(int), stream));
+        if (s & 16) throw std::runtime_error("WKV kernel gave up waiting for a staged state (device status bit 4)");
         if (s & 8) throw std::runtime_error("persistent decode kernel: schedule tables too small for this shape (device status bit 3)");
         if (s & 4) throw std::runtime_error("persistent decode kernel gave up waiting on a barrier (device status bit 2)");
         if (s & 2) throw std::runtime_error("tensor-core kernel gave up waiting on a barrier (device status bit 1)");

@@ -219,6 +219,24 @@ def test_batch_equals_single(bundles, tiny_paths):
         assert list(b.infer_sample_selfloop(int(prompts[i][-1]), 8, sp)) == list(got[i])
 
 
+def test_many_sessions_equal_single(bundles):
+    # 96 sessions x 8 heads: the persistent, shared-memory-staged form of the WKV-7 kernel (ragged prefill with multi-token
+    # segments, then decode steps with one-token segments); every session must match its single-session run
+    b = bundles["int8"]
+    m = b.model
+    rng = np.random.default_rng(11)
+    prompts = [rng.integers(0, 4096, size=int(n)).astype(np.uint32) for n in rng.integers(1, 9, size=96)]
+    B, n = len(prompts), 5
+    st = m.create_batch_state(B)
+    seeds = m.forward_seq_batch(st, prompts)
+    out = m.collect_sample_selfloop_batch(m.submit_sample_selfloop_batch(st, seeds, n, None))
+    for i in (0, 1, 17, 40, 63, 95):
+        b.reset()
+        b.infer_seq(prompts[i])
+        assert list(b.infer_argmax_selfloop(int(prompts[i][-1]), n)) == list(out[i]), i
+        assert np.abs(st.slot_back(i) - b.state_back()).max() <= 1e-4, i
+
+
 def test_error_paths(bundles, tiny_paths):
     b = bundles["fp16"]
     with pytest.raises(rsv.RsvError, match="vocab"):
