@@ -8,6 +8,7 @@
 #include "safetensors.hpp"
 #include "tc_linear.cuh"
 #include "decode_persistent.cuh"
+#include "wkv_rows.cuh"
 
 namespace rsv {
 
@@ -120,6 +121,16 @@ void encode_kmajor_map(CUtensorMap* map, bool i8, void* base, size_t rows, size_
                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) throw CudaError("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+}
+// All layers' WKV states of a State as one row-major fp32 tensor [rows][64]; box = 32 columns x 64 rows with the 128-byte swizzle.
+void encode_state_map(CUtensorMap* map, float* base, size_t rows) {
+    cuuint64_t dims[2] = {64, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {64 * sizeof(float)};
+    cuuint32_t box[2] = {32, 64};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw CudaError("cuTensorMapEncodeTiled (state) failed with code " + std::to_string((int)r));
 }
 inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -861,15 +872,23 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
         LAUNCH(*this, "wkv7") {
             const int n_items = H * S;
             if (n_items >= 4 * num_sms) {
-                // many (session, head) pairs: persistent CTAs with the state staged through shared memory
-                const size_t smem = (size_t)kWkvStages * kHeadSize * kHeadSize * sizeof(float);
+                // many (session, head) pairs: one state row per lane, states staged by TMA (wkv_rows.cuh)
+                const size_t rows_total = (size_t)cfg.n_layer * st.cap * H * kHeadSize;
+                if (rows_total >= (1ull << 31)) throw std::runtime_error("state too large for the 32-bit row coordinate of its tensor map");
+                if (!st.wkv_map_ok) {
+                    encode_state_map(&st.wkv_map, st.wkv, rows_total);
+                    st.wkv_map_ok = true;
+                }
                 static bool configured[16] = {false};
                 if (!configured[device & 15]) {
-                    RSV_CUDA(cudaFuncSetAttribute(wkv7_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                    RSV_CUDA(cudaFuncSetAttribute(wkv7_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWrSmemBytes));
                     configured[device & 15] = true;
                 }
-                launch_pdl(*this, wkv7_staged_kernel, dim3(std::min(n_items, 3 * num_sms)), dim3(kWkvThreads), smem, ws.seg_meta, n_items, ws.r, ws.k, ws.v, vgate,
-                           ws.vfirst, ws.w, ws.a, ws.g, L.k_k, L.k_a, L.r_k, L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C, ws.status);
+                if (C % 64) throw std::runtime_error("n_embd must be a multiple of 64");
+                const int ctas = std::min((n_items + kWrPairs - 1) / kWrPairs, num_sms);
+                launch_pdl(*this, wkv7_rows_kernel, dim3(ctas), dim3(kWrThreads), kWrSmemBytes, st.wkv_map, (long long)l * st.cap * H * kHeadSize, ws.seg_meta,
+                           n_items, ws.r, ws.k, ws.v, vgate, ws.vfirst, ws.w, ws.a, ws.g, L.k_k, L.k_a, L.r_k, L.lnx_w, L.lnx_b,
+                           l == 0 ? st.v_first : nullptr, ws.yg, H, C, ws.status);
             } else {
                 launch_pdl(*this, wkv7_kernel, dim3(H, S), dim3(kWkvThreads), 0, ws.seg_meta, ws.r, ws.k, ws.v, vgate, ws.vfirst, ws.w, ws.a, ws.g, L.k_k, L.k_a,
                            L.r_k, L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C);

@@ -106,6 +106,8 @@ struct State {
     Model* model = nullptr;
     int64_t cap = 0;
     float *tmix_x = nullptr, *wkv = nullptr, *cmix_x = nullptr, *v_first = nullptr;
+    CUtensorMap wkv_map;      // all layers' WKV states as one 2-D tensor [layers x slots x heads x 64][64] fp32 (TMA boxes of 64 rows x 32 columns)
+    bool wkv_map_ok = false;  // encoded on first use
     ~State();
 };
 

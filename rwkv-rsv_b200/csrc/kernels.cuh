@@ -517,15 +517,8 @@ __global__ void __launch_bounds__(kWkvThreads, 4) wkv7_kernel(const SegMeta* __r
     for (int jj = 0; jj < 4; ++jj) *reinterpret_cast<float4*>(srow + 16 * jj) = make_float4(S[4 * jj], S[4 * jj + 1], S[4 * jj + 2], S[4 * jj + 3]);
 }
 
-// ---- the same update for many (session, head) pairs: persistent CTAs, state staged through shared memory ----
-// With thousands of items the per-CTA form above is bound by its own latency chain (load 16 KB, compute, store) at four CTAs
-// per SM.  Here every CTA walks items blockIdx.x, blockIdx.x + gridDim.x, ...; the 16 KB state of the item after next
-// arrives by a bulk copy (cp.async.bulk + mbarrier) while the current one is updated, the updated state leaves by a bulk
-// store, and the first token's inputs of the next item are requested into registers one item ahead.  Rows are read from the
-// staged copy with the 16-byte chunk order rotated by one on odd rows, so the two rows of a quarter-warp do not meet in the
-// same banks.  All barrier waits are bounded; on expiry bit 16 of the status word is set and the CTA stops.
-constexpr int kWkvStages = 3;
-constexpr uint32_t kWkvSpin = 1u << 24;
+// The per-token inputs of one lane (two of the 64 channels, and the row's v and g), shared with the row-per-lane kernel for large
+// batches (wkv_rows.cuh).
 struct WkvIn {
     float k0, k1, a0, a1, r0, r1, w0, w1, v, g;
 };
@@ -546,184 +539,6 @@ __device__ __forceinline__ WkvIn wkv_load_inputs(const float* __restrict__ r, co
     if (vgate) x.v = x.v + vgate[hb + i] * (vfirst[hb + i] - x.v);
     return x;
 }
-__global__ void __launch_bounds__(kWkvThreads, 3) wkv7_staged_kernel(const SegMeta* __restrict__ segs, int n_items, const float* __restrict__ r,
-                                                                     const float* __restrict__ k, const float* __restrict__ v,
-                                                                     const float* __restrict__ vgate, const float* __restrict__ vfirst,
-                                                                     const float* __restrict__ w, const float* __restrict__ a, const float* __restrict__ g,
-                                                                     const float* __restrict__ k_k, const float* __restrict__ k_a,
-                                                                     const float* __restrict__ r_k, const float* __restrict__ lnx_w,
-                                                                     const float* __restrict__ lnx_b, float* __restrict__ state,
-                                                                     float* __restrict__ v_first_state, float* __restrict__ yg, int H, int C, int* status) {
-    constexpr int N = kHeadSize;
-    extern __shared__ __align__(128) float wkv_stage[];  // [kWkvStages][N * N]
-    __shared__ __align__(16) float s_vec[kWkvThreads / 32][5][N];
-    __shared__ float red_a[kWkvThreads / 32], red_b[kWkvThreads / 32];
-    __shared__ __align__(8) uint64_t full[kWkvStages];
-    __shared__ int s_abort;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, i = tid >> 2, quad = tid & 3, rot = i & 1;
-    const int my_items = n_items > (int)blockIdx.x ? (n_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-    auto item_of = [&](int n) { return (int)blockIdx.x + n * (int)gridDim.x; };
-    auto state_of = [&](int item) {
-        const SegMeta sg = segs[item / H];
-        return state + ((size_t)sg.slot * H + (item % H)) * (N * N);
-    };
-    if (tid == 0) {
-        for (int s = 0; s < kWkvStages; ++s) {
-            const uint32_t b = (uint32_t)__cvta_generic_to_shared(&full[s]);
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b));
-        }
-        s_abort = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    pdl_launch_dependents();
-    auto issue_load = [&](int n) {  // thread 0 only
-        const int st = n % kWkvStages;
-        const uint32_t b = (uint32_t)__cvta_generic_to_shared(&full[st]);
-        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(wkv_stage + (size_t)st * N * N);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"((uint32_t)(N * N * 4)) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(state_of(item_of(n))),
-                     "r"((uint32_t)(N * N * 4)), "r"(b)
-                     : "memory");
-    };
-    // the segment table and the states were written before this step's first kernel: they may be read ahead of the dependency wait
-    if (tid == 0)
-        for (int n = 0; n < min(kWkvStages - 1, my_items); ++n) issue_load(n);
-    pdl_wait();
-    WkvIn nxt;
-    if (my_items > 0) {
-        const int item = item_of(0);
-        nxt = wkv_load_inputs(r, k, v, vgate, vfirst, w, a, g, (size_t)segs[item / H].start * C + (size_t)(item % H) * N, lane, i);
-    }
-    float(*sv)[N] = s_vec[warp];
-    for (int n = 0; n < my_items; ++n) {
-        const int item = item_of(n), h = item % H, st = n % kWkvStages;
-        const SegMeta sg = segs[item / H];
-        const int hc = h * N;
-        if (tid == 0 && n + kWkvStages - 1 < my_items) {
-            // the stage of item n + 2 was last used by item n - 1: its bulk store must have finished reading shared memory
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-            issue_load(n + kWkvStages - 1);
-        }
-        const float kkc0 = k_k[hc + lane], kkc1 = k_k[hc + lane + 32], kac0 = k_a[hc + lane], kac1 = k_a[hc + lane + 32];
-        const float rkc0 = r_k[hc + lane], rkc1 = r_k[hc + lane + 32];
-        const float gw = lnx_w[hc + i], gb = lnx_b[hc + i];
-        WkvIn cur = nxt;
-        if (n + 1 < my_items) {
-            const int it2 = item_of(n + 1);
-            nxt = wkv_load_inputs(r, k, v, vgate, vfirst, w, a, g, (size_t)segs[it2 / H].start * C + (size_t)(it2 % H) * N, lane, i);
-        }
-        // wait for this item's state
-        {
-            const uint32_t b = (uint32_t)__cvta_generic_to_shared(&full[st]);
-            const uint32_t parity = (uint32_t)(n / kWkvStages) & 1u;
-            bool ok = false;
-            for (uint32_t spin = 0; spin < kWkvSpin; ++spin) {
-                uint32_t done;
-                asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(done) : "r"(b), "r"(parity) : "memory");
-                if (done) {
-                    ok = true;
-                    break;
-                }
-                if ((spin & 1023u) == 1023u && s_abort) break;
-            }
-            if (!ok) s_abort = 1;
-            if (__syncthreads_or(!ok)) {  // uniform decision for the CTA
-                if (tid == 0) atomicOr(status, 16);
-                break;
-            }
-        }
-        float* srow = wkv_stage + (size_t)st * N * N + i * N + quad * 4;
-        float S[16];
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-            const float4 t4 = *reinterpret_cast<const float4*>(srow + 16 * ((jj + rot) & 3));
-            S[4 * jj] = t4.x;
-            S[4 * jj + 1] = t4.y;
-            S[4 * jj + 2] = t4.z;
-            S[4 * jj + 3] = t4.w;
-        }
-        for (int t = 0; t < sg.len; ++t) {
-            const size_t hb = (size_t)(sg.start + t) * C + hc;
-            if (t > 0) cur = wkv_load_inputs(r, k, v, vgate, vfirst, w, a, g, hb, lane, i);
-            const float vj = cur.v;
-            const float kk0 = cur.k0 * kkc0, kk1 = cur.k1 * kkc1;
-            const float ss = warp_sum(kk0 * kk0 + kk1 * kk1);
-            const float inv = 1.0f / fmaxf(sqrtf(ss), kL2Eps);
-            const float kh0 = kk0 * inv, kh1 = kk1 * inv;
-            const float kt0 = cur.k0 + kac0 * (cur.k0 * cur.a0 - cur.k0), kt1 = cur.k1 + kac1 * (cur.k1 * cur.a1 - cur.k1);
-            const float srk = warp_sum(cur.r0 * kt0 * rkc0 + cur.r1 * kt1 * rkc1);
-            __syncwarp();  // the previous token's readers are done with sv
-            sv[0][lane] = kh0;
-            sv[0][lane + 32] = kh1;
-            sv[1][lane] = cur.w0;
-            sv[1][lane + 32] = cur.w1;
-            sv[2][lane] = kh0 * (-cur.a0);
-            sv[2][lane + 32] = kh1 * (-cur.a1);
-            sv[3][lane] = kt0;
-            sv[3][lane + 32] = kt1;
-            sv[4][lane] = cur.r0;
-            sv[4][lane + 32] = cur.r1;
-            __syncwarp();
-            float sa = 0.f;
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-                const float4 kk4 = *reinterpret_cast<const float4*>(&sv[0][16 * ((jj + rot) & 3) + 4 * quad]);
-                sa = fmaf(S[4 * jj], kk4.x, sa);
-                sa = fmaf(S[4 * jj + 1], kk4.y, sa);
-                sa = fmaf(S[4 * jj + 2], kk4.z, sa);
-                sa = fmaf(S[4 * jj + 3], kk4.w, sa);
-            }
-            sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-            sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-            float y = 0.f;
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-                const int c0 = 16 * ((jj + rot) & 3) + 4 * quad;
-                const float4 w4 = *reinterpret_cast<const float4*>(&sv[1][c0]);
-                const float4 b4 = *reinterpret_cast<const float4*>(&sv[2][c0]);
-                const float4 t4 = *reinterpret_cast<const float4*>(&sv[3][c0]);
-                const float4 r4 = *reinterpret_cast<const float4*>(&sv[4][c0]);
-                S[4 * jj] = fmaf(S[4 * jj], w4.x, fmaf(sa, b4.x, vj * t4.x));
-                S[4 * jj + 1] = fmaf(S[4 * jj + 1], w4.y, fmaf(sa, b4.y, vj * t4.y));
-                S[4 * jj + 2] = fmaf(S[4 * jj + 2], w4.z, fmaf(sa, b4.z, vj * t4.z));
-                S[4 * jj + 3] = fmaf(S[4 * jj + 3], w4.w, fmaf(sa, b4.w, vj * t4.w));
-                y = fmaf(S[4 * jj], r4.x, y);
-                y = fmaf(S[4 * jj + 1], r4.y, y);
-                y = fmaf(S[4 * jj + 2], r4.z, y);
-                y = fmaf(S[4 * jj + 3], r4.w, y);
-            }
-            y += __shfl_xor_sync(0xffffffffu, y, 1);
-            y += __shfl_xor_sync(0xffffffffu, y, 2);
-            const float ys = warp_sum(quad == 0 ? y : 0.f);
-            if (lane == 0) red_a[warp] = ys;
-            __syncthreads();
-            const float mean = (((red_a[0] + red_a[1]) + (red_a[2] + red_a[3])) + ((red_a[4] + red_a[5]) + (red_a[6] + red_a[7]))) / (float)N;
-            const float d = y - mean;
-            const float qs = warp_sum(quad == 0 ? d * d : 0.f);
-            if (lane == 0) red_b[warp] = qs;
-            __syncthreads();
-            const float var = (((red_b[0] + red_b[1]) + (red_b[2] + red_b[3])) + ((red_b[4] + red_b[5]) + (red_b[6] + red_b[7]))) / (float)N + kGnEps;
-            const float inv_std = 1.0f / sqrtf(var);
-            if (quad == 0) {
-                yg[hb + i] = (d * inv_std * gw + gb + srk * vj) * cur.g;
-                if (v_first_state && t == sg.len - 1) v_first_state[(size_t)sg.slot * C + hc + i] = vj;
-            }
-        }
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj)
-            *reinterpret_cast<float4*>(srow + 16 * ((jj + rot) & 3)) = make_float4(S[4 * jj], S[4 * jj + 1], S[4 * jj + 2], S[4 * jj + 3]);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the rows are read by the bulk store below
-        __syncthreads();
-        if (tid == 0) {
-            const uint32_t src = (uint32_t)__cvta_generic_to_shared(wkv_stage + (size_t)st * N * N);
-            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(state_of(item)), "r"(src), "r"((uint32_t)(N * N * 4)) : "memory");
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        }
-    }
-    if (tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every state has left shared memory before the CTA ends
-}
-
 // ------------------------------------------------------------------------------------------------
 // arg-max over each logits row, ties -> smaller index (rwkv_argmax, src/backend_cuda.rs:3640-3680).
 // Writes the token to next_tok[row] (the next step's input) and appends it to the row's sequence
