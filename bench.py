@@ -91,7 +91,7 @@ def algorithmic_bytes(sh, quant, B):
 # DRAM traffic of decode_persistent_kernel per decoded token, from one ncu capture of a 4-token launch
 # (dram__bytes_read.sum + dram__bytes_write.sum, divided by 4; summary under profiles/).  Every token streams the same weights,
 # so the traffic of a launch is this figure times its tokens.
-NCU_DRAM_BYTES_PER_TOKEN = {("3b", "int8", 1): (12.444611e9 + 0.382018e9) / 4}
+NCU_DRAM_BYTES_PER_TOKEN = {("3b", "int8", 1): (12.442648e9 + 0.344780e9) / 4}
 
 
 def kernel_bytes(sh, quant, B):
