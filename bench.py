@@ -46,6 +46,7 @@ def parse_args():
     ap.add_argument("--prompt", type=int, default=512, help="prompt tokens prefilled before decoding")
     ap.add_argument("--sweep", default="1,8,64,256,1024", help="batch sizes of the decode sweep (N=1 only); '' disables it")
     ap.add_argument("--sweep-steps", type=int, default=32)
+    ap.add_argument("--continuous", type=int, default=256, help="sessions of the continuous-batching workload (benchmark config 3, N=1 only); 0 disables it")
     ap.add_argument("--cpu-seconds", type=float, default=20.0, help="time budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--model-dir", default=os.environ.get("RSV_BENCH_DIR", "/tmp/rsv_bench"))
@@ -253,6 +254,45 @@ def prefix_states(rsv, model, B, prompt, vocab, rng):
     return st, np.asarray([seeds[b % nd] for b in range(B)], dtype=np.uint32)
 
 
+def continuous_batching(rsv, model, sh, n_sessions, seed=3, rate=64.0):
+    """Benchmark config 3: `n_sessions` sessions arrive as a Poisson process at `rate` requests per second (wall clock), prompt
+    lengths log-uniform in 16..2048, generation lengths geometric with mean 256, top-p 0.9, temperature 1.0, one sampler seed per
+    session; every scheduler step is a ragged mix of prompt chunks (<= 512 tokens per session) and one decode row per generating
+    session.  Returns tokens per second over the span from the first arrival to the last completion."""
+    rng = np.random.default_rng(seed)
+    arrive = np.cumsum(rng.exponential(1.0 / rate, size=n_sessions))
+    arrive -= arrive[0]
+    plen = np.clip(np.exp(rng.uniform(np.log(16), np.log(2048), size=n_sessions)).astype(np.int64), 16, 2048)
+    glen = np.clip(rng.geometric(1.0 / 256.0, size=n_sessions), 1, 2048)
+    prompts = [rng.integers(0, sh["vocab"], size=int(n)).astype(np.uint32) for n in plen]
+    sched = rsv.Scheduler(model, max_slots=n_sessions, chunk=512, max_new_cap=2048)
+    nxt, done, generated, steps, rows_total, max_rows = 0, 0, 0, 0, 0, 0
+    t0 = time.perf_counter()
+    while done < n_sessions:
+        now = time.perf_counter() - t0
+        while nxt < n_sessions and arrive[nxt] <= now:
+            sched.submit(prompts[nxt], int(glen[nxt]), rsv.SamplerParams(temperature=1.0, top_p=0.9, seed=1000 + nxt))
+            nxt += 1
+        rows, active = sched.step()
+        steps += 1 if rows else 0
+        rows_total += rows
+        max_rows = max(max_rows, rows)
+        for rid in sched.poll():
+            generated += len(sched.result(rid))
+            done += 1
+        if rows == 0 and active == 0 and nxt < n_sessions:
+            time.sleep(max(0.0, min(0.002, arrive[nxt] - (time.perf_counter() - t0))))
+        elif rows == 0:
+            sched.sync()
+    sched.sync()
+    el = time.perf_counter() - t0
+    sched.close()
+    return {"sessions": n_sessions, "arrival_rate_per_s": rate, "prompt_tokens": int(plen.sum()), "generated_tokens": int(generated),
+            "seconds": el, "decode_tok_s": generated / el, "total_tok_s": (int(plen.sum()) + generated) / el, "steps": steps,
+            "mean_rows_per_step": rows_total / max(steps, 1), "max_rows_per_step": max_rows,
+            "sampler": "top_p 0.9, temperature 1.0, seed 1000 + session", "prefill_chunk": 512}
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -381,6 +421,9 @@ def main():
                                  "hbm_frac": bts / (ms_b / args.sweep_steps / 1000.0) / 1e9 / peak}
                 st_b.close()
             result["batch_sweep"] = sweep
+        # ---- continuous batching (benchmark config 3), single GPU only ----
+        if world == 1 and args.continuous > 0:
+            result["continuous_batching"] = continuous_batching(rsv, model, sh, args.continuous)
     state.close()
     model.close()
     if rank == 0:

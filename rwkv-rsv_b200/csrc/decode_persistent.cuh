@@ -993,7 +993,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                                 float vq = val * dp_pow2(kDpP - sc_ex[sh * 4 + b]);
                                 vq = fminf(fmaxf(vq, -(float)(1 << kDpP)), (float)(1 << kDpP));
                                 int tq = (vq == vq) ? __float2int_rn(vq) : 0;
-                                long long ts = tq;
+                                const int t_full = tq;
 #pragma unroll
                                 for (int j = kDpDigits - 1; j > 0; --j) {
                                     const int dj = ((tq + 64) & 127) - 64;
@@ -1001,9 +1001,11 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                                     tq = (tq - dj) >> 7;
                                 }
                                 tile[dp_b_offset(b * kDpDigits, e)] = (uint8_t)(int8_t)tq;
-                                // the 32 lanes of a warp work on the same tile: one shared-memory add per warp
-#pragma unroll
-                                for (int o = 16; o > 0; o >>= 1) ts += __shfl_xor_sync(0xffffffffu, ts, o);
+                                // the 32 lanes of a warp work on the same tile: one shared-memory add per warp.  |t| <= 2^27, so the warp sum is
+                                // taken exactly with two 32-bit warp reductions (low 16 bits unsigned, the rest signed)
+                                const unsigned lo_sum = __reduce_add_sync(0xffffffffu, (unsigned)(t_full & 0xFFFF));
+                                const int hi_sum = __reduce_add_sync(0xffffffffu, t_full >> 16);
+                                const long long ts = (long long)hi_sum * 65536 + (long long)lo_sum;
                                 if (lane == 0) atomicAdd(reinterpret_cast<unsigned long long*>(&sc_tsum[(size_t)tile_idx * kDpMaxNB + b]), (unsigned long long)ts);
                             } else {
                                 float vq = val * dp_pow2(-sc_ex[sh * 4 + b]);
