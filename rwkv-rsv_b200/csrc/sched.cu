@@ -305,7 +305,14 @@ int rsv_sched_step(rsv_sched* Sp, int64_t* rows_out, int64_t* active_out) {
             }
             RSV_CUDA(cudaEventRecord(S.pin_ev[area], m.stream));
             engine_merge_tokens(m, S.host_tok_dev, S.slot_tok, R);
-            m.forward_rows(S.st, p, false);
+            if (R == O && R <= 4 && !p.multi_row_segments && !m.prof_on && m.persistent_available(R)) {
+                // a few decoding sessions and nothing else (the tail of a workload): one launch of the persistent decode kernel
+                int slots[4] = {0, 0, 0, 0};
+                for (int i = 0; i < R; ++i) slots[i] = p.rows[i].slot;
+                m.run_persistent(S.st, R, slots, 1, false, false, nullptr, nullptr, 0);
+            } else {
+                m.forward_rows(S.st, p, false);
+            }
             if (O) {
                 // a step whose sessions all asked for arg-max uses the arg-max kernel (ties -> smaller id); any other step
                 // goes through the sampler, where arg-max sessions carry a top_k = 1 row

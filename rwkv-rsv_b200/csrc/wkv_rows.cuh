@@ -3,13 +3,14 @@
 // a batch whose recurrent state (32 KB of traffic per pair) dominates the step:
 //   * a warp pair owns a head: lane l of warp half hf holds state row l + 32 hf, all 64 columns, in registers, so the two
 //     row-times-vector products of the recurrence need no shuffles at all;
-//   * everything an item needs arrives through one mbarrier two items ahead: the 16 KB state as two TMA boxes (64 rows x 128
+//   * everything an item needs arrives through one mbarrier, requested as soon as the previous item's copy is in registers: the 16 KB state as two TMA boxes (64 rows x 128
 //     bytes, SWIZZLE_128B: a lane reads its 128-byte row segment chunk by chunk without bank conflicts), the first token's
 //     eight input vectors and the head's five parameter vectors as 256-byte bulk copies.  No load of an iteration depends on
 //     another load: with the memory system loaded a dependent global load costs microseconds per item;
 //   * the updated rows leave through a staging tile and TMA stores;
-//   * three warp pairs per CTA walk their own item streams; they share nothing but the CTA's shared memory budget, and
-//     synchronise pairwise with named barriers (GroupNorm statistics over the head's 64 rows).
+//   * six warp pairs per CTA walk their own item streams (a head's chain of reductions and barriers is long and a thread holds
+//     64 state registers, so the pairs are what hides latency: 96 KB of state reads in flight per SM); they share nothing but
+//     the CTA's shared memory budget, and synchronise pairwise with named barriers (GroupNorm statistics over the 64 rows).
 // Every mbarrier wait is bounded; on expiry bit 16 of the status word is set and the pair stops.
 #pragma once
 #include "kernels.cuh"
@@ -17,15 +18,15 @@
 
 namespace rsv {
 
-constexpr int kWrPairs = 3;
+constexpr int kWrPairs = 6;
 constexpr int kWrThreads = 64 * kWrPairs;
-constexpr int kWrStages = 2;               // load stages per pair (plus one staging tile for the stores)
+constexpr int kWrStages = 1;               // load stages per pair (plus one staging tile for the stores)
 constexpr int kWrTileFloats = 64 * 32;     // one TMA box: 64 rows x 32 columns
 constexpr int kWrStateBytes = 2 * kWrTileFloats * 4;
 constexpr int kWrVecs = 13;                // r k v w a g vgate vfirst | k_k k_a r_k lnx_w lnx_b, 64 floats each
 constexpr int kWrStageBytes = kWrStateBytes + 4096;  // state + vectors, 1 KB aligned
 constexpr int kWrPairBytes = kWrStages * kWrStageBytes + kWrStateBytes;
-constexpr size_t kWrSmemBytes = 1024 /*alignment*/ + (size_t)kWrPairs * kWrPairBytes + (size_t)(kWrThreads / 32) * 5 * 64 * 4 + 512;
+constexpr size_t kWrSmemBytes = 1024 /*alignment*/ + (size_t)kWrPairs * kWrPairBytes + (size_t)kWrPairs * 5 * 64 * 4 + 512;
 
 __device__ __forceinline__ void wr_pair_sync(int pair) { asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory"); }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
@@ -52,8 +53,8 @@ __global__ void __launch_bounds__(kWrThreads, 1) wkv7_rows_kernel(const __grid_c
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, pair = warp >> 1, hf = warp & 1, rr = lane + 32 * hf;
     uint8_t* my = base + (size_t)pair * kWrPairBytes;                                   // [stage][state | vectors], then the store tile
     float* out_tile = reinterpret_cast<float*>(my + kWrStages * kWrStageBytes);
-    float* svec = reinterpret_cast<float*>(base + (size_t)kWrPairs * kWrPairBytes);    // [warp][5][64]
-    float* red = svec + (size_t)(kWrThreads / 32) * 5 * N;                              // [pair][2 halves][2]
+    float* svec = reinterpret_cast<float*>(base + (size_t)kWrPairs * kWrPairBytes);    // [pair][5][64]
+    float* red = svec + (size_t)kWrPairs * 5 * N;                              // [pair][2 halves][2]
     uint64_t* full = reinterpret_cast<uint64_t*>(red + kWrPairs * 4);                   // [pair][stage]
     volatile int* s_abort = reinterpret_cast<volatile int*>(full + kWrPairs * kWrStages) + pair;  // one flag per warp pair
     const bool leader = hf == 0 && lane == 0;
@@ -88,9 +89,9 @@ __global__ void __launch_bounds__(kWrThreads, 1) wkv7_rows_kernel(const __grid_c
     SegMeta sg0 = meta_of(0), sg1 = meta_of(1), sg2 = meta_of(2);
     if (leader) {
         if (my_items > 0) issue_load(0, sg0);
-        if (my_items > 1) issue_load(1, sg1);
+        if (kWrStages > 1 && my_items > 1) issue_load(1, sg1);
     }
-    float* sv = svec + (size_t)warp * 5 * N;
+    float* sv = svec + (size_t)pair * 5 * N;  // both warps of the pair write the same five vectors (identical values) and read them back
     float* pred = red + pair * 4;
     for (int n = 0; n < my_items; ++n) {
         const int item = first + n * stride, h = item % H, st = n % kWrStages;
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(kWrThreads, 1) wkv7_rows_kernel(const __grid_c
         const float rkc0 = vs[10 * N + lane], rkc1 = vs[10 * N + lane + 32], gw = vs[11 * N + rr], gb = vs[12 * N + rr];
         // the stage is free once both warps hold its contents: the data of item n + 2 may land in it
         wr_pair_sync(pair);
-        if (leader && n + kWrStages < my_items) issue_load(n + kWrStages, sg2);
+        if (leader && n + kWrStages < my_items) issue_load(n + kWrStages, kWrStages == 1 ? sg1 : sg2);
         for (int t = 0; t < sg.len; ++t) {
             const size_t hb = (size_t)(sg.start + t) * C + hc;
             if (t > 0) cur = wkv_load_inputs(r, k, v, vgate, vfirst, w, a, g, hb, lane, rr);
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(kWrThreads, 1) wkv7_rows_kernel(const __grid_c
             const float kh0 = kk0 * inv, kh1 = kk1 * inv;
             const float kt0 = cur.k0 + kac0 * (cur.k0 * cur.a0 - cur.k0), kt1 = cur.k1 + kac1 * (cur.k1 * cur.a1 - cur.k1);
             const float srk = warp_sum(cur.r0 * kt0 * rkc0 + cur.r1 * kt1 * rkc1);
-            __syncwarp();  // the previous token's readers are done with sv
+            wr_pair_sync(pair);  // the previous token's readers (both warps) are done with sv
             sv[0 * N + lane] = kh0;
             sv[0 * N + lane + 32] = kh1;
             sv[1 * N + lane] = cur.w0;
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(kWrThreads, 1) wkv7_rows_kernel(const __grid_c
             sv[3 * N + lane + 32] = kt1;
             sv[4 * N + lane] = cur.r0;
             sv[4 * N + lane + 32] = cur.r1;
-            __syncwarp();
+            wr_pair_sync(pair);
             float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f;
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
