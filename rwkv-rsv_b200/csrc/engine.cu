@@ -646,49 +646,59 @@ void ensure_tc_buffers(Model& m, size_t b_bytes, size_t rows, size_t partial_byt
 
 constexpr int kTcDigits = 4;  // base-128 digits of the fixed-point activations (P = 27 bits)
 
-// One launch group of the tensor-core path: all requests share the weight kind (int8 or fp16).
-void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, int R, bool i8) {
-    const int D = i8 ? kTcDigits : 2;
-    const int ncols = R * D;
-    int NT = 16;
-    while (NT < ncols && NT < 256) NT <<= 1;
-    const int ncols_pad = (int)round_up(ncols, NT);
+// One launch group of the tensor-core path: all requests share the weight kind (int8 or fp16).  A stage of a layer has up to
+// two groups; their activation operands are prepared by one launch, then each group's GEMM is launched.
+struct TcRegion {
+    const float* x;
+    int ldx, K, Kpad;
+    size_t off;  // bytes from the group's base in the operand buffer
+    int row0;    // first scale / sum row of the region inside the group
+};
+struct TcGroup {
+    bool i8 = false;
+    int n = 0, R = 0, D = 0, ncols = 0, NT = 0, ncols_pad = 0, rows = 0, U = 0, G = 0;
+    LinReq reqs[kTcMaxProblems];
+    std::vector<TcRegion> regions;
+    int region_of[kTcMaxProblems];
+    size_t b_bytes = 0, b_base = 0, partial_bytes = 0;
+    int row_base = 0;
+    TcLaunch L;
+};
+
+void tc_plan_group(Model& m, TcGroup& g) {
+    const bool i8 = g.i8;
+    const int n = g.n, R = g.R;
+    g.D = i8 ? kTcDigits : 2;
+    g.ncols = R * g.D;
+    g.NT = 16;
+    while (g.NT < g.ncols && g.NT < 256) g.NT <<= 1;
+    g.ncols_pad = (int)round_up(g.ncols, g.NT);
     const size_t es = i8 ? 1 : 2;
     // B operand regions (requests that read the same activations share one)
-    struct Region {
-        const float* x;
-        int ldx, K, Kpad;
-        size_t off;
-        int row0;
-    };
-    std::vector<Region> regions;
-    std::vector<int> region_of(n);
-    size_t b_bytes = 0;
-    int rows = 0;
     for (int i = 0; i < n; ++i) {
-        const LinearW& W = *reqs[i].W;
+        const LinearW& W = *g.reqs[i].W;
         int found = -1;
-        for (size_t j = 0; j < regions.size(); ++j)
-            if (regions[j].x == reqs[i].x && regions[j].K == W.K && regions[j].Kpad == W.Kpad && regions[j].ldx == reqs[i].ldx) found = (int)j;
+        for (size_t j = 0; j < g.regions.size(); ++j)
+            if (g.regions[j].x == g.reqs[i].x && g.regions[j].K == W.K && g.regions[j].Kpad == W.Kpad && g.regions[j].ldx == g.reqs[i].ldx) found = (int)j;
         if (found < 0) {
-            regions.push_back(Region{reqs[i].x, reqs[i].ldx, W.K, W.Kpad, b_bytes, rows});
-            found = (int)regions.size() - 1;
-            b_bytes += round_up((size_t)ncols_pad * W.Kpad * es, 1024);
-            rows += R;
+            g.regions.push_back(TcRegion{g.reqs[i].x, g.reqs[i].ldx, W.K, W.Kpad, g.b_bytes, g.rows});
+            found = (int)g.regions.size() - 1;
+            g.b_bytes += round_up((size_t)g.ncols_pad * W.Kpad * es, 1024);
+            g.rows += R;
         }
-        region_of[i] = found;
+        g.region_of[i] = found;
     }
     // units, tiles, CTA count
-    TcLaunch L;
+    TcLaunch& L = g.L;
     memset(&L, 0, sizeof(L));
     int U = 0, T = 0;
-    const int n_tiles = ncols_pad / NT;
+    const int n_tiles = g.ncols_pad / g.NT;
     for (int i = 0; i < n; ++i) {
-        const LinearW& W = *reqs[i].W;
+        const LinearW& W = *g.reqs[i].W;
         TcProb& P = L.p[i];
         P.M = W.M;
         P.kblocks = (int)((size_t)W.Kpad * es / kTcKBlockBytes);
-        P.ncols = ncols;
+        P.ncols = g.ncols;
         P.n_tiles = n_tiles;
         P.unit0 = U;
         P.tile0 = T;
@@ -716,39 +726,32 @@ void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, i
         }
         pmax = std::max(pmax, tc_cta_of_unit(tile_first + P.kblocks - 1, U, G) - tc_cta_of_unit(tile_first, U, G) + 1);
     }
-    const size_t partial_bytes = (size_t)nsplit * pmax * NT * kTcTileM * 4;
-    ensure_tc_buffers(m, b_bytes, (size_t)rows, partial_bytes);
+    g.partial_bytes = (size_t)nsplit * pmax * g.NT * kTcTileM * 4;
+    g.U = U;
+    g.G = G;
+    L.nprob = n;
+    L.total_units = U;
+    L.nt = g.NT;
+    L.is_i8 = i8;
+    L.pmax = pmax;
+    L.grid = G;
+    L.nsplit = nsplit;
+}
+
+void tc_launch_group(Model& m, const char* name, TcGroup& g) {
     Workspace& w = m.ws;
-    // operand preparation: one launch for all the group's activation operands
-    {
-        TcPrepLaunch PL;
-        memset(&PL, 0, sizeof(PL));
-        if (regions.size() > (size_t)kTcMaxProblems) throw std::runtime_error("tc_linear: too many operand regions");
-        for (size_t j = 0; j < regions.size(); ++j) {
-            const Region& rg = regions[j];
-            PL.r[j] = TcPrepRegion{rg.x, w.tc_b + rg.off, w.tc_xscale + rg.row0, w.tc_tsum + rg.row0, rg.ldx, rg.K, rg.Kpad, 0};
-        }
-        LAUNCH(m, i8 ? "tc_prepare_i8" : "tc_prepare_f16") {
-            const dim3 grid(R, (unsigned)regions.size());
-            const dim3 block((size_t)R * regions.size() < 2 * (size_t)m.num_sms ? kPrepThreadsWide : kPrepThreads);
-            if (i8)
-                launch_pdl(m, tc_prepare_i8_kernel<kTcDigits>, grid, block, 0, PL);
-            else
-                launch_pdl(m, tc_prepare_f16_kernel, grid, block, 0, PL);
-            check_launch("tc_prepare");
-        }
-    }
-    for (int i = 0; i < n; ++i) {
-        const Region& rg = regions[region_of[i]];
-        const LinReq& q = reqs[i];
-        encode_kmajor_map(&L.bmap[i], i8, w.tc_b + rg.off, ncols_pad, rg.Kpad, NT);
+    TcLaunch& L = g.L;
+    for (int i = 0; i < g.n; ++i) {
+        const TcRegion& rg = g.regions[g.region_of[i]];
+        const LinReq& q = g.reqs[i];
+        encode_kmajor_map(&L.bmap[i], g.i8, w.tc_b + g.b_base + rg.off, g.ncols_pad, rg.Kpad, g.NT);
         TcProb& P = L.p[i];
-        P.R = R;
-        P.D = D;
+        P.R = g.R;
+        P.D = g.D;
         P.wscale = q.W->wscale;
         P.wzero = q.W->wzero;
-        P.xscale = w.tc_xscale + rg.row0;
-        P.tsum = w.tc_tsum + rg.row0;
+        P.xscale = w.tc_xscale + g.row_base + rg.row0;
+        P.tsum = w.tc_tsum + g.row_base + rg.row0;
         P.y = q.y;
         P.y2 = q.y2;
         P.bias = q.bias;
@@ -757,14 +760,7 @@ void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, i
         P.ldaux = q.ldaux;
         P.epi = q.epi;
     }
-    L.nprob = n;
-    L.total_units = U;
-    L.nt = NT;
-    L.is_i8 = i8;
-    L.pmax = pmax;
-    L.grid = G;
-    L.nsplit = nsplit;
-    const size_t stage_bytes = (size_t)kTcTileM * kTcKBlockBytes + (size_t)NT * kTcKBlockBytes;
+    const size_t stage_bytes = (size_t)kTcTileM * kTcKBlockBytes + (size_t)g.NT * kTcKBlockBytes;
     L.nstages = (int)std::min<size_t>(8, (200 * 1024) / stage_bytes);
     L.partials = w.tc_partials;
     L.tile_cnt = w.tc_cnt;
@@ -777,24 +773,57 @@ void run_linear_tc_kind(Model& m, const char* name, const LinReq* reqs, int n, i
         configured[m.device & 15] = true;
     }
     LAUNCH(m, name) {
-        if (i8)
-            launch_pdl(m, tc_linear_kernel<true>, dim3(G), dim3(kTcThreads), smem, L);
+        if (g.i8)
+            launch_pdl(m, tc_linear_kernel<true>, dim3(g.G), dim3(kTcThreads), smem, L);
         else
-            launch_pdl(m, tc_linear_kernel<false>, dim3(G), dim3(kTcThreads), smem, L);
+            launch_pdl(m, tc_linear_kernel<false>, dim3(g.G), dim3(kTcThreads), smem, L);
         check_launch("tc_linear");
     }
+}
+
+void run_linear_tc(Model& m, const char* name, const LinReq* reqs, int n, int R) {
+    TcGroup ga, gb;
+    ga.i8 = true;
+    gb.i8 = false;
+    ga.R = gb.R = R;
+    for (int i = 0; i < n; ++i) {
+        TcGroup& g = reqs[i].W->wtype == W_INT8 ? ga : gb;
+        if (g.n >= kTcMaxProblems) throw std::runtime_error("tc_linear: too many problems in one group");
+        g.reqs[g.n++] = reqs[i];
+    }
+    if (ga.n) tc_plan_group(m, ga);
+    if (gb.n) tc_plan_group(m, gb);
+    gb.b_base = ga.b_bytes;  // the fp16 group's operands follow the int8 group's
+    gb.row_base = ga.rows;
+    if (ga.regions.size() + gb.regions.size() > (size_t)kTcMaxRegions) throw std::runtime_error("tc_linear: too many operand regions");
+    ensure_tc_buffers(m, ga.b_bytes + gb.b_bytes, (size_t)(ga.rows + gb.rows), std::max(ga.partial_bytes, gb.partial_bytes));
+    Workspace& w = m.ws;
+    // operand preparation: one launch for every activation operand of the stage
+    {
+        TcPrepLaunch PL;
+        memset(&PL, 0, sizeof(PL));
+        int nr = 0;
+        for (TcGroup* g : {&ga, &gb})
+            for (const TcRegion& rg : g->regions)
+                PL.r[nr++] = TcPrepRegion{rg.x, w.tc_b + g->b_base + rg.off, w.tc_xscale + g->row_base + rg.row0, w.tc_tsum + g->row_base + rg.row0,
+                                          rg.ldx, rg.K, rg.Kpad, g->i8 ? 1 : 0};
+        LAUNCH(m, "tc_prepare") {
+            const dim3 grid(R, (unsigned)nr);
+            const dim3 block((size_t)R * nr < 2 * (size_t)m.num_sms ? kPrepThreadsWide : kPrepThreads);
+            launch_pdl(m, tc_prepare_kernel<kTcDigits>, grid, block, 0, PL);
+            check_launch("tc_prepare");
+        }
+    }
+    std::string nm = std::string(name) + "_tc";
+    if (ga.n) tc_launch_group(m, nm.c_str(), ga);
+    if (gb.n) tc_launch_group(m, nm.c_str(), gb);
 }
 
 void run_linear(Model& m, const char* name, const LinReq* reqs, int n, int R) {
     bool tc = R >= m.tc_min_rows;
     for (int i = 0; i < n; ++i) tc = tc && reqs[i].W->tc_ok;
     if (!tc) return run_linear_simt(m, name, reqs, n, R);
-    LinReq a[kTcMaxProblems], b[kTcMaxProblems];
-    int na = 0, nb = 0;
-    for (int i = 0; i < n; ++i) (reqs[i].W->wtype == W_INT8 ? a[na++] : b[nb++]) = reqs[i];
-    std::string nm = std::string(name) + "_tc";
-    if (na) run_linear_tc_kind(m, nm.c_str(), a, na, R, true);
-    if (nb) run_linear_tc_kind(m, nm.c_str(), b, nb, R, false);
+    run_linear_tc(m, name, reqs, n, R);
 }
 }  // namespace
 
@@ -1368,8 +1397,7 @@ void engine_op_linear(Model& m, int path, int wtype, const void* w_host, const u
         RSV_CUDA(cudaMemcpyAsync(dx, x_host, (size_t)R * K * 4, cudaMemcpyHostToDevice, m.stream));
         LinReq q = {&W, dx, K, dy, M, EPI_STORE};
         if (path == 1) {
-            LinReq a[1] = {q};
-            run_linear_tc_kind(m, "op_linear_tc", a, 1, R, wtype == W_INT8);
+            run_linear_tc(m, "op_linear", &q, 1, R);
         } else {
             run_linear_simt(m, "op_linear_simt", &q, 1, R);
         }

@@ -601,10 +601,11 @@ struct TcPrepRegion {
     void* B;
     float* xscale;
     long long* tsum;
-    int ldx, K, Kpad, pad;
+    int ldx, K, Kpad, is_i8;
 };
+constexpr int kTcMaxRegions = 12;  // activation operands prepared by one launch (int8 and fp16 groups together)
 struct TcPrepLaunch {
-    TcPrepRegion r[kTcMaxProblems];
+    TcPrepRegion r[kTcMaxRegions];
 };
 // smallest ex with 2^ex >= amax (0 for an all-zero or non-finite row; non-finite input is clamped by the callers)
 __device__ __forceinline__ int tc_scale_exp(float amax) {
@@ -639,9 +640,10 @@ __device__ __forceinline__ float tc_prep_load(const float* xr, int K, float (&xv
     for (int k = threadIdx.x + kPrepCache * nt; k < K; k += nt) amax = fmaxf(amax, fabsf(xr[k]));
     return amax;
 }
-// grid (rows, regions): every activation operand of a launch group is prepared by one kernel
+// grid (rows, regions): every activation operand of a layer stage - the int8 group's digits and the fp16 group's hi / lo
+// halves - is prepared by one kernel
 template <int D>
-__global__ void __launch_bounds__(kPrepThreadsWide) tc_prepare_i8_kernel(const __grid_constant__ TcPrepLaunch L) {
+__global__ void __launch_bounds__(kPrepThreadsWide) tc_prepare_kernel(const __grid_constant__ TcPrepLaunch L) {
     __shared__ float redf[32];
     __shared__ long long redl[32];
     constexpr int P = 7 * D - 1;
@@ -650,79 +652,72 @@ __global__ void __launch_bounds__(kPrepThreadsWide) tc_prepare_i8_kernel(const _
     const TcPrepRegion& G = L.r[blockIdx.y];
     const int r = blockIdx.x, K = G.K, Kpad = G.Kpad, nt = blockDim.x;
     const float* xr = G.x + (size_t)r * G.ldx;
-    int8_t* B = reinterpret_cast<int8_t*>(G.B);
     float xv[kPrepCache];
     const int ex = tc_scale_exp(tc_block_max(tc_prep_load(xr, K, xv), redf));
-    const float inv = ldexpf(1.0f, P - ex);  // 2^P / e, exact
-    long long ts = 0;
-    auto digits = [&](int k, float x) {
-        float v = x * inv;
-        v = fminf(fmaxf(v, -(float)(1 << P)), (float)(1 << P));
-        int t = __float2int_rn(v);
-        if (!(v == v)) t = 0;  // NaN
-        ts += t;
-        int8_t d[D];
+    if (G.is_i8) {
+        int8_t* B = reinterpret_cast<int8_t*>(G.B);
+        const float inv = ldexpf(1.0f, P - ex);  // 2^P / e, exact
+        long long ts = 0;
+        auto digits = [&](int k, float x) {
+            float v = x * inv;
+            v = fminf(fmaxf(v, -(float)(1 << P)), (float)(1 << P));
+            int t = __float2int_rn(v);
+            if (!(v == v)) t = 0;  // NaN
+            ts += t;
+            int8_t d[D];
 #pragma unroll
-        for (int j = D - 1; j > 0; --j) {
-            const int dj = ((t + 64) & 127) - 64;
-            d[j] = (int8_t)dj;
-            t = (t - dj) >> 7;
+            for (int j = D - 1; j > 0; --j) {
+                const int dj = ((t + 64) & 127) - 64;
+                d[j] = (int8_t)dj;
+                t = (t - dj) >> 7;
+            }
+            d[0] = (int8_t)t;
+#pragma unroll
+            for (int j = 0; j < D; ++j) B[((size_t)r * D + j) * Kpad + k] = d[j];
+        };
+#pragma unroll
+        for (int c = 0; c < kPrepCache; ++c) {
+            const int k = threadIdx.x + c * nt;
+            if (k < K) digits(k, xv[c]);
         }
-        d[0] = (int8_t)t;
+        for (int k = threadIdx.x + kPrepCache * nt; k < K; k += nt) digits(k, xr[k]);
+        for (int k = K + threadIdx.x; k < Kpad; k += nt)
 #pragma unroll
-        for (int j = 0; j < D; ++j) B[((size_t)r * D + j) * Kpad + k] = d[j];
-    };
+            for (int j = 0; j < D; ++j) B[((size_t)r * D + j) * Kpad + k] = 0;
 #pragma unroll
-    for (int c = 0; c < kPrepCache; ++c) {
-        const int k = threadIdx.x + c * nt;
-        if (k < K) digits(k, xv[c]);
+        for (int o = 16; o > 0; o >>= 1) ts += __shfl_xor_sync(0xffffffffu, ts, o);
+        if ((threadIdx.x & 31) == 0) redl[threadIdx.x >> 5] = ts;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            long long t = 0;
+            for (int i = 0; i < (nt >> 5); ++i) t += redl[i];
+            G.tsum[r] = t;
+            G.xscale[r] = ldexpf(1.0f, ex - P);
+        }
+    } else {
+        __half* B = reinterpret_cast<__half*>(G.B);
+        const float inv = ldexpf(1.0f, -ex);
+        auto split = [&](int k, float x) {
+            float v = x * inv;
+            v = fminf(fmaxf(v, -1.0f), 1.0f);
+            if (!(v == v)) v = 0.f;
+            const __half hi = __float2half_rn(v);
+            const __half lo = __float2half_rn(v - __half2float(hi));
+            B[((size_t)r * 2) * Kpad + k] = hi;
+            B[((size_t)r * 2 + 1) * Kpad + k] = lo;
+        };
+#pragma unroll
+        for (int c = 0; c < kPrepCache; ++c) {
+            const int k = threadIdx.x + c * nt;
+            if (k < K) split(k, xv[c]);
+        }
+        for (int k = threadIdx.x + kPrepCache * nt; k < K; k += nt) split(k, xr[k]);
+        for (int k = K + threadIdx.x; k < Kpad; k += nt) {
+            B[((size_t)r * 2) * Kpad + k] = __float2half_rn(0.f);
+            B[((size_t)r * 2 + 1) * Kpad + k] = __float2half_rn(0.f);
+        }
+        if (threadIdx.x == 0) G.xscale[r] = ldexpf(1.0f, ex);
     }
-    for (int k = threadIdx.x + kPrepCache * nt; k < K; k += nt) digits(k, xr[k]);
-    for (int k = K + threadIdx.x; k < Kpad; k += nt)
-#pragma unroll
-        for (int j = 0; j < D; ++j) B[((size_t)r * D + j) * Kpad + k] = 0;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ts += __shfl_xor_sync(0xffffffffu, ts, o);
-    if ((threadIdx.x & 31) == 0) redl[threadIdx.x >> 5] = ts;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        long long t = 0;
-        for (int i = 0; i < (nt >> 5); ++i) t += redl[i];
-        G.tsum[r] = t;
-        G.xscale[r] = ldexpf(1.0f, ex - P);
-    }
-}
-__global__ void __launch_bounds__(kPrepThreadsWide) tc_prepare_f16_kernel(const __grid_constant__ TcPrepLaunch L) {
-    __shared__ float redf[32];
-    pdl_launch_dependents();
-    pdl_wait();
-    const TcPrepRegion& G = L.r[blockIdx.y];
-    const int r = blockIdx.x, K = G.K, Kpad = G.Kpad, nt = blockDim.x;
-    const float* xr = G.x + (size_t)r * G.ldx;
-    __half* B = reinterpret_cast<__half*>(G.B);
-    float xv[kPrepCache];
-    const int ex = tc_scale_exp(tc_block_max(tc_prep_load(xr, K, xv), redf));
-    const float inv = ldexpf(1.0f, -ex);
-    auto split = [&](int k, float x) {
-        float v = x * inv;
-        v = fminf(fmaxf(v, -1.0f), 1.0f);
-        if (!(v == v)) v = 0.f;
-        const __half hi = __float2half_rn(v);
-        const __half lo = __float2half_rn(v - __half2float(hi));
-        B[((size_t)r * 2) * Kpad + k] = hi;
-        B[((size_t)r * 2 + 1) * Kpad + k] = lo;
-    };
-#pragma unroll
-    for (int c = 0; c < kPrepCache; ++c) {
-        const int k = threadIdx.x + c * nt;
-        if (k < K) split(k, xv[c]);
-    }
-    for (int k = threadIdx.x + kPrepCache * nt; k < K; k += nt) split(k, xr[k]);
-    for (int k = K + threadIdx.x; k < Kpad; k += nt) {
-        B[((size_t)r * 2) * Kpad + k] = __float2half_rn(0.f);
-        B[((size_t)r * 2 + 1) * Kpad + k] = __float2half_rn(0.f);
-    }
-    if (threadIdx.x == 0) G.xscale[r] = ldexpf(1.0f, ex);
 }
 
 }  // namespace rsv
