@@ -46,6 +46,7 @@ def parse_args():
     ap.add_argument("--prompt", type=int, default=512, help="prompt tokens prefilled before decoding")
     ap.add_argument("--sweep", default="1,8,64,256,1024", help="batch sizes of the decode sweep (N=1 only); '' disables it")
     ap.add_argument("--sweep-steps", type=int, default=32)
+    ap.add_argument("--prefill", type=int, default=2048, help="prompt tokens of the timed chunked prefill (N=1 only); 0 disables it")
     ap.add_argument("--continuous", type=int, default=256, help="sessions of the continuous-batching workload (benchmark config 3, N=1 only); 0 disables it")
     ap.add_argument("--cpu-seconds", type=float, default=20.0, help="time budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -421,9 +422,27 @@ def main():
                                  "hbm_frac": bts / (ms_b / args.sweep_steps / 1000.0) / 1e9 / peak}
                 st_b.close()
             result["batch_sweep"] = sweep
+        # ---- prompt prefill (the chunked sequence path, Bundle::infer with chunk 512), single GPU only ----
+        if world == 1 and args.prefill > 0:
+            try:
+                pb = rsv.Bundle(model)
+                ptoks = rng.integers(0, sh["vocab"], size=args.prefill).astype(np.uint32)
+                pb.infer_chunked(ptoks[:min(512, args.prefill)], 512)  # sizes the work buffers
+                pb.reset()
+                model.timer_start()
+                pb.infer_chunked(ptoks, 512)
+                pms = model.timer_stop()
+                result["prefill"] = {"tokens": int(args.prefill), "chunk": 512, "ms": pms, "tok_s": args.prefill / (pms / 1000.0),
+                                     "api": "rsv_infer_chunked (Bundle::infer, RnnOption::Last), one session"}
+                pb.state.close()
+            except Exception as e:  # an optional section must not cost the headline line
+                result["prefill"] = {"error": str(e)}
         # ---- continuous batching (benchmark config 3), single GPU only ----
         if world == 1 and args.continuous > 0:
-            result["continuous_batching"] = continuous_batching(rsv, model, sh, args.continuous)
+            try:
+                result["continuous_batching"] = continuous_batching(rsv, model, sh, args.continuous)
+            except Exception as e:
+                result["continuous_batching"] = {"error": str(e)}
     state.close()
     model.close()
     if rank == 0:

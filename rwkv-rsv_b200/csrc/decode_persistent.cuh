@@ -568,6 +568,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                                 }
                             for (int b = 0; b < NB; ++b) pf(Ln->tmix_x + (size_t)P.slot[b] * C, cb);
                         } else if (v == DV_P3) {  // the heads phase runs before phase 3
+                            if (l + 1 < P.L) pf(P.layers + (l + 1), sizeof(DpLayer));  // the table the workers stage during phase 4
                             pf(Ln->w2, (size_t)C * P.wm * 2);
                             pf(Ln->a2, (size_t)C * P.am * 2);
                             pf(Ln->v2, (size_t)C * P.vm * 2);
