@@ -61,6 +61,14 @@ struct SegMeta {
 // launch.  Rule used here: a kernel reads or writes nothing but its parameters and the model's weights (and state that
 // only an earlier step wrote) before pdl_wait().
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// A pointer to data the predecessor produces, as seen after pdl_wait().  `const __restrict__` parameters promise the compiler
+// that nobody writes the data while the kernel runs, so it may move their loads above the wait; passing the pointer through
+// this (empty) asm after the wait makes every later load depend on it.
+template <typename T>
+__device__ __forceinline__ T* pdl_fresh(T* p) {
+    asm volatile("" : "+l"(p)::"memory");
+    return p;
+}
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 }  // namespace rsv

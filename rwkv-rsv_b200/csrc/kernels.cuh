@@ -132,6 +132,9 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_kernel(const float* __re
     __shared__ float red[kRowThreads / 32];
     pdl_launch_dependents();
     pdl_wait();
+    x_in = pdl_fresh(x_in);
+    delta = pdl_fresh(delta);
+    shift_state = pdl_fresh(shift_state);
     const int r = blockIdx.x;
     const RowMeta rm = rows[r];
     const float* xr = x_in + (size_t)r * C;
@@ -166,6 +169,7 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_kernel(const float* __re
 __global__ void commit_shift_kernel(const float* __restrict__ staging, const SegMeta* __restrict__ segs, int C, float* __restrict__ shift_state) {
     pdl_launch_dependents();
     pdl_wait();
+    staging = pdl_fresh(staging);
     const SegMeta sg = segs[blockIdx.x];
     for (int i = threadIdx.x; i < C; i += blockDim.x) shift_state[(size_t)sg.slot * C + i] = staging[(size_t)blockIdx.x * C + i];
 }
@@ -409,6 +413,34 @@ constexpr int kWkvThreads = 256;
 // depend on the inputs only (|kk|^2 and the bonus dot product) are computed by every warp for itself with warp
 // shuffles; only the GroupNorm statistics of y cross warps (two block barriers per token).  All global loads of a
 // token are issued before the first use, so a CTA waits for memory once per token.
+// The per-token inputs of one lane (two of the 64 channels, and the row's v, g and v-lerp operands), shared with the row-per-lane
+// kernel for large batches (wkv_rows.cuh).  Loading does no arithmetic, so that a token's inputs can be requested one token
+// ahead of their use: inside a multi-token segment (prefill) the recurrence is sequential and a memory round trip per token
+// would be its whole cost.
+struct WkvIn {
+    float k0, k1, a0, a1, r0, r1, w0, w1, v, g, vg, vf;
+};
+__device__ __forceinline__ WkvIn wkv_load_inputs(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
+                                                 const float* __restrict__ vgate, const float* __restrict__ vfirst, const float* __restrict__ w,
+                                                 const float* __restrict__ a, const float* __restrict__ g, size_t hb, int lane, int i) {
+    WkvIn x;
+    x.k0 = k[hb + lane];
+    x.k1 = k[hb + lane + 32];
+    x.a0 = a[hb + lane];
+    x.a1 = a[hb + lane + 32];
+    x.r0 = r[hb + lane];
+    x.r1 = r[hb + lane + 32];
+    x.w0 = w[hb + lane];
+    x.w1 = w[hb + lane + 32];
+    x.v = v[hb + i];
+    x.g = g[hb + i];
+    x.vg = vgate ? vgate[hb + i] : 0.f;
+    x.vf = vgate ? vfirst[hb + i] : 0.f;
+    return x;
+}
+// v of the token: layers > 0 lerp towards the first layer's v (src/model.rs:424-430)
+__device__ __forceinline__ float wkv_value(const WkvIn& x, bool has_gate) { return has_gate ? x.v + x.vg * (x.vf - x.v) : x.v; }
+
 // `vgate` (layers > 0): v <- v + vgate * (vfirst - v), the lerp of src/model.rs:424-430 (the gate itself,
 // sigmoid(v0 + (xv v1) v2), comes from the rank back-projection).
 __global__ void __launch_bounds__(kWkvThreads, 4) wkv7_kernel(const SegMeta* __restrict__ segs, const float* __restrict__ r, const float* __restrict__ k,
@@ -437,18 +469,27 @@ __global__ void __launch_bounds__(kWkvThreads, 4) wkv7_kernel(const SegMeta* __r
         S[4 * jj + 3] = t.w;
     }
     pdl_wait();
+    r = pdl_fresh(r);
+    k = pdl_fresh(k);
+    v = pdl_fresh(v);
+    vgate = pdl_fresh(vgate);
+    vfirst = pdl_fresh(vfirst);
+    w = pdl_fresh(w);
+    a = pdl_fresh(a);
+    g = pdl_fresh(g);
     const int hc = h * N;
     const float kkc0 = k_k[hc + lane], kkc1 = k_k[hc + lane + 32], kac0 = k_a[hc + lane], kac1 = k_a[hc + lane + 32];
     const float rkc0 = r_k[hc + lane], rkc1 = r_k[hc + lane + 32];
     const float gw = lnx_w[hc + i], gb = lnx_b[hc + i];
     float(*sv)[N] = s_vec[warp];
+    WkvIn nxt = wkv_load_inputs(r, k, v, vgate, vfirst, w, a, g, (size_t)sg.start * C + hc, lane, i);
     for (int t = 0; t < sg.len; ++t) {
         const size_t hb = (size_t)(sg.start + t) * C + hc;
-        const float k0 = k[hb + lane], k1 = k[hb + lane + 32], a0 = a[hb + lane], a1 = a[hb + lane + 32];
-        const float r0 = r[hb + lane], r1 = r[hb + lane + 32], w0 = w[hb + lane], w1 = w[hb + lane + 32];
-        float vj = v[hb + i];
-        const float gj = g[hb + i];
-        if (vgate) vj = vj + vgate[hb + i] * (vfirst[hb + i] - vj);
+        const WkvIn cur = nxt;
+        if (t + 1 < sg.len) nxt = wkv_load_inputs(r, k, v, vgate, vfirst, w, a, g, hb + C, lane, i);  // the next token's inputs, one token ahead
+        const float k0 = cur.k0, k1 = cur.k1, a0 = cur.a0, a1 = cur.a1, r0 = cur.r0, r1 = cur.r1, w0 = cur.w0, w1 = cur.w1;
+        const float vj = wkv_value(cur, vgate != nullptr);
+        const float gj = cur.g;
         const float kk0 = k0 * kkc0, kk1 = k1 * kkc1;
         const float ss = warp_sum(kk0 * kk0 + kk1 * kk1);
         const float inv = 1.0f / fmaxf(sqrtf(ss), kL2Eps);
@@ -517,28 +558,6 @@ __global__ void __launch_bounds__(kWkvThreads, 4) wkv7_kernel(const SegMeta* __r
     for (int jj = 0; jj < 4; ++jj) *reinterpret_cast<float4*>(srow + 16 * jj) = make_float4(S[4 * jj], S[4 * jj + 1], S[4 * jj + 2], S[4 * jj + 3]);
 }
 
-// The per-token inputs of one lane (two of the 64 channels, and the row's v and g), shared with the row-per-lane kernel for large
-// batches (wkv_rows.cuh).
-struct WkvIn {
-    float k0, k1, a0, a1, r0, r1, w0, w1, v, g;
-};
-__device__ __forceinline__ WkvIn wkv_load_inputs(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
-                                                 const float* __restrict__ vgate, const float* __restrict__ vfirst, const float* __restrict__ w,
-                                                 const float* __restrict__ a, const float* __restrict__ g, size_t hb, int lane, int i) {
-    WkvIn x;
-    x.k0 = k[hb + lane];
-    x.k1 = k[hb + lane + 32];
-    x.a0 = a[hb + lane];
-    x.a1 = a[hb + lane + 32];
-    x.r0 = r[hb + lane];
-    x.r1 = r[hb + lane + 32];
-    x.w0 = w[hb + lane];
-    x.w1 = w[hb + lane + 32];
-    x.v = v[hb + i];
-    x.g = g[hb + i];
-    if (vgate) x.v = x.v + vgate[hb + i] * (vfirst[hb + i] - x.v);
-    return x;
-}
 // ------------------------------------------------------------------------------------------------
 // arg-max over each logits row, ties -> smaller index (rwkv_argmax, src/backend_cuda.rs:3640-3680).
 // Writes the token to next_tok[row] (the next step's input) and appends it to the row's sequence

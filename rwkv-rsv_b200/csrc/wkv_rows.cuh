@@ -68,6 +68,14 @@ __global__ void __launch_bounds__(kWrThreads, 1) wkv7_rows_kernel(const __grid_c
     __syncthreads();
     pdl_launch_dependents();
     pdl_wait();  // the input vectors come from the predecessor kernels
+    r = pdl_fresh(r);
+    k = pdl_fresh(k);
+    v = pdl_fresh(v);
+    vgate = pdl_fresh(vgate);
+    vfirst = pdl_fresh(vfirst);
+    w = pdl_fresh(w);
+    a = pdl_fresh(a);
+    g = pdl_fresh(g);
     const int nvec = vgate ? kWrVecs : kWrVecs - 2;
     // segment descriptors run three items ahead in registers: the leader's copy addresses must not wait for a load of their own
     auto meta_of = [&](int n) { return n < my_items ? segs[(first + n * stride) / H] : SegMeta{0, 0, 0, 0}; };
@@ -125,7 +133,8 @@ __global__ void __launch_bounds__(kWrThreads, 1) wkv7_rows_kernel(const __grid_c
         cur.a0 = vs[4 * N + lane];
         cur.a1 = vs[4 * N + lane + 32];
         cur.g = vs[5 * N + rr];
-        if (vgate) cur.v = cur.v + vs[6 * N + rr] * (vs[7 * N + rr] - cur.v);
+        cur.vg = vgate ? vs[6 * N + rr] : 0.f;
+        cur.vf = vgate ? vs[7 * N + rr] : 0.f;
         const float kkc0 = vs[8 * N + lane], kkc1 = vs[8 * N + lane + 32], kac0 = vs[9 * N + lane], kac1 = vs[9 * N + lane + 32];
         const float rkc0 = vs[10 * N + lane], rkc1 = vs[10 * N + lane + 32], gw = vs[11 * N + rr], gb = vs[12 * N + rr];
         // the stage is free once both warps hold its contents: the data of item n + 2 may land in it
@@ -133,8 +142,9 @@ __global__ void __launch_bounds__(kWrThreads, 1) wkv7_rows_kernel(const __grid_c
         if (leader && n + kWrStages < my_items) issue_load(n + kWrStages, kWrStages == 1 ? sg1 : sg2);
         for (int t = 0; t < sg.len; ++t) {
             const size_t hb = (size_t)(sg.start + t) * C + hc;
-            if (t > 0) cur = wkv_load_inputs(r, k, v, vgate, vfirst, w, a, g, hb, lane, rr);
-            const float vj = cur.v;
+            WkvIn nx = cur;
+            if (t + 1 < sg.len) nx = wkv_load_inputs(r, k, v, vgate, vfirst, w, a, g, hb + C, lane, rr);  // the next token's inputs, one token ahead
+            const float vj = wkv_value(cur, vgate != nullptr);
             const float kk0 = cur.k0 * kkc0, kk1 = cur.k1 * kkc1;
             const float ss = warp_sum(kk0 * kk0 + kk1 * kk1);
             const float inv = 1.0f / fmaxf(sqrtf(ss), kL2Eps);
@@ -193,6 +203,7 @@ __global__ void __launch_bounds__(kWrThreads, 1) wkv7_rows_kernel(const __grid_c
             const float inv_std = 1.0f / sqrtf(var);
             yg[hb + rr] = (d * inv_std * gw + gb + srk * vj) * cur.g;
             if (v_first_state && t == sg.len - 1) v_first_state[(size_t)sg.slot * C + hc + rr] = vj;
+            cur = nx;
         }
         // updated rows -> staging tile (free once the previous item's stores have read it) -> TMA stores
         if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
