@@ -900,7 +900,11 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
         }
         LAUNCH(*this, "wkv7") {
             const int n_items = H * S;
-            if (n_items >= 4 * num_sms) {
+            if (plan.multi_row_segments) {
+                // prefill chunks: the form whose per-token chain holds only the state-dependent part
+                launch_pdl(*this, wkv7_seq_kernel, dim3(H, S), dim3(kWkvThreads), 0, ws.seg_meta, ws.r, ws.k, ws.v, vgate, ws.vfirst, ws.w, ws.a, ws.g, L.k_k,
+                           L.k_a, L.r_k, L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C);
+            } else if (n_items >= 4 * num_sms) {
                 // many (session, head) pairs: one state row per lane, states staged by TMA (wkv_rows.cuh)
                 const size_t rows_total = (size_t)cfg.n_layer * st.cap * H * kHeadSize;
                 if (rows_total >= (1ull << 31)) throw std::runtime_error("state too large for the 32-bit row coordinate of its tensor map");
