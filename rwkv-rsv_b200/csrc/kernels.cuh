@@ -626,15 +626,16 @@ __global__ void __launch_bounds__(kWkvThreads, 2) wkv7_seq_kernel(const SegMeta*
         if (t + 1 < sg.len) prep(c1, s_vec[warp][(t + 1) & 1]);
         float(*sv)[N] = s_vec[warp][t & 1];
         const float vj = wkv_value(c0, has_gate);
-        float sa = 0.f;
+        float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f;  // four short chains instead of one of sixteen
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
             const float4 kk4 = *reinterpret_cast<const float4*>(&sv[0][16 * jj + 4 * quad]);
-            sa = fmaf(S[4 * jj], kk4.x, sa);
-            sa = fmaf(S[4 * jj + 1], kk4.y, sa);
-            sa = fmaf(S[4 * jj + 2], kk4.z, sa);
-            sa = fmaf(S[4 * jj + 3], kk4.w, sa);
+            sa0 = fmaf(S[4 * jj], kk4.x, sa0);
+            sa1 = fmaf(S[4 * jj + 1], kk4.y, sa1);
+            sa2 = fmaf(S[4 * jj + 2], kk4.z, sa2);
+            sa3 = fmaf(S[4 * jj + 3], kk4.w, sa3);
         }
+        float sa = (sa0 + sa1) + (sa2 + sa3);
         sa += __shfl_xor_sync(0xffffffffu, sa, 1);
         sa += __shfl_xor_sync(0xffffffffu, sa, 2);
         float y = 0.f;
