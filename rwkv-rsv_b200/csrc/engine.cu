@@ -9,6 +9,7 @@
 #include "tc_linear.cuh"
 #include "decode_persistent.cuh"
 #include "wkv_rows.cuh"
+#include "wkv_seq.cuh"
 
 namespace rsv {
 
@@ -901,9 +902,11 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
         LAUNCH(*this, "wkv7") {
             const int n_items = H * S;
             if (plan.multi_row_segments) {
-                // prefill chunks: the form whose per-token chain holds only the state-dependent part
-                launch_pdl(*this, wkv7_seq_kernel, dim3(H, S), dim3(kWkvThreads), 0, ws.seg_meta, ws.r, ws.k, ws.v, vgate, ws.vfirst, ws.w, ws.a, ws.g, L.k_k,
-                           L.k_a, L.r_k, L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C);
+                // prefill chunks: vectors built by preparation warps, only state-dependent work in the per-token chain (wkv_seq.cuh)
+                launch_pdl(*this, wkv7_seq_kernel, dim3(H, S), dim3(kWsThreads), 0, ws.seg_meta, ws.r, ws.k, ws.v, vgate, ws.vfirst, ws.w, ws.a, ws.g, L.k_k,
+                           L.k_a, L.r_k, L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C, ws.status);
+                launch_pdl(*this, wkv7_finish_kernel, dim3((R * H + kWsFinishThreads / 32 - 1) / (kWsFinishThreads / 32)), dim3(kWsFinishThreads), 0, ws.r, ws.k,
+                           ws.v, vgate, ws.vfirst, ws.a, ws.g, L.k_a, L.r_k, L.lnx_w, L.lnx_b, ws.yg, R, H, C);
             } else if (n_items >= 4 * num_sms) {
                 // many (session, head) pairs: one state row per lane, states staged by TMA (wkv_rows.cuh)
                 const size_t rows_total = (size_t)cfg.n_layer * st.cap * H * kHeadSize;

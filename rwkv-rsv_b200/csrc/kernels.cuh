@@ -558,139 +558,6 @@ __global__ void __launch_bounds__(kWkvThreads, 4) wkv7_kernel(const SegMeta* __r
     for (int jj = 0; jj < 4; ++jj) *reinterpret_cast<float4*>(srow + 16 * jj) = make_float4(S[4 * jj], S[4 * jj + 1], S[4 * jj + 2], S[4 * jj + 3]);
 }
 
-// ---- the same update for steps with multi-token segments (prefill chunks) ----
-// Inside a segment the recurrence is sequential in the tokens, so the time of a chunk is (tokens) x (latency of one token's
-// chain).  This form keeps only what depends on the state in that chain: the five vectors of token t + 1 (normalised kk, w, b,
-// k~, r: inputs only) are built while token t is applied (two shared-memory buffers per warp, inputs requested two tokens
-// ahead), and GroupNorm, the bonus term and the gate - which need y but do not feed the state - run after the loop, one warp per
-// token, on the raw y the loop left in the output buffer.  No block barrier inside the loop: a warp owns eight state rows.
-__global__ void __launch_bounds__(kWkvThreads, 2) wkv7_seq_kernel(const SegMeta* __restrict__ segs, const float* __restrict__ r, const float* __restrict__ k,
-                                                                  const float* __restrict__ v, const float* __restrict__ vgate,
-                                                                  const float* __restrict__ vfirst, const float* __restrict__ w, const float* __restrict__ a,
-                                                                  const float* __restrict__ g, const float* __restrict__ k_k, const float* __restrict__ k_a,
-                                                                  const float* __restrict__ r_k, const float* __restrict__ lnx_w,
-                                                                  const float* __restrict__ lnx_b, float* __restrict__ state, float* __restrict__ v_first_state,
-                                                                  float* yg, int H, int C) {
-    constexpr int N = kHeadSize;
-    __shared__ __align__(16) float s_vec[kWkvThreads / 32][2][5][N];  // per warp, two tokens: kk, w, b, k~, r
-    const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, i = tid >> 2, quad = tid & 3;
-    pdl_launch_dependents();
-    const SegMeta sg = segs[blockIdx.y];  // plan data and state: written before the step's first kernel (see wkv7_kernel)
-    float* srow = state + (((size_t)sg.slot * H + h) * N + i) * N + quad * 4;
-    float S[16];
-#pragma unroll
-    for (int jj = 0; jj < 4; ++jj) {
-        const float4 t = *reinterpret_cast<const float4*>(srow + 16 * jj);
-        S[4 * jj] = t.x;
-        S[4 * jj + 1] = t.y;
-        S[4 * jj + 2] = t.z;
-        S[4 * jj + 3] = t.w;
-    }
-    pdl_wait();
-    r = pdl_fresh(r);
-    k = pdl_fresh(k);
-    v = pdl_fresh(v);
-    vgate = pdl_fresh(vgate);
-    vfirst = pdl_fresh(vfirst);
-    w = pdl_fresh(w);
-    a = pdl_fresh(a);
-    g = pdl_fresh(g);
-    const bool has_gate = vgate != nullptr;
-    const int hc = h * N;
-    const float kkc0 = k_k[hc + lane], kkc1 = k_k[hc + lane + 32], kac0 = k_a[hc + lane], kac1 = k_a[hc + lane + 32];
-    const float rkc0 = r_k[hc + lane], rkc1 = r_k[hc + lane + 32];
-    auto prep = [&](const WkvIn& x, float(*b)[N]) {
-        const float kk0 = x.k0 * kkc0, kk1 = x.k1 * kkc1;
-        const float ss = warp_sum(kk0 * kk0 + kk1 * kk1);
-        const float inv = 1.0f / fmaxf(sqrtf(ss), kL2Eps);
-        const float kh0 = kk0 * inv, kh1 = kk1 * inv;
-        b[0][lane] = kh0;
-        b[0][lane + 32] = kh1;
-        b[1][lane] = x.w0;
-        b[1][lane + 32] = x.w1;
-        b[2][lane] = kh0 * (-x.a0);
-        b[2][lane + 32] = kh1 * (-x.a1);
-        b[3][lane] = x.k0 + kac0 * (x.k0 * x.a0 - x.k0);
-        b[3][lane + 32] = x.k1 + kac1 * (x.k1 * x.a1 - x.k1);
-        b[4][lane] = x.r0;
-        b[4][lane + 32] = x.r1;
-    };
-    const size_t hb0 = (size_t)sg.start * C + hc;
-    WkvIn c0 = wkv_load_inputs(r, k, v, vgate, vfirst, w, a, g, hb0, lane, i);
-    WkvIn c1 = sg.len > 1 ? wkv_load_inputs(r, k, v, vgate, vfirst, w, a, g, hb0 + C, lane, i) : c0;
-    prep(c0, s_vec[warp][0]);
-    for (int t = 0; t < sg.len; ++t) {
-        const size_t hb = hb0 + (size_t)t * C;
-        const WkvIn c2 = t + 2 < sg.len ? wkv_load_inputs(r, k, v, vgate, vfirst, w, a, g, hb + 2 * (size_t)C, lane, i) : c1;
-        __syncwarp();  // this token's vectors are written; the other buffer's readers (token t - 1) are done
-        if (t + 1 < sg.len) prep(c1, s_vec[warp][(t + 1) & 1]);
-        float(*sv)[N] = s_vec[warp][t & 1];
-        const float vj = wkv_value(c0, has_gate);
-        float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f;  // four short chains instead of one of sixteen
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-            const float4 kk4 = *reinterpret_cast<const float4*>(&sv[0][16 * jj + 4 * quad]);
-            sa0 = fmaf(S[4 * jj], kk4.x, sa0);
-            sa1 = fmaf(S[4 * jj + 1], kk4.y, sa1);
-            sa2 = fmaf(S[4 * jj + 2], kk4.z, sa2);
-            sa3 = fmaf(S[4 * jj + 3], kk4.w, sa3);
-        }
-        float sa = (sa0 + sa1) + (sa2 + sa3);
-        sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-        sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-        float y = 0.f;
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-            const int c = 16 * jj + 4 * quad;
-            const float4 w4 = *reinterpret_cast<const float4*>(&sv[1][c]);
-            const float4 b4 = *reinterpret_cast<const float4*>(&sv[2][c]);
-            const float4 t4 = *reinterpret_cast<const float4*>(&sv[3][c]);
-            const float4 r4 = *reinterpret_cast<const float4*>(&sv[4][c]);
-            S[4 * jj] = fmaf(S[4 * jj], w4.x, fmaf(sa, b4.x, vj * t4.x));
-            S[4 * jj + 1] = fmaf(S[4 * jj + 1], w4.y, fmaf(sa, b4.y, vj * t4.y));
-            S[4 * jj + 2] = fmaf(S[4 * jj + 2], w4.z, fmaf(sa, b4.z, vj * t4.z));
-            S[4 * jj + 3] = fmaf(S[4 * jj + 3], w4.w, fmaf(sa, b4.w, vj * t4.w));
-            y = fmaf(S[4 * jj], r4.x, y);
-            y = fmaf(S[4 * jj + 1], r4.y, y);
-            y = fmaf(S[4 * jj + 2], r4.z, y);
-            y = fmaf(S[4 * jj + 3], r4.w, y);
-        }
-        y += __shfl_xor_sync(0xffffffffu, y, 1);
-        y += __shfl_xor_sync(0xffffffffu, y, 2);
-        if (quad == 0) {
-            yg[hb + i] = y;  // raw; finished below
-            if (v_first_state && t == sg.len - 1) v_first_state[(size_t)sg.slot * C + hc + i] = vj;
-        }
-        c0 = c1;
-        c1 = c2;
-    }
-#pragma unroll
-    for (int jj = 0; jj < 4; ++jj) *reinterpret_cast<float4*>(srow + 16 * jj) = make_float4(S[4 * jj], S[4 * jj + 1], S[4 * jj + 2], S[4 * jj + 3]);
-    __syncthreads();  // every raw y of the segment is in the output buffer (written by this CTA)
-    // GroupNorm (two-pass, like the CPU path), bonus term and gate: one warp per token, lane l holds rows l and l + 32
-    const float gw0 = lnx_w[hc + lane], gw1 = lnx_w[hc + lane + 32], gb0 = lnx_b[hc + lane], gb1 = lnx_b[hc + lane + 32];
-    for (int t = warp; t < sg.len; t += kWkvThreads / 32) {
-        const size_t hb = hb0 + (size_t)t * C;
-        const float y0 = yg[hb + lane], y1 = yg[hb + lane + 32];
-        const float k0 = k[hb + lane], k1 = k[hb + lane + 32], a0 = a[hb + lane], a1 = a[hb + lane + 32];
-        const float r0 = r[hb + lane], r1 = r[hb + lane + 32];
-        float v0 = v[hb + lane], v1 = v[hb + lane + 32];
-        const float g0 = g[hb + lane], g1 = g[hb + lane + 32];
-        if (has_gate) {
-            v0 = v0 + vgate[hb + lane] * (vfirst[hb + lane] - v0);
-            v1 = v1 + vgate[hb + lane + 32] * (vfirst[hb + lane + 32] - v1);
-        }
-        const float mean = warp_sum(y0 + y1) / (float)N;
-        const float d0 = y0 - mean, d1 = y1 - mean;
-        const float var = warp_sum(d0 * d0 + d1 * d1) / (float)N + kGnEps;
-        const float inv_std = 1.0f / sqrtf(var);
-        const float kt0 = k0 + kac0 * (k0 * a0 - k0), kt1 = k1 + kac1 * (k1 * a1 - k1);
-        const float srk = warp_sum(r0 * kt0 * rkc0 + r1 * kt1 * rkc1);
-        yg[hb + lane] = (d0 * inv_std * gw0 + gb0 + srk * v0) * g0;
-        yg[hb + lane + 32] = (d1 * inv_std * gw1 + gb1 + srk * v1) * g1;
-    }
-}
-
 // ------------------------------------------------------------------------------------------------
 // arg-max over each logits row, ties -> smaller index (rwkv_argmax, src/backend_cuda.rs:3640-3680).
 // Writes the token to next_tok[row] (the next step's input) and appends it to the row's sequence

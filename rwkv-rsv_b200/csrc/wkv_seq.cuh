@@ -1,0 +1,242 @@
+// WKV-7 state update for steps with multi-token segments (prefill chunks).  Same arithmetic as wkv7_kernel
+// (src/model.rs:436-471; rwkv_fuse_ka, rwkv_dplr_seq(_batch), GroupNorm and rwkv_sum_rk_rk of src/backend_cuda.rs).
+// Inside a segment the recurrence is sequential in the tokens, so the time of a chunk is (tokens) x (time of one token in the
+// warp that owns a state row).  The kernel therefore splits the work by role:
+//   * preparation warps read the token's inputs from global memory (several tokens ahead) and build the six vectors the
+//     recurrence needs (normalised kk, w, b = -kk a, k~, r, and the value v after its lerp) into a ring of token slots in
+//     shared memory; they alternate tokens, so a slot has one writer;
+//   * state warps (eight rows each, four lanes per row, sixteen state columns per lane) only wait for the slot, read the
+//     vectors and run the two row-times-vector products and the update: nothing but state-dependent work is in their chain;
+//   * slots are handed over with mbarriers (full: one arrival by the writer; empty: one arrival per state warp), so the state
+//     warps do not wait for one another;
+//   * GroupNorm, the bonus term and the gate need y but do not feed the state: the loop leaves the raw y in the output buffer and
+//     wkv7_finish_kernel applies them, one warp per (row, head) over the whole GPU.
+// Every mbarrier wait is bounded; on expiry bit 16 of the status word is set and the CTA's roles stop.
+#pragma once
+#include "kernels.cuh"
+#include "tc_linear.cuh"
+
+namespace rsv {
+
+constexpr int kWsStateWarps = 8;
+constexpr int kWsPrepWarps = 6;
+constexpr int kWsWarps = kWsStateWarps + kWsPrepWarps;
+constexpr int kWsThreads = 32 * kWsWarps;
+constexpr int kWsDepth = 12;  // token slots in the ring
+constexpr int kWsVecs = 6;   // kk, w, b, k~, r, v
+static_assert(kWsDepth % kWsPrepWarps == 0, "a ring slot must always be written by the same preparation warp");
+
+// The inputs of one token as a preparation warp holds them: channels `lane` and `lane + 32` of the head.  Loading does no
+// arithmetic, so that the loads of a later token can be in flight while an earlier one is processed.
+struct WsIn {
+    float k0, k1, a0, a1, r0, r1, w0, w1, v0, v1, vg0, vg1, vf0, vf1;
+};
+__device__ __forceinline__ WsIn ws_load(const float* r, const float* k, const float* v, const float* vgate, const float* vfirst, const float* w,
+                                        const float* a, size_t hb, int lane) {
+    WsIn x;
+    x.k0 = k[hb + lane];
+    x.k1 = k[hb + lane + 32];
+    x.a0 = a[hb + lane];
+    x.a1 = a[hb + lane + 32];
+    x.r0 = r[hb + lane];
+    x.r1 = r[hb + lane + 32];
+    x.w0 = w[hb + lane];
+    x.w1 = w[hb + lane + 32];
+    x.v0 = v[hb + lane];
+    x.v1 = v[hb + lane + 32];
+    x.vg0 = vgate ? vgate[hb + lane] : 0.f;
+    x.vg1 = vgate ? vgate[hb + lane + 32] : 0.f;
+    x.vf0 = vgate ? vfirst[hb + lane] : 0.f;
+    x.vf1 = vgate ? vfirst[hb + lane + 32] : 0.f;
+    return x;
+}
+
+// Grid (heads, segments).  `vgate` (layers > 0): v <- v + vgate * (vfirst - v), the lerp of src/model.rs:424-430.
+__global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* __restrict__ segs, const float* __restrict__ r, const float* __restrict__ k,
+                                                                 const float* __restrict__ v, const float* __restrict__ vgate,
+                                                                 const float* __restrict__ vfirst, const float* __restrict__ w, const float* __restrict__ a,
+                                                                 const float* __restrict__ g, const float* __restrict__ k_k, const float* __restrict__ k_a,
+                                                                 const float* __restrict__ r_k, const float* __restrict__ lnx_w,
+                                                                 const float* __restrict__ lnx_b, float* __restrict__ state, float* __restrict__ v_first_state,
+                                                                 float* yg, int H, int C, int* status) {
+    constexpr int N = kHeadSize;
+    __shared__ __align__(16) float ring[kWsDepth][kWsVecs][N];
+    __shared__ __align__(8) uint64_t full[kWsDepth], empty[kWsDepth];
+    __shared__ int s_abort;
+    const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int i = (tid >> 2) & (N - 1), quad = tid & 3;  // state warps: row and column quarter
+    if (tid == 0) {
+        for (int s = 0; s < kWsDepth; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kWsStateWarps);
+        }
+        s_abort = 0;
+    }
+    pdl_launch_dependents();
+    const SegMeta sg = segs[blockIdx.y];  // plan data and state: written before the step's first kernel (see wkv7_kernel)
+    const bool state_warp = warp < kWsStateWarps;
+    float* srow = state + (((size_t)sg.slot * H + h) * N + i) * N + quad * 4;
+    float S[16];
+    if (state_warp) {
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            const float4 t = *reinterpret_cast<const float4*>(srow + 16 * jj);
+            S[4 * jj] = t.x;
+            S[4 * jj + 1] = t.y;
+            S[4 * jj + 2] = t.z;
+            S[4 * jj + 3] = t.w;
+        }
+    }
+    __syncthreads();  // barriers initialised
+    pdl_wait();
+    r = pdl_fresh(r);
+    k = pdl_fresh(k);
+    v = pdl_fresh(v);
+    vgate = pdl_fresh(vgate);
+    vfirst = pdl_fresh(vfirst);
+    w = pdl_fresh(w);
+    a = pdl_fresh(a);
+    g = pdl_fresh(g);
+    const bool has_gate = vgate != nullptr;
+    const int hc = h * N;
+    const size_t hb0 = (size_t)sg.start * C + hc;
+    if (!state_warp) {
+        // ---- preparation: tokens p, p + P, p + 2P, ... ----
+        const int p = warp - kWsStateWarps;
+        const float kkc0 = k_k[hc + lane], kkc1 = k_k[hc + lane + 32], kac0 = k_a[hc + lane], kac1 = k_a[hc + lane + 32];
+        const int last = sg.len - 1;
+        // The warp's next token is requested before the current one is processed; a token's memory round trip is covered by
+        // the number of preparation warps, not by deeper register pipelines (a rotated register waits for its load).
+        WsIn c0 = ws_load(r, k, v, vgate, vfirst, w, a, hb0 + (size_t)min(p, last) * C, lane);
+        for (int t = p; t < sg.len; t += kWsPrepWarps) {
+            const WsIn c1 = ws_load(r, k, v, vgate, vfirst, w, a, hb0 + (size_t)min(t + kWsPrepWarps, last) * C, lane);
+            const int slot = t % kWsDepth, use = t / kWsDepth;
+            const float kk0 = c0.k0 * kkc0, kk1 = c0.k1 * kkc1;
+            const float ss = warp_sum(kk0 * kk0 + kk1 * kk1);
+            const float inv = 1.0f / fmaxf(sqrtf(ss), kL2Eps);
+            const float kh0 = kk0 * inv, kh1 = kk1 * inv;
+            const float v0 = has_gate ? c0.v0 + c0.vg0 * (c0.vf0 - c0.v0) : c0.v0;
+            const float v1 = has_gate ? c0.v1 + c0.vg1 * (c0.vf1 - c0.v1) : c0.v1;
+            if (use > 0 && !mbar_wait(&empty[slot], (uint32_t)(use - 1) & 1u, &s_abort)) {
+                if (lane == 0) atomicOr(status, 16);
+                break;
+            }
+            float(*b)[N] = ring[slot];
+            b[0][lane] = kh0;
+            b[0][lane + 32] = kh1;
+            b[1][lane] = c0.w0;
+            b[1][lane + 32] = c0.w1;
+            b[2][lane] = kh0 * (-c0.a0);
+            b[2][lane + 32] = kh1 * (-c0.a1);
+            b[3][lane] = c0.k0 + kac0 * (c0.k0 * c0.a0 - c0.k0);
+            b[3][lane + 32] = c0.k1 + kac1 * (c0.k1 * c0.a1 - c0.k1);
+            b[4][lane] = c0.r0;
+            b[4][lane + 32] = c0.r1;
+            b[5][lane] = v0;
+            b[5][lane + 32] = v1;
+            __syncwarp();  // the warp's stores are ordered before lane 0's arrival (release)
+            if (lane == 0) mbar_arrive(&full[slot]);
+            if (v_first_state && t == last) {
+                v_first_state[(size_t)sg.slot * C + hc + lane] = v0;
+                v_first_state[(size_t)sg.slot * C + hc + lane + 32] = v1;
+            }
+            c0 = c1;
+        }
+    } else {
+        // ---- state rows: wait for the token's slot, apply it, release the slot ----
+        for (int t = 0; t < sg.len; ++t) {
+            const int slot = t % kWsDepth, use = t / kWsDepth;
+            if (!mbar_wait(&full[slot], (uint32_t)use & 1u, &s_abort)) {
+                if (lane == 0) atomicOr(status, 16);
+                break;
+            }
+            const float(*sv)[N] = ring[slot];
+            const float vj = sv[5][i];
+            float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f;  // four short chains instead of one of sixteen
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const float4 kk4 = *reinterpret_cast<const float4*>(&sv[0][16 * jj + 4 * quad]);
+                sa0 = fmaf(S[4 * jj], kk4.x, sa0);
+                sa1 = fmaf(S[4 * jj + 1], kk4.y, sa1);
+                sa2 = fmaf(S[4 * jj + 2], kk4.z, sa2);
+                sa3 = fmaf(S[4 * jj + 3], kk4.w, sa3);
+            }
+            float sa = (sa0 + sa1) + (sa2 + sa3);
+            sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+            sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+            float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const int c = 16 * jj + 4 * quad;
+                const float4 w4 = *reinterpret_cast<const float4*>(&sv[1][c]);
+                const float4 b4 = *reinterpret_cast<const float4*>(&sv[2][c]);
+                const float4 t4 = *reinterpret_cast<const float4*>(&sv[3][c]);
+                const float4 r4 = *reinterpret_cast<const float4*>(&sv[4][c]);
+                S[4 * jj] = fmaf(S[4 * jj], w4.x, fmaf(sa, b4.x, vj * t4.x));
+                S[4 * jj + 1] = fmaf(S[4 * jj + 1], w4.y, fmaf(sa, b4.y, vj * t4.y));
+                S[4 * jj + 2] = fmaf(S[4 * jj + 2], w4.z, fmaf(sa, b4.z, vj * t4.z));
+                S[4 * jj + 3] = fmaf(S[4 * jj + 3], w4.w, fmaf(sa, b4.w, vj * t4.w));
+                y0 = fmaf(S[4 * jj], r4.x, y0);
+                y1 = fmaf(S[4 * jj + 1], r4.y, y1);
+                y2 = fmaf(S[4 * jj + 2], r4.z, y2);
+                y3 = fmaf(S[4 * jj + 3], r4.w, y3);
+            }
+            __syncwarp();  // every lane has read the slot
+            if (lane == 0) mbar_arrive(&empty[slot]);
+            float y = (y0 + y1) + (y2 + y3);
+            y += __shfl_xor_sync(0xffffffffu, y, 1);
+            y += __shfl_xor_sync(0xffffffffu, y, 2);
+            if (quad == 0) yg[hb0 + (size_t)t * C + i] = y;  // raw; finished by wkv7_finish_kernel
+        }
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) *reinterpret_cast<float4*>(srow + 16 * jj) = make_float4(S[4 * jj], S[4 * jj + 1], S[4 * jj + 2], S[4 * jj + 3]);
+    }
+}
+
+// GroupNorm over a head's 64 outputs (two-pass, like the CPU path), the bonus term (r . k~ r_k) v and the gate, on the raw y that
+// wkv7_seq_kernel left in `yg`: one warp per (row, head), lane l holds channels l and l + 32.  These need y but do not feed the
+// state, so they are kept out of the sequential loop and spread over the whole GPU here.
+constexpr int kWsFinishThreads = 256;
+__global__ void __launch_bounds__(kWsFinishThreads) wkv7_finish_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
+                                                                       const float* __restrict__ vgate, const float* __restrict__ vfirst,
+                                                                       const float* __restrict__ a, const float* __restrict__ g, const float* __restrict__ k_a,
+                                                                       const float* __restrict__ r_k, const float* __restrict__ lnx_w,
+                                                                       const float* __restrict__ lnx_b, float* yg, int R, int H, int C) {
+    constexpr int N = kHeadSize;
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * (kWsFinishThreads / 32) + (threadIdx.x >> 5);
+    pdl_launch_dependents();
+    if (item >= R * H) return;
+    const int row = item / H, h = item - row * H, hc = h * N;
+    const float kac0 = k_a[hc + lane], kac1 = k_a[hc + lane + 32], rkc0 = r_k[hc + lane], rkc1 = r_k[hc + lane + 32];
+    const float gw0 = lnx_w[hc + lane], gw1 = lnx_w[hc + lane + 32], gb0 = lnx_b[hc + lane], gb1 = lnx_b[hc + lane + 32];
+    pdl_wait();
+    r = pdl_fresh(r);
+    k = pdl_fresh(k);
+    v = pdl_fresh(v);
+    vgate = pdl_fresh(vgate);
+    vfirst = pdl_fresh(vfirst);
+    a = pdl_fresh(a);
+    g = pdl_fresh(g);
+    yg = pdl_fresh(yg);
+    const size_t hb = (size_t)row * C + hc;
+    const float y0 = yg[hb + lane], y1 = yg[hb + lane + 32];
+    const float k0 = k[hb + lane], k1 = k[hb + lane + 32], a0 = a[hb + lane], a1 = a[hb + lane + 32];
+    const float r0 = r[hb + lane], r1 = r[hb + lane + 32];
+    float v0 = v[hb + lane], v1 = v[hb + lane + 32];
+    const float g0 = g[hb + lane], g1 = g[hb + lane + 32];
+    if (vgate != nullptr) {
+        v0 = v0 + vgate[hb + lane] * (vfirst[hb + lane] - v0);
+        v1 = v1 + vgate[hb + lane + 32] * (vfirst[hb + lane + 32] - v1);
+    }
+    const float mean = warp_sum(y0 + y1) / (float)N;
+    const float d0 = y0 - mean, d1 = y1 - mean;
+    const float var = warp_sum(d0 * d0 + d1 * d1) / (float)N + kGnEps;
+    const float inv_std = 1.0f / sqrtf(var);
+    const float kt0 = k0 + kac0 * (k0 * a0 - k0), kt1 = k1 + kac1 * (k1 * a1 - k1);
+    const float srk = warp_sum(r0 * kt0 * rkc0 + r1 * kt1 * rkc1);
+    yg[hb + lane] = (d0 * inv_std * gw0 + gb0 + srk * v0) * g0;
+    yg[hb + lane + 32] = (d1 * inv_std * gw1 + gb1 + srk * v1) * g1;
+}
+
+}  // namespace rsv
