@@ -5,8 +5,9 @@
 //   * preparation warps read the token's inputs from global memory (several tokens ahead) and build the six vectors the
 //     recurrence needs (normalised kk, w, b = -kk a, k~, r, and the value v after its lerp) into a ring of token slots in
 //     shared memory; they alternate tokens, so a slot has one writer;
-//   * state warps (eight rows each, four lanes per row, sixteen state columns per lane) only wait for the slot, read the
-//     vectors and run the two row-times-vector products and the update: nothing but state-dependent work is in their chain;
+//   * state warps (sixteen rows each; eight lanes share four rows, eight state columns of each per lane) only wait for the
+//     slot, read the vectors and run the two row-times-vector products and the update: nothing but state-dependent work is
+//     in their chain, and every vector element read from shared memory serves four rows;
 //   * slots are handed over with mbarriers (full: one arrival by the writer; empty: one arrival per state warp), so the state
 //     warps do not wait for one another;
 //   * GroupNorm, the bonus term and the gate need y but do not feed the state: the loop leaves the raw y in the output buffer and
@@ -18,7 +19,7 @@
 
 namespace rsv {
 
-constexpr int kWsStateWarps = 8;
+constexpr int kWsStateWarps = 4;  // 16 state rows each
 constexpr int kWsPrepWarps = 6;
 constexpr int kWsWarps = kWsStateWarps + kWsPrepWarps;
 constexpr int kWsThreads = 32 * kWsWarps;
@@ -51,6 +52,13 @@ __device__ __forceinline__ WsIn ws_load(const float* r, const float* k, const fl
     return x;
 }
 
+// A lane's eight columns of one of the ring's vectors.
+__device__ __forceinline__ void ws_vec8(float (&d)[8], const float* vec, int sub) {
+    const float4 lo = *reinterpret_cast<const float4*>(vec + 4 * sub), hi = *reinterpret_cast<const float4*>(vec + 32 + 4 * sub);
+    d[0] = lo.x, d[1] = lo.y, d[2] = lo.z, d[3] = lo.w;
+    d[4] = hi.x, d[5] = hi.y, d[6] = hi.z, d[7] = hi.w;
+}
+
 // Grid (heads, segments).  `vgate` (layers > 0): v <- v + vgate * (vfirst - v), the lerp of src/model.rs:424-430.
 __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* __restrict__ segs, const float* __restrict__ r, const float* __restrict__ k,
                                                                  const float* __restrict__ v, const float* __restrict__ vgate,
@@ -64,7 +72,11 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
     __shared__ __align__(8) uint64_t full[kWsDepth], empty[kWsDepth];
     __shared__ int s_abort;
     const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int i = (tid >> 2) & (N - 1), quad = tid & 3;  // state warps: row and column quarter
+    // state warps: a group of eight lanes owns four rows; lane `sub` of the group holds columns 4 sub .. 4 sub + 3 and
+    // 32 + 4 sub .. 32 + 4 sub + 3 of them (a group's 16-byte reads of a vector are contiguous: no bank conflicts), so a vector
+    // element read from shared memory is used for four rows.  Shared-memory bandwidth, not arithmetic, bounds this loop: with
+    // one row per lane the eight warps of a head read 80 KB of vectors per token.
+    const int sub = lane & 7, row0 = (warp & (kWsStateWarps - 1)) * 16 + (lane >> 3) * 4;
     if (tid == 0) {
         for (int s = 0; s < kWsDepth; ++s) {
             mbar_init(&full[s], 1);
@@ -75,16 +87,14 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
     pdl_launch_dependents();
     const SegMeta sg = segs[blockIdx.y];  // plan data and state: written before the step's first kernel (see wkv7_kernel)
     const bool state_warp = warp < kWsStateWarps;
-    float* srow = state + (((size_t)sg.slot * H + h) * N + i) * N + quad * 4;
-    float S[16];
+    float* sbase = state + (((size_t)sg.slot * H + h) * N + row0) * N + 4 * sub;
+    float S[4][8];
     if (state_warp) {
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-            const float4 t = *reinterpret_cast<const float4*>(srow + 16 * jj);
-            S[4 * jj] = t.x;
-            S[4 * jj + 1] = t.y;
-            S[4 * jj + 2] = t.z;
-            S[4 * jj + 3] = t.w;
+        for (int rr = 0; rr < 4; ++rr) {
+            const float4 lo = *reinterpret_cast<const float4*>(sbase + rr * N), hi = *reinterpret_cast<const float4*>(sbase + rr * N + 32);
+            S[rr][0] = lo.x, S[rr][1] = lo.y, S[rr][2] = lo.z, S[rr][3] = lo.w;
+            S[rr][4] = hi.x, S[rr][5] = hi.y, S[rr][6] = hi.z, S[rr][7] = hi.w;
         }
     }
     __syncthreads();  // barriers initialised
@@ -151,45 +161,50 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
                 break;
             }
             const float(*sv)[N] = ring[slot];
-            const float vj = sv[5][i];
-            float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f;  // four short chains instead of one of sixteen
+            float vec[8];
+            ws_vec8(vec, sv[0], sub);  // kk
+            const float4 v4 = *reinterpret_cast<const float4*>(&sv[5][row0]);
+            const float vj[4] = {v4.x, v4.y, v4.z, v4.w};
+            float sa[4];
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-                const float4 kk4 = *reinterpret_cast<const float4*>(&sv[0][16 * jj + 4 * quad]);
-                sa0 = fmaf(S[4 * jj], kk4.x, sa0);
-                sa1 = fmaf(S[4 * jj + 1], kk4.y, sa1);
-                sa2 = fmaf(S[4 * jj + 2], kk4.z, sa2);
-                sa3 = fmaf(S[4 * jj + 3], kk4.w, sa3);
+            for (int rr = 0; rr < 4; ++rr) {
+                const float lo = fmaf(S[rr][3], vec[3], fmaf(S[rr][2], vec[2], fmaf(S[rr][1], vec[1], S[rr][0] * vec[0])));
+                const float hi = fmaf(S[rr][7], vec[7], fmaf(S[rr][6], vec[6], fmaf(S[rr][5], vec[5], S[rr][4] * vec[4])));
+                sa[rr] = lo + hi;
             }
-            float sa = (sa0 + sa1) + (sa2 + sa3);
-            sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-            sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-            float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-                const int c = 16 * jj + 4 * quad;
-                const float4 w4 = *reinterpret_cast<const float4*>(&sv[1][c]);
-                const float4 b4 = *reinterpret_cast<const float4*>(&sv[2][c]);
-                const float4 t4 = *reinterpret_cast<const float4*>(&sv[3][c]);
-                const float4 r4 = *reinterpret_cast<const float4*>(&sv[4][c]);
-                S[4 * jj] = fmaf(S[4 * jj], w4.x, fmaf(sa, b4.x, vj * t4.x));
-                S[4 * jj + 1] = fmaf(S[4 * jj + 1], w4.y, fmaf(sa, b4.y, vj * t4.y));
-                S[4 * jj + 2] = fmaf(S[4 * jj + 2], w4.z, fmaf(sa, b4.z, vj * t4.z));
-                S[4 * jj + 3] = fmaf(S[4 * jj + 3], w4.w, fmaf(sa, b4.w, vj * t4.w));
-                y0 = fmaf(S[4 * jj], r4.x, y0);
-                y1 = fmaf(S[4 * jj + 1], r4.y, y1);
-                y2 = fmaf(S[4 * jj + 2], r4.z, y2);
-                y3 = fmaf(S[4 * jj + 3], r4.w, y3);
+            for (int m = 1; m < 8; m <<= 1) {
+#pragma unroll
+                for (int rr = 0; rr < 4; ++rr) sa[rr] += __shfl_xor_sync(0xffffffffu, sa[rr], m);
             }
-            __syncwarp();  // every lane has read the slot
+            float wv[8], bv[8], tv[8];
+            ws_vec8(wv, sv[1], sub);
+            ws_vec8(bv, sv[2], sub);
+            ws_vec8(tv, sv[3], sub);
+            ws_vec8(vec, sv[4], sub);  // r
+            __syncwarp();              // every lane has read the slot
             if (lane == 0) mbar_arrive(&empty[slot]);
-            float y = (y0 + y1) + (y2 + y3);
-            y += __shfl_xor_sync(0xffffffffu, y, 1);
-            y += __shfl_xor_sync(0xffffffffu, y, 2);
-            if (quad == 0) yg[hb0 + (size_t)t * C + i] = y;  // raw; finished by wkv7_finish_kernel
+            float y[4];
+#pragma unroll
+            for (int rr = 0; rr < 4; ++rr) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) S[rr][c] = fmaf(S[rr][c], wv[c], fmaf(sa[rr], bv[c], vj[rr] * tv[c]));
+                const float lo = fmaf(S[rr][3], vec[3], fmaf(S[rr][2], vec[2], fmaf(S[rr][1], vec[1], S[rr][0] * vec[0])));
+                const float hi = fmaf(S[rr][7], vec[7], fmaf(S[rr][6], vec[6], fmaf(S[rr][5], vec[5], S[rr][4] * vec[4])));
+                y[rr] = lo + hi;
+            }
+#pragma unroll
+            for (int m = 1; m < 8; m <<= 1) {
+#pragma unroll
+                for (int rr = 0; rr < 4; ++rr) y[rr] += __shfl_xor_sync(0xffffffffu, y[rr], m);
+            }
+            if (sub == 0) *reinterpret_cast<float4*>(&yg[hb0 + (size_t)t * C + row0]) = make_float4(y[0], y[1], y[2], y[3]);  // raw; finished by wkv7_finish_kernel
         }
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) *reinterpret_cast<float4*>(srow + 16 * jj) = make_float4(S[4 * jj], S[4 * jj + 1], S[4 * jj + 2], S[4 * jj + 3]);
+        for (int rr = 0; rr < 4; ++rr) {
+            *reinterpret_cast<float4*>(sbase + rr * N) = make_float4(S[rr][0], S[rr][1], S[rr][2], S[rr][3]);
+            *reinterpret_cast<float4*>(sbase + rr * N + 32) = make_float4(S[rr][4], S[rr][5], S[rr][6], S[rr][7]);
+        }
     }
 }
 
