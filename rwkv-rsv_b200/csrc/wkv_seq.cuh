@@ -8,8 +8,8 @@
 //   * state warps (sixteen rows each; eight lanes share four rows, eight state columns of each per lane) only wait for the
 //     slot, read the vectors and run the two row-times-vector products and the update: nothing but state-dependent work is
 //     in their chain, and every vector element read from shared memory serves four rows;
-//   * slots are handed over with mbarriers (full: one arrival by the writer; empty: one arrival per state warp), so the state
-//     warps do not wait for one another;
+//   * slots are handed over in groups of four tokens with mbarriers (full: one arrival per token by its writer; empty: one
+//     arrival per state warp), so the state warps do not wait for one another;
 //   * GroupNorm, the bonus term and the gate need y but do not feed the state: the loop leaves the raw y in the output buffer and
 //     wkv7_finish_kernel applies them, one warp per (row, head) over the whole GPU.
 // Every mbarrier wait is bounded; on expiry bit 16 of the status word is set and the CTA's roles stop.
@@ -23,7 +23,10 @@ constexpr int kWsStateWarps = 4;  // 16 state rows each
 constexpr int kWsPrepWarps = 6;
 constexpr int kWsWarps = kWsStateWarps + kWsPrepWarps;
 constexpr int kWsThreads = 32 * kWsWarps;
+constexpr int kWsGroup = 4;   // tokens handed over per barrier phase
 constexpr int kWsDepth = 12;  // token slots in the ring
+constexpr int kWsGroups = kWsDepth / kWsGroup;
+static_assert(kWsDepth % kWsGroup == 0 && kWsGroup <= kWsPrepWarps, "a group's tokens are written by different preparation warps");
 constexpr int kWsVecs = 6;   // kk, w, b, k~, r, v
 static_assert(kWsDepth % kWsPrepWarps == 0, "a ring slot must always be written by the same preparation warp");
 
@@ -69,7 +72,7 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
                                                                  float* yg, int H, int C, int* status) {
     constexpr int N = kHeadSize;
     __shared__ __align__(16) float ring[kWsDepth][kWsVecs][N];
-    __shared__ __align__(8) uint64_t full[kWsDepth], empty[kWsDepth];
+    __shared__ __align__(8) uint64_t full[kWsGroups], empty[kWsGroups];
     __shared__ int s_abort;
     const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // state warps: a group of eight lanes owns four rows; lane `sub` of the group holds columns 4 sub .. 4 sub + 3 and
@@ -78,8 +81,8 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
     // one row per lane the eight warps of a head read 80 KB of vectors per token.
     const int sub = lane & 7, row0 = (warp & (kWsStateWarps - 1)) * 16 + (lane >> 3) * 4;
     if (tid == 0) {
-        for (int s = 0; s < kWsDepth; ++s) {
-            mbar_init(&full[s], 1);
+        for (int s = 0; s < kWsGroups; ++s) {
+            mbar_init(&full[s], kWsGroup);
             mbar_init(&empty[s], kWsStateWarps);
         }
         s_abort = 0;
@@ -118,16 +121,18 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
         // The warp's next token is requested before the current one is processed; a token's memory round trip is covered by
         // the number of preparation warps, not by deeper register pipelines (a rotated register waits for its load).
         WsIn c0 = ws_load(r, k, v, vgate, vfirst, w, a, hb0 + (size_t)min(p, last) * C, lane);
-        for (int t = p; t < sg.len; t += kWsPrepWarps) {
+        // the last group is filled up with repeats of the last token, so that its barrier completes
+        const int len_pad = (sg.len + kWsGroup - 1) / kWsGroup * kWsGroup;
+        for (int t = p; t < len_pad; t += kWsPrepWarps) {
             const WsIn c1 = ws_load(r, k, v, vgate, vfirst, w, a, hb0 + (size_t)min(t + kWsPrepWarps, last) * C, lane);
-            const int slot = t % kWsDepth, use = t / kWsDepth;
+            const int slot = t % kWsDepth, grp = slot / kWsGroup, use = t / kWsDepth;
             const float kk0 = c0.k0 * kkc0, kk1 = c0.k1 * kkc1;
             const float ss = warp_sum(kk0 * kk0 + kk1 * kk1);
             const float inv = 1.0f / fmaxf(sqrtf(ss), kL2Eps);
             const float kh0 = kk0 * inv, kh1 = kk1 * inv;
             const float v0 = has_gate ? c0.v0 + c0.vg0 * (c0.vf0 - c0.v0) : c0.v0;
             const float v1 = has_gate ? c0.v1 + c0.vg1 * (c0.vf1 - c0.v1) : c0.v1;
-            if (use > 0 && !mbar_wait(&empty[slot], (uint32_t)(use - 1) & 1u, &s_abort)) {
+            if (use > 0 && !mbar_wait(&empty[grp], (uint32_t)(use - 1) & 1u, &s_abort)) {
                 if (lane == 0) atomicOr(status, 16);
                 break;
             }
@@ -145,7 +150,7 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
             b[5][lane] = v0;
             b[5][lane + 32] = v1;
             __syncwarp();  // the warp's stores are ordered before lane 0's arrival (release)
-            if (lane == 0) mbar_arrive(&full[slot]);
+            if (lane == 0) mbar_arrive(&full[grp]);
             if (v_first_state && t == last) {
                 v_first_state[(size_t)sg.slot * C + hc + lane] = v0;
                 v_first_state[(size_t)sg.slot * C + hc + lane + 32] = v1;
@@ -153,13 +158,10 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
             c0 = c1;
         }
     } else {
-        // ---- state rows: wait for the token's slot, apply it, release the slot ----
-        for (int t = 0; t < sg.len; ++t) {
-            const int slot = t % kWsDepth, use = t / kWsDepth;
-            if (!mbar_wait(&full[slot], (uint32_t)use & 1u, &s_abort)) {
-                if (lane == 0) atomicOr(status, 16);
-                break;
-            }
+        // ---- state rows: wait for a group of tokens, apply them, release the group ----
+        // One wait and one arrival per group: a successful wait still costs its latency and keeps the compiler from moving the
+        // next token's shared-memory reads above it.
+        auto token = [&](int t, int slot) {
             const float(*sv)[N] = ring[slot];
             float vec[8];
             ws_vec8(vec, sv[0], sub);  // kk
@@ -182,8 +184,6 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
             ws_vec8(bv, sv[2], sub);
             ws_vec8(tv, sv[3], sub);
             ws_vec8(vec, sv[4], sub);  // r
-            __syncwarp();              // every lane has read the slot
-            if (lane == 0) mbar_arrive(&empty[slot]);
             float y[4];
 #pragma unroll
             for (int rr = 0; rr < 4; ++rr) {
@@ -199,6 +199,21 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
                 for (int rr = 0; rr < 4; ++rr) y[rr] += __shfl_xor_sync(0xffffffffu, y[rr], m);
             }
             if (sub == 0) *reinterpret_cast<float4*>(&yg[hb0 + (size_t)t * C + row0]) = make_float4(y[0], y[1], y[2], y[3]);  // raw; finished by wkv7_finish_kernel
+        };
+        for (int t0 = 0; t0 < sg.len; t0 += kWsGroup) {
+            const int slot0 = t0 % kWsDepth, grp = slot0 / kWsGroup, use = t0 / kWsDepth;
+            if (!mbar_wait(&full[grp], (uint32_t)use & 1u, &s_abort)) {
+                if (lane == 0) atomicOr(status, 16);
+                break;
+            }
+            if (t0 + kWsGroup <= sg.len) {
+#pragma unroll
+                for (int j = 0; j < kWsGroup; ++j) token(t0 + j, slot0 + j);
+            } else {
+                for (int j = 0; t0 + j < sg.len; ++j) token(t0 + j, slot0 + j);
+            }
+            __syncwarp();  // every lane has read the group
+            if (lane == 0) mbar_arrive(&empty[grp]);
         }
 #pragma unroll
         for (int rr = 0; rr < 4; ++rr) {
