@@ -161,6 +161,8 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
         // ---- state rows: wait for a group of tokens, apply them, release the group ----
         // One wait and one arrival per group: a successful wait still costs its latency and keeps the compiler from moving the
         // next token's shared-memory reads above it.
+        float yp[4] = {0.f, 0.f, 0.f, 0.f};  // the previous token's partial row sums of y
+        bool gave_up = false;
         auto token = [&](int t, int slot) {
             const float(*sv)[N] = ring[slot];
             float vec[8];
@@ -174,36 +176,36 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
                 const float hi = fmaf(S[rr][7], vec[7], fmaf(S[rr][6], vec[6], fmaf(S[rr][5], vec[5], S[rr][4] * vec[4])));
                 sa[rr] = lo + hi;
             }
+            // one reduction tree for this token's sa and the previous token's y: only sa is in the recurrence, and y(t - 1)
+            // would otherwise add a second three-level shuffle latency to every token
 #pragma unroll
             for (int m = 1; m < 8; m <<= 1) {
 #pragma unroll
-                for (int rr = 0; rr < 4; ++rr) sa[rr] += __shfl_xor_sync(0xffffffffu, sa[rr], m);
+                for (int rr = 0; rr < 4; ++rr) {
+                    sa[rr] += __shfl_xor_sync(0xffffffffu, sa[rr], m);
+                    yp[rr] += __shfl_xor_sync(0xffffffffu, yp[rr], m);
+                }
             }
+            if (sub == 0 && t > 0) *reinterpret_cast<float4*>(&yg[hb0 + (size_t)(t - 1) * C + row0]) = make_float4(yp[0], yp[1], yp[2], yp[3]);  // raw; finished by wkv7_finish_kernel
             float wv[8], bv[8], tv[8];
             ws_vec8(wv, sv[1], sub);
             ws_vec8(bv, sv[2], sub);
             ws_vec8(tv, sv[3], sub);
             ws_vec8(vec, sv[4], sub);  // r
-            float y[4];
 #pragma unroll
             for (int rr = 0; rr < 4; ++rr) {
 #pragma unroll
                 for (int c = 0; c < 8; ++c) S[rr][c] = fmaf(S[rr][c], wv[c], fmaf(sa[rr], bv[c], vj[rr] * tv[c]));
                 const float lo = fmaf(S[rr][3], vec[3], fmaf(S[rr][2], vec[2], fmaf(S[rr][1], vec[1], S[rr][0] * vec[0])));
                 const float hi = fmaf(S[rr][7], vec[7], fmaf(S[rr][6], vec[6], fmaf(S[rr][5], vec[5], S[rr][4] * vec[4])));
-                y[rr] = lo + hi;
+                yp[rr] = lo + hi;
             }
-#pragma unroll
-            for (int m = 1; m < 8; m <<= 1) {
-#pragma unroll
-                for (int rr = 0; rr < 4; ++rr) y[rr] += __shfl_xor_sync(0xffffffffu, y[rr], m);
-            }
-            if (sub == 0) *reinterpret_cast<float4*>(&yg[hb0 + (size_t)t * C + row0]) = make_float4(y[0], y[1], y[2], y[3]);  // raw; finished by wkv7_finish_kernel
         };
         for (int t0 = 0; t0 < sg.len; t0 += kWsGroup) {
             const int slot0 = t0 % kWsDepth, grp = slot0 / kWsGroup, use = t0 / kWsDepth;
             if (!mbar_wait(&full[grp], (uint32_t)use & 1u, &s_abort)) {
                 if (lane == 0) atomicOr(status, 16);
+                gave_up = true;
                 break;
             }
             if (t0 + kWsGroup <= sg.len) {
@@ -214,6 +216,14 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
             }
             __syncwarp();  // every lane has read the group
             if (lane == 0) mbar_arrive(&empty[grp]);
+        }
+        if (!gave_up) {  // the last token's y
+#pragma unroll
+            for (int m = 1; m < 8; m <<= 1) {
+#pragma unroll
+                for (int rr = 0; rr < 4; ++rr) yp[rr] += __shfl_xor_sync(0xffffffffu, yp[rr], m);
+            }
+            if (sub == 0) *reinterpret_cast<float4*>(&yg[hb0 + (size_t)(sg.len - 1) * C + row0]) = make_float4(yp[0], yp[1], yp[2], yp[3]);
         }
 #pragma unroll
         for (int rr = 0; rr < 4; ++rr) {
