@@ -903,8 +903,14 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
             const int n_items = H * S;
             if (plan.multi_row_segments) {
                 // prefill chunks: vectors built by preparation warps, only state-dependent work in the per-token chain (wkv_seq.cuh)
-                launch_pdl(*this, wkv7_seq_kernel, dim3(H, S), dim3(kWsThreads), 0, ws.seg_meta, ws.r, ws.k, ws.v, vgate, ws.vfirst, ws.w, ws.a, ws.g, L.k_k,
-                           L.k_a, L.r_k, L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C, ws.status);
+// few (head, segment) pairs: a head over two CTAs
+                if (H * S <= num_sms) {
+                    launch_pdl(*this, wkv7_seq_kernel<2>, dim3(2 * H, S), dim3(kWsThreads), 0, ws.seg_meta, ws.r, ws.k, ws.v, vgate, ws.vfirst, ws.w, ws.a, ws.g,
+                               L.k_k, L.k_a, L.r_k, L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C, ws.status);
+                } else {
+                    launch_pdl(*this, wkv7_seq_kernel<4>, dim3(H, S), dim3(kWsThreads), 0, ws.seg_meta, ws.r, ws.k, ws.v, vgate, ws.vfirst, ws.w, ws.a, ws.g,
+                               L.k_k, L.k_a, L.r_k, L.lnx_w, L.lnx_b, wkv, l == 0 ? st.v_first : nullptr, ws.yg, H, C, ws.status);
+                }
                 launch_pdl(*this, wkv7_finish_kernel, dim3((R * H + kWsFinishThreads / 32 - 1) / (kWsFinishThreads / 32)), dim3(kWsFinishThreads), 0, ws.r, ws.k,
                            ws.v, vgate, ws.vfirst, ws.a, ws.g, L.k_a, L.r_k, L.lnx_w, L.lnx_b, ws.yg, R, H, C);
             } else if (n_items >= 4 * num_sms) {

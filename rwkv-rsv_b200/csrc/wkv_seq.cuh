@@ -62,7 +62,30 @@ __device__ __forceinline__ void ws_vec8(float (&d)[8], const float* vec, int sub
     d[4] = hi.x, d[5] = hi.y, d[6] = hi.z, d[7] = hi.w;
 }
 
-// Grid (heads, segments).  `vgate` (layers > 0): v <- v + vgate * (vfirst - v), the lerp of src/model.rs:424-430.
+// RPL consecutive floats (the rows of a lane) from / to 4 RPL-byte aligned memory.
+template <int RPL>
+__device__ __forceinline__ void ws_rows_load(float (&d)[RPL], const float* p) {
+    static_assert(RPL == 2 || RPL == 4, "rows per lane");
+    if constexpr (RPL == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        d[0] = t.x, d[1] = t.y, d[2] = t.z, d[3] = t.w;
+    } else {
+        const float2 t = *reinterpret_cast<const float2*>(p);
+        d[0] = t.x, d[1] = t.y;
+    }
+}
+template <int RPL>
+__device__ __forceinline__ void ws_rows_store(float* p, const float (&d)[RPL]) {
+    if constexpr (RPL == 4)
+        *reinterpret_cast<float4*>(p) = make_float4(d[0], d[1], d[2], d[3]);
+    else
+        *reinterpret_cast<float2*>(p) = make_float2(d[0], d[1]);
+}
+
+// Grid (heads x 4 / RPL, segments): RPL = 4 state rows per lane puts a head in one CTA; RPL = 2 splits it over two CTAs (each
+// prepares the vectors itself), which halves the arithmetic in a state warp's per-token chain - used when the step has few
+// (head, segment) pairs, i.e. a prefill chunk of one or a few sessions.  `vgate` (layers > 0): v <- v + vgate * (vfirst - v), the lerp of src/model.rs:424-430.
+template <int RPL>
 __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* __restrict__ segs, const float* __restrict__ r, const float* __restrict__ k,
                                                                  const float* __restrict__ v, const float* __restrict__ vgate,
                                                                  const float* __restrict__ vfirst, const float* __restrict__ w, const float* __restrict__ a,
@@ -74,12 +97,13 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
     __shared__ __align__(16) float ring[kWsDepth][kWsVecs][N];
     __shared__ __align__(8) uint64_t full[kWsGroups], empty[kWsGroups];
     __shared__ int s_abort;
-    const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int kParts = 4 / RPL;  // CTAs per head
+    const int h = blockIdx.x / kParts, part = blockIdx.x % kParts, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // state warps: a group of eight lanes owns four rows; lane `sub` of the group holds columns 4 sub .. 4 sub + 3 and
     // 32 + 4 sub .. 32 + 4 sub + 3 of them (a group's 16-byte reads of a vector are contiguous: no bank conflicts), so a vector
     // element read from shared memory is used for four rows.  Shared-memory bandwidth, not arithmetic, bounds this loop: with
     // one row per lane the eight warps of a head read 80 KB of vectors per token.
-    const int sub = lane & 7, row0 = (warp & (kWsStateWarps - 1)) * 16 + (lane >> 3) * 4;
+    const int sub = lane & 7, row0 = (part * kWsStateWarps + (warp & (kWsStateWarps - 1))) * 4 * RPL + (lane >> 3) * RPL;
     if (tid == 0) {
         for (int s = 0; s < kWsGroups; ++s) {
             mbar_init(&full[s], kWsGroup);
@@ -91,10 +115,10 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
     const SegMeta sg = segs[blockIdx.y];  // plan data and state: written before the step's first kernel (see wkv7_kernel)
     const bool state_warp = warp < kWsStateWarps;
     float* sbase = state + (((size_t)sg.slot * H + h) * N + row0) * N + 4 * sub;
-    float S[4][8];
+    float S[RPL][8];
     if (state_warp) {
 #pragma unroll
-        for (int rr = 0; rr < 4; ++rr) {
+        for (int rr = 0; rr < RPL; ++rr) {
             const float4 lo = *reinterpret_cast<const float4*>(sbase + rr * N), hi = *reinterpret_cast<const float4*>(sbase + rr * N + 32);
             S[rr][0] = lo.x, S[rr][1] = lo.y, S[rr][2] = lo.z, S[rr][3] = lo.w;
             S[rr][4] = hi.x, S[rr][5] = hi.y, S[rr][6] = hi.z, S[rr][7] = hi.w;
@@ -151,7 +175,7 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
             b[5][lane + 32] = v1;
             __syncwarp();  // the warp's stores are ordered before lane 0's arrival (release)
             if (lane == 0) mbar_arrive(&full[grp]);
-            if (v_first_state && t == last) {
+            if (v_first_state && t == last && part == 0) {
                 v_first_state[(size_t)sg.slot * C + hc + lane] = v0;
                 v_first_state[(size_t)sg.slot * C + hc + lane + 32] = v1;
             }
@@ -161,17 +185,17 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
         // ---- state rows: wait for a group of tokens, apply them, release the group ----
         // One wait and one arrival per group: a successful wait still costs its latency and keeps the compiler from moving the
         // next token's shared-memory reads above it.
-        float yp[4] = {0.f, 0.f, 0.f, 0.f};  // the previous token's partial row sums of y
+        float yp[RPL] = {};  // the previous token's partial row sums of y
         bool gave_up = false;
         auto token = [&](int t, int slot) {
             const float(*sv)[N] = ring[slot];
             float vec[8];
             ws_vec8(vec, sv[0], sub);  // kk
-            const float4 v4 = *reinterpret_cast<const float4*>(&sv[5][row0]);
-            const float vj[4] = {v4.x, v4.y, v4.z, v4.w};
-            float sa[4];
+            float vj[RPL];
+            ws_rows_load<RPL>(vj, &sv[5][row0]);
+            float sa[RPL];
 #pragma unroll
-            for (int rr = 0; rr < 4; ++rr) {
+            for (int rr = 0; rr < RPL; ++rr) {
                 const float lo = fmaf(S[rr][3], vec[3], fmaf(S[rr][2], vec[2], fmaf(S[rr][1], vec[1], S[rr][0] * vec[0])));
                 const float hi = fmaf(S[rr][7], vec[7], fmaf(S[rr][6], vec[6], fmaf(S[rr][5], vec[5], S[rr][4] * vec[4])));
                 sa[rr] = lo + hi;
@@ -181,19 +205,19 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
 #pragma unroll
             for (int m = 1; m < 8; m <<= 1) {
 #pragma unroll
-                for (int rr = 0; rr < 4; ++rr) {
+                for (int rr = 0; rr < RPL; ++rr) {
                     sa[rr] += __shfl_xor_sync(0xffffffffu, sa[rr], m);
                     yp[rr] += __shfl_xor_sync(0xffffffffu, yp[rr], m);
                 }
             }
-            if (sub == 0 && t > 0) *reinterpret_cast<float4*>(&yg[hb0 + (size_t)(t - 1) * C + row0]) = make_float4(yp[0], yp[1], yp[2], yp[3]);  // raw; finished by wkv7_finish_kernel
+            if (sub == 0 && t > 0) ws_rows_store<RPL>(&yg[hb0 + (size_t)(t - 1) * C + row0], yp);  // raw; finished by wkv7_finish_kernel
             float wv[8], bv[8], tv[8];
             ws_vec8(wv, sv[1], sub);
             ws_vec8(bv, sv[2], sub);
             ws_vec8(tv, sv[3], sub);
             ws_vec8(vec, sv[4], sub);  // r
 #pragma unroll
-            for (int rr = 0; rr < 4; ++rr) {
+            for (int rr = 0; rr < RPL; ++rr) {
 #pragma unroll
                 for (int c = 0; c < 8; ++c) S[rr][c] = fmaf(S[rr][c], wv[c], fmaf(sa[rr], bv[c], vj[rr] * tv[c]));
                 const float lo = fmaf(S[rr][3], vec[3], fmaf(S[rr][2], vec[2], fmaf(S[rr][1], vec[1], S[rr][0] * vec[0])));
@@ -221,12 +245,12 @@ __global__ void __launch_bounds__(kWsThreads, 2) wkv7_seq_kernel(const SegMeta* 
 #pragma unroll
             for (int m = 1; m < 8; m <<= 1) {
 #pragma unroll
-                for (int rr = 0; rr < 4; ++rr) yp[rr] += __shfl_xor_sync(0xffffffffu, yp[rr], m);
+                for (int rr = 0; rr < RPL; ++rr) yp[rr] += __shfl_xor_sync(0xffffffffu, yp[rr], m);
             }
-            if (sub == 0) *reinterpret_cast<float4*>(&yg[hb0 + (size_t)(sg.len - 1) * C + row0]) = make_float4(yp[0], yp[1], yp[2], yp[3]);
+            if (sub == 0) ws_rows_store<RPL>(&yg[hb0 + (size_t)(sg.len - 1) * C + row0], yp);
         }
 #pragma unroll
-        for (int rr = 0; rr < 4; ++rr) {
+        for (int rr = 0; rr < RPL; ++rr) {
             *reinterpret_cast<float4*>(sbase + rr * N) = make_float4(S[rr][0], S[rr][1], S[rr][2], S[rr][3]);
             *reinterpret_cast<float4*>(sbase + rr * N + 32) = make_float4(S[rr][4], S[rr][5], S[rr][6], S[rr][7]);
         }
