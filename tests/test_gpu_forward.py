@@ -220,8 +220,9 @@ def test_batch_equals_single(bundles, tiny_paths):
 
 
 def test_many_sessions_equal_single(bundles):
-    # 96 sessions x 8 heads: the persistent, shared-memory-staged form of the WKV-7 kernel (ragged prefill with multi-token
-    # segments, then decode steps with one-token segments); every session must match its single-session run
+    # 96 sessions x 8 heads = 768 (head, segment) pairs: the ragged prefill (segments of 1-8 tokens: full and partial ring groups)
+    # runs wkv7_seq_kernel<4> (a head per CTA), the decode steps the row-per-lane kernel for large batches; the single-session
+    # runs they are compared with use wkv7_seq_kernel<2> (a head over two CTAs) and the persistent decode kernel
     b = bundles["int8"]
     m = b.model
     rng = np.random.default_rng(11)
