@@ -459,9 +459,12 @@ State::~State() {
 void Model::ensure_workspace(int rows, int outs, int segs) {
     if (rows <= ws.rows && outs <= ws.outs && segs <= ws.segs) return;
     RSV_CUDA(cudaStreamSynchronize(stream));
-    rows = std::max(rows, ws.rows);
-    outs = std::max(outs, ws.outs);
-    segs = std::max(segs, ws.segs);
+    // Growing frees and reallocates every array (each a device synchronisation), so a dimension that grows a second time gets
+    // a quarter of slack: a server whose step size creeps up reallocates a few times, not at every new maximum.
+    auto grow = [](int want, int have) { return want <= have ? have : (have > 1 ? want + want / 4 : want); };
+    rows = grow(rows, ws.rows);
+    outs = grow(outs, ws.outs);
+    segs = grow(segs, ws.segs);
     free_workspace(ws);
     const size_t C = cfg.n_embd, F = cfg.ffn_hidden, V = cfg.vocab, R = rows;
     auto fa = [&](float*& p, size_t n) { RSV_CUDA(cudaMalloc(&p, std::max<size_t>(n, 4) * sizeof(float))); };

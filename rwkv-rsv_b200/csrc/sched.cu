@@ -197,6 +197,7 @@ int rsv_sched_new(rsv_model* mh, int64_t max_slots, int64_t chunk, int64_t max_r
         S->out_ev.resize((size_t)max_slots, nullptr);
         for (auto& e : S->out_ev) RSV_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         S->retiring.assign((size_t)max_slots, 0);
+        m.ensure_workspace((int)max_rows, (int)max_slots, (int)max_slots);  // the largest step, so that no step reallocates
         RSV_CUDA(cudaMemsetAsync(S->slot_tok, 0, (size_t)max_slots * 4, m.stream));
         RSV_CUDA(cudaMemsetAsync(S->slot_cnt, 0, (size_t)max_slots * 4, m.stream));
         RSV_CUDA(cudaStreamSynchronize(m.stream));
