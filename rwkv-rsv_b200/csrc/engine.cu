@@ -711,10 +711,37 @@ void tc_plan_group(Model& m, TcGroup& g) {
         T += mtiles * n_tiles;
         L.amap[i] = W.amap;
     }
-    const int G = std::min(m.num_sms, U);
+    int G = std::min(m.num_sms, U);
+    // Short reductions (the rank back-projections: 1-5 K blocks per tile): a tile cut between two CTAs costs a partial-sum round
+    // trip through global memory that is longer than the tile itself, so CTAs get whole tiles, balanced by their K blocks.
+    int kb_max = 0;
+    for (int i = 0; i < n; ++i) kb_max = std::max(kb_max, L.p[i].kblocks);
+    const bool snap = kb_max <= 8 && std::min(m.num_sms, T) + 1 <= kTcMaxSplit;
+    if (snap) {
+        G = std::min(m.num_sms, T);
+        std::vector<int> tk;
+        tk.reserve((size_t)T);
+        for (int i = 0; i < n; ++i)
+            for (int t = (i + 1 < n ? L.p[i + 1].tile0 : T) - L.p[i].tile0; t > 0; --t) tk.push_back(L.p[i].kblocks);
+        int ti = 0, u = 0;
+        for (int c = 0; c < G; ++c) {
+            L.split_unit[c] = u;
+            const int left = G - c;  // CTAs still to be served, this one included: each gets at least one tile
+            const double target = (double)(U - u) / left;
+            int taken = 0;
+            while (ti < T && T - ti > left - 1) {
+                if (taken > 0 && taken + 0.5 * tk[ti] > target) break;
+                taken += tk[ti++];
+            }
+            u += taken;
+        }
+        if (u != U || ti != T) throw std::runtime_error("tc_linear: tile assignment does not cover the launch");
+        L.split_unit[G] = U;
+        L.snap = 1;
+    }
     // tiles cut by a CTA boundary keep partial sums; the epilogue warp that arrives last on a sub-block finishes it
     int pmax = 1, nsplit = 0;
-    for (int c = 1; c < G; ++c) {
+    for (int c = 1; c < G && !snap; ++c) {
         const int bnd = tc_cta_begin(c, U, G);
         int pi = 0;
         while (pi + 1 < n && bnd >= L.p[pi + 1].unit0) ++pi;

@@ -66,10 +66,11 @@ struct alignas(64) TcLaunch {
     CUtensorMap bmap[kTcMaxProblems];
     TcProb p[kTcMaxProblems];
     int nprob, total_units, nt, is_i8, pmax, nstages, grid, nsplit;
+    int snap;  // 1: CTA c owns the units [split_unit[c], split_unit[c + 1]), whole tiles only (no tile is cut; nsplit = 0)
     void* partials;  // [cut tile][pmax][nt][128] int32 or fp32
     int* tile_cnt;   // [cut tile][epilogue warp] arrival counters, zero between launches
     int* status;
-    int split_unit[kTcMaxSplit];  // first unit of every tile that is cut by a CTA boundary
+    int split_unit[kTcMaxSplit];  // first unit of every tile that is cut by a CTA boundary (snap: the CTAs' first units)
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -349,7 +350,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_linear_kernel(const __grid_c
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = gridDim.x, U = L.total_units;
-    const int u_begin = tc_cta_begin(blockIdx.x, U, G), u_end = tc_cta_begin(blockIdx.x + 1, U, G);
+    const int u_begin = L.snap ? L.split_unit[blockIdx.x] : tc_cta_begin(blockIdx.x, U, G);
+    const int u_end = L.snap ? L.split_unit[blockIdx.x + 1] : tc_cta_begin(blockIdx.x + 1, U, G);
     const uint32_t tmem_cols = (2 * NT <= 32) ? 32u : (uint32_t)(2 * NT);  // NT is a power of two >= 16
 
     if (threadIdx.x == 0) {
