@@ -718,7 +718,7 @@ void tc_plan_group(Model& m, TcGroup& g) {
     int kb_min = L.p[0].kblocks;
     for (int i = 1; i < n; ++i) kb_min = std::min(kb_min, L.p[i].kblocks);
     int upc = kb_min;
-    while (upc > 30 && upc % 2 == 0) upc /= 2;
+    while (upc > 30 && upc % 2 == 0) upc /= 2;  // K = 10240 tiles (80 K blocks) in four pieces: measured best of 1, 2, 4, 8
     int G = std::min(m.num_sms, std::max(1, U / upc));
     // Short reductions (the rank back-projections: 1-5 K blocks per tile), where a cut tile's partial-sum round trip is longer
     // than the tile itself, and launches with at least a tile per SM (many rows): CTAs get whole tiles, balanced by their K
