@@ -117,7 +117,8 @@ int rsv_sample_selfloop_collect(rsv_ticket* t, uint32_t* out, int64_t len);
  * sp->seed + r and the r tokens generated so far as penalty history (sp == NULL: arg-max). */
 typedef struct rsv_sched rsv_sched;
 /* max_slots: concurrent sessions (state slots); chunk: prompt tokens of one session per step; max_rows: rows per step
- * (>= max_slots); max_new_cap: upper bound on max_new of any session. */
+ * (>= max_slots); max_new_cap: upper bound on max_new of any session.  The model's step workspace is sized for max_rows rows
+ * here, so that no step allocates. */
 int rsv_sched_new(rsv_model* m, int64_t max_slots, int64_t chunk, int64_t max_rows, int64_t max_new_cap, rsv_sched** out);
 void rsv_sched_free(rsv_sched* s);
 int rsv_sched_submit(rsv_sched* s, const uint32_t* prompt, int64_t n_prompt, int64_t max_new, const rsv_sampler_params* sp, int64_t* id_out);
