@@ -8,6 +8,7 @@
 #include "safetensors.hpp"
 #include "tc_linear.cuh"
 #include "decode_persistent.cuh"
+#include "decode_stream.cuh"
 #include "wkv_rows.cuh"
 #include "wkv_seq.cuh"
 
@@ -308,6 +309,8 @@ std::unique_ptr<Model> Model::load(const std::string& path, int device) {
         if (*e) m->tc_min_rows = atoi(e);
     if (const char* e = getenv("RSV_NO_PERSISTENT"))
         if (*e && *e != '0') m->use_persistent = false;
+    if (const char* e = getenv("RSV_NO_STREAM"))
+        if (*e && *e != '0') m->use_stream = false;
     if (const char* e = getenv("RSV_NO_GRAPH"))
         if (*e && *e != '0') m->use_graphs = false;
     if (const char* e = getenv("RSV_NO_PDL"))
@@ -435,6 +438,9 @@ Model::~Model() {
     for (void* p : {pctx.d_layers, pctx.d_maps, (void*)pctx.x, (void*)pctx.yg, (void*)pctx.vfirst, (void*)pctx.cand_val, (void*)pctx.cand_idx, (void*)pctx.rkv, (void*)pctx.mid, (void*)pctx.hbuf,
                     (void*)pctx.grid_bar})
         if (p) cudaFree(p);
+    for (void* p : {sctx.d_layers, (void*)sctx.x, (void*)sctx.yg, (void*)sctx.vfirst, (void*)sctx.rkv, (void*)sctx.mid, (void*)sctx.hbuf, (void*)sctx.cand_val,
+                    (void*)sctx.cand_idx, (void*)sctx.grid_bar, (void*)sctx.dbg})
+        if (p) cudaFree(p);
     for (int i = 0; i < 5; ++i) {
         if (pctx.region_data[i]) cudaFree(pctx.region_data[i]);
         if (pctx.region_meta[i]) cudaFree(pctx.region_meta[i]);
@@ -451,7 +457,15 @@ Model::~Model() {
 }
 
 State::~State() {
-    if (model) cudaSetDevice(model->device);
+    if (model) {
+        cudaSetDevice(model->device);
+        // the persistent kernel's device layer table may point into this state: a later state that cudaMalloc places at the
+        // same addresses (with another batch, hence other per-layer strides) must not be taken for it
+        if (model->pctx.bound_tmix == tmix_x) {
+            model->pctx.bound_tmix = model->pctx.bound_wkv = model->pctx.bound_cmix = nullptr;
+            model->pctx.bound_cap = -1;
+        }
+    }
     for (float* p : {tmix_x, wkv, cmix_x, v_first})
         if (p) cudaFree(p);
 }
@@ -1082,6 +1096,7 @@ PhaseShape phase_shape(const std::vector<HostProb>& probs, int G) {
 
 bool Model::persistent_available(int nb) {
     if (!use_persistent || nb < 1 || nb > kDpMaxNB) return false;
+    if (nb == 1 && stream_available()) return true;  // one session: the weight-streaming kernel
     PersistentCtx& pc = pctx;
     if (pc.tried) return pc.ok;
     pc.tried = true;
@@ -1268,6 +1283,7 @@ bool Model::persistent_available(int nb) {
 
 void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bool tok_from_list, bool argmax_feed, uint32_t* seq_dev, int* seq_cnt_dev,
                            int seq_cap) {
+    if (nb == 1 && stream_available()) return run_stream(st, slots[0], n_tokens, tok_from_list, argmax_feed, seq_dev, seq_cnt_dev, seq_cap);
     if (!persistent_available(nb)) throw std::runtime_error("persistent decode path unavailable: " + pctx.why);
     PersistentCtx& pc = pctx;
     RSV_CUDA(cudaSetDevice(device));
@@ -1276,7 +1292,7 @@ void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bo
     DpParams P;
     memcpy(&P, pc.params_template.data(), sizeof(P));
     // the device layer table carries the state pointers: rewrite it only when another state is used
-    if (pc.bound_tmix != st.tmix_x || pc.bound_wkv != st.wkv || pc.bound_cmix != st.cmix_x) {
+    if (pc.bound_tmix != st.tmix_x || pc.bound_wkv != st.wkv || pc.bound_cmix != st.cmix_x || pc.bound_cap != st.cap) {
         std::vector<DpLayer> dl(L);
         memcpy(dl.data(), pc.params_template.data() + sizeof(P), dl.size() * sizeof(DpLayer));
         const size_t lay_x = (size_t)st.cap * C, lay_s = (size_t)st.cap * H * kHeadSize * kHeadSize;
@@ -1291,6 +1307,7 @@ void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bo
         pc.bound_tmix = st.tmix_x;
         pc.bound_wkv = st.wkv;
         pc.bound_cmix = st.cmix_x;
+        pc.bound_cap = st.cap;
     }
     P.nb = nb;
     for (int b = 0; b < kDpMaxNB; ++b) P.slot[b] = b < nb ? slots[b] : 0;
@@ -1347,6 +1364,259 @@ void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bo
         fprintf(stderr, "  ffn.key phase: producer issued its %lld tiles from %.2f to %.2f; MMA thread started %.2f, last issue %.2f, waited %.2f us for tiles/accumulators\n",
                 h[53], (h[55] - t0) / 1e3, (h[56] - t0) / 1e3, (h[50] - t0) / 1e3, (h[51] - t0) / 1e3, h[52] / 1e3);
     }
+}
+
+// ------------------------------------------------------------------------------------------------
+// batch-1 weight-streaming decode kernel: host side
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+DsEntry make_entry(const LinearW& W, int C, int xvec, int out, int out_off, const float* mix) {
+    DsEntry e;
+    memset(&e, 0, sizeof(e));
+    const bool i8 = W.wtype == W_INT8;
+    e.base = (const char*)W.w;
+    e.wscale = W.wscale;
+    e.wzero = W.wzero;
+    e.mix = mix;
+    e.M = W.M;
+    e.row_bytes = i8 ? C : 2 * C;
+    e.row_stride = i8 ? W.K : 2 * W.K;
+    e.npieces = W.K / C;
+    e.is_i8 = i8 ? 1 : 0;
+    e.xvec = xvec;
+    e.out = out;
+    e.out_off = out_off;
+    return e;
+}
+int entry_rows(const DsEntry& e, int cta, int G) {
+    if (e.M <= 0) return 0;
+    const int vc = (cta + e.rot) % G;
+    return (int)(((long long)(vc + 1) * e.M) / G) - (int)(((long long)vc * e.M) / G);
+}
+// Rotations of the row split of the phase-1 matrices: chosen one matrix after the other so that the largest number of bytes
+// any CTA streams in the phase stays smallest (the CTAs that get an extra row of one matrix are not those of the next).
+void balance_rotations(DsEntry* ents, int cnt, int G) {
+    std::vector<long long> load((size_t)G, 0);
+    for (int i = 0; i < cnt; ++i) {
+        DsEntry& e = ents[i];
+        if (e.M <= 0) continue;
+        int best_rot = 0;
+        long long best = -1;
+        for (int rot = 0; rot < G; ++rot) {
+            e.rot = rot;
+            long long mx = 0;
+            for (int c = 0; c < G; ++c) mx = std::max(mx, load[c] + (long long)entry_rows(e, c, G) * e.row_bytes * e.npieces);
+            if (best < 0 || mx < best) {
+                best = mx;
+                best_rot = rot;
+            }
+        }
+        e.rot = best_rot;
+        for (int c = 0; c < G; ++c) load[c] += (long long)entry_rows(e, c, G) * e.row_bytes * e.npieces;
+    }
+}
+
+template <int KL>
+void launch_stream(const DsParams& P, int grid, size_t smem, cudaStream_t stream, bool configure_only) {
+    if (configure_only) {
+        RSV_CUDA(cudaFuncSetAttribute(decode_stream_kernel<KL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        int per_sm = 0;
+        RSV_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stream_kernel<KL>, kDsThreads, smem));
+        if (per_sm < 1) throw std::runtime_error("weight-streaming decode kernel does not fit on an SM");
+        return;
+    }
+    void* args[] = {(void*)&P};
+    RSV_CUDA(cudaLaunchCooperativeKernel((const void*)decode_stream_kernel<KL>, dim3(grid), dim3(kDsThreads), args, smem, stream));
+}
+void dispatch_stream(int kl, const DsParams& P, int grid, size_t smem, cudaStream_t stream, bool configure_only) {
+    switch (kl) {
+        case 16: return launch_stream<16>(P, grid, smem, stream, configure_only);
+        case 32: return launch_stream<32>(P, grid, smem, stream, configure_only);
+        case 64: return launch_stream<64>(P, grid, smem, stream, configure_only);
+        case 80: return launch_stream<80>(P, grid, smem, stream, configure_only);
+        case 128: return launch_stream<128>(P, grid, smem, stream, configure_only);
+        default: throw std::runtime_error("weight-streaming decode kernel: unsupported n_embd");
+    }
+}
+
+}  // namespace
+
+bool Model::stream_available() {
+    if (!use_persistent || !use_stream) return false;
+    StreamCtx& sc = sctx;
+    if (sc.tried) return sc.ok;
+    sc.tried = true;
+    auto fail = [&](const std::string& why) {
+        sc.why = why;
+        sc.ok = false;
+        return false;
+    };
+    RSV_CUDA(cudaSetDevice(device));
+    int coop = 0;
+    RSV_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));
+    if (!coop) return fail("device does not support cooperative launches");
+    const int L = cfg.n_layer, C = cfg.n_embd, F = cfg.ffn_hidden, V = cfg.vocab, H = cfg.n_head, G = num_sms;
+    const int kl = C / 32;
+    if (C % 512 || !(kl == 16 || kl == 32 || kl == 64 || kl == 80 || kl == 128)) return fail("n_embd is not one of 512, 1024, 2048, 2560, 4096");
+    if (F != 4 * C) return fail("ffn_hidden is not 4 n_embd");
+    if (H > G) return fail("more heads than SMs");
+    if (cfg.w_mid % 8 || cfg.a_mid % 8 || cfg.v_mid % 8 || cfg.g_mid % 8) return fail("rank dimensions must be multiples of 8");
+    auto per_row = [](const LinearW& W) { return W.wtype != W_INT8 || (W.wscale && W.wzero); };
+    if (!per_row(head)) return fail("int8 head needs one (scale, zero) per output row");
+    for (const LayerW& Lw : layers)
+        for (const LinearW* W : {&Lw.Wr, &Lw.Wk, &Lw.Wv, &Lw.Wo, &Lw.Wfk, &Lw.Wfv})
+            if (!per_row(*W)) return fail("int8 matrices need one (scale, zero) per output row");
+    if (C / G + 1 > kDsMaxSlice) return fail("too many channels per SM");
+    if (3 * (C / G + 1) > kDsMaxRows || F / G + 1 > kDsMaxRows || V / G + 1 > kDsMaxRows) return fail("too many rows per SM");
+    // shared memory: ring + operand area + fixed part + rank-space vector
+    const size_t budget = 227 * 1024;
+    const int vec_floats = std::max(5 * C, F);
+    const size_t fixed = (size_t)vec_floats * 4 + sizeof(DsShared) + (size_t)cfg.mids() * 4 + 256;
+    if (fixed + 64 * 1024 > budget) return fail("operand area does not fit in shared memory");
+    const int ring_bytes = (int)((budget - fixed) / 128 * 128);
+    int max_chunk = std::max(64 * (cfg.w_mid + cfg.a_mid) * 2, 64 * cfg.v_mid * 2 + 32 * cfg.g_mid * 2);
+    for (int rb : {C, 2 * C}) max_chunk = std::max(max_chunk, ds_rows_per_chunk(rb) * rb);
+    if (2 * max_chunk > ring_bytes) return fail("a chunk of rows does not fit twice in the shared-memory ring");
+    sc.kl = kl;
+    sc.grid = G;
+    sc.ring_bytes = ring_bytes;
+    sc.vec_floats = vec_floats;
+    sc.smem = (size_t)ring_bytes + fixed;
+    DsParams P;
+    memset(&P, 0, sizeof(P));
+    try {
+        dispatch_stream(kl, P, G, sc.smem, stream, true);
+    } catch (const std::exception& e) {
+        return fail(e.what());
+    }
+    // per-layer tables
+    std::vector<DsLayer> dl((size_t)L);
+    for (int l = 0; l < L; ++l) {
+        const LayerW& Lw = layers[l];
+        DsLayer& d = dl[l];
+        memset(&d, 0, sizeof(d));
+        d.e[DSE_W1] = make_entry(Lw.w1, C, 0, DSO_MID_TANH, 0, Lw.x_w);
+        d.e[DSE_A1] = make_entry(Lw.a1, C, 0, DSO_MID, cfg.w_mid, Lw.x_a);
+        d.e[DSE_G1] = make_entry(Lw.g1, C, 0, DSO_MID_SIG, cfg.w_mid + cfg.a_mid + cfg.v_mid, Lw.x_g);
+        d.e[DSE_V1] = make_entry(Lw.v1, C, 0, DSO_MID, cfg.w_mid + cfg.a_mid, Lw.x_v);
+        if (l == 0) d.e[DSE_V1].M = 0;  // layer 0 has no v gate
+        d.e[DSE_WR] = make_entry(Lw.Wr, C, 0, DSO_R, 0, nullptr);
+        d.e[DSE_WK] = make_entry(Lw.Wk, C, 1, DSO_K, 0, nullptr);
+        d.e[DSE_WV] = make_entry(Lw.Wv, C, 2, DSO_V, 0, nullptr);
+        d.e[DSE_WO] = make_entry(Lw.Wo, C, 0, DSO_XADD, 0, nullptr);
+        d.e[DSE_WFK] = make_entry(Lw.Wfk, C, 0, DSO_H, 0, nullptr);
+        d.e[DSE_WFV] = make_entry(Lw.Wfv, C, 0, DSO_XADD, 0, nullptr);
+        balance_rotations(&d.e[DSE_W1], 7, G);  // att.output and ffn.value keep rotation 0: their rows are the CTA's slice of x
+        d.w2 = (const __half*)Lw.w2.w;
+        d.a2 = (const __half*)Lw.a2.w;
+        d.v2 = (const __half*)Lw.v2.w;
+        d.g2 = (const __half*)Lw.g2.w;
+        d.ln1_w = Lw.ln1_w;
+        d.ln1_b = Lw.ln1_b;
+        d.ln2_w = Lw.ln2_w;
+        d.ln2_b = Lw.ln2_b;
+        d.lnx_w = Lw.lnx_w;
+        d.lnx_b = Lw.lnx_b;
+        d.x_r = Lw.x_r;
+        d.x_k = Lw.x_k;
+        d.x_v = Lw.x_v;
+        d.ffn_x_k = Lw.ffn_x_k;
+        d.w0 = Lw.w0;
+        d.a0 = Lw.a0;
+        d.v0 = Lw.v0;
+        d.r_k = Lw.r_k;
+        d.k_k = Lw.k_k;
+        d.k_a = Lw.k_a;
+    }
+    RSV_CUDA(cudaMalloc(&sc.d_layers, dl.size() * sizeof(DsLayer)));
+    RSV_CUDA(cudaMemcpy(sc.d_layers, dl.data(), dl.size() * sizeof(DsLayer), cudaMemcpyHostToDevice));
+    RSV_CUDA(cudaMalloc(&sc.x, (size_t)C * 4));
+    RSV_CUDA(cudaMalloc(&sc.yg, (size_t)C * 4));
+    RSV_CUDA(cudaMalloc(&sc.vfirst, (size_t)C * 4));
+    RSV_CUDA(cudaMalloc(&sc.rkv, (size_t)3 * C * 4));
+    RSV_CUDA(cudaMalloc(&sc.mid, (size_t)std::max(cfg.mids(), 1) * 4));
+    RSV_CUDA(cudaMalloc(&sc.hbuf, (size_t)F * 4));
+    RSV_CUDA(cudaMalloc(&sc.cand_val, (size_t)G * 4));
+    RSV_CUDA(cudaMalloc(&sc.cand_idx, (size_t)G * 4));
+    RSV_CUDA(cudaMalloc(&sc.grid_bar, 4));
+    RSV_CUDA(cudaMemset(sc.mid, 0, (size_t)std::max(cfg.mids(), 1) * 4));
+    RSV_CUDA(cudaMemset(sc.vfirst, 0, (size_t)C * 4));
+#ifdef RSV_DS_DEBUG
+    RSV_CUDA(cudaMalloc(&sc.dbg, 64 * sizeof(long long)));
+    RSV_CUDA(cudaMemset(sc.dbg, 0, 64 * sizeof(long long)));
+#endif
+    P.layers = (const DsLayer*)sc.d_layers;
+    P.head = make_entry(head, C, 0, DSO_LOGITS, 0, nullptr);
+    P.emb = emb;
+    P.ln0_w = ln0_w;
+    P.ln0_b = ln0_b;
+    P.lno_w = ln_out_w;
+    P.lno_b = ln_out_b;
+    P.L = L;
+    P.C = C;
+    P.H = H;
+    P.F = F;
+    P.V = V;
+    P.wm = cfg.w_mid;
+    P.am = cfg.a_mid;
+    P.vm = cfg.v_mid;
+    P.gm = cfg.g_mid;
+    P.x = sc.x;
+    P.yg = sc.yg;
+    P.vfirst = sc.vfirst;
+    P.rkv = sc.rkv;
+    P.mid = sc.mid;
+    P.hbuf = sc.hbuf;
+    P.cand_val = sc.cand_val;
+    P.cand_idx = sc.cand_idx;
+    P.grid_bar = sc.grid_bar;
+    P.ring_bytes = ring_bytes;
+    P.vec_floats = vec_floats;
+    P.dbg = sc.dbg;
+    sc.params_template.resize(sizeof(DsParams));
+    memcpy(sc.params_template.data(), &P, sizeof(P));
+    sc.ok = true;
+    return true;
+}
+
+void Model::run_stream(State& st, int slot, int n_tokens, bool tok_from_list, bool argmax_feed, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap) {
+    if (!stream_available()) throw std::runtime_error("weight-streaming decode path unavailable: " + sctx.why);
+    StreamCtx& sc = sctx;
+    RSV_CUDA(cudaSetDevice(device));
+    if (slot < 0 || slot >= st.cap) throw std::runtime_error("state slot out of range");
+    ensure_workspace(1, 1, 1);
+    DsParams P;
+    memcpy(&P, sc.params_template.data(), sizeof(P));
+    P.slot = slot;
+    P.lay_x = (long long)st.cap * cfg.n_embd;
+    P.lay_s = (long long)st.cap * cfg.n_head * kHeadSize * kHeadSize;
+    P.tmix_x = st.tmix_x;
+    P.wkv = st.wkv;
+    P.cmix_x = st.cmix_x;
+    P.state_vfirst = st.v_first;
+    P.tokens = ws.tokens;
+    P.tok_list = ws.tok_list;
+    P.seq = seq_dev;
+    P.seq_cnt = seq_cnt_dev;
+    P.seq_cap = seq_cap;
+    P.logits = ws.logits;
+    P.status = ws.status;
+    P.n_tokens = n_tokens;
+    P.tok_from_list = tok_from_list ? 1 : 0;
+    P.argmax_feed = argmax_feed ? 1 : 0;
+    RSV_CUDA(cudaMemsetAsync(sc.grid_bar, 0, 4, stream));
+    LAUNCH(*this, "decode_stream") { dispatch_stream(sc.kl, P, sc.grid, sc.smem, stream, false); }
+#ifdef RSV_DS_DEBUG
+    if (sc.dbg && n_tokens >= 2) {
+        long long h[64];
+        RSV_CUDA(cudaStreamSynchronize(stream));
+        RSV_CUDA(cudaMemcpy(h, sc.dbg, sizeof(h), cudaMemcpyDeviceToHost));
+        const char* names[10] = {"layer start", "P1 operands", "P1 rows done", "heads done", "P3 operands", "P3 rows done", "P4 operands", "P4 rows done", "P5 operands", "P5 rows done"};
+        fprintf(stderr, "[decode_stream_kernel, CTA 0, token 1, layer 1] us since the layer started\n");
+        for (int i = 0; i < 10; ++i) fprintf(stderr, "  %-14s %.2f\n", names[i], (h[i] - h[0]) / 1e3);
+    }
+#endif
 }
 
 void Model::check_status() {

@@ -91,6 +91,21 @@ struct PersistentCtx {
     size_t smem = 0;
     std::vector<char> params_template;  // DpParams with everything but the per-call fields
     const float *bound_tmix = nullptr, *bound_wkv = nullptr, *bound_cmix = nullptr;  // state whose pointers the device layer table holds
+    int64_t bound_cap = -1;                                                           // and its slot capacity (the per-layer strides)
+};
+
+// Device-side tables and scratch of the batch-1 weight-streaming decode kernel (built on first use).
+struct StreamCtx {
+    bool tried = false, ok = false;
+    std::string why;           // reason when the model cannot take this path
+    void* d_layers = nullptr;  // DsLayer[L]
+    float *x = nullptr, *yg = nullptr, *vfirst = nullptr, *rkv = nullptr, *mid = nullptr, *hbuf = nullptr, *cand_val = nullptr;
+    int* cand_idx = nullptr;
+    unsigned* grid_bar = nullptr;
+    long long* dbg = nullptr;
+    int grid = 0, kl = 0, ring_bytes = 0, vec_floats = 0;
+    size_t smem = 0;
+    std::vector<char> params_template;  // DsParams with everything but the per-call fields
 };
 
 struct KernelProf {
@@ -151,6 +166,10 @@ struct Model {
 
     bool use_persistent = true;  // batch <= 4 decode goes through the persistent kernel (RSV_NO_PERSISTENT=1 disables)
     PersistentCtx pctx;
+    bool use_stream = true;  // one session: the row-owner weight-streaming kernel (RSV_NO_STREAM=1 falls back to the tensor-core persistent kernel)
+    StreamCtx sctx;
+    bool stream_available();
+    void run_stream(State& st, int slot, int n_tokens, bool tok_from_list, bool argmax_feed, uint32_t* seq_dev, int* seq_cnt_dev, int seq_cap);
     // Persistent decode: n_tokens steps for nb <= 4 sessions (slots[b] of `st`) in one cooperative launch.
     // Returns false (with pctx.why set) when this model cannot take that path.
     bool persistent_available(int nb);
