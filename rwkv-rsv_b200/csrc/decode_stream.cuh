@@ -651,17 +651,10 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
         };
         // Grid barrier in two halves: arrive as soon as this CTA's outputs are stored, wait just before the first load of
         // another CTA's outputs; what lies between (parameter loads of the next phase) overlaps the other CTAs' tails.
-        auto bar_arrive = [&]() {
-            ds_consumer_sync();
-            if (wtid == 0) {
-                fence_acq_rel_gpu();
-                atomicAdd(P.grid_bar, 1u);
-            }
-            bar_target += (unsigned)G;
-            pending = true;
-        };
+        // The counter only ever grows, so a CTA must have seen barrier n complete before it arrives on barrier n + 1
+        // (otherwise its second arrival could stand in for a CTA that has not reached barrier n yet).
         auto bar_wait = [&]() -> bool {
-            if (!pending) return true;
+            if (!pending) return *abort_flag == 0;
             pending = false;
             if (wtid == 0) {
                 bool got = false;
@@ -678,6 +671,16 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
             }
             ds_consumer_sync();
             return *abort_flag == 0;
+        };
+        auto bar_arrive = [&]() {
+            bar_wait();
+            ds_consumer_sync();
+            if (wtid == 0) {
+                fence_acq_rel_gpu();
+                atomicAdd(P.grid_bar, 1u);
+            }
+            bar_target += (unsigned)G;
+            pending = true;
         };
         auto rows_of = [&](const DsEntry& E, int& r0, int& n) {
             r0 = n = 0;
