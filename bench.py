@@ -386,7 +386,7 @@ def main():
             achieved = step_bytes * K / (ms / 1000.0) / 1e9
             per_tok = NCU_DRAM_BYTES_PER_TOKEN.get((args.shape, args.quant, B))
             traffic = per_tok * K if per_tok else None
-            roofline = {"bound": "hbm", "kernel": "decode_persistent_kernel", "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
+            roofline = {"bound": "hbm", "kernel": "decode_stream_kernel", "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
                         "frac": achieved / peak, "traffic": traffic, "bytes_per_launch": step_bytes * K, "ms_per_launch": ms, "share_of_step": 1.0,
                         "note": "one cooperative launch runs all timed steps; bytes = algorithmic bytes of a decode step x steps; "
                                 "traffic = ncu DRAM bytes per token (4-token capture) x steps",

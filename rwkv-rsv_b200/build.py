@@ -47,7 +47,8 @@ def build_cuda(force=False, verbose=False):
     cu = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     deps = cu + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.hpp")) + glob.glob(os.path.join(ROOT, "include", "*.h"))
     if force or _stale(LIB_CUDA, deps):
-        cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + cu + ["-o", LIB_CUDA]
+        extra = os.environ.get("RSV_NVCC_EXTRA", "").split()  # e.g. -DRSV_DS_DEBUG: phase time stamps of the batch-1 decode kernel
+        cmd = [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + cu + ["-o", LIB_CUDA]
         env = dict(os.environ)
         env["CXX"] = "g++"
         subprocess.check_call(cmd + ["-ccbin", "g++"], env=env)

@@ -1,4 +1,4 @@
-// Batch-1 decode as a row-owner weight-streaming GEMV inside one persistent launch.
+// Batch-1 decode as a row-owner weight-streaming matrix-vector product inside one persistent launch.
 //
 // One cooperative launch runs n tokens x L layers x (head, arg-max) for ONE session: the launch stands in for the
 // reference's captured-graph decode step (forward_token / forward_layer / selfloop_step, src/gpu_model.rs:1879-2392)
@@ -9,24 +9,30 @@
 // partial sums ever cross a CTA, so a phase is  activation vector -> dot products -> plain stores -> grid barrier.
 //   warp 0      producer.  Walks the fixed sequence of weight rows this CTA will ever need - token after token, layer
 //               after layer, phase after phase - and streams them with bulk asynchronous copies (cp.async.bulk, one
-//               per row, issued by the lanes in parallel) into a byte-granular ring in shared memory, a chunk (up to
-//               16 rows of one matrix) per mbarrier.  It never waits on a grid barrier, only on ring space, so HBM
-//               keeps streaming while the other warps synchronise: barriers cost latency, not bandwidth.
-//   warps 1-8   consumers.  Per phase they build the activation vector in shared memory (LayerNorm, token shift,
-//               fixed-point digits), then every warp takes rows of the chunk: a lane keeps its K slice of the
-//               activation in REGISTERS for the whole matrix, reads 16-byte pieces of the row from the ring, and the
-//               warp reduces once per row.
-// Arithmetic.  int8 matrices: the u8 codes q are multiplied as they are (dp4a, u8 x s8) with D = 4 signed base-128
-// digits of the fixed-point activation t = rint(x / e 2^27), e = 2^ceil(log2 max|x|); the four int32 sums recombine
-// to Q = sum_k q_k t_k exactly (int64), and with the container's per-row (scale s, zero z)
-// y = e 2^-27 (s Q + z T), T = sum_k t_k: the same numbers the tensor-core kernels produce, with no accumulation
-// rounding and no dependence on the schedule.  fp16 matrices (head, rank projections, fp16 checkpoints): fp32 FMA
-// on the converted halves, lane partial sums in a fixed order, then a shuffle tree.
+//               per row, issued by the lanes in parallel) into a byte-granular ring in shared memory; a chunk = one
+//               tile of up to 8 rows x one piece (<= 2560 bytes) of K, one mbarrier per chunk.  It never waits on a
+//               grid barrier, only on ring space, so HBM keeps streaming while the other warps synchronise:
+//               barriers cost latency, not bandwidth.
+//   warps 1-16  consumers.  Per phase they build the activation vector in shared memory (LayerNorm, token shift,
+//               fixed-point digits), laid out as the A fragments of the warp-level matrix instruction.  Then every
+//               tile belongs to ONE warp, which multiplies it out of the ring (ldmatrix -> mma.sync, the reduction
+//               over K happens inside the instruction, four independent accumulator chains) and keeps the
+//               accumulators in registers across the pieces of a long row: no shuffles in the loop, no sums across
+//               warps, nothing to wait for but the tile itself.  A row in the ring is padded by 16 bytes so that
+//               the eight rows of a tile fall into different banks.
+// Arithmetic.  int8 matrices: the u8 codes q are multiplied as they are (m16n8k32, s8 x u8 -> s32) with the four
+// signed base-256 digits of the fixed-point activation t = rint(x / e 2^30), e = 2^ceil(log2 max|x|) (the digits are
+// the bytes of (t + 0x808080) ^ 0x808080); the four int32 sums recombine to Q = sum_k q_k t_k exactly (int64), and
+// with the container's per-row (scale s, zero z)  y = e 2^-30 (s Q + z T), T = sum_k t_k: no accumulation rounding,
+// no dependence on the schedule.  fp16 matrices (head, rank projections, fp16 checkpoints): m16n8k16 f16 x f16 ->
+// f32 with x / e split into hi + lo halves (two operand rows).  These are 8-column problems that stream weights at
+// HBM speed; the tensor pipe is nearly idle, which is why the warp-level instruction is the right size here and the
+// tcgen05 kernels take over once several rows make the product a dense contraction.
 // Phases per layer, one grid barrier after each (bounded spin):
 //   1  LN1 + token shift -> r, k, v and the four rank projections (tanh / sigmoid applied)
 //   2  one CTA per head: rank back-projections (their rows arrive through the ring too), decay / a / v-gate / g,
 //      WKV-7 state update in place, GroupNorm, bonus, gate
-//   3  att.output, x += ...      4  LN2 + shift -> relu(ffn.key)^2      5  ffn.value (K = F in pieces of C), x += ...
+//   3  att.output, x += ...      4  LN2 + shift -> relu(ffn.key)^2      5  ffn.value, x += ...
 // then ln_out + head -> logits, arg-max across CTAs, next token.
 // All waits are bounded; on expiry bit 2 of the status word is set, every role drains its copies in flight and exits.
 #pragma once
@@ -34,14 +40,16 @@
 
 namespace rsv {
 
-constexpr int kDsConsumerWarps = 8;
-constexpr int kDsConsumers = kDsConsumerWarps * 32;  // 256
+constexpr int kDsConsumerWarps = 16;
+constexpr int kDsConsumers = kDsConsumerWarps * 32;  // 512
 constexpr int kDsThreads = kDsConsumers + 32;        // + producer warp
-constexpr int kDsBars = 8;                           // chunks in flight (mbarrier pairs)
-constexpr int kDsChunkBytes = 40 * 1024;             // target size of a chunk of rows
-constexpr int kDsMaxRows = 512;                      // rows of one matrix per CTA whose (scale, zero) are staged per phase
+constexpr int kDsBars = 16;                          // chunks in flight (mbarrier pairs)
+constexpr int kDsTileRows = 8;                       // rows of a tile (the n dimension of the matrix instruction)
+constexpr int kDsPad = 16;                           // bytes between the rows of a tile in the ring, beyond the piece
+constexpr int kDsMaxPiece = 2560;                    // bytes of K per piece
+constexpr int kDsMaxRows = 512;                      // rows of one phase per CTA whose (scale, zero) are staged
 constexpr int kDsMaxSlice = 32;                      // channels of the residual stream per CTA
-constexpr int kDsP = 27;                             // fixed-point bits of the activation digits (4 digits of 7 bits)
+constexpr int kDsP = 30;                             // fixed-point bits of the activation digits
 constexpr uint32_t kDsBarSpin = 1u << 22;
 
 // What a finished dot product becomes.
@@ -54,15 +62,14 @@ struct DsEntry {
     const float* wzero;
     const float* mix;     // rank projections: the token-shift mix vector of their input; null otherwise
     int M;                // output rows (0: the entry does not exist in this layer)
-    int row_bytes;        // bytes of one piece of a row: C (int8) or 2 C (fp16)
     int row_stride;       // bytes between rows
-    int npieces;          // K / C
+    int piece_bytes;      // bytes of K per piece (a multiple of 128, <= kDsMaxPiece)
+    int npieces;          // pieces per row
     int is_i8;
     int xvec;             // which vector of the phase's operand area the rows are multiplied with
     int out;              // DsOut
     int out_off;          // offset inside the rank-space vector for DSO_MID*
-    int rot;              // the CTA with index c owns the row range of virtual index (c + rot) mod G
-    int pad;
+    int cta0, ncta;       // the rows are split over the ncta CTAs cta0, cta0 + 1, ... (mod G)
 };
 enum { DSE_W1 = 0, DSE_A1, DSE_G1, DSE_V1, DSE_WR, DSE_WK, DSE_WV, DSE_WO, DSE_WFK, DSE_WFV, DSE_COUNT };
 struct DsLayer {
@@ -79,15 +86,15 @@ struct DsParams {
     const float *ln0_w, *ln0_b, *lno_w, *lno_b;
     int L, C, H, F, V, wm, am, vm, gm;
     int slot;
-    long long lay_x, lay_s;                // floats between consecutive layers of the shift states / the WKV states
-    float *tmix_x, *wkv, *cmix_x;          // state bases (layer 0, slot 0)
-    float* state_vfirst;                   // [cap][C]
-    float *x, *yg, *vfirst;                // [C]
-    float* rkv;                            // [3][C]
-    float* mid;                            // [wm+am+vm+gm]
-    float* hbuf;                           // [F]
-    uint32_t* tokens;                      // [1] current input token (read at start, written after arg-max)
-    const uint32_t* tok_list;              // [n_tokens], used when tok_from_list
+    long long lay_x, lay_s;        // floats between consecutive layers of the shift states / the WKV states
+    float *tmix_x, *wkv, *cmix_x;  // state bases (layer 0, slot 0)
+    float* state_vfirst;           // [cap][C]
+    float *x, *yg, *vfirst;        // [C]
+    float* rkv;                    // [3][C]
+    float* mid;                    // [wm+am+vm+gm]
+    float* hbuf;                   // [F]
+    uint32_t* tokens;              // [1] current input token (read at start, written after arg-max)
+    const uint32_t* tok_list;      // [n_tokens], used when tok_from_list
     uint32_t* seq;
     int* seq_cnt;
     int seq_cap;
@@ -97,22 +104,35 @@ struct DsParams {
     unsigned* grid_bar;
     int* status;
     int n_tokens, tok_from_list, argmax_feed;
-    int ring_bytes;    // shared-memory ring
-    int vec_floats;    // operand area, in 4-byte elements: max(5 C, F)
-    long long* dbg;    // optional time stamps (built with -DRSV_DS_DEBUG only)
+    int ring_bytes;  // shared-memory ring
+    int vec_floats;  // operand area, in 4-byte elements: max(4 C, F)
+    long long* dbg;  // optional time stamps (built with -DRSV_DS_DEBUG only)
 };
 
 // ---- small helpers ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void ds_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kDsConsumers) : "memory"); }
-__device__ __forceinline__ int ds_dp4a_us(uint32_t a_u8x4, uint32_t b_s8x4, int c) {
-    int d;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_u8x4), "r"(b_s8x4), "r"(c));
-    return d;
-}
 __device__ __forceinline__ uint4 ds_lds128(uint32_t saddr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
     return v;
+}
+// four 8 x 16-byte matrices, row addresses from lanes 8 i .. 8 i + 7: lane (g, t) gets bytes 4 t .. 4 t + 3 of row g of each
+__device__ __forceinline__ uint4 ds_ldmatrix4(uint32_t saddr) {
+    uint4 v;
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
+    return v;
+}
+// D += A (16 x 32 s8, row-major: the activation digits) x B (32 x 8 u8, column-major: eight weight rows)
+__device__ __forceinline__ void ds_mma_i8(int (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+// D += A (16 x 16 f16) x B (16 x 8 f16), fp32 accumulation
+__device__ __forceinline__ void ds_mma_f16(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ uint64_t ds_evict_first_policy() {
     uint64_t p;
@@ -143,47 +163,27 @@ __device__ __forceinline__ int ds_exponent(float amax) {
     if (amax >= 1.0e-30f && amax < 3.0e38f) ex = ds_ceil_log2(amax);
     return max(-90, min(90, ex));
 }
-// rows of an M-row matrix owned by virtual CTA index vc of G
-__device__ __forceinline__ int ds_row_begin(int vc, int M, int G) { return (int)(((long long)vc * M) / G); }
-// rows per chunk: about kDsChunkBytes, a multiple of the consumer warp count (two rows per warp) when rows are short
-__host__ __device__ inline int ds_rows_per_chunk(int row_bytes) {
-    const int fit = kDsChunkBytes / row_bytes;
-    return fit >= 16 ? 16 : (fit >= 8 ? 8 : (fit >= 4 ? 4 : (fit >= 2 ? 2 : 1)));
+// first row of the share of virtual CTA index vc when M rows are split over n CTAs
+__host__ __device__ inline int ds_row_begin(int vc, int M, int n) { return (int)(((long long)vc * M) / n); }
+// the rows [r0, r0 + n) of entry E that CTA `cta` of G owns (n = 0: none)
+__host__ __device__ inline void ds_rows_of(const DsEntry& E, int cta, int G, int& r0, int& n) {
+    r0 = n = 0;
+    if (E.M <= 0 || E.ncta <= 0) return;
+    const int vc = ((cta - E.cta0) % G + G) % G;
+    if (vc >= E.ncta) return;
+    r0 = ds_row_begin(vc, E.M, E.ncta);
+    n = ds_row_begin(vc + 1, E.M, E.ncta) - r0;
 }
+// bytes a chunk of entry E holds in the ring (always a full tile's worth, also for the last, shorter tile)
+__host__ __device__ inline int ds_chunk_bytes(const DsEntry& E) { return kDsTileRows * (E.piece_bytes + kDsPad); }
 // the CTA that runs head h of layer l (H <= G: heads spread with a stride, rotated per layer so that the extra bytes of a
 // head's back-projection rows do not always land on the same SMs); -1 when CTA `cta` has no head in that layer
 __host__ __device__ inline int ds_head_of_cta(int cta, int l, int H, int G) {
-    if (H > G) return -2;  // several heads per CTA: h = cta, cta + G, ...
     const int stride = G / H;
     const int d = ((cta - (l * 37) % G) % G + G) % G;
     if (d % stride) return -1;
     const int h = d / stride;
     return h < H ? h : -1;
-}
-
-// Four activations -> their base-128 digits, packed for dp4a: word d holds digit d (0 = most significant) of the four
-// consecutive k.  Adds the four fixed-point values to `tsum`.
-__device__ __forceinline__ uint4 ds_digits4(float4 v, float mult, long long& tsum) {
-    const float lim = (float)(1 << kDsP);
-    float f[4] = {v.x * mult, v.y * mult, v.z * mult, v.w * mult};
-    uint32_t w0 = 0, w1 = 0, w2 = 0, w3 = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        float q = fminf(fmaxf(f[j], -lim), lim);
-        int t = (q == q) ? __float2int_rn(q) : 0;
-        tsum += t;
-        const int d3 = ((t + 64) & 127) - 64;
-        t = (t - d3) >> 7;
-        const int d2 = ((t + 64) & 127) - 64;
-        t = (t - d2) >> 7;
-        const int d1 = ((t + 64) & 127) - 64;
-        t = (t - d1) >> 7;
-        w0 |= (uint32_t)(t & 0xFF) << (8 * j);
-        w1 |= (uint32_t)(d1 & 0xFF) << (8 * j);
-        w2 |= (uint32_t)(d2 & 0xFF) << (8 * j);
-        w3 |= (uint32_t)(d3 & 0xFF) << (8 * j);
-    }
-    return make_uint4(w0, w1, w2, w3);
 }
 // exact sum of a 64-bit value over the warp whose magnitude is below 2^40 per lane (two 32-bit reductions)
 __device__ __forceinline__ long long ds_warp_sum_ll(long long v) {
@@ -198,82 +198,135 @@ struct DsShared {
     int alloc[kDsBars];  // producer only: bytes (with wrap waste) a chunk in flight holds
     int abort_flag;
     uint32_t tok;
-    float red_a[8], red_b[8], red_c[3 * 8];
-    int red_i[8];
-    long long tsw[3][8];  // per consumer warp: exact sum of the fixed-point values of operand vector v
-    int ex[4];            // exponent of the power-of-two scale of operand vector v
-    float stats[2];
-    float xs_own[kDsMaxSlice];   // this CTA's slice of the residual stream
-    float cs_own[kDsMaxSlice];   // pending channel-mix shift state of the slice
-    long long qacc[kDsMaxSlice]; // per-row sums over the pieces of a long row (int8: exact; fp16: facc)
-    float facc[kDsMaxSlice];
+    float red_a[16], red_b[16], red_c[4 * 16];
+    int red_i[16];
+    long long tsw[4][16];  // per consumer warp: exact sum of the fixed-point values of operand vector v
+    int ex[4];             // exponent of the power-of-two scale of operand vector v
+    float xs_own[kDsMaxSlice];  // this CTA's slice of the residual stream
+    float ts_own[kDsMaxSlice];  // pending time-mix shift state of the slice
+    float cs_own[kDsMaxSlice];  // pending channel-mix shift state of the slice
     float ws[kDsMaxRows], wz[kDsMaxRows];  // (scale, zero) of the rows this CTA owns in the current phase
-    float hv[8 * 64];                      // the 64-vectors of a head
+    float hv[10 * 64];                     // the 64-vectors of a head
     DsLayer layer[2];                      // table of the current / next layer
 };
 
-// consumer-side view of the ring: every consumer warp walks the same chunk sequence as the producer
+// Operand area.  Vector v of a phase (`len` elements) occupies 4 len bytes at byte offset 4 v len, stored as the A fragments
+// the consumer lanes load with one 16-byte read per two k steps:
+//   int8 matrices (k step = 32 elements): index [k / 64][digit 0..3][t = (k % 16) / 4][word (k % 64) / 16], the word holding
+//     the digit of the four consecutive k in its bytes; lane (g, t) of a warp reads the 16 bytes at ((k/64) 4 + g) 4 + t.
+//   fp16 matrices (k step = 16 elements): index [k / 32][0 = hi, 1 = lo][t = (k % 8) / 2][word (k % 32) / 8], the word holding
+//     the halves of k, k + 1.
+// Writes the vectors (getval(v, i) = the i-th of a thread's NGR groups of four consecutive elements of vector v) in that form; the scale exponent
+// goes to S->ex[v], for int8 the exact fixed-point sum to S->tsw[v].
+template <int NV, int NGR, class GetVal>
+__device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const bool (&i8)[NV], GetVal getval, int wtid) {
+    const int wwarp = wtid >> 5, lane = wtid & 31, len4 = len >> 2;
+    float am[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        am[v] = 0.f;
+#pragma unroll
+        for (int gi = 0; gi < NGR; ++gi)
+            if (wtid + kDsConsumers * gi < len4) {
+                const float4 x = getval(v, gi);
+                am[v] = fmaxf(am[v], fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
+            }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) am[v] = fmaxf(am[v], __shfl_xor_sync(0xffffffffu, am[v], o));
+        if (lane == 0) S->red_c[v * 16 + wwarp] = am[v];
+    }
+    ds_consumer_sync();
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        float a = 0.f;
+#pragma unroll
+        for (int w = 0; w < kDsConsumerWarps; ++w) a = fmaxf(a, S->red_c[v * 16 + w]);
+        const int ex = ds_exponent(a);
+        if (wtid == 0) S->ex[v] = ex;
+        uint32_t* vb = reinterpret_cast<uint32_t*>(vec + (size_t)v * len);
+        if (i8[v]) {
+            const float mult = ds_pow2(kDsP - ex), lim = (float)(1 << kDsP);
+            long long ts = 0;
+#pragma unroll
+            for (int gi = 0; gi < NGR; ++gi) {
+                const int g4 = wtid + kDsConsumers * gi;
+                if (g4 < len4) {
+                    const float4 x = getval(v, gi);
+                    const float f[4] = {x.x * mult, x.y * mult, x.z * mult, x.w * mult};
+                    uint32_t u[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float q = fminf(fmaxf(f[j], -lim), lim);
+                        const int t = (q == q) ? __float2int_rn(q) : 0;
+                        ts += t;
+                        u[j] = ((uint32_t)t + 0x00808080u) ^ 0x00808080u;  // bytes = signed base-256 digits of t
+                    }
+                    // 4 x 4 byte transpose: word d = digit d of the four elements
+                    const uint32_t lo01 = __byte_perm(u[0], u[1], 0x5140), hi01 = __byte_perm(u[0], u[1], 0x7362);
+                    const uint32_t lo23 = __byte_perm(u[2], u[3], 0x5140), hi23 = __byte_perm(u[2], u[3], 0x7362);
+                    uint32_t* dst = vb + ((size_t)(g4 >> 4) * 16 + (g4 & 3)) * 4 + ((g4 >> 2) & 3);
+                    dst[0] = __byte_perm(lo01, lo23, 0x5410);
+                    dst[16] = __byte_perm(lo01, lo23, 0x7632);
+                    dst[32] = __byte_perm(hi01, hi23, 0x5410);
+                    dst[48] = __byte_perm(hi01, hi23, 0x7632);
+                }
+            }
+            ts = ds_warp_sum_ll(ts);
+            if (lane == 0) S->tsw[v][wwarp] = ts;
+        } else {
+            const float mult = ds_pow2(-ex);
+#pragma unroll
+            for (int gi = 0; gi < NGR; ++gi) {
+                const int g4 = wtid + kDsConsumers * gi;
+                if (g4 < len4) {
+                    const float4 x = getval(v, gi);
+                    const float f[4] = {x.x * mult, x.y * mult, x.z * mult, x.w * mult};
+                    __half hi[4], lo[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float q = fminf(fmaxf(f[j], -1.0f), 1.0f);
+                        if (!(q == q)) q = 0.f;
+                        hi[j] = __float2half_rn(q);
+                        lo[j] = __float2half_rn(q - __half2float(hi[j]));
+                    }
+                    uint32_t* dst = vb + ((size_t)(g4 >> 3) * 8 + (g4 & 1) * 2) * 4 + ((g4 & 7) >> 1);
+                    const __half2 h01 = __halves2half2(hi[0], hi[1]), h23 = __halves2half2(hi[2], hi[3]);
+                    const __half2 l01 = __halves2half2(lo[0], lo[1]), l23 = __halves2half2(lo[2], lo[3]);
+                    dst[0] = *reinterpret_cast<const uint32_t*>(&h01);   // row hi, t
+                    dst[4] = *reinterpret_cast<const uint32_t*>(&h23);   // row hi, t + 1
+                    dst[16] = *reinterpret_cast<const uint32_t*>(&l01);  // row lo, t
+                    dst[20] = *reinterpret_cast<const uint32_t*>(&l23);  // row lo, t + 1
+                }
+            }
+        }
+    }
+    ds_consumer_sync();
+}
+
+// consumer-side view of the ring: every consumer warp replays the placement of every chunk the producer issues
 struct DsCons {
     uint32_t ring_s;
     int R, head;
-    int cur;     // byte offset of the chunk the last wait returned
-    uint32_t j;  // chunks waited for so far
+    int cur;        // byte offset of the chunk the last advance returned
+    uint32_t j;     // chunks placed so far
+    int tile_base;  // tiles of the phase so far: tile i belongs to consumer warp i mod 16
 };
-// Waits for the next chunk (of `bytes` bytes); its offset in the ring is left in cs.cur and its index (for the release) is
-// returned; -1 after a timeout / abort.
-__device__ __forceinline__ int ds_chunk_wait(DsCons& cs, DsShared* S, int bytes) {
-    if (cs.head + bytes > cs.R) cs.head = 0;  // same placement rule as the producer
+// Places the next chunk (same rule as the producer); its offset goes to cs.cur, its barrier index is returned.
+__device__ __forceinline__ uint32_t ds_chunk_next(DsCons& cs, int bytes) {
+    if (cs.head + bytes > cs.R) cs.head = 0;
     cs.cur = cs.head;
     cs.head += bytes;
-    const uint32_t idx = cs.j++;
+    return cs.j++;
+}
+__device__ __forceinline__ bool ds_chunk_wait(DsShared* S, uint32_t idx) {
     const bool ok = mbar_wait(&S->full[idx % kDsBars], (idx / kDsBars) & 1u, (volatile int*)&S->abort_flag);
-    return __all_sync(0xffffffffu, ok) ? (int)(idx % kDsBars) : -1;
-}
-__device__ __forceinline__ void ds_chunk_release(DsShared* S, int bar_idx, int lane) {
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&S->empty[bar_idx]);
-}
-
-// dot product of one int8 row piece (in the ring) with the lane's digits: four int32 partial sums, one per digit
-template <int KL>
-__device__ __forceinline__ void ds_dot_i8(uint32_t row_s, int lane, const uint32_t (&xr)[KL], int (&a)[4]) {
-    constexpr int NCH = KL / 16;
-    uint4 w[NCH];
-#pragma unroll
-    for (int i = 0; i < NCH; ++i) w[i] = ds_lds128(row_s + (uint32_t)(lane + 32 * i) * 16u);
-#pragma unroll
-    for (int i = 0; i < NCH; ++i) {
-        const uint32_t ww[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
-#pragma unroll
-        for (int g = 0; g < 4; ++g)
-#pragma unroll
-            for (int d = 0; d < 4; ++d) a[d] = ds_dp4a_us(ww[g], xr[(i * 4 + g) * 4 + d], a[d]);
-    }
-}
-// dot product of one fp16 row piece with the lane's fp32 activations (four chains, fixed order)
-template <int KL>
-__device__ __forceinline__ float ds_dot_f16(uint32_t row_s, int lane, const uint32_t (&xr)[KL]) {
-    constexpr int NCH = KL / 8;
-    float a[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int i = 0; i < NCH; ++i) {
-        const uint4 w = ds_lds128(row_s + (uint32_t)(lane + 32 * i) * 16u);
-        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[e]));
-            a[e] = fmaf(f.x, __uint_as_float(xr[i * 8 + 2 * e]), a[e]);
-            a[e] = fmaf(f.y, __uint_as_float(xr[i * 8 + 2 * e + 1]), a[e]);
-        }
-    }
-    return (a[0] + a[1]) + (a[2] + a[3]);
+    return __all_sync(0xffffffffu, ok);
 }
 
 // What the consumer warps need to turn a row's sums into an output.
 struct DsPhaseCtx {
-    uint32_t vec_s;     // shared-memory address of the operand area
-    int stage_off;      // first staged (scale, zero) of the current entry
-    float best_val;     // running arg-max of the head rows this warp finished (lane 0)
+    uint32_t vec_s;  // shared-memory address of the operand area
+    float best_val;  // running arg-max of the head rows this lane finished
     int best_idx;
 };
 
@@ -306,125 +359,131 @@ __device__ __forceinline__ void ds_store(const DsParams& P, DsShared* S, const D
     }
 }
 
-// One matrix of a phase: the rows [r0, r0 + n) this CTA owns, piece after piece, chunk after chunk.  Row i (counted from r0)
-// belongs to consumer warp i mod 8.  Returns false after a timeout.
-template <int KL>
-__device__ __noinline__ bool ds_run_entry(const DsParams& P, DsShared* S, DsCons& cs, const DsEntry& E, int r0, int n, DsPhaseCtx& pc, int wwarp, int lane) {
-    constexpr int C = KL * 32;
-    const int rpc = ds_rows_per_chunk(E.row_bytes);
-    const bool i8 = E.is_i8 != 0;
-    const bool mine = n > wwarp;
-    float xs = 0.f;
-    long long T = 0;
-    if (i8) {
-        xs = ds_pow2(S->ex[E.xvec] - kDsP);
+// The matrices of one phase.  Chunk order (the producer issues the same): matrix after matrix; inside a matrix groups of 16
+// tiles; inside a group piece after piece; inside a piece the tiles of the group.  Tile i of the phase belongs to consumer
+// warp i mod 16, so a warp owns at most one tile of a group and keeps its accumulators in registers across the pieces.
+// Returns false after a timeout.
+__device__ __noinline__ bool ds_run_entries(const DsParams& P, DsShared* S, DsCons& cs, const DsEntry* ents, int cnt, DsPhaseCtx& pc, int cta, int G, int wwarp,
+                                            int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    int stage_off = 0;
+    cs.tile_base = 0;
+    for (int ei = 0; ei < cnt; ++ei) {
+        const DsEntry& E = ents[ei];
+        int r0, n;
+        ds_rows_of(E, cta, G, r0, n);
+        if (n <= 0) continue;
+        const bool i8 = E.is_i8 != 0;
+        const int ntiles = (n + kDsTileRows - 1) / kDsTileRows, cb = ds_chunk_bytes(E), stride = E.piece_bytes + kDsPad, steps = E.piece_bytes >> 6;
+        const int klen = (i8 ? E.piece_bytes : (E.piece_bytes >> 1)) * E.npieces;  // elements of the operand vector
+        // A fragments of this lane: 16 bytes per two k steps at [k-step pair][row g][t]; rows beyond the operand's are zero
+        const int arows = i8 ? 4 : 2, astep = arows * 64;
+        const uint32_t abase = pc.vec_s + (uint32_t)E.xvec * (uint32_t)klen * 4u + (uint32_t)(g * 4 + t) * 16u;
+        const bool arow_ok = g < arows;
+        float xs = 0.f;
+        long long T = 0;
+        if (i8) {
+            xs = ds_pow2(S->ex[E.xvec] - kDsP);
 #pragma unroll
-        for (int w = 0; w < 8; ++w) T += S->tsw[E.xvec][w];
-    }
-    for (int p = 0; p < E.npieces; ++p) {
-        // ---- the lane's K slice of the activation, in registers for all rows of this piece ----
-        uint32_t xr[KL];
-        if (mine) {
-            if (E.mix) {
-                // rank projections: cur + mix (prev - cur), built from the LayerNorm output and the shift difference in the operand area
-                const uint32_t cur_s = pc.vec_s + 3u * C * 4u, del_s = pc.vec_s + 4u * C * 4u;
+            for (int w = 0; w < kDsConsumerWarps; ++w) T += S->tsw[E.xvec][w];
+        } else {
+            xs = ds_pow2(S->ex[E.xvec]);
+        }
+        for (int g0 = 0; g0 < ntiles; g0 += kDsConsumerWarps) {
+            const int gsz = min(kDsConsumerWarps, ntiles - g0);
+            const int my = (wwarp - cs.tile_base - g0) & (kDsConsumerWarps - 1);
+            const bool mine = my < gsz;
+            const int row0 = (g0 + my) * kDsTileRows, nr = mine ? min(kDsTileRows, n - row0) : 0;
+            int ci[4][4];
+            float cf[4][4];
 #pragma unroll
-                for (int i = 0; i < KL / 8; ++i) {
-                    const int k0 = (lane + 32 * i) * 8;
-                    const float4 m0 = __ldg(reinterpret_cast<const float4*>(E.mix + k0)), m1 = __ldg(reinterpret_cast<const float4*>(E.mix + k0 + 4));
-                    const uint4 c0 = ds_lds128(cur_s + k0 * 4), c1 = ds_lds128(cur_s + k0 * 4 + 16);
-                    const uint4 d0 = ds_lds128(del_s + k0 * 4), d1 = ds_lds128(del_s + k0 * 4 + 16);
-                    const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
-                    const uint32_t cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-                    const uint32_t dd[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+            for (int a = 0; a < 4; ++a)
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) xr[i * 8 + e] = __float_as_uint(__uint_as_float(cc[e]) + mm[e] * __uint_as_float(dd[e]));
+                for (int b = 0; b < 4; ++b) {
+                    ci[a][b] = 0;
+                    cf[a][b] = 0.f;
                 }
-            } else if (i8) {
-                // digits: uint4 (g, c) of the vector holds the four digit words of k = 16 c + 4 g .. + 3, stored at index g * (len / 16) + c
-                const int len16 = (E.npieces * C) / 16;
-                const uint32_t base = pc.vec_s + (uint32_t)E.xvec * C * 4u;
-#pragma unroll
-                for (int i = 0; i < KL / 16; ++i)
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        const uint4 d = ds_lds128(base + (uint32_t)(g * len16 + p * (C / 16) + lane + 32 * i) * 16u);
-                        xr[(i * 4 + g) * 4 + 0] = d.x;
-                        xr[(i * 4 + g) * 4 + 1] = d.y;
-                        xr[(i * 4 + g) * 4 + 2] = d.z;
-                        xr[(i * 4 + g) * 4 + 3] = d.w;
+            for (int p = 0; p < E.npieces; ++p) {
+                for (int q = 0; q < (mine ? my : gsz); ++q) ds_chunk_next(cs, cb);
+                if (mine) {
+                    const uint32_t idx = ds_chunk_next(cs, cb);
+                    if (!ds_chunk_wait(S, idx)) return false;
+                    // ldmatrix row addresses: lane l -> row l % 8 (clamped to the tile's last row), 16-byte column l / 8 of each 64-byte step pair
+                    uint32_t baddr = cs.ring_s + (uint32_t)cs.cur + (uint32_t)min(lane & 7, nr - 1) * (uint32_t)stride + (uint32_t)(lane >> 3) * 16u;
+                    uint32_t aaddr = abase + (uint32_t)p * (uint32_t)steps * (uint32_t)astep;
+                    if (i8) {
+#pragma unroll 2
+                        for (int s = 0; s < steps; s += 2) {
+                            const uint4 b0 = ds_ldmatrix4(baddr), b1 = ds_ldmatrix4(baddr + 64);
+                            uint4 a0 = make_uint4(0, 0, 0, 0), a1 = make_uint4(0, 0, 0, 0);
+                            if (arow_ok) {
+                                a0 = ds_lds128(aaddr);
+                                a1 = ds_lds128(aaddr + astep);
+                            }
+                            ds_mma_i8(ci[0], a0.x, a0.y, b0.x, b0.y);
+                            ds_mma_i8(ci[1], a0.z, a0.w, b0.z, b0.w);
+                            ds_mma_i8(ci[2], a1.x, a1.y, b1.x, b1.y);
+                            ds_mma_i8(ci[3], a1.z, a1.w, b1.z, b1.w);
+                            baddr += 128;
+                            aaddr += 2 * astep;
+                        }
+                    } else {
+#pragma unroll 2
+                        for (int s = 0; s < steps; s += 2) {
+                            const uint4 b0 = ds_ldmatrix4(baddr), b1 = ds_ldmatrix4(baddr + 64);
+                            uint4 a0 = make_uint4(0, 0, 0, 0), a1 = make_uint4(0, 0, 0, 0);
+                            if (arow_ok) {
+                                a0 = ds_lds128(aaddr);
+                                a1 = ds_lds128(aaddr + astep);
+                            }
+                            ds_mma_f16(cf[0], a0.x, a0.y, b0.x, b0.y);
+                            ds_mma_f16(cf[1], a0.z, a0.w, b0.z, b0.w);
+                            ds_mma_f16(cf[2], a1.x, a1.y, b1.x, b1.y);
+                            ds_mma_f16(cf[3], a1.z, a1.w, b1.z, b1.w);
+                            baddr += 128;
+                            aaddr += 2 * astep;
+                        }
                     }
-            } else {
-                const uint32_t base = pc.vec_s + ((uint32_t)E.xvec * C + (uint32_t)p * C) * 4u;
-#pragma unroll
-                for (int i = 0; i < KL / 8; ++i) {
-                    const uint4 a = ds_lds128(base + (uint32_t)(lane + 32 * i) * 32u), b = ds_lds128(base + (uint32_t)(lane + 32 * i) * 32u + 16u);
-                    xr[i * 8 + 0] = a.x;
-                    xr[i * 8 + 1] = a.y;
-                    xr[i * 8 + 2] = a.z;
-                    xr[i * 8 + 3] = a.w;
-                    xr[i * 8 + 4] = b.x;
-                    xr[i * 8 + 5] = b.y;
-                    xr[i * 8 + 6] = b.z;
-                    xr[i * 8 + 7] = b.w;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&S->empty[idx % kDsBars]);
+                    for (int q = my + 1; q < gsz; ++q) ds_chunk_next(cs, cb);
                 }
             }
-        }
-        const bool first = p == 0, last = p == E.npieces - 1;
-        for (int c0 = 0; c0 < n; c0 += rpc) {
-            const int nr = min(rpc, n - c0);
-            const int bar_idx = ds_chunk_wait(cs, S, nr * E.row_bytes);
-            if (bar_idx < 0) return false;
-            const uint32_t ch = cs.ring_s + (uint32_t)cs.cur;
-            const int ia = c0 + ((wwarp - c0) & 7), ib = ia + 8;
-            const bool has_a = ia < c0 + nr, has_b = ib < c0 + nr;
-            if (has_a) {
-                const uint32_t ra = ch + (uint32_t)(ia - c0) * E.row_bytes, rb = ch + (uint32_t)(ib - c0) * E.row_bytes;
+            if (mine) {
+                // accumulator (row g, columns 2 t, 2 t + 1) = operand row g x weight rows 2 t, 2 t + 1 of the tile
                 if (i8) {
-                    int qa[4] = {0, 0, 0, 0}, qb[4] = {0, 0, 0, 0};
-                    ds_dot_i8<KL>(ra, lane, xr, qa);
-                    if (has_b) ds_dot_i8<KL>(rb, lane, xr, qb);
+                    const int q0 = (ci[0][0] + ci[1][0]) + (ci[2][0] + ci[3][0]), q1 = (ci[0][1] + ci[1][1]) + (ci[2][1] + ci[3][1]);
+                    long long v0 = arow_ok ? ((long long)q0 << (8 * g)) : 0, v1 = arow_ok ? ((long long)q1 << (8 * g)) : 0;  // digit g weighs 256^g
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, 4);
+                    v1 += __shfl_xor_sync(0xffffffffu, v1, 4);
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, 8);
+                    v1 += __shfl_xor_sync(0xffffffffu, v1, 8);
+                    if (lane < 4) {
 #pragma unroll
-                    for (int d = 0; d < 4; ++d) {
-                        qa[d] = __reduce_add_sync(0xffffffffu, qa[d]);
-                        qb[d] = __reduce_add_sync(0xffffffffu, qb[d]);
-                    }
-                    if (lane < 2 && (lane == 0 || has_b)) {
-                        // lane 0 finishes row a, lane 1 row b
-                        const int q0 = lane ? qb[0] : qa[0], q1 = lane ? qb[1] : qa[1], q2 = lane ? qb[2] : qa[2], q3 = lane ? qb[3] : qa[3];
-                        const int rl = lane ? ib : ia;
-                        long long Q = (((long long)q0 * 128 + q1) * 128 + q2) * 128 + q3;
-                        if (!first) Q += S->qacc[rl];
-                        if (!last) {
-                            S->qacc[rl] = Q;
-                        } else {
-                            const double ws = S->ws[pc.stage_off + rl], wz = S->wz[pc.stage_off + rl];
-                            ds_store(P, S, E, r0 + rl, rl, (float)((double)xs * (ws * (double)Q + wz * (double)T)), pc);
+                        for (int e = 0; e < 2; ++e) {
+                            const int rl = row0 + 2 * t + e;
+                            if (rl < n) {
+                                const double ws = S->ws[stage_off + rl], wz = S->wz[stage_off + rl];
+                                ds_store(P, S, E, r0 + rl, rl, (float)((double)xs * (ws * (double)(e ? v1 : v0) + wz * (double)T)), pc);
+                            }
                         }
                     }
                 } else {
-                    float ya = ds_dot_f16<KL>(ra, lane, xr), yb = has_b ? ds_dot_f16<KL>(rb, lane, xr) : 0.f;
+                    float f0 = (cf[0][0] + cf[1][0]) + (cf[2][0] + cf[3][0]), f1 = (cf[0][1] + cf[1][1]) + (cf[2][1] + cf[3][1]);
+                    f0 += __shfl_xor_sync(0xffffffffu, f0, 4);  // hi + lo
+                    f1 += __shfl_xor_sync(0xffffffffu, f1, 4);
+                    if (lane < 4) {
 #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) {
-                        ya += __shfl_xor_sync(0xffffffffu, ya, o);
-                        yb += __shfl_xor_sync(0xffffffffu, yb, o);
-                    }
-                    if (lane == 0) {
-                        // both rows by lane 0: the arg-max of the head rows is kept in its registers
-                        for (int s = 0; s < (has_b ? 2 : 1); ++s) {
-                            const int rl = s ? ib : ia;
-                            float y = s ? yb : ya;
-                            if (!first) y += S->facc[rl];
-                            if (!last)
-                                S->facc[rl] = y;
-                            else
-                                ds_store(P, S, E, r0 + rl, rl, y, pc);
+                        for (int e = 0; e < 2; ++e) {
+                            const int rl = row0 + 2 * t + e;
+                            if (rl < n) ds_store(P, S, E, r0 + rl, rl, (e ? f1 : f0) * xs, pc);
                         }
                     }
                 }
             }
-            ds_chunk_release(S, bar_idx, lane);
         }
+        cs.tile_base = (cs.tile_base + ntiles) & (kDsConsumerWarps - 1);
+        if (i8) stage_off += n;
     }
     return true;
 }
@@ -446,65 +505,20 @@ __device__ __forceinline__ long long ds_now() {
     } while (0)
 #endif
 
-// Sum / maximum over the 256 consumer threads through an 8-entry array: one barrier per call.  Calls that follow each other
-// must use different arrays (a thread may enter the next call while another still reads this one's array).
+// Sum over the 512 consumer threads through a 16-entry array: one barrier per call.  Calls that follow each other must use
+// different arrays (a thread may enter the next call while another still reads this one's array).
 __device__ __forceinline__ float ds_block_sum(float v, float* arr, int wwarp, int lane) {
     v = warp_sum(v);
     if (lane == 0) arr[wwarp] = v;
     ds_consumer_sync();
-    return ((arr[0] + arr[1]) + (arr[2] + arr[3])) + ((arr[4] + arr[5]) + (arr[6] + arr[7]));
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDsConsumerWarps; w += 4) s += (arr[w] + arr[w + 1]) + (arr[w + 2] + arr[w + 3]);
+    return s;
 }
-
-// The activation vectors of a phase -> the operand area.  Vector v (LEN elements, NGR groups of four per thread) becomes
-// base-128 digits in dp4a order when its matrix is int8 (uint4 (g, c) at index g * (LEN / 16) + c holds the digit words of
-// k = 16 c + 4 g .. + 3), plain fp32 otherwise; the scale exponent goes to S->ex[v], the exact fixed-point sum to S->tsw[v].
-template <int NV, int NGR>
-__device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const bool (&i8)[NV], const float4 (&val)[NV][NGR], int wtid) {
-    const int wwarp = wtid >> 5, lane = wtid & 31, len4 = len >> 2;
-    float am[NV];
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-        am[v] = 0.f;
-#pragma unroll
-        for (int gi = 0; gi < NGR; ++gi)
-            if (wtid + kDsConsumers * gi < len4)
-                am[v] = fmaxf(am[v], fmaxf(fmaxf(fabsf(val[v][gi].x), fabsf(val[v][gi].y)), fmaxf(fabsf(val[v][gi].z), fabsf(val[v][gi].w))));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) am[v] = fmaxf(am[v], __shfl_xor_sync(0xffffffffu, am[v], o));
-        if (lane == 0) S->red_c[v * 8 + wwarp] = am[v];
-    }
-    ds_consumer_sync();
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-        float a = 0.f;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) a = fmaxf(a, S->red_c[v * 8 + w]);
-        const int ex = ds_exponent(a);
-        const float mult = ds_pow2(kDsP - ex);
-        if (wtid == 0) S->ex[v] = ex;
-        long long ts = 0;
-        float* vbase = vec + (size_t)v * len;
-#pragma unroll
-        for (int gi = 0; gi < NGR; ++gi) {
-            const int g4 = wtid + kDsConsumers * gi;
-            if (g4 < len4) {
-                if (i8[v]) {
-                    const uint4 d = ds_digits4(val[v][gi], mult, ts);
-                    reinterpret_cast<uint4*>(vbase)[(g4 & 3) * (len >> 4) + (g4 >> 2)] = d;
-                } else {
-                    reinterpret_cast<float4*>(vbase)[g4] = val[v][gi];
-                }
-            }
-        }
-        ts = ds_warp_sum_ll(ts);
-        if (lane == 0) S->tsw[v][wwarp] = ts;
-    }
-    ds_consumer_sync();
-}
-
 // LayerNorm statistics (two passes, as the CPU path) of a C-vector spread over the consumer threads (NGR groups of four each)
-template <int C, int NGR>
-__device__ __forceinline__ void ds_ln_stats(DsShared* S, const float4 (&xv)[NGR], int wtid, float& mean, float& inv) {
+template <int NGR>
+__device__ __forceinline__ void ds_ln_stats(DsShared* S, int C, const float4 (&xv)[NGR], int wtid, float& mean, float& inv) {
     const int wwarp = wtid >> 5, lane = wtid & 31;
     float s = 0.f;
 #pragma unroll
@@ -529,10 +543,11 @@ __device__ __forceinline__ float4 ds_mix4(float4 cur, float4 m, float4 del) {
 __device__ __forceinline__ float4 ds_ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
 __device__ __forceinline__ float4 ds_ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
 
-template <int KL>
+// CMAX: the largest n_embd the instantiation handles (it sizes the per-thread register arrays of the activation vectors)
+template <int CMAX>
 __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __grid_constant__ DsParams P) {
-    constexpr int C = KL * 32;
-    constexpr int NG = (C / 4 + kDsConsumers - 1) / kDsConsumers;  // groups of four channels per consumer thread
+    constexpr int NG = (CMAX / 4 + kDsConsumers - 1) / kDsConsumers;  // groups of four channels per consumer thread
+    constexpr int NG5 = (CMAX + kDsConsumers - 1) / kDsConsumers;     // groups of four of the F = 4 C hidden values per thread
     extern __shared__ __align__(1024) uint8_t ds_smem_raw[];
     uint8_t* ring = (uint8_t*)(((uintptr_t)ds_smem_raw + 127) & ~(uintptr_t)127);
     float* vec = reinterpret_cast<float*>(ring + P.ring_bytes);
@@ -542,7 +557,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = gridDim.x, cta = blockIdx.x;
-    const int R = P.ring_bytes;
+    const int R = P.ring_bytes, C = P.C;
     const int nmid = P.wm + P.am + P.vm + P.gm;
     // bytes of the three chunks that carry a head's rank back-projection rows
     const int hbA = 64 * (P.wm + P.am) * 2, hbC = 32 * P.gm * 2;
@@ -550,7 +565,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
     if (threadIdx.x == 0) {
         for (int s = 0; s < kDsBars; ++s) {
             mbar_init(&S->full[s], 1);
-            mbar_init(&S->empty[s], kDsConsumerWarps);
+            mbar_init(&S->empty[s], 1);
         }
         S->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -564,21 +579,22 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
         int head = 0, used = 0;
         uint32_t j = 0, tail = 0;
         bool ok = true;
-        // Reserves `bytes` in the ring for chunk j (waiting for the oldest chunks to be released), arms its barrier, and
-        // leaves its offset in `head - bytes`.
-        auto reserve = [&](int bytes) -> bool {
-            const int waste = (head + bytes > R) ? R - head : 0;
+        // Reserves `bytes` in the ring for chunk j (waiting for the oldest chunks to be released) and arms its barrier for
+        // `tx` bytes of copies; the chunk starts at `head - bytes`.
+        auto reserve = [&](int bytes, int tx) -> bool {
+            const bool wrap = head + bytes > R;  // the chunk does not fit behind the last one: it goes to the start of the ring
+            const int waste = wrap ? R - head : 0;
             while (used + waste + bytes > R || j - tail >= (uint32_t)kDsBars) {
                 const bool w = mbar_wait(&S->empty[tail % kDsBars], (tail / kDsBars) & 1u, abort_flag);
                 if (!__all_sync(0xffffffffu, w)) return false;
                 used -= S->alloc[tail % kDsBars];
                 ++tail;
             }
-            if (waste) head = 0;
+            if (wrap) head = 0;
             __syncwarp();
             if (lane == 0) {
                 S->alloc[j % kDsBars] = waste + bytes;
-                mbar_expect_tx(&S->full[j % kDsBars], (uint32_t)bytes);
+                mbar_expect_tx(&S->full[j % kDsBars], (uint32_t)tx);
             }
             __syncwarp();
             used += waste + bytes;
@@ -586,21 +602,21 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
             return true;
         };
         auto put_entry = [&](const DsEntry& E) -> bool {
-            if (E.M <= 0) return true;
-            const int vc = (cta + E.rot) % G;
-            const int r0 = ds_row_begin(vc, E.M, G), n = ds_row_begin(vc + 1, E.M, G) - r0;
+            int r0, n;
+            ds_rows_of(E, cta, G, r0, n);
             if (n <= 0) return true;
-            const int rpc = ds_rows_per_chunk(E.row_bytes);
-            for (int p = 0; p < E.npieces; ++p)
-                for (int c0 = 0; c0 < n; c0 += rpc) {
-                    const int nr = min(rpc, n - c0), bytes = nr * E.row_bytes;
-                    if (!reserve(bytes)) return false;
-                    if (lane < nr)
-                        ds_bulk_load(ring_s + (uint32_t)(head - bytes + lane * E.row_bytes),
-                                     E.base + (size_t)(r0 + c0 + lane) * (size_t)E.row_stride + (size_t)p * E.row_bytes, (uint32_t)E.row_bytes,
-                                     &S->full[j % kDsBars], pol);
-                    ++j;
-                }
+            const int ntiles = (n + kDsTileRows - 1) / kDsTileRows, cb = ds_chunk_bytes(E), stride = E.piece_bytes + kDsPad;
+            for (int g0 = 0; g0 < ntiles; g0 += kDsConsumerWarps)
+                for (int p = 0; p < E.npieces; ++p)
+                    for (int ti = g0; ti < min(g0 + kDsConsumerWarps, ntiles); ++ti) {
+                        const int row0 = ti * kDsTileRows, nr = min(kDsTileRows, n - row0);
+                        if (!reserve(cb, nr * E.piece_bytes)) return false;
+                        if (lane < nr)
+                            ds_bulk_load(ring_s + (uint32_t)(head - cb + lane * stride),
+                                         E.base + (size_t)(r0 + row0 + lane) * (size_t)E.row_stride + (size_t)p * E.piece_bytes, (uint32_t)E.piece_bytes,
+                                         &S->full[j % kDsBars], pol);
+                        ++j;
+                    }
             return true;
         };
         for (int t = 0; t < P.n_tokens && ok; ++t) {
@@ -613,16 +629,16 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 if (h >= 0) {
                     // chunk A: w2, a2 rows of the head; chunk B: v2 rows (layers > 0) and the first 32 g2 rows; chunk C: the other 32
                     const int vb = l > 0 ? 64 * P.vm * 2 : 0;
-                    if (!(ok = reserve(hbA))) break;
+                    if (!(ok = reserve(hbA, hbA))) break;
                     if (lane == 0) ds_bulk_load(ring_s + (uint32_t)(head - hbA), Lg->w2 + (size_t)h * 64 * P.wm, 64u * P.wm * 2u, &S->full[j % kDsBars], pol);
                     if (lane == 1)
                         ds_bulk_load(ring_s + (uint32_t)(head - hbA + 64 * P.wm * 2), Lg->a2 + (size_t)h * 64 * P.am, 64u * P.am * 2u, &S->full[j % kDsBars], pol);
                     ++j;
-                    if (!(ok = reserve(vb + hbC))) break;
+                    if (!(ok = reserve(vb + hbC, vb + hbC))) break;
                     if (lane == 0 && vb) ds_bulk_load(ring_s + (uint32_t)(head - vb - hbC), Lg->v2 + (size_t)h * 64 * P.vm, (uint32_t)vb, &S->full[j % kDsBars], pol);
                     if (lane == 1) ds_bulk_load(ring_s + (uint32_t)(head - hbC), Lg->g2 + (size_t)h * 64 * P.gm, (uint32_t)hbC, &S->full[j % kDsBars], pol);
                     ++j;
-                    if (!(ok = reserve(hbC))) break;
+                    if (!(ok = reserve(hbC, hbC))) break;
                     if (lane == 0) ds_bulk_load(ring_s + (uint32_t)(head - hbC), Lg->g2 + ((size_t)h * 64 + 32) * P.gm, (uint32_t)hbC, &S->full[j % kDsBars], pol);
                     ++j;
                 }
@@ -636,8 +652,8 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
     } else {
         // =========================== consumers ===========================
         const int wtid = threadIdx.x - 32, wwarp = wtid >> 5;
-        DsCons cs{smem_u32(ring), R, 0, 0, 0u};
-        DsPhaseCtx pc{smem_u32(vec), 0, -1e30f, 0x7fffffff};
+        DsCons cs{smem_u32(ring), R, 0, 0, 0u, 0};
+        DsPhaseCtx pc{smem_u32(vec), -1e30f, 0x7fffffff};
         unsigned bar_target = 0;
         bool ok = true, pending = false;
         const int r0o = ds_row_begin(cta, C, G), nown = ds_row_begin(cta + 1, C, G) - r0o;  // this CTA's slice of the channels
@@ -650,7 +666,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
             for (int i = wtid; i < (int)(sizeof(DsLayer) / 4); i += kDsConsumers) dst[i] = __ldg(src + i);
         };
         // Grid barrier in two halves: arrive as soon as this CTA's outputs are stored, wait just before the first load of
-        // another CTA's outputs; what lies between (parameter loads of the next phase) overlaps the other CTAs' tails.
+        // another CTA's outputs; what lies between (parameter staging of the next phase) overlaps the other CTAs' tails.
         // The counter only ever grows, so a CTA must have seen barrier n complete before it arrives on barrier n + 1
         // (otherwise its second arrival could stand in for a CTA that has not reached barrier n yet).
         auto bar_wait = [&]() -> bool {
@@ -682,20 +698,13 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
             bar_target += (unsigned)G;
             pending = true;
         };
-        auto rows_of = [&](const DsEntry& E, int& r0, int& n) {
-            r0 = n = 0;
-            if (E.M <= 0) return;
-            const int vc = (cta + E.rot) % G;
-            r0 = ds_row_begin(vc, E.M, G);
-            n = ds_row_begin(vc + 1, E.M, G) - r0;
-        };
         // (scale, zero) of the int8 rows this CTA owns in the coming phase -> shared memory (weights: no dependency on a barrier)
         auto stage_scales = [&](const DsEntry* ents, int cnt) {
             int off = 0;
             for (int i = 0; i < cnt; ++i) {
                 const DsEntry& E = ents[i];
                 int r0, n;
-                rows_of(E, r0, n);
+                ds_rows_of(E, cta, G, r0, n);
                 if (!E.is_i8 || n <= 0) continue;
                 for (int q = wtid; q < n && off + q < kDsMaxRows; q += kDsConsumers) {
                     S->ws[off + q] = __ldg(E.wscale + r0 + q);
@@ -704,18 +713,14 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 off += n;
             }
         };
-        auto run_entries = [&](const DsEntry* ents, int cnt) -> bool {
-            int off = 0;
-            for (int i = 0; i < cnt; ++i) {
-                const DsEntry& E = ents[i];
+        // the rank projection whose rows this CTA owns (at most one: their rows are split over disjoint groups of CTAs)
+        auto my_rank_entry = [&](const DsLayer& Ly) -> int {
+            for (int e = DSE_W1; e <= DSE_V1; ++e) {
                 int r0, n;
-                rows_of(E, r0, n);
-                if (n <= 0) continue;
-                pc.stage_off = off;
-                if (!ds_run_entry<KL>(P, S, cs, E, r0, n, pc, wwarp, lane)) return false;
-                if (E.is_i8) off += n;
+                ds_rows_of(Ly.e[e], cta, G, r0, n);
+                if (n > 0) return e;
             }
-            return true;
+            return -1;
         };
 
         for (int t = 0; t < P.n_tokens && ok; ++t) {
@@ -740,19 +745,24 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 DS_STAMP(0);
                 // ================= phase 1: LN1 + token shift -> r, k, v, rank projections =================
                 {
-                    float4 lw[NG], lb[NG], pv[NG], mr[NG], mk[NG], mv[NG], xv[NG];
+                    const int re = my_rank_entry(Ly);
+                    const float* rmix = re >= 0 ? Ly.e[re].mix : Ly.x_r;
+                    stage_scales(&Ly.e[DSE_W1], 7);
+                    if (!(ok = bar_wait())) break;
+                    DS_STAMP(10);
+                    float4 xv[NG], lw[NG], lb[NG], pv[NG], mx[4][NG];
 #pragma unroll
                     for (int gi = 0; gi < NG; ++gi) {
                         const int g4 = wtid + kDsConsumers * gi, k = g4 < C / 4 ? 4 * g4 : 0;
+                        if (l > 0) xv[gi] = ds_ldcg4(P.x + k);
+                        pv[gi] = ds_ldcg4(tm_l + k);
                         lw[gi] = ds_ldg4(Ly.ln1_w + k);
                         lb[gi] = ds_ldg4(Ly.ln1_b + k);
-                        mr[gi] = ds_ldg4(Ly.x_r + k);
-                        mk[gi] = ds_ldg4(Ly.x_k + k);
-                        mv[gi] = ds_ldg4(Ly.x_v + k);
-                        pv[gi] = ds_ldcg4(tm_l + k);
+                        mx[0][gi] = ds_ldg4(Ly.x_r + k);
+                        mx[1][gi] = ds_ldg4(Ly.x_k + k);
+                        mx[2][gi] = ds_ldg4(Ly.x_v + k);
+                        mx[3][gi] = ds_ldg4(rmix + k);
                     }
-                    stage_scales(&Ly.e[DSE_W1], 7);
-                    if (!(ok = bar_wait())) break;
                     if (l == 0) {
                         // x = LN0(embedding row): every CTA builds the whole vector itself
                         const __half* erow = P.emb + (size_t)tok * C;
@@ -767,43 +777,35 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                             b0v[gi] = ds_ldg4(P.ln0_b + k);
                         }
                         float m0, i0;
-                        ds_ln_stats<C, NG>(S, xv, wtid, m0, i0);
+                        ds_ln_stats<NG>(S, C, xv, wtid, m0, i0);
 #pragma unroll
                         for (int gi = 0; gi < NG; ++gi) xv[gi] = ds_ln_apply(xv[gi], m0, i0, w0v[gi], b0v[gi]);
-                    } else {
-#pragma unroll
-                        for (int gi = 0; gi < NG; ++gi) {
-                            const int g4 = wtid + kDsConsumers * gi, k = g4 < C / 4 ? 4 * g4 : 0;
-                            xv[gi] = ds_ldcg4(P.x + k);
-                        }
                     }
                     float mean, inv;
-                    ds_ln_stats<C, NG>(S, xv, wtid, mean, inv);
-                    float4 val[3][NG];
+                    ds_ln_stats<NG>(S, C, xv, wtid, mean, inv);
+                    float4 cur[NG], del[NG];
 #pragma unroll
                     for (int gi = 0; gi < NG; ++gi) {
                         const int g4 = wtid + kDsConsumers * gi;
-                        const float4 cur = ds_ln_apply(xv[gi], mean, inv, lw[gi], lb[gi]);
-                        const float4 del = make_float4(pv[gi].x - cur.x, pv[gi].y - cur.y, pv[gi].z - cur.z, pv[gi].w - cur.w);
-                        val[0][gi] = ds_mix4(cur, mr[gi], del);
-                        val[1][gi] = ds_mix4(cur, mk[gi], del);
-                        val[2][gi] = ds_mix4(cur, mv[gi], del);
+                        cur[gi] = ds_ln_apply(xv[gi], mean, inv, lw[gi], lb[gi]);
+                        del[gi] = make_float4(pv[gi].x - cur[gi].x, pv[gi].y - cur[gi].y, pv[gi].z - cur[gi].z, pv[gi].w - cur[gi].w);
                         if (g4 < C / 4) {
-                            reinterpret_cast<float4*>(vec + 3 * C)[g4] = cur;  // LN1(x): the new shift state and the rank projections' input
-                            reinterpret_cast<float4*>(vec + 4 * C)[g4] = del;
-                            const float xe[4] = {xv[gi].x, xv[gi].y, xv[gi].z, xv[gi].w};
+                            const float xe[4] = {xv[gi].x, xv[gi].y, xv[gi].z, xv[gi].w}, ce[4] = {cur[gi].x, cur[gi].y, cur[gi].z, cur[gi].w};
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const int o = 4 * g4 + e - r0o;
-                                if (o >= 0 && o < nown) S->xs_own[o] = xe[e];
+                                if (o >= 0 && o < nown) {
+                                    S->xs_own[o] = xe[e];
+                                    S->ts_own[o] = ce[e];  // LN1(x): the new time-mix shift state, stored after barrier 2
+                                }
                             }
                         }
                     }
-                    const bool i8[3] = {Ly.e[DSE_WR].is_i8 != 0, Ly.e[DSE_WK].is_i8 != 0, Ly.e[DSE_WV].is_i8 != 0};
-                    ds_emit<3, NG>(S, vec, C, i8, val, wtid);
+                    const bool i8[4] = {Ly.e[DSE_WR].is_i8 != 0, Ly.e[DSE_WK].is_i8 != 0, Ly.e[DSE_WV].is_i8 != 0, false};
+                    ds_emit<4, NG>(S, vec, C, i8, [&](int v, int gi) { return ds_mix4(cur[gi], mx[v][gi], del[gi]); }, wtid);
                 }
                 DS_STAMP(1);
-                if (!(ok = run_entries(&Ly.e[DSE_W1], 7))) break;
+                if (!(ok = ds_run_entries(P, S, cs, &Ly.e[DSE_W1], 7, pc, cta, G, wwarp, lane))) break;
                 DS_STAMP(2);
                 bar_arrive();
 
@@ -811,16 +813,19 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 {
                     const int h = ds_head_of_cta(cta, l, P.H, G);
                     if (h >= 0) {
-                        const int rrow = wtid >> 2, quad = wtid & 3, ch = h * 64 + rrow;  // 4 threads per channel / state row
-                        float* srow = wkv_l + ((size_t)h * 64 + rrow) * 64 + quad * 16;
-                        float4 s4[4];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) s4[q] = ds_ldcg4(srow + 4 * q);
-                        const float p_w0 = __ldg(Ly.w0 + ch), p_a0 = __ldg(Ly.a0 + ch), p_kk = __ldg(Ly.k_k + ch), p_ka = __ldg(Ly.k_a + ch), p_rk = __ldg(Ly.r_k + ch);
+                        // state: 8 threads per row, 8 columns each; back-projections: threads 0-255 (4 per channel) do decay, a and the
+                        // v gate, threads 256-511 the (longer) output gate
+                        const int rrow = wtid >> 3, oct = wtid & 7, ch = h * 64 + rrow;
+                        const int drow = (wtid & 255) >> 2, quad = wtid & 3, dch = h * 64 + drow;
+                        const bool upper = wtid >= 256;
+                        float* srow = wkv_l + ((size_t)h * 64 + rrow) * 64 + oct * 8;
+                        const float4 s4a = ds_ldcg4(srow), s4b = ds_ldcg4(srow + 4);
+                        const float p_w0 = __ldg(Ly.w0 + dch), p_a0 = __ldg(Ly.a0 + dch), p_kk = __ldg(Ly.k_k + dch), p_ka = __ldg(Ly.k_a + dch), p_rk = __ldg(Ly.r_k + dch);
+                        const float p_v0 = l > 0 ? __ldg(Ly.v0 + dch) : 0.f;
                         const float p_gw = __ldg(Ly.lnx_w + ch), p_gb = __ldg(Ly.lnx_b + ch);
-                        const float p_v0 = l > 0 ? __ldg(Ly.v0 + ch) : 0.f;
                         if (!(ok = bar_wait())) break;
-                        const float p_vf = l > 0 ? __ldcg(P.vfirst + ch) : 0.f;
+                        DS_STAMP(11);
+                        const float p_vf = l > 0 ? __ldcg(P.vfirst + dch) : 0.f;
                         // rank-space vectors and r, k, v of this head -> shared memory
                         for (int q = wtid; q < nmid + 3 * 64; q += kDsConsumers) {
                             const int qq = q - nmid;
@@ -831,7 +836,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                                 S->hv[qq] = v2;
                         }
                         ds_consumer_sync();
-                        // back-projections: the four threads of a channel split the rank dimension in contiguous quarters
+                        // a row of a back-projection matrix times its rank-space vector: four threads split the rank dimension in contiguous quarters
                         auto dot_q = [&](const __half* W, int mid, const float* v) {
                             float a = 0.f;
                             const int ql = mid >> 2;
@@ -855,90 +860,107 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                             return a + __shfl_xor_sync(0xffffffffu, a, 2);
                         };
                         const int vb = l > 0 ? 64 * P.vm * 2 : 0;
-                        const int bA = ds_chunk_wait(cs, S, hbA);
-                        if (bA < 0) {
-                            ok = false;
-                            break;
-                        }
-                        const __half* w2s = reinterpret_cast<const __half*>(ring + cs.cur);
-                        const float dw = dot_q(w2s + (size_t)rrow * P.wm, P.wm, sc_mid);
-                        const float da = dot_q(w2s + (size_t)64 * P.wm + (size_t)rrow * P.am, P.am, sc_mid + P.wm);
-                        ds_chunk_release(S, bA, lane);
-                        const int bB = ds_chunk_wait(cs, S, vb + hbC);
+                        const uint32_t iA = ds_chunk_next(cs, hbA);
+                        const uint8_t* cA = ring + cs.cur;
+                        const uint32_t iB = ds_chunk_next(cs, vb + hbC);
                         const uint8_t* cB = ring + cs.cur;
-                        const int bC = bB < 0 ? -1 : ds_chunk_wait(cs, S, hbC);
+                        const uint32_t iC = ds_chunk_next(cs, hbC);
                         const uint8_t* cC = ring + cs.cur;
-                        if (bB < 0 || bC < 0) {
+                        if (!ds_chunk_wait(S, iA)) {
                             ok = false;
                             break;
                         }
-                        const __half* g2row = rrow < 32 ? reinterpret_cast<const __half*>(cB + vb) + (size_t)rrow * P.gm : reinterpret_cast<const __half*>(cC) + (size_t)(rrow - 32) * P.gm;
-                        const float dg = dot_q(g2row, P.gm, sc_mid + P.wm + P.am + P.vm);
-                        const float dv = l > 0 ? dot_q(reinterpret_cast<const __half*>(cB) + (size_t)rrow * P.vm, P.vm, sc_mid + P.wm + P.am) : 0.f;
-                        ds_chunk_release(S, bB, lane);
-                        ds_chunk_release(S, bC, lane);
-                        const float wdec = expf((1.0f / (1.0f + expf(-(dw + p_w0)))) * kDecayScale);
-                        const float aa = 1.0f / (1.0f + expf(-(da + p_a0)));
-                        const float rr = S->hv[rrow], kk0 = S->hv[64 + rrow];
-                        float vv0 = S->hv[128 + rrow];
-                        if (l == 0) {
-                            if (quad == 0) {
-                                P.vfirst[ch] = vv0;
-                                P.state_vfirst[(size_t)P.slot * C + ch] = vv0;
-                            }
-                        } else {
-                            const float gate = 1.0f / (1.0f + expf(-(dv + p_v0)));
-                            vv0 = vv0 + gate * (p_vf - vv0);
+                        float dw = 0.f, da = 0.f, dv = 0.f, dg = 0.f;
+                        if (!upper) {
+                            const __half* w2s = reinterpret_cast<const __half*>(cA);
+                            dw = dot_q(w2s + (size_t)drow * P.wm, P.wm, sc_mid);
+                            da = dot_q(w2s + (size_t)64 * P.wm + (size_t)drow * P.am, P.am, sc_mid + P.wm);
                         }
-                        const float kkj = kk0 * p_kk;
-                        const float kt = kk0 + p_ka * (kk0 * aa - kk0);
-                        // ||kk||^2 and the bonus sum over the head's 64 channels in one round
-                        float ss = warp_sum(quad == 0 ? kkj * kkj : 0.f), srk = warp_sum(quad == 0 ? rr * kt * p_rk : 0.f);
-                        if (lane == 0) {
-                            S->red_a[wwarp] = ss;
-                            S->red_b[wwarp] = srk;
+                        if (!ds_chunk_wait(S, iB) || !ds_chunk_wait(S, iC)) {
+                            ok = false;
+                            break;
                         }
-                        ds_consumer_sync();
-                        ss = ((S->red_a[0] + S->red_a[1]) + (S->red_a[2] + S->red_a[3])) + ((S->red_a[4] + S->red_a[5]) + (S->red_a[6] + S->red_a[7]));
-                        srk = ((S->red_b[0] + S->red_b[1]) + (S->red_b[2] + S->red_b[3])) + ((S->red_b[4] + S->red_b[5]) + (S->red_b[6] + S->red_b[7]));
-                        const float kkh = kkj * (1.0f / fmaxf(sqrtf(ss), kL2Eps));
+                        if (upper) {
+                            const __half* g2row = drow < 32 ? reinterpret_cast<const __half*>(cB + vb) + (size_t)drow * P.gm : reinterpret_cast<const __half*>(cC) + (size_t)(drow - 32) * P.gm;
+                            dg = dot_q(g2row, P.gm, sc_mid + P.wm + P.am + P.vm);
+                        } else if (l > 0) {
+                            dv = dot_q(reinterpret_cast<const __half*>(cB) + (size_t)drow * P.vm, P.vm, sc_mid + P.wm + P.am);
+                        }
+                        // per-channel quantities of the head -> shared memory; ||kk||^2 and the bonus sum over the 64 channels
+                        float ssp = 0.f, srp = 0.f;
                         if (quad == 0) {
-                            S->hv[3 * 64 + rrow] = wdec;
-                            S->hv[4 * 64 + rrow] = rr;
-                            S->hv[5 * 64 + rrow] = kkh;
-                            S->hv[6 * 64 + rrow] = kkh * (-aa);
-                            S->hv[7 * 64 + rrow] = kt;
+                            if (upper) {
+                                S->hv[8 * 64 + drow] = dg;
+                            } else {
+                                const float wdec = expf((1.0f / (1.0f + expf(-(dw + p_w0)))) * kDecayScale);
+                                const float aa = 1.0f / (1.0f + expf(-(da + p_a0)));
+                                const float rr = S->hv[drow], kk0 = S->hv[64 + drow];
+                                float vv0 = S->hv[128 + drow];
+                                if (l == 0) {
+                                    P.vfirst[dch] = vv0;
+                                    P.state_vfirst[(size_t)P.slot * C + dch] = vv0;
+                                } else {
+                                    const float gate = 1.0f / (1.0f + expf(-(dv + p_v0)));
+                                    vv0 = vv0 + gate * (p_vf - vv0);
+                                }
+                                const float kkj = kk0 * p_kk;
+                                const float kt = kk0 + p_ka * (kk0 * aa - kk0);
+                                S->hv[3 * 64 + drow] = wdec;
+                                S->hv[4 * 64 + drow] = kkj;
+                                S->hv[5 * 64 + drow] = aa;
+                                S->hv[6 * 64 + drow] = kt;
+                                S->hv[7 * 64 + drow] = vv0;
+                                ssp = kkj * kkj;
+                                srp = rr * kt * p_rk;
+                            }
                         }
-                        ds_consumer_sync();
-                        float St[16];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            St[4 * q] = s4[q].x;
-                            St[4 * q + 1] = s4[q].y;
-                            St[4 * q + 2] = s4[q].z;
-                            St[4 * q + 3] = s4[q].w;
+                        ssp = warp_sum(ssp);
+                        srp = warp_sum(srp);
+                        if (lane == 0) {
+                            S->red_a[wwarp] = ssp;
+                            S->red_b[wwarp] = srp;
                         }
-                        const float *s_w = S->hv + 3 * 64 + quad * 16, *s_r = S->hv + 4 * 64 + quad * 16, *s_kk = S->hv + 5 * 64 + quad * 16,
-                                    *s_b = S->hv + 6 * 64 + quad * 16, *s_kt = S->hv + 7 * 64 + quad * 16;
-                        float sa = 0.f;
+                        ds_consumer_sync();  // also: every warp is done with the three chunks
+                        if (wtid == 0) {
+                            mbar_arrive(&S->empty[iA % kDsBars]);
+                            mbar_arrive(&S->empty[iB % kDsBars]);
+                            mbar_arrive(&S->empty[iC % kDsBars]);
+                        }
+                        float ss = 0.f, srk = 0.f;
 #pragma unroll
-                        for (int q = 0; q < 16; ++q) sa = fmaf(St[q], s_kk[q], sa);
+                        for (int w = 0; w < 8; w += 4) {
+                            ss += (S->red_a[w] + S->red_a[w + 1]) + (S->red_a[w + 2] + S->red_a[w + 3]);
+                            srk += (S->red_b[w] + S->red_b[w + 1]) + (S->red_b[w + 2] + S->red_b[w + 3]);
+                        }
+                        const float invn = 1.0f / fmaxf(sqrtf(ss), kL2Eps);
+                        const float vv_row = S->hv[7 * 64 + rrow];
+                        float St[8] = {s4a.x, s4a.y, s4a.z, s4a.w, s4b.x, s4b.y, s4b.z, s4b.w};
+                        float kkh[8], sa = 0.f;
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            kkh[q] = S->hv[4 * 64 + oct * 8 + q] * invn;
+                            sa = fmaf(St[q], kkh[q], sa);
+                        }
                         sa += __shfl_xor_sync(0xffffffffu, sa, 1);
                         sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+                        sa += __shfl_xor_sync(0xffffffffu, sa, 4);
                         float y = 0.f;
 #pragma unroll
-                        for (int q = 0; q < 16; ++q) {
-                            St[q] = fmaf(St[q], s_w[q], fmaf(sa, s_b[q], vv0 * s_kt[q]));
-                            y = fmaf(St[q], s_r[q], y);
+                        for (int q = 0; q < 8; ++q) {
+                            const int c = oct * 8 + q;
+                            const float bq = kkh[q] * (-S->hv[5 * 64 + c]);
+                            St[q] = fmaf(St[q], S->hv[3 * 64 + c], fmaf(sa, bq, vv_row * S->hv[6 * 64 + c]));
+                            y = fmaf(St[q], S->hv[c], y);
                         }
                         y += __shfl_xor_sync(0xffffffffu, y, 1);
                         y += __shfl_xor_sync(0xffffffffu, y, 2);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) *reinterpret_cast<float4*>(srow + 4 * q) = make_float4(St[4 * q], St[4 * q + 1], St[4 * q + 2], St[4 * q + 3]);
-                        const float gmean = ds_block_sum(quad == 0 ? y : 0.f, S->red_c, wwarp, lane) / 64.0f;
+                        y += __shfl_xor_sync(0xffffffffu, y, 4);
+                        *reinterpret_cast<float4*>(srow) = make_float4(St[0], St[1], St[2], St[3]);
+                        *reinterpret_cast<float4*>(srow + 4) = make_float4(St[4], St[5], St[6], St[7]);
+                        const float gmean = ds_block_sum(oct == 0 ? y : 0.f, S->red_c, wwarp, lane) / 64.0f;
                         const float d = y - gmean;
-                        const float var = ds_block_sum(quad == 0 ? d * d : 0.f, S->red_c + 8, wwarp, lane) / 64.0f + kGnEps;
-                        if (quad == 0) P.yg[ch] = (d * (1.0f / sqrtf(var)) * p_gw + p_gb + srk * vv0) * dg;
+                        const float var = ds_block_sum(oct == 0 ? d * d : 0.f, S->red_c + 16, wwarp, lane) / 64.0f + kGnEps;
+                        if (oct == 0) P.yg[ch] = (d * (1.0f / sqrtf(var)) * p_gw + p_gb + srk * vv_row) * S->hv[8 * 64 + rrow];
                     }
                 }
                 DS_STAMP(3);
@@ -948,50 +970,48 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 {
                     stage_scales(&Ly.e[DSE_WO], 1);
                     if (!(ok = bar_wait())) break;
-                    if (wtid < nown) tm_l[r0o + wtid] = vec[3 * C + r0o + wtid];  // new time-mix shift state (every reader of the old one is past barrier 1)
-                    float4 yv[1][NG];
+                    DS_STAMP(12);
+                    if (wtid < nown) tm_l[r0o + wtid] = S->ts_own[wtid];  // new time-mix shift state (every reader of the old one is past barrier 1)
+                    float4 yv[NG];
 #pragma unroll
                     for (int gi = 0; gi < NG; ++gi) {
                         const int g4 = wtid + kDsConsumers * gi, k = g4 < C / 4 ? 4 * g4 : 0;
-                        yv[0][gi] = ds_ldcg4(P.yg + k);
+                        yv[gi] = ds_ldcg4(P.yg + k);
                     }
                     const bool i8[1] = {Ly.e[DSE_WO].is_i8 != 0};
-                    ds_emit<1, NG>(S, vec, C, i8, yv, wtid);
+                    ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return yv[gi]; }, wtid);
                     DS_STAMP(4);
-                    if (!(ok = run_entries(&Ly.e[DSE_WO], 1))) break;
+                    if (!(ok = ds_run_entries(P, S, cs, &Ly.e[DSE_WO], 1, pc, cta, G, wwarp, lane))) break;
                 }
                 DS_STAMP(5);
                 bar_arrive();
 
                 // ================= phase 4: LN2 + shift -> relu(ffn.key)^2 =================
                 {
-                    float4 lw[NG], lb[NG], pv[NG], mx[NG], xv[NG];
-#pragma unroll
-                    for (int gi = 0; gi < NG; ++gi) {
-                        const int g4 = wtid + kDsConsumers * gi, k = g4 < C / 4 ? 4 * g4 : 0;
-                        lw[gi] = ds_ldg4(Ly.ln2_w + k);
-                        lb[gi] = ds_ldg4(Ly.ln2_b + k);
-                        mx[gi] = ds_ldg4(Ly.ffn_x_k + k);
-                        pv[gi] = ds_ldcg4(cm_l + k);
-                    }
                     stage_scales(&Ly.e[DSE_WFK], 1);
                     const int lnext = l + 1 < P.L ? l + 1 : 0;
                     stage_layer(lnext, lt + 1);  // the table of the layer that runs next (the first one again after the last)
                     if (!(ok = bar_wait())) break;
+                    DS_STAMP(13);
+                    float4 lw[NG], lb[NG], pv[NG], mx[NG], xv[NG];
 #pragma unroll
                     for (int gi = 0; gi < NG; ++gi) {
                         const int g4 = wtid + kDsConsumers * gi, k = g4 < C / 4 ? 4 * g4 : 0;
                         xv[gi] = ds_ldcg4(P.x + k);
+                        pv[gi] = ds_ldcg4(cm_l + k);
+                        lw[gi] = ds_ldg4(Ly.ln2_w + k);
+                        lb[gi] = ds_ldg4(Ly.ln2_b + k);
+                        mx[gi] = ds_ldg4(Ly.ffn_x_k + k);
                     }
                     float mean, inv;
-                    ds_ln_stats<C, NG>(S, xv, wtid, mean, inv);
-                    float4 val[1][NG];
+                    ds_ln_stats<NG>(S, C, xv, wtid, mean, inv);
+                    float4 val[NG];
 #pragma unroll
                     for (int gi = 0; gi < NG; ++gi) {
                         const int g4 = wtid + kDsConsumers * gi;
                         const float4 cur = ds_ln_apply(xv[gi], mean, inv, lw[gi], lb[gi]);
                         const float4 del = make_float4(pv[gi].x - cur.x, pv[gi].y - cur.y, pv[gi].z - cur.z, pv[gi].w - cur.w);
-                        val[0][gi] = ds_mix4(cur, mx[gi], del);
+                        val[gi] = ds_mix4(cur, mx[gi], del);
                         if (g4 < C / 4) {
                             const float ce[4] = {cur.x, cur.y, cur.z, cur.w};
 #pragma unroll
@@ -1002,29 +1022,29 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         }
                     }
                     const bool i8[1] = {Ly.e[DSE_WFK].is_i8 != 0};
-                    ds_emit<1, NG>(S, vec, C, i8, val, wtid);
+                    ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return val[gi]; }, wtid);
                     DS_STAMP(6);
-                    if (!(ok = run_entries(&Ly.e[DSE_WFK], 1))) break;
+                    if (!(ok = ds_run_entries(P, S, cs, &Ly.e[DSE_WFK], 1, pc, cta, G, wwarp, lane))) break;
                 }
                 DS_STAMP(7);
                 bar_arrive();
 
                 // ================= phase 5: ffn.value (K = F = 4 C), x += =================
                 {
-                    constexpr int NG5 = (C + kDsConsumers - 1) / kDsConsumers;  // groups of four of the F = 4 C hidden values per thread
                     stage_scales(&Ly.e[DSE_WFV], 1);
                     if (!(ok = bar_wait())) break;
+                    DS_STAMP(14);
                     if (wtid < nown) cm_l[r0o + wtid] = S->cs_own[wtid];
-                    float4 hv4[1][NG5];
+                    float4 hv4[NG5];
 #pragma unroll
                     for (int gi = 0; gi < NG5; ++gi) {
                         const int g4 = wtid + kDsConsumers * gi, k = g4 < C ? 4 * g4 : 0;
-                        hv4[0][gi] = ds_ldcg4(P.hbuf + k);
+                        hv4[gi] = ds_ldcg4(P.hbuf + k);
                     }
                     const bool i8[1] = {Ly.e[DSE_WFV].is_i8 != 0};
-                    ds_emit<1, NG5>(S, vec, 4 * C, i8, hv4, wtid);
+                    ds_emit<1, NG5>(S, vec, 4 * C, i8, [&](int, int gi) { return hv4[gi]; }, wtid);
                     DS_STAMP(8);
-                    if (!(ok = run_entries(&Ly.e[DSE_WFV], 1))) break;
+                    if (!(ok = ds_run_entries(P, S, cs, &Ly.e[DSE_WFV], 1, pc, cta, G, wwarp, lane))) break;
                 }
                 DS_STAMP(9);
                 bar_arrive();
@@ -1033,30 +1053,26 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 
             // ================= ln_out + head -> logits, arg-max =================
             if (do_head) {
+                stage_scales(&P.head, 1);
+                if (!(ok = bar_wait())) break;
                 float4 lw[NG], lb[NG], xv[NG];
 #pragma unroll
                 for (int gi = 0; gi < NG; ++gi) {
                     const int g4 = wtid + kDsConsumers * gi, k = g4 < C / 4 ? 4 * g4 : 0;
+                    xv[gi] = ds_ldcg4(P.x + k);
                     lw[gi] = ds_ldg4(P.lno_w + k);
                     lb[gi] = ds_ldg4(P.lno_b + k);
                 }
-                stage_scales(&P.head, 1);
-                if (!(ok = bar_wait())) break;
-#pragma unroll
-                for (int gi = 0; gi < NG; ++gi) {
-                    const int g4 = wtid + kDsConsumers * gi, k = g4 < C / 4 ? 4 * g4 : 0;
-                    xv[gi] = ds_ldcg4(P.x + k);
-                }
                 float mean, inv;
-                ds_ln_stats<C, NG>(S, xv, wtid, mean, inv);
-                float4 val[1][NG];
+                ds_ln_stats<NG>(S, C, xv, wtid, mean, inv);
+                float4 val[NG];
 #pragma unroll
-                for (int gi = 0; gi < NG; ++gi) val[0][gi] = ds_ln_apply(xv[gi], mean, inv, lw[gi], lb[gi]);
+                for (int gi = 0; gi < NG; ++gi) val[gi] = ds_ln_apply(xv[gi], mean, inv, lw[gi], lb[gi]);
                 const bool i8[1] = {P.head.is_i8 != 0};
-                ds_emit<1, NG>(S, vec, C, i8, val, wtid);
+                ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return val[gi]; }, wtid);
                 pc.best_val = -1e30f;
                 pc.best_idx = 0x7fffffff;
-                if (!(ok = run_entries(&P.head, 1))) break;
+                if (!(ok = ds_run_entries(P, S, cs, &P.head, 1, pc, cta, G, wwarp, lane))) break;
                 if (P.argmax_feed) {
                     // arg-max: lanes -> warp -> CTA -> grid; ties go to the smaller index
                     float bv = pc.best_val;

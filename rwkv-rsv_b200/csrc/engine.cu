@@ -1371,71 +1371,50 @@ void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bo
 // ------------------------------------------------------------------------------------------------
 namespace {
 
-DsEntry make_entry(const LinearW& W, int C, int xvec, int out, int out_off, const float* mix) {
+DsEntry make_entry(const LinearW& W, int G, int xvec, int out, int out_off, const float* mix) {
     DsEntry e;
     memset(&e, 0, sizeof(e));
     const bool i8 = W.wtype == W_INT8;
+    const int row_bytes = i8 ? W.K : 2 * W.K;
+    // pieces of at most kDsMaxPiece bytes, each a multiple of 128 bytes
+    int np = (row_bytes + kDsMaxPiece - 1) / kDsMaxPiece;
+    while (np <= row_bytes / 128 && row_bytes % (np * 128)) ++np;
     e.base = (const char*)W.w;
     e.wscale = W.wscale;
     e.wzero = W.wzero;
     e.mix = mix;
     e.M = W.M;
-    e.row_bytes = i8 ? C : 2 * C;
-    e.row_stride = i8 ? W.K : 2 * W.K;
-    e.npieces = W.K / C;
+    e.row_stride = row_bytes;
+    e.piece_bytes = row_bytes / np;
+    e.npieces = np;
     e.is_i8 = i8 ? 1 : 0;
     e.xvec = xvec;
     e.out = out;
     e.out_off = out_off;
+    e.cta0 = 0;
+    e.ncta = G;
     return e;
 }
-int entry_rows(const DsEntry& e, int cta, int G) {
-    if (e.M <= 0) return 0;
-    const int vc = (cta + e.rot) % G;
-    return (int)(((long long)(vc + 1) * e.M) / G) - (int)(((long long)vc * e.M) / G);
-}
-// Rotations of the row split of the phase-1 matrices: chosen one matrix after the other so that the largest number of bytes
-// any CTA streams in the phase stays smallest (the CTAs that get an extra row of one matrix are not those of the next).
-void balance_rotations(DsEntry* ents, int cnt, int G) {
-    std::vector<long long> load((size_t)G, 0);
-    for (int i = 0; i < cnt; ++i) {
-        DsEntry& e = ents[i];
-        if (e.M <= 0) continue;
-        int best_rot = 0;
-        long long best = -1;
-        for (int rot = 0; rot < G; ++rot) {
-            e.rot = rot;
-            long long mx = 0;
-            for (int c = 0; c < G; ++c) mx = std::max(mx, load[c] + (long long)entry_rows(e, c, G) * e.row_bytes * e.npieces);
-            if (best < 0 || mx < best) {
-                best = mx;
-                best_rot = rot;
-            }
-        }
-        e.rot = best_rot;
-        for (int c = 0; c < G; ++c) load[c] += (long long)entry_rows(e, c, G) * e.row_bytes * e.npieces;
-    }
-}
 
-template <int KL>
+template <int CMAX>
 void launch_stream(const DsParams& P, int grid, size_t smem, cudaStream_t stream, bool configure_only) {
     if (configure_only) {
-        RSV_CUDA(cudaFuncSetAttribute(decode_stream_kernel<KL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        RSV_CUDA(cudaFuncSetAttribute(decode_stream_kernel<CMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         int per_sm = 0;
-        RSV_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stream_kernel<KL>, kDsThreads, smem));
+        RSV_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stream_kernel<CMAX>, kDsThreads, smem));
         if (per_sm < 1) throw std::runtime_error("weight-streaming decode kernel does not fit on an SM");
         return;
     }
     void* args[] = {(void*)&P};
-    RSV_CUDA(cudaLaunchCooperativeKernel((const void*)decode_stream_kernel<KL>, dim3(grid), dim3(kDsThreads), args, smem, stream));
+    RSV_CUDA(cudaLaunchCooperativeKernel((const void*)decode_stream_kernel<CMAX>, dim3(grid), dim3(kDsThreads), args, smem, stream));
 }
-void dispatch_stream(int kl, const DsParams& P, int grid, size_t smem, cudaStream_t stream, bool configure_only) {
-    switch (kl) {
-        case 16: return launch_stream<16>(P, grid, smem, stream, configure_only);
-        case 32: return launch_stream<32>(P, grid, smem, stream, configure_only);
-        case 64: return launch_stream<64>(P, grid, smem, stream, configure_only);
-        case 80: return launch_stream<80>(P, grid, smem, stream, configure_only);
-        case 128: return launch_stream<128>(P, grid, smem, stream, configure_only);
+void dispatch_stream(int cmax, const DsParams& P, int grid, size_t smem, cudaStream_t stream, bool configure_only) {
+    switch (cmax) {
+        case 512: return launch_stream<512>(P, grid, smem, stream, configure_only);
+        case 1024: return launch_stream<1024>(P, grid, smem, stream, configure_only);
+        case 2048: return launch_stream<2048>(P, grid, smem, stream, configure_only);
+        case 2560: return launch_stream<2560>(P, grid, smem, stream, configure_only);
+        case 4096: return launch_stream<4096>(P, grid, smem, stream, configure_only);
         default: throw std::runtime_error("weight-streaming decode kernel: unsupported n_embd");
     }
 }
@@ -1450,6 +1429,8 @@ bool Model::stream_available() {
     auto fail = [&](const std::string& why) {
         sc.why = why;
         sc.ok = false;
+        if (const char* e = getenv("RSV_VERBOSE"))
+            if (*e && *e != '0') fprintf(stderr, "[rsv] weight-streaming decode kernel not used: %s\n", why.c_str());
         return false;
     };
     RSV_CUDA(cudaSetDevice(device));
@@ -1457,8 +1438,10 @@ bool Model::stream_available() {
     RSV_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));
     if (!coop) return fail("device does not support cooperative launches");
     const int L = cfg.n_layer, C = cfg.n_embd, F = cfg.ffn_hidden, V = cfg.vocab, H = cfg.n_head, G = num_sms;
-    const int kl = C / 32;
-    if (C % 512 || !(kl == 16 || kl == 32 || kl == 64 || kl == 80 || kl == 128)) return fail("n_embd is not one of 512, 1024, 2048, 2560, 4096");
+    int cmax = 0;
+    for (int c : {512, 1024, 2048, 2560, 4096})
+        if (!cmax && C <= c) cmax = c;
+    if (C % 128 || !cmax) return fail("n_embd must be a multiple of 128 and at most 4096");
     if (F != 4 * C) return fail("ffn_hidden is not 4 n_embd");
     if (H > G) return fail("more heads than SMs");
     if (cfg.w_mid % 8 || cfg.a_mid % 8 || cfg.v_mid % 8 || cfg.g_mid % 8) return fail("rank dimensions must be multiples of 8");
@@ -1471,14 +1454,14 @@ bool Model::stream_available() {
     if (3 * (C / G + 1) > kDsMaxRows || F / G + 1 > kDsMaxRows || V / G + 1 > kDsMaxRows) return fail("too many rows per SM");
     // shared memory: ring + operand area + fixed part + rank-space vector
     const size_t budget = 227 * 1024;
-    const int vec_floats = std::max(5 * C, F);
+    const int vec_floats = std::max(4 * C, F);
     const size_t fixed = (size_t)vec_floats * 4 + sizeof(DsShared) + (size_t)cfg.mids() * 4 + 256;
     if (fixed + 64 * 1024 > budget) return fail("operand area does not fit in shared memory");
     const int ring_bytes = (int)((budget - fixed) / 128 * 128);
     int max_chunk = std::max(64 * (cfg.w_mid + cfg.a_mid) * 2, 64 * cfg.v_mid * 2 + 32 * cfg.g_mid * 2);
-    for (int rb : {C, 2 * C}) max_chunk = std::max(max_chunk, ds_rows_per_chunk(rb) * rb);
+    max_chunk = std::max(max_chunk, kDsTileRows * (kDsMaxPiece + kDsPad));
     if (2 * max_chunk > ring_bytes) return fail("a chunk of rows does not fit twice in the shared-memory ring");
-    sc.kl = kl;
+    sc.kl = cmax;
     sc.grid = G;
     sc.ring_bytes = ring_bytes;
     sc.vec_floats = vec_floats;
@@ -1486,7 +1469,7 @@ bool Model::stream_available() {
     DsParams P;
     memset(&P, 0, sizeof(P));
     try {
-        dispatch_stream(kl, P, G, sc.smem, stream, true);
+        dispatch_stream(cmax, P, G, sc.smem, stream, true);
     } catch (const std::exception& e) {
         return fail(e.what());
     }
@@ -1496,18 +1479,42 @@ bool Model::stream_available() {
         const LayerW& Lw = layers[l];
         DsLayer& d = dl[l];
         memset(&d, 0, sizeof(d));
-        d.e[DSE_W1] = make_entry(Lw.w1, C, 0, DSO_MID_TANH, 0, Lw.x_w);
-        d.e[DSE_A1] = make_entry(Lw.a1, C, 0, DSO_MID, cfg.w_mid, Lw.x_a);
-        d.e[DSE_G1] = make_entry(Lw.g1, C, 0, DSO_MID_SIG, cfg.w_mid + cfg.a_mid + cfg.v_mid, Lw.x_g);
-        d.e[DSE_V1] = make_entry(Lw.v1, C, 0, DSO_MID, cfg.w_mid + cfg.a_mid, Lw.x_v);
+        d.e[DSE_W1] = make_entry(Lw.w1, G, 3, DSO_MID_TANH, 0, Lw.x_w);
+        d.e[DSE_A1] = make_entry(Lw.a1, G, 3, DSO_MID, cfg.w_mid, Lw.x_a);
+        d.e[DSE_G1] = make_entry(Lw.g1, G, 3, DSO_MID_SIG, cfg.w_mid + cfg.a_mid + cfg.v_mid, Lw.x_g);
+        d.e[DSE_V1] = make_entry(Lw.v1, G, 3, DSO_MID, cfg.w_mid + cfg.a_mid, Lw.x_v);
+        // The rows of the four rank projections go to disjoint groups of CTAs, sized by their row counts, so that a CTA builds the
+        // shifted input of one of them only.
+        {
+            const int order[4] = {DSE_W1, DSE_A1, DSE_V1, DSE_G1};
+            const int rows_of_e[4] = {cfg.w_mid, cfg.a_mid, cfg.v_mid, cfg.g_mid};
+            int c0 = 0, rows_left = cfg.mids(), ctas_left = G;
+            for (int i = 0; i < 4; ++i) {
+                DsEntry& e = d.e[order[i]];
+                int nc = i == 3 ? ctas_left : std::max(1, (int)((long long)ctas_left * rows_of_e[i] / std::max(rows_left, 1)));
+                nc = std::max(1, std::min(nc, ctas_left - (3 - i)));
+                e.cta0 = c0;
+                e.ncta = nc;
+                c0 += nc;
+                ctas_left -= nc;
+                rows_left -= rows_of_e[i];
+            }
+        }
         if (l == 0) d.e[DSE_V1].M = 0;  // layer 0 has no v gate
-        d.e[DSE_WR] = make_entry(Lw.Wr, C, 0, DSO_R, 0, nullptr);
-        d.e[DSE_WK] = make_entry(Lw.Wk, C, 1, DSO_K, 0, nullptr);
-        d.e[DSE_WV] = make_entry(Lw.Wv, C, 2, DSO_V, 0, nullptr);
-        d.e[DSE_WO] = make_entry(Lw.Wo, C, 0, DSO_XADD, 0, nullptr);
-        d.e[DSE_WFK] = make_entry(Lw.Wfk, C, 0, DSO_H, 0, nullptr);
-        d.e[DSE_WFV] = make_entry(Lw.Wfv, C, 0, DSO_XADD, 0, nullptr);
-        balance_rotations(&d.e[DSE_W1], 7, G);  // att.output and ffn.value keep rotation 0: their rows are the CTA's slice of x
+        for (const DsEntry* e : {&d.e[DSE_W1], &d.e[DSE_A1], &d.e[DSE_G1], &d.e[DSE_V1]})
+            if (e->is_i8 || e->npieces * e->piece_bytes != 2 * C) return fail("rank projections must be fp16 [mid, n_embd]");
+        d.e[DSE_WR] = make_entry(Lw.Wr, G, 0, DSO_R, 0, nullptr);
+        d.e[DSE_WK] = make_entry(Lw.Wk, G, 1, DSO_K, 0, nullptr);
+        d.e[DSE_WV] = make_entry(Lw.Wv, G, 2, DSO_V, 0, nullptr);
+        d.e[DSE_WO] = make_entry(Lw.Wo, G, 0, DSO_XADD, 0, nullptr);
+        d.e[DSE_WFK] = make_entry(Lw.Wfk, G, 0, DSO_H, 0, nullptr);
+        d.e[DSE_WFV] = make_entry(Lw.Wfv, G, 0, DSO_XADD, 0, nullptr);
+        // r, k, v: the CTAs that get an extra row of one matrix are not those of the next (att.output and ffn.value keep
+        // offset 0: their rows are the CTA's slice of x)
+        d.e[DSE_WK].cta0 = G / 3;
+        d.e[DSE_WV].cta0 = 2 * G / 3;
+        for (int i = 0; i < DSE_COUNT; ++i)
+            if (d.e[i].piece_bytes % 128 || d.e[i].piece_bytes > kDsMaxPiece) return fail("a weight row does not split into pieces of a multiple of 128 bytes");
         d.w2 = (const __half*)Lw.w2.w;
         d.a2 = (const __half*)Lw.a2.w;
         d.v2 = (const __half*)Lw.v2.w;
@@ -1547,7 +1554,8 @@ bool Model::stream_available() {
     RSV_CUDA(cudaMemset(sc.dbg, 0, 64 * sizeof(long long)));
 #endif
     P.layers = (const DsLayer*)sc.d_layers;
-    P.head = make_entry(head, C, 0, DSO_LOGITS, 0, nullptr);
+    P.head = make_entry(head, G, 0, DSO_LOGITS, 0, nullptr);
+    if (P.head.piece_bytes % 128 || P.head.piece_bytes > kDsMaxPiece) return fail("a head row does not split into pieces of a multiple of 128 bytes");
     P.emb = emb;
     P.ln0_w = ln0_w;
     P.ln0_b = ln0_b;
@@ -1612,9 +1620,11 @@ void Model::run_stream(State& st, int slot, int n_tokens, bool tok_from_list, bo
         long long h[64];
         RSV_CUDA(cudaStreamSynchronize(stream));
         RSV_CUDA(cudaMemcpy(h, sc.dbg, sizeof(h), cudaMemcpyDeviceToHost));
-        const char* names[10] = {"layer start", "P1 operands", "P1 rows done", "heads done", "P3 operands", "P3 rows done", "P4 operands", "P4 rows done", "P5 operands", "P5 rows done"};
+        const int order[15] = {0, 10, 1, 2, 11, 3, 12, 4, 5, 13, 6, 7, 14, 8, 9};
+        const char* names[15] = {"layer start", "P1 operands", "P1 rows done", "heads done", "P3 operands", "P3 rows done", "P4 operands", "P4 rows done", "P5 operands", "P5 rows done",
+                                 "barrier 5 passed", "barrier 1 passed", "barrier 2 passed", "barrier 3 passed", "barrier 4 passed"};
         fprintf(stderr, "[decode_stream_kernel, CTA 0, token 1, layer 1] us since the layer started\n");
-        for (int i = 0; i < 10; ++i) fprintf(stderr, "  %-14s %.2f\n", names[i], (h[i] - h[0]) / 1e3);
+        for (int i = 0; i < 15; ++i) fprintf(stderr, "  %-18s %.2f\n", names[order[i]], (h[order[i]] - h[0]) / 1e3);
     }
 #endif
 }
