@@ -10,22 +10,23 @@
 //   warp 0      producer.  Walks the fixed sequence of weight rows this CTA will ever need - token after token, layer
 //               after layer, phase after phase - and streams them with bulk asynchronous copies (cp.async.bulk, one
 //               per row, issued by the lanes in parallel) into a byte-granular ring in shared memory; a chunk = one
-//               tile of up to 8 rows x one piece (<= 2560 bytes) of K, one mbarrier per chunk.  It never waits on a
+//               tile of up to 16 rows x one piece (<= 1280 bytes) of K, one mbarrier per chunk.  It never waits on a
 //               grid barrier, only on ring space, so HBM keeps streaming while the other warps synchronise:
 //               barriers cost latency, not bandwidth.
 //   warps 1-16  consumers.  Per phase they build the activation vector in shared memory (LayerNorm, token shift,
-//               fixed-point digits), laid out as the A fragments of the warp-level matrix instruction.  Then every
-//               tile belongs to ONE warp, which multiplies it out of the ring (ldmatrix -> mma.sync, the reduction
-//               over K happens inside the instruction, four independent accumulator chains) and keeps the
-//               accumulators in registers across the pieces of a long row: no shuffles in the loop, no sums across
-//               warps, nothing to wait for but the tile itself.  A row in the ring is padded by 16 bytes so that
-//               the eight rows of a tile fall into different banks.
-// Arithmetic.  int8 matrices: the u8 codes q are multiplied as they are (m16n8k32, s8 x u8 -> s32) with the four
+//               fixed-point digits), laid out as the B fragments of the warp-level matrix instruction.  Then every
+//               chunk belongs to ONE warp (chunk i of a phase to warp i mod 16, so the pieces of a long row are
+//               multiplied by different warps at once), which multiplies it out of the ring (ldmatrix -> mma.sync,
+//               the reduction over K happens inside the instruction): no shuffles in the loop, nothing to wait for
+//               but the chunk itself.  The warp that finishes a tile's last piece adds the pieces' partial sums in
+//               piece order and stores the outputs.  A row in the ring is padded by 16 bytes so that the rows of a
+//               tile fall into different banks.
+// Arithmetic.  int8 matrices: the u8 codes q are multiplied as they are (m16n8k32, u8 x s8 -> s32) with the four
 // signed base-256 digits of the fixed-point activation t = rint(x / e 2^30), e = 2^ceil(log2 max|x|) (the digits are
 // the bytes of (t + 0x808080) ^ 0x808080); the four int32 sums recombine to Q = sum_k q_k t_k exactly (int64), and
 // with the container's per-row (scale s, zero z)  y = e 2^-30 (s Q + z T), T = sum_k t_k: no accumulation rounding,
 // no dependence on the schedule.  fp16 matrices (head, rank projections, fp16 checkpoints): m16n8k16 f16 x f16 ->
-// f32 with x / e split into hi + lo halves (two operand rows).  These are 8-column problems that stream weights at
+// f32 with x / e split into hi + lo halves (two operand columns).  These are 8-column problems that stream weights at
 // HBM speed; the tensor pipe is nearly idle, which is why the warp-level instruction is the right size here and the
 // tcgen05 kernels take over once several rows make the product a dense contraction.
 // Phases per layer, one grid barrier after each (bounded spin):
@@ -44,9 +45,11 @@ constexpr int kDsConsumerWarps = 16;
 constexpr int kDsConsumers = kDsConsumerWarps * 32;  // 512
 constexpr int kDsThreads = kDsConsumers + 32;        // + producer warp
 constexpr int kDsBars = 16;                          // chunks in flight (mbarrier pairs)
-constexpr int kDsTileRows = 8;                       // rows of a tile (the n dimension of the matrix instruction)
+constexpr int kDsTileRows = 16;                      // rows of a tile (the m dimension of the matrix instruction)
 constexpr int kDsPad = 16;                           // bytes between the rows of a tile in the ring, beyond the piece
-constexpr int kDsMaxPiece = 2560;                    // bytes of K per piece
+constexpr int kDsMaxPiece = 1280;                    // bytes of K per piece
+constexpr int kDsMaxTiles = 64;                      // tiles of one phase per CTA
+constexpr int kDsPartBytes = 8 * 1024;               // per-piece partial sums of the tiles of one phase
 constexpr int kDsMaxRows = 512;                      // rows of one phase per CTA whose (scale, zero) are staged
 constexpr int kDsMaxSlice = 32;                      // channels of the residual stream per CTA
 constexpr int kDsP = 30;                             // fixed-point bits of the activation digits
@@ -122,17 +125,17 @@ __device__ __forceinline__ uint4 ds_ldmatrix4(uint32_t saddr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
     return v;
 }
-// D += A (16 x 32 s8, row-major: the activation digits) x B (32 x 8 u8, column-major: eight weight rows)
-__device__ __forceinline__ void ds_mma_i8(int (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+// D += A (16 x 32 u8, row-major: sixteen weight rows) x B (32 x 8 s8, column-major: the activation digits, one per column)
+__device__ __forceinline__ void ds_mma_i8(int (&c)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
 }
-// D += A (16 x 16 f16) x B (16 x 8 f16), fp32 accumulation
-__device__ __forceinline__ void ds_mma_f16(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+// D += A (16 x 16 f16: sixteen weight rows) x B (16 x 8 f16: hi and lo halves of the activations), fp32 accumulation
+__device__ __forceinline__ void ds_mma_f16(float (&c)[4], const uint4& a, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ uint64_t ds_evict_first_policy() {
     uint64_t p;
@@ -207,10 +210,12 @@ struct DsShared {
     float cs_own[kDsMaxSlice];  // pending channel-mix shift state of the slice
     float ws[kDsMaxRows], wz[kDsMaxRows];  // (scale, zero) of the rows this CTA owns in the current phase
     float hv[10 * 64];                     // the 64-vectors of a head
+    int tile_cnt[kDsMaxTiles];             // pieces of a tile finished so far (zero between phases)
+    long long part[kDsPartBytes / 8];      // per-piece partial sums: int64 (int8 matrices) or fp32 (fp16 matrices), 16 rows each
     DsLayer layer[2];                      // table of the current / next layer
 };
 
-// Operand area.  Vector v of a phase (`len` elements) occupies 4 len bytes at byte offset 4 v len, stored as the A fragments
+// Operand area.  Vector v of a phase (`len` elements) occupies 4 len bytes at byte offset 4 v len, stored as the B fragments
 // the consumer lanes load with one 16-byte read per two k steps:
 //   int8 matrices (k step = 32 elements): index [k / 64][digit 0..3][t = (k % 16) / 4][word (k % 64) / 16], the word holding
 //     the digit of the four consecutive k in its bytes; lane (g, t) of a warp reads the 16 bytes at ((k/64) 4 + g) 4 + t.
@@ -309,7 +314,6 @@ struct DsCons {
     int R, head;
     int cur;        // byte offset of the chunk the last advance returned
     uint32_t j;     // chunks placed so far
-    int tile_base;  // tiles of the phase so far: tile i belongs to consumer warp i mod 16
 };
 // Places the next chunk (same rule as the producer); its offset goes to cs.cur, its barrier index is returned.
 __device__ __forceinline__ uint32_t ds_chunk_next(DsCons& cs, int bytes) {
@@ -328,7 +332,17 @@ struct DsPhaseCtx {
     uint32_t vec_s;  // shared-memory address of the operand area
     float best_val;  // running arg-max of the head rows this lane finished
     int best_idx;
+#ifdef RSV_DS_DEBUG
+    long long* dbg;  // non-null: this call adds warp 0's time waiting for chunks to dbg[0] and its time multiplying to dbg[1]
+#endif
 };
+#ifdef RSV_DS_DEBUG
+__device__ __forceinline__ long long ds_now() {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#endif
 
 __device__ __forceinline__ void ds_store(const DsParams& P, DsShared* S, const DsEntry& E, int m, int rl, float y, DsPhaseCtx& pc) {
     switch (E.out) {
@@ -359,15 +373,15 @@ __device__ __forceinline__ void ds_store(const DsParams& P, DsShared* S, const D
     }
 }
 
-// The matrices of one phase.  Chunk order (the producer issues the same): matrix after matrix; inside a matrix groups of 16
-// tiles; inside a group piece after piece; inside a piece the tiles of the group.  Tile i of the phase belongs to consumer
-// warp i mod 16, so a warp owns at most one tile of a group and keeps its accumulators in registers across the pieces.
-// Returns false after a timeout.
+// The matrices of one phase.  Work items (the producer issues their chunks in the same order): matrix after matrix, tile
+// after tile (16 rows), piece after piece (<= 1280 bytes of K); item i of the phase belongs to consumer warp i mod 16, so the
+// pieces of a long row are multiplied by different warps at the same time.  A warp leaves the partial sums of its piece in
+// shared memory and counts its arrival on the tile; the warp that arrives last adds the pieces in piece order (exact for
+// int8, fixed order for fp16) and stores the outputs.  Returns false after a timeout.
 __device__ __noinline__ bool ds_run_entries(const DsParams& P, DsShared* S, DsCons& cs, const DsEntry* ents, int cnt, DsPhaseCtx& pc, int cta, int G, int wwarp,
                                             int lane) {
     const int g = lane >> 2, t = lane & 3;
-    int stage_off = 0;
-    cs.tile_base = 0;
+    int stage_off = 0, item = 0, tile_idx = 0, part_off = 0;  // part_off: bytes of partial sums of the tiles before this one
     for (int ei = 0; ei < cnt; ++ei) {
         const DsEntry& E = ents[ei];
         int r0, n;
@@ -375,125 +389,111 @@ __device__ __noinline__ bool ds_run_entries(const DsParams& P, DsShared* S, DsCo
         if (n <= 0) continue;
         const bool i8 = E.is_i8 != 0;
         const int ntiles = (n + kDsTileRows - 1) / kDsTileRows, cb = ds_chunk_bytes(E), stride = E.piece_bytes + kDsPad, steps = E.piece_bytes >> 6;
-        const int klen = (i8 ? E.piece_bytes : (E.piece_bytes >> 1)) * E.npieces;  // elements of the operand vector
-        // A fragments of this lane: 16 bytes per two k steps at [k-step pair][row g][t]; rows beyond the operand's are zero
-        const int arows = i8 ? 4 : 2, astep = arows * 64;
-        const uint32_t abase = pc.vec_s + (uint32_t)E.xvec * (uint32_t)klen * 4u + (uint32_t)(g * 4 + t) * 16u;
-        const bool arow_ok = g < arows;
-        float xs = 0.f;
-        long long T = 0;
-        if (i8) {
-            xs = ds_pow2(S->ex[E.xvec] - kDsP);
-#pragma unroll
-            for (int w = 0; w < kDsConsumerWarps; ++w) T += S->tsw[E.xvec][w];
-        } else {
-            xs = ds_pow2(S->ex[E.xvec]);
-        }
-        for (int g0 = 0; g0 < ntiles; g0 += kDsConsumerWarps) {
-            const int gsz = min(kDsConsumerWarps, ntiles - g0);
-            const int my = (wwarp - cs.tile_base - g0) & (kDsConsumerWarps - 1);
-            const bool mine = my < gsz;
-            const int row0 = (g0 + my) * kDsTileRows, nr = mine ? min(kDsTileRows, n - row0) : 0;
-            int ci[4][4];
-            float cf[4][4];
-#pragma unroll
-            for (int a = 0; a < 4; ++a)
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    ci[a][b] = 0;
-                    cf[a][b] = 0.f;
-                }
-            for (int p = 0; p < E.npieces; ++p) {
-                for (int q = 0; q < (mine ? my : gsz); ++q) ds_chunk_next(cs, cb);
-                if (mine) {
-                    const uint32_t idx = ds_chunk_next(cs, cb);
-                    if (!ds_chunk_wait(S, idx)) return false;
-                    // ldmatrix row addresses: lane l -> row l % 8 (clamped to the tile's last row), 16-byte column l / 8 of each 64-byte step pair
-                    uint32_t baddr = cs.ring_s + (uint32_t)cs.cur + (uint32_t)min(lane & 7, nr - 1) * (uint32_t)stride + (uint32_t)(lane >> 3) * 16u;
-                    uint32_t aaddr = abase + (uint32_t)p * (uint32_t)steps * (uint32_t)astep;
-                    if (i8) {
-#pragma unroll 2
-                        for (int s = 0; s < steps; s += 2) {
-                            const uint4 b0 = ds_ldmatrix4(baddr), b1 = ds_ldmatrix4(baddr + 64);
-                            uint4 a0 = make_uint4(0, 0, 0, 0), a1 = make_uint4(0, 0, 0, 0);
-                            if (arow_ok) {
-                                a0 = ds_lds128(aaddr);
-                                a1 = ds_lds128(aaddr + astep);
-                            }
-                            ds_mma_i8(ci[0], a0.x, a0.y, b0.x, b0.y);
-                            ds_mma_i8(ci[1], a0.z, a0.w, b0.z, b0.w);
-                            ds_mma_i8(ci[2], a1.x, a1.y, b1.x, b1.y);
-                            ds_mma_i8(ci[3], a1.z, a1.w, b1.z, b1.w);
-                            baddr += 128;
-                            aaddr += 2 * astep;
-                        }
-                    } else {
-#pragma unroll 2
-                        for (int s = 0; s < steps; s += 2) {
-                            const uint4 b0 = ds_ldmatrix4(baddr), b1 = ds_ldmatrix4(baddr + 64);
-                            uint4 a0 = make_uint4(0, 0, 0, 0), a1 = make_uint4(0, 0, 0, 0);
-                            if (arow_ok) {
-                                a0 = ds_lds128(aaddr);
-                                a1 = ds_lds128(aaddr + astep);
-                            }
-                            ds_mma_f16(cf[0], a0.x, a0.y, b0.x, b0.y);
-                            ds_mma_f16(cf[1], a0.z, a0.w, b0.z, b0.w);
-                            ds_mma_f16(cf[2], a1.x, a1.y, b1.x, b1.y);
-                            ds_mma_f16(cf[3], a1.z, a1.w, b1.z, b1.w);
-                            baddr += 128;
-                            aaddr += 2 * astep;
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&S->empty[idx % kDsBars]);
-                    for (int q = my + 1; q < gsz; ++q) ds_chunk_next(cs, cb);
-                }
-            }
-            if (mine) {
-                // accumulator (row g, columns 2 t, 2 t + 1) = operand row g x weight rows 2 t, 2 t + 1 of the tile
+        const int np = E.npieces, klen = (i8 ? E.piece_bytes : (E.piece_bytes >> 1)) * np;  // elements of the operand vector
+        // B fragments of this lane: 16 bytes per two k steps at [k-step pair][operand row g][t]; columns beyond the operand's rows are zero
+        const int brows = i8 ? 4 : 2, bstep = brows * 64, slot = i8 ? 8 : 4;
+        const uint32_t bbase = pc.vec_s + (uint32_t)E.xvec * (uint32_t)klen * 4u + (uint32_t)(g * 4 + t) * 16u;
+        const bool bcol_ok = g < brows;
+        for (int ti = 0; ti < ntiles; ++ti, ++tile_idx, part_off += np * kDsTileRows * slot) {
+            const int row0 = ti * kDsTileRows, nr = min(kDsTileRows, n - row0);
+            for (int p = 0; p < np; ++p, ++item) {
+                const uint32_t idx = ds_chunk_next(cs, cb);
+                if ((item & (kDsConsumerWarps - 1)) != wwarp) continue;
+#ifdef RSV_DS_DEBUG
+                const long long tw0 = ds_now();
+#endif
+                if (!ds_chunk_wait(S, idx)) return false;
+#ifdef RSV_DS_DEBUG
+                const long long tw1 = ds_now();
+#endif
+                // ldmatrix row addresses: lanes 0-7 rows 0-7, 8-15 rows 8-15 (bytes 0-15 of a 32-byte k step), lanes 16-31 the same rows, bytes 16-31
+                const int arow = min((lane & 7) + ((lane >> 3) & 1) * 8, nr - 1);
+                uint32_t aaddr = cs.ring_s + (uint32_t)cs.cur + (uint32_t)arow * (uint32_t)stride + (uint32_t)(lane >> 4) * 16u;
+                uint32_t baddr = bbase + (uint32_t)p * (uint32_t)steps * (uint32_t)bstep;
+                char* part = reinterpret_cast<char*>(S->part) + part_off + p * kDsTileRows * slot;
                 if (i8) {
-                    const int q0 = (ci[0][0] + ci[1][0]) + (ci[2][0] + ci[3][0]), q1 = (ci[0][1] + ci[1][1]) + (ci[2][1] + ci[3][1]);
-                    long long v0 = arow_ok ? ((long long)q0 << (8 * g)) : 0, v1 = arow_ok ? ((long long)q1 << (8 * g)) : 0;  // digit g weighs 256^g
-                    v0 += __shfl_xor_sync(0xffffffffu, v0, 4);
-                    v1 += __shfl_xor_sync(0xffffffffu, v1, 4);
-                    v0 += __shfl_xor_sync(0xffffffffu, v0, 8);
-                    v1 += __shfl_xor_sync(0xffffffffu, v1, 8);
-                    if (lane < 4) {
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int rl = row0 + 2 * t + e;
-                            if (rl < n) {
-                                const double ws = S->ws[stage_off + rl], wz = S->wz[stage_off + rl];
-                                ds_store(P, S, E, r0 + rl, rl, (float)((double)xs * (ws * (double)(e ? v1 : v0) + wz * (double)T)), pc);
-                            }
-                        }
+                    int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+#pragma unroll 2
+                    for (int s2 = 0; s2 < steps; ++s2) {
+                        const uint4 a0 = ds_ldmatrix4(aaddr), a1 = ds_ldmatrix4(aaddr + 32);
+                        uint4 b = make_uint4(0, 0, 0, 0);
+                        if (bcol_ok) b = ds_lds128(baddr);
+                        ds_mma_i8(c0, a0, b.x, b.y);
+                        ds_mma_i8(c1, a1, b.z, b.w);
+                        aaddr += 64;
+                        baddr += bstep;
+                    }
+                    // accumulator (rows g, g + 8; columns 2 t, 2 t + 1) = weight rows x digits 2 t, 2 t + 1 (t < 2); digit d weighs 256^d
+                    const int lo = t < 2 ? 16 * t : 0;
+                    long long va = t < 2 ? (((long long)(c0[0] + c1[0]) << lo) + ((long long)(c0[1] + c1[1]) << (lo + 8))) : 0;
+                    long long vb = t < 2 ? (((long long)(c0[2] + c1[2]) << lo) + ((long long)(c0[3] + c1[3]) << (lo + 8))) : 0;
+                    va += __shfl_xor_sync(0xffffffffu, va, 1);
+                    vb += __shfl_xor_sync(0xffffffffu, vb, 1);
+                    if (t == 0) {
+                        reinterpret_cast<long long*>(part)[g] = va;
+                        reinterpret_cast<long long*>(part)[g + 8] = vb;
                     }
                 } else {
-                    float f0 = (cf[0][0] + cf[1][0]) + (cf[2][0] + cf[3][0]), f1 = (cf[0][1] + cf[1][1]) + (cf[2][1] + cf[3][1]);
-                    f0 += __shfl_xor_sync(0xffffffffu, f0, 4);  // hi + lo
-                    f1 += __shfl_xor_sync(0xffffffffu, f1, 4);
-                    if (lane < 4) {
+                    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+                    for (int s2 = 0; s2 < steps; ++s2) {
+                        const uint4 a0 = ds_ldmatrix4(aaddr), a1 = ds_ldmatrix4(aaddr + 32);
+                        uint4 b = make_uint4(0, 0, 0, 0);
+                        if (bcol_ok) b = ds_lds128(baddr);
+                        ds_mma_f16(c0, a0, b.x, b.y);
+                        ds_mma_f16(c1, a1, b.z, b.w);
+                        aaddr += 64;
+                        baddr += bstep;
+                    }
+                    if (t == 0) {  // columns 0, 1 = hi, lo
+                        reinterpret_cast<float*>(part)[g] = (c0[0] + c1[0]) + (c0[1] + c1[1]);
+                        reinterpret_cast<float*>(part)[g + 8] = (c0[2] + c1[2]) + (c0[3] + c1[3]);
+                    }
+                }
+                __syncwarp();
+                int old = 0;
+                if (lane == 0) {
+                    mbar_arrive(&S->empty[idx % kDsBars]);
+                    __threadfence_block();
+                    old = atomicAdd(&S->tile_cnt[tile_idx], 1);
+                }
+                old = __shfl_sync(0xffffffffu, old, 0);
+#ifdef RSV_DS_DEBUG
+                if (pc.dbg && lane == 0 && wwarp == 0) {
+                    pc.dbg[0] += tw1 - tw0;
+                    pc.dbg[1] += ds_now() - tw1;
+                    pc.dbg[2] += 1;
+                }
+#endif
+                if (old == np - 1) {
+                    // last piece of the tile: lane r adds the pieces of row r in piece order and stores the output
+                    __threadfence_block();
+                    const int rl = row0 + lane;
+                    if (lane < nr) {
+                        const char* pt = reinterpret_cast<const char*>(S->part) + part_off;
+                        if (i8) {
+                            long long Q = 0, T = 0;
+                            for (int q = 0; q < np; ++q) Q += reinterpret_cast<const volatile long long*>(pt + q * kDsTileRows * 8)[lane];
 #pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int rl = row0 + 2 * t + e;
-                            if (rl < n) ds_store(P, S, E, r0 + rl, rl, (e ? f1 : f0) * xs, pc);
+                            for (int w = 0; w < kDsConsumerWarps; ++w) T += S->tsw[E.xvec][w];
+                            const double ws = S->ws[stage_off + rl], wz = S->wz[stage_off + rl];
+                            ds_store(P, S, E, r0 + rl, rl, (float)((double)ds_pow2(S->ex[E.xvec] - kDsP) * (ws * (double)Q + wz * (double)T)), pc);
+                        } else {
+                            float y = 0.f;
+                            for (int q = 0; q < np; ++q) y += reinterpret_cast<const volatile float*>(pt + q * kDsTileRows * 4)[lane];
+                            ds_store(P, S, E, r0 + rl, rl, y * ds_pow2(S->ex[E.xvec]), pc);
                         }
                     }
+                    if (lane == 0) S->tile_cnt[tile_idx] = 0;
                 }
             }
         }
-        cs.tile_base = (cs.tile_base + ntiles) & (kDsConsumerWarps - 1);
         if (i8) stage_off += n;
     }
     return true;
 }
 
 #ifdef RSV_DS_DEBUG
-__device__ __forceinline__ long long ds_now() {
-    long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
 // time stamps of CTA 0 at phase boundaries of token 1, layer 1
 #define DS_STAMP(id)                                                                  \
     do {                                                                              \
@@ -570,6 +570,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
         S->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    for (int i = threadIdx.x; i < kDsMaxTiles; i += kDsThreads) S->tile_cnt[i] = 0;
     __syncthreads();
 
     if (warp == 0) {
@@ -606,25 +607,30 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
             ds_rows_of(E, cta, G, r0, n);
             if (n <= 0) return true;
             const int ntiles = (n + kDsTileRows - 1) / kDsTileRows, cb = ds_chunk_bytes(E), stride = E.piece_bytes + kDsPad;
-            for (int g0 = 0; g0 < ntiles; g0 += kDsConsumerWarps)
-                for (int p = 0; p < E.npieces; ++p)
-                    for (int ti = g0; ti < min(g0 + kDsConsumerWarps, ntiles); ++ti) {
-                        const int row0 = ti * kDsTileRows, nr = min(kDsTileRows, n - row0);
-                        if (!reserve(cb, nr * E.piece_bytes)) return false;
-                        if (lane < nr)
-                            ds_bulk_load(ring_s + (uint32_t)(head - cb + lane * stride),
-                                         E.base + (size_t)(r0 + row0 + lane) * (size_t)E.row_stride + (size_t)p * E.piece_bytes, (uint32_t)E.piece_bytes,
-                                         &S->full[j % kDsBars], pol);
-                        ++j;
-                    }
+            for (int ti = 0; ti < ntiles; ++ti)
+                for (int p = 0; p < E.npieces; ++p) {
+                    const int row0 = ti * kDsTileRows, nr = min(kDsTileRows, n - row0);
+                    if (!reserve(cb, nr * E.piece_bytes)) return false;
+                    if (lane < nr)
+                        ds_bulk_load(ring_s + (uint32_t)(head - cb + lane * stride),
+                                     E.base + (size_t)(r0 + row0 + lane) * (size_t)E.row_stride + (size_t)p * E.piece_bytes, (uint32_t)E.piece_bytes,
+                                     &S->full[j % kDsBars], pol);
+                    ++j;
+                }
             return true;
         };
         for (int t = 0; t < P.n_tokens && ok; ++t) {
             const bool do_head = P.argmax_feed || t == P.n_tokens - 1;
             for (int l = 0; l < P.L && ok; ++l) {
                 const DsLayer* Lg = P.layers + l;
+#ifdef RSV_DS_DEBUG
+                if (P.dbg && cta == 0 && lane == 0 && t == 1 && l == 1) P.dbg[40] = ds_now();
+#endif
                 for (int e = DSE_W1; e <= DSE_WV && ok; ++e) ok = put_entry(Lg->e[e]);
                 if (!ok) break;
+#ifdef RSV_DS_DEBUG
+                if (P.dbg && cta == 0 && lane == 0 && t == 1 && l == 1) P.dbg[41] = ds_now();
+#endif
                 const int h = ds_head_of_cta(cta, l, P.H, G);
                 if (h >= 0) {
                     // chunk A: w2, a2 rows of the head; chunk B: v2 rows (layers > 0) and the first 32 g2 rows; chunk C: the other 32
@@ -642,7 +648,15 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     if (lane == 0) ds_bulk_load(ring_s + (uint32_t)(head - hbC), Lg->g2 + ((size_t)h * 64 + 32) * P.gm, (uint32_t)hbC, &S->full[j % kDsBars], pol);
                     ++j;
                 }
-                for (int e = DSE_WO; e <= DSE_WFV && ok; ++e) ok = put_entry(Lg->e[e]);
+#ifdef RSV_DS_DEBUG
+                if (P.dbg && cta == 0 && lane == 0 && t == 1 && l == 1) P.dbg[42] = ds_now();
+#endif
+                for (int e = DSE_WO; e <= DSE_WFV && ok; ++e) {
+                    ok = put_entry(Lg->e[e]);
+#ifdef RSV_DS_DEBUG
+                    if (P.dbg && cta == 0 && lane == 0 && t == 1 && l == 1) P.dbg[43 + e - DSE_WO] = ds_now();
+#endif
+                }
             }
             if (ok && do_head) ok = put_entry(P.head);
         }
@@ -652,8 +666,11 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
     } else {
         // =========================== consumers ===========================
         const int wtid = threadIdx.x - 32, wwarp = wtid >> 5;
-        DsCons cs{smem_u32(ring), R, 0, 0, 0u, 0};
-        DsPhaseCtx pc{smem_u32(vec), -1e30f, 0x7fffffff};
+        DsCons cs{smem_u32(ring), R, 0, 0, 0u};
+        DsPhaseCtx pc{};
+        pc.vec_s = smem_u32(vec);
+        pc.best_val = -1e30f;
+        pc.best_idx = 0x7fffffff;
         unsigned bar_target = 0;
         bool ok = true, pending = false;
         const int r0o = ds_row_begin(cta, C, G), nown = ds_row_begin(cta + 1, C, G) - r0o;  // this CTA's slice of the channels
@@ -805,6 +822,9 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     ds_emit<4, NG>(S, vec, C, i8, [&](int v, int gi) { return ds_mix4(cur[gi], mx[v][gi], del[gi]); }, wtid);
                 }
                 DS_STAMP(1);
+#ifdef RSV_DS_DEBUG
+                pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 20 : nullptr;
+#endif
                 if (!(ok = ds_run_entries(P, S, cs, &Ly.e[DSE_W1], 7, pc, cta, G, wwarp, lane))) break;
                 DS_STAMP(2);
                 bar_arrive();
@@ -981,6 +1001,9 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     const bool i8[1] = {Ly.e[DSE_WO].is_i8 != 0};
                     ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return yv[gi]; }, wtid);
                     DS_STAMP(4);
+#ifdef RSV_DS_DEBUG
+                pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 24 : nullptr;
+#endif
                     if (!(ok = ds_run_entries(P, S, cs, &Ly.e[DSE_WO], 1, pc, cta, G, wwarp, lane))) break;
                 }
                 DS_STAMP(5);
@@ -1024,6 +1047,9 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     const bool i8[1] = {Ly.e[DSE_WFK].is_i8 != 0};
                     ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return val[gi]; }, wtid);
                     DS_STAMP(6);
+#ifdef RSV_DS_DEBUG
+                pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 28 : nullptr;
+#endif
                     if (!(ok = ds_run_entries(P, S, cs, &Ly.e[DSE_WFK], 1, pc, cta, G, wwarp, lane))) break;
                 }
                 DS_STAMP(7);
@@ -1044,6 +1070,9 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     const bool i8[1] = {Ly.e[DSE_WFV].is_i8 != 0};
                     ds_emit<1, NG5>(S, vec, 4 * C, i8, [&](int, int gi) { return hv4[gi]; }, wtid);
                     DS_STAMP(8);
+#ifdef RSV_DS_DEBUG
+                pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 32 : nullptr;
+#endif
                     if (!(ok = ds_run_entries(P, S, cs, &Ly.e[DSE_WFV], 1, pc, cta, G, wwarp, lane))) break;
                 }
                 DS_STAMP(9);
@@ -1072,6 +1101,9 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return val[gi]; }, wtid);
                 pc.best_val = -1e30f;
                 pc.best_idx = 0x7fffffff;
+#ifdef RSV_DS_DEBUG
+                pc.dbg = nullptr;
+#endif
                 if (!(ok = ds_run_entries(P, S, cs, &P.head, 1, pc, cta, G, wwarp, lane))) break;
                 if (P.argmax_feed) {
                     // arg-max: lanes -> warp -> CTA -> grid; ties go to the smaller index

@@ -1461,6 +1461,21 @@ bool Model::stream_available() {
     int max_chunk = std::max(64 * (cfg.w_mid + cfg.a_mid) * 2, 64 * cfg.v_mid * 2 + 32 * cfg.g_mid * 2);
     max_chunk = std::max(max_chunk, kDsTileRows * (kDsMaxPiece + kDsPad));
     if (2 * max_chunk > ring_bytes) return fail("a chunk of rows does not fit twice in the shared-memory ring");
+    {
+        // tiles and partial-sum bytes of the largest phase of any CTA (rows per CTA rounded up)
+        auto tiles_of = [&](int M, int nct) { return ((M + nct - 1) / nct + kDsTileRows - 1) / kDsTileRows + 1; };
+        auto part_of = [&](int M, int nct, int row_bytes, bool i8) {
+            int np = (row_bytes + kDsMaxPiece - 1) / kDsMaxPiece;
+            while (np <= row_bytes / 128 && row_bytes % (np * 128)) ++np;
+            return tiles_of(M, nct) * np * kDsTileRows * (i8 ? 8 : 4);
+        };
+        const bool i8b = layers[0].Wr.wtype == W_INT8, i8h = head.wtype == W_INT8;
+        const int rb = i8b ? C : 2 * C;
+        const int p1_tiles = 3 * tiles_of(C, G) + 2, p1_part = 3 * part_of(C, G, rb, i8b) + 2 * part_of(16, 1, 2 * C, false);
+        const int p4_part = part_of(F, G, rb, i8b), p5_part = part_of(C, G, i8b ? F : 2 * F, i8b), ph_part = part_of(V, G, i8h ? C : 2 * C, i8h);
+        if (std::max({p1_tiles, tiles_of(F, G), tiles_of(V, G)}) > kDsMaxTiles) return fail("too many tiles per SM");
+        if (std::max({p1_part, p4_part, p5_part, ph_part}) > kDsPartBytes) return fail("partial sums of a phase do not fit in shared memory");
+    }
     sc.kl = cmax;
     sc.grid = G;
     sc.ring_bytes = ring_bytes;
@@ -1625,6 +1640,12 @@ void Model::run_stream(State& st, int slot, int n_tokens, bool tok_from_list, bo
                                  "barrier 5 passed", "barrier 1 passed", "barrier 2 passed", "barrier 3 passed", "barrier 4 passed"};
         fprintf(stderr, "[decode_stream_kernel, CTA 0, token 1, layer 1] us since the layer started\n");
         for (int i = 0; i < 15; ++i) fprintf(stderr, "  %-18s %.2f\n", names[order[i]], (h[order[i]] - h[0]) / 1e3);
+        const char* ph[4] = {"P1", "P3", "P4", "P5"};
+        for (int i = 0; i < 4; ++i)
+            fprintf(stderr, "  %s rows, consumer warp 0: %lld chunks, %.2f us waiting for them, %.2f us multiplying\n", ph[i], h[20 + 4 * i + 2], h[20 + 4 * i] / 1e3, h[20 + 4 * i + 1] / 1e3);
+        fprintf(stderr, "  producer: P1 rows issued %.2f .. %.2f, later phases start %.2f, att.out issued %.2f, ffn.key %.2f, ffn.value %.2f\n", (h[40] - h[0]) / 1e3,
+                (h[41] - h[0]) / 1e3, (h[42] - h[0]) / 1e3, (h[43] - h[0]) / 1e3, (h[44] - h[0]) / 1e3, (h[45] - h[0]) / 1e3);
+        RSV_CUDA(cudaMemset(sc.dbg, 0, 64 * sizeof(long long)));
     }
 #endif
 }
