@@ -37,6 +37,8 @@
 // then ln_out + head -> logits, arg-max across CTAs, next token.
 // All waits are bounded; on expiry bit 2 of the status word is set, every role drains its copies in flight and exits.
 #pragma once
+#include <cstddef>
+
 #include "tc_linear.cuh"
 
 namespace rsv {
@@ -177,8 +179,8 @@ __host__ __device__ inline void ds_rows_of(const DsEntry& E, int cta, int G, int
     r0 = ds_row_begin(vc, E.M, E.ncta);
     n = ds_row_begin(vc + 1, E.M, E.ncta) - r0;
 }
-// bytes a chunk of entry E holds in the ring (always a full tile's worth, also for the last, shorter tile)
-__host__ __device__ inline int ds_chunk_bytes(const DsEntry& E) { return kDsTileRows * (E.piece_bytes + kDsPad); }
+// bytes a chunk of nr rows of entry E holds in the ring
+__host__ __device__ inline int ds_chunk_bytes(const DsEntry& E, int nr) { return nr * (E.piece_bytes + kDsPad); }
 // the CTA that runs head h of layer l (H <= G: heads spread with a stride, rotated per layer so that the extra bytes of a
 // head's back-projection rows do not always land on the same SMs); -1 when CTA `cta` has no head in that layer
 __host__ __device__ inline int ds_head_of_cta(int cta, int l, int H, int G) {
@@ -195,6 +197,23 @@ __device__ __forceinline__ long long ds_warp_sum_ll(long long v) {
     return (long long)hi * 65536 + (long long)lo;
 }
 
+// What the producer tells the consumer about a chunk.  Chunk j of the launch always uses barrier pair j mod 16 and, when it
+// carries weight rows, belongs to consumer warp j mod 16: the consumers do no placement arithmetic of their own.
+struct alignas(16) DsDesc {  // read with two 16-byte loads
+    int ring_off;    // byte offset of the chunk in the ring
+    int nr;          // rows in the chunk (<= 16)
+    int steps;       // 64-byte column steps (pairs of k steps) of the piece
+    int piece;       // which piece of the rows' K
+    uint32_t baddr;  // shared-memory address of the activation fragments of this piece (lane offset not included)
+    int part_off;    // byte offset of the tile's partial sums
+    int tile_idx;    // arrival counter of the tile
+    int e;           // matrix: DSE_* (DSE_COUNT: the head)
+    int row0;        // first row of the tile, counted from the CTA's first row of the matrix
+    int stage_off;   // first staged (scale, zero) of the matrix
+    int pad[2];
+};
+static_assert(sizeof(DsDesc) == 48 && offsetof(DsDesc, baddr) == 16, "DsDesc is read as two 16-byte halves");
+
 // ---- shared-memory layout: [ring][operand area: vec_floats x 4 bytes][DsShared][rank-space vector] ----------------
 struct DsShared {
     uint64_t full[kDsBars], empty[kDsBars];
@@ -210,6 +229,10 @@ struct DsShared {
     float cs_own[kDsMaxSlice];  // pending channel-mix shift state of the slice
     float ws[kDsMaxRows], wz[kDsMaxRows];  // (scale, zero) of the rows this CTA owns in the current phase
     float hv[10 * 64];                     // the 64-vectors of a head
+    int er0[DSE_COUNT + 1], en[DSE_COUNT + 1];  // rows [er0, er0 + en) of every matrix (DSE_*; last: the head) this CTA owns: the same in all layers
+    int rank_entry;                        // the rank projection whose rows this CTA owns (-1: none)
+    DsDesc desc[kDsBars];                  // what the chunk on barrier b is (written by the producer before it arms the barrier)
+    int nch[6];                            // chunks of this CTA per phase: phase 1 of layer 0, phase 1, 3, 4, 5, head
     int tile_cnt[kDsMaxTiles];             // pieces of a tile finished so far (zero between phases)
     long long part[kDsPartBytes / 8];      // per-piece partial sums: int64 (int8 matrices) or fp32 (fp16 matrices), 16 rows each
     DsLayer layer[2];                      // table of the current / next layer
@@ -308,25 +331,6 @@ __device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const 
     ds_consumer_sync();
 }
 
-// consumer-side view of the ring: every consumer warp replays the placement of every chunk the producer issues
-struct DsCons {
-    uint32_t ring_s;
-    int R, head;
-    int cur;        // byte offset of the chunk the last advance returned
-    uint32_t j;     // chunks placed so far
-};
-// Places the next chunk (same rule as the producer); its offset goes to cs.cur, its barrier index is returned.
-__device__ __forceinline__ uint32_t ds_chunk_next(DsCons& cs, int bytes) {
-    if (cs.head + bytes > cs.R) cs.head = 0;
-    cs.cur = cs.head;
-    cs.head += bytes;
-    return cs.j++;
-}
-__device__ __forceinline__ bool ds_chunk_wait(DsShared* S, uint32_t idx) {
-    const bool ok = mbar_wait(&S->full[idx % kDsBars], (idx / kDsBars) & 1u, (volatile int*)&S->abort_flag);
-    return __all_sync(0xffffffffu, ok);
-}
-
 // What the consumer warps need to turn a row's sums into an output.
 struct DsPhaseCtx {
     uint32_t vec_s;  // shared-memory address of the operand area
@@ -373,122 +377,130 @@ __device__ __forceinline__ void ds_store(const DsParams& P, DsShared* S, const D
     }
 }
 
-// The matrices of one phase.  Work items (the producer issues their chunks in the same order): matrix after matrix, tile
-// after tile (16 rows), piece after piece (<= 1280 bytes of K); item i of the phase belongs to consumer warp i mod 16, so the
-// pieces of a long row are multiplied by different warps at the same time.  A warp leaves the partial sums of its piece in
-// shared memory and counts its arrival on the tile; the warp that arrives last adds the pieces in piece order (exact for
-// int8, fixed order for fp16) and stores the outputs.  Returns false after a timeout.
-__device__ __noinline__ bool ds_run_entries(const DsParams& P, DsShared* S, DsCons& cs, const DsEntry* ents, int cnt, DsPhaseCtx& pc, int cta, int G, int wwarp,
-                                            int lane) {
+// number of chunks the matrices ents[0 .. cnt) give this CTA (e0: index of ents[0] in the row-range cache)
+__device__ inline int ds_count_chunks(const DsShared* S, const DsEntry* ents, int e0, int cnt) {
+    int c = 0;
+    for (int i = 0; i < cnt; ++i) {
+        const int n = ents[i].M > 0 ? S->en[e0 + i] : 0;
+        c += ((n + kDsTileRows - 1) / kDsTileRows) * ents[i].npieces;
+    }
+    return c;
+}
+
+// The weight rows of one phase: its chunks are J, J + 1, ..., J + n - 1 of the launch (matrix after matrix, tile after tile
+// of 16 rows, piece after piece of <= 1280 bytes of K: the producer's order), and chunk j belongs to consumer warp j mod 16,
+// so the pieces of a long row are multiplied by different warps at the same time.  A warp leaves the partial sums of its
+// piece in shared memory and counts its arrival on the tile; the warp that arrives last adds the pieces in piece order (exact
+// for int8, fixed order for fp16) and stores the outputs.  `tab`: the layer's matrices (indexed by DSE_*).  Returns false after a timeout.
+__device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const DsEntry* tab, uint32_t ring_s, uint32_t J, int n, DsPhaseCtx& pc, int wwarp, int lane) {
     const int g = lane >> 2, t = lane & 3;
-    int stage_off = 0, item = 0, tile_idx = 0, part_off = 0;  // part_off: bytes of partial sums of the tiles before this one
-    for (int ei = 0; ei < cnt; ++ei) {
-        const DsEntry& E = ents[ei];
-        int r0, n;
-        ds_rows_of(E, cta, G, r0, n);
-        if (n <= 0) continue;
+    for (uint32_t j = J + ((wwarp - J) & (kDsConsumerWarps - 1)); (int)(j - J) < n; j += kDsConsumerWarps) {
+#ifdef RSV_DS_DEBUG
+        const long long tw0 = ds_now();
+#endif
+        const bool got = mbar_wait(&S->full[wwarp], (j / kDsBars) & 1u, (volatile int*)&S->abort_flag);
+        if (!__all_sync(0xffffffffu, got)) return false;
+#ifdef RSV_DS_DEBUG
+        const long long tw1 = ds_now();
+#endif
+        const uint4 d0 = *reinterpret_cast<const uint4*>(&S->desc[wwarp].ring_off), d1 = *reinterpret_cast<const uint4*>(&S->desc[wwarp].baddr);
+        const int ring_off = (int)d0.x, nr = (int)d0.y, steps = (int)d0.z, piece = (int)d0.w, part_off = (int)d1.y, tile_idx = (int)d1.z, e = (int)d1.w;
+        const DsEntry& E = e == DSE_COUNT ? P.head : tab[e];
         const bool i8 = E.is_i8 != 0;
-        const int ntiles = (n + kDsTileRows - 1) / kDsTileRows, cb = ds_chunk_bytes(E), stride = E.piece_bytes + kDsPad, steps = E.piece_bytes >> 6;
-        const int np = E.npieces, klen = (i8 ? E.piece_bytes : (E.piece_bytes >> 1)) * np;  // elements of the operand vector
+        const int np = E.npieces, stride = E.piece_bytes + kDsPad;
         // B fragments of this lane: 16 bytes per two k steps at [k-step pair][operand row g][t]; columns beyond the operand's rows are zero
         const int brows = i8 ? 4 : 2, bstep = brows * 64, slot = i8 ? 8 : 4;
-        const uint32_t bbase = pc.vec_s + (uint32_t)E.xvec * (uint32_t)klen * 4u + (uint32_t)(g * 4 + t) * 16u;
         const bool bcol_ok = g < brows;
-        for (int ti = 0; ti < ntiles; ++ti, ++tile_idx, part_off += np * kDsTileRows * slot) {
-            const int row0 = ti * kDsTileRows, nr = min(kDsTileRows, n - row0);
-            for (int p = 0; p < np; ++p, ++item) {
-                const uint32_t idx = ds_chunk_next(cs, cb);
-                if ((item & (kDsConsumerWarps - 1)) != wwarp) continue;
-#ifdef RSV_DS_DEBUG
-                const long long tw0 = ds_now();
-#endif
-                if (!ds_chunk_wait(S, idx)) return false;
-#ifdef RSV_DS_DEBUG
-                const long long tw1 = ds_now();
-#endif
-                // ldmatrix row addresses: lanes 0-7 rows 0-7, 8-15 rows 8-15 (bytes 0-15 of a 32-byte k step), lanes 16-31 the same rows, bytes 16-31
-                const int arow = min((lane & 7) + ((lane >> 3) & 1) * 8, nr - 1);
-                uint32_t aaddr = cs.ring_s + (uint32_t)cs.cur + (uint32_t)arow * (uint32_t)stride + (uint32_t)(lane >> 4) * 16u;
-                uint32_t baddr = bbase + (uint32_t)p * (uint32_t)steps * (uint32_t)bstep;
-                char* part = reinterpret_cast<char*>(S->part) + part_off + p * kDsTileRows * slot;
-                if (i8) {
-                    int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+        uint32_t baddr = d1.x + (uint32_t)(g * 4 + t) * 16u;
+        // ldmatrix row addresses: lanes 0-7 rows 0-7, 8-15 rows 8-15 (bytes 0-15 of a 32-byte k step), lanes 16-31 the same rows, bytes 16-31
+        const int arow = min((lane & 7) + ((lane >> 3) & 1) * 8, nr - 1);
+        uint32_t aaddr = ring_s + (uint32_t)ring_off + (uint32_t)arow * (uint32_t)stride + (uint32_t)(lane >> 4) * 16u;
+        char* part = reinterpret_cast<char*>(S->part) + part_off + piece * kDsTileRows * slot;
+        if (i8) {
+            int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
 #pragma unroll 2
-                    for (int s2 = 0; s2 < steps; ++s2) {
-                        const uint4 a0 = ds_ldmatrix4(aaddr), a1 = ds_ldmatrix4(aaddr + 32);
-                        uint4 b = make_uint4(0, 0, 0, 0);
-                        if (bcol_ok) b = ds_lds128(baddr);
-                        ds_mma_i8(c0, a0, b.x, b.y);
-                        ds_mma_i8(c1, a1, b.z, b.w);
-                        aaddr += 64;
-                        baddr += bstep;
-                    }
-                    // accumulator (rows g, g + 8; columns 2 t, 2 t + 1) = weight rows x digits 2 t, 2 t + 1 (t < 2); digit d weighs 256^d
-                    const int lo = t < 2 ? 16 * t : 0;
-                    long long va = t < 2 ? (((long long)(c0[0] + c1[0]) << lo) + ((long long)(c0[1] + c1[1]) << (lo + 8))) : 0;
-                    long long vb = t < 2 ? (((long long)(c0[2] + c1[2]) << lo) + ((long long)(c0[3] + c1[3]) << (lo + 8))) : 0;
-                    va += __shfl_xor_sync(0xffffffffu, va, 1);
-                    vb += __shfl_xor_sync(0xffffffffu, vb, 1);
-                    if (t == 0) {
-                        reinterpret_cast<long long*>(part)[g] = va;
-                        reinterpret_cast<long long*>(part)[g + 8] = vb;
-                    }
-                } else {
-                    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int s2 = 0; s2 < steps; ++s2) {
+                const uint4 a0 = ds_ldmatrix4(aaddr), a1 = ds_ldmatrix4(aaddr + 32);
+                uint4 b = make_uint4(0, 0, 0, 0);
+                if (bcol_ok) b = ds_lds128(baddr);
+                ds_mma_i8(c0, a0, b.x, b.y);
+                ds_mma_i8(c1, a1, b.z, b.w);
+                aaddr += 64;
+                baddr += bstep;
+            }
+            // accumulator (rows g, g + 8; columns 2 t, 2 t + 1) = weight rows x digits 2 t, 2 t + 1 (t < 2); digit d weighs 256^d
+            const int lo = t < 2 ? 16 * t : 0;
+            long long va = t < 2 ? (((long long)(c0[0] + c1[0]) << lo) + ((long long)(c0[1] + c1[1]) << (lo + 8))) : 0;
+            long long vb = t < 2 ? (((long long)(c0[2] + c1[2]) << lo) + ((long long)(c0[3] + c1[3]) << (lo + 8))) : 0;
+            va += __shfl_xor_sync(0xffffffffu, va, 1);
+            vb += __shfl_xor_sync(0xffffffffu, vb, 1);
+            if (t == 0) {
+                reinterpret_cast<long long*>(part)[g] = va;
+                reinterpret_cast<long long*>(part)[g + 8] = vb;
+            }
+        } else {
+            float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 2
-                    for (int s2 = 0; s2 < steps; ++s2) {
-                        const uint4 a0 = ds_ldmatrix4(aaddr), a1 = ds_ldmatrix4(aaddr + 32);
-                        uint4 b = make_uint4(0, 0, 0, 0);
-                        if (bcol_ok) b = ds_lds128(baddr);
-                        ds_mma_f16(c0, a0, b.x, b.y);
-                        ds_mma_f16(c1, a1, b.z, b.w);
-                        aaddr += 64;
-                        baddr += bstep;
-                    }
-                    if (t == 0) {  // columns 0, 1 = hi, lo
-                        reinterpret_cast<float*>(part)[g] = (c0[0] + c1[0]) + (c0[1] + c1[1]);
-                        reinterpret_cast<float*>(part)[g + 8] = (c0[2] + c1[2]) + (c0[3] + c1[3]);
-                    }
-                }
-                __syncwarp();
-                int old = 0;
-                if (lane == 0) {
-                    mbar_arrive(&S->empty[idx % kDsBars]);
-                    __threadfence_block();
-                    old = atomicAdd(&S->tile_cnt[tile_idx], 1);
-                }
-                old = __shfl_sync(0xffffffffu, old, 0);
-#ifdef RSV_DS_DEBUG
-                if (pc.dbg && lane == 0 && wwarp == 0) {
-                    pc.dbg[0] += tw1 - tw0;
-                    pc.dbg[1] += ds_now() - tw1;
-                    pc.dbg[2] += 1;
-                }
-#endif
-                if (old == np - 1) {
-                    // last piece of the tile: lane r adds the pieces of row r in piece order and stores the output
-                    __threadfence_block();
-                    const int rl = row0 + lane;
-                    if (lane < nr) {
-                        const char* pt = reinterpret_cast<const char*>(S->part) + part_off;
-                        if (i8) {
-                            long long Q = 0, T = 0;
-                            for (int q = 0; q < np; ++q) Q += reinterpret_cast<const volatile long long*>(pt + q * kDsTileRows * 8)[lane];
-#pragma unroll
-                            for (int w = 0; w < kDsConsumerWarps; ++w) T += S->tsw[E.xvec][w];
-                            const double ws = S->ws[stage_off + rl], wz = S->wz[stage_off + rl];
-                            ds_store(P, S, E, r0 + rl, rl, (float)((double)ds_pow2(S->ex[E.xvec] - kDsP) * (ws * (double)Q + wz * (double)T)), pc);
-                        } else {
-                            float y = 0.f;
-                            for (int q = 0; q < np; ++q) y += reinterpret_cast<const volatile float*>(pt + q * kDsTileRows * 4)[lane];
-                            ds_store(P, S, E, r0 + rl, rl, y * ds_pow2(S->ex[E.xvec]), pc);
-                        }
-                    }
-                    if (lane == 0) S->tile_cnt[tile_idx] = 0;
-                }
+            for (int s2 = 0; s2 < steps; ++s2) {
+                const uint4 a0 = ds_ldmatrix4(aaddr), a1 = ds_ldmatrix4(aaddr + 32);
+                uint4 b = make_uint4(0, 0, 0, 0);
+                if (bcol_ok) b = ds_lds128(baddr);
+                ds_mma_f16(c0, a0, b.x, b.y);
+                ds_mma_f16(c1, a1, b.z, b.w);
+                aaddr += 64;
+                baddr += bstep;
+            }
+            if (t == 0) {  // columns 0, 1 = hi, lo
+                reinterpret_cast<float*>(part)[g] = (c0[0] + c1[0]) + (c0[1] + c1[1]);
+                reinterpret_cast<float*>(part)[g + 8] = (c0[2] + c1[2]) + (c0[3] + c1[3]);
             }
         }
-        if (i8) stage_off += n;
+        const int row0 = S->desc[wwarp].row0, stage_off = S->desc[wwarp].stage_off;  // read before the barrier pair is handed back
+        __syncwarp();
+        int old = 0;
+        if (lane == 0) {
+            mbar_arrive(&S->empty[wwarp]);
+            __threadfence_block();
+            old = atomicAdd(&S->tile_cnt[tile_idx], 1);
+        }
+        old = __shfl_sync(0xffffffffu, old, 0);
+#ifdef RSV_DS_DEBUG
+        if (pc.dbg && lane == 0 && wwarp == 0) {
+            pc.dbg[0] += tw1 - tw0;
+            pc.dbg[1] += ds_now() - tw1;
+            pc.dbg[2] += 1;
+        }
+        if (pc.dbg && pc.dbg == P.dbg + 20 && lane == 0) {  // phase 1: per warp, the times of its last chunk
+            P.dbg[64 + wwarp * 4 + 0] = tw0;
+            P.dbg[64 + wwarp * 4 + 1] = tw1;
+            P.dbg[64 + wwarp * 4 + 2] = ds_now();
+        }
+#endif
+        if (old == np - 1) {
+            // last piece of the tile: lane r adds the pieces of row r in piece order and stores the output
+            __threadfence_block();
+            const int rl = row0 + lane;
+            if (lane < nr) {
+                const char* pt = reinterpret_cast<const char*>(S->part) + part_off;
+                const int r0 = S->er0[e];
+                if (i8) {
+                    long long Q = 0, T = 0;
+                    for (int q = 0; q < np; ++q) Q += reinterpret_cast<const volatile long long*>(pt + q * kDsTileRows * 8)[lane];
+#pragma unroll
+                    for (int w = 0; w < kDsConsumerWarps; ++w) T += S->tsw[E.xvec][w];
+                    const double ws = S->ws[stage_off + rl], wz = S->wz[stage_off + rl];
+                    ds_store(P, S, E, r0 + rl, rl, (float)((double)ds_pow2(S->ex[E.xvec] - kDsP) * (ws * (double)Q + wz * (double)T)), pc);
+                } else {
+                    float y = 0.f;
+                    for (int q = 0; q < np; ++q) y += reinterpret_cast<const volatile float*>(pt + q * kDsTileRows * 4)[lane];
+                    ds_store(P, S, E, r0 + rl, rl, y * ds_pow2(S->ex[E.xvec]), pc);
+                }
+            }
+            if (lane == 0) S->tile_cnt[tile_idx] = 0;
+#ifdef RSV_DS_DEBUG
+            if (pc.dbg && pc.dbg == P.dbg + 20 && lane == 0) P.dbg[64 + wwarp * 4 + 3] = ds_now();
+#endif
+        }
     }
     return true;
 }
@@ -551,7 +563,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
     extern __shared__ __align__(1024) uint8_t ds_smem_raw[];
     uint8_t* ring = (uint8_t*)(((uintptr_t)ds_smem_raw + 127) & ~(uintptr_t)127);
     float* vec = reinterpret_cast<float*>(ring + P.ring_bytes);
-    DsShared* S = reinterpret_cast<DsShared*>(vec + P.vec_floats);
+    DsShared* S = reinterpret_cast<DsShared*>(vec + P.vec_floats);  // 16-byte aligned: ring and operand area are multiples of 16 bytes
     float* sc_mid = reinterpret_cast<float*>(S + 1);
     volatile int* abort_flag = (volatile int*)&S->abort_flag;
 
@@ -571,6 +583,29 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int i = threadIdx.x; i < kDsMaxTiles; i += kDsThreads) S->tile_cnt[i] = 0;
+    if (threadIdx.x <= DSE_COUNT) {
+        // layer 1's table when there is one: layer 0 has no v-gate projection, otherwise all layers split alike
+        const DsEntry& E = threadIdx.x == DSE_COUNT ? P.head : P.layers[P.L > 1 ? 1 : 0].e[threadIdx.x];
+        int r0, n;
+        ds_rows_of(E, cta, G, r0, n);
+        S->er0[threadIdx.x] = r0;
+        S->en[threadIdx.x] = n;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int re = -1;
+        for (int e = DSE_W1; e <= DSE_V1; ++e)
+            if (S->en[e] > 0 && re < 0) re = e;
+        S->rank_entry = re;
+        const DsEntry* e0 = P.layers[0].e;
+        const DsEntry* e1 = P.layers[P.L > 1 ? 1 : 0].e;
+        S->nch[0] = ds_count_chunks(S, e0 + DSE_W1, DSE_W1, 7);
+        S->nch[1] = ds_count_chunks(S, e1 + DSE_W1, DSE_W1, 7);
+        S->nch[2] = ds_count_chunks(S, e1 + DSE_WO, DSE_WO, 1);
+        S->nch[3] = ds_count_chunks(S, e1 + DSE_WFK, DSE_WFK, 1);
+        S->nch[4] = ds_count_chunks(S, e1 + DSE_WFV, DSE_WFV, 1);
+        S->nch[5] = ds_count_chunks(S, &P.head, DSE_COUNT, 1);
+    }
     __syncthreads();
 
     if (warp == 0) {
@@ -580,9 +615,10 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
         int head = 0, used = 0;
         uint32_t j = 0, tail = 0;
         bool ok = true;
-        // Reserves `bytes` in the ring for chunk j (waiting for the oldest chunks to be released) and arms its barrier for
-        // `tx` bytes of copies; the chunk starts at `head - bytes`.
-        auto reserve = [&](int bytes, int tx) -> bool {
+        const uint32_t vec_s = smem_u32(vec);
+        // Reserves `bytes` in the ring for chunk j (waiting for the oldest chunks to be released); the chunk starts at `head - bytes`.
+        // Lane 0 then writes the chunk's descriptor and arms the barrier (arm) before the copies are issued.
+        auto reserve = [&](int bytes) -> bool {
             const bool wrap = head + bytes > R;  // the chunk does not fit behind the last one: it goes to the start of the ring
             const int waste = wrap ? R - head : 0;
             while (used + waste + bytes > R || j - tail >= (uint32_t)kDsBars) {
@@ -593,30 +629,62 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
             }
             if (wrap) head = 0;
             __syncwarp();
-            if (lane == 0) {
-                S->alloc[j % kDsBars] = waste + bytes;
-                mbar_expect_tx(&S->full[j % kDsBars], (uint32_t)tx);
-            }
-            __syncwarp();
+            if (lane == 0) S->alloc[j % kDsBars] = waste + bytes;
             used += waste + bytes;
             head += bytes;
             return true;
         };
-        auto put_entry = [&](const DsEntry& E) -> bool {
-            int r0, n;
-            ds_rows_of(E, cta, G, r0, n);
+        auto arm = [&](int tx) {
+            if (lane == 0) mbar_expect_tx(&S->full[j % kDsBars], (uint32_t)tx);  // release: the descriptor is visible to whoever sees the barrier complete
+            __syncwarp();
+        };
+        // running counters of the current phase (the consumer side finds them in the descriptors)
+        int ph_tile = 0, ph_part = 0, ph_stage = 0;
+        auto put_entry = [&](const DsEntry& E, int e) -> bool {
+            const int r0 = S->er0[e], n = E.M > 0 ? S->en[e] : 0;
             if (n <= 0) return true;
-            const int ntiles = (n + kDsTileRows - 1) / kDsTileRows, cb = ds_chunk_bytes(E), stride = E.piece_bytes + kDsPad;
-            for (int ti = 0; ti < ntiles; ++ti)
+            const bool i8 = E.is_i8 != 0;
+            const int ntiles = (n + kDsTileRows - 1) / kDsTileRows, stride = E.piece_bytes + kDsPad, steps = E.piece_bytes >> 6;
+            const int klen = (i8 ? E.piece_bytes : (E.piece_bytes >> 1)) * E.npieces, bstep = (i8 ? 4 : 2) * 64, slot = i8 ? 8 : 4;
+            for (int ti = 0; ti < ntiles; ++ti) {
+                const int row0 = ti * kDsTileRows, nr = min(kDsTileRows, n - row0), cb = ds_chunk_bytes(E, nr);
                 for (int p = 0; p < E.npieces; ++p) {
-                    const int row0 = ti * kDsTileRows, nr = min(kDsTileRows, n - row0);
-                    if (!reserve(cb, nr * E.piece_bytes)) return false;
+                    if (!reserve(cb)) return false;
+                    if (lane == 0) {
+                        DsDesc& D = S->desc[j % kDsBars];
+                        D.ring_off = head - cb;
+                        D.nr = nr;
+                        D.steps = steps;
+                        D.piece = p;
+                        D.baddr = vec_s + (uint32_t)E.xvec * (uint32_t)klen * 4u + (uint32_t)p * (uint32_t)steps * (uint32_t)bstep;
+                        D.part_off = ph_part;
+                        D.tile_idx = ph_tile;
+                        D.e = e;
+                        D.row0 = row0;
+                        D.stage_off = ph_stage;
+                    }
+                    arm(nr * E.piece_bytes);
                     if (lane < nr)
                         ds_bulk_load(ring_s + (uint32_t)(head - cb + lane * stride),
                                      E.base + (size_t)(r0 + row0 + lane) * (size_t)E.row_stride + (size_t)p * E.piece_bytes, (uint32_t)E.piece_bytes,
                                      &S->full[j % kDsBars], pol);
                     ++j;
                 }
+                ++ph_tile;
+                ph_part += E.npieces * kDsTileRows * slot;
+            }
+            if (i8) ph_stage += n;
+            return true;
+        };
+        auto new_phase = [&]() { ph_tile = ph_part = ph_stage = 0; };
+        // a chunk that is not weight rows (a head's back-projection rows): one or two plain copies, only the offset is published
+        auto put_raw = [&](int bytes, const void* src0, int n0, const void* src1, int n1) -> bool {
+            if (!reserve(bytes)) return false;
+            if (lane == 0) S->desc[j % kDsBars].ring_off = head - bytes;
+            arm(bytes);
+            if (lane == 0 && n0) ds_bulk_load(ring_s + (uint32_t)(head - bytes), src0, (uint32_t)n0, &S->full[j % kDsBars], pol);
+            if (lane == 1 && n1) ds_bulk_load(ring_s + (uint32_t)(head - bytes + n0), src1, (uint32_t)n1, &S->full[j % kDsBars], pol);
+            ++j;
             return true;
         };
         for (int t = 0; t < P.n_tokens && ok; ++t) {
@@ -626,7 +694,8 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #ifdef RSV_DS_DEBUG
                 if (P.dbg && cta == 0 && lane == 0 && t == 1 && l == 1) P.dbg[40] = ds_now();
 #endif
-                for (int e = DSE_W1; e <= DSE_WV && ok; ++e) ok = put_entry(Lg->e[e]);
+                new_phase();
+                for (int e = DSE_W1; e <= DSE_WV && ok; ++e) ok = put_entry(Lg->e[e], e);
                 if (!ok) break;
 #ifdef RSV_DS_DEBUG
                 if (P.dbg && cta == 0 && lane == 0 && t == 1 && l == 1) P.dbg[41] = ds_now();
@@ -635,30 +704,25 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 if (h >= 0) {
                     // chunk A: w2, a2 rows of the head; chunk B: v2 rows (layers > 0) and the first 32 g2 rows; chunk C: the other 32
                     const int vb = l > 0 ? 64 * P.vm * 2 : 0;
-                    if (!(ok = reserve(hbA, hbA))) break;
-                    if (lane == 0) ds_bulk_load(ring_s + (uint32_t)(head - hbA), Lg->w2 + (size_t)h * 64 * P.wm, 64u * P.wm * 2u, &S->full[j % kDsBars], pol);
-                    if (lane == 1)
-                        ds_bulk_load(ring_s + (uint32_t)(head - hbA + 64 * P.wm * 2), Lg->a2 + (size_t)h * 64 * P.am, 64u * P.am * 2u, &S->full[j % kDsBars], pol);
-                    ++j;
-                    if (!(ok = reserve(vb + hbC, vb + hbC))) break;
-                    if (lane == 0 && vb) ds_bulk_load(ring_s + (uint32_t)(head - vb - hbC), Lg->v2 + (size_t)h * 64 * P.vm, (uint32_t)vb, &S->full[j % kDsBars], pol);
-                    if (lane == 1) ds_bulk_load(ring_s + (uint32_t)(head - hbC), Lg->g2 + (size_t)h * 64 * P.gm, (uint32_t)hbC, &S->full[j % kDsBars], pol);
-                    ++j;
-                    if (!(ok = reserve(hbC, hbC))) break;
-                    if (lane == 0) ds_bulk_load(ring_s + (uint32_t)(head - hbC), Lg->g2 + ((size_t)h * 64 + 32) * P.gm, (uint32_t)hbC, &S->full[j % kDsBars], pol);
-                    ++j;
+                    if (!(ok = put_raw(hbA, Lg->w2 + (size_t)h * 64 * P.wm, 64 * P.wm * 2, Lg->a2 + (size_t)h * 64 * P.am, 64 * P.am * 2))) break;
+                    if (!(ok = put_raw(vb + hbC, Lg->v2 + (size_t)h * 64 * P.vm, vb, Lg->g2 + (size_t)h * 64 * P.gm, hbC))) break;
+                    if (!(ok = put_raw(hbC, Lg->g2 + ((size_t)h * 64 + 32) * P.gm, hbC, nullptr, 0))) break;
                 }
 #ifdef RSV_DS_DEBUG
                 if (P.dbg && cta == 0 && lane == 0 && t == 1 && l == 1) P.dbg[42] = ds_now();
 #endif
                 for (int e = DSE_WO; e <= DSE_WFV && ok; ++e) {
-                    ok = put_entry(Lg->e[e]);
+                    new_phase();
+                    ok = put_entry(Lg->e[e], e);
 #ifdef RSV_DS_DEBUG
                     if (P.dbg && cta == 0 && lane == 0 && t == 1 && l == 1) P.dbg[43 + e - DSE_WO] = ds_now();
 #endif
                 }
             }
-            if (ok && do_head) ok = put_entry(P.head);
+            if (ok && do_head) {
+                new_phase();
+                ok = put_entry(P.head, DSE_COUNT);
+            }
         }
         // copies still in flight must land before the CTA may exit (only after an abort: otherwise every chunk was consumed)
         if (!ok)
@@ -666,14 +730,15 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
     } else {
         // =========================== consumers ===========================
         const int wtid = threadIdx.x - 32, wwarp = wtid >> 5;
-        DsCons cs{smem_u32(ring), R, 0, 0, 0u};
+        const uint32_t ring_s = smem_u32(ring);
+        uint32_t J = 0;  // chunks of this CTA consumed so far (the producer numbers them the same way)
         DsPhaseCtx pc{};
         pc.vec_s = smem_u32(vec);
         pc.best_val = -1e30f;
         pc.best_idx = 0x7fffffff;
         unsigned bar_target = 0;
         bool ok = true, pending = false;
-        const int r0o = ds_row_begin(cta, C, G), nown = ds_row_begin(cta + 1, C, G) - r0o;  // this CTA's slice of the channels
+        const int r0o = S->er0[DSE_WO], nown = S->en[DSE_WO];  // this CTA's slice of the channels = its rows of att.output / ffn.value
         uint32_t lt = 0;  // layers run so far: the table of the current layer sits in S->layer[lt & 1]
 
         auto stage_layer = [&](int l, uint32_t slot) {
@@ -716,12 +781,11 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
             pending = true;
         };
         // (scale, zero) of the int8 rows this CTA owns in the coming phase -> shared memory (weights: no dependency on a barrier)
-        auto stage_scales = [&](const DsEntry* ents, int cnt) {
+        auto stage_scales = [&](const DsEntry* ents, int e0, int cnt) {
             int off = 0;
             for (int i = 0; i < cnt; ++i) {
                 const DsEntry& E = ents[i];
-                int r0, n;
-                ds_rows_of(E, cta, G, r0, n);
+                const int r0 = S->er0[e0 + i], n = E.M > 0 ? S->en[e0 + i] : 0;
                 if (!E.is_i8 || n <= 0) continue;
                 for (int q = wtid; q < n && off + q < kDsMaxRows; q += kDsConsumers) {
                     S->ws[off + q] = __ldg(E.wscale + r0 + q);
@@ -729,15 +793,6 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 }
                 off += n;
             }
-        };
-        // the rank projection whose rows this CTA owns (at most one: their rows are split over disjoint groups of CTAs)
-        auto my_rank_entry = [&](const DsLayer& Ly) -> int {
-            for (int e = DSE_W1; e <= DSE_V1; ++e) {
-                int r0, n;
-                ds_rows_of(Ly.e[e], cta, G, r0, n);
-                if (n > 0) return e;
-            }
-            return -1;
         };
 
         for (int t = 0; t < P.n_tokens && ok; ++t) {
@@ -762,9 +817,9 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 DS_STAMP(0);
                 // ================= phase 1: LN1 + token shift -> r, k, v, rank projections =================
                 {
-                    const int re = my_rank_entry(Ly);
+                    const int re = S->rank_entry;  // at most one: the rank projections' rows are split over disjoint groups of CTAs
                     const float* rmix = re >= 0 ? Ly.e[re].mix : Ly.x_r;
-                    stage_scales(&Ly.e[DSE_W1], 7);
+                    stage_scales(&Ly.e[DSE_W1], DSE_W1, 7);
                     if (!(ok = bar_wait())) break;
                     DS_STAMP(10);
                     float4 xv[NG], lw[NG], lb[NG], pv[NG], mx[4][NG];
@@ -798,8 +853,10 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #pragma unroll
                         for (int gi = 0; gi < NG; ++gi) xv[gi] = ds_ln_apply(xv[gi], m0, i0, w0v[gi], b0v[gi]);
                     }
+                    DS_STAMP(15);
                     float mean, inv;
                     ds_ln_stats<NG>(S, C, xv, wtid, mean, inv);
+                    DS_STAMP(16);
                     float4 cur[NG], del[NG];
 #pragma unroll
                     for (int gi = 0; gi < NG; ++gi) {
@@ -818,6 +875,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                             }
                         }
                     }
+                    DS_STAMP(17);
                     const bool i8[4] = {Ly.e[DSE_WR].is_i8 != 0, Ly.e[DSE_WK].is_i8 != 0, Ly.e[DSE_WV].is_i8 != 0, false};
                     ds_emit<4, NG>(S, vec, C, i8, [&](int v, int gi) { return ds_mix4(cur[gi], mx[v][gi], del[gi]); }, wtid);
                 }
@@ -825,7 +883,11 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #ifdef RSV_DS_DEBUG
                 pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 20 : nullptr;
 #endif
-                if (!(ok = ds_run_entries(P, S, cs, &Ly.e[DSE_W1], 7, pc, cta, G, wwarp, lane))) break;
+                {
+                    const int nc = S->nch[l == 0 ? 0 : 1];
+                    if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, nc, pc, wwarp, lane))) break;
+                    J += (uint32_t)nc;
+                }
                 DS_STAMP(2);
                 bar_arrive();
 
@@ -880,26 +942,30 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                             return a + __shfl_xor_sync(0xffffffffu, a, 2);
                         };
                         const int vb = l > 0 ? 64 * P.vm * 2 : 0;
-                        const uint32_t iA = ds_chunk_next(cs, hbA);
-                        const uint8_t* cA = ring + cs.cur;
-                        const uint32_t iB = ds_chunk_next(cs, vb + hbC);
-                        const uint8_t* cB = ring + cs.cur;
-                        const uint32_t iC = ds_chunk_next(cs, hbC);
-                        const uint8_t* cC = ring + cs.cur;
-                        if (!ds_chunk_wait(S, iA)) {
+                        // the three chunks of the head's back-projection rows: J, J + 1, J + 2
+                        const uint32_t iA = J, iB = J + 1, iC = J + 2;
+                        J += 3;
+                        auto wait_chunk = [&](uint32_t idx) {
+                            const bool w = mbar_wait(&S->full[idx % kDsBars], (idx / kDsBars) & 1u, abort_flag);
+                            return __all_sync(0xffffffffu, w);
+                        };
+                        if (!wait_chunk(iA)) {
                             ok = false;
                             break;
                         }
+                        const uint8_t* cA = ring + S->desc[iA % kDsBars].ring_off;
                         float dw = 0.f, da = 0.f, dv = 0.f, dg = 0.f;
                         if (!upper) {
                             const __half* w2s = reinterpret_cast<const __half*>(cA);
                             dw = dot_q(w2s + (size_t)drow * P.wm, P.wm, sc_mid);
                             da = dot_q(w2s + (size_t)64 * P.wm + (size_t)drow * P.am, P.am, sc_mid + P.wm);
                         }
-                        if (!ds_chunk_wait(S, iB) || !ds_chunk_wait(S, iC)) {
+                        if (!wait_chunk(iB) || !wait_chunk(iC)) {
                             ok = false;
                             break;
                         }
+                        const uint8_t* cB = ring + S->desc[iB % kDsBars].ring_off;
+                        const uint8_t* cC = ring + S->desc[iC % kDsBars].ring_off;
                         if (upper) {
                             const __half* g2row = drow < 32 ? reinterpret_cast<const __half*>(cB + vb) + (size_t)drow * P.gm : reinterpret_cast<const __half*>(cC) + (size_t)(drow - 32) * P.gm;
                             dg = dot_q(g2row, P.gm, sc_mid + P.wm + P.am + P.vm);
@@ -988,7 +1054,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 
                 // ================= phase 3: att.output, x += =================
                 {
-                    stage_scales(&Ly.e[DSE_WO], 1);
+                    stage_scales(&Ly.e[DSE_WO], DSE_WO, 1);
                     if (!(ok = bar_wait())) break;
                     DS_STAMP(12);
                     if (wtid < nown) tm_l[r0o + wtid] = S->ts_own[wtid];  // new time-mix shift state (every reader of the old one is past barrier 1)
@@ -1004,14 +1070,15 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #ifdef RSV_DS_DEBUG
                 pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 24 : nullptr;
 #endif
-                    if (!(ok = ds_run_entries(P, S, cs, &Ly.e[DSE_WO], 1, pc, cta, G, wwarp, lane))) break;
+                    if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, S->nch[2], pc, wwarp, lane))) break;
+                    J += (uint32_t)S->nch[2];
                 }
                 DS_STAMP(5);
                 bar_arrive();
 
                 // ================= phase 4: LN2 + shift -> relu(ffn.key)^2 =================
                 {
-                    stage_scales(&Ly.e[DSE_WFK], 1);
+                    stage_scales(&Ly.e[DSE_WFK], DSE_WFK, 1);
                     const int lnext = l + 1 < P.L ? l + 1 : 0;
                     stage_layer(lnext, lt + 1);  // the table of the layer that runs next (the first one again after the last)
                     if (!(ok = bar_wait())) break;
@@ -1050,14 +1117,15 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #ifdef RSV_DS_DEBUG
                 pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 28 : nullptr;
 #endif
-                    if (!(ok = ds_run_entries(P, S, cs, &Ly.e[DSE_WFK], 1, pc, cta, G, wwarp, lane))) break;
+                    if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, S->nch[3], pc, wwarp, lane))) break;
+                    J += (uint32_t)S->nch[3];
                 }
                 DS_STAMP(7);
                 bar_arrive();
 
                 // ================= phase 5: ffn.value (K = F = 4 C), x += =================
                 {
-                    stage_scales(&Ly.e[DSE_WFV], 1);
+                    stage_scales(&Ly.e[DSE_WFV], DSE_WFV, 1);
                     if (!(ok = bar_wait())) break;
                     DS_STAMP(14);
                     if (wtid < nown) cm_l[r0o + wtid] = S->cs_own[wtid];
@@ -1073,7 +1141,8 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #ifdef RSV_DS_DEBUG
                 pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 32 : nullptr;
 #endif
-                    if (!(ok = ds_run_entries(P, S, cs, &Ly.e[DSE_WFV], 1, pc, cta, G, wwarp, lane))) break;
+                    if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, S->nch[4], pc, wwarp, lane))) break;
+                    J += (uint32_t)S->nch[4];
                 }
                 DS_STAMP(9);
                 bar_arrive();
@@ -1082,7 +1151,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 
             // ================= ln_out + head -> logits, arg-max =================
             if (do_head) {
-                stage_scales(&P.head, 1);
+                stage_scales(&P.head, DSE_COUNT, 1);
                 if (!(ok = bar_wait())) break;
                 float4 lw[NG], lb[NG], xv[NG];
 #pragma unroll
@@ -1104,7 +1173,8 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #ifdef RSV_DS_DEBUG
                 pc.dbg = nullptr;
 #endif
-                if (!(ok = ds_run_entries(P, S, cs, &P.head, 1, pc, cta, G, wwarp, lane))) break;
+                if (!(ok = ds_consume(P, S, nullptr, ring_s, J, S->nch[5], pc, wwarp, lane))) break;
+                J += (uint32_t)S->nch[5];
                 if (P.argmax_feed) {
                     // arg-max: lanes -> warp -> CTA -> grid; ties go to the smaller index
                     float bv = pc.best_val;

@@ -1565,8 +1565,8 @@ bool Model::stream_available() {
     RSV_CUDA(cudaMemset(sc.mid, 0, (size_t)std::max(cfg.mids(), 1) * 4));
     RSV_CUDA(cudaMemset(sc.vfirst, 0, (size_t)C * 4));
 #ifdef RSV_DS_DEBUG
-    RSV_CUDA(cudaMalloc(&sc.dbg, 64 * sizeof(long long)));
-    RSV_CUDA(cudaMemset(sc.dbg, 0, 64 * sizeof(long long)));
+    RSV_CUDA(cudaMalloc(&sc.dbg, 256 * sizeof(long long)));
+    RSV_CUDA(cudaMemset(sc.dbg, 0, 256 * sizeof(long long)));
 #endif
     P.layers = (const DsLayer*)sc.d_layers;
     P.head = make_entry(head, G, 0, DSO_LOGITS, 0, nullptr);
@@ -1632,7 +1632,7 @@ void Model::run_stream(State& st, int slot, int n_tokens, bool tok_from_list, bo
     LAUNCH(*this, "decode_stream") { dispatch_stream(sc.kl, P, sc.grid, sc.smem, stream, false); }
 #ifdef RSV_DS_DEBUG
     if (sc.dbg && n_tokens >= 2) {
-        long long h[64];
+        long long h[256];
         RSV_CUDA(cudaStreamSynchronize(stream));
         RSV_CUDA(cudaMemcpy(h, sc.dbg, sizeof(h), cudaMemcpyDeviceToHost));
         const int order[15] = {0, 10, 1, 2, 11, 3, 12, 4, 5, 13, 6, 7, 14, 8, 9};
@@ -1640,12 +1640,16 @@ void Model::run_stream(State& st, int slot, int n_tokens, bool tok_from_list, bo
                                  "barrier 5 passed", "barrier 1 passed", "barrier 2 passed", "barrier 3 passed", "barrier 4 passed"};
         fprintf(stderr, "[decode_stream_kernel, CTA 0, token 1, layer 1] us since the layer started\n");
         for (int i = 0; i < 15; ++i) fprintf(stderr, "  %-18s %.2f\n", names[order[i]], (h[order[i]] - h[0]) / 1e3);
+        fprintf(stderr, "  P1 prologue: loads issued %.2f, statistics done %.2f, shift / slice done %.2f\n", (h[15] - h[0]) / 1e3, (h[16] - h[0]) / 1e3, (h[17] - h[0]) / 1e3);
         const char* ph[4] = {"P1", "P3", "P4", "P5"};
         for (int i = 0; i < 4; ++i)
             fprintf(stderr, "  %s rows, consumer warp 0: %lld chunks, %.2f us waiting for them, %.2f us multiplying\n", ph[i], h[20 + 4 * i + 2], h[20 + 4 * i] / 1e3, h[20 + 4 * i + 1] / 1e3);
         fprintf(stderr, "  producer: P1 rows issued %.2f .. %.2f, later phases start %.2f, att.out issued %.2f, ffn.key %.2f, ffn.value %.2f\n", (h[40] - h[0]) / 1e3,
                 (h[41] - h[0]) / 1e3, (h[42] - h[0]) / 1e3, (h[43] - h[0]) / 1e3, (h[44] - h[0]) / 1e3, (h[45] - h[0]) / 1e3);
-        RSV_CUDA(cudaMemset(sc.dbg, 0, 64 * sizeof(long long)));
+        for (int w = 0; w < 16; ++w)
+            fprintf(stderr, "  P1 warp %2d: last chunk wait %.2f .. %.2f, multiplied %.2f, tile finished %.2f\n", w, (h[64 + 4 * w] - h[0]) / 1e3, (h[65 + 4 * w] - h[0]) / 1e3,
+                    (h[66 + 4 * w] - h[0]) / 1e3, h[67 + 4 * w] ? (h[67 + 4 * w] - h[0]) / 1e3 : 0.0);
+        RSV_CUDA(cudaMemset(sc.dbg, 0, 256 * sizeof(long long)));
     }
 #endif
 }
