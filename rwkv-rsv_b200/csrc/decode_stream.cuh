@@ -229,6 +229,8 @@ struct DsShared {
     float cs_own[kDsMaxSlice];  // pending channel-mix shift state of the slice
     float ws[kDsMaxRows], wz[kDsMaxRows];  // (scale, zero) of the rows this CTA owns in the current phase
     float hv[10 * 64];                     // the 64-vectors of a head
+    float best_val[kDsConsumers];          // per consumer thread: arg-max of the head rows it finished
+    int best_idx[kDsConsumers];
     int er0[DSE_COUNT + 1], en[DSE_COUNT + 1];  // rows [er0, er0 + en) of every matrix (DSE_*; last: the head) this CTA owns: the same in all layers
     int rank_entry;                        // the rank projection whose rows this CTA owns (-1: none)
     DsDesc desc[kDsBars];                  // what the chunk on barrier b is (written by the producer before it arms the barrier)
@@ -266,14 +268,14 @@ __device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const 
     ds_consumer_sync();
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
-        float a = 0.f;
+        float a = S->red_c[v * 16 + (lane & 15)];
 #pragma unroll
-        for (int w = 0; w < kDsConsumerWarps; ++w) a = fmaxf(a, S->red_c[v * 16 + w]);
+        for (int o = 8; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
         const int ex = ds_exponent(a);
         if (wtid == 0) S->ex[v] = ex;
         uint32_t* vb = reinterpret_cast<uint32_t*>(vec + (size_t)v * len);
         if (i8[v]) {
-            const float mult = ds_pow2(kDsP - ex), lim = (float)(1 << kDsP);
+            const float mult = ds_pow2(kDsP - ex);  // |x| <= 2^ex, so |t| <= 2^30; a NaN converts to 0
             long long ts = 0;
 #pragma unroll
             for (int gi = 0; gi < NGR; ++gi) {
@@ -284,8 +286,7 @@ __device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const 
                     uint32_t u[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const float q = fminf(fmaxf(f[j], -lim), lim);
-                        const int t = (q == q) ? __float2int_rn(q) : 0;
+                        const int t = __float2int_rn(f[j]);
                         ts += t;
                         u[j] = ((uint32_t)t + 0x00808080u) ^ 0x00808080u;  // bytes = signed base-256 digits of t
                     }
@@ -331,11 +332,9 @@ __device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const 
     ds_consumer_sync();
 }
 
-// What the consumer warps need to turn a row's sums into an output.
+// What the consumer warps need to turn a row's sums into an output (passed by value: nothing of it lives in local memory).
 struct DsPhaseCtx {
     uint32_t vec_s;  // shared-memory address of the operand area
-    float best_val;  // running arg-max of the head rows this lane finished
-    int best_idx;
 #ifdef RSV_DS_DEBUG
     long long* dbg;  // non-null: this call adds warp 0's time waiting for chunks to dbg[0] and its time multiplying to dbg[1]
 #endif
@@ -348,7 +347,7 @@ __device__ __forceinline__ long long ds_now() {
 }
 #endif
 
-__device__ __forceinline__ void ds_store(const DsParams& P, DsShared* S, const DsEntry& E, int m, int rl, float y, DsPhaseCtx& pc) {
+__device__ __forceinline__ void ds_store(const DsParams& P, DsShared* S, const DsEntry& E, int m, int rl, float y) {
     switch (E.out) {
         case DSO_R:
         case DSO_K:
@@ -367,13 +366,16 @@ __device__ __forceinline__ void ds_store(const DsParams& P, DsShared* S, const D
             P.hbuf[m] = a * a;
             break;
         }
-        default:
+        default: {
             P.logits[m] = y;
-            if (y > pc.best_val || (y == pc.best_val && m < pc.best_idx)) {
-                pc.best_val = y;
-                pc.best_idx = m;
+            // running arg-max of the head rows this lane finished (ties: smaller index); one slot per consumer thread
+            const int sl = (int)threadIdx.x - 32;
+            if (y > S->best_val[sl] || (y == S->best_val[sl] && m < S->best_idx[sl])) {
+                S->best_val[sl] = y;
+                S->best_idx[sl] = m;
             }
             break;
+        }
     }
 }
 
@@ -392,7 +394,7 @@ __device__ inline int ds_count_chunks(const DsShared* S, const DsEntry* ents, in
 // so the pieces of a long row are multiplied by different warps at the same time.  A warp leaves the partial sums of its
 // piece in shared memory and counts its arrival on the tile; the warp that arrives last adds the pieces in piece order (exact
 // for int8, fixed order for fp16) and stores the outputs.  `tab`: the layer's matrices (indexed by DSE_*).  Returns false after a timeout.
-__device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const DsEntry* tab, uint32_t ring_s, uint32_t J, int n, DsPhaseCtx& pc, int wwarp, int lane) {
+__device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const DsEntry* tab, uint32_t ring_s, uint32_t J, int n, DsPhaseCtx pc, int wwarp, int lane) {
     const int g = lane >> 2, t = lane & 3;
     for (uint32_t j = J + ((wwarp - J) & (kDsConsumerWarps - 1)); (int)(j - J) < n; j += kDsConsumerWarps) {
 #ifdef RSV_DS_DEBUG
@@ -480,20 +482,24 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
             // last piece of the tile: lane r adds the pieces of row r in piece order and stores the output
             __threadfence_block();
             const int rl = row0 + lane;
+            long long T = 0;
+            if (i8) {  // exact sum of the operand's fixed-point values: 16 per-warp sums, one per lane, then a shuffle tree
+                T = S->tsw[E.xvec][lane & 15];
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) T += __shfl_xor_sync(0xffffffffu, T, o);
+            }
             if (lane < nr) {
                 const char* pt = reinterpret_cast<const char*>(S->part) + part_off;
                 const int r0 = S->er0[e];
                 if (i8) {
-                    long long Q = 0, T = 0;
+                    long long Q = 0;
                     for (int q = 0; q < np; ++q) Q += reinterpret_cast<const volatile long long*>(pt + q * kDsTileRows * 8)[lane];
-#pragma unroll
-                    for (int w = 0; w < kDsConsumerWarps; ++w) T += S->tsw[E.xvec][w];
                     const double ws = S->ws[stage_off + rl], wz = S->wz[stage_off + rl];
-                    ds_store(P, S, E, r0 + rl, rl, (float)((double)ds_pow2(S->ex[E.xvec] - kDsP) * (ws * (double)Q + wz * (double)T)), pc);
+                    ds_store(P, S, E, r0 + rl, rl, (float)((double)ds_pow2(S->ex[E.xvec] - kDsP) * (ws * (double)Q + wz * (double)T)));
                 } else {
                     float y = 0.f;
                     for (int q = 0; q < np; ++q) y += reinterpret_cast<const volatile float*>(pt + q * kDsTileRows * 4)[lane];
-                    ds_store(P, S, E, r0 + rl, rl, y * ds_pow2(S->ex[E.xvec]), pc);
+                    ds_store(P, S, E, r0 + rl, rl, y * ds_pow2(S->ex[E.xvec]));
                 }
             }
             if (lane == 0) S->tile_cnt[tile_idx] = 0;
@@ -523,9 +529,9 @@ __device__ __forceinline__ float ds_block_sum(float v, float* arr, int wwarp, in
     v = warp_sum(v);
     if (lane == 0) arr[wwarp] = v;
     ds_consumer_sync();
-    float s = 0.f;
+    float s = arr[lane & 15];  // one read per lane, then a fixed shuffle tree over the 16 warp sums
 #pragma unroll
-    for (int w = 0; w < kDsConsumerWarps; w += 4) s += (arr[w] + arr[w + 1]) + (arr[w + 2] + arr[w + 3]);
+    for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     return s;
 }
 // LayerNorm statistics (two passes, as the CPU path) of a C-vector spread over the consumer threads (NGR groups of four each)
@@ -734,8 +740,6 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
         uint32_t J = 0;  // chunks of this CTA consumed so far (the producer numbers them the same way)
         DsPhaseCtx pc{};
         pc.vec_s = smem_u32(vec);
-        pc.best_val = -1e30f;
-        pc.best_idx = 0x7fffffff;
         unsigned bar_target = 0;
         bool ok = true, pending = false;
         const int r0o = S->er0[DSE_WO], nown = S->en[DSE_WO];  // this CTA's slice of the channels = its rows of att.output / ffn.value
@@ -822,7 +826,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     stage_scales(&Ly.e[DSE_W1], DSE_W1, 7);
                     if (!(ok = bar_wait())) break;
                     DS_STAMP(10);
-                    float4 xv[NG], lw[NG], lb[NG], pv[NG], mx[4][NG];
+                    float4 xv[NG], lw[NG], lb[NG], pv[NG];
 #pragma unroll
                     for (int gi = 0; gi < NG; ++gi) {
                         const int g4 = wtid + kDsConsumers * gi, k = g4 < C / 4 ? 4 * g4 : 0;
@@ -830,10 +834,6 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         pv[gi] = ds_ldcg4(tm_l + k);
                         lw[gi] = ds_ldg4(Ly.ln1_w + k);
                         lb[gi] = ds_ldg4(Ly.ln1_b + k);
-                        mx[0][gi] = ds_ldg4(Ly.x_r + k);
-                        mx[1][gi] = ds_ldg4(Ly.x_k + k);
-                        mx[2][gi] = ds_ldg4(Ly.x_v + k);
-                        mx[3][gi] = ds_ldg4(rmix + k);
                     }
                     if (l == 0) {
                         // x = LN0(embedding row): every CTA builds the whole vector itself
@@ -857,14 +857,16 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     float mean, inv;
                     ds_ln_stats<NG>(S, C, xv, wtid, mean, inv);
                     DS_STAMP(16);
-                    float4 cur[NG], del[NG];
+                    // the mix vectors are loaded here, behind the barriers of the statistics, so that they do not sit in registers next to the row
+                    float4 val[4][NG];
 #pragma unroll
                     for (int gi = 0; gi < NG; ++gi) {
-                        const int g4 = wtid + kDsConsumers * gi;
-                        cur[gi] = ds_ln_apply(xv[gi], mean, inv, lw[gi], lb[gi]);
-                        del[gi] = make_float4(pv[gi].x - cur[gi].x, pv[gi].y - cur[gi].y, pv[gi].z - cur[gi].z, pv[gi].w - cur[gi].w);
+                        const int g4 = wtid + kDsConsumers * gi, k = g4 < C / 4 ? 4 * g4 : 0;
+                        const float4 m0 = ds_ldg4(Ly.x_r + k), m1 = ds_ldg4(Ly.x_k + k), m2 = ds_ldg4(Ly.x_v + k), m3 = ds_ldg4(rmix + k);
+                        const float4 cur = ds_ln_apply(xv[gi], mean, inv, lw[gi], lb[gi]);
+                        const float4 del = make_float4(pv[gi].x - cur.x, pv[gi].y - cur.y, pv[gi].z - cur.z, pv[gi].w - cur.w);
                         if (g4 < C / 4) {
-                            const float xe[4] = {xv[gi].x, xv[gi].y, xv[gi].z, xv[gi].w}, ce[4] = {cur[gi].x, cur[gi].y, cur[gi].z, cur[gi].w};
+                            const float xe[4] = {xv[gi].x, xv[gi].y, xv[gi].z, xv[gi].w}, ce[4] = {cur.x, cur.y, cur.z, cur.w};
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const int o = 4 * g4 + e - r0o;
@@ -874,10 +876,14 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                                 }
                             }
                         }
+                        val[0][gi] = ds_mix4(cur, m0, del);
+                        val[1][gi] = ds_mix4(cur, m1, del);
+                        val[2][gi] = ds_mix4(cur, m2, del);
+                        val[3][gi] = ds_mix4(cur, m3, del);
                     }
                     DS_STAMP(17);
                     const bool i8[4] = {Ly.e[DSE_WR].is_i8 != 0, Ly.e[DSE_WK].is_i8 != 0, Ly.e[DSE_WV].is_i8 != 0, false};
-                    ds_emit<4, NG>(S, vec, C, i8, [&](int v, int gi) { return ds_mix4(cur[gi], mx[v][gi], del[gi]); }, wtid);
+                    ds_emit<4, NG>(S, vec, C, i8, [&](int v, int gi) { return val[v][gi]; }, wtid);
                 }
                 DS_STAMP(1);
 #ifdef RSV_DS_DEBUG
@@ -918,6 +924,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                                 S->hv[qq] = v2;
                         }
                         ds_consumer_sync();
+                        DS_STAMP(18);
                         // a row of a back-projection matrix times its rank-space vector: four threads split the rank dimension in contiguous quarters
                         auto dot_q = [&](const __half* W, int mid, const float* v) {
                             float a = 0.f;
@@ -1006,6 +1013,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                             S->red_a[wwarp] = ssp;
                             S->red_b[wwarp] = srp;
                         }
+                        DS_STAMP(19);
                         ds_consumer_sync();  // also: every warp is done with the three chunks
                         if (wtid == 0) {
                             mbar_arrive(&S->empty[iA % kDsBars]);
@@ -1043,6 +1051,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         y += __shfl_xor_sync(0xffffffffu, y, 4);
                         *reinterpret_cast<float4*>(srow) = make_float4(St[0], St[1], St[2], St[3]);
                         *reinterpret_cast<float4*>(srow + 4) = make_float4(St[4], St[5], St[6], St[7]);
+                        DS_STAMP(50);
                         const float gmean = ds_block_sum(oct == 0 ? y : 0.f, S->red_c, wwarp, lane) / 64.0f;
                         const float d = y - gmean;
                         const float var = ds_block_sum(oct == 0 ? d * d : 0.f, S->red_c + 16, wwarp, lane) / 64.0f + kGnEps;
@@ -1168,8 +1177,9 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 for (int gi = 0; gi < NG; ++gi) val[gi] = ds_ln_apply(xv[gi], mean, inv, lw[gi], lb[gi]);
                 const bool i8[1] = {P.head.is_i8 != 0};
                 ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return val[gi]; }, wtid);
-                pc.best_val = -1e30f;
-                pc.best_idx = 0x7fffffff;
+                S->best_val[wtid] = -1e30f;
+                S->best_idx[wtid] = 0x7fffffff;
+                __syncwarp();
 #ifdef RSV_DS_DEBUG
                 pc.dbg = nullptr;
 #endif
@@ -1177,8 +1187,9 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 J += (uint32_t)S->nch[5];
                 if (P.argmax_feed) {
                     // arg-max: lanes -> warp -> CTA -> grid; ties go to the smaller index
-                    float bv = pc.best_val;
-                    int bi = pc.best_idx;
+                    __syncwarp();
+                    float bv = S->best_val[wtid];
+                    int bi = S->best_idx[wtid];
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) {
                         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);

@@ -1641,6 +1641,7 @@ void Model::run_stream(State& st, int slot, int n_tokens, bool tok_from_list, bo
         fprintf(stderr, "[decode_stream_kernel, CTA 0, token 1, layer 1] us since the layer started\n");
         for (int i = 0; i < 15; ++i) fprintf(stderr, "  %-18s %.2f\n", names[order[i]], (h[order[i]] - h[0]) / 1e3);
         fprintf(stderr, "  P1 prologue: loads issued %.2f, statistics done %.2f, shift / slice done %.2f\n", (h[15] - h[0]) / 1e3, (h[16] - h[0]) / 1e3, (h[17] - h[0]) / 1e3);
+        fprintf(stderr, "  heads: vectors gathered %.2f, dot products done %.2f, state updated %.2f\n", (h[18] - h[0]) / 1e3, (h[19] - h[0]) / 1e3, (h[50] - h[0]) / 1e3);
         const char* ph[4] = {"P1", "P3", "P4", "P5"};
         for (int i = 0; i < 4; ++i)
             fprintf(stderr, "  %s rows, consumer warp 0: %lld chunks, %.2f us waiting for them, %.2f us multiplying\n", ph[i], h[20 + 4 * i + 2], h[20 + 4 * i] / 1e3, h[20 + 4 * i + 1] / 1e3);
