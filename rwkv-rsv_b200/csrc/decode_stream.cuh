@@ -10,7 +10,7 @@
 //   warp 0      producer.  Walks the fixed sequence of weight rows this CTA will ever need - token after token, layer
 //               after layer, phase after phase - and streams them with bulk asynchronous copies (cp.async.bulk, one
 //               per row, issued by the lanes in parallel) into a byte-granular ring in shared memory; a chunk = one
-//               tile of up to 16 rows x one piece (<= 1280 bytes) of K, one mbarrier per chunk.  It never waits on a
+//               tile of up to 16 rows x one piece (1280 bytes; 2560 for the head) of K, one mbarrier per chunk.  It never waits on a
 //               grid barrier, only on ring space, so HBM keeps streaming while the other warps synchronise:
 //               barriers cost latency, not bandwidth.
 //   warps 1-16  consumers.  Per phase they build the activation vector in shared memory (LayerNorm, token shift,
@@ -49,7 +49,8 @@ constexpr int kDsThreads = kDsConsumers + 32;        // + producer warp
 constexpr int kDsBars = 16;                          // chunks in flight (mbarrier pairs)
 constexpr int kDsTileRows = 16;                      // rows of a tile (the m dimension of the matrix instruction)
 constexpr int kDsPad = 16;                           // bytes between the rows of a tile in the ring, beyond the piece
-constexpr int kDsMaxPiece = 1280;                    // bytes of K per piece
+constexpr int kDsMaxPiece = 2560;                    // bytes of K per piece (the head's rows)
+constexpr int kDsLayerPiece = 1280;                  // bytes of K per piece of the layers' matrices (more chunks in flight; half of it was slower: the producer's time per chunk)
 constexpr int kDsMaxTiles = 64;                      // tiles of one phase per CTA
 constexpr int kDsPartBytes = 8 * 1024;               // per-piece partial sums of the tiles of one phase
 constexpr int kDsMaxRows = 512;                      // rows of one phase per CTA whose (scale, zero) are staged
@@ -109,6 +110,10 @@ struct DsParams {
     unsigned* grid_bar;
     int* status;
     int n_tokens, tok_from_list, argmax_feed;
+    const char* wstream;      // the layers' weights in consumption order: region (layer l, CTA c) at (l G + c) wslot
+    long long wslot;
+    const char* hstream;      // the head's rows in consumption order: region of CTA c at c hslot
+    long long hslot;
     int ring_bytes;  // shared-memory ring
     int vec_floats;  // operand area, in 4-byte elements: max(4 C, F)
     long long* dbg;  // optional time stamps (built with -DRSV_DS_DEBUG only)
@@ -157,6 +162,13 @@ __device__ __forceinline__ void ds_mbar_drain(uint64_t* bar, uint32_t parity) {
     for (uint32_t i = 0; i < (1u << 20); ++i)
         if (mbar_try_wait(bar, parity)) return;
 }
+#ifdef RSV_DS_DEBUG
+__device__ __forceinline__ long long ds_now0() {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#endif
 __device__ __forceinline__ float ds_pow2(int n) { return __int_as_float((n + 127) << 23); }
 __device__ __forceinline__ int ds_ceil_log2(float a) {
     const int bits = __float_as_int(a);
@@ -197,22 +209,38 @@ __device__ __forceinline__ long long ds_warp_sum_ll(long long v) {
     return (long long)hi * 65536 + (long long)lo;
 }
 
-// What the producer tells the consumer about a chunk.  Chunk j of the launch always uses barrier pair j mod 16 and, when it
-// carries weight rows, belongs to consumer warp j mod 16: the consumers do no placement arithmetic of their own.
-struct alignas(16) DsDesc {  // read with two 16-byte loads
-    int ring_off;    // byte offset of the chunk in the ring
-    int nr;          // rows in the chunk (<= 16)
-    int steps;       // 64-byte column steps (pairs of k steps) of the piece
-    int piece;       // which piece of the rows' K
-    uint32_t baddr;  // shared-memory address of the activation fragments of this piece (lane offset not included)
-    int part_off;    // byte offset of the tile's partial sums
-    int tile_idx;    // arrival counter of the tile
-    int e;           // matrix: DSE_* (DSE_COUNT: the head)
-    int row0;        // first row of the tile, counted from the CTA's first row of the matrix
-    int stage_off;   // first staged (scale, zero) of the matrix
-    int pad[2];
+// A chunk of weight rows: one tile (up to 16 rows of a matrix) x one piece of K.  The chunks a CTA consumes are the same in
+// every layer (its row ranges do not change), so they are tabulated once per launch; the weights themselves are stored a
+// second time in exactly this order (rows padded by 16 bytes, chunk after chunk), so that a chunk is ONE bulk copy.
+struct DsChunk {
+    int cb;            // bytes of the chunk, in the stream and in the ring: nr * stride
+    int nr_steps;      // rows (<= 16) | 64-byte column steps (pairs of k steps) of the piece << 16
+    int piece_np;      // which piece of the rows' K | pieces per row << 16
+    uint32_t baddr;    // shared-memory address of the activation fragments of this piece (lane offset not included)
+    int part_tile;     // byte offset of the tile's partial sums | arrival counter of the tile << 16
+    int e_flags_row0;  // matrix DSE_* (DSE_COUNT: the head) | flags << 8 (1: int8, 2: absent in layer 0) | first row of the tile (from the CTA's first row) << 16
+    int stage_off;     // first staged (scale, zero) of the matrix
+    int stride;        // bytes between the rows of the chunk: piece + 16
 };
-static_assert(sizeof(DsDesc) == 48 && offsetof(DsDesc, baddr) == 16, "DsDesc is read as two 16-byte halves");
+// What the producer tells the consumer about the chunk on a barrier pair: where it lies in the ring, and its table entry.
+// Chunk j of the launch always uses barrier pair j mod 16 and, when it carries weight rows, belongs to consumer warp j mod 16:
+// the consumers do no placement arithmetic of their own.
+struct alignas(16) DsDesc {  // read with three 16-byte loads
+    int ring_off;  // byte offset of the chunk in the ring
+    int pad[3];
+    DsChunk c;
+};
+static_assert(sizeof(DsChunk) == 32 && sizeof(DsDesc) == 48, "DsDesc is read as three 16-byte words");
+constexpr int kDsMaxChunks = 160;  // table entries per CTA: the chunks of a layer plus the head's
+enum { DSP_P1 = 0, DSP_P3, DSP_P4, DSP_P5, DSP_HEAD, DSP_COUNT };
+// The CTA's static plan (built once per launch).
+struct DsPlan {
+    int er0[DSE_COUNT + 1], en[DSE_COUNT + 1];  // rows [er0, er0 + en) of every matrix (DSE_*; last: the head) this CTA owns: the same in all layers
+    int rank_entry;                             // the rank projection whose rows this CTA owns (-1: none)
+    int ph0[DSP_COUNT], phn[DSP_COUNT];         // the phases' ranges in ctab
+    int phn_l0;                                 // chunks of phase 1 in layer 0 (no v-gate projection there)
+    DsChunk ctab[kDsMaxChunks];
+};
 
 // ---- shared-memory layout: [ring][operand area: vec_floats x 4 bytes][DsShared][rank-space vector] ----------------
 struct DsShared {
@@ -231,10 +259,8 @@ struct DsShared {
     float hv[10 * 64];                     // the 64-vectors of a head
     float best_val[kDsConsumers];          // per consumer thread: arg-max of the head rows it finished
     int best_idx[kDsConsumers];
-    int er0[DSE_COUNT + 1], en[DSE_COUNT + 1];  // rows [er0, er0 + en) of every matrix (DSE_*; last: the head) this CTA owns: the same in all layers
-    int rank_entry;                        // the rank projection whose rows this CTA owns (-1: none)
+    DsPlan plan;
     DsDesc desc[kDsBars];                  // what the chunk on barrier b is (written by the producer before it arms the barrier)
-    int nch[6];                            // chunks of this CTA per phase: phase 1 of layer 0, phase 1, 3, 4, 5, head
     int tile_cnt[kDsMaxTiles];             // pieces of a tile finished so far (zero between phases)
     long long part[kDsPartBytes / 8];      // per-piece partial sums: int64 (int8 matrices) or fp32 (fp16 matrices), 16 rows each
     DsLayer layer[2];                      // table of the current / next layer
@@ -249,7 +275,7 @@ struct DsShared {
 // Writes the vectors (getval(v, i) = the i-th of a thread's NGR groups of four consecutive elements of vector v) in that form; the scale exponent
 // goes to S->ex[v], for int8 the exact fixed-point sum to S->tsw[v].
 template <int NV, int NGR, class GetVal>
-__device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const bool (&i8)[NV], GetVal getval, int wtid) {
+__device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const bool (&i8)[NV], GetVal getval, int wtid, long long* dbg = nullptr) {
     const int wwarp = wtid >> 5, lane = wtid & 31, len4 = len >> 2;
     float am[NV];
 #pragma unroll
@@ -265,7 +291,13 @@ __device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const 
         for (int o = 16; o > 0; o >>= 1) am[v] = fmaxf(am[v], __shfl_xor_sync(0xffffffffu, am[v], o));
         if (lane == 0) S->red_c[v * 16 + wwarp] = am[v];
     }
+#ifdef RSV_DS_DEBUG
+    if (dbg && wtid == 0) dbg[0] = ds_now0();
+#endif
     ds_consumer_sync();
+#ifdef RSV_DS_DEBUG
+    if (dbg && wtid == 0) dbg[1] = ds_now0();
+#endif
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
         float a = S->red_c[v * 16 + (lane & 15)];
@@ -329,6 +361,9 @@ __device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const 
             }
         }
     }
+#ifdef RSV_DS_DEBUG
+    if (dbg && wtid == 0) dbg[2] = ds_now0();
+#endif
     ds_consumer_sync();
 }
 
@@ -379,14 +414,59 @@ __device__ __forceinline__ void ds_store(const DsParams& P, DsShared* S, const D
     }
 }
 
-// number of chunks the matrices ents[0 .. cnt) give this CTA (e0: index of ents[0] in the row-range cache)
-__device__ inline int ds_count_chunks(const DsShared* S, const DsEntry* ents, int e0, int cnt) {
-    int c = 0;
-    for (int i = 0; i < cnt; ++i) {
-        const int n = ents[i].M > 0 ? S->en[e0 + i] : 0;
-        c += ((n + kDsTileRows - 1) / kDsTileRows) * ents[i].npieces;
+// Builds the CTA's plan: row ranges (the one place where the rows are divided), then the chunk table phase by phase
+// (matrix after matrix, tile after tile, piece after piece).  `ents` = a layer's matrices (one with a v-gate projection),
+// vec_s = shared-memory address of the operand area (0 where the table is only used to lay out the weight stream).
+// Executed by one thread.  Returns false when the table would overflow.
+__host__ __device__ inline bool ds_build_plan(DsPlan& pl, const DsEntry* ents, const DsEntry& head, int cta, int G, uint32_t vec_s) {
+    for (int e = 0; e <= DSE_COUNT; ++e) {
+        int r0, n;
+        ds_rows_of(e == DSE_COUNT ? head : ents[e], cta, G, r0, n);
+        pl.er0[e] = r0;
+        pl.en[e] = n;
     }
-    return c;
+    pl.rank_entry = -1;
+    for (int e = DSE_W1; e <= DSE_V1; ++e)
+        if (pl.en[e] > 0 && pl.rank_entry < 0) pl.rank_entry = e;
+    const int first[DSP_COUNT] = {DSE_W1, DSE_WO, DSE_WFK, DSE_WFV, DSE_COUNT}, last[DSP_COUNT] = {DSE_WV, DSE_WO, DSE_WFK, DSE_WFV, DSE_COUNT};
+    int k = 0;
+    bool fits = true;
+    pl.phn_l0 = 0;
+    for (int ph = 0; ph < DSP_COUNT; ++ph) {
+        pl.ph0[ph] = k;
+        int tile = 0, part = 0, stage = 0;
+        for (int e = first[ph]; e <= last[ph]; ++e) {
+            const DsEntry& E = e == DSE_COUNT ? head : ents[e];
+            const int n = pl.en[e];
+            if (n <= 0) continue;
+            const bool i8 = E.is_i8 != 0;
+            const int steps = E.piece_bytes >> 6, klen = (i8 ? E.piece_bytes : (E.piece_bytes >> 1)) * E.npieces, bstep = (i8 ? 4 : 2) * 64, slot = i8 ? 8 : 4;
+            for (int row0 = 0; row0 < n; row0 += kDsTileRows) {
+                const int nr = n - row0 < kDsTileRows ? n - row0 : kDsTileRows;
+                for (int p = 0; p < E.npieces; ++p) {
+                    if (k >= kDsMaxChunks) {
+                        fits = false;
+                        continue;
+                    }
+                    DsChunk& c = pl.ctab[k++];
+                    c.stride = E.piece_bytes + kDsPad;
+                    c.cb = nr * c.stride;
+                    c.nr_steps = nr | (steps << 16);
+                    c.piece_np = p | (E.npieces << 16);
+                    c.baddr = vec_s + (uint32_t)E.xvec * (uint32_t)klen * 4u + (uint32_t)p * (uint32_t)steps * (uint32_t)bstep;
+                    c.part_tile = part | (tile << 16);
+                    c.e_flags_row0 = e | ((i8 ? 1 : 0) << 8) | ((e == DSE_V1 ? 2 : 0) << 8) | (row0 << 16);
+                    c.stage_off = stage;
+                    if (ph == DSP_P1 && e != DSE_V1) ++pl.phn_l0;
+                }
+                ++tile;
+                part += E.npieces * kDsTileRows * slot;
+            }
+            if (i8) stage += n;
+        }
+        pl.phn[ph] = k - pl.ph0[ph];
+    }
+    return fits;
 }
 
 // The weight rows of one phase: its chunks are J, J + 1, ..., J + n - 1 of the launch (matrix after matrix, tile after tile
@@ -405,15 +485,17 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
 #ifdef RSV_DS_DEBUG
         const long long tw1 = ds_now();
 #endif
-        const uint4 d0 = *reinterpret_cast<const uint4*>(&S->desc[wwarp].ring_off), d1 = *reinterpret_cast<const uint4*>(&S->desc[wwarp].baddr);
-        const int ring_off = (int)d0.x, nr = (int)d0.y, steps = (int)d0.z, piece = (int)d0.w, part_off = (int)d1.y, tile_idx = (int)d1.z, e = (int)d1.w;
-        const DsEntry& E = e == DSE_COUNT ? P.head : tab[e];
-        const bool i8 = E.is_i8 != 0;
-        const int np = E.npieces, stride = E.piece_bytes + kDsPad;
+        const uint4 d0 = reinterpret_cast<const uint4*>(&S->desc[wwarp])[0], d1 = reinterpret_cast<const uint4*>(&S->desc[wwarp])[1],
+                    d2 = reinterpret_cast<const uint4*>(&S->desc[wwarp])[2];
+        const int ring_off = (int)d0.x, nr = (int)(d1.y & 0xFFFFu), steps = (int)(d1.y >> 16), piece = (int)(d1.z & 0xFFFFu), np = (int)(d1.z >> 16);
+        const int part_off = (int)(d2.x & 0xFFFFu), tile_idx = (int)(d2.x >> 16), e = (int)(d2.y & 0xFFu), row0 = (int)(d2.y >> 16), stage_off = (int)d2.z,
+                  stride = (int)d2.w;
+        const bool i8 = (d2.y >> 8) & 1u;
+        const DsEntry& E = e == DSE_COUNT ? P.head : tab[e];  // only the warp that finishes the tile looks at it
         // B fragments of this lane: 16 bytes per two k steps at [k-step pair][operand row g][t]; columns beyond the operand's rows are zero
         const int brows = i8 ? 4 : 2, bstep = brows * 64, slot = i8 ? 8 : 4;
         const bool bcol_ok = g < brows;
-        uint32_t baddr = d1.x + (uint32_t)(g * 4 + t) * 16u;
+        uint32_t baddr = d1.w + (uint32_t)(g * 4 + t) * 16u;
         // ldmatrix row addresses: lanes 0-7 rows 0-7, 8-15 rows 8-15 (bytes 0-15 of a 32-byte k step), lanes 16-31 the same rows, bytes 16-31
         const int arow = min((lane & 7) + ((lane >> 3) & 1) * 8, nr - 1);
         uint32_t aaddr = ring_s + (uint32_t)ring_off + (uint32_t)arow * (uint32_t)stride + (uint32_t)(lane >> 4) * 16u;
@@ -457,7 +539,6 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
                 reinterpret_cast<float*>(part)[g + 8] = (c0[2] + c1[2]) + (c0[3] + c1[3]);
             }
         }
-        const int row0 = S->desc[wwarp].row0, stage_off = S->desc[wwarp].stage_off;  // read before the barrier pair is handed back
         __syncwarp();
         int old = 0;
         if (lane == 0) {
@@ -490,7 +571,7 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
             }
             if (lane < nr) {
                 const char* pt = reinterpret_cast<const char*>(S->part) + part_off;
-                const int r0 = S->er0[e];
+                const int r0 = S->plan.er0[e];
                 if (i8) {
                     long long Q = 0;
                     for (int q = 0; q < np; ++q) Q += reinterpret_cast<const volatile long long*>(pt + q * kDsTileRows * 8)[lane];
@@ -517,9 +598,16 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
     do {                                                                              \
         if (P.dbg && cta == 0 && wtid == 0 && t == 1 && l == 1) P.dbg[id] = ds_now(); \
     } while (0)
+#define DS_STAMP_ALL(k)                                                                       \
+    do {                                                                                      \
+        if (P.dbg && wtid == 0 && t == 1 && l == 1) P.dbg[256 + cta * 16 + (k)] = ds_now0(); \
+    } while (0)
 #else
 #define DS_STAMP(id) \
     do {             \
+    } while (0)
+#define DS_STAMP_ALL(k) \
+    do {                \
     } while (0)
 #endif
 
@@ -589,28 +677,12 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int i = threadIdx.x; i < kDsMaxTiles; i += kDsThreads) S->tile_cnt[i] = 0;
-    if (threadIdx.x <= DSE_COUNT) {
-        // layer 1's table when there is one: layer 0 has no v-gate projection, otherwise all layers split alike
-        const DsEntry& E = threadIdx.x == DSE_COUNT ? P.head : P.layers[P.L > 1 ? 1 : 0].e[threadIdx.x];
-        int r0, n;
-        ds_rows_of(E, cta, G, r0, n);
-        S->er0[threadIdx.x] = r0;
-        S->en[threadIdx.x] = n;
-    }
-    __syncthreads();
     if (threadIdx.x == 0) {
-        int re = -1;
-        for (int e = DSE_W1; e <= DSE_V1; ++e)
-            if (S->en[e] > 0 && re < 0) re = e;
-        S->rank_entry = re;
-        const DsEntry* e0 = P.layers[0].e;
-        const DsEntry* e1 = P.layers[P.L > 1 ? 1 : 0].e;
-        S->nch[0] = ds_count_chunks(S, e0 + DSE_W1, DSE_W1, 7);
-        S->nch[1] = ds_count_chunks(S, e1 + DSE_W1, DSE_W1, 7);
-        S->nch[2] = ds_count_chunks(S, e1 + DSE_WO, DSE_WO, 1);
-        S->nch[3] = ds_count_chunks(S, e1 + DSE_WFK, DSE_WFK, 1);
-        S->nch[4] = ds_count_chunks(S, e1 + DSE_WFV, DSE_WFV, 1);
-        S->nch[5] = ds_count_chunks(S, &P.head, DSE_COUNT, 1);
+        // layer 1's table when there is one: layer 0 has no v-gate projection, otherwise all layers split alike
+        if (!ds_build_plan(S->plan, P.layers[P.L > 1 ? 1 : 0].e, P.head, cta, G, smem_u32(vec))) {
+            atomicOr(P.status, 8);
+            S->abort_flag = 1;
+        }
     }
     __syncthreads();
 
@@ -621,9 +693,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
         int head = 0, used = 0;
         uint32_t j = 0, tail = 0;
         bool ok = true;
-        const uint32_t vec_s = smem_u32(vec);
         // Reserves `bytes` in the ring for chunk j (waiting for the oldest chunks to be released); the chunk starts at `head - bytes`.
-        // Lane 0 then writes the chunk's descriptor and arms the barrier (arm) before the copies are issued.
         auto reserve = [&](int bytes) -> bool {
             const bool wrap = head + bytes > R;  // the chunk does not fit behind the last one: it goes to the start of the ring
             const int waste = wrap ? R - head : 0;
@@ -634,100 +704,65 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 ++tail;
             }
             if (wrap) head = 0;
-            __syncwarp();
             if (lane == 0) S->alloc[j % kDsBars] = waste + bytes;
             used += waste + bytes;
             head += bytes;
             return true;
         };
-        auto arm = [&](int tx) {
-            if (lane == 0) mbar_expect_tx(&S->full[j % kDsBars], (uint32_t)tx);  // release: the descriptor is visible to whoever sees the barrier complete
+        // The weights lie in the stream in the order they are consumed: every chunk is one bulk copy from a running pointer.
+        const char* src = nullptr;
+        // table entry k: lanes 1-8 copy its eight words into the barrier pair's descriptor, lane 0 adds the ring offset, arms the
+        // barrier (a release: the descriptor is visible to whoever sees the barrier complete) and issues the copy
+        auto put_chunk = [&](int k) -> bool {
+            const int cb = S->plan.ctab[k].cb;
+            if (!reserve(cb)) return false;
+            DsDesc& D = S->desc[j % kDsBars];
+            if (lane >= 1 && lane <= 8) reinterpret_cast<int*>(&D.c)[lane - 1] = reinterpret_cast<const int*>(&S->plan.ctab[k])[lane - 1];
+            if (lane == 0) D.ring_off = head - cb;
             __syncwarp();
-        };
-        // running counters of the current phase (the consumer side finds them in the descriptors)
-        int ph_tile = 0, ph_part = 0, ph_stage = 0;
-        auto put_entry = [&](const DsEntry& E, int e) -> bool {
-            const int r0 = S->er0[e], n = E.M > 0 ? S->en[e] : 0;
-            if (n <= 0) return true;
-            const bool i8 = E.is_i8 != 0;
-            const int ntiles = (n + kDsTileRows - 1) / kDsTileRows, stride = E.piece_bytes + kDsPad, steps = E.piece_bytes >> 6;
-            const int klen = (i8 ? E.piece_bytes : (E.piece_bytes >> 1)) * E.npieces, bstep = (i8 ? 4 : 2) * 64, slot = i8 ? 8 : 4;
-            for (int ti = 0; ti < ntiles; ++ti) {
-                const int row0 = ti * kDsTileRows, nr = min(kDsTileRows, n - row0), cb = ds_chunk_bytes(E, nr);
-                for (int p = 0; p < E.npieces; ++p) {
-                    if (!reserve(cb)) return false;
-                    if (lane == 0) {
-                        DsDesc& D = S->desc[j % kDsBars];
-                        D.ring_off = head - cb;
-                        D.nr = nr;
-                        D.steps = steps;
-                        D.piece = p;
-                        D.baddr = vec_s + (uint32_t)E.xvec * (uint32_t)klen * 4u + (uint32_t)p * (uint32_t)steps * (uint32_t)bstep;
-                        D.part_off = ph_part;
-                        D.tile_idx = ph_tile;
-                        D.e = e;
-                        D.row0 = row0;
-                        D.stage_off = ph_stage;
-                    }
-                    arm(nr * E.piece_bytes);
-                    if (lane < nr)
-                        ds_bulk_load(ring_s + (uint32_t)(head - cb + lane * stride),
-                                     E.base + (size_t)(r0 + row0 + lane) * (size_t)E.row_stride + (size_t)p * E.piece_bytes, (uint32_t)E.piece_bytes,
-                                     &S->full[j % kDsBars], pol);
-                    ++j;
-                }
-                ++ph_tile;
-                ph_part += E.npieces * kDsTileRows * slot;
+            if (lane == 0) {
+                mbar_expect_tx(&S->full[j % kDsBars], (uint32_t)cb);
+                ds_bulk_load(ring_s + (uint32_t)(head - cb), src, (uint32_t)cb, &S->full[j % kDsBars], pol);
             }
-            if (i8) ph_stage += n;
+            src += cb;
+            ++j;
             return true;
         };
-        auto new_phase = [&]() { ph_tile = ph_part = ph_stage = 0; };
-        // a chunk that is not weight rows (a head's back-projection rows): one or two plain copies, only the offset is published
-        auto put_raw = [&](int bytes, const void* src0, int n0, const void* src1, int n1) -> bool {
+        // a chunk that is not weight rows (a head's back-projection rows): only the offset is published
+        auto put_raw = [&](int bytes) -> bool {
             if (!reserve(bytes)) return false;
-            if (lane == 0) S->desc[j % kDsBars].ring_off = head - bytes;
-            arm(bytes);
-            if (lane == 0 && n0) ds_bulk_load(ring_s + (uint32_t)(head - bytes), src0, (uint32_t)n0, &S->full[j % kDsBars], pol);
-            if (lane == 1 && n1) ds_bulk_load(ring_s + (uint32_t)(head - bytes + n0), src1, (uint32_t)n1, &S->full[j % kDsBars], pol);
+            if (lane == 0) {
+                S->desc[j % kDsBars].ring_off = head - bytes;
+                mbar_expect_tx(&S->full[j % kDsBars], (uint32_t)bytes);
+                ds_bulk_load(ring_s + (uint32_t)(head - bytes), src, (uint32_t)bytes, &S->full[j % kDsBars], pol);
+            }
+            src += bytes;
             ++j;
+            return true;
+        };
+        auto put_phase = [&](int ph, bool layer0) -> bool {
+            const int k0 = S->plan.ph0[ph], k1 = k0 + S->plan.phn[ph];
+            for (int k = k0; k < k1; ++k) {
+                if (layer0 && ((S->plan.ctab[k].e_flags_row0 >> 8) & 2)) continue;  // the v-gate projection does not exist in layer 0
+                if (!put_chunk(k)) return false;
+            }
             return true;
         };
         for (int t = 0; t < P.n_tokens && ok; ++t) {
             const bool do_head = P.argmax_feed || t == P.n_tokens - 1;
             for (int l = 0; l < P.L && ok; ++l) {
-                const DsLayer* Lg = P.layers + l;
-#ifdef RSV_DS_DEBUG
-                if (P.dbg && cta == 0 && lane == 0 && t == 1 && l == 1) P.dbg[40] = ds_now();
-#endif
-                new_phase();
-                for (int e = DSE_W1; e <= DSE_WV && ok; ++e) ok = put_entry(Lg->e[e], e);
-                if (!ok) break;
-#ifdef RSV_DS_DEBUG
-                if (P.dbg && cta == 0 && lane == 0 && t == 1 && l == 1) P.dbg[41] = ds_now();
-#endif
-                const int h = ds_head_of_cta(cta, l, P.H, G);
-                if (h >= 0) {
+                src = P.wstream + ((size_t)l * G + cta) * (size_t)P.wslot;
+                if (!(ok = put_phase(DSP_P1, l == 0))) break;
+                if (ds_head_of_cta(cta, l, P.H, G) >= 0) {
                     // chunk A: w2, a2 rows of the head; chunk B: v2 rows (layers > 0) and the first 32 g2 rows; chunk C: the other 32
                     const int vb = l > 0 ? 64 * P.vm * 2 : 0;
-                    if (!(ok = put_raw(hbA, Lg->w2 + (size_t)h * 64 * P.wm, 64 * P.wm * 2, Lg->a2 + (size_t)h * 64 * P.am, 64 * P.am * 2))) break;
-                    if (!(ok = put_raw(vb + hbC, Lg->v2 + (size_t)h * 64 * P.vm, vb, Lg->g2 + (size_t)h * 64 * P.gm, hbC))) break;
-                    if (!(ok = put_raw(hbC, Lg->g2 + ((size_t)h * 64 + 32) * P.gm, hbC, nullptr, 0))) break;
+                    if (!(ok = put_raw(hbA) && put_raw(vb + hbC) && put_raw(hbC))) break;
                 }
-#ifdef RSV_DS_DEBUG
-                if (P.dbg && cta == 0 && lane == 0 && t == 1 && l == 1) P.dbg[42] = ds_now();
-#endif
-                for (int e = DSE_WO; e <= DSE_WFV && ok; ++e) {
-                    new_phase();
-                    ok = put_entry(Lg->e[e], e);
-#ifdef RSV_DS_DEBUG
-                    if (P.dbg && cta == 0 && lane == 0 && t == 1 && l == 1) P.dbg[43 + e - DSE_WO] = ds_now();
-#endif
-                }
+                ok = put_phase(DSP_P3, false) && put_phase(DSP_P4, false) && put_phase(DSP_P5, false);
             }
             if (ok && do_head) {
-                new_phase();
-                ok = put_entry(P.head, DSE_COUNT);
+                src = P.hstream + (size_t)cta * (size_t)P.hslot;
+                ok = put_phase(DSP_HEAD, false);
             }
         }
         // copies still in flight must land before the CTA may exit (only after an abort: otherwise every chunk was consumed)
@@ -742,7 +777,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
         pc.vec_s = smem_u32(vec);
         unsigned bar_target = 0;
         bool ok = true, pending = false;
-        const int r0o = S->er0[DSE_WO], nown = S->en[DSE_WO];  // this CTA's slice of the channels = its rows of att.output / ffn.value
+        const int r0o = S->plan.er0[DSE_WO], nown = S->plan.en[DSE_WO];  // this CTA's slice of the channels = its rows of att.output / ffn.value
         uint32_t lt = 0;  // layers run so far: the table of the current layer sits in S->layer[lt & 1]
 
         auto stage_layer = [&](int l, uint32_t slot) {
@@ -789,7 +824,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
             int off = 0;
             for (int i = 0; i < cnt; ++i) {
                 const DsEntry& E = ents[i];
-                const int r0 = S->er0[e0 + i], n = E.M > 0 ? S->en[e0 + i] : 0;
+                const int r0 = S->plan.er0[e0 + i], n = E.M > 0 ? S->plan.en[e0 + i] : 0;
                 if (!E.is_i8 || n <= 0) continue;
                 for (int q = wtid; q < n && off + q < kDsMaxRows; q += kDsConsumers) {
                     S->ws[off + q] = __ldg(E.wscale + r0 + q);
@@ -819,13 +854,15 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 float* cm_l = P.cmix_x + (size_t)l * P.lay_x + (size_t)P.slot * C;
                 float* wkv_l = P.wkv + (size_t)l * P.lay_s + (size_t)P.slot * P.H * 4096;
                 DS_STAMP(0);
+                DS_STAMP_ALL(0);
                 // ================= phase 1: LN1 + token shift -> r, k, v, rank projections =================
                 {
-                    const int re = S->rank_entry;  // at most one: the rank projections' rows are split over disjoint groups of CTAs
+                    const int re = S->plan.rank_entry;  // at most one: the rank projections' rows are split over disjoint groups of CTAs
                     const float* rmix = re >= 0 ? Ly.e[re].mix : Ly.x_r;
                     stage_scales(&Ly.e[DSE_W1], DSE_W1, 7);
                     if (!(ok = bar_wait())) break;
                     DS_STAMP(10);
+                    DS_STAMP_ALL(10);
                     float4 xv[NG], lw[NG], lb[NG], pv[NG];
 #pragma unroll
                     for (int gi = 0; gi < NG; ++gi) {
@@ -883,18 +920,24 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     }
                     DS_STAMP(17);
                     const bool i8[4] = {Ly.e[DSE_WR].is_i8 != 0, Ly.e[DSE_WK].is_i8 != 0, Ly.e[DSE_WV].is_i8 != 0, false};
+#ifdef RSV_DS_DEBUG
+                    ds_emit<4, NG>(S, vec, C, i8, [&](int v, int gi) { return val[v][gi]; }, wtid, (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 52 : nullptr);
+#else
                     ds_emit<4, NG>(S, vec, C, i8, [&](int v, int gi) { return val[v][gi]; }, wtid);
+#endif
                 }
                 DS_STAMP(1);
+                DS_STAMP_ALL(1);
 #ifdef RSV_DS_DEBUG
                 pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 20 : nullptr;
 #endif
                 {
-                    const int nc = S->nch[l == 0 ? 0 : 1];
+                    const int nc = l == 0 ? S->plan.phn_l0 : S->plan.phn[DSP_P1];
                     if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, nc, pc, wwarp, lane))) break;
                     J += (uint32_t)nc;
                 }
                 DS_STAMP(2);
+                DS_STAMP_ALL(2);
                 bar_arrive();
 
                 // ================= phase 2: one CTA per head =================
@@ -1059,6 +1102,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     }
                 }
                 DS_STAMP(3);
+                DS_STAMP_ALL(3);
                 bar_arrive();
 
                 // ================= phase 3: att.output, x += =================
@@ -1066,6 +1110,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     stage_scales(&Ly.e[DSE_WO], DSE_WO, 1);
                     if (!(ok = bar_wait())) break;
                     DS_STAMP(12);
+                    DS_STAMP_ALL(12);
                     if (wtid < nown) tm_l[r0o + wtid] = S->ts_own[wtid];  // new time-mix shift state (every reader of the old one is past barrier 1)
                     float4 yv[NG];
 #pragma unroll
@@ -1076,13 +1121,15 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     const bool i8[1] = {Ly.e[DSE_WO].is_i8 != 0};
                     ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return yv[gi]; }, wtid);
                     DS_STAMP(4);
+                    DS_STAMP_ALL(4);
 #ifdef RSV_DS_DEBUG
                 pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 24 : nullptr;
 #endif
-                    if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, S->nch[2], pc, wwarp, lane))) break;
-                    J += (uint32_t)S->nch[2];
+                    if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, S->plan.phn[DSP_P3], pc, wwarp, lane))) break;
+                    J += (uint32_t)S->plan.phn[DSP_P3];
                 }
                 DS_STAMP(5);
+                DS_STAMP_ALL(5);
                 bar_arrive();
 
                 // ================= phase 4: LN2 + shift -> relu(ffn.key)^2 =================
@@ -1092,6 +1139,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     stage_layer(lnext, lt + 1);  // the table of the layer that runs next (the first one again after the last)
                     if (!(ok = bar_wait())) break;
                     DS_STAMP(13);
+                    DS_STAMP_ALL(13);
                     float4 lw[NG], lb[NG], pv[NG], mx[NG], xv[NG];
 #pragma unroll
                     for (int gi = 0; gi < NG; ++gi) {
@@ -1123,13 +1171,15 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     const bool i8[1] = {Ly.e[DSE_WFK].is_i8 != 0};
                     ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return val[gi]; }, wtid);
                     DS_STAMP(6);
+                    DS_STAMP_ALL(6);
 #ifdef RSV_DS_DEBUG
                 pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 28 : nullptr;
 #endif
-                    if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, S->nch[3], pc, wwarp, lane))) break;
-                    J += (uint32_t)S->nch[3];
+                    if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, S->plan.phn[DSP_P4], pc, wwarp, lane))) break;
+                    J += (uint32_t)S->plan.phn[DSP_P4];
                 }
                 DS_STAMP(7);
+                DS_STAMP_ALL(7);
                 bar_arrive();
 
                 // ================= phase 5: ffn.value (K = F = 4 C), x += =================
@@ -1137,6 +1187,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     stage_scales(&Ly.e[DSE_WFV], DSE_WFV, 1);
                     if (!(ok = bar_wait())) break;
                     DS_STAMP(14);
+                    DS_STAMP_ALL(14);
                     if (wtid < nown) cm_l[r0o + wtid] = S->cs_own[wtid];
                     float4 hv4[NG5];
 #pragma unroll
@@ -1147,13 +1198,15 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     const bool i8[1] = {Ly.e[DSE_WFV].is_i8 != 0};
                     ds_emit<1, NG5>(S, vec, 4 * C, i8, [&](int, int gi) { return hv4[gi]; }, wtid);
                     DS_STAMP(8);
+                    DS_STAMP_ALL(8);
 #ifdef RSV_DS_DEBUG
                 pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 32 : nullptr;
 #endif
-                    if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, S->nch[4], pc, wwarp, lane))) break;
-                    J += (uint32_t)S->nch[4];
+                    if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, S->plan.phn[DSP_P5], pc, wwarp, lane))) break;
+                    J += (uint32_t)S->plan.phn[DSP_P5];
                 }
                 DS_STAMP(9);
+                DS_STAMP_ALL(9);
                 bar_arrive();
             }
             if (!ok) break;
@@ -1183,8 +1236,8 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #ifdef RSV_DS_DEBUG
                 pc.dbg = nullptr;
 #endif
-                if (!(ok = ds_consume(P, S, nullptr, ring_s, J, S->nch[5], pc, wwarp, lane))) break;
-                J += (uint32_t)S->nch[5];
+                if (!(ok = ds_consume(P, S, nullptr, ring_s, J, S->plan.phn[DSP_HEAD], pc, wwarp, lane))) break;
+                J += (uint32_t)S->plan.phn[DSP_HEAD];
                 if (P.argmax_feed) {
                     // arg-max: lanes -> warp -> CTA -> grid; ties go to the smaller index
                     __syncwarp();
@@ -1259,6 +1312,61 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
     }
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicOr(P.status, 4);
+}
+
+// Writes the second copy of the weights: for every layer and every CTA of the decode kernel, the CTA's chunks in the order it
+// consumes them (rows padded to `stride`, the head's rows in a region of their own).  Launched once per model with the decode
+// kernel's grid size; CTA c lays out the region of decode CTA c.
+__global__ void __launch_bounds__(256) ds_retile_kernel(const __grid_constant__ DsParams P, char* wstream, long long wslot, char* hstream, long long hslot) {
+    __shared__ DsPlan pl;
+    const int G = gridDim.x, cta = blockIdx.x;
+    if (threadIdx.x == 0) ds_build_plan(pl, P.layers[P.L > 1 ? 1 : 0].e, P.head, cta, G, 0u);
+    __syncthreads();
+    auto copy_chunk = [&](const DsEntry& E, const DsChunk& c, char* dst) {
+        const int nr = c.nr_steps & 0xFFFF, piece = c.piece_np & 0xFFFF, e = c.e_flags_row0 & 0xFF, row0 = c.e_flags_row0 >> 16, per_row = c.stride >> 4;
+        const char* src = E.base + (size_t)(pl.er0[e] + row0) * (size_t)E.row_stride + (size_t)piece * E.piece_bytes;
+        for (int i = threadIdx.x; i < nr * per_row; i += blockDim.x) {
+            const int row = i / per_row, col = (i % per_row) * 16;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (col < E.piece_bytes) v = *reinterpret_cast<const uint4*>(src + (size_t)row * E.row_stride + col);
+            *reinterpret_cast<uint4*>(dst + (size_t)row * c.stride + col) = v;
+        }
+    };
+    auto copy_raw = [&](const void* src, int bytes, char* dst) {
+        for (int i = threadIdx.x * 16; i < bytes; i += blockDim.x * 16) *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>((const char*)src + i);
+    };
+    for (int l = 0; l < P.L; ++l) {
+        const DsLayer& Ly = P.layers[l];
+        char* dst = wstream + ((size_t)l * G + cta) * (size_t)wslot;
+        for (int ph = DSP_P1; ph <= DSP_P5; ++ph) {
+            for (int k = pl.ph0[ph]; k < pl.ph0[ph] + pl.phn[ph]; ++k) {
+                const DsChunk& c = pl.ctab[k];
+                if (l == 0 && ((c.e_flags_row0 >> 8) & 2)) continue;
+                copy_chunk(Ly.e[c.e_flags_row0 & 0xFF], c, dst);
+                dst += c.cb;
+            }
+            if (ph == DSP_P1) {
+                const int h = ds_head_of_cta(cta, l, P.H, G);
+                if (h >= 0) {  // the head's back-projection rows: w2, a2 | v2 (layers > 0), first 32 g2 rows | the other 32 g2 rows
+                    copy_raw(Ly.w2 + (size_t)h * 64 * P.wm, 64 * P.wm * 2, dst);
+                    dst += 64 * P.wm * 2;
+                    copy_raw(Ly.a2 + (size_t)h * 64 * P.am, 64 * P.am * 2, dst);
+                    dst += 64 * P.am * 2;
+                    if (l > 0) {
+                        copy_raw(Ly.v2 + (size_t)h * 64 * P.vm, 64 * P.vm * 2, dst);
+                        dst += 64 * P.vm * 2;
+                    }
+                    copy_raw(Ly.g2 + (size_t)h * 64 * P.gm, 64 * P.gm * 2, dst);
+                    dst += 64 * P.gm * 2;
+                }
+            }
+        }
+    }
+    char* dst = hstream + (size_t)cta * (size_t)hslot;
+    for (int k = pl.ph0[DSP_HEAD]; k < pl.ph0[DSP_HEAD] + pl.phn[DSP_HEAD]; ++k) {
+        copy_chunk(P.head, pl.ctab[k], dst);
+        dst += pl.ctab[k].cb;
+    }
 }
 
 }  // namespace rsv

@@ -438,7 +438,7 @@ Model::~Model() {
     for (void* p : {pctx.d_layers, pctx.d_maps, (void*)pctx.x, (void*)pctx.yg, (void*)pctx.vfirst, (void*)pctx.cand_val, (void*)pctx.cand_idx, (void*)pctx.rkv, (void*)pctx.mid, (void*)pctx.hbuf,
                     (void*)pctx.grid_bar})
         if (p) cudaFree(p);
-    for (void* p : {sctx.d_layers, (void*)sctx.x, (void*)sctx.yg, (void*)sctx.vfirst, (void*)sctx.rkv, (void*)sctx.mid, (void*)sctx.hbuf, (void*)sctx.cand_val,
+    for (void* p : {sctx.d_layers, sctx.wstream, sctx.hstream, (void*)sctx.x, (void*)sctx.yg, (void*)sctx.vfirst, (void*)sctx.rkv, (void*)sctx.mid, (void*)sctx.hbuf, (void*)sctx.cand_val,
                     (void*)sctx.cand_idx, (void*)sctx.grid_bar, (void*)sctx.dbg})
         if (p) cudaFree(p);
     for (int i = 0; i < 5; ++i) {
@@ -1371,13 +1371,13 @@ void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bo
 // ------------------------------------------------------------------------------------------------
 namespace {
 
-DsEntry make_entry(const LinearW& W, int G, int xvec, int out, int out_off, const float* mix) {
+DsEntry make_entry(const LinearW& W, int G, int xvec, int out, int out_off, const float* mix, int max_piece = kDsMaxPiece) {
     DsEntry e;
     memset(&e, 0, sizeof(e));
     const bool i8 = W.wtype == W_INT8;
     const int row_bytes = i8 ? W.K : 2 * W.K;
     // pieces of at most kDsMaxPiece bytes, each a multiple of 128 bytes
-    int np = (row_bytes + kDsMaxPiece - 1) / kDsMaxPiece;
+    int np = (row_bytes + max_piece - 1) / max_piece;
     while (np <= row_bytes / 128 && row_bytes % (np * 128)) ++np;
     e.base = (const char*)W.w;
     e.wscale = W.wscale;
@@ -1489,6 +1489,7 @@ bool Model::stream_available() {
         return fail(e.what());
     }
     // per-layer tables
+    const int piece_layers = kDsLayerPiece;  // the head's rows (many tiles, nothing to overlap with) take the larger kDsMaxPiece
     std::vector<DsLayer> dl((size_t)L);
     for (int l = 0; l < L; ++l) {
         const LayerW& Lw = layers[l];
@@ -1518,12 +1519,12 @@ bool Model::stream_available() {
         if (l == 0) d.e[DSE_V1].M = 0;  // layer 0 has no v gate
         for (const DsEntry* e : {&d.e[DSE_W1], &d.e[DSE_A1], &d.e[DSE_G1], &d.e[DSE_V1]})
             if (e->is_i8 || e->npieces * e->piece_bytes != 2 * C) return fail("rank projections must be fp16 [mid, n_embd]");
-        d.e[DSE_WR] = make_entry(Lw.Wr, G, 0, DSO_R, 0, nullptr);
-        d.e[DSE_WK] = make_entry(Lw.Wk, G, 1, DSO_K, 0, nullptr);
-        d.e[DSE_WV] = make_entry(Lw.Wv, G, 2, DSO_V, 0, nullptr);
-        d.e[DSE_WO] = make_entry(Lw.Wo, G, 0, DSO_XADD, 0, nullptr);
-        d.e[DSE_WFK] = make_entry(Lw.Wfk, G, 0, DSO_H, 0, nullptr);
-        d.e[DSE_WFV] = make_entry(Lw.Wfv, G, 0, DSO_XADD, 0, nullptr);
+        d.e[DSE_WR] = make_entry(Lw.Wr, G, 0, DSO_R, 0, nullptr, piece_layers);
+        d.e[DSE_WK] = make_entry(Lw.Wk, G, 1, DSO_K, 0, nullptr, piece_layers);
+        d.e[DSE_WV] = make_entry(Lw.Wv, G, 2, DSO_V, 0, nullptr, piece_layers);
+        d.e[DSE_WO] = make_entry(Lw.Wo, G, 0, DSO_XADD, 0, nullptr, piece_layers);
+        d.e[DSE_WFK] = make_entry(Lw.Wfk, G, 0, DSO_H, 0, nullptr, piece_layers);
+        d.e[DSE_WFV] = make_entry(Lw.Wfv, G, 0, DSO_XADD, 0, nullptr, piece_layers);
         // r, k, v: the CTAs that get an extra row of one matrix are not those of the next (att.output and ffn.value keep
         // offset 0: their rows are the CTA's slice of x)
         d.e[DSE_WK].cta0 = G / 3;
@@ -1553,6 +1554,45 @@ bool Model::stream_available() {
     }
     RSV_CUDA(cudaMalloc(&sc.d_layers, dl.size() * sizeof(DsLayer)));
     RSV_CUDA(cudaMemcpy(sc.d_layers, dl.data(), dl.size() * sizeof(DsLayer), cudaMemcpyHostToDevice));
+    {
+        // second copy of the weights in the order the kernel consumes them (a chunk = one bulk copy): region sizes = the largest CTA's
+        long long wslot = 0, hslot = 0;
+        DsEntry head_e = make_entry(head, G, 0, DSO_LOGITS, 0, nullptr);
+        auto plan = std::make_unique<DsPlan>();
+        for (int c = 0; c < G; ++c) {
+            if (!ds_build_plan(*plan, dl[L > 1 ? 1 : 0].e, head_e, c, G, 0u)) return fail("too many chunks per SM for the chunk table");
+            long long rows = 0, hd = 0;
+            for (int ph = DSP_P1; ph <= DSP_P5; ++ph)
+                for (int k = plan->ph0[ph]; k < plan->ph0[ph] + plan->phn[ph]; ++k) rows += plan->ctab[k].cb;
+            for (int k = plan->ph0[DSP_HEAD]; k < plan->ph0[DSP_HEAD] + plan->phn[DSP_HEAD]; ++k) hd += plan->ctab[k].cb;
+            wslot = std::max(wslot, rows);
+            hslot = std::max(hslot, hd);
+        }
+        wslot += 128LL * (cfg.w_mid + cfg.a_mid + cfg.v_mid + cfg.g_mid);  // a head's back-projection rows
+        wslot = (wslot + 255) / 256 * 256;
+        hslot = (hslot + 255) / 256 * 256;
+        sc.wslot = wslot;
+        sc.hslot = hslot;
+        RSV_CUDA(cudaMalloc(&sc.wstream, (size_t)wslot * G * L));
+        RSV_CUDA(cudaMalloc(&sc.hstream, (size_t)hslot * G));
+        DsParams Q;
+        memset(&Q, 0, sizeof(Q));
+        Q.layers = (const DsLayer*)sc.d_layers;
+        Q.head = head_e;
+        Q.L = L;
+        Q.H = H;
+        Q.wm = cfg.w_mid;
+        Q.am = cfg.a_mid;
+        Q.vm = cfg.v_mid;
+        Q.gm = cfg.g_mid;
+        ds_retile_kernel<<<G, 256, 0, stream>>>(Q, (char*)sc.wstream, wslot, (char*)sc.hstream, hslot);
+        check_launch("ds_retile");
+        RSV_CUDA(cudaStreamSynchronize(stream));
+        if (const char* e = getenv("RSV_VERBOSE"))
+            if (*e && *e != '0')
+                fprintf(stderr, "[rsv] weight-streaming decode kernel: %.2f GB second copy of the weights in consumption order (%lld bytes per layer and SM)\n",
+                        ((double)wslot * G * L + (double)hslot * G) / 1e9, wslot);
+    }
     RSV_CUDA(cudaMalloc(&sc.x, (size_t)C * 4));
     RSV_CUDA(cudaMalloc(&sc.yg, (size_t)C * 4));
     RSV_CUDA(cudaMalloc(&sc.vfirst, (size_t)C * 4));
@@ -1565,8 +1605,8 @@ bool Model::stream_available() {
     RSV_CUDA(cudaMemset(sc.mid, 0, (size_t)std::max(cfg.mids(), 1) * 4));
     RSV_CUDA(cudaMemset(sc.vfirst, 0, (size_t)C * 4));
 #ifdef RSV_DS_DEBUG
-    RSV_CUDA(cudaMalloc(&sc.dbg, 256 * sizeof(long long)));
-    RSV_CUDA(cudaMemset(sc.dbg, 0, 256 * sizeof(long long)));
+    RSV_CUDA(cudaMalloc(&sc.dbg, (256 + 16 * 256) * sizeof(long long)));
+    RSV_CUDA(cudaMemset(sc.dbg, 0, (256 + 16 * 256) * sizeof(long long)));
 #endif
     P.layers = (const DsLayer*)sc.d_layers;
     P.head = make_entry(head, G, 0, DSO_LOGITS, 0, nullptr);
@@ -1594,6 +1634,10 @@ bool Model::stream_available() {
     P.cand_val = sc.cand_val;
     P.cand_idx = sc.cand_idx;
     P.grid_bar = sc.grid_bar;
+    P.wstream = (const char*)sc.wstream;
+    P.wslot = sc.wslot;
+    P.hstream = (const char*)sc.hstream;
+    P.hslot = sc.hslot;
     P.ring_bytes = ring_bytes;
     P.vec_floats = vec_floats;
     P.dbg = sc.dbg;
@@ -1632,7 +1676,7 @@ void Model::run_stream(State& st, int slot, int n_tokens, bool tok_from_list, bo
     LAUNCH(*this, "decode_stream") { dispatch_stream(sc.kl, P, sc.grid, sc.smem, stream, false); }
 #ifdef RSV_DS_DEBUG
     if (sc.dbg && n_tokens >= 2) {
-        long long h[256];
+        static long long h[256 + 16 * 256];
         RSV_CUDA(cudaStreamSynchronize(stream));
         RSV_CUDA(cudaMemcpy(h, sc.dbg, sizeof(h), cudaMemcpyDeviceToHost));
         const int order[15] = {0, 10, 1, 2, 11, 3, 12, 4, 5, 13, 6, 7, 14, 8, 9};
@@ -1641,6 +1685,10 @@ void Model::run_stream(State& st, int slot, int n_tokens, bool tok_from_list, bo
         fprintf(stderr, "[decode_stream_kernel, CTA 0, token 1, layer 1] us since the layer started\n");
         for (int i = 0; i < 15; ++i) fprintf(stderr, "  %-18s %.2f\n", names[order[i]], (h[order[i]] - h[0]) / 1e3);
         fprintf(stderr, "  P1 prologue: loads issued %.2f, statistics done %.2f, shift / slice done %.2f\n", (h[15] - h[0]) / 1e3, (h[16] - h[0]) / 1e3, (h[17] - h[0]) / 1e3);
+        fprintf(stderr, "  producer, first chunks of the launch (ring empty), us between issues:");
+        for (int i = 1; i < 8; ++i) fprintf(stderr, " %.2f", (h[200 + i] - h[200 + i - 1]) / 1e3);
+        fprintf(stderr, "\n");
+        fprintf(stderr, "  P1 operands: magnitudes %.2f, barrier %.2f, digits written %.2f\n", (h[52] - h[0]) / 1e3, (h[53] - h[0]) / 1e3, (h[54] - h[0]) / 1e3);
         fprintf(stderr, "  heads: vectors gathered %.2f, dot products done %.2f, state updated %.2f\n", (h[18] - h[0]) / 1e3, (h[19] - h[0]) / 1e3, (h[50] - h[0]) / 1e3);
         const char* ph[4] = {"P1", "P3", "P4", "P5"};
         for (int i = 0; i < 4; ++i)
@@ -1650,7 +1698,30 @@ void Model::run_stream(State& st, int slot, int n_tokens, bool tok_from_list, bo
         for (int w = 0; w < 16; ++w)
             fprintf(stderr, "  P1 warp %2d: last chunk wait %.2f .. %.2f, multiplied %.2f, tile finished %.2f\n", w, (h[64 + 4 * w] - h[0]) / 1e3, (h[65 + 4 * w] - h[0]) / 1e3,
                     (h[66 + 4 * w] - h[0]) / 1e3, h[67 + 4 * w] ? (h[67 + 4 * w] - h[0]) / 1e3 : 0.0);
-        RSV_CUDA(cudaMemset(sc.dbg, 0, 256 * sizeof(long long)));
+        {
+            const int ord[15] = {0, 10, 1, 2, 3, 12, 4, 5, 13, 6, 7, 14, 8, 9, -1};
+            const char* nm[15] = {"layer start", "P1 operands", "P1 rows done", "heads done", "P3 operands", "P3 rows done", "P4 operands", "P4 rows done", "P5 operands", "P5 rows done",
+                                  "barrier 5 passed", "", "barrier 2 passed", "barrier 3 passed", "barrier 4 passed"};
+            fprintf(stderr, "  all CTAs (us since CTA 0's layer start): min / mean / max (CTA)\n");
+            for (int i = 0; ord[i] >= 0; ++i) {
+                const int k = ord[i];
+                long long mn = 1LL << 62, mx = 0, sum = 0;
+                int amx = -1, n = 0;
+                for (int c = 0; c < sc.grid && c < 256; ++c) {
+                    const long long v = h[256 + c * 16 + k];
+                    if (!v) continue;
+                    ++n;
+                    sum += v - h[0];
+                    mn = std::min(mn, v);
+                    if (v > mx) {
+                        mx = v;
+                        amx = c;
+                    }
+                }
+                if (n) fprintf(stderr, "    %-18s %7.2f %7.2f %7.2f (%d)\n", nm[k], (mn - h[0]) / 1e3, sum / 1e3 / n, (mx - h[0]) / 1e3, amx);
+            }
+        }
+        RSV_CUDA(cudaMemset(sc.dbg, 0, (256 + 16 * 256) * sizeof(long long)));
     }
 #endif
 }

@@ -99,6 +99,8 @@ struct StreamCtx {
     bool tried = false, ok = false;
     std::string why;           // reason when the model cannot take this path
     void* d_layers = nullptr;  // DsLayer[L]
+    void *wstream = nullptr, *hstream = nullptr;  // second copy of the weights in the order the kernel consumes them
+    long long wslot = 0, hslot = 0;
     float *x = nullptr, *yg = nullptr, *vfirst = nullptr, *rkv = nullptr, *mid = nullptr, *hbuf = nullptr, *cand_val = nullptr;
     int* cand_idx = nullptr;
     unsigned* grid_bar = nullptr;
