@@ -95,7 +95,7 @@ void ensure_tok_list(Model& m, size_t n) {
 void decode_tokens(Model& m, State& st, const uint32_t* tokens, int64_t n) {
     need(st.model == &m, "state belongs to a different model");
     need(st.cap == 1, "this call needs a single-session state (batch == 1)");
-    need(n >= 1, "empty token list");
+    need(n >= 1 && n <= 0x7fffffff, "token count must be between 1 and 2^31 - 1");
     check_tokens(m, tokens, n);
     RSV_CUDA(cudaSetDevice(m.device));
     if (!m.prof_on && m.persistent_available(1)) {
@@ -158,7 +158,7 @@ void pack_sampler_row(float* row, const rsv_sampler_params& sp, uint32_t seed, u
 
 std::unique_ptr<rsv_ticket> selfloop_submit(Model& m, State& st, const uint32_t* seeds, int64_t batch, int64_t n, const rsv_sampler_params* sp) {
     need(st.model == &m, "state belongs to a different model");
-    need(batch >= 1 && n >= 1, "batch and n must be >= 1");
+    need(batch >= 1 && n >= 1 && batch <= 0x7fffffff && n <= 0x7fffffff, "batch and n must be between 1 and 2^31 - 1");
     need(st.cap == batch, "state batch differs from the number of seeds");  // src/gpu_model.rs:1649-1657
     check_tokens(m, seeds, batch);
     RSV_CUDA(cudaSetDevice(m.device));
@@ -245,9 +245,10 @@ std::unique_ptr<rsv_ticket> selfloop_submit(Model& m, State& st, const uint32_t*
 }
 
 void selfloop_collect(rsv_ticket* tk, uint32_t* out, int64_t len) {
+    // a wrong length leaves the ticket (and its queued results) with the caller, who may call again
+    need(len == tk->t.batch * tk->t.n, "output length must be batch * n");
     std::unique_ptr<rsv_ticket> own(tk);
     Ticket& t = tk->t;
-    need(len == t.batch * t.n, "output length must be batch * n");
     Model& m = *t.model;
     RSV_CUDA(cudaSetDevice(m.device));
     RSV_CUDA(cudaMemcpyAsync(out, t.seq, (size_t)len * sizeof(uint32_t), cudaMemcpyDeviceToHost, m.stream));
@@ -442,6 +443,7 @@ int rsv_infer_sample(rsv_model* mh, rsv_state* s, const uint32_t* tokens, int64_
                      int64_t nh, uint32_t* token_out) {
     return guarded([&] {
         need(mh && s && tokens && sp && token_out, "null argument");
+        need(nh >= 0 && nh <= 0x7fffffff, "history length must be between 0 and 2^31 - 1");
         need(nh == 0 || history, "history is null but nh > 0");
         Model& m = *mh->m;
         decode_tokens(m, s->s, tokens, n);
@@ -478,7 +480,8 @@ int rsv_prefill_batch(rsv_model* mh, rsv_state* sh, const uint32_t* flat, const 
         Model& m = *mh->m;
         State& st = sh->s;
         need(st.model == &m, "state belongs to a different model");
-        need(batch >= 1, "forward_seq_batch: empty batch");                             // src/gpu_model.rs:921-923
+        need(batch >= 1 && batch <= 0x7fffffff, "forward_seq_batch: empty batch");      // src/gpu_model.rs:921-923
+        need(t_pad >= 1 && t_pad <= 0x7fffffff, "forward_seq_batch: t_pad must be >= 1");
         need(st.cap == batch, "forward_seq_batch: state batch differs from the prompts");  // :924-931
         std::vector<int64_t> len(batch), done(batch, 0);
         for (int64_t b = 0; b < batch; ++b) {
@@ -620,6 +623,7 @@ int rsv_op_linear(int device, int path, int wtype, const void* w, const uint32_t
         need(w && x && y, "null argument");
         need(wtype == W_F16 || (wtype == W_INT8 && sz), "op_linear: wtype must be 0 (fp16) or 1 (int8, with sz)");
         need(path == 0 || path == 1, "op_linear: path must be 0 (SIMT) or 1 (tensor core)");
+        need(M >= 1 && K >= 1 && R >= 1 && M <= 0x7fffffff && K <= 0x7fffffff && R <= 0x7fffffff, "op_linear: M, K and R must be between 1 and 2^31 - 1");
         select_device(device);
         auto m = Model::create_bare(device);
         engine_op_linear(*m, path, wtype, w, sz, (int)M, (int)K, x, (int)R, y);

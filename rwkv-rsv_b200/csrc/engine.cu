@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <cstring>
+#include <mutex>
 
 #include "kernels.cuh"
 #include "safetensors.hpp"
@@ -1232,6 +1233,7 @@ bool Model::persistent_available(int nb) {
         RSV_CUDA(cudaMalloc(&pc.region_data[i], runs * kDpN * 128 * 4));
         RSV_CUDA(cudaMalloc(&pc.region_meta[i], runs * kDpWarps * sizeof(DpRunMeta)));
         RSV_CUDA(cudaMalloc(&pc.region_cnt[i], (size_t)tiles[i] * kDpWarps * sizeof(int)));
+        pc.region_cnt_bytes[i] = (size_t)tiles[i] * kDpWarps * sizeof(int);
         RSV_CUDA(cudaMemset(pc.region_data[i], 0, runs * kDpN * 128 * 4));
         RSV_CUDA(cudaMemset(pc.region_meta[i], 0, runs * kDpWarps * sizeof(DpRunMeta)));
         RSV_CUDA(cudaMemset(pc.region_cnt[i], 0, (size_t)tiles[i] * kDpWarps * sizeof(int)));
@@ -1732,6 +1734,12 @@ void Model::check_status() {
     RSV_CUDA(cudaStreamSynchronize(stream));
     if (s) {
         RSV_CUDA(cudaMemsetAsync(ws.status, 0, sizeof(int), stream));
+        if (s & (2 | 4)) {
+            // a kernel that gave up on a wait may have left arrival counters non-zero: the next launch must start from zero
+            if (ws.tc_cnt) RSV_CUDA(cudaMemsetAsync(ws.tc_cnt, 0, (size_t)kTcMaxSplit * kTcEpiWarps * sizeof(int), stream));
+            for (int i = 0; i < 5; ++i)
+                if (pctx.region_cnt[i]) RSV_CUDA(cudaMemsetAsync(pctx.region_cnt[i], 0, pctx.region_cnt_bytes[i], stream));
+        }
         if (s & 16) throw std::runtime_error("WKV kernel gave up waiting for a staged state (device status bit 4)");
         if (s & 8) throw std::runtime_error("persistent decode kernel: schedule tables too small for this shape (device status bit 3)");
         if (s & 4) throw std::runtime_error("persistent decode kernel gave up waiting on a barrier (device status bit 2)");
@@ -1869,6 +1877,7 @@ struct StaticScratch {
 };
 constexpr int kMaxDevices = 64;
 StaticScratch g_static_scratch[kMaxDevices];
+std::once_flag g_static_once[kMaxDevices];
 }  // namespace
 
 void set_last_error(const std::string& msg);  // defined with the C ABI
@@ -1884,22 +1893,24 @@ extern "C" int rsv_op_sample_static(int device, void* stream, const float* logit
         if (!logits_dev || !sampler8_dev || !out_dev) throw std::runtime_error("sample_static: null argument");
         if (rows < 1 || V < 1) throw std::runtime_error("sample_static: empty input");
         if (hist_stride < 0 || (hist_stride > 0 && !hist_dev)) throw std::runtime_error("sample_static: history is null but hist_stride > 0");
+        if (hist_stride > 0x7fffffffLL || rows > 0x7fffffffLL || V > 0x7fffffffLL) throw std::runtime_error("sample_static: rows, V and hist_stride must fit in 31 bits");
         if ((uint64_t)rows * (uint64_t)V > kStaticSampleMaxElems)
             throw std::runtime_error("sample_static: rows * V = " + std::to_string((uint64_t)rows * (uint64_t)V) + " exceeds the static work area of " +
                                      std::to_string(kStaticSampleMaxElems) + " elements; use rsv_op_sample or fewer rows per call");
         if (device < 0 || device >= kMaxDevices) throw std::runtime_error("sample_static: device index out of range");
         RSV_CUDA(cudaSetDevice(device));
         StaticScratch& sc = g_static_scratch[device];
-        if (!sc.temp) {
-            // first call on this device: resolve the device addresses of the static arrays (in host code their
-            // names are only handles, not device pointers)
+        // first call on this device: resolve the device addresses of the static arrays (in host code their names are only
+        // handles, not device pointers).  Once per device, also when several host threads make their first call together.
+        std::call_once(g_static_once[device], [&] {
             float* t = nullptr;
             uint32_t* c = nullptr;
-            RSV_CUDA(cudaGetSymbolAddress((void**)&t, g_static_sample_temp));
-            RSV_CUDA(cudaGetSymbolAddress((void**)&c, g_static_sample_cnt));
-            sc.cnt = c;
-            sc.temp = t;
-        }
+            if (cudaGetSymbolAddress((void**)&t, g_static_sample_temp) == cudaSuccess && cudaGetSymbolAddress((void**)&c, g_static_sample_cnt) == cudaSuccess) {
+                sc.cnt = c;
+                sc.temp = t;
+            }
+        });
+        if (!sc.temp || !sc.cnt) throw CudaError("sample_static: cudaGetSymbolAddress failed for the static work area");
         sample_rows_kernel<<<(unsigned)rows, kSampleThreads, 0, (cudaStream_t)stream>>>(logits_dev, (int)V, sampler8_dev, hist_stride ? hist_dev : nullptr,
                                                                                         (int)hist_stride, nullptr, sc.temp, sc.cnt, out_dev, nullptr,
                                                                                         nullptr, 0, nullptr);

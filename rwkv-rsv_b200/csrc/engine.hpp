@@ -85,6 +85,7 @@ struct PersistentCtx {
     void* region_data[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     void* region_meta[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     int* region_cnt[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    size_t region_cnt_bytes[5] = {0, 0, 0, 0, 0};
     float *rkv = nullptr, *mid = nullptr, *hbuf = nullptr;
     int region_pmax[5] = {1, 1, 1, 1, 1};
     int grid = 0, nstages = 0, btiles = 0;

@@ -246,6 +246,26 @@ private:
                 if (b < 0 || e < b || (size_t)e > data_len) throw std::runtime_error("safetensors: data_offsets out of range for " + name);
                 t.data = data + b;
                 t.nbytes = (size_t)(e - b);
+                // the byte range must be exactly shape x element size (the reference's safetensors crate rejects such files too):
+                // readers copy numel() elements without looking at nbytes again
+                {
+                    size_t es = 0;
+                    if (t.dtype == "F64" || t.dtype == "I64" || t.dtype == "U64") es = 8;
+                    else if (t.dtype == "F32" || t.dtype == "I32" || t.dtype == "U32") es = 4;
+                    else if (t.dtype == "F16" || t.dtype == "BF16" || t.dtype == "I16" || t.dtype == "U16") es = 2;
+                    else if (t.dtype == "U8" || t.dtype == "I8" || t.dtype == "BOOL" || t.dtype == "F8_E4M3" || t.dtype == "F8_E5M2") es = 1;
+                    if (es) {
+                        size_t n = 1;
+                        for (int64_t d : t.shape) {
+                            if (d < 0) throw std::runtime_error("safetensors: negative dimension in " + name);
+                            if (d != 0 && n > (size_t)-1 / (size_t)d) throw std::runtime_error("safetensors: shape overflows in " + name);
+                            n *= (size_t)d;
+                        }
+                        if (n > (size_t)-1 / es || n * es != t.nbytes)
+                            throw std::runtime_error("safetensors: " + name + " holds " + std::to_string(t.nbytes) + " bytes but its shape and dtype need " +
+                                                     std::to_string(n * es));
+                    }
+                }
                 tensors_[name] = std::move(t);
             }
             if (peek(c, ',')) {

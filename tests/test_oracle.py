@@ -178,3 +178,33 @@ def test_oracle_rejects_bad_token(tiny_paths):
     m = orc.OracleModel(tiny_paths["fp16"])
     with pytest.raises(RuntimeError):
         m.forward([4096])
+
+
+def _rewrite_header(src, dst, edit):
+    """Copies a safetensors file with its JSON header passed through `edit` (the data bytes stay as they are)."""
+    import json
+    import struct
+    raw = open(src, "rb").read()
+    n = struct.unpack("<Q", raw[:8])[0]
+    hdr = json.loads(raw[8:8 + n])
+    edit(hdr)
+    out = json.dumps(hdr, separators=(",", ":")).encode()
+    out += b" " * ((8 - len(out) % 8) % 8)
+    open(dst, "wb").write(struct.pack("<Q", len(out)) + out + raw[8 + n:])
+    return dst
+
+
+def test_parser_rejects_a_shape_larger_than_its_data(tiny_paths, tmp_path):
+    # A header whose shape claims more elements than the byte range holds must be refused (the reference's safetensors
+    # crate refuses it too): readers copy shape-many elements.  The product library uses the same parser.
+    def grow(hdr):
+        hdr["ln_out.weight"]["shape"] = [hdr["ln_out.weight"]["shape"][0] * 2]
+    bad = _rewrite_header(tiny_paths["fp16"], str(tmp_path / "bad_shape.st"), grow)
+    with pytest.raises(RuntimeError, match="bytes but its shape"):
+        orc.OracleModel(bad)
+
+    def negative(hdr):
+        hdr["emb.weight"]["shape"] = [-4096, -512]
+    bad2 = _rewrite_header(tiny_paths["fp16"], str(tmp_path / "bad_neg.st"), negative)
+    with pytest.raises(RuntimeError):
+        orc.OracleModel(bad2)
