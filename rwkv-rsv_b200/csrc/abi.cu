@@ -95,7 +95,7 @@ void ensure_tok_list(Model& m, size_t n) {
 void decode_tokens(Model& m, State& st, const uint32_t* tokens, int64_t n) {
     need(st.model == &m, "state belongs to a different model");
     need(st.cap == 1, "this call needs a single-session state (batch == 1)");
-    need(n >= 1 && n <= 0x7fffffff, "token count must be between 1 and 2^31 - 1");
+    need(n >= 1 && n <= 0x7fffffff, "empty token list (the count must be between 1 and 2^31 - 1)");
     check_tokens(m, tokens, n);
     RSV_CUDA(cudaSetDevice(m.device));
     if (!m.prof_on && m.persistent_available(1)) {
