@@ -50,7 +50,7 @@ constexpr int kDsBars = 16;                          // chunks in flight (mbarri
 constexpr int kDsTileRows = 16;                      // rows of a tile (the m dimension of the matrix instruction)
 constexpr int kDsPad = 16;                           // bytes between the rows of a tile in the ring, beyond the piece
 constexpr int kDsMaxPiece = 2560;                    // bytes of K per piece (the head's rows)
-constexpr int kDsLayerPiece = 1280;                  // bytes of K per piece of the layers' matrices (more chunks in flight; half of it was slower: the producer's time per chunk)
+constexpr int kDsLayerPiece = 1280;                  // bytes of K per piece of the layers' matrices (measured at the 3B shape: 640 -> 1.74, 1280 -> 1.55, 2560 -> 1.66 ms per token)
 constexpr int kDsMaxTiles = 64;                      // tiles of one phase per CTA
 constexpr int kDsPartBytes = 8 * 1024;               // per-piece partial sums of the tiles of one phase
 constexpr int kDsMaxRows = 512;                      // rows of one phase per CTA whose (scale, zero) are staged
@@ -256,7 +256,7 @@ struct DsShared {
     float ts_own[kDsMaxSlice];  // pending time-mix shift state of the slice
     float cs_own[kDsMaxSlice];  // pending channel-mix shift state of the slice
     float ws[kDsMaxRows], wz[kDsMaxRows];  // (scale, zero) of the rows this CTA owns in the current phase
-    float hv[10 * 64];                     // the 64-vectors of a head
+    alignas(16) float hv[10 * 64];                     // the 64-vectors of a head
     float best_val[kDsConsumers];          // per consumer thread: arg-max of the head rows it finished
     int best_idx[kDsConsumers];
     DsPlan plan;
@@ -970,24 +970,30 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         DS_STAMP(18);
                         // a row of a back-projection matrix times its rank-space vector: four threads split the rank dimension in contiguous quarters
                         auto dot_q = [&](const __half* W, int mid, const float* v) {
-                            float a = 0.f;
+                            float a0 = 0.f, a1 = 0.f;
                             const int ql = mid >> 2;
                             if ((mid & 3) == 0 && (ql & 7) == 0) {
+                                // 8 weights (one 16-byte read) against 8 vector elements (two 16-byte reads) per step, two accumulation chains
                                 const __half* wrow = W + quad * ql;
                                 const float* vv = v + quad * ql;
                                 for (int q = 0; q < ql; q += 8) {
                                     const uint4 pk = *reinterpret_cast<const uint4*>(wrow + q);
+                                    const float4 x0 = *reinterpret_cast<const float4*>(vv + q), x1 = *reinterpret_cast<const float4*>(vv + q + 4);
                                     const __half2* h2 = reinterpret_cast<const __half2*>(&pk);
-#pragma unroll
-                                    for (int e = 0; e < 4; ++e) {
-                                        const float2 f = __half22float2(h2[e]);
-                                        a = fmaf(f.x, vv[q + 2 * e], a);
-                                        a = fmaf(f.y, vv[q + 2 * e + 1], a);
-                                    }
+                                    const float2 f0 = __half22float2(h2[0]), f1 = __half22float2(h2[1]), f2 = __half22float2(h2[2]), f3 = __half22float2(h2[3]);
+                                    a0 = fmaf(f0.x, x0.x, a0);
+                                    a1 = fmaf(f0.y, x0.y, a1);
+                                    a0 = fmaf(f1.x, x0.z, a0);
+                                    a1 = fmaf(f1.y, x0.w, a1);
+                                    a0 = fmaf(f2.x, x1.x, a0);
+                                    a1 = fmaf(f2.y, x1.y, a1);
+                                    a0 = fmaf(f3.x, x1.z, a0);
+                                    a1 = fmaf(f3.y, x1.w, a1);
                                 }
                             } else {
-                                for (int q = quad; q < mid; q += 4) a = fmaf(__half2float(W[q]), v[q], a);
+                                for (int q = quad; q < mid; q += 4) a0 = fmaf(__half2float(W[q]), v[q], a0);
                             }
+                            float a = a0 + a1;
                             a += __shfl_xor_sync(0xffffffffu, a, 1);
                             return a + __shfl_xor_sync(0xffffffffu, a, 2);
                         };
@@ -1072,10 +1078,20 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         const float invn = 1.0f / fmaxf(sqrtf(ss), kL2Eps);
                         const float vv_row = S->hv[7 * 64 + rrow];
                         float St[8] = {s4a.x, s4a.y, s4a.z, s4a.w, s4b.x, s4b.y, s4b.z, s4b.w};
-                        float kkh[8], sa = 0.f;
+                        // this thread's eight columns of the head's vectors (16-byte reads)
+                        auto ld8 = [&](int arr, float (&o)[8]) {
+                            const float4 lo = *reinterpret_cast<const float4*>(&S->hv[arr * 64 + oct * 8]), hi = *reinterpret_cast<const float4*>(&S->hv[arr * 64 + oct * 8 + 4]);
+                            o[0] = lo.x, o[1] = lo.y, o[2] = lo.z, o[3] = lo.w, o[4] = hi.x, o[5] = hi.y, o[6] = hi.z, o[7] = hi.w;
+                        };
+                        float kkh[8], wv[8], av[8], ktv[8], rv[8], sa = 0.f;
+                        ld8(4, kkh);
+                        ld8(3, wv);
+                        ld8(5, av);
+                        ld8(6, ktv);
+                        ld8(0, rv);
 #pragma unroll
                         for (int q = 0; q < 8; ++q) {
-                            kkh[q] = S->hv[4 * 64 + oct * 8 + q] * invn;
+                            kkh[q] *= invn;
                             sa = fmaf(St[q], kkh[q], sa);
                         }
                         sa += __shfl_xor_sync(0xffffffffu, sa, 1);
@@ -1084,10 +1100,9 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         float y = 0.f;
 #pragma unroll
                         for (int q = 0; q < 8; ++q) {
-                            const int c = oct * 8 + q;
-                            const float bq = kkh[q] * (-S->hv[5 * 64 + c]);
-                            St[q] = fmaf(St[q], S->hv[3 * 64 + c], fmaf(sa, bq, vv_row * S->hv[6 * 64 + c]));
-                            y = fmaf(St[q], S->hv[c], y);
+                            const float bq = kkh[q] * (-av[q]);
+                            St[q] = fmaf(St[q], wv[q], fmaf(sa, bq, vv_row * ktv[q]));
+                            y = fmaf(St[q], rv[q], y);
                         }
                         y += __shfl_xor_sync(0xffffffffu, y, 1);
                         y += __shfl_xor_sync(0xffffffffu, y, 2);
