@@ -90,10 +90,10 @@ def algorithmic_bytes(sh, quant, B):
     return w + B * (s_rw + a), w
 
 
-# DRAM traffic of decode_persistent_kernel per decoded token, from one ncu capture of a 4-token launch
+# DRAM traffic of decode_stream_kernel per decoded token, from one ncu capture of a 4-token launch
 # (dram__bytes_read.sum + dram__bytes_write.sum, divided by 4; summary under profiles/).  Every token streams the same weights,
 # so the traffic of a launch is this figure times its tokens.
-NCU_DRAM_BYTES_PER_TOKEN = {("3b", "int8", 1): (12.442648e9 + 0.344780e9) / 4}
+NCU_DRAM_BYTES_PER_TOKEN = {}
 
 
 def kernel_bytes(sh, quant, B):
@@ -161,7 +161,7 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_baseline(path, sh, seconds, threads=None, prompt=8):
+def cpu_baseline(path, sh, seconds, threads=None, prompt=8, single_tokens=3):
     """Times the CPU oracle (fp32, the reference's algorithm) on a bounded sample of the same workload."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import orc
@@ -180,7 +180,20 @@ def cpu_baseline(path, sh, seconds, threads=None, prompt=8):
         el = time.perf_counter() - t0
         if (el >= seconds and n >= 3) or n >= 4096:
             break
-    res = {"value": n / el, "unit": UNIT, "cores": nthr, "kind": "port",
+    # the reference's CPU path is single-threaded (no rayon in src/model.rs): the same oracle on one thread, a few tokens
+    single = None
+    if single_tokens > 0:
+        orc.set_threads(1)
+        t1 = time.perf_counter()
+        k = 0
+        while k < single_tokens:
+            tok = orc.argmax(m.forward([tok]))
+            k += 1
+            if time.perf_counter() - t1 > 45.0:
+                break
+        single = {"value": k / (time.perf_counter() - t1), "unit": UNIT, "cores": 1, "tokens": k}
+        orc.set_threads(nthr)
+    res = {"value": n / el, "unit": UNIT, "cores": nthr, "kind": "port", "single_thread": single,
            "sample": f"{n} arg-max decode tokens of the same checkpoint after a {2}-token warm-up, fp32 CPU oracle, {nthr} OpenMP threads "
                      f"(model load {load_s:.1f} s not timed)"}
     m.close()
@@ -220,10 +233,17 @@ def run_reference(args):
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": n, "warmup": args.warmup,
         "ms_per_step": 1000.0 * el / n, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args), "shape": args.shape, "weights": args.quant, "batch_per_gpu": 1},
+        "config": bench_config(args, 1),
+        "reference_note": "the CPU arm decodes from a fresh state (the cost of a decode step does not depend on the state's content); its prompt is not prefilled",
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": nthr, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+def bench_config(args, B):
+    """The `config` object of the JSON line: the same for the GPU arm and the reference arm."""
+    return {"workload": workload_name(args), "shape": args.shape, "weights": args.quant, "batch_per_gpu": B, "prompt": args.prompt,
+            "l2": "every step streams all weights (>> 126 MB L2); no flush needed", "sessions": "one full replica per GPU, no collective"}
 
 
 def workload_name(args):
@@ -318,20 +338,29 @@ def main():
     model = rsv.Model(path, device=local)
     state, seeds = prefix_states(rsv, model, B, args.prompt, sh["vocab"], rng)
 
-    # ---- device-resident decode: warm-up, then exactly K timed steps ----
-    decode_run(rsv, model, state, seeds, W)
+    # ---- device-resident decode: warm-up, then timed regions of exactly K steps each ----
+    # A region of K steps can be far shorter than the clock sampler's period, so the region is repeated (R >= 3 times, about a
+    # second in all) while the sampler runs; the reported time is the median region (each one the max over ranks), the spread is
+    # reported beside it.
+    from rwkv_rsv_b200.shard import max_over_ranks
+    w_ms, _ = decode_run(rsv, model, state, seeds, W)
+    torch.cuda.synchronize()
+    w_ms = max_over_ranks(w_ms, dist, torch.device("cuda", local))  # the same on every rank: they must agree on the number of regions
+    reps = int(min(25, max(3, np.ceil(1000.0 / max(w_ms / W * K, 1e-3)))))
     clocks = ClockSampler(local)
     clocks.start()
-    if dist:
-        dist.barrier()
-    torch.cuda.synchronize()
-    model.clear_kernel_prof()
-    ms, out = decode_run(rsv, model, state, seeds, K)
-    launches = model.launch_count()
-    torch.cuda.synchronize()
-    from rwkv_rsv_b200.shard import max_over_ranks
-    ms = max_over_ranks(ms, dist, torch.device("cuda", local))  # the slowest replica's device time
+    region_ms, launches = [], 0
+    for _ in range(reps):
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        model.clear_kernel_prof()
+        ms_r, out = decode_run(rsv, model, state, seeds, K)
+        launches = model.launch_count()
+        torch.cuda.synchronize()
+        region_ms.append(max_over_ranks(ms_r, dist, torch.device("cuda", local)))  # the slowest replica's device time
     clk = clocks.stop()
+    ms = float(np.median(region_ms))
     value = world * B * K / (ms / 1000.0)
 
     # ---- end to end through the host-buffer API (batch 1: Bundle::infer_tokens per token) ----
@@ -403,9 +432,9 @@ def main():
         result = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload_name(args), "shape": args.shape, "weights": args.quant, "batch_per_gpu": B, "prompt": args.prompt,
-                       "l2": "every step streams all weights (>> 126 MB L2); no flush needed", "sessions": "one full replica per GPU, no collective"},
+            "config": bench_config(args, B),
             "clocks": clk, "gpu_launches": launches, "e2e": e2e, "roofline": roofline,
+            "timed_regions": {"count": reps, "ms_min": float(min(region_ms)), "ms_median": ms, "ms_max": float(max(region_ms))},
         }
         # ---- decode batch sweep (benchmark config 4), single GPU only ----
         if world == 1 and args.sweep:

@@ -35,7 +35,7 @@
 //      WKV-7 state update in place, GroupNorm, bonus, gate
 //   3  att.output, x += ...      4  LN2 + shift -> relu(ffn.key)^2      5  ffn.value, x += ...
 // then ln_out + head -> logits, arg-max across CTAs, next token.
-// All waits are bounded; on expiry bit 2 of the status word is set, every role drains its copies in flight and exits.
+// All waits are bounded; on expiry bit 5 of the status word is set (and the word after it says which wait), every role drains its copies in flight and exits.
 #pragma once
 #include <cstddef>
 
@@ -231,7 +231,7 @@ struct alignas(16) DsDesc {  // read with three 16-byte loads
     DsChunk c;
 };
 static_assert(sizeof(DsChunk) == 32 && sizeof(DsDesc) == 48, "DsDesc is read as three 16-byte words");
-constexpr int kDsMaxChunks = 160;  // table entries per CTA: the chunks of a layer plus the head's
+constexpr int kDsMaxChunks = 256;  // table entries per CTA: the chunks of a layer plus the head's
 enum { DSP_P1 = 0, DSP_P3, DSP_P4, DSP_P5, DSP_HEAD, DSP_COUNT };
 // The CTA's static plan (built once per launch).
 struct DsPlan {
@@ -247,6 +247,7 @@ struct DsShared {
     uint64_t full[kDsBars], empty[kDsBars];
     int alloc[kDsBars];  // producer only: bytes (with wrap waste) a chunk in flight holds
     int abort_flag;
+    int abort_where;  // which wait gave up first (1 rows: full, 2 producer: empty, 3 grid barrier, 4 heads: full) | detail << 4
     uint32_t tok;
     float red_a[16], red_b[16], red_c[4 * 16];
     int red_i[16];
@@ -481,7 +482,10 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
         const long long tw0 = ds_now();
 #endif
         const bool got = mbar_wait(&S->full[wwarp], (j / kDsBars) & 1u, (volatile int*)&S->abort_flag);
-        if (!__all_sync(0xffffffffu, got)) return false;
+        if (!__all_sync(0xffffffffu, got)) {
+            if (lane == 0) atomicCAS(&S->abort_where, 0, 1 | (int)((j - J) << 4));
+            return false;
+        }
 #ifdef RSV_DS_DEBUG
         const long long tw1 = ds_now();
 #endif
@@ -674,6 +678,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
             mbar_init(&S->empty[s], 1);
         }
         S->abort_flag = 0;
+        S->abort_where = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int i = threadIdx.x; i < kDsMaxTiles; i += kDsThreads) S->tile_cnt[i] = 0;
@@ -699,7 +704,10 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
             const int waste = wrap ? R - head : 0;
             while (used + waste + bytes > R || j - tail >= (uint32_t)kDsBars) {
                 const bool w = mbar_wait(&S->empty[tail % kDsBars], (tail / kDsBars) & 1u, abort_flag);
-                if (!__all_sync(0xffffffffu, w)) return false;
+                if (!__all_sync(0xffffffffu, w)) {
+                    if (lane == 0) atomicCAS(&S->abort_where, 0, 2 | (int)(j << 4));
+                    return false;
+                }
                 used -= S->alloc[tail % kDsBars];
                 ++tail;
             }
@@ -804,7 +812,10 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     }
                     if ((i & 255u) == 255u && *abort_flag) break;
                 }
-                if (!got) *abort_flag = 1;
+                if (!got) {
+                    atomicCAS(&S->abort_where, 0, 3 | (int)(bar_target << 4));
+                    *abort_flag = 1;
+                }
             }
             ds_consumer_sync();
             return *abort_flag == 0;
@@ -1003,6 +1014,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         J += 3;
                         auto wait_chunk = [&](uint32_t idx) {
                             const bool w = mbar_wait(&S->full[idx % kDsBars], (idx / kDsBars) & 1u, abort_flag);
+                            if (!w) atomicCAS(&S->abort_where, 0, 4 | (int)(idx << 4));
                             return __all_sync(0xffffffffu, w);
                         };
                         if (!wait_chunk(iA)) {
@@ -1326,7 +1338,11 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
         }
     }
     __syncthreads();
-    if (threadIdx.x == 0 && *abort_flag) atomicOr(P.status, 4);
+    if (threadIdx.x == 0 && *abort_flag) {
+        atomicOr(P.status, 32);
+        // where: a CTA that gave up on its own chunks or ring outranks the CTAs that gave up on the grid barrier because of it
+        if (S->abort_where) atomicMax(P.status + 1, (((S->abort_where & 15) == 3 ? 1 : 2) << 28) | (cta << 20) | (S->abort_where & 0xFFFFF));
+    }
 }
 
 // Writes the second copy of the weights: for every layer and every CTA of the decode kernel, the CTA's chunks in the order it

@@ -374,9 +374,9 @@ std::unique_ptr<Model> Model::load(const std::string& path, int device) {
     m->pinned_bytes = 1 << 18;
     RSV_CUDA(cudaMallocHost(&m->pinned, m->pinned_bytes * Model::kPinRing));
     for (int i = 0; i < Model::kPinRing; ++i) RSV_CUDA(cudaEventCreateWithFlags(&m->pin_ev[i], cudaEventDisableTiming));
-    RSV_CUDA(cudaMalloc(&m->ws.status, sizeof(int)));
+    RSV_CUDA(cudaMalloc(&m->ws.status, 2 * sizeof(int)));
     RSV_CUDA(cudaMalloc(&m->ws.tok_pos, sizeof(int)));
-    RSV_CUDA(cudaMemset(m->ws.status, 0, sizeof(int)));
+    RSV_CUDA(cudaMemset(m->ws.status, 0, 2 * sizeof(int)));
     RSV_CUDA(cudaMemset(m->ws.tok_pos, 0, sizeof(int)));
     return m;
 }
@@ -399,8 +399,8 @@ std::unique_ptr<Model> Model::create_bare(int device) {
     RSV_CUDA(cudaEventCreate(&m->ev1));
     RSV_CUDA(cudaEventCreate(&m->tev[0]));
     RSV_CUDA(cudaEventCreate(&m->tev[1]));
-    RSV_CUDA(cudaMalloc(&m->ws.status, sizeof(int)));
-    RSV_CUDA(cudaMemset(m->ws.status, 0, sizeof(int)));
+    RSV_CUDA(cudaMalloc(&m->ws.status, 2 * sizeof(int)));
+    RSV_CUDA(cudaMemset(m->ws.status, 0, 2 * sizeof(int)));
     return m;
 }
 
@@ -1729,16 +1729,23 @@ void Model::run_stream(State& st, int slot, int n_tokens, bool tok_from_list, bo
 }
 
 void Model::check_status() {
-    int s = 0;
-    RSV_CUDA(cudaMemcpyAsync(&s, ws.status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    int sw[2] = {0, 0};  // status bits; where the weight-streaming decode kernel gave up
+    RSV_CUDA(cudaMemcpyAsync(sw, ws.status, 2 * sizeof(int), cudaMemcpyDeviceToHost, stream));
     RSV_CUDA(cudaStreamSynchronize(stream));
+    const int s = sw[0];
     if (s) {
-        RSV_CUDA(cudaMemsetAsync(ws.status, 0, sizeof(int), stream));
-        if (s & (2 | 4)) {
+        RSV_CUDA(cudaMemsetAsync(ws.status, 0, 2 * sizeof(int), stream));
+        if (s & (2 | 4 | 32)) {
             // a kernel that gave up on a wait may have left arrival counters non-zero: the next launch must start from zero
             if (ws.tc_cnt) RSV_CUDA(cudaMemsetAsync(ws.tc_cnt, 0, (size_t)kTcMaxSplit * kTcEpiWarps * sizeof(int), stream));
             for (int i = 0; i < 5; ++i)
                 if (pctx.region_cnt[i]) RSV_CUDA(cudaMemsetAsync(pctx.region_cnt[i], 0, pctx.region_cnt_bytes[i], stream));
+        }
+        if (s & 32) {
+            static const char* const site[5] = {"a wait", "a chunk of weight rows", "room in the ring", "a grid barrier", "a chunk of a head's rows"};
+            const int k = sw[1] & 15;
+            throw std::runtime_error(std::string("weight-streaming decode kernel gave up waiting for ") + site[k >= 1 && k <= 4 ? k : 0] + " (device status bit 5; CTA " +
+                                     std::to_string((sw[1] >> 20) & 255) + ", index " + std::to_string((sw[1] >> 4) & 0xFFFF) + ")");
         }
         if (s & 16) throw std::runtime_error("WKV kernel gave up waiting for a staged state (device status bit 4)");
         if (s & 8) throw std::runtime_error("persistent decode kernel: schedule tables too small for this shape (device status bit 3)");
