@@ -44,10 +44,10 @@ def parse_args():
     ap.add_argument("--quant", default="int8", choices=["fp16", "int8"])
     ap.add_argument("--batch", type=int, default=1, help="sessions per GPU")
     ap.add_argument("--prompt", type=int, default=512, help="prompt tokens prefilled before decoding")
-    ap.add_argument("--sweep", default="1,8,64,256,1024", help="batch sizes of the decode sweep (N=1 only); '' disables it")
+    ap.add_argument("--sweep", default="1,8,64,256,1024", help="batch sizes of the decode sweep, per GPU; '' disables it")
     ap.add_argument("--sweep-steps", type=int, default=32)
-    ap.add_argument("--prefill", type=int, default=2048, help="prompt tokens of the timed chunked prefill (N=1 only); 0 disables it")
-    ap.add_argument("--continuous", type=int, default=256, help="sessions of the continuous-batching workload (benchmark config 3, N=1 only); 0 disables it")
+    ap.add_argument("--prefill", type=int, default=2048, help="prompt tokens of the timed chunked prefill, per GPU; 0 disables it")
+    ap.add_argument("--continuous", type=int, default=256, help="sessions per GPU of the continuous-batching workload (benchmark config 3); 0 disables it")
     ap.add_argument("--cpu-seconds", type=float, default=20.0, help="time budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--model-dir", default=os.environ.get("RSV_BENCH_DIR", "/tmp/rsv_bench"))
@@ -275,24 +275,36 @@ def prefix_states(rsv, model, B, prompt, vocab, rng):
     return st, np.asarray([seeds[b % nd] for b in range(B)], dtype=np.uint32)
 
 
-def continuous_batching(rsv, model, sh, n_sessions, seed=3, rate=64.0):
-    """Benchmark config 3: `n_sessions` sessions arrive as a Poisson process at `rate` requests per second (wall clock), prompt
-    lengths log-uniform in 16..2048, generation lengths geometric with mean 256, top-p 0.9, temperature 1.0, one sampler seed per
-    session; every scheduler step is a ragged mix of prompt chunks (<= 512 tokens per session) and one decode row per generating
-    session.  Returns tokens per second over the span from the first arrival to the last completion."""
+def continuous_batching(rsv, model, sh, n_sessions, seed=3, rate=64.0, rank=0, world=1, dist=None, device=None):
+    """Benchmark config 3: `n_sessions` sessions per GPU arrive as one Poisson process at `rate` requests per second and GPU (wall
+    clock), prompt lengths log-uniform in 16..2048, generation lengths geometric with mean 256, top-p 0.9, temperature 1.0, one
+    sampler seed per session; every scheduler step is a ragged mix of prompt chunks (<= 512 tokens per session) and one decode
+    row per generating session.  With several GPUs every rank builds the same arrival list, places the sessions with the
+    least-loaded router (rwkv_rsv_b200.router.place_arrivals: deterministic, nothing is exchanged) and serves its own; the
+    clock starts at a barrier.  Returns tokens per second over the span from the first arrival to the last completion on the
+    slowest rank."""
+    from rwkv_rsv_b200.router import place_arrivals
+    from rwkv_rsv_b200.shard import max_over_ranks, sum_over_ranks
+    total = n_sessions * world
     rng = np.random.default_rng(seed)
-    arrive = np.cumsum(rng.exponential(1.0 / rate, size=n_sessions))
+    arrive = np.cumsum(rng.exponential(1.0 / (rate * world), size=total))
     arrive -= arrive[0]
-    plen = np.clip(np.exp(rng.uniform(np.log(16), np.log(2048), size=n_sessions)).astype(np.int64), 16, 2048)
-    glen = np.clip(rng.geometric(1.0 / 256.0, size=n_sessions), 1, 2048)
+    plen = np.clip(np.exp(rng.uniform(np.log(16), np.log(2048), size=total)).astype(np.int64), 16, 2048)
+    glen = np.clip(rng.geometric(1.0 / 256.0, size=total), 1, 2048)
     prompts = [rng.integers(0, sh["vocab"], size=int(n)).astype(np.uint32) for n in plen]
-    sched = rsv.Scheduler(model, max_slots=n_sessions, chunk=512, max_new_cap=2048)
+    # the router's book drains at about one GPU's measured rate on this workload (prompt + generated tokens per second)
+    place = place_arrivals(arrive, plen + glen, world, "least_loaded", drain_rate=8000.0) if world > 1 else [0] * total
+    mine = [i for i in range(total) if place[i] == rank]
+    sched = rsv.Scheduler(model, max_slots=max(len(mine), 1), chunk=512, max_new_cap=2048)
     nxt, done, generated, steps, rows_total, max_rows = 0, 0, 0, 0, 0, 0
+    if dist:
+        dist.barrier()
     t0 = time.perf_counter()
-    while done < n_sessions:
+    while done < len(mine):
         now = time.perf_counter() - t0
-        while nxt < n_sessions and arrive[nxt] <= now:
-            sched.submit(prompts[nxt], int(glen[nxt]), rsv.SamplerParams(temperature=1.0, top_p=0.9, seed=1000 + nxt))
+        while nxt < len(mine) and arrive[mine[nxt]] <= now:
+            i = mine[nxt]
+            sched.submit(prompts[i], int(glen[i]), rsv.SamplerParams(temperature=1.0, top_p=0.9, seed=1000 + i))
             nxt += 1
         rows, active = sched.step()
         steps += 1 if rows else 0
@@ -301,16 +313,21 @@ def continuous_batching(rsv, model, sh, n_sessions, seed=3, rate=64.0):
         for rid in sched.poll():
             generated += len(sched.result(rid))
             done += 1
-        if rows == 0 and active == 0 and nxt < n_sessions:
-            time.sleep(max(0.0, min(0.002, arrive[nxt] - (time.perf_counter() - t0))))
+        if rows == 0 and active == 0 and nxt < len(mine):
+            time.sleep(max(0.0, min(0.002, arrive[mine[nxt]] - (time.perf_counter() - t0))))
         elif rows == 0:
             sched.sync()
     sched.sync()
-    el = time.perf_counter() - t0
+    el_own = time.perf_counter() - t0
     sched.close()
-    return {"sessions": n_sessions, "arrival_rate_per_s": rate, "prompt_tokens": int(plen.sum()), "generated_tokens": int(generated),
-            "seconds": el, "decode_tok_s": generated / el, "total_tok_s": (int(plen.sum()) + generated) / el, "steps": steps,
-            "mean_rows_per_step": rows_total / max(steps, 1), "max_rows_per_step": max_rows,
+    el = max_over_ranks(el_own, dist, device)
+    gen_all = int(sum_over_ranks(generated, dist, device))
+    assert gen_all == int(glen.sum()), "every session must produce its full generation length"
+    per_rank = [int(sum(1 for g in place if g == r)) for r in range(world)]
+    return {"sessions": total, "sessions_per_gpu": per_rank, "arrival_rate_per_s": rate * world, "prompt_tokens": int(plen.sum()), "generated_tokens": gen_all,
+            "seconds": el, "decode_tok_s": gen_all / el, "total_tok_s": (int(plen.sum()) + gen_all) / el, "steps_rank0": steps,
+            "mean_rows_per_step_rank0": rows_total / max(steps, 1), "max_rows_per_step_rank0": max_rows,
+            "placement": "one GPU" if world == 1 else "least-loaded at admission (virtual-time drain 8000 tok/s), replayed identically on every rank",
             "sampler": "top_p 0.9, temperature 1.0, seed 1000 + session", "prefill_chunk": 512}
 
 
@@ -436,42 +453,77 @@ def main():
             "clocks": clk, "gpu_launches": launches, "e2e": e2e, "roofline": roofline,
             "timed_regions": {"count": reps, "ms_min": float(min(region_ms)), "ms_median": ms, "ms_max": float(max(region_ms))},
         }
-        # ---- decode batch sweep (benchmark config 4), single GPU only ----
-        if world == 1 and args.sweep:
-            sweep = {}
-            for b in [int(x) for x in args.sweep.split(",") if x]:
-                if b == B:
-                    sweep[str(b)] = {"tok_s": value, "ms_per_step": ms / K, "hbm_frac": roofline["step"]["frac"]}
-                    continue
-                st_b, seeds_b = prefix_states(rsv, model, b, min(args.prompt, 256), sh["vocab"], rng)
+    # ---- the other workloads: every rank runs its share, times are the slowest rank's, tokens are summed ----
+    from rwkv_rsv_b200.shard import shard_sessions, sum_over_ranks
+    dev = torch.device("cuda", local)
+    peak_gbs = None
+    try:
+        peak_gbs = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))).get("hbm_gbs")
+    except OSError:
+        pass
+    peak_gbs = peak_gbs or 6650.0
+    legs = {}
+    # decode batch sweep (benchmark config 4): b sessions on every GPU (weak) and, with several GPUs, b sessions in all, sharded
+    # by session id mod N (strong: per-GPU batches shrink and move back toward the weight-stream regime)
+    if args.sweep:
+        def sweep_point(n_local):
+            """`n_local` sessions on this rank (0: this rank only joins the barriers)."""
+            ms_b = 0.0
+            if n_local > 0:
+                st_b, seeds_b = prefix_states(rsv, model, n_local, min(args.prompt, 256), sh["vocab"], rng)
                 decode_run(rsv, model, st_b, seeds_b, 3)
+                torch.cuda.synchronize()
+            if dist:
+                dist.barrier()
+            if n_local > 0:
                 ms_b, _ = decode_run(rsv, model, st_b, seeds_b, args.sweep_steps)
-                bts, _ = algorithmic_bytes(sh, args.quant, b)
-                sweep[str(b)] = {"tok_s": b * args.sweep_steps / (ms_b / 1000.0), "ms_per_step": ms_b / args.sweep_steps,
-                                 "hbm_frac": bts / (ms_b / args.sweep_steps / 1000.0) / 1e9 / peak}
                 st_b.close()
-            result["batch_sweep"] = sweep
-        # ---- prompt prefill (the chunked sequence path, Bundle::infer with chunk 512), single GPU only ----
-        if world == 1 and args.prefill > 0:
-            try:
-                pb = rsv.Bundle(model)
-                ptoks = rng.integers(0, sh["vocab"], size=args.prefill).astype(np.uint32)
-                pb.infer_chunked(ptoks[:min(512, args.prefill)], 512)  # sizes the work buffers
-                pb.reset()
-                model.timer_start()
-                pb.infer_chunked(ptoks, 512)
-                pms = model.timer_stop()
-                result["prefill"] = {"tokens": int(args.prefill), "chunk": 512, "ms": pms, "tok_s": args.prefill / (pms / 1000.0),
-                                     "api": "rsv_infer_chunked (Bundle::infer, RnnOption::Last), one session"}
-                pb.state.close()
-            except Exception as e:  # an optional section must not cost the headline line
-                result["prefill"] = {"error": str(e)}
-        # ---- continuous batching (benchmark config 3), single GPU only ----
-        if world == 1 and args.continuous > 0:
-            try:
-                result["continuous_batching"] = continuous_batching(rsv, model, sh, args.continuous)
-            except Exception as e:
-                result["continuous_batching"] = {"error": str(e)}
+            return max_over_ranks(ms_b, dist, dev)
+        weak, strong = {}, {}
+        for b in [int(x) for x in args.sweep.split(",") if x]:
+            if b == B:
+                ms_b = ms / K * args.sweep_steps
+            else:
+                ms_b = sweep_point(b)
+            bts, _ = algorithmic_bytes(sh, args.quant, b)
+            weak[str(b)] = {"tok_s": world * b * args.sweep_steps / (ms_b / 1000.0), "ms_per_step": ms_b / args.sweep_steps,
+                            "hbm_frac": bts / (ms_b / args.sweep_steps / 1000.0) / 1e9 / peak_gbs}
+            if world > 1 and b >= world:
+                share = len(shard_sessions(b, world)[rank])
+                ms_s = sweep_point(share)
+                strong[str(b)] = {"tok_s": b * args.sweep_steps / (ms_s / 1000.0), "ms_per_step": ms_s / args.sweep_steps, "sessions_per_gpu": b // world}
+        legs["batch_sweep"] = weak
+        if strong:
+            legs["batch_sweep_fixed_total"] = strong
+    # prompt prefill (the chunked sequence path, Bundle::infer with chunk 512): one session per GPU
+    if args.prefill > 0:
+        try:
+            pb = rsv.Bundle(model)
+            ptoks = rng.integers(0, sh["vocab"], size=args.prefill).astype(np.uint32)
+            pb.infer_chunked(ptoks[:min(512, args.prefill)], 512)  # sizes the work buffers
+            pb.reset()
+            if dist:
+                dist.barrier()
+            model.timer_start()
+            pb.infer_chunked(ptoks, 512)
+            pms = max_over_ranks(model.timer_stop(), dist, dev)
+            legs["prefill"] = {"tokens": int(args.prefill) * world, "chunk": 512, "ms": pms, "tok_s": world * args.prefill / (pms / 1000.0),
+                               "api": "rsv_infer_chunked (Bundle::infer, RnnOption::Last), one session per GPU"}
+            pb.state.close()
+        except Exception as e:  # an optional section must not cost the headline line
+            if world > 1:
+                raise  # the other ranks are waiting in a reduction
+            legs["prefill"] = {"error": str(e)}
+    # continuous batching (benchmark config 3)
+    if args.continuous > 0:
+        try:
+            legs["continuous_batching"] = continuous_batching(rsv, model, sh, args.continuous, rank=rank, world=world, dist=dist, device=dev)
+        except Exception as e:
+            if world > 1:
+                raise
+            legs["continuous_batching"] = {"error": str(e)}
+    if rank == 0:
+        result.update(legs)
     state.close()
     model.close()
     if rank == 0:

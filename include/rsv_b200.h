@@ -72,6 +72,18 @@ int rsv_state_load(rsv_state* s, const float* data, int64_t len);
 /* State::slot_back / slot_load (src/gpu_model.rs:4038-4095, 884-905). */
 int rsv_state_slot_back(rsv_state* s, int64_t slot, float* out, int64_t len);
 int rsv_state_slot_load(rsv_state* s, int64_t slot, const float* data, int64_t len);
+/* State files: the f32 array of State::back as raw little-endian bytes, no header - the file the reference's
+ * examples/state_persist.rs:38-47 writes with std::fs::write(bytemuck::cast_slice(&state)) and reads back into
+ * Bundle::state_load.  save writes to "<path>.part" and renames; restore refuses a file whose size is not exactly
+ * rsv_state_len (one slot's length for the slot variants) f32 and leaves the state untouched in that case. */
+int rsv_state_save(rsv_state* s, const char* path);
+int rsv_state_restore(rsv_state* s, const char* path);
+int rsv_state_slot_save(rsv_state* s, int64_t slot, const char* path);
+int rsv_state_slot_restore(rsv_state* s, int64_t slot, const char* path);
+/* Session migration: slot src_slot of src -> slot dst_slot of dst, device to device, bit for bit (State::slot_back on one
+ * state followed by State::slot_load on the other, src/gpu_model.rs:4038-4095, without the host round trip).  The states may
+ * belong to different model handles, on one GPU or two; the model shapes must agree. */
+int rsv_state_slot_copy(rsv_state* dst, int64_t dst_slot, rsv_state* src, int64_t src_slot);
 /* State::reset / Bundle::reset (src/gpu_model.rs:4098-4104, 3759). */
 int rsv_state_reset(rsv_state* s);
 

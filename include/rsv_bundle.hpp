@@ -68,6 +68,13 @@ public:
         return out;
     }
     void slot_load(size_t slot, const std::vector<float>& data) const { check(rsv_state_slot_load(h_, (int64_t)slot, data.data(), (int64_t)data.size())); }
+    // state files: the f32 array of back() as raw bytes (examples/state_persist.rs:38-47)
+    void save(const std::string& path) const { check(rsv_state_save(h_, path.c_str())); }
+    void restore(const std::string& path) const { check(rsv_state_restore(h_, path.c_str())); }
+    void slot_save(size_t slot, const std::string& path) const { check(rsv_state_slot_save(h_, (int64_t)slot, path.c_str())); }
+    void slot_restore(size_t slot, const std::string& path) const { check(rsv_state_slot_restore(h_, (int64_t)slot, path.c_str())); }
+    // session migration: slot src_slot of src -> slot `slot` here, device to device (slot_back + slot_load without the host)
+    void slot_copy_from(size_t slot, const State& src, size_t src_slot) const { check(rsv_state_slot_copy(h_, (int64_t)slot, src.h_, (int64_t)src_slot)); }
     void reset() const { check(rsv_state_reset(h_)); }
     rsv_state* handle() const { return h_; }
 

@@ -27,6 +27,7 @@ class RsvError(RuntimeError):
 ABI_SYMBOLS = [
     "rsv_last_error", "rsv_model_load", "rsv_model_free", "rsv_model_info_get", "rsv_model_weight_bytes", "rsv_state_new", "rsv_state_free",
     "rsv_state_batch", "rsv_state_len", "rsv_state_back", "rsv_state_load", "rsv_state_slot_back", "rsv_state_slot_load", "rsv_state_reset",
+    "rsv_state_save", "rsv_state_restore", "rsv_state_slot_save", "rsv_state_slot_restore", "rsv_state_slot_copy",
     "rsv_infer_tokens", "rsv_infer_seq", "rsv_infer_chunked", "rsv_infer_full", "rsv_infer_argmax", "rsv_infer_argmax_selfloop",
     "rsv_infer_sample", "rsv_infer_sample_selfloop", "rsv_prefill_batch", "rsv_sample_selfloop_submit", "rsv_sample_selfloop_collect",
     "rsv_prof_enable", "rsv_prof_clear", "rsv_prof_dump", "rsv_launch_count", "rsv_timer_start", "rsv_timer_stop", "rsv_synchronize",
@@ -80,6 +81,11 @@ def native():
         L.rsv_state_slot_back.argtypes = [vp, i64, vp, i64]
         L.rsv_state_slot_load.argtypes = [vp, i64, vp, i64]
         L.rsv_state_reset.argtypes = [vp]
+        L.rsv_state_save.argtypes = [vp, _c.c_char_p]
+        L.rsv_state_restore.argtypes = [vp, _c.c_char_p]
+        L.rsv_state_slot_save.argtypes = [vp, i64, _c.c_char_p]
+        L.rsv_state_slot_restore.argtypes = [vp, i64, _c.c_char_p]
+        L.rsv_state_slot_copy.argtypes = [vp, i64, vp, i64]
         for f in ("rsv_infer_tokens", "rsv_infer_seq", "rsv_infer_full", "rsv_infer_argmax"):
             getattr(L, f).argtypes = [vp, vp, vp, i64, vp]
         L.rsv_infer_chunked.argtypes = [vp, vp, vp, i64, i64, vp]
@@ -274,6 +280,23 @@ class State:
     def slot_load(self, slot, data):
         d = _np.ascontiguousarray(data, dtype=_np.float32).reshape(-1)
         _check(native().rsv_state_slot_load(self._h, int(slot), _ptr(d), d.size))
+
+    def save(self, path):
+        """The whole state as a raw f32 file (the file of examples/state_persist.rs:38-47)."""
+        _check(native().rsv_state_save(self._h, _os.fsencode(path)))
+
+    def restore(self, path):
+        _check(native().rsv_state_restore(self._h, _os.fsencode(path)))
+
+    def slot_save(self, slot, path):
+        _check(native().rsv_state_slot_save(self._h, int(slot), _os.fsencode(path)))
+
+    def slot_restore(self, slot, path):
+        _check(native().rsv_state_slot_restore(self._h, int(slot), _os.fsencode(path)))
+
+    def slot_copy_from(self, slot, src, src_slot):
+        """Session migration: slot `src_slot` of state `src` (any model handle of the same shape, any GPU) -> slot `slot` here."""
+        _check(native().rsv_state_slot_copy(self._h, int(slot), src._h, int(src_slot)))
 
     def reset(self):
         _check(native().rsv_state_reset(self._h))

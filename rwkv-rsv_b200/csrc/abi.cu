@@ -377,6 +377,103 @@ int rsv_state_slot_load(rsv_state* s, int64_t slot, const float* data, int64_t l
         state_copy(s->s, slot, 1, const_cast<float*>(data), false);
     });
 }
+// ---- state files and slot migration -------------------------------------------------------------------
+// A state file is the f32 array of State::back as raw little-endian bytes with no header: the bytes the reference's
+// examples/state_persist.rs:38-47 writes and reads back.  The size of the file is the only check there is.
+static std::vector<float> read_state_file(const char* path, size_t floats) {
+    FILE* f = fopen(path, "rb");
+    if (!f) throw std::runtime_error(std::string("cannot open state file ") + path);
+    std::vector<float> buf(floats);
+    const size_t got = fread(buf.data(), 4, floats, f);
+    char extra;
+    const bool more = got == floats && fread(&extra, 1, 1, f) == 1;
+    fclose(f);
+    if (got != floats || more)
+        throw std::runtime_error(std::string("state file ") + path + " does not hold exactly " + std::to_string(floats) + " f32 (State::load length mismatch)");
+    return buf;
+}
+static void write_state_file(const char* path, const std::vector<float>& buf) {
+    // written under a temporary name and renamed, so that a reader never sees half a state
+    const std::string tmp = std::string(path) + ".part";
+    FILE* f = fopen(tmp.c_str(), "wb");
+    if (!f) throw std::runtime_error(std::string("cannot create state file ") + path);
+    const size_t put = fwrite(buf.data(), 4, buf.size(), f);
+    const bool ok = fclose(f) == 0 && put == buf.size();
+    if (!ok || rename(tmp.c_str(), path) != 0) {
+        remove(tmp.c_str());
+        throw std::runtime_error(std::string("cannot write state file ") + path);
+    }
+}
+int rsv_state_save(rsv_state* s, const char* path) {
+    return guarded([&] {
+        need(s && path, "null argument");
+        std::vector<float> buf((size_t)rsv_state_len(s));
+        state_copy(s->s, 0, s->s.cap, buf.data(), true);
+        write_state_file(path, buf);
+    });
+}
+int rsv_state_restore(rsv_state* s, const char* path) {
+    return guarded([&] {
+        need(s && path, "null argument");
+        std::vector<float> buf = read_state_file(path, (size_t)rsv_state_len(s));  // the state is untouched when the file is refused
+        state_copy(s->s, 0, s->s.cap, buf.data(), false);
+    });
+}
+int rsv_state_slot_save(rsv_state* s, int64_t slot, const char* path) {
+    return guarded([&] {
+        need(s && path, "null argument");
+        need(slot >= 0 && slot < s->s.cap, "slot_back: slot >= batch");
+        std::vector<float> buf(s->s.model->cfg.state_floats_per_slot());
+        state_copy(s->s, slot, 1, buf.data(), true);
+        write_state_file(path, buf);
+    });
+}
+int rsv_state_slot_restore(rsv_state* s, int64_t slot, const char* path) {
+    return guarded([&] {
+        need(s && path, "null argument");
+        need(slot >= 0 && slot < s->s.cap, "slot_load: slot >= batch");
+        std::vector<float> buf = read_state_file(path, s->s.model->cfg.state_floats_per_slot());
+        state_copy(s->s, slot, 1, buf.data(), false);
+    });
+}
+// Moves one session: slot `src_slot` of `src` -> slot `dst_slot` of `dst`, device to device (the two states may belong to
+// different model handles on the same GPU or on two GPUs; the shapes must agree).  3 L + 1 copies, no host staging of ours:
+// cudaMemcpyPeerAsync goes over NVLink when the driver allows peer access and through the host otherwise.
+int rsv_state_slot_copy(rsv_state* dst, int64_t dst_slot, rsv_state* src, int64_t src_slot) {
+    return guarded([&] {
+        need(dst && src, "null argument");
+        State &D = dst->s, &S = src->s;
+        const Config &cd = D.model->cfg, &cs = S.model->cfg;
+        need(dst_slot >= 0 && dst_slot < D.cap, "slot_load: slot >= batch");
+        need(src_slot >= 0 && src_slot < S.cap, "slot_back: slot >= batch");
+        need(cd.n_layer == cs.n_layer && cd.n_embd == cs.n_embd && cd.n_head == cs.n_head, "slot copy: the two states belong to models of different shapes");
+        if (&D == &S && dst_slot == src_slot) return;
+        const size_t C = cs.n_embd, HNN = (size_t)cs.n_head * kHeadSize * kHeadSize;
+        const int dd = D.model->device, sd = S.model->device;
+        // what the source's stream has queued (the session's last step) must be complete before the copy reads it; the copy
+        // runs on the destination's stream, behind whatever that GPU still does with the slot
+        RSV_CUDA(cudaSetDevice(sd));
+        RSV_CUDA(cudaStreamSynchronize(S.model->stream));
+        RSV_CUDA(cudaSetDevice(dd));
+        cudaStream_t st = D.model->stream;
+        auto cp = [&](float* dbase, const float* sbase, size_t width, int l) {
+            float* d = dbase + ((size_t)l * D.cap + (size_t)dst_slot) * width;
+            const float* q = sbase + ((size_t)l * S.cap + (size_t)src_slot) * width;
+            if (dd == sd)
+                RSV_CUDA(cudaMemcpyAsync(d, q, width * 4, cudaMemcpyDeviceToDevice, st));
+            else
+                RSV_CUDA(cudaMemcpyPeerAsync(d, dd, q, sd, width * 4, st));
+        };
+        for (int l = 0; l < cs.n_layer; ++l) {
+            cp(D.tmix_x, S.tmix_x, C, l);
+            cp(D.wkv, S.wkv, HNN, l);
+            cp(D.cmix_x, S.cmix_x, C, l);
+        }
+        cp(D.v_first, S.v_first, C, 0);
+        RSV_CUDA(cudaStreamSynchronize(st));
+    });
+}
+
 int rsv_state_reset(rsv_state* sh) {
     return guarded([&] {
         need(sh, "null argument");

@@ -128,19 +128,32 @@ struct DpVar {
     DpShare share[kDpMaxShares];
 };
 
+// Phase time stamps (token 1, layer 1) for tuning: compiled in only with -DRSV_DP_DEBUG, together with the host code that
+// allocates and prints them; otherwise the macros expand to nothing.
+#ifdef RSV_DP_DEBUG
 __device__ __forceinline__ long long dp_now() {
     long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-#define DP_STAMP_ALL(k)                                                                                         \
-    do {                                                                                                        \
-        if (P.dbg && wtid == 0 && t == 1 && l == 1 && v == DV_P3) P.dbg[64 + cta * 8 + (k)] = dp_now();         \
+#define DP_STAMP_ALL(k)                                                                                 \
+    do {                                                                                                \
+        if (P.dbg && wtid == 0 && t == 1 && l == 1 && v == DV_P3) P.dbg[64 + cta * 8 + (k)] = dp_now(); \
     } while (0)
 #define DP_STAMP(id)                                                                  \
     do {                                                                              \
         if (P.dbg && cta == 0 && wtid == 0 && t == 1 && l == 1) P.dbg[id] = dp_now(); \
     } while (0)
+#define DP_DBG(...) __VA_ARGS__
+#else
+#define DP_STAMP_ALL(k) \
+    do {                \
+    } while (0)
+#define DP_STAMP(id) \
+    do {             \
+    } while (0)
+#define DP_DBG(...)
+#endif
 
 // Number of CTAs that take part in a phase of `n` problems with `unit0[i]` = first unit of problem i and U units in all.
 // Normally min(G, U).  A CTA whose range straddles two problems has to build two sets of activation operands one after the
@@ -594,8 +607,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                     }
                     if (lane == 0) {
                         const DpUnit* un = units + V.unit0;
-                        const bool dbg_here = P.dbg && cta == 0 && t == 1 && l == 1 && v == DV_P4;
-                        if (dbg_here) P.dbg[55] = dp_now();
+                        DP_DBG(const bool dbg_here = P.dbg && cta == 0 && t == 1 && l == 1 && v == DV_P4; if (dbg_here) P.dbg[55] = dp_now();)
                         for (int i = 0; i < V.nunits; ++i, ++it) {
                             const DpUnit e = un[i];
                             const int map = V.p_mat[e.prob] == DM_HEAD ? P.L * 10 : l * 10 + V.p_mat[e.prob];
@@ -607,7 +619,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                             mbar_expect_tx(&full[s], kDpATile);
                             tma_load_2d(&P.maps[map], &full[s], ring + (size_t)s * kDpATile, (int)e.kb * ((e.flags & 4) ? 128 : 64), (int)e.mt * 128);
                         }
-                        if (dbg_here) P.dbg[56] = dp_now();
+                        DP_DBG(if (dbg_here) P.dbg[56] = dp_now();)
                     }
                     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // keeps the lanes in step with the tile issue
                 }
@@ -635,8 +647,7 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                         ++phase_seq;
                         if (!ok) break;
                         tc_fence_after();
-                        const bool dbg_here = P.dbg && cta == 0 && t == 1 && l == 1 && v == DV_P4;
-                        if (dbg_here && lane == 0) P.dbg[50] = dp_now();
+                        DP_DBG(const bool dbg_here = P.dbg && cta == 0 && t == 1 && l == 1 && v == DV_P4; if (dbg_here && lane == 0) P.dbg[50] = dp_now();)
                         for (int i = 0; i < nunits; ++i) {
                             const DpUnit e = un[i];
                             if (e.flags & 1) {
@@ -672,11 +683,11 @@ __global__ void __launch_bounds__(kDpThreads, 1) decode_persistent_kernel(const 
                                 slot_par ^= 1u;
                             }
                         }
-                        if (dbg_here && lane == 0) {
+                        DP_DBG(if (dbg_here && lane == 0) {
                             P.dbg[51] = dp_now();
                             P.dbg[52] = 0;
                             P.dbg[53] = nunits;
-                        }
+                        })
                     }
                 }
             }

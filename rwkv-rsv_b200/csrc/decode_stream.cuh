@@ -115,6 +115,7 @@ struct DsParams {
     const char* hstream;      // the head's rows in consumption order: region of CTA c at c hslot
     long long hslot;
     int ring_bytes;  // shared-memory ring
+    int head_early;  // 1: a head's first chunk (w2, a2 rows) is released before the other two are awaited (ring too small for all three)
     int vec_floats;  // operand area, in 4-byte elements: max(4 C, F)
     long long* dbg;  // optional time stamps (built with -DRSV_DS_DEBUG only)
 };
@@ -1028,6 +1029,11 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                             dw = dot_q(w2s + (size_t)drow * P.wm, P.wm, sc_mid);
                             da = dot_q(w2s + (size_t)64 * P.wm + (size_t)drow * P.am, P.am, sc_mid + P.wm);
                         }
+                        if (P.head_early && !upper) {
+                            // the ring cannot hold all three chunks: the first goes back as soon as the 8 warps that read it are done
+                            asm volatile("bar.sync 2, 256;" ::: "memory");
+                            if (wtid == 0) mbar_arrive(&S->empty[iA % kDsBars]);
+                        }
                         if (!wait_chunk(iB) || !wait_chunk(iC)) {
                             ok = false;
                             break;
@@ -1077,7 +1083,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         DS_STAMP(19);
                         ds_consumer_sync();  // also: every warp is done with the three chunks
                         if (wtid == 0) {
-                            mbar_arrive(&S->empty[iA % kDsBars]);
+                            if (!P.head_early) mbar_arrive(&S->empty[iA % kDsBars]);
                             mbar_arrive(&S->empty[iB % kDsBars]);
                             mbar_arrive(&S->empty[iC % kDsBars]);
                         }

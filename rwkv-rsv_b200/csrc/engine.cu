@@ -306,8 +306,6 @@ std::unique_ptr<Model> Model::load(const std::string& path, int device) {
     if (c.n_embd % 8 || c.ffn_hidden % 8) throw std::runtime_error("n_embd and ffn_hidden must be multiples of 8");
 
     m->num_sms = prop.multiProcessorCount;
-    if (const char* e = getenv("RSV_TC_MIN_ROWS"))
-        if (*e) m->tc_min_rows = atoi(e);
     if (const char* e = getenv("RSV_NO_PERSISTENT"))
         if (*e && *e != '0') m->use_persistent = false;
     if (const char* e = getenv("RSV_NO_STREAM"))
@@ -1222,11 +1220,10 @@ bool Model::persistent_available(int nb) {
     RSV_CUDA(cudaMalloc(&pc.cand_val, (size_t)G * kDpMaxNB * 4));
     RSV_CUDA(cudaMalloc(&pc.cand_idx, (size_t)G * kDpMaxNB * 4));
     RSV_CUDA(cudaMalloc(&pc.grid_bar, 4));
-    if (const char* e = getenv("RSV_DP_DEBUG"))
-        if (*e && *e != '0') {
-            RSV_CUDA(cudaMalloc(&pc.dbg, (64 + 8 * 1024) * sizeof(long long)));
-            RSV_CUDA(cudaMemset(pc.dbg, 0, (64 + 8 * 1024) * sizeof(long long)));
-        }
+#ifdef RSV_DP_DEBUG
+    RSV_CUDA(cudaMalloc(&pc.dbg, (64 + 8 * 1024) * sizeof(long long)));
+    RSV_CUDA(cudaMemset(pc.dbg, 0, (64 + 8 * 1024) * sizeof(long long)));
+#endif
     RSV_CUDA(cudaMemset(pc.vfirst, 0, (size_t)kDpMaxNB * C * 4));
     for (int i = 0; i < 5; ++i) {
         const size_t runs = (size_t)tiles[i] * pmax[i];
@@ -1329,6 +1326,7 @@ void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bo
     LAUNCH(*this, "decode_persistent") {
         RSV_CUDA(cudaLaunchCooperativeKernel((const void*)decode_persistent_kernel, dim3(pc.grid), dim3(kDpThreads), args, pc.smem, stream));
     }
+#ifdef RSV_DP_DEBUG
     if (pc.dbg && n_tokens >= 2) {
         std::vector<long long> hv(64 + 8 * 1024);
         long long* h = hv.data();
@@ -1366,6 +1364,7 @@ void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bo
         fprintf(stderr, "  ffn.key phase: producer issued its %lld tiles from %.2f to %.2f; MMA thread started %.2f, last issue %.2f, waited %.2f us for tiles/accumulators\n",
                 h[53], (h[55] - t0) / 1e3, (h[56] - t0) / 1e3, (h[50] - t0) / 1e3, (h[51] - t0) / 1e3, h[52] / 1e3);
     }
+#endif
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1460,9 +1459,13 @@ bool Model::stream_available() {
     const size_t fixed = (size_t)vec_floats * 4 + sizeof(DsShared) + (size_t)cfg.mids() * 4 + 256;
     if (fixed + 64 * 1024 > budget) return fail("operand area does not fit in shared memory");
     const int ring_bytes = (int)((budget - fixed) / 128 * 128);
-    int max_chunk = std::max(64 * (cfg.w_mid + cfg.a_mid) * 2, 64 * cfg.v_mid * 2 + 32 * cfg.g_mid * 2);
-    max_chunk = std::max(max_chunk, kDsTileRows * (kDsMaxPiece + kDsPad));
-    if (2 * max_chunk > ring_bytes) return fail("a chunk of rows does not fit twice in the shared-memory ring");
+    // A head's back-projection rows come as three chunks (w2 + a2; v2 + half of g2; the other half of g2).  The ring hands out
+    // contiguous space in order, so what must be resident together needs its bytes plus one wrap's waste (< the largest chunk):
+    // all three when the head phase returns them together, else the first alone and then the other two.
+    const int hb_a = 64 * (cfg.w_mid + cfg.a_mid) * 2, hb_b = 64 * cfg.v_mid * 2 + 32 * cfg.g_mid * 2, hb_c = 32 * cfg.g_mid * 2;
+    const bool head_early = hb_a + hb_b + hb_c + std::max({hb_a, hb_b, hb_c}) > ring_bytes;
+    if (head_early && std::max(2 * hb_a, hb_b + hb_c + std::max(hb_b, hb_c)) > ring_bytes) return fail("a head's back-projection rows do not fit in the shared-memory ring");
+    if (2 * kDsTileRows * (kDsMaxPiece + kDsPad) > ring_bytes) return fail("a chunk of rows does not fit twice in the shared-memory ring");
     {
         // tiles and partial-sum bytes of the largest phase of any CTA (rows per CTA rounded up)
         auto tiles_of = [&](int M, int nct) { return ((M + nct - 1) / nct + kDsTileRows - 1) / kDsTileRows + 1; };
@@ -1592,8 +1595,8 @@ bool Model::stream_available() {
         RSV_CUDA(cudaStreamSynchronize(stream));
         if (const char* e = getenv("RSV_VERBOSE"))
             if (*e && *e != '0')
-                fprintf(stderr, "[rsv] weight-streaming decode kernel: %.2f GB second copy of the weights in consumption order (%lld bytes per layer and SM)\n",
-                        ((double)wslot * G * L + (double)hslot * G) / 1e9, wslot);
+                fprintf(stderr, "[rsv] weight-streaming decode kernel: %.2f GB second copy of the weights in consumption order (%lld bytes per layer and SM); ring %d bytes%s\n",
+                        ((double)wslot * G * L + (double)hslot * G) / 1e9, wslot, ring_bytes, head_early ? ", a head's first chunk released early" : "");
     }
     RSV_CUDA(cudaMalloc(&sc.x, (size_t)C * 4));
     RSV_CUDA(cudaMalloc(&sc.yg, (size_t)C * 4));
@@ -1641,6 +1644,7 @@ bool Model::stream_available() {
     P.hstream = (const char*)sc.hstream;
     P.hslot = sc.hslot;
     P.ring_bytes = ring_bytes;
+    P.head_early = head_early ? 1 : 0;
     P.vec_floats = vec_floats;
     P.dbg = sc.dbg;
     sc.params_template.resize(sizeof(DsParams));

@@ -81,7 +81,7 @@ struct PersistentCtx {
     float *x = nullptr, *yg = nullptr, *vfirst = nullptr, *cand_val = nullptr;
     int* cand_idx = nullptr;
     unsigned* grid_bar = nullptr;
-    long long* dbg = nullptr;  // RSV_DP_DEBUG=1: phase time stamps of the persistent kernel
+    long long* dbg = nullptr;  // builds with -DRSV_DP_DEBUG: phase time stamps of the persistent kernel
     void* region_data[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     void* region_meta[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     int* region_cnt[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};

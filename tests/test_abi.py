@@ -25,6 +25,47 @@ def test_library_exports_every_declared_symbol():
     assert sorted(rsv.ABI_SYMBOLS) == syms
 
 
+def test_cpp_mirror_header_compiles_and_links(tmp_path):
+    # include/rsv_bundle.hpp (the C++ mirror of ModelBuilder / Bundle / State) instantiates every wrapper against the C header,
+    # links against the shared library, and a program using it fails loudly on a box without a GPU
+    import shutil
+    import subprocess
+    if not shutil.which("g++"):
+        pytest.skip("no g++")
+    src = tmp_path / "use_bundle.cpp"
+    src.write_text(r"""
+#include <cstdio>
+#include "rsv_bundle.hpp"
+int main(int argc, char** argv) {
+    try {
+        rsv::Bundle b = rsv::ModelBuilder(argc > 1 ? argv[1] : "missing.st").build();
+        std::vector<float> lg = b.infer_tokens({1, 2, 3});
+        std::vector<uint32_t> out = b.infer_argmax_selfloop(3, 4);
+        b.state.save("s.bin");
+        b.state.restore("s.bin");
+        b.state_load(b.state_back());
+        rsv::SamplerParams sp;
+        b.infer_sample_selfloop(3, 2, sp);
+        std::printf("%zu %zu\n", lg.size(), out.size());
+    } catch (const rsv::Error& e) {
+        std::printf("rsv::Error: %s\n", e.what());
+        return 3;
+    }
+    return 0;
+}
+""")
+    exe = tmp_path / "use_bundle"
+    libdir = os.path.dirname(rsv.LIB_CUDA)
+    cmd = ["g++", "-std=c++17", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe), "-L", libdir,
+           "-l:" + os.path.basename(rsv.LIB_CUDA), "-Wl,-rpath," + libdir]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    import torch
+    if not torch.cuda.is_available():
+        run = subprocess.run([str(exe)], capture_output=True, text=True, cwd=tmp_path)
+        assert run.returncode == 3 and "rsv::Error" in run.stdout, (run.returncode, run.stdout, run.stderr)
+
+
 def test_header_cites_reference_for_each_entry_point():
     text = open(os.path.join(ROOT, "include", "rsv_b200.h")).read()
     assert text.count("src/gpu_model.rs") >= 20
