@@ -275,9 +275,10 @@ def prefix_states(rsv, model, B, prompt, vocab, rng):
     return st, np.asarray([seeds[b % nd] for b in range(B)], dtype=np.uint32)
 
 
-def continuous_batching(rsv, model, sh, n_sessions, seed=3, rate=64.0, rank=0, world=1, dist=None, device=None):
+def continuous_batching(rsv, model, sh, n_sessions, seed=3, rate=64.0, rank=0, world=1, dist=None, device=None, fixed_total=False):
     """Benchmark config 3: `n_sessions` sessions per GPU arrive as one Poisson process at `rate` requests per second and GPU (wall
-    clock), prompt lengths log-uniform in 16..2048, generation lengths geometric with mean 256, top-p 0.9, temperature 1.0, one
+    clock; with `fixed_total` both figures are totals over all GPUs: the arrival span, about n_sessions / rate seconds, then bounds
+    the run from below however many GPUs serve it), prompt lengths log-uniform in 16..2048, generation lengths geometric with mean 256, top-p 0.9, temperature 1.0, one
     sampler seed per session; every scheduler step is a ragged mix of prompt chunks (<= 512 tokens per session) and one decode
     row per generating session.  With several GPUs every rank builds the same arrival list, places the sessions with the
     least-loaded router (rwkv_rsv_b200.router.place_arrivals: deterministic, nothing is exchanged) and serves its own; the
@@ -285,9 +286,10 @@ def continuous_batching(rsv, model, sh, n_sessions, seed=3, rate=64.0, rank=0, w
     slowest rank."""
     from rwkv_rsv_b200.router import place_arrivals
     from rwkv_rsv_b200.shard import max_over_ranks, sum_over_ranks
-    total = n_sessions * world
+    total = n_sessions if fixed_total else n_sessions * world
+    rate_all = rate if fixed_total else rate * world
     rng = np.random.default_rng(seed)
-    arrive = np.cumsum(rng.exponential(1.0 / (rate * world), size=total))
+    arrive = np.cumsum(rng.exponential(1.0 / rate_all, size=total))
     arrive -= arrive[0]
     plen = np.clip(np.exp(rng.uniform(np.log(16), np.log(2048), size=total)).astype(np.int64), 16, 2048)
     glen = np.clip(rng.geometric(1.0 / 256.0, size=total), 1, 2048)
@@ -324,7 +326,7 @@ def continuous_batching(rsv, model, sh, n_sessions, seed=3, rate=64.0, rank=0, w
     gen_all = int(sum_over_ranks(generated, dist, device))
     assert gen_all == int(glen.sum()), "every session must produce its full generation length"
     per_rank = [int(sum(1 for g in place if g == r)) for r in range(world)]
-    return {"sessions": total, "sessions_per_gpu": per_rank, "arrival_rate_per_s": rate * world, "prompt_tokens": int(plen.sum()), "generated_tokens": gen_all,
+    return {"sessions": total, "sessions_per_gpu": per_rank, "arrival_rate_per_s": rate_all, "arrival_span_s": float(arrive[-1]), "prompt_tokens": int(plen.sum()), "generated_tokens": gen_all,
             "seconds": el, "decode_tok_s": gen_all / el, "total_tok_s": (int(plen.sum()) + gen_all) / el, "steps_rank0": steps,
             "mean_rows_per_step_rank0": rows_total / max(steps, 1), "max_rows_per_step_rank0": max_rows,
             "placement": "one GPU" if world == 1 else "least-loaded at admission (virtual-time drain 8000 tok/s), replayed identically on every rank",
@@ -522,6 +524,9 @@ def main():
             if world > 1:
                 raise
             legs["continuous_batching"] = {"error": str(e)}
+        if world > 1:
+            legs["continuous_batching_fixed_total"] = continuous_batching(rsv, model, sh, args.continuous, rank=rank, world=world, dist=dist, device=dev,
+                                                                          fixed_total=True)
     if rank == 0:
         result.update(legs)
     state.close()

@@ -166,6 +166,18 @@ int rsv_op_dequant_int8(int device, const uint8_t* idx, const uint32_t* sz, int6
  * Stands in for the reference's per-kernel GEMV/GEMM unit tests (gemv_f16, gemv_variant, gemm; src/backend_cuda.rs:7440-7480,
  * 8880-9066, 9607-9675). */
 int rsv_op_linear(int device, int path, int wtype, const void* w, const uint32_t* sz, int64_t M, int64_t K, const float* x, int64_t R, float* y);
+/* The WKV-7 step of one layer on its own, nseg sessions x T tokens (rows session-major, [nseg*T, H*64] f32 each):
+ *   kk = normalize(k * k_k) per head, k~ = k + k_a (k a - k), v' = v + vgate (vfirst - v) (vgate, vfirst NULL: v' = v),
+ *   S <- S diag(w) + (S kk)(-kk a)^T + v' k~^T, y = (GroupNorm_head(S r; lnx_w, lnx_b, eps 64e-5) + (sum r k~ r_k) v') g
+ * with w the decay (already exp(-e^-0.5 sigmoid(.))), a already sigmoid, S[h][i][j] i = value row, j = key column; state
+ * [nseg, H, 64, 64] in and out.  The CPU path's l2_norm_groups / dplr_update / dplr_matvec / group_norm / sum_rk_rk
+ * (src/model.rs:716-826) and the kernels fuse_ka_dplr_norm and rwkv_dplr_seq + rwkv_fuse_ka + rwkv_sum_rk_rk
+ * (src/backend_cuda.rs:2620-2764, 4231-4309, 4507-4575; their unit tests :8549-8669).  variant picks the kernel:
+ * 0 as the forward step would, 1 token kernel, 2 row-per-lane kernel with TMA-staged states, 3 / 4 sequence kernel with a
+ * head over two CTAs / in one CTA. */
+int rsv_op_wkv7(int device, int variant, int64_t nseg, int64_t T, int64_t H, const float* r, const float* k, const float* v, const float* w, const float* a,
+                const float* g, const float* vgate, const float* vfirst, const float* k_k, const float* k_a, const float* r_k, const float* lnx_w,
+                const float* lnx_b, float* state, float* y);
 /* arg-max per row of logits[rows*V], ties to the smaller index (rwkv_argmax, src/backend_cuda.rs:3640-3680). */
 int rsv_op_argmax(int device, const float* logits, int64_t rows, int64_t V, uint32_t* out);
 /* The sampling kernel on its own (rwkv_sample(_batch), src/backend_cuda.rs:3690-4009, 2069-2387):

@@ -42,6 +42,7 @@ def lib():
         L.orc_state_import.argtypes = [vp, vp]
         L.orc_forward.argtypes = [vp, vp, vp, c.c_int64, vp, vp]
         L.orc_dequant_int8.argtypes = [vp, vp, c.c_int64, c.c_int64, vp]
+        L.orc_wkv7.argtypes = [c.c_int64, c.c_int64] + [vp] * 15
         L.orc_argmax.restype = c.c_uint32
         L.orc_argmax.argtypes = [vp, c.c_int64]
         L.orc_sample.restype = c.c_uint32
@@ -73,6 +74,19 @@ def dequant_int8(idx_u8, sz_u32):
     out = np.empty((m, k), dtype=np.float32)
     lib().orc_dequant_int8(_p(idx), _p(sz), m, k, _p(out))
     return out
+
+
+def wkv7(r, k, v, w, a, g, k_k, k_a, r_k, lnx_w, lnx_b, state, vgate=None, vfirst=None):
+    """The WKV-7 step of one layer for one session: rows [T, H*64], parameters [H*64], state [H, 64, 64].  Returns (y, new state)."""
+    rr = np.ascontiguousarray(r, dtype=np.float32)
+    T, C = rr.shape
+    rows = [np.ascontiguousarray(x, dtype=np.float32).reshape(T, C) for x in (k, v, w, a, g)]
+    opt = [None if x is None else np.ascontiguousarray(x, dtype=np.float32).reshape(T, C) for x in (vgate, vfirst)]
+    par = [np.ascontiguousarray(x, dtype=np.float32).reshape(C) for x in (k_k, k_a, r_k, lnx_w, lnx_b)]
+    st = np.array(state, dtype=np.float32, order="C").reshape(C // 64, 64, 64)
+    y = np.empty((T, C), dtype=np.float32)
+    lib().orc_wkv7(C // 64, T, _p(rr), *[_p(x) for x in rows], *[None if x is None else _p(x) for x in opt], *[_p(x) for x in par], _p(st), _p(y))
+    return y, st
 
 
 def argmax(logits):

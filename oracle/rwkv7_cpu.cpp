@@ -617,6 +617,68 @@ int orc_forward(void* m, void* s, const uint32_t* tokens, int64_t n, float* logi
 }
 void orc_dequant_int8(const uint32_t* idx, const uint32_t* sz, int64_t m, int64_t k, float* out) { dequant_int8(idx, sz, (size_t)m, (size_t)k, out); }
 // arg-max with ties -> smaller index (src/backend_cuda.rs:3640-3680)
+// The WKV-7 step of one layer on its own, for one session over T tokens: the same statements, in the same order, as the time-mixing
+// block of forward() above - v lerp (src/model.rs:418-434), kk / k~ / b (:445-460), l2_norm_groups (:716-727), dplr_update (:732-766),
+// dplr_matvec (:769-782), group_norm (:785-797), sum_rk_rk (:801-826), gate.  Rows are [T, H*64]; vgate / vfirst may be null
+// (first layer); state [H, 64, 64] is updated in place; y [T, H*64].
+int orc_wkv7(int64_t H, int64_t T, const float* r, const float* k, const float* v_in, const float* w, const float* a, const float* g, const float* vgate,
+             const float* vfirst, const float* k_k, const float* k_a, const float* r_k, const float* lnx_w, const float* lnx_b, float* state, float* y_out) {
+    const size_t n = 64, h = (size_t)H, c = h * n;
+    std::vector<float> v(c), kk(c), k_mod(c), kk_l2(c), b_vec(c), y(c), sa(n);
+    for (int64_t t = 0; t < T; ++t) {
+        const float *rt = r + t * c, *kt = k + t * c, *wt = w + t * c, *at = a + t * c, *gt = g + t * c;
+        for (size_t j = 0; j < c; ++j) {
+            const float vj = v_in[t * c + j];
+            v[j] = vgate ? vj + vgate[t * c + j] * (vfirst[t * c + j] - vj) : vj;
+        }
+        for (size_t j = 0; j < c; ++j) kk[j] = kt[j] * k_k[j];
+        for (size_t j = 0; j < c; ++j) {
+            float ka = kt[j] * at[j];
+            k_mod[j] = kt[j] + k_a[j] * (ka - kt[j]);
+        }
+        for (size_t hi = 0; hi < h; ++hi) {
+            float ss = 0.f;
+            for (size_t j = 0; j < n; ++j) ss += kk[hi * n + j] * kk[hi * n + j];
+            float norm = std::max(std::sqrt(ss), L2_EPS);
+            float inv = 1.0f / norm;
+            for (size_t j = 0; j < n; ++j) kk_l2[hi * n + j] = kk[hi * n + j] * inv;
+        }
+        for (size_t j = 0; j < c; ++j) b_vec[j] = kk_l2[j] * (-at[j]);
+        for (size_t hi = 0; hi < h; ++hi) {
+            float* s = state + hi * n * n;
+            const float *wh = &wt[hi * n], *kh = &k_mod[hi * n], *vh = &v[hi * n], *ah = &kk_l2[hi * n], *bh = &b_vec[hi * n], *rh = &rt[hi * n];
+            std::fill(sa.begin(), sa.end(), 0.f);
+            for (size_t ii = 0; ii < n; ++ii)
+                for (size_t j = 0; j < n; ++j) sa[ii] += s[ii * n + j] * ah[j];
+            for (size_t ii = 0; ii < n; ++ii)
+                for (size_t j = 0; j < n; ++j) s[ii * n + j] = s[ii * n + j] * wh[j] + sa[ii] * bh[j] + vh[ii] * kh[j];
+            for (size_t ii = 0; ii < n; ++ii) {
+                float acc = 0.f;
+                for (size_t j = 0; j < n; ++j) acc += s[ii * n + j] * rh[j];
+                y[hi * n + ii] = acc;
+            }
+        }
+        for (size_t hi = 0; hi < h; ++hi) {
+            float* grp = &y[hi * n];
+            float sum = 0.f;
+            for (size_t j = 0; j < n; ++j) sum += grp[j];
+            float mean = sum / (float)n;
+            float sq = 0.f;
+            for (size_t j = 0; j < n; ++j) sq += (grp[j] - mean) * (grp[j] - mean);
+            float var = sq / (float)n + GN_EPS;
+            float inv_std = 1.0f / std::sqrt(var);
+            float srk = 0.f;
+            for (size_t j = 0; j < n; ++j) srk += rt[hi * n + j] * k_mod[hi * n + j] * r_k[hi * n + j];
+            for (size_t j = 0; j < n; ++j) {
+                float gn = (grp[j] - mean) * inv_std * lnx_w[hi * n + j] + lnx_b[hi * n + j];
+                grp[j] = gn + srk * v[hi * n + j];
+            }
+        }
+        for (size_t j = 0; j < c; ++j) y_out[t * c + j] = y[j] * gt[j];
+    }
+    return 0;
+}
+
 uint32_t orc_argmax(const float* logits, int64_t n) {
     float lm = -1e30f;
     int64_t li = 0;

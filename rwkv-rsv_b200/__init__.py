@@ -16,7 +16,7 @@ LIB_CUDA = _os.path.join(_PKG, "librsv_b200.so")
 LIB_SYNTH = _os.path.join(_PKG, "librsv_synth.so")
 
 __all__ = ["ModelBuilder", "Bundle", "State", "Scheduler", "SamplerParams", "RnnInput", "RnnOption", "ModelInfo", "RsvError", "write_synthetic", "SHAPES",
-           "op_dequant_int8", "op_linear", "op_argmax", "op_sample", "native", "ABI_SYMBOLS"]
+           "op_dequant_int8", "op_linear", "op_wkv7", "op_argmax", "op_sample", "native", "ABI_SYMBOLS"]
 
 
 class RsvError(RuntimeError):
@@ -32,7 +32,7 @@ ABI_SYMBOLS = [
     "rsv_infer_sample", "rsv_infer_sample_selfloop", "rsv_prefill_batch", "rsv_sample_selfloop_submit", "rsv_sample_selfloop_collect",
     "rsv_prof_enable", "rsv_prof_clear", "rsv_prof_dump", "rsv_launch_count", "rsv_timer_start", "rsv_timer_stop", "rsv_synchronize",
     "rsv_sched_new", "rsv_sched_free", "rsv_sched_submit", "rsv_sched_step", "rsv_sched_poll", "rsv_sched_result", "rsv_sched_sync",
-    "rsv_sched_stats", "rsv_op_dequant_int8", "rsv_op_linear", "rsv_op_argmax", "rsv_op_sample", "rsv_op_sample_static",
+    "rsv_sched_stats", "rsv_op_dequant_int8", "rsv_op_linear", "rsv_op_wkv7", "rsv_op_argmax", "rsv_op_sample", "rsv_op_sample_static",
 ]
 
 
@@ -115,6 +115,7 @@ def native():
         L.rsv_op_dequant_int8.argtypes = [_c.c_int, vp, vp, i64, i64, vp]
         L.rsv_op_argmax.argtypes = [_c.c_int, vp, i64, i64, vp]
         L.rsv_op_linear.argtypes = [_c.c_int, _c.c_int, _c.c_int, vp, vp, i64, i64, vp, i64, vp]
+        L.rsv_op_wkv7.argtypes = [_c.c_int, _c.c_int, i64, i64, i64] + [vp] * 15
         L.rsv_op_sample.argtypes = [_c.c_int, vp, i64, i64, vp, vp, i64, vp]
         L.rsv_op_sample_static.argtypes = [_c.c_int, vp, vp, i64, i64, vp, vp, i64, vp]
         _native = L
@@ -488,6 +489,21 @@ def op_linear(x, w, sz=None, path=0, device=0):
     y = _np.empty((xx.shape[0], m), dtype=_np.float32)
     _check(native().rsv_op_linear(device, int(path), wtype, _ptr(ww), szp, m, k, _ptr(xx), xx.shape[0], _ptr(y)))
     return y
+
+
+def op_wkv7(r, k, v, w, a, g, k_k, k_a, r_k, lnx_w, lnx_b, state, vgate=None, vfirst=None, variant=0, device=0):
+    """The WKV-7 step of one layer: inputs [nseg, T, H*64], parameters [H*64], state [nseg, H, 64, 64].  Returns (y, new state)."""
+    rr = _np.ascontiguousarray(r, dtype=_np.float32)
+    nseg, T, C = rr.shape
+    H = C // 64
+    rows = [_np.ascontiguousarray(x, dtype=_np.float32).reshape(nseg, T, C) for x in (k, v, w, a, g)]
+    opt = [None if x is None else _np.ascontiguousarray(x, dtype=_np.float32).reshape(nseg, T, C) for x in (vgate, vfirst)]
+    par = [_np.ascontiguousarray(x, dtype=_np.float32).reshape(C) for x in (k_k, k_a, r_k, lnx_w, lnx_b)]
+    st = _np.array(state, dtype=_np.float32, order="C").reshape(nseg, H, 64, 64)
+    y = _np.empty((nseg, T, C), dtype=_np.float32)
+    _check(native().rsv_op_wkv7(device, int(variant), nseg, T, H, _ptr(rr), *[_ptr(x) for x in rows], *[None if x is None else _ptr(x) for x in opt],
+                                *[_ptr(x) for x in par], _ptr(st), _ptr(y)))
+    return y, st
 
 
 def op_argmax(logits, device=0):

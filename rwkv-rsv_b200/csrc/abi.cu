@@ -726,6 +726,20 @@ int rsv_op_linear(int device, int path, int wtype, const void* w, const uint32_t
         engine_op_linear(*m, path, wtype, w, sz, (int)M, (int)K, x, (int)R, y);
     });
 }
+int rsv_op_wkv7(int device, int variant, int64_t nseg, int64_t T, int64_t H, const float* r, const float* k, const float* v, const float* w, const float* a,
+                const float* g, const float* vgate, const float* vfirst, const float* k_k, const float* k_a, const float* r_k, const float* lnx_w,
+                const float* lnx_b, float* state, float* y) {
+    return guarded([&] {
+        need(r && k && v && w && a && g && k_k && k_a && r_k && lnx_w && lnx_b && state && y, "null argument");
+        need((vgate == nullptr) == (vfirst == nullptr), "wkv7: vgate and vfirst come together");
+        need(nseg >= 1 && T >= 1 && H >= 1, "wkv7: empty input");
+        need(nseg * T * H * 64 <= 0x7fffffffLL && nseg * H * 64 <= 0x7fffffffLL && nseg <= 65535, "wkv7: input too large");
+        select_device(device);
+        const float* in[8] = {r, k, v, w, a, g, vgate, vfirst};
+        const float* par[5] = {k_k, k_a, r_k, lnx_w, lnx_b};
+        engine_op_wkv7(device, variant, (int)nseg, (int)T, (int)H, in, par, state, y);
+    });
+}
 int rsv_op_argmax(int device, const float* logits, int64_t rows, int64_t V, uint32_t* out) {
     return guarded([&] {
         need(logits && out, "null argument");

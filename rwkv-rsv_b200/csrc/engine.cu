@@ -1818,6 +1818,76 @@ void engine_dequant_int8(cudaStream_t stream, const uint8_t* idx_dev, const uint
 }
 
 
+// Operator-level WKV-7 step on host data (see the declaration).  The four kernels are launched as forward_rows launches them.
+void engine_op_wkv7(int device, int variant, int nseg, int T, int H, const float* const in[8], const float* const par[5], float* state_host, float* y_host) {
+    RSV_CUDA(cudaSetDevice(device));
+    const int C = H * kHeadSize, R = nseg * T;
+    const size_t row_bytes = (size_t)R * C * 4, st_floats = (size_t)nseg * H * kHeadSize * kHeadSize;
+    struct Buf {
+        void* p = nullptr;
+        ~Buf() {
+            if (p) cudaFree(p);
+        }
+    };
+    Buf din[8], dpar[5], dstate, dy, dseg, dstatus;
+    for (int i = 0; i < 8; ++i)
+        if (in[i]) {
+            RSV_CUDA(cudaMalloc(&din[i].p, row_bytes));
+            RSV_CUDA(cudaMemcpy(din[i].p, in[i], row_bytes, cudaMemcpyHostToDevice));
+        }
+    for (int i = 0; i < 5; ++i) {
+        RSV_CUDA(cudaMalloc(&dpar[i].p, (size_t)C * 4));
+        RSV_CUDA(cudaMemcpy(dpar[i].p, par[i], (size_t)C * 4, cudaMemcpyHostToDevice));
+    }
+    RSV_CUDA(cudaMalloc(&dstate.p, st_floats * 4));
+    RSV_CUDA(cudaMemcpy(dstate.p, state_host, st_floats * 4, cudaMemcpyHostToDevice));
+    RSV_CUDA(cudaMalloc(&dy.p, row_bytes));
+    RSV_CUDA(cudaMemset(dy.p, 0, row_bytes));
+    std::vector<SegMeta> segs((size_t)nseg);
+    for (int s2 = 0; s2 < nseg; ++s2) segs[s2] = SegMeta{s2 * T, T, s2, 0};
+    RSV_CUDA(cudaMalloc(&dseg.p, segs.size() * sizeof(SegMeta)));
+    RSV_CUDA(cudaMemcpy(dseg.p, segs.data(), segs.size() * sizeof(SegMeta), cudaMemcpyHostToDevice));
+    RSV_CUDA(cudaMalloc(&dstatus.p, 8));
+    RSV_CUDA(cudaMemset(dstatus.p, 0, 8));
+    const float *r = (const float*)din[0].p, *k = (const float*)din[1].p, *v = (const float*)din[2].p, *w = (const float*)din[3].p, *a = (const float*)din[4].p,
+                *g = (const float*)din[5].p, *vgate = (const float*)din[6].p, *vfirst = (const float*)din[7].p;
+    const float *k_k = (const float*)dpar[0].p, *k_a = (const float*)dpar[1].p, *r_k = (const float*)dpar[2].p, *lnx_w = (const float*)dpar[3].p,
+                *lnx_b = (const float*)dpar[4].p;
+    float *state = (float*)dstate.p, *yg = (float*)dy.p;
+    int* status = (int*)dstatus.p;
+    const SegMeta* sm = (const SegMeta*)dseg.p;
+    cudaDeviceProp prop;
+    RSV_CUDA(cudaGetDeviceProperties(&prop, device));
+    const int sms = prop.multiProcessorCount, n_items = H * nseg;
+    if (variant == 0) variant = T > 1 ? (n_items <= sms ? 3 : 4) : (n_items >= 4 * sms ? 2 : 1);
+    if (variant == 1) {
+        wkv7_kernel<<<dim3(H, nseg), kWkvThreads>>>(sm, r, k, v, vgate, vfirst, w, a, g, k_k, k_a, r_k, lnx_w, lnx_b, state, nullptr, yg, H, C);
+    } else if (variant == 2) {
+        CUtensorMap map;
+        encode_state_map(&map, state, (size_t)nseg * H * kHeadSize);
+        RSV_CUDA(cudaFuncSetAttribute(wkv7_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWrSmemBytes));
+        const int ctas = std::min((n_items + kWrPairs - 1) / kWrPairs, sms);
+        wkv7_rows_kernel<<<ctas, kWrThreads, kWrSmemBytes>>>(map, 0LL, sm, n_items, r, k, v, vgate, vfirst, w, a, g, k_k, k_a, r_k, lnx_w, lnx_b, nullptr, yg, H, C, status);
+    } else if (variant == 3 || variant == 4) {
+        if (variant == 3)
+            wkv7_seq_kernel<2><<<dim3(2 * H, nseg), kWsThreads>>>(sm, r, k, v, vgate, vfirst, w, a, g, k_k, k_a, r_k, lnx_w, lnx_b, state, nullptr, yg, H, C, status);
+        else
+            wkv7_seq_kernel<4><<<dim3(H, nseg), kWsThreads>>>(sm, r, k, v, vgate, vfirst, w, a, g, k_k, k_a, r_k, lnx_w, lnx_b, state, nullptr, yg, H, C, status);
+        check_launch("wkv7_seq");
+        wkv7_finish_kernel<<<(R * H + kWsFinishThreads / 32 - 1) / (kWsFinishThreads / 32), kWsFinishThreads>>>(r, k, v, vgate, vfirst, a, g, k_a, r_k, lnx_w, lnx_b, yg,
+                                                                                                              R, H, C);
+    } else {
+        throw std::runtime_error("wkv7: variant must be 0 (automatic), 1 (token kernel), 2 (row-per-lane kernel), 3 or 4 (sequence kernel, head over two CTAs / one CTA)");
+    }
+    check_launch("wkv7");
+    RSV_CUDA(cudaDeviceSynchronize());
+    int st = 0;
+    RSV_CUDA(cudaMemcpy(&st, status, 4, cudaMemcpyDeviceToHost));
+    if (st) throw std::runtime_error("WKV kernel gave up waiting for a staged state (device status " + std::to_string(st) + ")");
+    RSV_CUDA(cudaMemcpy(state_host, state, st_floats * 4, cudaMemcpyDeviceToHost));
+    RSV_CUDA(cudaMemcpy(y_host, yg, row_bytes, cudaMemcpyDeviceToHost));
+}
+
 void engine_op_linear(Model& m, int path, int wtype, const void* w_host, const uint32_t* sz_host, int M, int K, const float* x_host, int R,
                       float* y_host) {
     RSV_CUDA(cudaSetDevice(m.device));

@@ -218,6 +218,10 @@ void engine_sample_raw(cudaStream_t stream, const float* logits_dev, int rows, i
 // Operator-level linear layer on host data: y[R,M] = x[R,K] . W[M,K]^T.  path 0 = SIMT kernel, 1 = tcgen05 kernel.
 void engine_op_linear(Model& m, int path, int wtype, const void* w_host, const uint32_t* sz_host, int M, int K, const float* x_host, int R,
                       float* y_host);
+// Operator-level WKV-7 step of one layer on host data: nseg sessions x T tokens, rows session-major.  in[] = r, k, v, w (decay), a, g,
+// vgate, vfirst ([nseg T, H 64] each; the last two null for the first layer); par[] = k_k, k_a, r_k, lnx_w, lnx_b ([H 64]);
+// state [nseg, H, 64, 64] is updated in place; y = (GroupNorm(S r) + (r . k~ r_k) v) g.  variant: 0 automatic, 1-4 one kernel each.
+void engine_op_wkv7(int device, int variant, int nseg, int T, int H, const float* const in[8], const float* const par[5], float* state_host, float* y_host);
 void engine_dequant_int8(cudaStream_t stream, const uint8_t* idx_dev, const uint32_t* sz_dev, size_t M, size_t K, float* out_dev);
 
 }  // namespace rsv

@@ -155,3 +155,60 @@ def test_linear_tc_is_schedule_independent_and_exact_in_integers():
     want = x.astype(np.int64) @ (idx.astype(np.int64) - 128).T
     got = rsv.op_linear(x, idx, sz, path=1)
     assert np.array_equal(got.astype(np.int64), want)
+
+
+# ---- the WKV-7 step of one layer, each of its kernels on its own --------------------------------------------------------------
+def _wkv_case(nseg, T, H, seed, gate):
+    """Seeded inputs with the forward step's value ranges: decay in (e^-0.61, 1), a and the gates in (0, 1), a state with history."""
+    rng = np.random.default_rng(seed)
+    C = H * 64
+    f = lambda *s: rng.standard_normal(s).astype(np.float32)
+    sig = lambda x: (1.0 / (1.0 + np.exp(-x))).astype(np.float32)
+    d = dict(r=f(nseg, T, C), k=f(nseg, T, C), v=f(nseg, T, C), w=np.exp(-np.exp(-0.5) * sig(f(nseg, T, C) * 2 - 2)).astype(np.float32),
+             a=sig(f(nseg, T, C)), g=f(nseg, T, C), k_k=rng.uniform(0.5, 1.5, C).astype(np.float32), k_a=rng.uniform(0, 1, C).astype(np.float32),
+             r_k=(0.02 * f(C)), lnx_w=(1 + 0.02 * f(C)), lnx_b=(0.02 * f(C)), state=0.1 * f(nseg, H, 64, 64))
+    if gate:
+        d["vgate"], d["vfirst"] = sig(f(nseg, T, C)), f(nseg, T, C)
+    return d
+
+
+def _wkv_oracle(d):
+    nseg = d["r"].shape[0]
+    ys, ss = [], []
+    per_seg = ("r", "k", "v", "w", "a", "g", "vgate", "vfirst", "state")
+    for s in range(nseg):
+        y, st = orc.wkv7(**{k: (v[s] if k in per_seg else v) for k, v in d.items()})
+        ys.append(y)
+        ss.append(st)
+    return np.stack(ys), np.stack(ss)
+
+
+# variant 1 token kernel, 2 row-per-lane kernel (TMA-staged states), 3 / 4 sequence kernel with a head over two CTAs / in one CTA
+@pytest.mark.parametrize("variant,nseg,T,H,gate", [
+    (1, 1, 1, 8, False), (1, 5, 1, 40, True), (1, 3, 7, 8, True),
+    (2, 1, 1, 8, True), (2, 37, 1, 40, True), (2, 100, 1, 8, False), (2, 3, 5, 8, True),
+    (3, 1, 1, 8, True), (3, 1, 33, 8, False), (3, 2, 200, 8, True), (3, 1, 64, 40, True),
+    (4, 1, 1, 8, True), (4, 6, 50, 8, True), (4, 2, 129, 40, False),
+    (0, 1, 1, 40, True), (0, 1, 96, 40, True), (0, 30, 1, 40, True),
+])
+def test_wkv7_kernels_match_cpu_step(variant, nseg, T, H, gate):
+    d = _wkv_case(nseg, T, H, seed=100 * variant + nseg + T, gate=gate)
+    y_want, s_want = _wkv_oracle(d)
+    y, s = rsv.op_wkv7(variant=variant, **d)
+    # same fp32 operations in a different summation order (lanes split the 64-long dot products): a few ulps per token, relative to
+    # the vector's scale; the reference's own kernel tests allow 1e-4 / 1e-3 (src/backend_cuda.rs:8549-8669)
+    assert np.abs(s - s_want).max() <= 2e-5 * max(1.0, float(np.abs(s_want).max()))
+    assert np.abs(y - y_want).max() <= 1e-4 * max(1.0, float(np.abs(y_want).max()))
+
+
+def test_wkv7_kernels_agree_with_each_other_and_reject_bad_arguments():
+    d = _wkv_case(4, 1, 8, seed=9, gate=True)
+    outs = [rsv.op_wkv7(variant=v, **d) for v in (1, 2, 3, 4)]
+    for y, s in outs[1:]:
+        assert np.abs(y - outs[0][0]).max() <= 1e-4 and np.abs(s - outs[0][1]).max() <= 2e-5
+    with pytest.raises(rsv.RsvError, match="variant"):
+        rsv.op_wkv7(variant=9, **d)
+    bad = dict(d)
+    bad.pop("vfirst")
+    with pytest.raises(rsv.RsvError, match="come together"):
+        rsv.op_wkv7(**bad)
