@@ -111,6 +111,10 @@ int rsv_infer_sample_selfloop(rsv_model* m, rsv_state* s, uint32_t seed, int64_t
 /* GpuModel::forward_seq_batch (src/gpu_model.rs:1001-1011): slot b consumes flat[b*t_pad .. b*t_pad+lens[b]).
  * Ragged: only real tokens become rows (the reference pads to t_pad).  seeds_out[b] = last token of slot b. */
 int rsv_prefill_batch(rsv_model* m, rsv_state* s, const uint32_t* flat, const uint32_t* lens, int64_t batch, int64_t t_pad, uint32_t* seeds_out);
+/* GpuModel::forward_seq_batch_mean_hidden (src/gpu_model.rs:1013-1036) with rwkv_segmean (src/backend_cuda.rs:4412-4431): the
+ * state is reset, the prompts are prefilled as above, and mean_out[batch * n_embd] receives per slot the mean over its lens[b]
+ * tokens of the last layer's residual stream (before ln_out), accumulated in token order - the router feature. */
+int rsv_prefill_batch_mean_hidden(rsv_model* m, rsv_state* s, const uint32_t* flat, const uint32_t* lens, int64_t batch, int64_t t_pad, float* mean_out);
 /* GpuModel::submit_sample_selfloop(_batch) (src/gpu_model.rs:732-852, 1639-1781): queues n rounds for `batch`
  * slots without a host round-trip; seeds[b] is slot b's first input token and the base of its RNG seed.
  * sp == NULL selects arg-max instead of sampling. */

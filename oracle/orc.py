@@ -42,6 +42,7 @@ def lib():
         L.orc_state_import.argtypes = [vp, vp]
         L.orc_forward.argtypes = [vp, vp, vp, c.c_int64, vp, vp]
         L.orc_dequant_int8.argtypes = [vp, vp, c.c_int64, c.c_int64, vp]
+        L.orc_mean_hidden.argtypes = [vp, vp, vp, c.c_int64, vp]
         L.orc_wkv7.argtypes = [c.c_int64, c.c_int64] + [vp] * 15
         L.orc_argmax.restype = c.c_uint32
         L.orc_argmax.argtypes = [vp, c.c_int64]
@@ -152,6 +153,15 @@ class OracleModel:
         if rc:
             raise RuntimeError(lib().orc_last_error().decode())
         return allp if full else last
+
+    def mean_hidden(self, tokens):
+        """From a zero state: mean over the tokens of the last layer's residual stream (the router feature)."""
+        toks = np.ascontiguousarray(tokens, dtype=np.uint32)
+        self.reset()
+        out = np.empty(self.n_embd, dtype=np.float32)
+        if lib().orc_mean_hidden(self._h, self._s, _p(toks), toks.size, _p(out)):
+            raise RuntimeError(lib().orc_last_error().decode())
+        return out
 
     def state_back(self):
         out = np.empty(self.state_len, dtype=np.float32)

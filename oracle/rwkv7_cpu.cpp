@@ -292,7 +292,7 @@ State init_state(const Model& m) {  // src/model.rs:365-371
 }
 
 // ---- src/model.rs:374-517 forward, one token ----
-void forward_token(const Model& M, State& st, uint32_t token, float* logits) {
+void forward_token(const Model& M, State& st, uint32_t token, float* logits, float* hidden = nullptr) {
     const Config& cf = M.cfg;
     const size_t c = cf.n_embd, h = cf.n_head, n = cf.head_size;
     const size_t wm = cf.w_mid, am = cf.a_mid, vm = cf.v_mid, gm = cf.g_mid, fh = cf.ffn_hidden;
@@ -408,6 +408,7 @@ void forward_token(const Model& M, State& st, uint32_t token, float* logits) {
         for (size_t j = 0; j < c; ++j) x[j] = x[j] + v2[j];
     }
     st.v_first = v_first;
+    if (hidden) memcpy(hidden, x.data(), c * 4);  // the last layer's residual stream, before ln_out
     if (logits) {
         Vec xn(c);
         layer_norm(x.data(), M.ln_out_w.data(), M.ln_out_b.data(), c, LN_EPS, xn.data());
@@ -616,7 +617,6 @@ int orc_forward(void* m, void* s, const uint32_t* tokens, int64_t n, float* logi
     }
 }
 void orc_dequant_int8(const uint32_t* idx, const uint32_t* sz, int64_t m, int64_t k, float* out) { dequant_int8(idx, sz, (size_t)m, (size_t)k, out); }
-// arg-max with ties -> smaller index (src/backend_cuda.rs:3640-3680)
 // The WKV-7 step of one layer on its own, for one session over T tokens: the same statements, in the same order, as the time-mixing
 // block of forward() above - v lerp (src/model.rs:418-434), kk / k~ / b (:445-460), l2_norm_groups (:716-727), dplr_update (:732-766),
 // dplr_matvec (:769-782), group_norm (:785-797), sum_rk_rk (:801-826), gate.  Rows are [T, H*64]; vgate / vfirst may be null
@@ -679,6 +679,26 @@ int orc_wkv7(int64_t H, int64_t T, const float* r, const float* k, const float* 
     return 0;
 }
 
+// Mean over a prompt's tokens of the last layer's residual stream x (before ln_out), from a zero state: the router feature of
+// forward_seq_batch_mean_hidden (src/gpu_model.rs:1013-1036), accumulated token by token like rwkv_segmean
+// (src/backend_cuda.rs:4412-4431: acc += x[t] in token order, then acc / len).  out [n_embd].
+int orc_mean_hidden(void* m, void* s, const uint32_t* tokens, int64_t n, float* out) {
+    try {
+        const Model& M = *(Model*)m;
+        const size_t c = M.cfg.n_embd;
+        Vec hid(c), acc(c, 0.f);
+        for (int64_t t = 0; t < n; ++t) {
+            forward_token(M, *(State*)s, tokens[t], nullptr, hid.data());
+            for (size_t j = 0; j < c; ++j) acc[j] += hid[j];
+        }
+        for (size_t j = 0; j < c; ++j) out[j] = acc[j] / (float)n;
+        return 0;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return 1;
+    }
+}
+// arg-max with ties -> smaller index (src/backend_cuda.rs:3640-3680)
 uint32_t orc_argmax(const float* logits, int64_t n) {
     float lm = -1e30f;
     int64_t li = 0;

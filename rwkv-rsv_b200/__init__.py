@@ -29,7 +29,7 @@ ABI_SYMBOLS = [
     "rsv_state_batch", "rsv_state_len", "rsv_state_back", "rsv_state_load", "rsv_state_slot_back", "rsv_state_slot_load", "rsv_state_reset",
     "rsv_state_save", "rsv_state_restore", "rsv_state_slot_save", "rsv_state_slot_restore", "rsv_state_slot_copy",
     "rsv_infer_tokens", "rsv_infer_seq", "rsv_infer_chunked", "rsv_infer_full", "rsv_infer_argmax", "rsv_infer_argmax_selfloop",
-    "rsv_infer_sample", "rsv_infer_sample_selfloop", "rsv_prefill_batch", "rsv_sample_selfloop_submit", "rsv_sample_selfloop_collect",
+    "rsv_infer_sample", "rsv_infer_sample_selfloop", "rsv_prefill_batch", "rsv_prefill_batch_mean_hidden", "rsv_sample_selfloop_submit", "rsv_sample_selfloop_collect",
     "rsv_prof_enable", "rsv_prof_clear", "rsv_prof_dump", "rsv_launch_count", "rsv_timer_start", "rsv_timer_stop", "rsv_synchronize",
     "rsv_sched_new", "rsv_sched_free", "rsv_sched_submit", "rsv_sched_step", "rsv_sched_poll", "rsv_sched_result", "rsv_sched_sync",
     "rsv_sched_stats", "rsv_op_dequant_int8", "rsv_op_linear", "rsv_op_wkv7", "rsv_op_argmax", "rsv_op_sample", "rsv_op_sample_static",
@@ -93,6 +93,7 @@ def native():
         L.rsv_infer_sample.argtypes = [vp, vp, vp, i64, _c.POINTER(SamplerParams), vp, i64, vp]
         L.rsv_infer_sample_selfloop.argtypes = [vp, vp, u32, i64, _c.POINTER(SamplerParams), vp]
         L.rsv_prefill_batch.argtypes = [vp, vp, vp, vp, i64, i64, vp]
+        L.rsv_prefill_batch_mean_hidden.argtypes = [vp, vp, vp, vp, i64, i64, vp]
         L.rsv_sample_selfloop_submit.argtypes = [vp, vp, vp, i64, i64, _c.POINTER(SamplerParams), pp]
         L.rsv_sample_selfloop_collect.argtypes = [vp, vp, i64]
         L.rsv_prof_enable.argtypes = [vp, _c.c_int]
@@ -209,6 +210,23 @@ class Model:
         seeds = _np.zeros(batch, dtype=_np.uint32)
         _check(native().rsv_prefill_batch(self._h, state._h, _ptr(flat), _ptr(lens), batch, t_pad, _ptr(seeds)))
         return seeds
+
+    def forward_seq_batch_mean_hidden(self, state, tokens_batch, pad_to=None):
+        """Resets the state, prefills slot b with tokens_batch[b] and returns [batch, n_embd]: per slot the mean over its tokens of the
+        last layer's residual stream (src/gpu_model.rs:1013-1036).  `pad_to` fixes the row pitch of the token matrix (rows past a
+        prompt's length are never read)."""
+        batch = len(tokens_batch)
+        if batch == 0:
+            raise RsvError("forward_seq_batch: empty batch")
+        t_pad = max(1, max(len(t) for t in tokens_batch), int(pad_to or 0))
+        flat = _np.zeros((batch, t_pad), dtype=_np.uint32)
+        lens = _np.zeros(batch, dtype=_np.uint32)
+        for b, t in enumerate(tokens_batch):
+            flat[b, :len(t)] = t
+            lens[b] = len(t)
+        out = _np.empty((batch, self.info().num_emb), dtype=_np.float32)
+        _check(native().rsv_prefill_batch_mean_hidden(self._h, state._h, _ptr(flat), _ptr(lens), batch, t_pad, _ptr(out)))
+        return out
 
     def submit_sample_selfloop_batch(self, state, seeds, n, sp):
         seeds = _tokens(seeds)

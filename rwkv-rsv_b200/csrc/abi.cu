@@ -571,47 +571,76 @@ int rsv_infer_sample_selfloop(rsv_model* m, rsv_state* s, uint32_t seed, int64_t
     });
 }
 
+// forward_seq_batch_core (src/gpu_model.rs:914-997) over packed steps; with `mean_out` also the per-slot mean of the last layer's
+// residual stream (forward_seq_batch_mean_hidden, :1013-1036).
+static void prefill_batch(Model& m, State& st, const uint32_t* flat, const uint32_t* lens, int64_t batch, int64_t t_pad, uint32_t* seeds_out, float* mean_out) {
+    need(batch >= 1 && batch <= 0x7fffffff, "forward_seq_batch: empty batch");      // src/gpu_model.rs:921-923
+    need(t_pad >= 1 && t_pad <= 0x7fffffff, "forward_seq_batch: t_pad must be >= 1");
+    need(st.cap == batch, "forward_seq_batch: state batch differs from the prompts");  // :924-931
+    std::vector<int64_t> len(batch), done(batch, 0);
+    for (int64_t b = 0; b < batch; ++b) {
+        len[b] = std::min<int64_t>(std::max<int64_t>(lens[b], 1), t_pad);  // lens clamp, :947-950
+        check_tokens(m, flat + b * t_pad, len[b]);
+        if (seeds_out) seeds_out[b] = flat[b * t_pad + len[b] - 1];
+    }
+    RSV_CUDA(cudaSetDevice(m.device));
+    const size_t C = m.cfg.n_embd;
+    float* acc = nullptr;
+    struct Free {
+        float*& p;
+        ~Free() {
+            if (p) cudaFree(p);
+        }
+    } guard{acc};
+    if (mean_out) {
+        RSV_CUDA(cudaMalloc(&acc, (size_t)batch * C * 4));
+        RSV_CUDA(cudaMemsetAsync(acc, 0, (size_t)batch * C * 4, m.stream));
+    }
+    // pack chunks of several sessions into steps of at most kMaxChunk rows
+    std::vector<uint32_t> toks;
+    for (;;) {
+        StepPlan p;
+        toks.clear();
+        for (int64_t b = 0; b < batch && (int)p.rows.size() < kMaxChunk; ++b) {
+            const int64_t rem = len[b] - done[b];
+            if (rem <= 0) continue;
+            const int T = (int)std::min<int64_t>(rem, kMaxChunk - (int64_t)p.rows.size());
+            const int start = (int)p.rows.size(), seg = (int)p.segs.size();
+            for (int r = 0; r < T; ++r) {
+                p.rows.push_back(RowMeta{(int)b, r > 0 ? 1 : 0, r == T - 1 ? 1 : 0, seg});
+                toks.push_back(flat[b * t_pad + done[b] + r]);
+            }
+            p.segs.push_back(SegMeta{start, T, (int)b, 0});
+            if (T > 1) p.multi_row_segments = true;
+            done[b] += T;
+        }
+        if (p.rows.empty()) break;
+        m.upload_plan(p);
+        RSV_CUDA(cudaMemcpyAsync(m.ws.tokens, toks.data(), toks.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, m.stream));
+        m.forward_rows(st, p, false);
+        if (mean_out) engine_segment_sums(m, (int)p.segs.size(), acc);
+        RSV_CUDA(cudaStreamSynchronize(m.stream));  // `toks` is reused by the next step
+    }
+    m.check_status();
+    if (mean_out) {
+        RSV_CUDA(cudaMemcpy(mean_out, acc, (size_t)batch * C * 4, cudaMemcpyDeviceToHost));
+        for (int64_t b = 0; b < batch; ++b)
+            for (size_t c = 0; c < C; ++c) mean_out[b * C + c] = mean_out[b * C + c] / (float)len[b];  // acc / (float)len, src/backend_cuda.rs:4429
+    }
+}
 int rsv_prefill_batch(rsv_model* mh, rsv_state* sh, const uint32_t* flat, const uint32_t* lens, int64_t batch, int64_t t_pad, uint32_t* seeds_out) {
     return guarded([&] {
         need(mh && sh && flat && lens && seeds_out, "null argument");
-        Model& m = *mh->m;
-        State& st = sh->s;
-        need(st.model == &m, "state belongs to a different model");
-        need(batch >= 1 && batch <= 0x7fffffff, "forward_seq_batch: empty batch");      // src/gpu_model.rs:921-923
-        need(t_pad >= 1 && t_pad <= 0x7fffffff, "forward_seq_batch: t_pad must be >= 1");
-        need(st.cap == batch, "forward_seq_batch: state batch differs from the prompts");  // :924-931
-        std::vector<int64_t> len(batch), done(batch, 0);
-        for (int64_t b = 0; b < batch; ++b) {
-            len[b] = std::min<int64_t>(std::max<int64_t>(lens[b], 1), t_pad);  // lens clamp, :947-950
-            check_tokens(m, flat + b * t_pad, len[b]);
-            seeds_out[b] = flat[b * t_pad + len[b] - 1];
-        }
-        RSV_CUDA(cudaSetDevice(m.device));
-        // pack chunks of several sessions into steps of at most kMaxChunk rows
-        std::vector<uint32_t> toks;
-        for (;;) {
-            StepPlan p;
-            toks.clear();
-            for (int64_t b = 0; b < batch && (int)p.rows.size() < kMaxChunk; ++b) {
-                const int64_t rem = len[b] - done[b];
-                if (rem <= 0) continue;
-                const int T = (int)std::min<int64_t>(rem, kMaxChunk - (int64_t)p.rows.size());
-                const int start = (int)p.rows.size(), seg = (int)p.segs.size();
-                for (int r = 0; r < T; ++r) {
-                    p.rows.push_back(RowMeta{(int)b, r > 0 ? 1 : 0, r == T - 1 ? 1 : 0, seg});
-                    toks.push_back(flat[b * t_pad + done[b] + r]);
-                }
-                p.segs.push_back(SegMeta{start, T, (int)b, 0});
-                if (T > 1) p.multi_row_segments = true;
-                done[b] += T;
-            }
-            if (p.rows.empty()) break;
-            m.upload_plan(p);
-            RSV_CUDA(cudaMemcpyAsync(m.ws.tokens, toks.data(), toks.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, m.stream));
-            m.forward_rows(st, p, false);
-            RSV_CUDA(cudaStreamSynchronize(m.stream));  // `toks` is reused by the next step
-        }
-        m.check_status();
+        need(sh->s.model == mh->m.get(), "state belongs to a different model");
+        prefill_batch(*mh->m, sh->s, flat, lens, batch, t_pad, seeds_out, nullptr);
+    });
+}
+int rsv_prefill_batch_mean_hidden(rsv_model* mh, rsv_state* sh, const uint32_t* flat, const uint32_t* lens, int64_t batch, int64_t t_pad, float* mean_out) {
+    return guarded([&] {
+        need(mh && sh && flat && lens && mean_out, "null argument");
+        need(sh->s.model == mh->m.get(), "state belongs to a different model");
+        need(rsv_state_reset(sh) == 0, "state reset failed");  // the feature starts from a zero state (src/gpu_model.rs:1024)
+        prefill_batch(*mh->m, sh->s, flat, lens, batch, t_pad, nullptr, mean_out);
     });
 }
 

@@ -203,6 +203,12 @@ __host__ __device__ inline int ds_head_of_cta(int cta, int l, int H, int G) {
     const int h = d / stride;
     return h < H ? h : -1;
 }
+// two fp16 packed in a 32-bit register -> two floats (no address of a local is taken, so nothing goes through local memory)
+__device__ __forceinline__ float2 ds_half2_bits_to_float2(uint32_t u) {
+    float2 f;
+    asm("{\n\t.reg .f16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}" : "=f"(f.x), "=f"(f.y) : "r"(u));
+    return f;
+}
 // exact sum of a 64-bit value over the warp whose magnitude is below 2^40 per lane (two 32-bit reductions)
 __device__ __forceinline__ long long ds_warp_sum_ll(long long v) {
     const unsigned lo = __reduce_add_sync(0xffffffffu, (unsigned)(v & 0xFFFF));
@@ -507,16 +513,26 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
         char* part = reinterpret_cast<char*>(S->part) + part_off + piece * kDsTileRows * slot;
         if (i8) {
             int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+            // operands of the next step are loaded before this step's products are issued (the loop is a chain of shared-memory
+            // latency + MMA latency otherwise)
+            uint4 a0 = ds_ldmatrix4(aaddr), a1 = ds_ldmatrix4(aaddr + 32);
+            uint4 b = make_uint4(0, 0, 0, 0);
+            if (bcol_ok) b = ds_lds128(baddr);
 #pragma unroll 2
-            for (int s2 = 0; s2 < steps; ++s2) {
-                const uint4 a0 = ds_ldmatrix4(aaddr), a1 = ds_ldmatrix4(aaddr + 32);
-                uint4 b = make_uint4(0, 0, 0, 0);
-                if (bcol_ok) b = ds_lds128(baddr);
-                ds_mma_i8(c0, a0, b.x, b.y);
-                ds_mma_i8(c1, a1, b.z, b.w);
+            for (int s2 = 1; s2 < steps; ++s2) {
                 aaddr += 64;
                 baddr += bstep;
+                const uint4 n0 = ds_ldmatrix4(aaddr), n1 = ds_ldmatrix4(aaddr + 32);
+                uint4 nb = make_uint4(0, 0, 0, 0);
+                if (bcol_ok) nb = ds_lds128(baddr);
+                ds_mma_i8(c0, a0, b.x, b.y);
+                ds_mma_i8(c1, a1, b.z, b.w);
+                a0 = n0;
+                a1 = n1;
+                b = nb;
             }
+            ds_mma_i8(c0, a0, b.x, b.y);
+            ds_mma_i8(c1, a1, b.z, b.w);
             // accumulator (rows g, g + 8; columns 2 t, 2 t + 1) = weight rows x digits 2 t, 2 t + 1 (t < 2); digit d weighs 256^d
             const int lo = t < 2 ? 16 * t : 0;
             long long va = t < 2 ? (((long long)(c0[0] + c1[0]) << lo) + ((long long)(c0[1] + c1[1]) << (lo + 8))) : 0;
@@ -529,16 +545,24 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
             }
         } else {
             float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+            uint4 a0 = ds_ldmatrix4(aaddr), a1 = ds_ldmatrix4(aaddr + 32);
+            uint4 b = make_uint4(0, 0, 0, 0);
+            if (bcol_ok) b = ds_lds128(baddr);
 #pragma unroll 2
-            for (int s2 = 0; s2 < steps; ++s2) {
-                const uint4 a0 = ds_ldmatrix4(aaddr), a1 = ds_ldmatrix4(aaddr + 32);
-                uint4 b = make_uint4(0, 0, 0, 0);
-                if (bcol_ok) b = ds_lds128(baddr);
-                ds_mma_f16(c0, a0, b.x, b.y);
-                ds_mma_f16(c1, a1, b.z, b.w);
+            for (int s2 = 1; s2 < steps; ++s2) {
                 aaddr += 64;
                 baddr += bstep;
+                const uint4 n0 = ds_ldmatrix4(aaddr), n1 = ds_ldmatrix4(aaddr + 32);
+                uint4 nb = make_uint4(0, 0, 0, 0);
+                if (bcol_ok) nb = ds_lds128(baddr);
+                ds_mma_f16(c0, a0, b.x, b.y);
+                ds_mma_f16(c1, a1, b.z, b.w);
+                a0 = n0;
+                a1 = n1;
+                b = nb;
             }
+            ds_mma_f16(c0, a0, b.x, b.y);
+            ds_mma_f16(c1, a1, b.z, b.w);
             if (t == 0) {  // columns 0, 1 = hi, lo
                 reinterpret_cast<float*>(part)[g] = (c0[0] + c1[0]) + (c0[1] + c1[1]);
                 reinterpret_cast<float*>(part)[g + 8] = (c0[2] + c1[2]) + (c0[3] + c1[3]);
@@ -607,7 +631,14 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
     do {                                                                                      \
         if (P.dbg && wtid == 0 && t == 1 && l == 1) P.dbg[256 + cta * 16 + (k)] = ds_now0(); \
     } while (0)
+#define DS_PSTAMP(id)                                                                 \
+    do {                                                                              \
+        if (P.dbg && cta == 0 && lane == 0 && t == 1 && l == 1) P.dbg[id] = ds_now(); \
+    } while (0)
 #else
+#define DS_PSTAMP(id) \
+    do {              \
+    } while (0)
 #define DS_STAMP(id) \
     do {             \
     } while (0)
@@ -761,13 +792,21 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
             const bool do_head = P.argmax_feed || t == P.n_tokens - 1;
             for (int l = 0; l < P.L && ok; ++l) {
                 src = P.wstream + ((size_t)l * G + cta) * (size_t)P.wslot;
+                DS_PSTAMP(40);
                 if (!(ok = put_phase(DSP_P1, l == 0))) break;
+                DS_PSTAMP(41);
                 if (ds_head_of_cta(cta, l, P.H, G) >= 0) {
                     // chunk A: w2, a2 rows of the head; chunk B: v2 rows (layers > 0) and the first 32 g2 rows; chunk C: the other 32
                     const int vb = l > 0 ? 64 * P.vm * 2 : 0;
-                    if (!(ok = put_raw(hbA) && put_raw(vb + hbC) && put_raw(hbC))) break;
+                    if (!(ok = put_raw(hbA))) break;
+                    DS_PSTAMP(42);
+                    if (!(ok = put_raw(vb + hbC) && put_raw(hbC))) break;
+                    DS_PSTAMP(43);
                 }
-                ok = put_phase(DSP_P3, false) && put_phase(DSP_P4, false) && put_phase(DSP_P5, false);
+                ok = put_phase(DSP_P3, false);
+                DS_PSTAMP(44);
+                ok = ok && put_phase(DSP_P4, false) && put_phase(DSP_P5, false);
+                DS_PSTAMP(45);
             }
             if (ok && do_head) {
                 src = P.hstream + (size_t)cta * (size_t)P.hslot;
@@ -962,7 +1001,6 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         const int drow = (wtid & 255) >> 2, quad = wtid & 3, dch = h * 64 + drow;
                         const bool upper = wtid >= 256;
                         float* srow = wkv_l + ((size_t)h * 64 + rrow) * 64 + oct * 8;
-                        const float4 s4a = ds_ldcg4(srow), s4b = ds_ldcg4(srow + 4);
                         const float p_w0 = __ldg(Ly.w0 + dch), p_a0 = __ldg(Ly.a0 + dch), p_kk = __ldg(Ly.k_k + dch), p_ka = __ldg(Ly.k_a + dch), p_rk = __ldg(Ly.r_k + dch);
                         const float p_v0 = l > 0 ? __ldg(Ly.v0 + dch) : 0.f;
                         const float p_gw = __ldg(Ly.lnx_w + ch), p_gb = __ldg(Ly.lnx_b + ch);
@@ -991,8 +1029,8 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                                 for (int q = 0; q < ql; q += 8) {
                                     const uint4 pk = *reinterpret_cast<const uint4*>(wrow + q);
                                     const float4 x0 = *reinterpret_cast<const float4*>(vv + q), x1 = *reinterpret_cast<const float4*>(vv + q + 4);
-                                    const __half2* h2 = reinterpret_cast<const __half2*>(&pk);
-                                    const float2 f0 = __half22float2(h2[0]), f1 = __half22float2(h2[1]), f2 = __half22float2(h2[2]), f3 = __half22float2(h2[3]);
+                                    const float2 f0 = ds_half2_bits_to_float2(pk.x), f1 = ds_half2_bits_to_float2(pk.y), f2 = ds_half2_bits_to_float2(pk.z),
+                                                 f3 = ds_half2_bits_to_float2(pk.w);
                                     a0 = fmaf(f0.x, x0.x, a0);
                                     a1 = fmaf(f0.y, x0.y, a1);
                                     a0 = fmaf(f1.x, x0.z, a0);
@@ -1022,6 +1060,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                             ok = false;
                             break;
                         }
+                        DS_STAMP(55);
                         const uint8_t* cA = ring + S->desc[iA % kDsBars].ring_off;
                         float dw = 0.f, da = 0.f, dv = 0.f, dg = 0.f;
                         if (!upper) {
@@ -1029,6 +1068,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                             dw = dot_q(w2s + (size_t)drow * P.wm, P.wm, sc_mid);
                             da = dot_q(w2s + (size_t)64 * P.wm + (size_t)drow * P.am, P.am, sc_mid + P.wm);
                         }
+                        DS_STAMP(57);
                         if (P.head_early && !upper) {
                             // the ring cannot hold all three chunks: the first goes back as soon as the 8 warps that read it are done
                             asm volatile("bar.sync 2, 256;" ::: "memory");
@@ -1038,6 +1078,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                             ok = false;
                             break;
                         }
+                        DS_STAMP(56);
                         const uint8_t* cB = ring + S->desc[iB % kDsBars].ring_off;
                         const uint8_t* cC = ring + S->desc[iC % kDsBars].ring_off;
                         if (upper) {
@@ -1046,6 +1087,9 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         } else if (l > 0) {
                             dv = dot_q(reinterpret_cast<const __half*>(cB) + (size_t)drow * P.vm, P.vm, sc_mid + P.wm + P.am);
                         }
+                        // this thread's eight state elements: requested only now, so that they do not occupy registers during the dot products
+                        // (the epilogue below and the block-wide sums cover most of their latency)
+                        const float4 s4a = ds_ldcg4(srow), s4b = ds_ldcg4(srow + 4);
                         // per-channel quantities of the head -> shared memory; ||kk||^2 and the bonus sum over the 64 channels
                         float ssp = 0.f, srp = 0.f;
                         if (quad == 0) {

@@ -1013,6 +1013,8 @@ void Model::forward_rows(State& st, const StepPlan& plan, bool use_cursor) {
             pending = ws.delta;
         }
     }
+    ws.final_x = x_cur;
+    ws.final_delta = pending;
     if (O) {
         LAUNCH(*this, "ln_out") {
             ln_rows_kernel<<<O, kRowThreads, 0, stream>>>(x_cur, pending, ln_out_w, ln_out_b, ws.out_rows, C, ws.xn);
@@ -1695,11 +1697,12 @@ void Model::run_stream(State& st, int slot, int n_tokens, bool tok_from_list, bo
         for (int i = 1; i < 8; ++i) fprintf(stderr, " %.2f", (h[200 + i] - h[200 + i - 1]) / 1e3);
         fprintf(stderr, "\n");
         fprintf(stderr, "  P1 operands: magnitudes %.2f, barrier %.2f, digits written %.2f\n", (h[52] - h[0]) / 1e3, (h[53] - h[0]) / 1e3, (h[54] - h[0]) / 1e3);
-        fprintf(stderr, "  heads: vectors gathered %.2f, dot products done %.2f, state updated %.2f\n", (h[18] - h[0]) / 1e3, (h[19] - h[0]) / 1e3, (h[50] - h[0]) / 1e3);
+        fprintf(stderr, "  heads: vectors gathered %.2f, first chunk there %.2f, its dot products done %.2f, all three there %.2f, dot products done %.2f, state updated %.2f\n", (h[18] - h[0]) / 1e3,
+                (h[55] - h[0]) / 1e3, (h[57] - h[0]) / 1e3, (h[56] - h[0]) / 1e3, (h[19] - h[0]) / 1e3, (h[50] - h[0]) / 1e3);
         const char* ph[4] = {"P1", "P3", "P4", "P5"};
         for (int i = 0; i < 4; ++i)
             fprintf(stderr, "  %s rows, consumer warp 0: %lld chunks, %.2f us waiting for them, %.2f us multiplying\n", ph[i], h[20 + 4 * i + 2], h[20 + 4 * i] / 1e3, h[20 + 4 * i + 1] / 1e3);
-        fprintf(stderr, "  producer: P1 rows issued %.2f .. %.2f, later phases start %.2f, att.out issued %.2f, ffn.key %.2f, ffn.value %.2f\n", (h[40] - h[0]) / 1e3,
+        fprintf(stderr, "  producer: P1 rows issued %.2f .. %.2f, head chunk A issued %.2f, C issued %.2f, att.out issued %.2f, ffn.value issued %.2f\n", (h[40] - h[0]) / 1e3,
                 (h[41] - h[0]) / 1e3, (h[42] - h[0]) / 1e3, (h[43] - h[0]) / 1e3, (h[44] - h[0]) / 1e3, (h[45] - h[0]) / 1e3);
         for (int w = 0; w < 16; ++w)
             fprintf(stderr, "  P1 warp %2d: last chunk wait %.2f .. %.2f, multiplied %.2f, tile finished %.2f\n", w, (h[64 + 4 * w] - h[0]) / 1e3, (h[65 + 4 * w] - h[0]) / 1e3,
@@ -1817,6 +1820,14 @@ void engine_dequant_int8(cudaStream_t stream, const uint8_t* idx_dev, const uint
     check_launch("dequant_int8");
 }
 
+
+void engine_segment_sums(Model& m, int n_segments, float* acc_dev) {
+    if (!m.ws.final_x) throw std::runtime_error("segment sums: no step has run");
+    LAUNCH(m, "segment_sums") {
+        segment_sums_kernel<<<dim3(n_segments, (m.cfg.n_embd + 255) / 256), 256, 0, m.stream>>>(m.ws.final_x, m.ws.final_delta, m.ws.seg_meta, m.cfg.n_embd, acc_dev);
+        check_launch("segment_sums");
+    }
+}
 
 // Operator-level WKV-7 step on host data (see the declaration).  The four kernels are launched as forward_rows launches them.
 void engine_op_wkv7(int device, int variant, int nseg, int T, int H, const float* const in[8], const float* const par[5], float* state_host, float* y_host) {

@@ -49,6 +49,7 @@ struct LayerW {
 
 struct Workspace {
     int rows = 0, outs = 0, segs = 0;  // capacities
+    const float *final_x = nullptr, *final_delta = nullptr;  // after forward_rows: the last layer's residual stream of row i is final_x[i] + final_delta[i]
     float *x = nullptr, *x2 = nullptr, *delta = nullptr, *xmix = nullptr, *r = nullptr, *k = nullptr, *v = nullptr, *w = nullptr, *a = nullptr, *g = nullptr;
     float *yg = nullptr, *xb = nullptr, *mid = nullptr, *h = nullptr, *vfirst = nullptr, *xn = nullptr, *logits = nullptr, *staging = nullptr;
     // tensor-core linear path: B operands, per-row scales, fixed-point sums, split-K partials (grown on demand)
@@ -222,6 +223,8 @@ void engine_op_linear(Model& m, int path, int wtype, const void* w_host, const u
 // vgate, vfirst ([nseg T, H 64] each; the last two null for the first layer); par[] = k_k, k_a, r_k, lnx_w, lnx_b ([H 64]);
 // state [nseg, H, 64, 64] is updated in place; y = (GroupNorm(S r) + (r . k~ r_k) v) g.  variant: 0 automatic, 1-4 one kernel each.
 void engine_op_wkv7(int device, int variant, int nseg, int T, int H, const float* const in[8], const float* const par[5], float* state_host, float* y_host);
+// acc[slot of segment][c] += sum over the segment's rows, in row order, of the last layer's residual stream left by forward_rows
+void engine_segment_sums(Model& m, int n_segments, float* acc_dev);
 void engine_dequant_int8(cudaStream_t stream, const uint8_t* idx_dev, const uint32_t* sz_dev, size_t M, size_t K, float* out_dev);
 
 }  // namespace rsv

@@ -858,6 +858,22 @@ __global__ void __launch_bounds__(kSampleThreads) sample_rows_kernel(const float
 
 // Continuous batching: the input token of row r is either a prompt token supplied by the host or, for a decode
 // row (host value 0xFFFFFFFF), the token last generated for the row's session, which never left the GPU.
+// Per-session sum of the last layer's residual stream over a step's rows (the accumulation of rwkv_segmean,
+// src/backend_cuda.rs:4412-4431: acc += x[t] in token order; the caller divides by the prompt length at the end).  A prompt
+// longer than a step continues the same accumulator in the next step, so the order of the additions is the token order.
+// Grid (segments, ceil(C / 256)).
+__global__ void segment_sums_kernel(const float* __restrict__ x, const float* __restrict__ delta, const SegMeta* __restrict__ segs, int C, float* __restrict__ acc) {
+    const SegMeta sg = segs[blockIdx.x];
+    const int c = blockIdx.y * 256 + threadIdx.x;
+    if (c >= C) return;
+    float a = acc[(size_t)sg.slot * C + c];
+    for (int t = 0; t < sg.len; ++t) {
+        const size_t i = (size_t)(sg.start + t) * C + c;
+        a += delta ? x[i] + delta[i] : x[i];
+    }
+    acc[(size_t)sg.slot * C + c] = a;
+}
+
 __global__ void merge_tokens_kernel(const uint32_t* __restrict__ host_tok, const RowMeta* __restrict__ rows, const uint32_t* __restrict__ slot_tok, int R,
                                     uint32_t* __restrict__ tokens) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;

@@ -273,3 +273,25 @@ def test_kernel_profile_and_launch_count(bundles):
     prof = b.model.kernel_prof()
     assert prof["wkv7"]["launches"] == 3 * 4 and prof["linear_head"]["launches"] == 1
     assert b.model.launch_count() == sum(v["launches"] for v in prof.values())
+
+
+def test_batch_mean_hidden_matches_cpu_path(bundles, oracles):
+    # forward_seq_batch_mean_hidden (src/gpu_model.rs:1013-1036): per slot the token mean of the last layer's residual stream,
+    # from a zero state whatever the state held before; ragged lengths, one prompt longer than a packed step
+    m, o = bundles["int8"].model, oracles["int8"]
+    rng = np.random.default_rng(21)
+    prompts = [rng.integers(0, m.info().num_vocab, size=k).astype(np.uint32) for k in (1, 7, 40, 1300)]
+    st = m.create_batch_state(len(prompts))
+    try:
+        m.forward_seq_batch(st, [p[:5] for p in prompts])  # something to reset
+        feat = m.forward_seq_batch_mean_hidden(st, prompts, pad_to=1536)
+        assert feat.shape == (4, m.info().num_emb)
+        for b, p in enumerate(prompts):
+            want = o.mean_hidden(p)
+            assert np.abs(feat[b] - want).max() <= 1e-4 * max(1.0, float(np.abs(want).max())), b
+            assert np.abs(st.slot_back(b) - o.state_back()).max() <= 1e-4 * max(1.0, float(np.abs(o.state_back()).max())), b
+        again = m.forward_seq_batch_mean_hidden(st, prompts)  # deterministic, and independent of the row pitch
+        assert np.array_equal(again, feat)
+    finally:
+        st.close()
+        o.reset()
