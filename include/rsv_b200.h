@@ -165,6 +165,11 @@ int rsv_synchronize(rsv_model* m);
 /* ---- operator-level entry points (host buffers in and out; used for kernel parity tests) ------ */
 /* int8 container decode, w = scale*q + zero in fp32 (dequant_int8, src/model.rs:234-252): out[M*K]. */
 int rsv_op_dequant_int8(int device, const uint8_t* idx, const uint32_t* sz, int64_t M, int64_t K, float* out);
+/* The reference's offline int8 quantiser for one matrix (quantize_int8_matrix, tools/quantize_any4.py:241-300): w[M*K] f32 ->
+ * idx_out u8 [M,K] and sz_out u32 [M,K/128] (scale fp16 | zero fp16 << 16), per group of 128: zero = min, scale = (max - min) /
+ * 255, q = clip(round-half-even((w - zero) / scale), 0, 255); a constant group gets scale 0.  Bit for bit what the numpy tool
+ * writes, so a checkpoint quantised here loads in the reference and the other way round. */
+int rsv_quantize_int8(int device, const float* w, int64_t M, int64_t K, uint8_t* idx_out, uint32_t* sz_out);
 /* One linear layer on its own: y[R*M] = x[R*K] . W[M,K]^T with W either fp16 (wtype 0, sz NULL) or the int8 container
  * (wtype 1: w = u8 [M,K], sz = u32 [M,K/128]).  path 0 = SIMT weight-streaming kernel, 1 = tcgen05 tensor-core kernel.
  * Stands in for the reference's per-kernel GEMV/GEMM unit tests (gemv_f16, gemv_variant, gemm; src/backend_cuda.rs:7440-7480,

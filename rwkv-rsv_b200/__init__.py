@@ -16,7 +16,7 @@ LIB_CUDA = _os.path.join(_PKG, "librsv_b200.so")
 LIB_SYNTH = _os.path.join(_PKG, "librsv_synth.so")
 
 __all__ = ["ModelBuilder", "Bundle", "State", "Scheduler", "SamplerParams", "RnnInput", "RnnOption", "ModelInfo", "RsvError", "write_synthetic", "SHAPES",
-           "op_dequant_int8", "op_linear", "op_wkv7", "op_argmax", "op_sample", "native", "ABI_SYMBOLS"]
+           "quantize_int8", "op_dequant_int8", "op_linear", "op_wkv7", "op_argmax", "op_sample", "native", "ABI_SYMBOLS"]
 
 
 class RsvError(RuntimeError):
@@ -32,7 +32,7 @@ ABI_SYMBOLS = [
     "rsv_infer_sample", "rsv_infer_sample_selfloop", "rsv_prefill_batch", "rsv_prefill_batch_mean_hidden", "rsv_sample_selfloop_submit", "rsv_sample_selfloop_collect",
     "rsv_prof_enable", "rsv_prof_clear", "rsv_prof_dump", "rsv_launch_count", "rsv_timer_start", "rsv_timer_stop", "rsv_synchronize",
     "rsv_sched_new", "rsv_sched_free", "rsv_sched_submit", "rsv_sched_step", "rsv_sched_poll", "rsv_sched_result", "rsv_sched_sync",
-    "rsv_sched_stats", "rsv_op_dequant_int8", "rsv_op_linear", "rsv_op_wkv7", "rsv_op_argmax", "rsv_op_sample", "rsv_op_sample_static",
+    "rsv_sched_stats", "rsv_quantize_int8", "rsv_op_dequant_int8", "rsv_op_linear", "rsv_op_wkv7", "rsv_op_argmax", "rsv_op_sample", "rsv_op_sample_static",
 ]
 
 
@@ -114,6 +114,7 @@ def native():
         L.rsv_sched_sync.argtypes = [vp]
         L.rsv_sched_stats.argtypes = [vp, _c.POINTER(i64), _c.POINTER(i64)]
         L.rsv_op_dequant_int8.argtypes = [_c.c_int, vp, vp, i64, i64, vp]
+        L.rsv_quantize_int8.argtypes = [_c.c_int, vp, i64, i64, vp, vp]
         L.rsv_op_argmax.argtypes = [_c.c_int, vp, i64, i64, vp]
         L.rsv_op_linear.argtypes = [_c.c_int, _c.c_int, _c.c_int, vp, vp, i64, i64, vp, i64, vp]
         L.rsv_op_wkv7.argtypes = [_c.c_int, _c.c_int, i64, i64, i64] + [vp] * 15
@@ -485,6 +486,15 @@ class ModelBuilder:
 
 
 # ---- operator-level entry points (kernel parity tests) ----
+def quantize_int8(w, device=0):
+    """The reference's per-group (128) asymmetric int8 quantiser (tools/quantize_any4.py:241-300): float [M,K] -> (idx u8 [M,K], sz u32 [M,K/128])."""
+    ww = _np.ascontiguousarray(w, dtype=_np.float32)
+    m, k = ww.shape
+    idx, sz = _np.empty((m, k), dtype=_np.uint8), _np.empty((m, k // 128), dtype=_np.uint32)
+    _check(native().rsv_quantize_int8(device, _ptr(ww), m, k, _ptr(idx), _ptr(sz)))
+    return idx, sz
+
+
 def op_dequant_int8(idx_u8, sz_u32, device=0):
     idx = _np.ascontiguousarray(idx_u8, dtype=_np.uint8)
     sz = _np.ascontiguousarray(sz_u32, dtype=_np.uint32)

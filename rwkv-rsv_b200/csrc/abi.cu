@@ -744,6 +744,19 @@ int rsv_op_dequant_int8(int device, const uint8_t* idx, const uint32_t* sz, int6
         RSV_CUDA(cudaMemcpy(out, dout.p, (size_t)M * K * 4, cudaMemcpyDeviceToHost));
     });
 }
+int rsv_quantize_int8(int device, const float* w, int64_t M, int64_t K, uint8_t* idx_out, uint32_t* sz_out) {
+    return guarded([&] {
+        need(w && idx_out && sz_out, "null argument");
+        need(M >= 1 && K >= 128 && K % 128 == 0, "quantize_int8: K must be a positive multiple of 128");  // assert K % group == 0, tools/quantize_any4.py:253
+        need(M <= 0x7fffffff && K <= 0x7fffffff, "quantize_int8: matrix too large");
+        select_device(device);
+        DevBuf dw((size_t)M * K * 4), di((size_t)M * K), dz((size_t)M * (K / 128) * 4);
+        RSV_CUDA(cudaMemcpy(dw.p, w, (size_t)M * K * 4, cudaMemcpyHostToDevice));
+        engine_quantize_int8(nullptr, (const float*)dw.p, (size_t)M, (size_t)K, (uint8_t*)di.p, (uint32_t*)dz.p);
+        RSV_CUDA(cudaMemcpy(idx_out, di.p, (size_t)M * K, cudaMemcpyDeviceToHost));
+        RSV_CUDA(cudaMemcpy(sz_out, dz.p, (size_t)M * (K / 128) * 4, cudaMemcpyDeviceToHost));
+    });
+}
 int rsv_op_linear(int device, int path, int wtype, const void* w, const uint32_t* sz, int64_t M, int64_t K, const float* x, int64_t R, float* y) {
     return guarded([&] {
         need(w && x && y, "null argument");

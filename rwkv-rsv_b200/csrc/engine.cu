@@ -1821,6 +1821,13 @@ void engine_dequant_int8(cudaStream_t stream, const uint8_t* idx_dev, const uint
 }
 
 
+void engine_quantize_int8(cudaStream_t stream, const float* w_dev, size_t M, size_t K, uint8_t* idx_dev, uint32_t* sz_dev) {
+    const size_t groups = M * (K / 128);
+    const int blocks = (int)std::min<size_t>((groups + 7) / 8, 148 * 16);
+    quantize_int8_kernel<<<blocks, 256, 0, stream>>>(w_dev, groups, idx_dev, sz_dev);
+    check_launch("quantize_int8");
+}
+
 void engine_segment_sums(Model& m, int n_segments, float* acc_dev) {
     if (!m.ws.final_x) throw std::runtime_error("segment sums: no step has run");
     LAUNCH(m, "segment_sums") {

@@ -225,6 +225,7 @@ void engine_op_linear(Model& m, int path, int wtype, const void* w_host, const u
 void engine_op_wkv7(int device, int variant, int nseg, int T, int H, const float* const in[8], const float* const par[5], float* state_host, float* y_host);
 // acc[slot of segment][c] += sum over the segment's rows, in row order, of the last layer's residual stream left by forward_rows
 void engine_segment_sums(Model& m, int n_segments, float* acc_dev);
+void engine_quantize_int8(cudaStream_t stream, const float* w_dev, size_t M, size_t K, uint8_t* idx_dev, uint32_t* sz_dev);
 void engine_dequant_int8(cudaStream_t stream, const uint8_t* idx_dev, const uint32_t* sz_dev, size_t M, size_t K, float* out_dev);
 
 }  // namespace rsv

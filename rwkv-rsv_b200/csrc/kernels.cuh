@@ -894,4 +894,36 @@ __global__ void dequant_int8_kernel(const uint8_t* __restrict__ idx, const uint3
     }
 }
 
+// Per-group asymmetric int8 quantiser of the reference's offline tool (quantize_int8_matrix, tools/quantize_any4.py:241-300), group
+// = 128 weights of a row: zero = min, scale = (max - min) / 255 (a constant group: scale 0, every q = 0),
+// q = clip(rint((w - zero) / scale), 0, 255) with the quotient an IEEE fp32 division and ties to even, as numpy evaluates it; the
+// container stores scale and zero as fp16 (round to nearest even), packed zero << 16 | scale.  One warp per group: four weights
+// per lane, min and max by shuffles.  Grid-stride over the M * K / 128 groups.
+__global__ void quantize_int8_kernel(const float* __restrict__ w, size_t groups, uint8_t* __restrict__ idx, uint32_t* __restrict__ sz) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t g = warp; g < groups; g += nwarps) {
+        const float4 x = reinterpret_cast<const float4*>(w + g * 128)[lane];
+        float mn = fminf(fminf(x.x, x.y), fminf(x.z, x.w)), mx = fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+        const float span = __fsub_rn(mx, mn);
+        const bool flat = span == 0.0f;
+        const float scale = __fdiv_rn(flat ? 1.0f : span, 255.0f);
+        const float in[4] = {x.x, x.y, x.z, x.w};
+        uint32_t packed = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float q = fminf(fmaxf(rintf(__fdiv_rn(__fsub_rn(in[j], mn), scale)), 0.0f), 255.0f);
+            packed |= (uint32_t)q << (8 * j);
+        }
+        reinterpret_cast<uint32_t*>(idx + g * 128)[lane] = packed;
+        if (lane == 0)
+            sz[g] = ((uint32_t)__half_as_ushort(__float2half_rn(mn)) << 16) | (uint32_t)__half_as_ushort(__float2half_rn(flat ? 0.0f : scale));
+    }
+}
+
 }  // namespace rsv

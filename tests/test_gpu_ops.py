@@ -212,3 +212,51 @@ def test_wkv7_kernels_agree_with_each_other_and_reject_bad_arguments():
     bad.pop("vfirst")
     with pytest.raises(rsv.RsvError, match="come together"):
         rsv.op_wkv7(**bad)
+
+
+# ---- the offline int8 quantiser (tools/quantize_any4.py:241-300) ---------------------------------------------------------------
+def _quantize_numpy(w, group=128):
+    """quantize_int8_matrix restated with numpy, fp32 throughout like the tool."""
+    m, k = w.shape
+    wr = w.reshape(m, k // group, group)
+    wmin, wmax = wr.min(axis=2), wr.max(axis=2)
+    span = wmax - wmin
+    flat = span == 0
+    scale = (np.where(flat, np.float32(1.0), span) / np.float32(255.0)).astype(np.float32)
+    q = np.clip(np.round((wr - wmin[..., None]) / scale[..., None]), 0, 255).astype(np.uint8).reshape(m, k)
+    scale[flat] = 0.0
+    s16 = scale.astype(np.float16).view(np.uint16).astype(np.uint32)
+    z16 = wmin.astype(np.float16).view(np.uint16).astype(np.uint32)
+    return q, ((z16 << 16) | s16).astype(np.uint32)
+
+
+def test_quantize_int8_bit_exact_and_meets_the_precision_target():
+    rng = np.random.default_rng(42)
+    w = (0.02 * rng.standard_normal((32, 2560))).astype(np.float32)  # the shape of the reference's precision test (src/model.rs:878-918)
+    w[3, 128:256] = 0.125                                            # a constant group
+    w[5, :128] = np.linspace(-1, 1, 128, dtype=np.float32)           # exact ties of the rounding
+    idx, sz = rsv.quantize_int8(w)
+    qi, qs = _quantize_numpy(w)
+    assert np.array_equal(idx, qi) and np.array_equal(sz, qs)
+    assert np.all(idx[3, 128:256] == 0) and (sz[3, 1] & 0xFFFF) == 0 and (sz[3, 1] >> 16) == f16bits(0.125)
+    back = rsv.op_dequant_int8(idx, sz)
+    assert np.array_equal(back, orc.dequant_int8(idx, sz))
+    assert np.all(back[3, 128:256] == 0.125)
+    cos = float((w * back).sum() / (np.linalg.norm(w) * np.linalg.norm(back)))
+    rel = float(np.linalg.norm(back - w) / np.linalg.norm(w))
+    assert cos >= 0.999 and rel <= 0.02  # the reference's thresholds
+    with pytest.raises(rsv.RsvError, match="multiple of 128"):
+        rsv.quantize_int8(np.zeros((2, 100), dtype=np.float32))
+
+
+def test_quantized_matrix_runs_through_the_linear_kernel():
+    rng = np.random.default_rng(4)
+    w = (0.02 * rng.standard_normal((256, 512))).astype(np.float32)
+    x = rng.standard_normal((3, 512)).astype(np.float32)
+    idx, sz = rsv.quantize_int8(w)
+    want = x @ orc.dequant_int8(idx, sz).T
+    y = rsv.op_linear(x, idx, sz, path=0)
+    assert np.abs(y - want).max() <= 1e-4 * max(1.0, float(np.abs(want).max()))
+    # per-group scales run on the weight-streaming kernel only: the tensor-core kernel takes one (scale, zero) per row and says so
+    with pytest.raises(rsv.RsvError, match="one scale/zero per row"):
+        rsv.op_linear(x, idx, sz, path=1)
