@@ -93,7 +93,7 @@ def algorithmic_bytes(sh, quant, B):
 # DRAM traffic of decode_stream_kernel per decoded token, from one ncu capture of a 4-token launch
 # (dram__bytes_read.sum + dram__bytes_write.sum, divided by 4; summary under profiles/).  Every token streams the same weights,
 # so the traffic of a launch is this figure times its tokens.
-NCU_DRAM_BYTES_PER_TOKEN = {}
+NCU_DRAM_BYTES_PER_TOKEN = {("3b", "int8", 1): 3.0933e9}
 
 
 def kernel_bytes(sh, quant, B):
