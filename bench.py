@@ -48,6 +48,7 @@ def parse_args():
     ap.add_argument("--sweep-steps", type=int, default=32)
     ap.add_argument("--prefill", type=int, default=2048, help="prompt tokens of the timed chunked prefill, per GPU; 0 disables it")
     ap.add_argument("--continuous", type=int, default=256, help="sessions per GPU of the continuous-batching workload (benchmark config 3); 0 disables it")
+    ap.add_argument("--other-format", type=int, default=1, help="1: also time batch 1 and 64 with the other weight format (fp16 <-> int8), N=1 only")
     ap.add_argument("--cpu-seconds", type=float, default=20.0, help="time budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--model-dir", default=os.environ.get("RSV_BENCH_DIR", "/tmp/rsv_bench"))
@@ -531,6 +532,27 @@ def main():
         result.update(legs)
     state.close()
     model.close()
+    # ---- the same shape with the other weight format (fp16 when the headline is int8): batch 1 and batch 64, one GPU only ----
+    if rank == 0 and world == 1 and args.other_format:
+        try:
+            import copy
+            a2 = copy.copy(args)
+            a2.quant = "fp16" if args.quant == "int8" else "int8"
+            ensure_model(a2)
+            m2 = rsv.Model(model_path(a2), device=local)
+            leg = {"weights": a2.quant}
+            for b in (1, 64):
+                st_b, seeds_b = prefix_states(rsv, m2, b, 64, sh["vocab"], rng)
+                decode_run(rsv, m2, st_b, seeds_b, 3)
+                n = 64 if b == 1 else args.sweep_steps
+                ms_b, _ = decode_run(rsv, m2, st_b, seeds_b, n)
+                bts, _ = algorithmic_bytes(sh, a2.quant, b)
+                leg[str(b)] = {"tok_s": b * n / (ms_b / 1000.0), "ms_per_step": ms_b / n, "hbm_frac": bts / (ms_b / n / 1000.0) / 1e9 / peak_gbs}
+                st_b.close()
+            m2.close()
+            result["other_weight_format"] = leg
+        except Exception as e:  # an optional section must not cost the headline line
+            result["other_weight_format"] = {"error": str(e)}
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:
             result["cpu_baseline"], _ = cpu_baseline(path, sh, args.cpu_seconds)

@@ -1,8 +1,8 @@
 """GPU parity of the forward step against the CPU oracle, through the reference-shaped API
 (ModelBuilder / Bundle / State), which calls the C ABI.
 
-Tolerances (as the benchmark's north star states them): int8 dequant and state round-trip bit-exact,
-arg-max token streams identical, logits within an RMSE of 1e-3 of the fp32 CPU path.
+Tolerances: int8 dequant and state round-trip bit-exact, arg-max token streams identical, logits within an RMSE of
+1e-3 of the fp32 CPU path.
 """
 import os
 
@@ -295,3 +295,61 @@ def test_batch_mean_hidden_matches_cpu_path(bundles, oracles):
     finally:
         st.close()
         o.reset()
+
+
+def test_states_of_different_batch_sizes_one_after_the_other(bundles):
+    # The one-launch decode kernels keep per-layer state pointers in a device table; a new state may reuse the freed
+    # state's addresses with another slot count (other per-layer strides), so the table has to follow the state, not its address.
+    b = bundles["int8"]
+    m = b.model
+    rng = np.random.default_rng(31)
+    prompts = [rng.integers(0, m.info().num_vocab, size=k).astype(np.uint32) for k in (9, 3, 17, 5)]
+    want = []
+    for p in prompts:
+        b.reset()
+        b.infer_seq(p)
+        want.append(list(b.infer_argmax_selfloop(int(p[-1]), 12)))
+    for batch in (4, 1, 2, 3, 4):  # allocate, decode, free - the allocator hands the same blocks out again
+        st = m.create_batch_state(batch)
+        try:
+            seeds = m.forward_seq_batch(st, prompts[:batch])
+            out = m.collect_sample_selfloop_batch(m.submit_sample_selfloop_batch(st, seeds, 12, None))
+            for i in range(batch):
+                assert list(out[i]) == want[i], (batch, i)
+        finally:
+            st.close()
+
+
+def test_malformed_checkpoints_are_refused_by_the_loader(tiny_paths, tmp_path):
+    import json
+    import struct
+
+    def rewrite(dst, edit):
+        raw = open(tiny_paths["fp16"], "rb").read()
+        n = struct.unpack("<Q", raw[:8])[0]
+        hdr = json.loads(raw[8:8 + n])
+        edit(hdr)
+        out = json.dumps(hdr, separators=(",", ":")).encode()
+        out += b" " * ((8 - len(out) % 8) % 8)
+        open(dst, "wb").write(struct.pack("<Q", len(out)) + out + raw[8 + n:])
+        return str(dst)
+
+    def grow(hdr):  # a shape that claims twice the elements its byte range holds
+        hdr["ln_out.weight"]["shape"] = [hdr["ln_out.weight"]["shape"][0] * 2]
+    with pytest.raises(rsv.RsvError, match="bytes but its shape"):
+        rsv.Model(rewrite(tmp_path / "grow.st", grow))
+
+    def negative(hdr):
+        hdr["emb.weight"]["shape"] = [-4096, -512]
+    with pytest.raises(rsv.RsvError):
+        rsv.Model(rewrite(tmp_path / "neg.st", negative))
+
+    def past_the_end(hdr):
+        a, e = hdr["head.weight"]["data_offsets"]
+        hdr["head.weight"]["data_offsets"] = [a, e + (1 << 30)]
+    with pytest.raises(rsv.RsvError):
+        rsv.Model(rewrite(tmp_path / "range.st", past_the_end))
+    open(tmp_path / "short.st", "wb").write(open(tiny_paths["fp16"], "rb").read()[:1000])
+    with pytest.raises(rsv.RsvError):
+        rsv.Model(str(tmp_path / "short.st"))
+    assert rsv.Model(tiny_paths["fp16"]).info().num_layer == 4  # the library still loads a good file afterwards
