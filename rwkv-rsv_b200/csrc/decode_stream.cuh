@@ -219,7 +219,7 @@ __device__ __forceinline__ long long ds_warp_sum_ll(long long v) {
 // A chunk of weight rows: one tile (up to 16 rows of a matrix) x one piece of K.  The chunks a CTA consumes are the same in
 // every layer (its row ranges do not change), so they are tabulated once per launch; the weights themselves are stored a
 // second time in exactly this order (rows padded by 16 bytes, chunk after chunk), so that a chunk is ONE bulk copy.
-struct DsChunk {
+struct alignas(16) DsChunk {
     int cb;            // bytes of the chunk, in the stream and in the ring: nr * stride
     int nr_steps;      // rows (<= 16) | 64-byte column steps (pairs of k steps) of the piece << 16
     int piece_np;      // which piece of the rows' K | pieces per row << 16
@@ -229,15 +229,14 @@ struct DsChunk {
     int stage_off;     // first staged (scale, zero) of the matrix
     int stride;        // bytes between the rows of the chunk: piece + 16
 };
-// What the producer tells the consumer about the chunk on a barrier pair: where it lies in the ring, and its table entry.
-// Chunk j of the launch always uses barrier pair j mod 16 and, when it carries weight rows, belongs to consumer warp j mod 16:
-// the consumers do no placement arithmetic of their own.
-struct alignas(16) DsDesc {  // read with three 16-byte loads
+// What the producer tells the consumer about the chunk on a barrier pair: where it landed in the ring.  Chunk j of the launch
+// always uses barrier pair j mod 16 and, when it carries weight rows, belongs to consumer warp j mod 16; which table entry it
+// is follows from its position in the phase, so the consumer reads the entry itself (two 16-byte loads) and the producer's work
+// per chunk is a reservation, this word, and one bulk copy.
+struct DsDesc {
     int ring_off;  // byte offset of the chunk in the ring
-    int pad[3];
-    DsChunk c;
 };
-static_assert(sizeof(DsChunk) == 32 && sizeof(DsDesc) == 48, "DsDesc is read as three 16-byte words");
+static_assert(sizeof(DsChunk) == 32, "a table entry is read as two 16-byte words");
 constexpr int kDsMaxChunks = 256;  // table entries per CTA: the chunks of a layer plus the head's
 enum { DSP_P1 = 0, DSP_P3, DSP_P4, DSP_P5, DSP_HEAD, DSP_COUNT };
 // The CTA's static plan (built once per launch).
@@ -378,6 +377,7 @@ __device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const 
 // What the consumer warps need to turn a row's sums into an output (passed by value: nothing of it lives in local memory).
 struct DsPhaseCtx {
     uint32_t vec_s;  // shared-memory address of the operand area
+    int k0;          // table index of the phase's first chunk
 #ifdef RSV_DS_DEBUG
     long long* dbg;  // non-null: this call adds warp 0's time waiting for chunks to dbg[0] and its time multiplying to dbg[1]
 #endif
@@ -496,8 +496,10 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
 #ifdef RSV_DS_DEBUG
         const long long tw1 = ds_now();
 #endif
-        const uint4 d0 = reinterpret_cast<const uint4*>(&S->desc[wwarp])[0], d1 = reinterpret_cast<const uint4*>(&S->desc[wwarp])[1],
-                    d2 = reinterpret_cast<const uint4*>(&S->desc[wwarp])[2];
+        // the chunk's table entry (the j-th chunk of the phase) and, from the producer, where in the ring it landed
+        const DsChunk* ce = &S->plan.ctab[pc.k0 + (int)(j - J)];
+        const uint4 d0 = make_uint4((uint32_t)S->desc[wwarp].ring_off, 0u, 0u, 0u), c0w = reinterpret_cast<const uint4*>(ce)[0], c1w = reinterpret_cast<const uint4*>(ce)[1];
+        const uint4 d1 = make_uint4(0u, c0w.y, c0w.z, c0w.w), d2 = c1w;
         const int ring_off = (int)d0.x, nr = (int)(d1.y & 0xFFFFu), steps = (int)(d1.y >> 16), piece = (int)(d1.z & 0xFFFFu), np = (int)(d1.z >> 16);
         const int part_off = (int)(d2.x & 0xFFFFu), tile_idx = (int)(d2.x >> 16), e = (int)(d2.y & 0xFFu), row0 = (int)(d2.y >> 16), stage_off = (int)d2.z,
                   stride = (int)d2.w;
@@ -751,16 +753,13 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
         };
         // The weights lie in the stream in the order they are consumed: every chunk is one bulk copy from a running pointer.
         const char* src = nullptr;
-        // table entry k: lanes 1-8 copy its eight words into the barrier pair's descriptor, lane 0 adds the ring offset, arms the
-        // barrier (a release: the descriptor is visible to whoever sees the barrier complete) and issues the copy
+        // table entry k: lane 0 publishes the ring offset, arms the barrier (a release: the offset is visible to whoever sees the
+        // barrier complete) and issues the copy
         auto put_chunk = [&](int k) -> bool {
             const int cb = S->plan.ctab[k].cb;
             if (!reserve(cb)) return false;
-            DsDesc& D = S->desc[j % kDsBars];
-            if (lane >= 1 && lane <= 8) reinterpret_cast<int*>(&D.c)[lane - 1] = reinterpret_cast<const int*>(&S->plan.ctab[k])[lane - 1];
-            if (lane == 0) D.ring_off = head - cb;
-            __syncwarp();
             if (lane == 0) {
+                S->desc[j % kDsBars].ring_off = head - cb;
                 mbar_expect_tx(&S->full[j % kDsBars], (uint32_t)cb);
                 ds_bulk_load(ring_s + (uint32_t)(head - cb), src, (uint32_t)cb, &S->full[j % kDsBars], pol);
             }
@@ -984,6 +983,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #endif
                 {
                     const int nc = l == 0 ? S->plan.phn_l0 : S->plan.phn[DSP_P1];
+                    pc.k0 = S->plan.ph0[DSP_P1] + (S->plan.phn[DSP_P1] - nc);  // layer 0: the v-gate projection's chunks (first in the list of a CTA that has them) are skipped
                     if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, nc, pc, wwarp, lane))) break;
                     J += (uint32_t)nc;
                 }
@@ -1202,6 +1202,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #ifdef RSV_DS_DEBUG
                 pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 24 : nullptr;
 #endif
+                    pc.k0 = S->plan.ph0[DSP_P3];
                     if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, S->plan.phn[DSP_P3], pc, wwarp, lane))) break;
                     J += (uint32_t)S->plan.phn[DSP_P3];
                 }
@@ -1252,6 +1253,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #ifdef RSV_DS_DEBUG
                 pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 28 : nullptr;
 #endif
+                    pc.k0 = S->plan.ph0[DSP_P4];
                     if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, S->plan.phn[DSP_P4], pc, wwarp, lane))) break;
                     J += (uint32_t)S->plan.phn[DSP_P4];
                 }
@@ -1279,6 +1281,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #ifdef RSV_DS_DEBUG
                 pc.dbg = (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 32 : nullptr;
 #endif
+                    pc.k0 = S->plan.ph0[DSP_P5];
                     if (!(ok = ds_consume(P, S, Ly.e, ring_s, J, S->plan.phn[DSP_P5], pc, wwarp, lane))) break;
                     J += (uint32_t)S->plan.phn[DSP_P5];
                 }
@@ -1313,6 +1316,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #ifdef RSV_DS_DEBUG
                 pc.dbg = nullptr;
 #endif
+                pc.k0 = S->plan.ph0[DSP_HEAD];
                 if (!(ok = ds_consume(P, S, nullptr, ring_s, J, S->plan.phn[DSP_HEAD], pc, wwarp, lane))) break;
                 J += (uint32_t)S->plan.phn[DSP_HEAD];
                 if (P.argmax_feed) {
