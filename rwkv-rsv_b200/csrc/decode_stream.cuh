@@ -383,6 +383,9 @@ struct DsPhaseCtx {
 #endif
 };
 #ifdef RSV_DS_DEBUG
+#ifndef RSV_DS_DEBUG_WARPS
+#define RSV_DS_DEBUG_WARPS 20  // which phase's per-warp stamps are recorded: 20 phase 1, 24 phase 3, 28 phase 4, 32 phase 5
+#endif
 __device__ __forceinline__ long long ds_now() {
     long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -584,7 +587,7 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
             pc.dbg[1] += ds_now() - tw1;
             pc.dbg[2] += 1;
         }
-        if (pc.dbg && pc.dbg == P.dbg + 20 && lane == 0) {  // phase 1: per warp, the times of its last chunk
+        if (pc.dbg && pc.dbg == P.dbg + RSV_DS_DEBUG_WARPS && lane == 0) {  // phase 1: per warp, the times of its last chunk
             P.dbg[64 + wwarp * 4 + 0] = tw0;
             P.dbg[64 + wwarp * 4 + 1] = tw1;
             P.dbg[64 + wwarp * 4 + 2] = ds_now();
@@ -616,7 +619,7 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
             }
             if (lane == 0) S->tile_cnt[tile_idx] = 0;
 #ifdef RSV_DS_DEBUG
-            if (pc.dbg && pc.dbg == P.dbg + 20 && lane == 0) P.dbg[64 + wwarp * 4 + 3] = ds_now();
+            if (pc.dbg && pc.dbg == P.dbg + RSV_DS_DEBUG_WARPS && lane == 0) P.dbg[64 + wwarp * 4 + 3] = ds_now();
 #endif
         }
     }
