@@ -298,31 +298,45 @@ def continuous_batching(rsv, model, sh, n_sessions, seed=3, rate=64.0, rank=0, w
     # the router's book drains at about one GPU's measured rate on this workload (prompt + generated tokens per second)
     place = place_arrivals(arrive, plen + glen, world, "least_loaded", drain_rate=8000.0) if world > 1 else [0] * total
     mine = [i for i in range(total) if place[i] == rank]
-    sched = rsv.Scheduler(model, max_slots=max(len(mine), 1), chunk=512, max_new_cap=2048)
+    from rwkv_rsv_b200.shard import all_ranks_ok
+    sched, failure = None, None
+    try:
+        sched = rsv.Scheduler(model, max_slots=max(len(mine), 1), chunk=512, max_new_cap=2048)
+    except Exception as e:
+        failure = str(e)
+    if not all_ranks_ok(failure is None, dist, device):
+        if sched:
+            sched.close()
+        raise RuntimeError(failure or "another rank could not create its scheduler")
     nxt, done, generated, steps, rows_total, max_rows = 0, 0, 0, 0, 0, 0
     if dist:
         dist.barrier()
     t0 = time.perf_counter()
-    while done < len(mine):
-        now = time.perf_counter() - t0
-        while nxt < len(mine) and arrive[mine[nxt]] <= now:
-            i = mine[nxt]
-            sched.submit(prompts[i], int(glen[i]), rsv.SamplerParams(temperature=1.0, top_p=0.9, seed=1000 + i))
-            nxt += 1
-        rows, active = sched.step()
-        steps += 1 if rows else 0
-        rows_total += rows
-        max_rows = max(max_rows, rows)
-        for rid in sched.poll():
-            generated += len(sched.result(rid))
-            done += 1
-        if rows == 0 and active == 0 and nxt < len(mine):
-            time.sleep(max(0.0, min(0.002, arrive[mine[nxt]] - (time.perf_counter() - t0))))
-        elif rows == 0:
-            sched.sync()
-    sched.sync()
+    try:
+        while done < len(mine):
+            now = time.perf_counter() - t0
+            while nxt < len(mine) and arrive[mine[nxt]] <= now:
+                i = mine[nxt]
+                sched.submit(prompts[i], int(glen[i]), rsv.SamplerParams(temperature=1.0, top_p=0.9, seed=1000 + i))
+                nxt += 1
+            rows, active = sched.step()
+            steps += 1 if rows else 0
+            rows_total += rows
+            max_rows = max(max_rows, rows)
+            for rid in sched.poll():
+                generated += len(sched.result(rid))
+                done += 1
+            if rows == 0 and active == 0 and nxt < len(mine):
+                time.sleep(max(0.0, min(0.002, arrive[mine[nxt]] - (time.perf_counter() - t0))))
+            elif rows == 0:
+                sched.sync()
+        sched.sync()
+    except Exception as e:  # reported to the other ranks below: they must not wait for this one in a reduction
+        failure = str(e)
     el_own = time.perf_counter() - t0
     sched.close()
+    if not all_ranks_ok(failure is None, dist, device):
+        raise RuntimeError(failure or "another rank's scheduler failed")
     el = max_over_ranks(el_own, dist, device)
     gen_all = int(sum_over_ranks(generated, dist, device))
     assert gen_all == int(glen.sum()), "every session must produce its full generation length"
@@ -500,34 +514,44 @@ def main():
             legs["batch_sweep_fixed_total"] = strong
     # prompt prefill (the chunked sequence path, Bundle::infer with chunk 512): one session per GPU
     if args.prefill > 0:
+        from rwkv_rsv_b200.shard import all_ranks_ok
+        pms, perr = 0.0, None
         try:
             pb = rsv.Bundle(model)
             ptoks = rng.integers(0, sh["vocab"], size=args.prefill).astype(np.uint32)
             pb.infer_chunked(ptoks[:min(512, args.prefill)], 512)  # sizes the work buffers
             pb.reset()
+        except Exception as e:  # an optional section must not cost the headline line
+            perr = str(e)
+        if all_ranks_ok(perr is None, dist, dev):
             if dist:
                 dist.barrier()
-            model.timer_start()
-            pb.infer_chunked(ptoks, 512)
-            pms = max_over_ranks(model.timer_stop(), dist, dev)
-            legs["prefill"] = {"tokens": int(args.prefill) * world, "chunk": 512, "ms": pms, "tok_s": world * args.prefill / (pms / 1000.0),
-                               "api": "rsv_infer_chunked (Bundle::infer, RnnOption::Last), one session per GPU"}
-            pb.state.close()
-        except Exception as e:  # an optional section must not cost the headline line
-            if world > 1:
-                raise  # the other ranks are waiting in a reduction
-            legs["prefill"] = {"error": str(e)}
+            try:
+                model.timer_start()
+                pb.infer_chunked(ptoks, 512)
+                pms = model.timer_stop()
+                pb.state.close()
+            except Exception as e:
+                perr = str(e)
+            ok = all_ranks_ok(perr is None, dist, dev)
+            pms = max_over_ranks(pms, dist, dev)
+            if ok:
+                legs["prefill"] = {"tokens": int(args.prefill) * world, "chunk": 512, "ms": pms, "tok_s": world * args.prefill / (pms / 1000.0),
+                                   "api": "rsv_infer_chunked (Bundle::infer, RnnOption::Last), one session per GPU"}
+        if "prefill" not in legs:
+            legs["prefill"] = {"error": perr or "another rank failed"}
     # continuous batching (benchmark config 3)
     if args.continuous > 0:
         try:
             legs["continuous_batching"] = continuous_batching(rsv, model, sh, args.continuous, rank=rank, world=world, dist=dist, device=dev)
-        except Exception as e:
-            if world > 1:
-                raise
+        except Exception as e:  # raised on every rank together (see all_ranks_ok)
             legs["continuous_batching"] = {"error": str(e)}
         if world > 1:
-            legs["continuous_batching_fixed_total"] = continuous_batching(rsv, model, sh, args.continuous, rank=rank, world=world, dist=dist, device=dev,
-                                                                          fixed_total=True)
+            try:
+                legs["continuous_batching_fixed_total"] = continuous_batching(rsv, model, sh, args.continuous, rank=rank, world=world, dist=dist, device=dev,
+                                                                              fixed_total=True)
+            except Exception as e:
+                legs["continuous_batching_fixed_total"] = {"error": str(e)}
     if rank == 0:
         result.update(legs)
     state.close()

@@ -32,3 +32,10 @@ def sum_over_ranks(value, dist=None, device=None):
     t = torch.tensor([float(value)], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.SUM)
     return float(t.item())
+
+
+def all_ranks_ok(ok, dist=None, device=None):
+    """True on every rank only if `ok` is true on every rank.  Called between steps (nothing in flight on any GPU): a rank whose
+    step raised reports it here, and the others learn of it on the host before their next launch instead of waiting for it in a
+    reduction that never comes."""
+    return max_over_ranks(0.0 if ok else 1.0, dist, device) == 0.0

@@ -353,3 +353,35 @@ def test_malformed_checkpoints_are_refused_by_the_loader(tiny_paths, tmp_path):
     with pytest.raises(rsv.RsvError):
         rsv.Model(str(tmp_path / "short.st"))
     assert rsv.Model(tiny_paths["fp16"]).info().num_layer == 4  # the library still loads a good file afterwards
+
+
+def test_text_level_driver(bundles, tiny_paths, tmp_path, capsys):
+    # examples/generate.rs:20-113 as a library function and a command: text -> tokens -> prefill -> self-loop -> text
+    import json
+
+    from rwkv_rsv_b200 import generate as gen
+    from rwkv_rsv_b200.tokenizer import Tokenizer
+    vocab = {str(i + 1): [i] for i in range(256)}
+    vocab.update({"300": "the ", "301": "tower", "302": " tow"})
+    vocab.update({str(i): [128 + (i >> 8), i & 255] for i in range(303, 4096)})  # every id the tiny model can emit decodes
+    vf = tmp_path / "vocab.json"
+    vf.write_text(json.dumps(vocab))
+    tk = Tokenizer(vf.read_text())
+    prompt = tk.encode("the tower")
+    assert prompt == [300, 301]
+    b = bundles["int8"]
+    b.reset()
+    out, _ = gen.generate(b, prompt, 12, mode="argmax")
+    b.reset()
+    b.infer_tokens(prompt)
+    assert out == [int(t) for t in b.infer_argmax_selfloop(prompt[-1], 12)]
+    b.reset()
+    s1, _ = gen.generate(b, prompt, 12)
+    b.reset()
+    s2, _ = gen.generate(b, prompt, 12)
+    assert s1 == s2 and len(s1) == 12  # seeded sampling is reproducible
+    assert gen.main(["--model", tiny_paths["int8"], "--vocab", str(vf), "--prompt", "the tower", "--tokens", "5", "--mode", "argmax"]) == 0
+    printed = capsys.readouterr().out.splitlines()
+    assert json.loads(printed[0])[:2] == prompt and len(json.loads(printed[0])) == 7
+    with pytest.raises(SystemExit):
+        gen.main(["--model", tiny_paths["int8"], "--prompt", "x"])
