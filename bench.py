@@ -41,14 +41,15 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--shape", default="3b", choices=["tiny", "3b", "7b"])
-    ap.add_argument("--quant", default="int8", choices=["fp16", "int8"])
+    ap.add_argument("--quant", default="int8", choices=["fp16", "int8", "int8g"],
+                    help="int8: one (scale, zero) per output row; int8g: the reference container, one per row and group of 128 weights")
     ap.add_argument("--batch", type=int, default=1, help="sessions per GPU")
     ap.add_argument("--prompt", type=int, default=512, help="prompt tokens prefilled before decoding")
     ap.add_argument("--sweep", default="1,8,64,256,1024", help="batch sizes of the decode sweep, per GPU; '' disables it")
     ap.add_argument("--sweep-steps", type=int, default=32)
     ap.add_argument("--prefill", type=int, default=2048, help="prompt tokens of the timed chunked prefill, per GPU; 0 disables it")
     ap.add_argument("--continuous", type=int, default=256, help="sessions per GPU of the continuous-batching workload (benchmark config 3); 0 disables it")
-    ap.add_argument("--other-format", type=int, default=1, help="1: also time batch 1 and 64 with the other weight format (fp16 <-> int8), N=1 only")
+    ap.add_argument("--other-format", type=int, default=1, help="1: also time batch 1 and 64 with the other weight formats (fp16, int8 per row, int8 per group), N=1 only")
     ap.add_argument("--cpu-seconds", type=float, default=20.0, help="time budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--model-dir", default=os.environ.get("RSV_BENCH_DIR", "/tmp/rsv_bench"))
@@ -65,7 +66,7 @@ def ensure_model(args):
     if not os.path.exists(path):
         os.makedirs(args.model_dir, exist_ok=True)
         tmp = path + f".tmp{os.getpid()}"
-        rsv.write_synthetic(tmp, args.shape, seed=0, quant=1 if args.quant == "int8" else 0)
+        rsv.write_synthetic(tmp, args.shape, seed=0, quant={"fp16": 0, "int8": 1, "int8g": 2}[args.quant])
         os.replace(tmp, path)
     return path
 
@@ -81,7 +82,7 @@ def algorithmic_bytes(sh, quant, B):
     L, C, F, V, H, N = sh["n_layer"], sh["n_embd"], sh["ffn_hidden"], sh["vocab"], sh["n_head"], sh["head_size"]
     mids = sh["w_mid"] + sh["a_mid"] + sh["v_mid"] + sh["g_mid"]
     big = L * (4 * C * C + 2 * C * F)
-    if quant == "int8":
+    if quant in ("int8", "int8g"):
         w = big + big // 128 * 4
     else:
         w = big * 2
@@ -101,7 +102,7 @@ def kernel_bytes(sh, quant, B):
     """Algorithmic bytes of one launch of each weight-streaming kernel (weights once + activations in/out)."""
     C, F, V = sh["n_embd"], sh["ffn_hidden"], sh["vocab"]
     mids = sh["w_mid"] + sh["a_mid"] + sh["v_mid"] + sh["g_mid"]
-    wb = (lambda m, k: m * k + m * k // 128 * 4) if quant == "int8" else (lambda m, k: m * k * 2)
+    wb = (lambda m, k: m * k + m * k // 128 * 4) if quant in ("int8", "int8g") else (lambda m, k: m * k * 2)
     act = lambda n_in, n_out: 4 * B * (n_in + n_out)
     return {
         "linear_rkv_rank": 3 * wb(C, C) + C * mids * 2 + act(6 * C, 3 * C + mids),
@@ -560,23 +561,26 @@ def main():
     if rank == 0 and world == 1 and args.other_format:
         try:
             import copy
-            a2 = copy.copy(args)
-            a2.quant = "fp16" if args.quant == "int8" else "int8"
-            ensure_model(a2)
-            m2 = rsv.Model(model_path(a2), device=local)
-            leg = {"weights": a2.quant}
-            for b in (1, 64):
-                st_b, seeds_b = prefix_states(rsv, m2, b, 64, sh["vocab"], rng)
-                decode_run(rsv, m2, st_b, seeds_b, 3)
-                n = 64 if b == 1 else args.sweep_steps
-                ms_b, _ = decode_run(rsv, m2, st_b, seeds_b, n)
-                bts, _ = algorithmic_bytes(sh, a2.quant, b)
-                leg[str(b)] = {"tok_s": b * n / (ms_b / 1000.0), "ms_per_step": ms_b / n, "hbm_frac": bts / (ms_b / n / 1000.0) / 1e9 / peak_gbs}
-                st_b.close()
-            m2.close()
-            result["other_weight_format"] = leg
+            legs2 = {}
+            for q2 in [q for q in ("fp16", "int8", "int8g") if q != args.quant]:
+                a2 = copy.copy(args)
+                a2.quant = q2
+                ensure_model(a2)
+                m2 = rsv.Model(model_path(a2), device=local)
+                leg = {}
+                for b in (1, 64):
+                    st_b, seeds_b = prefix_states(rsv, m2, b, 64, sh["vocab"], rng)
+                    decode_run(rsv, m2, st_b, seeds_b, 3)
+                    n = 64 if b == 1 else args.sweep_steps
+                    ms_b, _ = decode_run(rsv, m2, st_b, seeds_b, n)
+                    bts, _ = algorithmic_bytes(sh, q2, b)
+                    leg[str(b)] = {"tok_s": b * n / (ms_b / 1000.0), "ms_per_step": ms_b / n, "hbm_frac": bts / (ms_b / n / 1000.0) / 1e9 / peak_gbs}
+                    st_b.close()
+                m2.close()
+                legs2[q2] = leg
+            result["other_weight_formats"] = legs2
         except Exception as e:  # an optional section must not cost the headline line
-            result["other_weight_format"] = {"error": str(e)}
+            result["other_weight_formats"] = {"error": str(e)}
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:
             result["cpu_baseline"], _ = cpu_baseline(path, sh, args.cpu_seconds)

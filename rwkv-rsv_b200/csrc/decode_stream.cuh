@@ -67,11 +67,12 @@ struct DsEntry {
     const float* wscale;  // int8: [M] per-row scale and zero of the container
     const float* wzero;
     const float* mix;     // rank projections: the token-shift mix vector of their input; null otherwise
+    const uint32_t* sz;   // int8 with one (scale, zero) per row and group of 128 (is_i8 == 2): the container's [M, K/128] words, fp16 scale | fp16 zero << 16
     int M;                // output rows (0: the entry does not exist in this layer)
     int row_stride;       // bytes between rows
     int piece_bytes;      // bytes of K per piece (a multiple of 128, <= kDsMaxPiece)
     int npieces;          // pieces per row
-    int is_i8;
+    int is_i8;            // 0: fp16; 1: int8, one (scale, zero) per row (wscale, wzero); 2: int8, one per row and group of 128 (sz)
     int xvec;             // which vector of the phase's operand area the rows are multiplied with
     int out;              // DsOut
     int out_off;          // offset inside the rank-space vector for DSO_MID*
@@ -122,6 +123,11 @@ struct DsParams {
 
 // ---- small helpers ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void ds_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kDsConsumers) : "memory"); }
+__device__ __forceinline__ uint32_t ds_lds32(uint32_t saddr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr));
+    return v;
+}
 __device__ __forceinline__ uint4 ds_lds128(uint32_t saddr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
@@ -237,6 +243,7 @@ struct DsDesc {
     int ring_off;  // byte offset of the chunk in the ring
 };
 static_assert(sizeof(DsChunk) == 32, "a table entry is read as two 16-byte words");
+constexpr int kDsMaxGroups = 128;  // groups of 128 in the longest reduction (K <= 16384)
 constexpr int kDsMaxChunks = 256;  // table entries per CTA: the chunks of a layer plus the head's
 enum { DSP_P1 = 0, DSP_P3, DSP_P4, DSP_P5, DSP_HEAD, DSP_COUNT };
 // The CTA's static plan (built once per launch).
@@ -253,6 +260,7 @@ struct DsShared {
     uint64_t full[kDsBars], empty[kDsBars];
     int alloc[kDsBars];  // producer only: bytes (with wrap waste) a chunk in flight holds
     int abort_flag;
+    float tg[4][kDsMaxGroups];  // per operand vector: the fixed-point sum of every group of 128 elements (as float; for per-group int8 rows)
     int abort_where;  // which wait gave up first (1 rows: full, 2 producer: empty, 3 grid barrier, 4 heads: full) | detail << 4
     uint32_t tok;
     float red_a[16], red_b[16], red_c[4 * 16];
@@ -282,7 +290,7 @@ struct DsShared {
 // Writes the vectors (getval(v, i) = the i-th of a thread's NGR groups of four consecutive elements of vector v) in that form; the scale exponent
 // goes to S->ex[v], for int8 the exact fixed-point sum to S->tsw[v].
 template <int NV, int NGR, class GetVal>
-__device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const bool (&i8)[NV], GetVal getval, int wtid, long long* dbg = nullptr) {
+__device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const bool (&i8)[NV], GetVal getval, int wtid, bool group_sums = false, long long* dbg = nullptr) {
     const int wwarp = wtid >> 5, lane = wtid & 31, len4 = len >> 2;
     float am[NV];
 #pragma unroll
@@ -323,11 +331,19 @@ __device__ __forceinline__ void ds_emit(DsShared* S, float* vec, int len, const 
                     const float4 x = getval(v, gi);
                     const float f[4] = {x.x * mult, x.y * mult, x.z * mult, x.w * mult};
                     uint32_t u[4];
+                    long long t4 = 0;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int t = __float2int_rn(f[j]);
-                        ts += t;
+                        t4 += t;
                         u[j] = ((uint32_t)t + 0x00808080u) ^ 0x00808080u;  // bytes = signed base-256 digits of t
+                    }
+                    ts += t4;
+                    if (group_sums) {
+                        // a warp's 32 groups of four are one group of 128 elements: its sum, for rows with a (scale, zero) per group
+                        // (uniform branch: len4 is a multiple of 32, so a warp is inside the vector as a whole or not at all)
+                        const long long tgrp = ds_warp_sum_ll(t4);
+                        if (lane == 0) S->tg[v][g4 >> 5] = (float)tgrp;
                     }
                     // 4 x 4 byte transpose: word d = digit d of the four elements
                     const uint32_t lo01 = __byte_perm(u[0], u[1], 0x5140), hi01 = __byte_perm(u[0], u[1], 0x7362);
@@ -450,8 +466,10 @@ __host__ __device__ inline bool ds_build_plan(DsPlan& pl, const DsEntry* ents, c
             const DsEntry& E = e == DSE_COUNT ? head : ents[e];
             const int n = pl.en[e];
             if (n <= 0) continue;
-            const bool i8 = E.is_i8 != 0;
-            const int steps = E.piece_bytes >> 6, klen = (i8 ? E.piece_bytes : (E.piece_bytes >> 1)) * E.npieces, bstep = (i8 ? 4 : 2) * 64, slot = i8 ? 8 : 4;
+            const bool i8 = E.is_i8 != 0, pg = E.is_i8 == 2;
+            const int steps = E.piece_bytes >> 6, klen = (i8 ? E.piece_bytes : (E.piece_bytes >> 1)) * E.npieces, bstep = (i8 ? 4 : 2) * 64, slot = (i8 && !pg) ? 8 : 4;
+            // rows with a (scale, zero) per group of 128 carry them behind the rows: [group of the piece][16 rows] words
+            const int sz_bytes = pg ? (E.piece_bytes >> 7) * kDsTileRows * 4 : 0;
             for (int row0 = 0; row0 < n; row0 += kDsTileRows) {
                 const int nr = n - row0 < kDsTileRows ? n - row0 : kDsTileRows;
                 for (int p = 0; p < E.npieces; ++p) {
@@ -461,19 +479,19 @@ __host__ __device__ inline bool ds_build_plan(DsPlan& pl, const DsEntry* ents, c
                     }
                     DsChunk& c = pl.ctab[k++];
                     c.stride = E.piece_bytes + kDsPad;
-                    c.cb = nr * c.stride;
+                    c.cb = nr * c.stride + sz_bytes;
                     c.nr_steps = nr | (steps << 16);
                     c.piece_np = p | (E.npieces << 16);
                     c.baddr = vec_s + (uint32_t)E.xvec * (uint32_t)klen * 4u + (uint32_t)p * (uint32_t)steps * (uint32_t)bstep;
                     c.part_tile = part | (tile << 16);
-                    c.e_flags_row0 = e | ((i8 ? 1 : 0) << 8) | ((e == DSE_V1 ? 2 : 0) << 8) | (row0 << 16);
+                    c.e_flags_row0 = e | ((i8 ? 1 : 0) << 8) | ((e == DSE_V1 ? 2 : 0) << 8) | ((pg ? 4 : 0) << 8) | (row0 << 16);
                     c.stage_off = stage;
                     if (ph == DSP_P1 && e != DSE_V1) ++pl.phn_l0;
                 }
                 ++tile;
                 part += E.npieces * kDsTileRows * slot;
             }
-            if (i8) stage += n;
+            if (i8 && !pg) stage += n;
         }
         pl.phn[ph] = k - pl.ph0[ph];
     }
@@ -509,14 +527,55 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
         const bool i8 = (d2.y >> 8) & 1u;
         const DsEntry& E = e == DSE_COUNT ? P.head : tab[e];  // only the warp that finishes the tile looks at it
         // B fragments of this lane: 16 bytes per two k steps at [k-step pair][operand row g][t]; columns beyond the operand's rows are zero
-        const int brows = i8 ? 4 : 2, bstep = brows * 64, slot = i8 ? 8 : 4;
+        const int brows = i8 ? 4 : 2, bstep = brows * 64;
         const bool bcol_ok = g < brows;
         uint32_t baddr = d1.w + (uint32_t)(g * 4 + t) * 16u;
         // ldmatrix row addresses: lanes 0-7 rows 0-7, 8-15 rows 8-15 (bytes 0-15 of a 32-byte k step), lanes 16-31 the same rows, bytes 16-31
         const int arow = min((lane & 7) + ((lane >> 3) & 1) * 8, nr - 1);
         uint32_t aaddr = ring_s + (uint32_t)ring_off + (uint32_t)arow * (uint32_t)stride + (uint32_t)(lane >> 4) * 16u;
+        const bool pg = (d2.y >> 10) & 1u;
+        const int slot = (i8 && !pg) ? 8 : 4;
         char* part = reinterpret_cast<char*>(S->part) + part_off + piece * kDsTileRows * slot;
-        if (i8) {
+        if (pg) {
+            // int8 rows with a (scale, zero) per group of 128: the integer sums of a group (two 64-byte steps) are weighted by the
+            // digits' powers of 256 in fp32 (exact: |sum| < 2^23, power-of-two weights), multiplied by the group's scale and
+            // accumulated in fp32 together with zero x (sum of the group's activations).
+            const uint32_t sz_s = ring_s + (uint32_t)ring_off + (uint32_t)(nr * stride) + (uint32_t)g * 4u;  // [group][16 rows] words behind the rows
+            const float* tgp = S->tg[E.xvec] + piece * (steps >> 1);
+            const float w_lo = t < 2 ? (t == 0 ? 1.0f : 65536.0f) : 0.f, w_hi = w_lo * 256.0f;
+            float acc0 = 0.f, acc1 = 0.f;
+            const int ngp = steps >> 1;
+            for (int gi = 0; gi < ngp; ++gi) {
+                int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    const uint4 a0 = ds_ldmatrix4(aaddr), a1 = ds_ldmatrix4(aaddr + 32);
+                    uint4 b = make_uint4(0, 0, 0, 0);
+                    if (bcol_ok) b = ds_lds128(baddr);
+                    ds_mma_i8(c0, a0, b.x, b.y);
+                    ds_mma_i8(c1, a1, b.z, b.w);
+                    aaddr += 64;
+                    baddr += bstep;
+                }
+                const uint32_t za = ds_lds32(sz_s + (uint32_t)gi * 64u), zb = ds_lds32(sz_s + (uint32_t)gi * 64u + 32u);
+                const float2 fa = ds_half2_bits_to_float2(za), fb = ds_half2_bits_to_float2(zb);  // (scale, zero) of rows g and g + 8
+                const float qa = fmaf((float)(c0[1] + c1[1]), w_hi, (float)(c0[0] + c1[0]) * w_lo);
+                const float qb = fmaf((float)(c0[3] + c1[3]), w_hi, (float)(c0[2] + c1[2]) * w_lo);
+                acc0 = fmaf(fa.x, qa, acc0);
+                acc1 = fmaf(fb.x, qb, acc1);
+                if (t == 0) {
+                    const float tgv = tgp[gi];
+                    acc0 = fmaf(fa.y, tgv, acc0);
+                    acc1 = fmaf(fb.y, tgv, acc1);
+                }
+            }
+            acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+            if (t == 0) {
+                reinterpret_cast<float*>(part)[g] = acc0;
+                reinterpret_cast<float*>(part)[g + 8] = acc1;
+            }
+        } else if (i8) {
             int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
             // operands of the next step are loaded before this step's products are issued (the loop is a chain of shared-memory
             // latency + MMA latency otherwise)
@@ -598,7 +657,7 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
             __threadfence_block();
             const int rl = row0 + lane;
             long long T = 0;
-            if (i8) {  // exact sum of the operand's fixed-point values: 16 per-warp sums, one per lane, then a shuffle tree
+            if (i8 && !pg) {  // exact sum of the operand's fixed-point values: 16 per-warp sums, one per lane, then a shuffle tree
                 T = S->tsw[E.xvec][lane & 15];
 #pragma unroll
                 for (int o = 8; o > 0; o >>= 1) T += __shfl_xor_sync(0xffffffffu, T, o);
@@ -606,7 +665,7 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
             if (lane < nr) {
                 const char* pt = reinterpret_cast<const char*>(S->part) + part_off;
                 const int r0 = S->plan.er0[e];
-                if (i8) {
+                if (i8 && !pg) {
                     long long Q = 0;
                     for (int q = 0; q < np; ++q) Q += reinterpret_cast<const volatile long long*>(pt + q * kDsTileRows * 8)[lane];
                     const double ws = S->ws[stage_off + rl], wz = S->wz[stage_off + rl];
@@ -614,7 +673,7 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
                 } else {
                     float y = 0.f;
                     for (int q = 0; q < np; ++q) y += reinterpret_cast<const volatile float*>(pt + q * kDsTileRows * 4)[lane];
-                    ds_store(P, S, E, r0 + rl, rl, y * ds_pow2(S->ex[E.xvec]));
+                    ds_store(P, S, E, r0 + rl, rl, y * ds_pow2(S->ex[E.xvec] - (pg ? kDsP : 0)));
                 }
             }
             if (lane == 0) S->tile_cnt[tile_idx] = 0;
@@ -878,7 +937,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
             for (int i = 0; i < cnt; ++i) {
                 const DsEntry& E = ents[i];
                 const int r0 = S->plan.er0[e0 + i], n = E.M > 0 ? S->plan.en[e0 + i] : 0;
-                if (!E.is_i8 || n <= 0) continue;
+                if (E.is_i8 != 1 || n <= 0) continue;
                 for (int q = wtid; q < n && off + q < kDsMaxRows; q += kDsConsumers) {
                     S->ws[off + q] = __ldg(E.wscale + r0 + q);
                     S->wz[off + q] = __ldg(E.wzero + r0 + q);
@@ -974,9 +1033,9 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     DS_STAMP(17);
                     const bool i8[4] = {Ly.e[DSE_WR].is_i8 != 0, Ly.e[DSE_WK].is_i8 != 0, Ly.e[DSE_WV].is_i8 != 0, false};
 #ifdef RSV_DS_DEBUG
-                    ds_emit<4, NG>(S, vec, C, i8, [&](int v, int gi) { return val[v][gi]; }, wtid, (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 52 : nullptr);
+                    ds_emit<4, NG>(S, vec, C, i8, [&](int v, int gi) { return val[v][gi]; }, wtid, Ly.e[DSE_WR].is_i8 == 2, (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 52 : nullptr);
 #else
-                    ds_emit<4, NG>(S, vec, C, i8, [&](int v, int gi) { return val[v][gi]; }, wtid);
+                    ds_emit<4, NG>(S, vec, C, i8, [&](int v, int gi) { return val[v][gi]; }, wtid, Ly.e[DSE_WR].is_i8 == 2);
 #endif
                 }
                 DS_STAMP(1);
@@ -1199,7 +1258,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         yv[gi] = ds_ldcg4(P.yg + k);
                     }
                     const bool i8[1] = {Ly.e[DSE_WO].is_i8 != 0};
-                    ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return yv[gi]; }, wtid);
+                    ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return yv[gi]; }, wtid, Ly.e[DSE_WO].is_i8 == 2);
                     DS_STAMP(4);
                     DS_STAMP_ALL(4);
 #ifdef RSV_DS_DEBUG
@@ -1250,7 +1309,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         }
                     }
                     const bool i8[1] = {Ly.e[DSE_WFK].is_i8 != 0};
-                    ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return val[gi]; }, wtid);
+                    ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return val[gi]; }, wtid, Ly.e[DSE_WFK].is_i8 == 2);
                     DS_STAMP(6);
                     DS_STAMP_ALL(6);
 #ifdef RSV_DS_DEBUG
@@ -1278,7 +1337,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         hv4[gi] = ds_ldcg4(P.hbuf + k);
                     }
                     const bool i8[1] = {Ly.e[DSE_WFV].is_i8 != 0};
-                    ds_emit<1, NG5>(S, vec, 4 * C, i8, [&](int, int gi) { return hv4[gi]; }, wtid);
+                    ds_emit<1, NG5>(S, vec, 4 * C, i8, [&](int, int gi) { return hv4[gi]; }, wtid, Ly.e[DSE_WFV].is_i8 == 2);
                     DS_STAMP(8);
                     DS_STAMP_ALL(8);
 #ifdef RSV_DS_DEBUG
@@ -1312,7 +1371,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
 #pragma unroll
                 for (int gi = 0; gi < NG; ++gi) val[gi] = ds_ln_apply(xv[gi], mean, inv, lw[gi], lb[gi]);
                 const bool i8[1] = {P.head.is_i8 != 0};
-                ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return val[gi]; }, wtid);
+                ds_emit<1, NG>(S, vec, C, i8, [&](int, int gi) { return val[gi]; }, wtid, P.head.is_i8 == 2);
                 S->best_val[wtid] = -1e30f;
                 S->best_idx[wtid] = 0x7fffffff;
                 __syncwarp();
@@ -1418,6 +1477,14 @@ __global__ void __launch_bounds__(256) ds_retile_kernel(const __grid_constant__ 
             uint4 v = make_uint4(0, 0, 0, 0);
             if (col < E.piece_bytes) v = *reinterpret_cast<const uint4*>(src + (size_t)row * E.row_stride + col);
             *reinterpret_cast<uint4*>(dst + (size_t)row * c.stride + col) = v;
+        }
+        if ((c.e_flags_row0 >> 8) & 4) {  // the rows' (scale, zero) words of this piece's groups: [group][16 rows], zero for rows past nr
+            const int ngp = E.piece_bytes >> 7, kgroups = E.row_stride >> 7;
+            uint32_t* zd = reinterpret_cast<uint32_t*>(dst + (size_t)nr * c.stride);
+            for (int i = threadIdx.x; i < ngp * kDsTileRows; i += blockDim.x) {
+                const int gi = i / kDsTileRows, row = i % kDsTileRows;
+                zd[i] = row < nr ? E.sz[(size_t)(pl.er0[e] + row0 + row) * kgroups + (size_t)piece * ngp + gi] : 0u;
+            }
         }
     };
     auto copy_raw = [&](const void* src, int bytes, char* dst) {

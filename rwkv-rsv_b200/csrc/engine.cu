@@ -1390,7 +1390,8 @@ DsEntry make_entry(const LinearW& W, int G, int xvec, int out, int out_off, cons
     e.row_stride = row_bytes;
     e.piece_bytes = row_bytes / np;
     e.npieces = np;
-    e.is_i8 = i8 ? 1 : 0;
+    e.is_i8 = !i8 ? 0 : (W.wscale && W.wzero) ? 1 : 2;  // int8 with one (scale, zero) per row, or the container's one per row and group of 128
+    e.sz = W.sz;
     e.xvec = xvec;
     e.out = out;
     e.out_off = out_off;
@@ -1448,11 +1449,15 @@ bool Model::stream_available() {
     if (F != 4 * C) return fail("ffn_hidden is not 4 n_embd");
     if (H > G) return fail("more heads than SMs");
     if (cfg.w_mid % 8 || cfg.a_mid % 8 || cfg.v_mid % 8 || cfg.g_mid % 8) return fail("rank dimensions must be multiples of 8");
-    auto per_row = [](const LinearW& W) { return W.wtype != W_INT8 || (W.wscale && W.wzero); };
-    if (!per_row(head)) return fail("int8 head needs one (scale, zero) per output row");
-    for (const LayerW& Lw : layers)
+    // int8 matrices: one (scale, zero) per output row, or the reference container's one per row and group of 128 weights
+    auto format_of = [](const LinearW& W) { return W.wtype != W_INT8 ? 0 : (W.wscale && W.wzero) ? 1 : W.sz ? 2 : -1; };
+    if (format_of(head) < 0) return fail("int8 head without scales");
+    for (const LayerW& Lw : layers) {
         for (const LinearW* W : {&Lw.Wr, &Lw.Wk, &Lw.Wv, &Lw.Wo, &Lw.Wfk, &Lw.Wfv})
-            if (!per_row(*W)) return fail("int8 matrices need one (scale, zero) per output row");
+            if (format_of(*W) < 0) return fail("int8 matrix without scales");
+        if (format_of(Lw.Wr) != format_of(Lw.Wk) || format_of(Lw.Wr) != format_of(Lw.Wv)) return fail("receptance, key and value of a layer differ in their weight format");
+    }
+    if (F / 128 > kDsMaxGroups || C / 128 > kDsMaxGroups) return fail("reduction longer than 16384");
     if (C / G + 1 > kDsMaxSlice) return fail("too many channels per SM");
     if (3 * (C / G + 1) > kDsMaxRows || F / G + 1 > kDsMaxRows || V / G + 1 > kDsMaxRows) return fail("too many rows per SM");
     // shared memory: ring + operand area + fixed part + rank-space vector
@@ -1467,7 +1472,7 @@ bool Model::stream_available() {
     const int hb_a = 64 * (cfg.w_mid + cfg.a_mid) * 2, hb_b = 64 * cfg.v_mid * 2 + 32 * cfg.g_mid * 2, hb_c = 32 * cfg.g_mid * 2;
     const bool head_early = hb_a + hb_b + hb_c + std::max({hb_a, hb_b, hb_c}) > ring_bytes;
     if (head_early && std::max(2 * hb_a, hb_b + hb_c + std::max(hb_b, hb_c)) > ring_bytes) return fail("a head's back-projection rows do not fit in the shared-memory ring");
-    if (2 * kDsTileRows * (kDsMaxPiece + kDsPad) > ring_bytes) return fail("a chunk of rows does not fit twice in the shared-memory ring");
+    if (2 * (kDsTileRows * (kDsMaxPiece + kDsPad) + (kDsMaxPiece / 128) * kDsTileRows * 4) > ring_bytes) return fail("a chunk of rows does not fit twice in the shared-memory ring");
     {
         // tiles and partial-sum bytes of the largest phase of any CTA (rows per CTA rounded up)
         auto tiles_of = [&](int M, int nct) { return ((M + nct - 1) / nct + kDsTileRows - 1) / kDsTileRows + 1; };

@@ -55,7 +55,7 @@ def test_decode_logits_and_state_vs_oracle_and_golden(bundles, oracles, name):
     assert np.abs(sg - so).max() <= 1e-4 * max(1.0, float(np.abs(so).max()))
 
 
-@pytest.mark.parametrize("name", ["fp16", "int8"])
+@pytest.mark.parametrize("name", ["fp16", "int8", "int8g"])
 def test_argmax_stream_identical_config1(bundles, name):
     # benchmark config 1: 128 prompt tokens, then 64 arg-max tokens from the GPU self-loop
     b = bundles[name]

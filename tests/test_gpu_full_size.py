@@ -175,7 +175,7 @@ def _checkpoint(shape, quant_name):
     if not os.path.exists(path):
         os.makedirs(d, exist_ok=True)
         tmp = path + f".tmp{os.getpid()}"
-        rsv.write_synthetic(tmp, shape, seed=0, quant=1 if quant_name == "int8" else 0)
+        rsv.write_synthetic(tmp, shape, seed=0, quant={"fp16": 0, "int8": 1, "int8g": 2}[quant_name])
         os.replace(tmp, path)
     return path
 
@@ -227,3 +227,9 @@ def test_7b_int8_matches_oracle():
     # benchmark config 5's model: C = 4096, 64 heads, FFN 16384 (wider LayerNorm rows, more pieces per row, more tiles per SM),
     # prefill chunk 1024
     _short_parity(_checkpoint("7b", "int8"), n_prompt=6, n_stream=6, chunk_tokens=1024)
+
+
+def test_3b_per_group_int8_matches_oracle():
+    # the reference's own container (one scale and zero per row and group of 128 weights) at the 3B shape: the one-launch decode
+    # kernel rescales every group inside its multiply loop; prefill runs on the weight-streaming SIMT kernel
+    _short_parity(_checkpoint("3b", "int8g"), n_prompt=6, n_stream=16, chunk_tokens=64)
