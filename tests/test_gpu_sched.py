@@ -93,3 +93,43 @@ def test_scheduler_errors(bundle):
         sch.result(rid)
     with pytest.raises(rsv.RsvError):
         rsv.Scheduler(bundle.model, max_slots=4, chunk=8, max_rows=2)
+
+
+def _replica_set_equals_single_sessions(path, devices, bundle):
+    """A front end over one scheduler per model handle (rwkv_rsv_b200.router.ReplicaSet): sessions of very different sizes are
+    placed least-loaded, every replica packs its own steps, and every session's tokens equal the single-session API's."""
+    from rwkv_rsv_b200.router import ReplicaSet
+    rng = np.random.default_rng(23)
+    lens = [3, 90, 5, 17, 140, 2, 33, 8, 61, 12]
+    news = [6, 3, 10, 5, 2, 9, 4, 7, 3, 8]
+    sps = [None if i % 3 == 0 else rsv.SamplerParams(top_p=0.9, temperature=0.9, seed=1000 + i) for i in range(len(lens))]
+    prompts = [rng.integers(0, 4096, size=n).astype(np.uint32) for n in lens]
+    want = [single_session(bundle, p, n, sp) for p, n, sp in zip(prompts, news, sps)]
+    models = [rsv.Model(path, device=d) for d in devices]
+    rs = ReplicaSet([rsv.Scheduler(m, max_slots=3, chunk=32, max_rows=48, max_new_cap=16) for m in models])
+    try:
+        sids = [rs.submit(p, n, sp) for p, n, sp in zip(prompts, news, sps)]
+        placed = [rs.router.gpu_of(s) for s in sids]
+        assert set(placed) == set(range(len(devices)))             # both replicas got work ...
+        work = [sum(lens[i] + news[i] for i in range(len(lens)) if placed[i] == g) for g in range(len(devices))]
+        assert max(work) - min(work) <= max(l + n for l, n in zip(lens, news))  # ... balanced by tokens to within one session
+        done = rs.run_until_done()
+        assert sorted(done) == sids
+        for i, sid in enumerate(sids):
+            assert list(done[sid]) == want[i], f"session {i} on replica {placed[i]}"
+        assert rs.router.sessions == [0] * len(devices)
+    finally:
+        rs.close()
+        for m in models:
+            m.close()
+
+
+def test_replica_set_over_two_model_handles(bundle, tiny_paths):
+    _replica_set_equals_single_sessions(tiny_paths["int8"], [0, 0], bundle)
+
+
+def test_replica_set_over_two_gpus(bundle, tiny_paths):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _replica_set_equals_single_sessions(tiny_paths["int8"], [0, 1], bundle)
