@@ -969,8 +969,12 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 DS_STAMP_ALL(0);
                 // ================= phase 1: LN1 + token shift -> r, k, v, rank projections =================
                 {
-                    const int re = S->plan.rank_entry;  // at most one: the rank projections' rows are split over disjoint groups of CTAs
-                    const float* rmix = re >= 0 ? Ly.e[re].mix : Ly.x_r;
+                    // this CTA's two operand vectors: the shifted input of its big matrix (receptance, key and value rows lie on
+                    // disjoint thirds of the CTAs) and that of its rank projection (disjoint groups as well)
+                    const int re = S->plan.rank_entry;
+                    const int be = S->plan.en[DSE_WR] > 0 ? DSE_WR : S->plan.en[DSE_WK] > 0 ? DSE_WK : DSE_WV;
+                    const float* bmix = Ly.e[be].mix;
+                    const float* rmix = re >= 0 ? Ly.e[re].mix : bmix;
                     stage_scales(&Ly.e[DSE_W1], DSE_W1, 7);
                     if (!(ok = bar_wait())) break;
                     DS_STAMP(10);
@@ -1007,11 +1011,11 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                     ds_ln_stats<NG>(S, C, xv, wtid, mean, inv);
                     DS_STAMP(16);
                     // the mix vectors are loaded here, behind the barriers of the statistics, so that they do not sit in registers next to the row
-                    float4 val[4][NG];
+                    float4 val[2][NG];
 #pragma unroll
                     for (int gi = 0; gi < NG; ++gi) {
                         const int g4 = wtid + kDsConsumers * gi, k = g4 < C / 4 ? 4 * g4 : 0;
-                        const float4 m0 = ds_ldg4(Ly.x_r + k), m1 = ds_ldg4(Ly.x_k + k), m2 = ds_ldg4(Ly.x_v + k), m3 = ds_ldg4(rmix + k);
+                        const float4 m0 = ds_ldg4(bmix + k), m1 = ds_ldg4(rmix + k);
                         const float4 cur = ds_ln_apply(xv[gi], mean, inv, lw[gi], lb[gi]);
                         const float4 del = make_float4(pv[gi].x - cur.x, pv[gi].y - cur.y, pv[gi].z - cur.z, pv[gi].w - cur.w);
                         if (g4 < C / 4) {
@@ -1027,15 +1031,13 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         }
                         val[0][gi] = ds_mix4(cur, m0, del);
                         val[1][gi] = ds_mix4(cur, m1, del);
-                        val[2][gi] = ds_mix4(cur, m2, del);
-                        val[3][gi] = ds_mix4(cur, m3, del);
                     }
                     DS_STAMP(17);
-                    const bool i8[4] = {Ly.e[DSE_WR].is_i8 != 0, Ly.e[DSE_WK].is_i8 != 0, Ly.e[DSE_WV].is_i8 != 0, false};
+                    const bool i8[2] = {Ly.e[be].is_i8 != 0, false};
 #ifdef RSV_DS_DEBUG
-                    ds_emit<4, NG>(S, vec, C, i8, [&](int v, int gi) { return val[v][gi]; }, wtid, Ly.e[DSE_WR].is_i8 == 2, (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 52 : nullptr);
+                    ds_emit<2, NG>(S, vec, C, i8, [&](int v, int gi) { return val[v][gi]; }, wtid, Ly.e[be].is_i8 == 2, (P.dbg && cta == 0 && t == 1 && l == 1) ? P.dbg + 52 : nullptr);
 #else
-                    ds_emit<4, NG>(S, vec, C, i8, [&](int v, int gi) { return val[v][gi]; }, wtid, Ly.e[DSE_WR].is_i8 == 2);
+                    ds_emit<2, NG>(S, vec, C, i8, [&](int v, int gi) { return val[v][gi]; }, wtid, Ly.e[be].is_i8 == 2);
 #endif
                 }
                 DS_STAMP(1);

@@ -1459,7 +1459,8 @@ bool Model::stream_available() {
     }
     if (F / 128 > kDsMaxGroups || C / 128 > kDsMaxGroups) return fail("reduction longer than 16384");
     if (C / G + 1 > kDsMaxSlice) return fail("too many channels per SM");
-    if (3 * (C / G + 1) > kDsMaxRows || F / G + 1 > kDsMaxRows || V / G + 1 > kDsMaxRows) return fail("too many rows per SM");
+    if (G < 3) return fail("fewer than three SMs");
+    if (C / (G / 3) + 1 > kDsMaxRows || F / G + 1 > kDsMaxRows || V / G + 1 > kDsMaxRows) return fail("too many rows per SM");
     // shared memory: ring + operand area + fixed part + rank-space vector
     const size_t budget = 227 * 1024;
     const int vec_floats = std::max(4 * C, F);
@@ -1483,7 +1484,7 @@ bool Model::stream_available() {
         };
         const bool i8b = layers[0].Wr.wtype == W_INT8, i8h = head.wtype == W_INT8;
         const int rb = i8b ? C : 2 * C;
-        const int p1_tiles = 3 * tiles_of(C, G) + 2, p1_part = 3 * part_of(C, G, rb, i8b) + 2 * part_of(16, 1, 2 * C, false);
+        const int p1_tiles = tiles_of(C, G / 3) + 2, p1_part = part_of(C, G / 3, rb, i8b) + 2 * part_of(16, 1, 2 * C, false);
         const int p4_part = part_of(F, G, rb, i8b), p5_part = part_of(C, G, i8b ? F : 2 * F, i8b), ph_part = part_of(V, G, i8h ? C : 2 * C, i8h);
         if (std::max({p1_tiles, tiles_of(F, G), tiles_of(V, G)}) > kDsMaxTiles) return fail("too many tiles per SM");
         if (std::max({p1_part, p4_part, p5_part, ph_part}) > kDsPartBytes) return fail("partial sums of a phase do not fit in shared memory");
@@ -1507,10 +1508,12 @@ bool Model::stream_available() {
         const LayerW& Lw = layers[l];
         DsLayer& d = dl[l];
         memset(&d, 0, sizeof(d));
-        d.e[DSE_W1] = make_entry(Lw.w1, G, 3, DSO_MID_TANH, 0, Lw.x_w);
-        d.e[DSE_A1] = make_entry(Lw.a1, G, 3, DSO_MID, cfg.w_mid, Lw.x_a);
-        d.e[DSE_G1] = make_entry(Lw.g1, G, 3, DSO_MID_SIG, cfg.w_mid + cfg.a_mid + cfg.v_mid, Lw.x_g);
-        d.e[DSE_V1] = make_entry(Lw.v1, G, 3, DSO_MID, cfg.w_mid + cfg.a_mid, Lw.x_v);
+        // operand vectors of phase 1: 0 = the shifted input of the CTA's big matrix (receptance, key or value: see below), 1 = that of its
+        // rank projection
+        d.e[DSE_W1] = make_entry(Lw.w1, G, 1, DSO_MID_TANH, 0, Lw.x_w);
+        d.e[DSE_A1] = make_entry(Lw.a1, G, 1, DSO_MID, cfg.w_mid, Lw.x_a);
+        d.e[DSE_G1] = make_entry(Lw.g1, G, 1, DSO_MID_SIG, cfg.w_mid + cfg.a_mid + cfg.v_mid, Lw.x_g);
+        d.e[DSE_V1] = make_entry(Lw.v1, G, 1, DSO_MID, cfg.w_mid + cfg.a_mid, Lw.x_v);
         // The rows of the four rank projections go to disjoint groups of CTAs, sized by their row counts, so that a CTA builds the
         // shifted input of one of them only.
         {
@@ -1531,16 +1534,23 @@ bool Model::stream_available() {
         if (l == 0) d.e[DSE_V1].M = 0;  // layer 0 has no v gate
         for (const DsEntry* e : {&d.e[DSE_W1], &d.e[DSE_A1], &d.e[DSE_G1], &d.e[DSE_V1]})
             if (e->is_i8 || e->npieces * e->piece_bytes != 2 * C) return fail("rank projections must be fp16 [mid, n_embd]");
-        d.e[DSE_WR] = make_entry(Lw.Wr, G, 0, DSO_R, 0, nullptr, piece_layers);
-        d.e[DSE_WK] = make_entry(Lw.Wk, G, 1, DSO_K, 0, nullptr, piece_layers);
-        d.e[DSE_WV] = make_entry(Lw.Wv, G, 2, DSO_V, 0, nullptr, piece_layers);
+        d.e[DSE_WR] = make_entry(Lw.Wr, G, 0, DSO_R, 0, Lw.x_r, piece_layers);
+        d.e[DSE_WK] = make_entry(Lw.Wk, G, 0, DSO_K, 0, Lw.x_k, piece_layers);
+        d.e[DSE_WV] = make_entry(Lw.Wv, G, 0, DSO_V, 0, Lw.x_v, piece_layers);
         d.e[DSE_WO] = make_entry(Lw.Wo, G, 0, DSO_XADD, 0, nullptr, piece_layers);
         d.e[DSE_WFK] = make_entry(Lw.Wfk, G, 0, DSO_H, 0, nullptr, piece_layers);
         d.e[DSE_WFV] = make_entry(Lw.Wfv, G, 0, DSO_XADD, 0, nullptr, piece_layers);
-        // r, k, v: the CTAs that get an extra row of one matrix are not those of the next (att.output and ffn.value keep
-        // offset 0: their rows are the CTA's slice of x)
-        d.e[DSE_WK].cta0 = G / 3;
-        d.e[DSE_WV].cta0 = 2 * G / 3;
+        // receptance, key and value go to three disjoint thirds of the CTAs (all rows of one matrix over a third), so that a CTA
+        // builds the shifted input and the fixed-point digits of one of them instead of all three, and its rows make full tiles
+        {
+            const int third = G / 3;
+            d.e[DSE_WR].cta0 = 0;
+            d.e[DSE_WR].ncta = third;
+            d.e[DSE_WK].cta0 = third;
+            d.e[DSE_WK].ncta = third;
+            d.e[DSE_WV].cta0 = 2 * third;
+            d.e[DSE_WV].ncta = G - 2 * third;
+        }
         for (int i = 0; i < DSE_COUNT; ++i)
             if (d.e[i].piece_bytes % 128 || d.e[i].piece_bytes > kDsMaxPiece) return fail("a weight row does not split into pieces of a multiple of 128 bytes");
         d.w2 = (const __half*)Lw.w2.w;
