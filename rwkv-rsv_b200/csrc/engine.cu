@@ -374,8 +374,8 @@ std::unique_ptr<Model> Model::load(const std::string& path, int device) {
     for (int i = 0; i < Model::kPinRing; ++i) RSV_CUDA(cudaEventCreateWithFlags(&m->pin_ev[i], cudaEventDisableTiming));
     RSV_CUDA(cudaMalloc(&m->ws.status, 2 * sizeof(int)));
     RSV_CUDA(cudaMalloc(&m->ws.tok_pos, sizeof(int)));
-    RSV_CUDA(cudaMemset(m->ws.status, 0, 2 * sizeof(int)));
-    RSV_CUDA(cudaMemset(m->ws.tok_pos, 0, sizeof(int)));
+    RSV_CUDA(cudaMemsetAsync(m->ws.status, 0, 2 * sizeof(int), m->stream));
+    RSV_CUDA(cudaMemsetAsync(m->ws.tok_pos, 0, sizeof(int), m->stream));
     return m;
 }
 
@@ -398,7 +398,7 @@ std::unique_ptr<Model> Model::create_bare(int device) {
     RSV_CUDA(cudaEventCreate(&m->tev[0]));
     RSV_CUDA(cudaEventCreate(&m->tev[1]));
     RSV_CUDA(cudaMalloc(&m->ws.status, 2 * sizeof(int)));
-    RSV_CUDA(cudaMemset(m->ws.status, 0, 2 * sizeof(int)));
+    RSV_CUDA(cudaMemsetAsync(m->ws.status, 0, 2 * sizeof(int), m->stream));
     return m;
 }
 
@@ -502,7 +502,7 @@ void Model::ensure_workspace(int rows, int outs, int segs) {
     fa(ws.samp_temp, (size_t)outs * V);
     RSV_CUDA(cudaMalloc(&ws.samp_cnt, std::max<size_t>((size_t)outs * V, 4) * sizeof(uint32_t)));
     RSV_CUDA(cudaMalloc(&ws.tokens, R * sizeof(uint32_t)));
-    RSV_CUDA(cudaMemset(ws.tokens, 0, R * sizeof(uint32_t)));
+    RSV_CUDA(cudaMemsetAsync(ws.tokens, 0, R * sizeof(uint32_t), stream));
     RSV_CUDA(cudaMalloc(&ws.row_meta, R * sizeof(RowMeta)));
     RSV_CUDA(cudaMalloc(&ws.seg_meta, (size_t)segs * sizeof(SegMeta)));
     RSV_CUDA(cudaMalloc(&ws.out_rows, (size_t)std::max(outs, 1) * sizeof(int)));
@@ -627,7 +627,7 @@ void ensure_tc_buffers(Model& m, size_t b_bytes, size_t rows, size_t partial_byt
     Workspace& w = m.ws;
     if (!w.tc_cnt) {
         RSV_CUDA(cudaMalloc(&w.tc_cnt, (size_t)kTcMaxSplit * kTcEpiWarps * sizeof(int)));
-        RSV_CUDA(cudaMemset(w.tc_cnt, 0, (size_t)kTcMaxSplit * kTcEpiWarps * sizeof(int)));
+        RSV_CUDA(cudaMemsetAsync(w.tc_cnt, 0, (size_t)kTcMaxSplit * kTcEpiWarps * sizeof(int), m.stream));
     }
     if (b_bytes <= w.tc_b_bytes && rows <= w.tc_rows && partial_bytes <= w.tc_partials_bytes) return;
     RSV_CUDA(cudaStreamSynchronize(m.stream));
@@ -637,7 +637,7 @@ void ensure_tc_buffers(Model& m, size_t b_bytes, size_t rows, size_t partial_byt
         w.tc_b_bytes = 0;
         const size_t nb = b_bytes + b_bytes / 4;
         RSV_CUDA(cudaMalloc(&w.tc_b, nb));
-        RSV_CUDA(cudaMemset(w.tc_b, 0, nb));
+        RSV_CUDA(cudaMemsetAsync(w.tc_b, 0, nb, m.stream));
         w.tc_b_bytes = nb;
     }
     if (rows > w.tc_rows) {
@@ -1218,24 +1218,24 @@ bool Model::persistent_available(int nb) {
     RSV_CUDA(cudaMalloc(&pc.rkv, (size_t)kDpMaxNB * 3 * C * 4));
     RSV_CUDA(cudaMalloc(&pc.mid, (size_t)kDpMaxNB * cfg.mids() * 4));
     RSV_CUDA(cudaMalloc(&pc.hbuf, (size_t)kDpMaxNB * cfg.ffn_hidden * 4));
-    RSV_CUDA(cudaMemset(pc.mid, 0, (size_t)kDpMaxNB * cfg.mids() * 4));
+    RSV_CUDA(cudaMemsetAsync(pc.mid, 0, (size_t)kDpMaxNB * cfg.mids() * 4, stream));
     RSV_CUDA(cudaMalloc(&pc.cand_val, (size_t)G * kDpMaxNB * 4));
     RSV_CUDA(cudaMalloc(&pc.cand_idx, (size_t)G * kDpMaxNB * 4));
     RSV_CUDA(cudaMalloc(&pc.grid_bar, 4));
 #ifdef RSV_DP_DEBUG
     RSV_CUDA(cudaMalloc(&pc.dbg, (64 + 8 * 1024) * sizeof(long long)));
-    RSV_CUDA(cudaMemset(pc.dbg, 0, (64 + 8 * 1024) * sizeof(long long)));
+    RSV_CUDA(cudaMemsetAsync(pc.dbg, 0, (64 + 8 * 1024) * sizeof(long long), stream));
 #endif
-    RSV_CUDA(cudaMemset(pc.vfirst, 0, (size_t)kDpMaxNB * C * 4));
+    RSV_CUDA(cudaMemsetAsync(pc.vfirst, 0, (size_t)kDpMaxNB * C * 4, stream));
     for (int i = 0; i < 5; ++i) {
         const size_t runs = (size_t)tiles[i] * pmax[i];
         RSV_CUDA(cudaMalloc(&pc.region_data[i], runs * kDpN * 128 * 4));
         RSV_CUDA(cudaMalloc(&pc.region_meta[i], runs * kDpWarps * sizeof(DpRunMeta)));
         RSV_CUDA(cudaMalloc(&pc.region_cnt[i], (size_t)tiles[i] * kDpWarps * sizeof(int)));
         pc.region_cnt_bytes[i] = (size_t)tiles[i] * kDpWarps * sizeof(int);
-        RSV_CUDA(cudaMemset(pc.region_data[i], 0, runs * kDpN * 128 * 4));
-        RSV_CUDA(cudaMemset(pc.region_meta[i], 0, runs * kDpWarps * sizeof(DpRunMeta)));
-        RSV_CUDA(cudaMemset(pc.region_cnt[i], 0, (size_t)tiles[i] * kDpWarps * sizeof(int)));
+        RSV_CUDA(cudaMemsetAsync(pc.region_data[i], 0, runs * kDpN * 128 * 4, stream));
+        RSV_CUDA(cudaMemsetAsync(pc.region_meta[i], 0, runs * kDpWarps * sizeof(DpRunMeta), stream));
+        RSV_CUDA(cudaMemsetAsync(pc.region_cnt[i], 0, (size_t)tiles[i] * kDpWarps * sizeof(int), stream));
         pc.region_pmax[i] = pmax[i];
     }
     // layer tables need the state pointers of the call: only the state-independent part is stored here
@@ -1624,11 +1624,11 @@ bool Model::stream_available() {
     RSV_CUDA(cudaMalloc(&sc.cand_val, (size_t)G * 4));
     RSV_CUDA(cudaMalloc(&sc.cand_idx, (size_t)G * 4));
     RSV_CUDA(cudaMalloc(&sc.grid_bar, 4));
-    RSV_CUDA(cudaMemset(sc.mid, 0, (size_t)std::max(cfg.mids(), 1) * 4));
-    RSV_CUDA(cudaMemset(sc.vfirst, 0, (size_t)C * 4));
+    RSV_CUDA(cudaMemsetAsync(sc.mid, 0, (size_t)std::max(cfg.mids(), 1) * 4, stream));
+    RSV_CUDA(cudaMemsetAsync(sc.vfirst, 0, (size_t)C * 4, stream));
 #ifdef RSV_DS_DEBUG
     RSV_CUDA(cudaMalloc(&sc.dbg, (256 + 16 * 256) * sizeof(long long)));
-    RSV_CUDA(cudaMemset(sc.dbg, 0, (256 + 16 * 256) * sizeof(long long)));
+    RSV_CUDA(cudaMemsetAsync(sc.dbg, 0, (256 + 16 * 256) * sizeof(long long), stream));
 #endif
     P.layers = (const DsLayer*)sc.d_layers;
     P.head = make_entry(head, G, 0, DSO_LOGITS, 0, nullptr);
@@ -1745,7 +1745,7 @@ void Model::run_stream(State& st, int slot, int n_tokens, bool tok_from_list, bo
                 if (n) fprintf(stderr, "    %-18s %7.2f %7.2f %7.2f (%d)\n", nm[k], (mn - h[0]) / 1e3, sum / 1e3 / n, (mx - h[0]) / 1e3, amx);
             }
         }
-        RSV_CUDA(cudaMemset(sc.dbg, 0, (256 + 16 * 256) * sizeof(long long)));
+        RSV_CUDA(cudaMemsetAsync(sc.dbg, 0, (256 + 16 * 256) * sizeof(long long), stream));
     }
 #endif
 }

@@ -385,3 +385,29 @@ def test_text_level_driver(bundles, tiny_paths, tmp_path, capsys):
     assert json.loads(printed[0])[:2] == prompt and len(json.loads(printed[0])) == 7
     with pytest.raises(SystemExit):
         gen.main(["--model", tiny_paths["int8"], "--prompt", "x"])
+
+
+def test_first_use_of_the_small_batch_kernel_on_recycled_memory(bundles, tiny_paths):
+    # The one-launch kernels allocate their counters and scratch on first use; the allocator may hand them memory another buffer
+    # has just left full of other bits, and zeroing it has to be ordered before the first launch on the model's own stream.
+    b = bundles["int8"]
+    rng = np.random.default_rng(41)
+    prompts = [rng.integers(0, 4096, size=k).astype(np.uint32) for k in (11, 4, 23)]
+    want = []
+    for p in prompts:
+        b.reset()
+        b.infer_seq(p)
+        want.append(list(b.infer_argmax_selfloop(int(p[-1]), 10)))
+    m = rsv.Model(tiny_paths["int8"])  # a fresh handle: nothing built yet
+    try:
+        big = m.create_batch_state(96)
+        big.load(np.full(len(big), -3.0e38, dtype=np.float32))  # 50 MB of non-zero bits ...
+        big.close()                                             # ... back to the allocator
+        st = m.create_batch_state(3)
+        seeds = m.forward_seq_batch(st, prompts)
+        out = m.collect_sample_selfloop_batch(m.submit_sample_selfloop_batch(st, seeds, 10, None))  # first launch of the 2-4 session kernel
+        for i in range(3):
+            assert list(out[i]) == want[i], i
+        st.close()
+    finally:
+        m.close()
