@@ -116,7 +116,6 @@ struct DsParams {
     const char* hstream;      // the head's rows in consumption order: region of CTA c at c hslot
     long long hslot;
     int ring_bytes;  // shared-memory ring
-    int variant;     // experiment switches (bit mask)
     int head_early;  // 1: a head's first chunk (w2, a2 rows) is released before the other two are awaited (ring too small for all three)
     int vec_floats;  // operand area, in 4-byte elements: max(4 C, F)
     long long* dbg;  // optional time stamps (built with -DRSV_DS_DEBUG only)
@@ -637,14 +636,8 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
         int old = 0;
         if (lane == 0) {
             mbar_arrive(&S->empty[wwarp]);
-            if (P.variant & 8) {
-                // one acquire-release atomic at CTA scope: releases this warp's partial sums (ordered before it by __syncwarp) and, for
-                // the warp that arrives last, acquires the others'
-                asm volatile("atom.acq_rel.cta.shared.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(smem_u32(&S->tile_cnt[tile_idx])) : "memory");
-            } else {
-                __threadfence_block();
-                old = atomicAdd(&S->tile_cnt[tile_idx], 1);
-            }
+            __threadfence_block();
+            old = atomicAdd(&S->tile_cnt[tile_idx], 1);
         }
         old = __shfl_sync(0xffffffffu, old, 0);
 #ifdef RSV_DS_DEBUG
@@ -661,20 +654,13 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
 #endif
         if (old == np - 1) {
             // last piece of the tile: lane r adds the pieces of row r in piece order and stores the output
-            if (!(P.variant & 8)) __threadfence_block();
+            __threadfence_block();
             const int rl = row0 + lane;
             long long T = 0;
             if (i8 && !pg) {  // exact sum of the operand's fixed-point values: 16 per-warp sums, one per lane, then a shuffle tree
-                if (P.variant & 4) {
-                    // every lane adds the 16 per-warp sums itself (broadcast reads, no shuffle chain)
-                    const long long* tw = S->tsw[E.xvec];
+                T = S->tsw[E.xvec][lane & 15];
 #pragma unroll
-                    for (int q = 0; q < 16; ++q) T += tw[q];
-                } else {
-                    T = S->tsw[E.xvec][lane & 15];
-#pragma unroll
-                    for (int o = 8; o > 0; o >>= 1) T += __shfl_xor_sync(0xffffffffu, T, o);
-                }
+                for (int o = 8; o > 0; o >>= 1) T += __shfl_xor_sync(0xffffffffu, T, o);
             }
             if (lane < nr) {
                 const char* pt = reinterpret_cast<const char*>(S->part) + part_off;
@@ -920,17 +906,13 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                 bool got = false;
                 for (uint32_t i = 0; i < kDsBarSpin; ++i) {
                     unsigned v;
-                    if (P.variant & 2)
-                        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.grid_bar) : "memory");
-                    else
-                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.grid_bar) : "memory");
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.grid_bar) : "memory");
                     if ((int)(v - bar_target) >= 0) {
                         got = true;
                         break;
                     }
                     if ((i & 255u) == 255u && *abort_flag) break;
                 }
-                if (P.variant & 2) fence_acq_rel_gpu();
                 if (!got) {
                     atomicCAS(&S->abort_where, 0, 3 | (int)(bar_target << 4));
                     *abort_flag = 1;
@@ -945,12 +927,7 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
             if (wtid == 0) {
                 // one release operation instead of a fence and a relaxed atomic (the bar.sync above ordered the other warps' stores
                 // before this thread)
-                if (P.variant & 1) {
-                    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.grid_bar) : "memory");
-                } else {
-                    fence_acq_rel_gpu();
-                    atomicAdd(P.grid_bar, 1u);
-                }
+                asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.grid_bar) : "memory");
             }
             bar_target += (unsigned)G;
             pending = true;

@@ -1662,7 +1662,6 @@ bool Model::stream_available() {
     P.hslot = sc.hslot;
     P.ring_bytes = ring_bytes;
     P.head_early = head_early ? 1 : 0;
-    if (const char* e = getenv("RSV_DS_VARIANT")) P.variant = atoi(e);
     P.vec_floats = vec_floats;
     P.dbg = sc.dbg;
     sc.params_template.resize(sizeof(DsParams));
