@@ -137,6 +137,24 @@ public:
         check(rsv_prefill_batch(h_, st.handle(), flat.data(), lens.data(), (int64_t)tokens_batch.size(), (int64_t)t_pad, seeds.data()));
         return seeds;
     }
+    // forward_seq_batch_mean_hidden (:1013-1036): resets the state, prefills, returns per slot the token mean of the last layer's
+    // residual stream; pad_to (0: none) fixes the row pitch of the token matrix
+    std::vector<std::vector<float>> forward_seq_batch_mean_hidden(State& st, const std::vector<std::vector<uint32_t>>& tokens_batch, size_t pad_to = 0) {
+        if (tokens_batch.empty()) throw Error("forward_seq_batch: empty batch");
+        size_t t_pad = std::max<size_t>(1, pad_to);
+        for (auto& t : tokens_batch) t_pad = std::max(t_pad, t.size());
+        std::vector<uint32_t> flat(tokens_batch.size() * t_pad, 0u), lens(tokens_batch.size());
+        for (size_t b = 0; b < tokens_batch.size(); ++b) {
+            std::copy(tokens_batch[b].begin(), tokens_batch[b].end(), flat.begin() + b * t_pad);
+            lens[b] = (uint32_t)tokens_batch[b].size();
+        }
+        const size_t c = (size_t)info().num_emb;
+        std::vector<float> mean(tokens_batch.size() * c);
+        check(rsv_prefill_batch_mean_hidden(h_, st.handle(), flat.data(), lens.data(), (int64_t)tokens_batch.size(), (int64_t)t_pad, mean.data()));
+        std::vector<std::vector<float>> out(tokens_batch.size());
+        for (size_t b = 0; b < out.size(); ++b) out[b].assign(mean.begin() + b * c, mean.begin() + (b + 1) * c);
+        return out;
+    }
     // submit_sample_selfloop_batch (:1639-1781); sp == nullptr -> arg-max
     SelfloopTicket submit_sample_selfloop_batch(State& st, const std::vector<uint32_t>& seeds, size_t n, const SamplerParams* sp) {
         SelfloopTicket t;
