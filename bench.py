@@ -11,7 +11,12 @@ prompt prefilled and then an arg-max self-loop).  Prints ONE JSON line.
   e2e       the same metric through the host-buffer API: per step the tokens go host->device and the
             logits come back device->host
   roofline  the dominant kernel's algorithmic bytes / its mean device time, against the measured HBM peak
-  cpu_baseline  the CPU oracle timed on this box (bounded sample)
+  cpu_baseline  the CPU oracle timed on this box (bounded sample; all cores and one core)
+Further keys, each run by every rank (times = the slowest rank's, tokens summed): `batch_sweep` (decode at 1, 8, 64, 256, 1024
+sessions per GPU), `batch_sweep_fixed_total` (N > 1: that many sessions in all, sharded by id mod N), `prefill` (one session's
+2048 tokens in 512-token chunks per GPU), `continuous_batching` (benchmark config 3: 256 Poisson sessions per GPU, routed
+least-loaded; `..._fixed_total` at N > 1), `other_weight_formats` (N = 1: fp16 and the reference's per-group int8 container at
+batch 1 and 64), `timed_regions` (the timed region of K steps is repeated for about a second; the median is reported).
 Inputs are synthetic: seeded random-init weights of the named shape, uniform random prompt tokens.
 Every step streams all weights (3.1 GB at the 3B int8 shape), far more than the 126 MB L2, so no L2 flush
 is needed between timed iterations.
