@@ -1008,15 +1008,22 @@ __global__ void __launch_bounds__(kDsThreads, 1) decode_stream_kernel(const __gr
                         for (int gi = 0; gi < NG; ++gi) xv[gi] = ds_ln_apply(xv[gi], m0, i0, w0v[gi], b0v[gi]);
                     }
                     DS_STAMP(15);
+                    // the two mix vectors are requested before the statistics: their latency hides behind the two block-wide sums
+                    float4 mx0[NG], mx1[NG];
+#pragma unroll
+                    for (int gi = 0; gi < NG; ++gi) {
+                        const int g4 = wtid + kDsConsumers * gi, k = g4 < C / 4 ? 4 * g4 : 0;
+                        mx0[gi] = ds_ldg4(bmix + k);
+                        mx1[gi] = ds_ldg4(rmix + k);
+                    }
                     float mean, inv;
                     ds_ln_stats<NG>(S, C, xv, wtid, mean, inv);
                     DS_STAMP(16);
-                    // the mix vectors are loaded here, behind the barriers of the statistics, so that they do not sit in registers next to the row
                     float4 val[2][NG];
 #pragma unroll
                     for (int gi = 0; gi < NG; ++gi) {
                         const int g4 = wtid + kDsConsumers * gi, k = g4 < C / 4 ? 4 * g4 : 0;
-                        const float4 m0 = ds_ldg4(bmix + k), m1 = ds_ldg4(rmix + k);
+                        const float4 m0 = mx0[gi], m1 = mx1[gi];
                         const float4 cur = ds_ln_apply(xv[gi], mean, inv, lw[gi], lb[gi]);
                         const float4 del = make_float4(pv[gi].x - cur.x, pv[gi].y - cur.y, pv[gi].z - cur.z, pv[gi].w - cur.w);
                         if (g4 < C / 4) {
