@@ -39,6 +39,7 @@
 #pragma once
 #include <cstddef>
 
+#include "kernels.cuh"
 #include "tc_linear.cuh"
 
 namespace rsv {

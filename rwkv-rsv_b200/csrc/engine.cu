@@ -9,7 +9,7 @@
 #include "safetensors.hpp"
 #include "tc_linear.cuh"
 #include "decode_persistent.cuh"
-#include "decode_stream.cuh"
+#include "decode_stream_layout.hpp"
 #include "wkv_rows.cuh"
 #include "wkv_seq.cuh"
 
@@ -1374,32 +1374,6 @@ void Model::run_persistent(State& st, int nb, const int* slots, int n_tokens, bo
 // ------------------------------------------------------------------------------------------------
 namespace {
 
-DsEntry make_entry(const LinearW& W, int G, int xvec, int out, int out_off, const float* mix, int max_piece = kDsMaxPiece) {
-    DsEntry e;
-    memset(&e, 0, sizeof(e));
-    const bool i8 = W.wtype == W_INT8;
-    const int row_bytes = i8 ? W.K : 2 * W.K;
-    // pieces of at most kDsMaxPiece bytes, each a multiple of 128 bytes
-    int np = (row_bytes + max_piece - 1) / max_piece;
-    while (np <= row_bytes / 128 && row_bytes % (np * 128)) ++np;
-    e.base = (const char*)W.w;
-    e.wscale = W.wscale;
-    e.wzero = W.wzero;
-    e.mix = mix;
-    e.M = W.M;
-    e.row_stride = row_bytes;
-    e.piece_bytes = row_bytes / np;
-    e.npieces = np;
-    e.is_i8 = !i8 ? 0 : (W.wscale && W.wzero) ? 1 : 2;  // int8 with one (scale, zero) per row, or the container's one per row and group of 128
-    e.sz = W.sz;
-    e.xvec = xvec;
-    e.out = out;
-    e.out_off = out_off;
-    e.cta0 = 0;
-    e.ncta = G;
-    return e;
-}
-
 template <int CMAX>
 void launch_stream(const DsParams& P, int grid, size_t smem, cudaStream_t stream, bool configure_only) {
     if (configure_only) {
@@ -1442,58 +1416,27 @@ bool Model::stream_available() {
     RSV_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));
     if (!coop) return fail("device does not support cooperative launches");
     const int L = cfg.n_layer, C = cfg.n_embd, F = cfg.ffn_hidden, V = cfg.vocab, H = cfg.n_head, G = num_sms;
-    int cmax = 0;
-    for (int c : {512, 1024, 2048, 2560, 4096})
-        if (!cmax && C <= c) cmax = c;
-    if (C % 128 || !cmax) return fail("n_embd must be a multiple of 128 and at most 4096");
-    if (F != 4 * C) return fail("ffn_hidden is not 4 n_embd");
-    if (H > G) return fail("more heads than SMs");
-    if (cfg.w_mid % 8 || cfg.a_mid % 8 || cfg.v_mid % 8 || cfg.g_mid % 8) return fail("rank dimensions must be multiples of 8");
     // int8 matrices: one (scale, zero) per output row, or the reference container's one per row and group of 128 weights
     auto format_of = [](const LinearW& W) { return W.wtype != W_INT8 ? 0 : (W.wscale && W.wzero) ? 1 : W.sz ? 2 : -1; };
     if (format_of(head) < 0) return fail("int8 head without scales");
-    for (const LayerW& Lw : layers) {
+    const int fmt = layers.empty() ? 0 : format_of(layers[0].Wr);
+    for (const LayerW& Lw : layers)
         for (const LinearW* W : {&Lw.Wr, &Lw.Wk, &Lw.Wv, &Lw.Wo, &Lw.Wfk, &Lw.Wfv})
-            if (format_of(*W) < 0) return fail("int8 matrix without scales");
-        if (format_of(Lw.Wr) != format_of(Lw.Wk) || format_of(Lw.Wr) != format_of(Lw.Wv)) return fail("receptance, key and value of a layer differ in their weight format");
-    }
-    if (F / 128 > kDsMaxGroups || C / 128 > kDsMaxGroups) return fail("reduction longer than 16384");
-    if (C / G + 1 > kDsMaxSlice) return fail("too many channels per SM");
-    if (G < 3) return fail("fewer than three SMs");
-    if (C / (G / 3) + 1 > kDsMaxRows || F / G + 1 > kDsMaxRows || V / G + 1 > kDsMaxRows) return fail("too many rows per SM");
-    // shared memory: ring + operand area + fixed part + rank-space vector
-    const size_t budget = 227 * 1024;
-    const int vec_floats = std::max(4 * C, F);
-    const size_t fixed = (size_t)vec_floats * 4 + sizeof(DsShared) + (size_t)cfg.mids() * 4 + 256;
-    if (fixed + 64 * 1024 > budget) return fail("operand area does not fit in shared memory");
-    const int ring_bytes = (int)((budget - fixed) / 128 * 128);
-    // A head's back-projection rows come as three chunks (w2 + a2; v2 + half of g2; the other half of g2).  The ring hands out
-    // contiguous space in order, so what must be resident together needs its bytes plus one wrap's waste (< the largest chunk):
-    // all three when the head phase returns them together, else the first alone and then the other two.
-    const int hb_a = 64 * (cfg.w_mid + cfg.a_mid) * 2, hb_b = 64 * cfg.v_mid * 2 + 32 * cfg.g_mid * 2, hb_c = 32 * cfg.g_mid * 2;
-    const bool head_early = hb_a + hb_b + hb_c + std::max({hb_a, hb_b, hb_c}) > ring_bytes;
-    if (head_early && std::max(2 * hb_a, hb_b + hb_c + std::max(hb_b, hb_c)) > ring_bytes) return fail("a head's back-projection rows do not fit in the shared-memory ring");
-    if (2 * (kDsTileRows * (kDsMaxPiece + kDsPad) + (kDsMaxPiece / 128) * kDsTileRows * 4) > ring_bytes) return fail("a chunk of rows does not fit twice in the shared-memory ring");
+            if (format_of(*W) != fmt || fmt < 0) return fail("the big matrices of the layers differ in their weight format, or an int8 matrix has no scales");
+    // the layout (row ownership, chunks, shared memory, every capacity of the kernel's tables) is pure arithmetic on the shape
+    const DsShape shp{L, C, F, V, H, cfg.w_mid, cfg.a_mid, cfg.v_mid, cfg.g_mid, fmt, format_of(head)};
+    DsLayout lay;
     {
-        // tiles and partial-sum bytes of the largest phase of any CTA (rows per CTA rounded up)
-        auto tiles_of = [&](int M, int nct) { return ((M + nct - 1) / nct + kDsTileRows - 1) / kDsTileRows + 1; };
-        auto part_of = [&](int M, int nct, int row_bytes, bool i8) {
-            int np = (row_bytes + kDsMaxPiece - 1) / kDsMaxPiece;
-            while (np <= row_bytes / 128 && row_bytes % (np * 128)) ++np;
-            return tiles_of(M, nct) * np * kDsTileRows * (i8 ? 8 : 4);
-        };
-        const bool i8b = layers[0].Wr.wtype == W_INT8, i8h = head.wtype == W_INT8;
-        const int rb = i8b ? C : 2 * C;
-        const int p1_tiles = tiles_of(C, G / 3) + 2, p1_part = part_of(C, G / 3, rb, i8b) + 2 * part_of(16, 1, 2 * C, false);
-        const int p4_part = part_of(F, G, rb, i8b), p5_part = part_of(C, G, i8b ? F : 2 * F, i8b), ph_part = part_of(V, G, i8h ? C : 2 * C, i8h);
-        if (std::max({p1_tiles, tiles_of(F, G), tiles_of(V, G)}) > kDsMaxTiles) return fail("too many tiles per SM");
-        if (std::max({p1_part, p4_part, p5_part, ph_part}) > kDsPartBytes) return fail("partial sums of a phase do not fit in shared memory");
+        std::string why;
+        if (!ds_layout(shp, G, lay, why)) return fail(why);
     }
+    const int cmax = lay.cmax, vec_floats = lay.vec_floats, ring_bytes = lay.ring_bytes;
+    const bool head_early = lay.head_early;
     sc.kl = cmax;
     sc.grid = G;
     sc.ring_bytes = ring_bytes;
     sc.vec_floats = vec_floats;
-    sc.smem = (size_t)ring_bytes + fixed;
+    sc.smem = lay.smem;
     DsParams P;
     memset(&P, 0, sizeof(P));
     try {
@@ -1501,58 +1444,28 @@ bool Model::stream_available() {
     } catch (const std::exception& e) {
         return fail(e.what());
     }
-    // per-layer tables
-    const int piece_layers = kDsLayerPiece;  // the head's rows (many tiles, nothing to overlap with) take the larger kDsMaxPiece
+    // per-layer tables: sizes and CTA groups from the layout, pointers from the checkpoint
+    auto bind = [&](DsEntry& e, const LinearW& W, const float* mix) -> bool {
+        if (e.M != 0 && (W.M != e.M || (e.is_i8 ? W.K : 2 * W.K) != e.row_stride)) return false;
+        e.base = (const char*)W.w;
+        e.wscale = W.wscale;
+        e.wzero = W.wzero;
+        e.sz = W.sz;
+        e.mix = mix;
+        return true;
+    };
     std::vector<DsLayer> dl((size_t)L);
     for (int l = 0; l < L; ++l) {
         const LayerW& Lw = layers[l];
         DsLayer& d = dl[l];
         memset(&d, 0, sizeof(d));
-        // operand vectors of phase 1: 0 = the shifted input of the CTA's big matrix (receptance, key or value: see below), 1 = that of its
-        // rank projection
-        d.e[DSE_W1] = make_entry(Lw.w1, G, 1, DSO_MID_TANH, 0, Lw.x_w);
-        d.e[DSE_A1] = make_entry(Lw.a1, G, 1, DSO_MID, cfg.w_mid, Lw.x_a);
-        d.e[DSE_G1] = make_entry(Lw.g1, G, 1, DSO_MID_SIG, cfg.w_mid + cfg.a_mid + cfg.v_mid, Lw.x_g);
-        d.e[DSE_V1] = make_entry(Lw.v1, G, 1, DSO_MID, cfg.w_mid + cfg.a_mid, Lw.x_v);
-        // The rows of the four rank projections go to disjoint groups of CTAs, sized by their row counts, so that a CTA builds the
-        // shifted input of one of them only.
-        {
-            const int order[4] = {DSE_W1, DSE_A1, DSE_V1, DSE_G1};
-            const int rows_of_e[4] = {cfg.w_mid, cfg.a_mid, cfg.v_mid, cfg.g_mid};
-            int c0 = 0, rows_left = cfg.mids(), ctas_left = G;
-            for (int i = 0; i < 4; ++i) {
-                DsEntry& e = d.e[order[i]];
-                int nc = i == 3 ? ctas_left : std::max(1, (int)((long long)ctas_left * rows_of_e[i] / std::max(rows_left, 1)));
-                nc = std::max(1, std::min(nc, ctas_left - (3 - i)));
-                e.cta0 = c0;
-                e.ncta = nc;
-                c0 += nc;
-                ctas_left -= nc;
-                rows_left -= rows_of_e[i];
-            }
-        }
-        if (l == 0) d.e[DSE_V1].M = 0;  // layer 0 has no v gate
-        for (const DsEntry* e : {&d.e[DSE_W1], &d.e[DSE_A1], &d.e[DSE_G1], &d.e[DSE_V1]})
-            if (e->is_i8 || e->npieces * e->piece_bytes != 2 * C) return fail("rank projections must be fp16 [mid, n_embd]");
-        d.e[DSE_WR] = make_entry(Lw.Wr, G, 0, DSO_R, 0, Lw.x_r, piece_layers);
-        d.e[DSE_WK] = make_entry(Lw.Wk, G, 0, DSO_K, 0, Lw.x_k, piece_layers);
-        d.e[DSE_WV] = make_entry(Lw.Wv, G, 0, DSO_V, 0, Lw.x_v, piece_layers);
-        d.e[DSE_WO] = make_entry(Lw.Wo, G, 0, DSO_XADD, 0, nullptr, piece_layers);
-        d.e[DSE_WFK] = make_entry(Lw.Wfk, G, 0, DSO_H, 0, nullptr, piece_layers);
-        d.e[DSE_WFV] = make_entry(Lw.Wfv, G, 0, DSO_XADD, 0, nullptr, piece_layers);
-        // receptance, key and value go to three disjoint thirds of the CTAs (all rows of one matrix over a third), so that a CTA
-        // builds the shifted input and the fixed-point digits of one of them instead of all three, and its rows make full tiles
-        {
-            const int third = G / 3;
-            d.e[DSE_WR].cta0 = 0;
-            d.e[DSE_WR].ncta = third;
-            d.e[DSE_WK].cta0 = third;
-            d.e[DSE_WK].ncta = third;
-            d.e[DSE_WV].cta0 = 2 * third;
-            d.e[DSE_WV].ncta = G - 2 * third;
-        }
-        for (int i = 0; i < DSE_COUNT; ++i)
-            if (d.e[i].piece_bytes % 128 || d.e[i].piece_bytes > kDsMaxPiece) return fail("a weight row does not split into pieces of a multiple of 128 bytes");
+        ds_layer_entries(shp, G, l > 0, d.e);
+        if (!(bind(d.e[DSE_W1], Lw.w1, Lw.x_w) && bind(d.e[DSE_A1], Lw.a1, Lw.x_a) && bind(d.e[DSE_G1], Lw.g1, Lw.x_g) && bind(d.e[DSE_V1], Lw.v1, Lw.x_v) &&
+              bind(d.e[DSE_WR], Lw.Wr, Lw.x_r) && bind(d.e[DSE_WK], Lw.Wk, Lw.x_k) && bind(d.e[DSE_WV], Lw.Wv, Lw.x_v) && bind(d.e[DSE_WO], Lw.Wo, nullptr) &&
+              bind(d.e[DSE_WFK], Lw.Wfk, nullptr) && bind(d.e[DSE_WFV], Lw.Wfv, nullptr)))
+            return fail("a matrix of the checkpoint does not have the model's shape");
+        for (const LinearW* W : {&Lw.w1, &Lw.a1, &Lw.g1, &Lw.v1})
+            if (W->wtype != W_F16) return fail("rank projections must be fp16 [mid, n_embd]");
         d.w2 = (const __half*)Lw.w2.w;
         d.a2 = (const __half*)Lw.a2.w;
         d.v2 = (const __half*)Lw.v2.w;
@@ -1578,21 +1491,9 @@ bool Model::stream_available() {
     RSV_CUDA(cudaMemcpy(sc.d_layers, dl.data(), dl.size() * sizeof(DsLayer), cudaMemcpyHostToDevice));
     {
         // second copy of the weights in the order the kernel consumes them (a chunk = one bulk copy): region sizes = the largest CTA's
-        long long wslot = 0, hslot = 0;
-        DsEntry head_e = make_entry(head, G, 0, DSO_LOGITS, 0, nullptr);
-        auto plan = std::make_unique<DsPlan>();
-        for (int c = 0; c < G; ++c) {
-            if (!ds_build_plan(*plan, dl[L > 1 ? 1 : 0].e, head_e, c, G, 0u)) return fail("too many chunks per SM for the chunk table");
-            long long rows = 0, hd = 0;
-            for (int ph = DSP_P1; ph <= DSP_P5; ++ph)
-                for (int k = plan->ph0[ph]; k < plan->ph0[ph] + plan->phn[ph]; ++k) rows += plan->ctab[k].cb;
-            for (int k = plan->ph0[DSP_HEAD]; k < plan->ph0[DSP_HEAD] + plan->phn[DSP_HEAD]; ++k) hd += plan->ctab[k].cb;
-            wslot = std::max(wslot, rows);
-            hslot = std::max(hslot, hd);
-        }
-        wslot += 128LL * (cfg.w_mid + cfg.a_mid + cfg.v_mid + cfg.g_mid);  // a head's back-projection rows
-        wslot = (wslot + 255) / 256 * 256;
-        hslot = (hslot + 255) / 256 * 256;
+        const long long wslot = lay.wslot, hslot = lay.hslot;
+        DsEntry head_e = ds_head_entry(shp, G);
+        if (!bind(head_e, head, nullptr)) return fail("the head of the checkpoint does not have the model's shape");
         sc.wslot = wslot;
         sc.hslot = hslot;
         RSV_CUDA(cudaMalloc(&sc.wstream, (size_t)wslot * G * L));
@@ -1631,8 +1532,8 @@ bool Model::stream_available() {
     RSV_CUDA(cudaMemsetAsync(sc.dbg, 0, (256 + 16 * 256) * sizeof(long long), stream));
 #endif
     P.layers = (const DsLayer*)sc.d_layers;
-    P.head = make_entry(head, G, 0, DSO_LOGITS, 0, nullptr);
-    if (P.head.piece_bytes % 128 || P.head.piece_bytes > kDsMaxPiece) return fail("a head row does not split into pieces of a multiple of 128 bytes");
+    P.head = ds_head_entry(shp, G);
+    bind(P.head, head, nullptr);
     P.emb = emb;
     P.ln0_w = ln0_w;
     P.ln0_b = ln0_b;
