@@ -114,6 +114,7 @@ class Rwkv7Numpy:
             prev_c, st["cmix_x"] = st["cmix_x"], ln2
             xb = ln2 + L["ffn_x_k"] * (prev_c - ln2)
             x = x + L["Wfv"] @ (np.maximum(L["Wfk"] @ xb, 0.0) ** 2)
+        self.last_hidden = x  # the last layer's residual stream, before ln_out
         return self.head @ self._ln(x, self.ln_out, LN_EPS)
 
     def forward(self, state, tokens):

@@ -208,3 +208,55 @@ def test_parser_rejects_a_shape_larger_than_its_data(tiny_paths, tmp_path):
     bad2 = _rewrite_header(tiny_paths["fp16"], str(tmp_path / "bad_neg.st"), negative)
     with pytest.raises(RuntimeError):
         orc.OracleModel(bad2)
+
+
+def test_wkv7_step_matches_an_independent_float64_statement():
+    # the op-level restatement (orc_wkv7) against the matrix form of the same recurrence written with einsum in float64
+    rng = np.random.default_rng(12)
+    H, T, N = 3, 5, 64
+    C = H * N
+    f = lambda *s: rng.standard_normal(s)
+    sig = lambda z: 1.0 / (1.0 + np.exp(-z))
+    r, k, v, g = f(T, C), f(T, C), f(T, C), f(T, C)
+    w, a = np.exp(-np.exp(-0.5) * sig(f(T, C))), sig(f(T, C))
+    vgate, vfirst = sig(f(T, C)), f(T, C)
+    k_k, k_a, r_k = rng.uniform(0.5, 1.5, C), rng.uniform(0, 1, C), 0.02 * f(C)
+    lnx_w, lnx_b = 1 + 0.02 * f(C), 0.02 * f(C)
+    S0 = 0.1 * f(H, N, N)
+    for gate in (False, True):
+        S, ys = S0.copy(), []
+        for t in range(T):
+            vt = (v[t] + vgate[t] * (vfirst[t] - v[t])) if gate else v[t]
+            kk = (k[t] * k_k).reshape(H, N)
+            kk = kk / np.maximum(np.sqrt((kk * kk).sum(1, keepdims=True)), 1e-12)
+            kt = (k[t] + k_a * (k[t] * a[t] - k[t])).reshape(H, N)
+            b = -kk * a[t].reshape(H, N)
+            sa = np.einsum("hij,hj->hi", S, kk)
+            S = S * w[t].reshape(H, 1, N) + sa[:, :, None] * b[:, None, :] + vt.reshape(H, N)[:, :, None] * kt[:, None, :]
+            y = np.einsum("hij,hj->hi", S, r[t].reshape(H, N))
+            m = y.mean(1, keepdims=True)
+            y = ((y - m) / np.sqrt(((y - m) ** 2).mean(1, keepdims=True) + 64e-5)).reshape(-1) * lnx_w + lnx_b
+            y = y + ((r[t].reshape(H, N) * kt * r_k.reshape(H, N)).sum(1, keepdims=True) * vt.reshape(H, N)).reshape(-1)
+            ys.append(y * g[t])
+        got_y, got_s = orc.wkv7(r, k, v, w, a, g, k_k, k_a, r_k, lnx_w, lnx_b, S0, vgate=vgate if gate else None, vfirst=vfirst if gate else None)
+        assert np.abs(got_y - np.stack(ys)).max() < 2e-5 * max(1.0, float(np.abs(np.stack(ys)).max()))
+        assert np.abs(got_s - S).max() < 2e-5 * max(1.0, float(np.abs(S).max()))
+
+
+def test_mean_hidden_matches_numpy_restatement(tiny_paths):
+    from rwkv7_numpy import Rwkv7Numpy
+    toks = config1_tokens()[:9]
+    m = orc.OracleModel(tiny_paths["int8"])
+    got = m.mean_hidden(toks)
+    ref = Rwkv7Numpy(tiny_paths["int8"], np.float64)
+    st = ref.new_state()
+    acc = np.zeros(ref.C)
+    for t in toks:
+        ref.forward_token(st, int(t))
+        acc += ref.last_hidden
+    want = acc / len(toks)
+    assert got.shape == want.shape and np.abs(got - want).max() < 1e-5 * max(1.0, float(np.abs(want).max()))
+    # it starts from a zero state whatever the oracle held before, and leaves the prompt's state behind
+    m.forward([1, 2, 3])
+    assert np.array_equal(m.mean_hidden(toks), got)
+    m.close()

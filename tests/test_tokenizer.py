@@ -74,3 +74,10 @@ def test_errors():
     for bad in ("not json", "[1, 2]", json.dumps({"x": "a"}), json.dumps({"1": [300]})):
         with pytest.raises(TokenizerError, match="failed to parse vocabulary"):
             Tokenizer(bad)
+
+
+def test_text_driver_refuses_a_prompt_without_a_vocabulary_before_touching_the_gpu():
+    # examples/generate.rs:49 "PROMPT requires VOCAB_JSON": the check comes before the model is loaded, so it runs anywhere
+    from rwkv_rsv_b200 import generate as gen
+    with pytest.raises(SystemExit):
+        gen.main(["--model", "no_such_model.st", "--prompt", "hello"])
