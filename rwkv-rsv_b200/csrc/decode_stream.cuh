@@ -499,6 +499,40 @@ __host__ __device__ inline bool ds_build_plan(DsPlan& pl, const DsEntry* ents, c
     return fits;
 }
 
+// The multiply loop of a chunk whose rows carry a (scale, zero) per group of 128 weights (a function of its own so that its
+// registers do not weigh on the other formats' loop): per group two 64-byte steps into fresh integer accumulators, then the
+// four digit sums weighted by their powers of 256 in fp32 (exact), times the group's scale, plus zero x the group's activation
+// sum.  Returns this lane's contributions to rows g and g + 8 (lanes t = 0, 1 hold two digits each; t = 0 also the zero terms).
+__device__ __noinline__ float2 ds_multiply_grouped(uint32_t aaddr, uint32_t baddr, int bstep, bool bcol_ok, int ngp, uint32_t sz_s, const float* tgp, int t) {
+    const float w_lo = t < 2 ? (t == 0 ? 1.0f : 65536.0f) : 0.f, w_hi = w_lo * 256.0f;
+    float acc0 = 0.f, acc1 = 0.f;
+    for (int gi = 0; gi < ngp; ++gi) {
+        int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+            const uint4 a0 = ds_ldmatrix4(aaddr), a1 = ds_ldmatrix4(aaddr + 32);
+            uint4 b = make_uint4(0, 0, 0, 0);
+            if (bcol_ok) b = ds_lds128(baddr);
+            ds_mma_i8(c0, a0, b.x, b.y);
+            ds_mma_i8(c1, a1, b.z, b.w);
+            aaddr += 64;
+            baddr += bstep;
+        }
+        const uint32_t za = ds_lds32(sz_s + (uint32_t)gi * 64u), zb = ds_lds32(sz_s + (uint32_t)gi * 64u + 32u);
+        const float2 fa = ds_half2_bits_to_float2(za), fb = ds_half2_bits_to_float2(zb);  // (scale, zero) of rows g and g + 8
+        const float qa = fmaf((float)(c0[1] + c1[1]), w_hi, (float)(c0[0] + c1[0]) * w_lo);
+        const float qb = fmaf((float)(c0[3] + c1[3]), w_hi, (float)(c0[2] + c1[2]) * w_lo);
+        acc0 = fmaf(fa.x, qa, acc0);
+        acc1 = fmaf(fb.x, qb, acc1);
+        if (t == 0) {
+            const float tgv = tgp[gi];
+            acc0 = fmaf(fa.y, tgv, acc0);
+            acc1 = fmaf(fb.y, tgv, acc1);
+        }
+    }
+    return make_float2(acc0, acc1);
+}
+
 // The weight rows of one phase: its chunks are J, J + 1, ..., J + n - 1 of the launch (matrix after matrix, tile after tile
 // of 16 rows, piece after piece of <= 1280 bytes of K: the producer's order), and chunk j belongs to consumer warp j mod 16,
 // so the pieces of a long row are multiplied by different warps at the same time.  A warp leaves the partial sums of its
@@ -542,34 +576,8 @@ __device__ __noinline__ bool ds_consume(const DsParams& P, DsShared* S, const Ds
             // digits' powers of 256 in fp32 (exact: |sum| < 2^23, power-of-two weights), multiplied by the group's scale and
             // accumulated in fp32 together with zero x (sum of the group's activations).
             const uint32_t sz_s = ring_s + (uint32_t)ring_off + (uint32_t)(nr * stride) + (uint32_t)g * 4u;  // [group][16 rows] words behind the rows
-            const float* tgp = S->tg[E.xvec] + piece * (steps >> 1);
-            const float w_lo = t < 2 ? (t == 0 ? 1.0f : 65536.0f) : 0.f, w_hi = w_lo * 256.0f;
-            float acc0 = 0.f, acc1 = 0.f;
-            const int ngp = steps >> 1;
-            for (int gi = 0; gi < ngp; ++gi) {
-                int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
-#pragma unroll
-                for (int h2 = 0; h2 < 2; ++h2) {
-                    const uint4 a0 = ds_ldmatrix4(aaddr), a1 = ds_ldmatrix4(aaddr + 32);
-                    uint4 b = make_uint4(0, 0, 0, 0);
-                    if (bcol_ok) b = ds_lds128(baddr);
-                    ds_mma_i8(c0, a0, b.x, b.y);
-                    ds_mma_i8(c1, a1, b.z, b.w);
-                    aaddr += 64;
-                    baddr += bstep;
-                }
-                const uint32_t za = ds_lds32(sz_s + (uint32_t)gi * 64u), zb = ds_lds32(sz_s + (uint32_t)gi * 64u + 32u);
-                const float2 fa = ds_half2_bits_to_float2(za), fb = ds_half2_bits_to_float2(zb);  // (scale, zero) of rows g and g + 8
-                const float qa = fmaf((float)(c0[1] + c1[1]), w_hi, (float)(c0[0] + c1[0]) * w_lo);
-                const float qb = fmaf((float)(c0[3] + c1[3]), w_hi, (float)(c0[2] + c1[2]) * w_lo);
-                acc0 = fmaf(fa.x, qa, acc0);
-                acc1 = fmaf(fb.x, qb, acc1);
-                if (t == 0) {
-                    const float tgv = tgp[gi];
-                    acc0 = fmaf(fa.y, tgv, acc0);
-                    acc1 = fmaf(fb.y, tgv, acc1);
-                }
-            }
+            const float2 acc = ds_multiply_grouped(aaddr, baddr, bstep, bcol_ok, steps >> 1, sz_s, S->tg[E.xvec] + piece * (steps >> 1), t);
+            float acc0 = acc.x, acc1 = acc.y;
             acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
             acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
             if (t == 0) {
